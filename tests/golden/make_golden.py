@@ -1,0 +1,208 @@
+"""Generate the golden vectors under tests/golden/ by running the UNMODIFIED fairchem reference.
+
+Run once on a machine that has the reference checkout (default /root/reference, override with
+FAIRCHEM_REF_ROOT):
+
+    python tests/golden/make_golden.py
+
+The reference is imported in place through ``oracle/ref_shim.py``; weights come from
+``fairchem_b200.weights.random_init_state_dict(seed)`` loaded into the reference module, so the
+fixtures hold only seeds, inputs that are cheap to regenerate, and the reference's outputs.
+Per-edge roll angle gamma is pinned to 0 (the reference draws it at random; outputs are
+gamma-invariant up to ~2e-7 relative).
+"""
+
+from __future__ import annotations
+
+import os
+import sys
+
+import numpy as np
+import torch
+
+ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+sys.path.insert(0, ROOT)
+
+from fairchem_b200 import synthetic, weights  # noqa: E402
+from oracle import ref_shim  # noqa: E402
+from oracle.radius_graph_oracle import sort_edges  # noqa: E402
+
+OUT = os.path.dirname(os.path.abspath(__file__))
+
+
+def ref_model(seed):
+    bb, head = ref_shim.build_reference_model(seed)
+    sd = weights.random_init_state_dict(weights.UMA_S, seed)
+    bsd, hsd = weights.split_head(sd)
+    missing, unexpected = bb.load_state_dict(bsd, strict=False)
+    assert not unexpected, unexpected
+    assert all(k.startswith("Jd_") for k in missing), missing
+    head.energy_block.load_state_dict(hsd)
+    return bb, head
+
+
+def ref_graph(data, cutoff, max_neighbors, node_partition=None):
+    ref_shim.load()
+    from fairchem.core.graph.compute import generate_graph
+
+    d = data.clone()
+    g = generate_graph(d, cutoff=cutoff, max_neighbors=max_neighbors, enforce_max_neighbors_strictly=False,
+                       radius_pbc_version=2, pbc=d.pbc, node_partition=node_partition)
+    ei = g["edge_index"].numpy()
+    co = g["cell_offsets"].numpy().astype(np.int64)
+    p = sort_edges(ei, co)
+    return ei[:, p].astype(np.int32), co[p].astype(np.int8), g["neighbors"].numpy().astype(np.int64), \
+        g["edge_distance_vec"].numpy()[p]
+
+
+def fcc_primitive(pbc):
+    b = 3.58 / 2
+    cell = np.array([[0, b, b], [b, 0, b], [b, b, 0]], dtype=np.float32)
+    return synthetic._pack(np.zeros((1, 3), np.float32), [29], cell[None], [pbc], [1], "omat", 0, 0)
+
+
+def triclinic(seed=3, n=60):
+    rng = np.random.default_rng(seed)
+    cell = np.array([[7.1, 0.3, -0.4], [1.9, 6.2, 0.5], [-0.8, 1.1, 8.3]])
+    frac = rng.uniform(0, 1, (n, 3))
+    pos = (frac @ cell).astype(np.float32)
+    return synthetic._pack(pos, rng.choice([1, 6, 8, 29], n), cell[None], [[True, True, True]], [n], "omat", 0, 0)
+
+
+def mixed_batch(seed=5):
+    a = synthetic.fcc_cu((2, 2, 2), seed=seed)
+    b = synthetic.molecule_batch(2, seed=seed)
+    c = triclinic(seed)
+    c["pbc"] = torch.tensor([[True, True, False]])
+    parts = [a, b, c]
+    out = synthetic.AtomicDataLike()
+    for k in ("pos", "atomic_numbers", "cell", "pbc", "natoms", "charge", "spin"):
+        out[k] = torch.cat([p[k] for p in parts])
+    out["dataset"] = sum((p["dataset"] for p in parts), [])
+    out["batch"] = torch.repeat_interleave(torch.arange(len(out["natoms"])), out["natoms"])
+    return out
+
+
+def make_graph_golden():
+    out = {}
+    # known answers of tests/core/graph/test_radius_graph.py:117-258 (fcc Cu a=3.58, one atom)
+    for name, pbc, cases in (("fcc1d", [True, False, False], ((10, 4), (1, 2))),
+                             ("fcc2d", [True, True, False], ((20, 18), (2, 6))),
+                             ("fcc3d", [True, True, True], ((100, 78), (10, 12)))):
+        d = fcc_primitive(pbc)
+        for k, expect in cases:
+            ei, co, nb, _ = ref_graph(d, 6.0, k)
+            assert int(nb[0]) == expect, (name, k, nb, expect)
+            out[f"{name}_k{k}_edge_index"], out[f"{name}_k{k}_offsets"] = ei, co
+            out[f"{name}_k{k}_neighbors"] = nb
+    cases = {
+        "fcc_cu_256": (synthetic.fcc_cu((4, 4, 4), seed=0), 6.0, 30),
+        "molecules_64": (synthetic.molecule_batch(64, seed=0), 6.0, 30),
+        "bcc_alloy_2000": (synthetic.bcc_alloy((10, 10, 10), seed=0), 6.0, 30),
+        "triclinic_60": (triclinic(), 6.0, 30),
+        "triclinic_60_r12": (triclinic(), 12.0, 10000),
+        "triclinic_60_r1": (triclinic(), 1.0, 1),
+        "mixed_batch": (mixed_batch(), 6.0, 30),
+        "water_600": (synthetic.water_box(600, seed=0), 6.0, 30),
+        "water_600_k300": (synthetic.water_box(600, seed=0), 6.0, 300),
+    }
+    for name, (d, r, k) in cases.items():
+        ei, co, nb, vec = ref_graph(d, r, k)
+        out[f"{name}_edge_index"], out[f"{name}_offsets"], out[f"{name}_neighbors"] = ei, co, nb
+        print(name, "N", len(d.pos), "E", ei.shape[1])
+    # partitioned targets (radius_graph_pbc.py:509-515): every third atom of the alloy
+    d = synthetic.bcc_alloy((4, 4, 4), seed=1)
+    part = torch.arange(0, len(d.pos), 3)
+    ei, co, nb, _ = ref_graph(d, 6.0, 30, node_partition=part)
+    out["bcc_128_partition_edge_index"], out["bcc_128_partition_offsets"] = ei, co
+    out["bcc_128_partition_neighbors"] = nb
+    # inputs that are not produced by fairchem_b200.synthetic
+    for name, d in (("triclinic_60", triclinic()), ("mixed_batch", mixed_batch())):
+        for k in ("pos", "atomic_numbers", "cell", "pbc", "natoms"):
+            out[f"{name}_in_{k}"] = d[k].numpy()
+    np.savez_compressed(os.path.join(OUT, "radius_graph.npz"), **out)
+
+
+def make_wigner_golden():
+    ref_shim.load()
+    from fairchem.core.models.uma.common.quaternion.wigner_d_hybrid import axis_angle_wigner_hybrid
+
+    bb, _ = ref_shim.build_reference_model(0)
+    rng = np.random.default_rng(11)
+    v = rng.normal(size=(48, 3))
+    special = np.array([[0, 1, 0], [0, -1, 0], [1e-4, 1, 0], [0, -1, 1e-4], [1, 0, 0], [0, 0, 1], [0.3, -0.9, 0.2],
+                        [0.3, 0.9, -0.2], [0.1, -0.95, 0.05], [0.43, -0.898, 0.1], [0.43, 0.902, 0.1],
+                        [1e-3, -1, 1e-3], [2.5, 0.1, -3.0], [-1.2, -0.05, 0.7], [0, 0.5, 0.5], [5.9, 0.1, 0.2]])
+    vec = torch.tensor(np.concatenate([v * rng.uniform(0.8, 5.9, (48, 1)), special]), dtype=torch.float32)
+    out = {"vec": vec.numpy()}
+    for gname, gamma in (("g0", torch.zeros(len(vec))), ("g1", torch.linspace(0.1, 6.0, len(vec)))):
+        x = vec.clone().requires_grad_(True)
+        d, dinv = axis_angle_wigner_hybrid(x, 2, gamma=gamma, coeffs=bb.wigner_data.coeffs,
+                                           U_blocks=bb.wigner_data.U_blocks, custom_kernels=bb.wigner_data.custom_kernels)
+        wgt = torch.tensor(rng.normal(size=(len(vec), 9, 9)), dtype=torch.float32)
+        (g,) = torch.autograd.grad((d * wgt).sum(), x)
+        out[f"{gname}_gamma"] = gamma.numpy()
+        out[f"{gname}_wigner"] = d.detach().numpy()
+        out[f"{gname}_cotangent"] = wgt.numpy()
+        out[f"{gname}_grad_vec"] = g.numpy()
+    np.savez_compressed(os.path.join(OUT, "wigner.npz"), **out)
+
+
+def make_backend_op_golden():
+    """The reference's general-backend rotate/gather/scatter ops on seeded random tensors
+    (execution_backends.py:121-263); N=12 nodes, E=40 edges, C=128, lmax=mmax=2."""
+    ref_shim.load()
+    from fairchem.core.models.uma.common.so3 import CoefficientMapping
+    from fairchem.core.models.uma.nn.execution_backends import ExecutionBackend
+
+    g = torch.Generator().manual_seed(7)
+    n, e, c = 12, 40, 128
+    x = torch.randn(n, 9, c, generator=g)
+    edge_index = torch.stack([torch.randint(0, n, (e,), generator=g), torch.sort(torch.randint(0, n, (e,), generator=g))[0]])
+    vec = torch.randn(e, 3, generator=g)
+    from oracle.escn_md_oracle import edge_quaternion, wigner_blocks
+
+    d = wigner_blocks(edge_quaternion(vec), 2)
+    env = torch.rand(e, 1, 1, generator=g)
+    mapping = CoefficientMapping(2, 2)
+    w, winv = ExecutionBackend.prepare_wigner(d, d.transpose(1, 2).contiguous() * env, mapping, None)
+    msg = ExecutionBackend.node_to_edge_wigner_permute(x, edge_index, w)
+    y = torch.randn(e, 9, c, generator=g)
+    back = ExecutionBackend.permute_wigner_inv_edge_to_node(y, winv, edge_index[1], n)
+    rad = torch.randn(e, 3 * c, generator=g)
+    deg = ExecutionBackend.edge_degree_scatter(x, rad, winv, edge_index[1], 3, c, 5.0)
+    np.savez_compressed(os.path.join(OUT, "backend_ops.npz"), x=x.numpy(), edge_index=edge_index.numpy(),
+                        wigner=d.numpy(), env=env.view(-1).numpy(), msg=msg.numpy(), y=y.numpy(), back=back.numpy(),
+                        rad=rad.numpy(), deg=deg.numpy())
+
+
+def make_model_golden():
+    bb, head = ref_model(0)
+    cases = {
+        "fcc_cu_32": synthetic.fcc_cu((2, 2, 2), seed=0),
+        "fcc_cu_256": synthetic.fcc_cu((4, 4, 4), seed=0),
+        "molecules_64": synthetic.molecule_batch(64, seed=0),
+        "bcc_alloy_2000": synthetic.bcc_alloy((10, 10, 10), seed=0),
+        "water_600": synthetic.water_box(600, seed=0),
+    }
+    out = {}
+    torch.set_num_threads(os.cpu_count() or 8)
+    for name, d in cases.items():
+        e, f, _ = ref_shim.run_reference(bb, head, d, gamma=0.0)
+        out[f"{name}_energy"] = e.numpy()
+        out[f"{name}_forces"] = f.numpy()
+        print(name, "E", e.numpy()[:3], "max|F|", f.abs().max().item())
+    out["weights_seed"] = np.array(0)
+    np.savez_compressed(os.path.join(OUT, "uma_s_energy_forces.npz"), **out)
+
+
+if __name__ == "__main__":
+    which = sys.argv[1:] or ["graph", "wigner", "ops", "model"]
+    if "graph" in which:
+        make_graph_golden()
+    if "wigner" in which:
+        make_wigner_golden()
+    if "ops" in which:
+        make_backend_op_golden()
+    if "model" in which:
+        make_model_golden()

@@ -1,0 +1,100 @@
+"""Pins the CPU oracle to vectors produced by the unmodified fairchem reference."""
+
+import numpy as np
+import pytest
+import torch
+
+from fairchem_b200 import synthetic, weights
+from oracle import escn_md_oracle as O
+from oracle import radius_graph_oracle as G
+
+
+def _data_from_golden(g, name):
+    pos = g[f"{name}_in_pos"]
+    natoms = g[f"{name}_in_natoms"]
+    return synthetic._pack(pos, g[f"{name}_in_atomic_numbers"], g[f"{name}_in_cell"], g[f"{name}_in_pbc"], natoms,
+                           "omat", 0, 0)
+
+
+GRAPH_CASES = {
+    "fcc_cu_256": (lambda g: synthetic.fcc_cu((4, 4, 4), seed=0), 6.0, 30),
+    "molecules_64": (lambda g: synthetic.molecule_batch(64, seed=0), 6.0, 30),
+    "bcc_alloy_2000": (lambda g: synthetic.bcc_alloy((10, 10, 10), seed=0), 6.0, 30),
+    "triclinic_60": (lambda g: _data_from_golden(g, "triclinic_60"), 6.0, 30),
+    "triclinic_60_r12": (lambda g: _data_from_golden(g, "triclinic_60"), 12.0, 10000),
+    "triclinic_60_r1": (lambda g: _data_from_golden(g, "triclinic_60"), 1.0, 1),
+    "mixed_batch": (lambda g: _data_from_golden(g, "mixed_batch"), 6.0, 30),
+    "water_600": (lambda g: synthetic.water_box(600, seed=0), 6.0, 30),
+    "water_600_k300": (lambda g: synthetic.water_box(600, seed=0), 6.0, 300),
+}
+
+
+def fcc_primitive(pbc):
+    b = 3.58 / 2
+    cell = np.array([[0, b, b], [b, 0, b], [b, b, 0]], dtype=np.float32)
+    return synthetic._pack(np.zeros((1, 3), np.float32), [29], cell[None], [pbc], [1], "omat", 0, 0)
+
+
+@pytest.mark.parametrize("name", sorted(GRAPH_CASES))
+def test_radius_graph_oracle_matches_reference_edge_set(golden, name):
+    g = golden("radius_graph.npz")
+    make, r, k = GRAPH_CASES[name]
+    d = make(g)
+    ei, co, _, nb = G.radius_graph(d.pos.numpy(), d.cell.numpy(), d.pbc.numpy(), d.natoms.numpy(), r, k)
+    assert np.array_equal(ei, g[f"{name}_edge_index"].astype(np.int64))
+    assert np.array_equal(co, g[f"{name}_offsets"].astype(np.int64))
+    assert np.array_equal(nb, g[f"{name}_neighbors"])
+
+
+@pytest.mark.parametrize("name,pbc,k,expect", [
+    ("fcc1d", [True, False, False], 10, 4), ("fcc1d", [True, False, False], 1, 2),
+    ("fcc2d", [True, True, False], 20, 18), ("fcc2d", [True, True, False], 2, 6),
+    ("fcc3d", [True, True, True], 100, 78), ("fcc3d", [True, True, True], 10, 12)])
+def test_radius_graph_oracle_known_neighbor_counts(golden, name, pbc, k, expect):
+    # counts asserted by the reference's tests/core/graph/test_radius_graph.py:117-258
+    g = golden("radius_graph.npz")
+    d = fcc_primitive(pbc)
+    ei, co, _, nb = G.radius_graph(d.pos.numpy(), d.cell.numpy(), d.pbc.numpy(), d.natoms.numpy(), 6.0, k)
+    assert int(nb[0]) == expect
+    assert np.array_equal(ei, g[f"{name}_k{k}_edge_index"].astype(np.int64))
+    assert np.array_equal(co, g[f"{name}_k{k}_offsets"].astype(np.int64))
+
+
+def test_radius_graph_oracle_partitioned_targets(golden):
+    g = golden("radius_graph.npz")
+    d = synthetic.bcc_alloy((4, 4, 4), seed=1)
+    part = np.arange(0, len(d.pos), 3)
+    ei, co, _, nb = G.radius_graph(d.pos.numpy(), d.cell.numpy(), d.pbc.numpy(), d.natoms.numpy(), 6.0, 30, part)
+    assert np.array_equal(ei, g["bcc_128_partition_edge_index"].astype(np.int64))
+    assert np.array_equal(co, g["bcc_128_partition_offsets"].astype(np.int64))
+
+
+@pytest.mark.parametrize("gname", ["g0", "g1"])
+def test_wigner_oracle_matches_reference(golden, gname):
+    g = golden("wigner.npz")
+    vec = torch.tensor(g["vec"]).requires_grad_(True)
+    d = O.wigner_blocks(O.edge_quaternion(vec, torch.tensor(g[f"{gname}_gamma"])), 2)
+    assert torch.allclose(d.detach(), torch.tensor(g[f"{gname}_wigner"]), atol=2e-6, rtol=0)
+    (grad,) = torch.autograd.grad((d * torch.tensor(g[f"{gname}_cotangent"])).sum(), vec)
+    ref = torch.tensor(g[f"{gname}_grad_vec"])
+    assert torch.allclose(grad, ref, atol=2e-4 * ref.abs().max().item(), rtol=1e-4)
+
+
+MODEL_CASES = {
+    "fcc_cu_32": lambda: synthetic.fcc_cu((2, 2, 2), seed=0),
+    "fcc_cu_256": lambda: synthetic.fcc_cu((4, 4, 4), seed=0),
+    "water_600": lambda: synthetic.water_box(600, seed=0),
+}
+
+
+@pytest.mark.parametrize("name", sorted(MODEL_CASES))
+def test_energy_forces_oracle_matches_reference(golden, name):
+    g = golden("uma_s_energy_forces.npz")
+    d = MODEL_CASES[name]()
+    sd = weights.random_init_state_dict(weights.UMA_S, int(g["weights_seed"]))
+    ei, co, _, _ = G.radius_graph(d.pos.numpy(), d.cell.numpy(), d.pbc.numpy(), d.natoms.numpy(), 6.0, 30)
+    torch.set_num_threads(8)
+    e, f = O.energy_and_forces(sd, weights.UMA_S, d, torch.from_numpy(ei), torch.from_numpy(co))
+    e_ref, f_ref = g[f"{name}_energy"], g[f"{name}_forces"]
+    assert np.max(np.abs(e.numpy() - e_ref) / np.abs(e_ref)) < 2e-6
+    assert np.max(np.abs(f.numpy() - f_ref)) < 5e-6
