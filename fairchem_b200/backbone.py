@@ -1,0 +1,607 @@
+"""eSCN-MD (UMA) backbone and energy/force head on the B200 edge-block kernels.
+
+``eSCNMDBackboneB200`` mirrors the constructor keywords, ``forward(data) -> {"node_embedding",
+"batch"}`` contract, attributes and ``state_dict`` keys of fairchem's ``eSCNMDBackbone``
+(src/fairchem/core/models/uma/escn_md.py:280-905) for the configuration the UMA models use
+(``norm_type="rms_norm_sh"``, ``act_type="gate"``, ``ff_type="spectral"``,
+``chg_spin_emb_type="rand_emb"``, lmax = mmax = 2), and ``MLP_EFS_HeadB200`` mirrors
+``MLP_EFS_Head`` (escn_md.py:1062-1168).  Reference weights load unchanged.
+
+What differs from the reference is how the edge block runs.  Edges are CSR-sorted by target and
+cut into chunks on target boundaries; a chunk runs gather+rotate+radial-scale -> SO(2) GEMMs ->
+gate -> SO(2) GEMMs -> rotate-back + segmented reduce with the chunk's [E_c, *] intermediates
+living only inside the chunk.  The backward pass recomputes a chunk before differentiating it
+(the role ``activation_checkpointing`` plays in escn_md_block.py:157-202), so memory is
+O(nodes) + O(chunk) instead of O(edges * layers), which is what lets a 100k-atom system run on
+one GPU.  The first radial Linear is split into a distance part (a [E,64] GEMM) and two
+per-element tables (``embedding @ W^T``), which removes the [E,320] edge-feature tensor.
+"""
+
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from . import ops
+from .graph import generate_graph, get_pbc_shifts
+from .ops import EdgeGraph
+
+# compact-Wigner index of the transposed entry, and of the m=0 column entries
+_L_OF = [0, 1, 1, 1, 2, 2, 2, 2, 2]
+
+
+def _compact_index(row: int, col: int) -> int:
+    l = _L_OF[row]
+    off = (0, 1, 10)[l]
+    return off + (row - l * l) * (2 * l + 1) + (col - l * l)
+
+
+def _transpose_index() -> list[int]:
+    idx = [0] * ops.WIG
+    for row in range(9):
+        for col in range(9):
+            if _L_OF[row] == _L_OF[col]:
+                idx[_compact_index(row, col)] = _compact_index(col, row)
+    return idx
+
+
+def dense_to_compact_index() -> list[int]:
+    """Flat index into a dense [9,9] matrix of each compact Wigner entry."""
+    flat = [0] * ops.WIG
+    for row in range(9):
+        for col in range(9):
+            if _L_OF[row] == _L_OF[col]:
+                flat[_compact_index(row, col)] = row * 9 + col
+    return flat
+
+
+# ------------------------------------------------------------------------------------------
+# parameter containers with the reference's names
+# ------------------------------------------------------------------------------------------
+
+
+class RadialMLP(nn.Module):
+    """Linear-LayerNorm-SiLU-Linear-LayerNorm-SiLU-Linear (src/fairchem/core/models/uma/nn/radial.py:61-86)."""
+
+    def __init__(self, widths):
+        super().__init__()
+        mods = []
+        for i in range(1, len(widths)):
+            mods.append(nn.Linear(widths[i - 1], widths[i]))
+            if i != len(widths) - 1:
+                mods += [nn.LayerNorm(widths[i]), nn.SiLU()]
+        self.net = nn.Sequential(*mods)
+
+    def forward(self, x):
+        return self.net(x)
+
+
+class _SO2mConv(nn.Module):
+    def __init__(self, k_in, n_out):
+        super().__init__()
+        self.fc = nn.Linear(k_in, n_out, bias=False)
+        self.fc.weight.data.mul_(1 / math.sqrt(2))
+
+
+class SO2Convolution(nn.Module):
+    """Weights of one SO(2) convolution (src/fairchem/core/models/uma/nn/so2_layers.py:519-598)."""
+
+    def __init__(self, c_in, c_out, lmax, mmax, radial_widths=None, extra_m0=0):
+        super().__init__()
+        k0 = (lmax + 1) * c_in
+        self.fc_m0 = nn.Linear(k0, (lmax + 1) * c_out + extra_m0)
+        self.so2_m_conv = nn.ModuleList()
+        n_rad = k0
+        for m in range(1, mmax + 1):
+            km = (lmax - m + 1) * c_in
+            self.so2_m_conv.append(_SO2mConv(km, 2 * (lmax - m + 1) * c_out))
+            n_rad += km
+        self.rad_func = RadialMLP(list(radial_widths) + [n_rad]) if radial_widths is not None else None
+
+
+class Edgewise(nn.Module):
+    def __init__(self, c, h, lmax, mmax, edge_widths):
+        super().__init__()
+        self.so2_conv_1 = SO2Convolution(2 * c, h, lmax, mmax, edge_widths, extra_m0=lmax * h)
+        self.so2_conv_2 = SO2Convolution(h, c, lmax, mmax, None, 0)
+
+
+class SO3Linear(nn.Module):
+    """Per-degree linear map (src/fairchem/core/models/uma/nn/so3_layers.py:15-52)."""
+
+    def __init__(self, c_in, c_out, lmax):
+        super().__init__()
+        bound = 1 / math.sqrt(c_in)
+        self.weight = nn.Parameter(torch.empty(lmax + 1, c_out, c_in).uniform_(-bound, bound))
+        self.bias = nn.Parameter(torch.zeros(c_out))
+        self.lmax = lmax
+
+    def forward(self, x):  # x [N,(lmax+1)^2,Cin]
+        outs = []
+        for l in range(self.lmax + 1):
+            y = torch.matmul(x[:, l * l:(l + 1) * (l + 1)], self.weight[l].t())
+            if l == 0:
+                y = y + self.bias
+            outs.append(y)
+        return torch.cat(outs, dim=1)
+
+
+class SpectralAtomwise(nn.Module):
+    """Gated per-degree feed-forward (src/fairchem/core/models/uma/escn_md_block.py:288-328)."""
+
+    def __init__(self, c, h, lmax):
+        super().__init__()
+        self.scalar_mlp = nn.Sequential(nn.Linear(c, lmax * h), nn.SiLU())
+        self.so3_linear_1 = SO3Linear(c, h, lmax)
+        self.so3_linear_2 = SO3Linear(h, c, lmax)
+        self.lmax, self.h = lmax, h
+
+    def forward(self, x):
+        gates = torch.sigmoid(self.scalar_mlp(x[:, 0])).view(x.shape[0], self.lmax, self.h)
+        y = self.so3_linear_1(x)
+        parts = [F.silu(y[:, :1])]
+        for l in range(1, self.lmax + 1):
+            parts.append(y[:, l * l:(l + 1) * (l + 1)] * gates[:, l - 1:l])
+        return self.so3_linear_2(torch.cat(parts, dim=1))
+
+
+class RMSNormSH(nn.Module):
+    """Degree-balanced RMS norm (src/fairchem/core/models/uma/nn/layer_norm.py:308-419)."""
+
+    def __init__(self, lmax, c, eps=1e-5):
+        super().__init__()
+        self.affine_weight = nn.Parameter(torch.ones(lmax + 1, c))
+        self.affine_bias = nn.Parameter(torch.zeros(c))
+        self.lmax, self.eps = lmax, eps
+        l_of = [l for l in range(lmax + 1) for _ in range(2 * l + 1)]
+        self.register_buffer("l_index", torch.tensor(l_of), persistent=False)
+        self.register_buffer("balance", torch.tensor([1.0 / ((2 * l + 1) * (lmax + 1)) for l in l_of]).view(1, -1, 1),
+                             persistent=False)
+
+    def forward(self, x):
+        x0 = x[:, :1] - x[:, :1].mean(dim=2, keepdim=True)
+        feat = torch.cat([x0, x[:, 1:]], dim=1)
+        nrm = (feat.square() * self.balance).sum(dim=1, keepdim=True).mean(dim=2, keepdim=True)
+        out = feat * ((nrm + self.eps).rsqrt() * self.affine_weight[self.l_index].unsqueeze(0))
+        return torch.cat([out[:, :1] + self.affine_bias, out[:, 1:]], dim=1)
+
+
+class _Block(nn.Module):
+    def __init__(self, c, h, lmax, mmax, edge_widths):
+        super().__init__()
+        self.norm_1 = RMSNormSH(lmax, c)
+        self.edge_wise = Edgewise(c, h, lmax, mmax, edge_widths)
+        self.norm_2 = RMSNormSH(lmax, c)
+        self.atom_wise = SpectralAtomwise(c, h, lmax)
+
+
+class _RandEmb(nn.Module):
+    def __init__(self, num, c, offset):
+        super().__init__()
+        self.rand_emb = nn.Embedding(num, c)
+        self.offset = offset
+
+    def forward(self, v):
+        return self.rand_emb(v.long() + self.offset)
+
+
+class _DatasetEmbedding(nn.Module):
+    def __init__(self, c, mapping):
+        super().__init__()
+        self.mapping = dict(mapping)
+        self.dataset_emb_dict = nn.ModuleDict({name: nn.Embedding(1, c) for name in sorted(set(mapping.values()))})
+
+    def forward(self, names):
+        return torch.stack([self.dataset_emb_dict[self.mapping[n]].weight[0] for n in names], dim=0)
+
+
+class _EdgeDegreeEmbedding(nn.Module):
+    def __init__(self, widths):
+        super().__init__()
+        self.rad_func = RadialMLP(widths)
+
+
+# ------------------------------------------------------------------------------------------
+# chunk plan
+# ------------------------------------------------------------------------------------------
+
+
+@dataclass
+class _Chunk:
+    e0: int
+    e1: int
+    n0: int
+    n1: int
+    row_ptr: torch.Tensor      # [n1-n0+1] int32, relative to e0
+    src_nodes: torch.Tensor    # [U] int32 distinct source nodes of the chunk
+    src_ptr: torch.Tensor      # [U+1] int32 into src_perm
+    src_perm: torch.Tensor     # [e1-e0] int32 chunk-local edge ids grouped by source
+
+
+def build_chunks(graph: EdgeGraph, chunk_edges: int) -> list[_Chunk]:
+    """Cut the CSR edge list into chunks of about ``chunk_edges`` edges on target boundaries."""
+    e, nt = graph.num_edges, graph.num_targets
+    dev = graph.src.device
+    if e == 0:
+        return []
+    nchunk = max(1, (e + chunk_edges - 1) // chunk_edges)
+    starts = torch.arange(0, nchunk, device=dev, dtype=torch.int32) * chunk_edges
+    node_lo = torch.searchsorted(graph.row_ptr, starts, right=False).clamp(max=nt)
+    node_bounds = sorted(set([0] + node_lo.tolist()[1:] + [nt]))
+    rp = graph.row_ptr
+    edge_bounds = rp[torch.tensor(node_bounds, device=dev)].tolist()
+    chunk_of_edge = torch.bucketize(torch.arange(e, device=dev), torch.tensor(edge_bounds[1:], device=dev), right=True)
+    key = chunk_of_edge * graph.num_nodes + graph.src.long()
+    skey, order = torch.sort(key, stable=True)
+    uniq, counts = torch.unique_consecutive(skey, return_counts=True)
+    uptr = torch.zeros(uniq.shape[0] + 1, dtype=torch.int64, device=dev)
+    uptr[1:] = torch.cumsum(counts, 0)
+    ub = torch.searchsorted(uniq, torch.arange(len(node_bounds), device=dev) * graph.num_nodes).tolist()
+    chunks = []
+    for i in range(len(node_bounds) - 1):
+        n0, n1, e0, e1 = node_bounds[i], node_bounds[i + 1], edge_bounds[i], edge_bounds[i + 1]
+        if e1 == e0:
+            continue
+        u0, u1 = ub[i], ub[i + 1]
+        chunks.append(_Chunk(
+            e0, e1, n0, n1,
+            (rp[n0:n1 + 1] - e0).contiguous(),
+            (uniq[u0:u1] - i * graph.num_nodes).to(torch.int32).contiguous(),
+            (uptr[u0:u1 + 1] - e0).to(torch.int32).contiguous(),
+            (order[e0:e1] - e0).to(torch.int32).contiguous()))
+    return chunks
+
+
+# ------------------------------------------------------------------------------------------
+# the edge block
+# ------------------------------------------------------------------------------------------
+
+
+class _EdgeCtx:
+    """Per-forward edge data shared by all layers."""
+
+    def __init__(self, graph, chunks, wig, winv, gauss, z_src, z_tgt):
+        self.graph, self.chunks = graph, chunks
+        self.wig, self.winv, self.gauss = wig, winv, gauss
+        self.z_src, self.z_tgt = z_src, z_tgt
+
+
+def _linear(x2d, weight, bias=None):
+    return F.linear(x2d, weight, bias)
+
+
+def _radial(rad: RadialMLP, tables, gauss_c, zs, zt, nb: int):
+    """RadialMLP on [gauss | src_emb[z_s] | tgt_emb[z_t]] with the embedding part of the first Linear
+    folded into per-element tables."""
+    w0 = rad.net[0]
+    pre = F.linear(gauss_c, w0.weight[:, :nb], w0.bias) + tables[0][zs] + tables[1][zt]
+    h = F.silu(F.layer_norm(pre, pre.shape[-1:], rad.net[1].weight, rad.net[1].bias, rad.net[1].eps))
+    h = F.silu(F.layer_norm(rad.net[3](h), h.shape[-1:], rad.net[4].weight, rad.net[4].bias, rad.net[4].eps))
+    return rad.net[6](h)
+
+
+def _so2_middle(ew: Edgewise, m0, m1, m2):
+    """conv1 GEMMs -> combine+gate -> conv2 GEMMs -> combine, on the planar operands."""
+    c1, c2 = ew.so2_conv_1, ew.so2_conv_2
+    e = m0.shape[0]
+    y0 = _linear(m0, c1.fc_m0.weight, c1.fc_m0.bias)
+    y1 = _linear(m1.view(2 * e, -1), c1.so2_m_conv[0].fc.weight).view(e, 2, -1)
+    y2 = _linear(m2.view(2 * e, -1), c1.so2_m_conv[1].fc.weight).view(e, 2, -1)
+    a0, a1, a2 = ops.SO2Gate.apply(y0, y1, y2)
+    z0 = _linear(a0, c2.fc_m0.weight, c2.fc_m0.bias)
+    z1 = _linear(a1.view(2 * e, -1), c2.so2_m_conv[0].fc.weight).view(e, 2, -1)
+    z2 = _linear(a2.view(2 * e, -1), c2.so2_m_conv[1].fc.weight).view(e, 2, -1)
+    return ops.SO2Combine.apply(z0, z1, z2)
+
+
+class _EdgeBlockFn(torch.autograd.Function):
+    """One layer's edge block over all chunks; differentiable in x, wig, winv and gauss."""
+
+    @staticmethod
+    def forward(ctx, x, wig, winv, gauss, ew: Edgewise, tables, ectx: _EdgeCtx, nb: int):
+        g = ectx.graph
+        c = x.shape[2]
+        x = x.contiguous()
+        out = torch.zeros(g.num_targets, 9, c, dtype=x.dtype, device=x.device)
+        with torch.no_grad():
+            for ch in ectx.chunks:
+                sl = slice(ch.e0, ch.e1)
+                rad = _radial(ew.so2_conv_1.rad_func, tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb)
+                ec = ch.e1 - ch.e0
+                m0 = torch.empty(ec, 6 * c, dtype=x.dtype, device=x.device)
+                m1 = torch.empty(ec, 2, 4 * c, dtype=x.dtype, device=x.device)
+                m2 = torch.empty(ec, 2, 2 * c, dtype=x.dtype, device=x.device)
+                ops.gather_rotate_fwd_(x, g.src[sl], g.tgt[sl], wig[sl], rad, m0, m1, m2)
+                msg = _so2_middle(ew, m0, m1, m2)
+                ops.rotate_back_reduce_fwd_(msg, winv[sl], ch.row_ptr, out[ch.n0:ch.n1])
+        ctx.save_for_backward(x, wig, winv, gauss)
+        ctx.ew, ctx.tables, ctx.ectx, ctx.nb = ew, tables, ectx, nb
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, wig, winv, gauss = ctx.saved_tensors
+        ew, tables, ectx, nb = ctx.ew, ctx.tables, ctx.ectx, ctx.nb
+        g = ectx.graph
+        c = x.shape[2]
+        grad_out = grad_out.contiguous()
+        gx = torch.zeros_like(x)
+        gwig = torch.empty_like(wig)
+        gwinv = torch.empty_like(winv)
+        ggauss = torch.empty_like(gauss)
+        for ch in ectx.chunks:
+            sl = slice(ch.e0, ch.e1)
+            ec = ch.e1 - ch.e0
+            with torch.enable_grad():
+                g_c = gauss[sl].detach().requires_grad_(True)
+                rad = _radial(ew.so2_conv_1.rad_func, tables, g_c, ectx.z_src[sl], ectx.z_tgt[sl], nb)
+                rad_d = rad.detach()
+                m0 = torch.empty(ec, 6 * c, dtype=x.dtype, device=x.device)
+                m1 = torch.empty(ec, 2, 4 * c, dtype=x.dtype, device=x.device)
+                m2 = torch.empty(ec, 2, 2 * c, dtype=x.dtype, device=x.device)
+                ops.gather_rotate_fwd_(x, g.src[sl], g.tgt[sl], wig[sl], rad_d, m0, m1, m2)
+                m0.requires_grad_(True), m1.requires_grad_(True), m2.requires_grad_(True)
+                msg = _so2_middle(ew, m0, m1, m2)
+            grad_msg = torch.empty_like(msg)
+            ops.rotate_back_bwd_(grad_out, msg.detach(), winv[sl], g.tgt[sl], grad_msg, gwinv[sl])
+            gm0, gm1, gm2 = torch.autograd.grad(msg, (m0, m1, m2), grad_msg)
+            del msg, grad_msg
+            g_src = torch.empty(ec, 9, c, dtype=x.dtype, device=x.device)
+            g_tgt = torch.empty(ec, 9, c, dtype=x.dtype, device=x.device)
+            grad_rad = torch.empty_like(rad_d)
+            ops.gather_rotate_bwd_(gm0.contiguous(), gm1.contiguous(), gm2.contiguous(), x, g.src[sl], g.tgt[sl], wig[sl],
+                                   rad_d, g_src, g_tgt, gwig[sl], grad_rad)
+            del gm0, gm1, gm2, m0, m1, m2
+            # node reductions: target rows of the chunk are contiguous; source rows are the chunk's distinct sources
+            ops.segment_sum(g_tgt, ch.row_ptr, None, ch.n1 - ch.n0, out=gx[ch.n0:ch.n1], accumulate=True)
+            ops.segment_sum(g_src, ch.src_ptr, ch.src_perm, ch.src_nodes.shape[0], out=gx, out_index=ch.src_nodes,
+                            accumulate=True)
+            del g_src, g_tgt
+            (gg,) = torch.autograd.grad(rad, g_c, grad_rad)
+            ggauss[sl] = gg
+            del rad, rad_d, grad_rad, gg
+        return gx, gwig, gwinv, ggauss, None, None, None, None
+
+
+class _EdgeDegreeFn(torch.autograd.Function):
+    """x + segment_sum_tgt(Winv[:, m0 cols] @ RadialMLP(x_edge)) / rescale, chunked with recompute."""
+
+    @staticmethod
+    def forward(ctx, x, winv, gauss, rad_func: RadialMLP, tables, ectx: _EdgeCtx, nb: int, rescale: float):
+        g = ectx.graph
+        c = x.shape[2]
+        x = x.contiguous()
+        out = x.clone()
+        with torch.no_grad():
+            for ch in ectx.chunks:
+                sl = slice(ch.e0, ch.e1)
+                r3 = _radial(rad_func, tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb)
+                ops.edge_degree_fwd_(r3, winv[sl], ch.row_ptr, x[ch.n0:ch.n1], out[ch.n0:ch.n1], rescale)
+        ctx.save_for_backward(winv, gauss)
+        ctx.rad_func, ctx.tables, ctx.ectx, ctx.nb, ctx.rescale, ctx.c = rad_func, tables, ectx, nb, rescale, c
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        winv, gauss = ctx.saved_tensors
+        ectx, nb = ctx.ectx, ctx.nb
+        g = ectx.graph
+        grad_out = grad_out.contiguous()
+        gwinv = torch.empty_like(winv)
+        ggauss = torch.empty_like(gauss)
+        for ch in ectx.chunks:
+            sl = slice(ch.e0, ch.e1)
+            with torch.enable_grad():
+                g_c = gauss[sl].detach().requires_grad_(True)
+                r3 = _radial(ctx.rad_func, ctx.tables, g_c, ectx.z_src[sl], ectx.z_tgt[sl], nb)
+            gr = torch.empty_like(r3)
+            ops.edge_degree_bwd_(grad_out, r3.detach(), winv[sl], g.tgt[sl], gr, gwinv[sl], ctx.rescale)
+            (gg,) = torch.autograd.grad(r3, g_c, gr)
+            ggauss[sl] = gg
+        return grad_out, gwinv, ggauss, None, None, None, None, None
+
+
+# ------------------------------------------------------------------------------------------
+# backbone
+# ------------------------------------------------------------------------------------------
+
+
+class eSCNMDBackboneB200(nn.Module):
+    def __init__(
+        self,
+        max_num_elements: int = 100,
+        sphere_channels: int = 128,
+        lmax: int = 2,
+        mmax: int = 2,
+        otf_graph: bool = True,
+        max_neighbors: int = 300,
+        cutoff: float = 5.0,
+        edge_channels: int = 128,
+        distance_function: str = "gaussian",
+        num_distance_basis: int = 512,
+        direct_forces: bool = False,
+        regress_forces: bool = True,
+        regress_stress: bool = False,
+        num_layers: int = 2,
+        hidden_channels: int = 128,
+        norm_type: str = "rms_norm_sh",
+        act_type: str = "gate",
+        ff_type: str = "spectral",
+        activation_checkpointing: bool = True,
+        chg_spin_emb_type: str = "rand_emb",
+        dataset_mapping: Optional[dict] = None,
+        use_dataset_embedding: bool = True,
+        radius_pbc_version: int = 200,
+        always_use_pbc: bool = False,
+        execution_mode: str = "b200",
+        edge_chunk_size: int = 65536,
+        **unused,
+    ) -> None:
+        super().__init__()
+        if (lmax, mmax) != (2, 2):
+            raise ValueError("the sm_100a edge-block kernels are built for lmax = mmax = 2")
+        if norm_type != "rms_norm_sh" or act_type != "gate" or ff_type != "spectral" or chg_spin_emb_type != "rand_emb":
+            raise ValueError("only the UMA configuration (rms_norm_sh / gate / spectral / rand_emb) is implemented")
+        if direct_forces or regress_stress or distance_function != "gaussian" or not use_dataset_embedding:
+            raise ValueError("unsupported option for the B200 backbone")
+        if sphere_channels % 128 or hidden_channels % 128:
+            raise ValueError("sphere_channels and hidden_channels must be multiples of 128")
+        self.max_num_elements, self.sphere_channels, self.hidden_channels = max_num_elements, sphere_channels, hidden_channels
+        self.lmax, self.mmax, self.num_layers = lmax, mmax, num_layers
+        self.cutoff, self.max_neighbors, self.otf_graph = float(cutoff), max_neighbors, otf_graph
+        self.edge_channels, self.num_distance_basis = edge_channels, num_distance_basis
+        self.always_use_pbc, self.radius_pbc_version = always_use_pbc, radius_pbc_version
+        self.regress_forces, self.direct_forces = regress_forces, direct_forces
+        self.edge_chunk_size = int(edge_chunk_size)
+        self.dataset_mapping = dict(dataset_mapping or {"omat": "omat", "omol": "omol"})
+        self.sph_feature_size = (lmax + 1) ** 2
+        c, h = sphere_channels, hidden_channels
+
+        self.sphere_embedding = nn.Embedding(max_num_elements, c)
+        self.charge_embedding = _RandEmb(201, c, 100)
+        self.spin_embedding = _RandEmb(101, c, 0)
+        self.dataset_embedding = _DatasetEmbedding(c, self.dataset_mapping)
+        self.mix_csd = nn.Linear(3 * c, c)
+        self.source_embedding = nn.Embedding(max_num_elements, edge_channels)
+        self.target_embedding = nn.Embedding(max_num_elements, edge_channels)
+        nn.init.uniform_(self.source_embedding.weight.data, -0.001, 0.001)
+        nn.init.uniform_(self.target_embedding.weight.data, -0.001, 0.001)
+        self.edge_channels_list = [num_distance_basis + 2 * edge_channels, edge_channels, edge_channels]
+        self.edge_degree_embedding = _EdgeDegreeEmbedding(self.edge_channels_list + [(lmax + 1) * c])
+        self.rescale_factor = 5.0
+        self.blocks = nn.ModuleList([_Block(c, h, lmax, mmax, self.edge_channels_list) for _ in range(num_layers)])
+        self.norm = RMSNormSH(lmax, c)
+        self.register_buffer("_wig_transpose", torch.tensor(_transpose_index()), persistent=False)
+        self.last_graph = None
+
+    # -- reference-facing helpers ------------------------------------------------------------
+    @property
+    def num_params(self) -> int:
+        return sum(p.numel() for p in self.parameters())
+
+    def prepare_for_inference(self, *a, **k):
+        for p in self.parameters():
+            p.requires_grad_(False)
+        return self
+
+    # -- forward -----------------------------------------------------------------------------
+    def _tables(self, rad: RadialMLP):
+        nb, ec = self.num_distance_basis, self.edge_channels
+        w0 = rad.net[0].weight
+        return (self.source_embedding.weight @ w0[:, nb:nb + ec].t(), self.target_embedding.weight @ w0[:, nb + ec:].t())
+
+    def csd_embedding(self, charge, spin, dataset):
+        emb = torch.cat([self.charge_embedding(charge), self.spin_embedding(spin), self.dataset_embedding(dataset)], dim=1)
+        return F.silu(self.mix_csd(emb))
+
+    def _graph(self, data):
+        if self.otf_graph:
+            pbc = torch.ones(len(data["natoms"]), 3, dtype=torch.bool) if self.always_use_pbc else data["pbc"]
+            with torch.no_grad():
+                from .graph import radius_graph_pbc_b200
+
+                edge_index, cell_offsets, neighbors = radius_graph_pbc_b200(data, self.cutoff, self.max_neighbors, False, pbc)
+        else:
+            edge_index, cell_offsets = data["edge_index"], data["cell_offsets"]
+            order = torch.sort(edge_index[1], stable=True).indices
+            edge_index, cell_offsets = edge_index[:, order], cell_offsets[order]
+        return edge_index, cell_offsets
+
+    def forward(self, data, gamma: Optional[torch.Tensor] = None):
+        with torch.enable_grad():
+            return self._forward(data, gamma)
+
+    def _forward(self, data, gamma):
+        data["atomic_numbers"] = data["atomic_numbers"].long()
+        data["atomic_numbers_full"] = data["atomic_numbers"]
+        data["batch_full"] = data["batch"]
+        z, batch = data["atomic_numbers"], data["batch"]
+        pos = data["pos"]
+        if self.regress_forces and not self.direct_forces:
+            pos.requires_grad_(True)
+        n = pos.shape[0]
+        c, nb = self.sphere_channels, self.num_distance_basis
+        csd = self.csd_embedding(data["charge"], data["spin"], data.get("dataset", None))
+        sys_node = csd[batch]
+
+        edge_index, cell_offsets = self._graph(data)
+        data["scatter_target"] = edge_index[1]
+        if edge_index.shape[1] == 0:
+            # isolated atoms: one zero-weight self-loop at the cutoff keeps every kernel shape valid
+            # (the reference does the same, escn_md.py:700-712)
+            edge_index = torch.zeros(2, 1, dtype=torch.long, device=pos.device)
+            cell_offsets = torch.zeros(1, 3, dtype=pos.dtype, device=pos.device)
+            shift = torch.tensor([[self.cutoff, 0.0, 0.0]], dtype=pos.dtype, device=pos.device)
+        else:
+            edge_sys = None if data["cell"].shape[0] == 1 else batch[edge_index[1]]
+            shift = get_pbc_shifts(data["cell"].to(pos.dtype), cell_offsets, edge_sys).contiguous()
+        graph = EdgeGraph.from_edge_index(edge_index, n)
+        self.last_graph = {"edge_index": edge_index, "cell_offsets": cell_offsets}
+        chunks = build_chunks(graph, self.edge_chunk_size)
+
+        vec, dist, env, wig, gauss = ops.EdgeGeometry.apply(pos, shift, gamma, graph, self.cutoff, nb, 0.0, self.cutoff, 2.0)
+        winv = wig[:, self._wig_transpose] * env.unsqueeze(1)
+        ectx = _EdgeCtx(graph, chunks, wig, winv, gauss, z[edge_index[0]], z[edge_index[1]])
+
+        x = torch.zeros(n, self.sph_feature_size, c, dtype=pos.dtype, device=pos.device)
+        x[:, 0, :] = self.sphere_embedding(z) + sys_node
+        ede = self.edge_degree_embedding.rad_func
+        x = _EdgeDegreeFn.apply(x, winv, gauss, ede, self._tables(ede), ectx, nb, self.rescale_factor)
+
+        for blk in self.blocks:
+            x_res = x
+            xn = blk.norm_1(x)
+            xn = torch.cat([xn[:, :1] + sys_node.unsqueeze(1), xn[:, 1:]], dim=1)
+            rad = blk.edge_wise.so2_conv_1.rad_func
+            x = _EdgeBlockFn.apply(xn, wig, winv, gauss, blk.edge_wise, self._tables(rad), ectx, nb) + x_res
+            x_res = x
+            x = blk.atom_wise(blk.norm_2(x)) + x_res
+        x = self.norm(x)
+        return {"node_embedding": x, "batch": batch}
+
+
+class MLP_EFS_HeadB200(nn.Module):
+    """Energy MLP on the l=0 channels, float64 per-system sum, forces = -dE/dpos
+    (src/fairchem/core/models/uma/escn_md.py:1062-1168, src/fairchem/core/models/uma/outputs.py:41-162)."""
+
+    def __init__(self, backbone: eSCNMDBackboneB200):
+        super().__init__()
+        c, h = backbone.sphere_channels, backbone.hidden_channels
+        self.energy_block = nn.Sequential(nn.Linear(c, h), nn.SiLU(), nn.Linear(h, h), nn.SiLU(), nn.Linear(h, 1))
+        self.regress_forces = backbone.regress_forces
+
+    def forward(self, data, emb):
+        with torch.enable_grad():
+            e_node = self.energy_block(emb["node_embedding"][:, 0]).view(-1)
+            nsys = len(data["natoms"])
+            energy = torch.zeros(nsys, dtype=torch.float64, device=e_node.device).index_add(0, data["batch"], e_node.double())
+            out = {"energy": energy.detach()}
+            if self.regress_forces:
+                (grad,) = torch.autograd.grad(energy.sum(), data["pos"], create_graph=False)
+                out["forces"] = -grad
+        return out
+
+
+def build_model(cfg: dict, state_dict: Optional[dict] = None, device="cuda", **overrides):
+    """Backbone + head from a config dict (fairchem_b200.weights.UMA_S keys) and an optional combined state_dict."""
+    from .weights import split_head
+
+    kw = dict(cfg)
+    kw.update(overrides)
+    bb = eSCNMDBackboneB200(otf_graph=True, **kw)
+    head = MLP_EFS_HeadB200(bb)
+    if state_dict is not None:
+        bsd, hsd = split_head(state_dict)
+        bsd = {k: v for k, v in bsd.items() if not k.startswith("Jd_")}
+        bb.load_state_dict(bsd, strict=True)
+        head.energy_block.load_state_dict(hsd, strict=True)
+    bb.to(device).eval()
+    head.to(device).eval()
+    for p in list(bb.parameters()) + list(head.parameters()):
+        p.requires_grad_(False)
+    return bb, head

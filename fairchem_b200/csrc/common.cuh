@@ -1,0 +1,88 @@
+// Shared helpers for the fairchem_b200 kernels (sm_100a).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include "../../include/fairchem_b200.h"
+
+namespace fcb200 {
+
+constexpr int kWarp = 32;
+constexpr unsigned kFull = 0xffffffffu;
+
+// ---- lmax = mmax = 2 coefficient bookkeeping -------------------------------------------------
+// M-major row -> L-major index: m=0:(l0,l1,l2) | m=+1:(l1,l2) | m=-1:(l1,l2) | m=+2:(l2) | m=-2:(l2)
+__host__ __device__ constexpr int m2l(int m) {
+    constexpr int t[9] = {0, 2, 6, 3, 7, 1, 5, 8, 4};
+    return t[m];
+}
+__host__ __device__ constexpr int l2m(int L) {
+    constexpr int t[9] = {0, 5, 1, 3, 8, 6, 2, 4, 7};
+    return t[L];
+}
+__host__ __device__ constexpr int deg_of(int L) { return L == 0 ? 0 : (L < 4 ? 1 : 2); }
+// offset of block l inside the compact 35-entry Wigner
+__host__ __device__ constexpr int woff(int l) { return l == 0 ? 0 : (l == 1 ? 1 : 10); }
+// compact index of entry (row L, col K) of the block-diagonal matrix; both in the same l block
+__host__ __device__ constexpr int wix(int L, int K) {
+    return woff(deg_of(L)) + (L - deg_of(L) * deg_of(L)) * (2 * deg_of(L) + 1) + (K - deg_of(L) * deg_of(L));
+}
+// radial slot (in units of 2C) that multiplies M-major row m: [m0: 0,1,2 | m1: 3,4 (shared by +-1) | m2: 5]
+__host__ __device__ constexpr int radslot(int m) {
+    constexpr int t[9] = {0, 1, 2, 3, 4, 3, 4, 5, 5};
+    return t[m];
+}
+
+__device__ __forceinline__ float4 ld4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ void st4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ float4 f4zero() { return make_float4(0.f, 0.f, 0.f, 0.f); }
+__device__ __forceinline__ float4 fma4(float a, float4 x, float4 acc) {
+    acc.x = fmaf(a, x.x, acc.x);
+    acc.y = fmaf(a, x.y, acc.y);
+    acc.z = fmaf(a, x.z, acc.z);
+    acc.w = fmaf(a, x.w, acc.w);
+    return acc;
+}
+__device__ __forceinline__ float4 mul4(float4 a, float4 b) { return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w); }
+__device__ __forceinline__ float4 add4(float4 a, float4 b) { return make_float4(a.x + b.x, a.y + b.y, a.z + b.z, a.w + b.w); }
+__device__ __forceinline__ float4 sub4(float4 a, float4 b) { return make_float4(a.x - b.x, a.y - b.y, a.z - b.z, a.w - b.w); }
+__device__ __forceinline__ float4 scale4(float a, float4 b) { return make_float4(a * b.x, a * b.y, a * b.z, a * b.w); }
+__device__ __forceinline__ float dot4(float4 a, float4 b) { return fmaf(a.x, b.x, fmaf(a.y, b.y, fmaf(a.z, b.z, a.w * b.w))); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(kFull, v, o);
+    return v;
+}
+__device__ __forceinline__ int warp_sum_i(int v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(kFull, v, o);
+    return v;
+}
+
+// Load the 35 compact Wigner entries of one edge into registers, identical in every lane.
+__device__ __forceinline__ void load_wig(const float* __restrict__ wig, int64_t e, int lane, float (&w)[FCB200_WIG]) {
+    const float* p = wig + e * FCB200_WIG;
+    float a = p[lane];
+    float b = lane < FCB200_WIG - 32 ? p[32 + lane] : 0.f;
+#pragma unroll
+    for (int i = 0; i < FCB200_WIG; ++i) w[i] = i < 32 ? __shfl_sync(kFull, a, i) : __shfl_sync(kFull, b, i - 32);
+}
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+inline int launch_status() {
+    cudaError_t err = cudaGetLastError();
+    return err == cudaSuccess ? FCB200_OK : static_cast<int>(err);
+}
+
+// number of blocks for a warp-per-item kernel with `warps_per_block`, capped to a few waves of 148 SMs
+inline int warp_grid(int64_t items, int warps_per_block, int max_blocks = 148 * 16) {
+    int64_t b = (items + warps_per_block - 1) / warps_per_block;
+    if (b < 1) b = 1;
+    if (b > max_blocks) b = max_blocks;
+    return static_cast<int>(b);
+}
+
+}  // namespace fcb200

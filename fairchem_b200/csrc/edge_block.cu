@@ -1,0 +1,663 @@
+// Edge-block kernels of the eSCN-MD message-passing layer for lmax = mmax = 2 (sm_100a).
+//
+// All kernels are HBM-bound streaming kernels: one warp owns one edge (or one node segment),
+// a lane owns 4 consecutive channels (one float4) of a 128-channel tile, node/edge rows move as
+// 512-byte coalesced warp transactions, and the 35 Wigner entries of the edge live in registers
+// (broadcast once per edge by shuffles).  Reductions over edges are segmented (CSR) sums with a
+// fixed order: no atomics anywhere.
+#include "common.cuh"
+
+namespace fcb200 {
+
+constexpr int kWarpsPerBlock = 8;
+
+// Row m (M-major) of edge e inside the three planar GEMM operands: rows 0-2 -> buf0 [E,3,w],
+// rows 3-6 -> buf1 [E,4,w] (= [E,2,2w]: real pair, imaginary pair), rows 7-8 -> buf2 [E,2,w].
+template <class P>
+__device__ __forceinline__ P* packed_row(P* b0, P* b1, P* b2, int64_t e, int m, int w) {
+    if (m < 3) return b0 + (e * 3 + m) * (int64_t)w;
+    if (m < 7) return b1 + (e * 4 + (m - 3)) * (int64_t)w;
+    return b2 + (e * 2 + (m - 7)) * (int64_t)w;
+}
+
+// ---------------------------------------------------------------------------------------------
+// gather + rotate (+ radial scale) forward
+// ---------------------------------------------------------------------------------------------
+template <bool HAS_RAD>
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
+    gather_rotate_fwd_kernel(const float* __restrict__ x, const int32_t* __restrict__ src, const int32_t* __restrict__ tgt,
+                             const float* __restrict__ wig, const float* __restrict__ radial, float* __restrict__ out0,
+                             float* __restrict__ out1, float* __restrict__ out2, int64_t num_edges, int channels) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
+    const int64_t node_stride = 9LL * channels;
+    for (int64_t e = warp0; e < num_edges; e += nwarps) {
+        float w[FCB200_WIG];
+        load_wig(wig, e, lane, w);
+        const float* xs_base = x + (int64_t)src[e] * node_stride;
+        const float* xt_base = x + (int64_t)tgt[e] * node_stride;
+        const float* r_base = HAS_RAD ? radial + e * 12LL * channels : nullptr;
+        for (int c0 = lane * 4; c0 < channels; c0 += 128) {
+            float4 xs[9], xt[9];
+#pragma unroll
+            for (int L = 0; L < 9; ++L) {
+                xs[L] = ld4(xs_base + L * channels + c0);
+                xt[L] = ld4(xt_base + L * channels + c0);
+            }
+#pragma unroll
+            for (int m = 0; m < 9; ++m) {
+                const int L = m2l(m);
+                const int l = deg_of(L);
+                float4 as = f4zero(), at = f4zero();
+#pragma unroll
+                for (int b = 0; b < 5; ++b) {
+                    if (b < 2 * l + 1) {
+                        const float wv = w[wix(L, l * l + b)];
+                        as = fma4(wv, xs[l * l + b], as);
+                        at = fma4(wv, xt[l * l + b], at);
+                    }
+                }
+                if (HAS_RAD) {
+                    const float* r = r_base + radslot(m) * 2 * channels + c0;
+                    as = mul4(as, ld4(r));
+                    at = mul4(at, ld4(r + channels));
+                }
+                float* o = packed_row(out0, out1, out2, e, m, 2 * channels) + c0;
+                st4(o, as);
+                st4(o + channels, at);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// rotate back + segmented reduce by target (forward), optional residual input and scale
+// ---------------------------------------------------------------------------------------------
+// MODE 0: full 9-row messages.  MODE 1: edge-degree embedding (3 m=0 rows), out = x_in + sum / rescale.
+template <int MODE>
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
+    rotate_back_reduce_kernel(const float* __restrict__ msg, const float* __restrict__ winv, const int32_t* __restrict__ row_ptr,
+                              const float* __restrict__ x_in, float* __restrict__ out, float rescale, int64_t num_nodes,
+                              int channels) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
+    const int rows_in = MODE == 0 ? 9 : 3;
+    for (int64_t n = warp0; n < num_nodes; n += nwarps) {
+        const int e0 = row_ptr[n], e1 = row_ptr[n + 1];
+        for (int c0 = lane * 4; c0 < channels; c0 += 128) {
+            float4 acc[9];
+#pragma unroll
+            for (int L = 0; L < 9; ++L) acc[L] = f4zero();
+            for (int e = e0; e < e1; ++e) {
+                float w[FCB200_WIG];
+                load_wig(winv, e, lane, w);
+                const float* y_base = msg + (int64_t)e * rows_in * channels + c0;
+                if (MODE == 0) {
+                    float4 y[9];
+#pragma unroll
+                    for (int m = 0; m < 9; ++m) y[m] = ld4(y_base + m * channels);
+#pragma unroll
+                    for (int L = 0; L < 9; ++L) {
+                        const int l = deg_of(L);
+#pragma unroll
+                        for (int b = 0; b < 5; ++b)
+                            if (b < 2 * l + 1) acc[L] = fma4(w[wix(L, l * l + b)], y[l2m(l * l + b)], acc[L]);
+                    }
+                } else {
+                    float4 y[3];
+#pragma unroll
+                    for (int j = 0; j < 3; ++j) y[j] = ld4(y_base + j * channels);
+#pragma unroll
+                    for (int L = 0; L < 9; ++L) {
+                        const int l = deg_of(L);
+                        acc[L] = fma4(w[wix(L, l * l + l)], y[l], acc[L]);  // only the m=0 column of each block
+                    }
+                }
+            }
+            float* o = out + n * 9LL * channels + c0;
+#pragma unroll
+            for (int L = 0; L < 9; ++L) {
+                float4 v = acc[L];
+                if (MODE == 1) {
+                    v = make_float4(v.x / rescale, v.y / rescale, v.z / rescale, v.w / rescale);
+                    if (x_in != nullptr) v = add4(v, ld4(x_in + n * 9LL * channels + L * channels + c0));
+                }
+                st4(o + L * channels, v);
+            }
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// gather + rotate backward (per edge): g_src, g_tgt, grad_wig, grad_radial
+// ---------------------------------------------------------------------------------------------
+template <bool HAS_RAD>
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
+    gather_rotate_bwd_kernel(const float* __restrict__ go0, const float* __restrict__ go1, const float* __restrict__ go2,
+                             const float* __restrict__ x, const int32_t* __restrict__ src,
+                             const int32_t* __restrict__ tgt, const float* __restrict__ wig, const float* __restrict__ radial,
+                             float* __restrict__ g_src, float* __restrict__ g_tgt, float* __restrict__ grad_wig,
+                             float* __restrict__ grad_radial, int64_t num_edges, int channels) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
+    const int64_t node_stride = 9LL * channels;
+    // row order that finishes each shared radial slot right after its second row
+    constexpr int order[9] = {0, 1, 2, 3, 5, 4, 6, 7, 8};
+    for (int64_t e = warp0; e < num_edges; e += nwarps) {
+        float w[FCB200_WIG], dw[FCB200_WIG];
+        load_wig(wig, e, lane, w);
+#pragma unroll
+        for (int i = 0; i < FCB200_WIG; ++i) dw[i] = 0.f;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int64_t node = half == 0 ? src[e] : tgt[e];
+            const float* x_base = x + node * node_stride;
+            float* g_base = (half == 0 ? g_src : g_tgt) + e * node_stride;
+            for (int c0 = lane * 4; c0 < channels; c0 += 128) {
+                float4 xv[9], g[9];
+#pragma unroll
+                for (int L = 0; L < 9; ++L) {
+                    xv[L] = ld4(x_base + L * channels + c0);
+                    g[L] = f4zero();
+                }
+                float4 pend = f4zero();
+#pragma unroll
+                for (int k = 0; k < 9; ++k) {
+                    const int m = order[k];
+                    const int L = m2l(m);
+                    const int l = deg_of(L);
+                    float4 go = ld4(packed_row(go0, go1, go2, e, m, 2 * channels) + half * channels + c0);
+                    if (HAS_RAD) {
+                        float4 rot = f4zero();
+#pragma unroll
+                        for (int b = 0; b < 5; ++b)
+                            if (b < 2 * l + 1) rot = fma4(w[wix(L, l * l + b)], xv[l * l + b], rot);
+                        const int64_t roff = e * 12LL * channels + radslot(m) * 2 * channels + half * channels + c0;
+                        float4 contrib = mul4(go, rot);
+                        if (m < 3) {
+                            st4(grad_radial + roff, contrib);
+                        } else if (m == 3 || m == 4 || m == 7) {
+                            pend = contrib;
+                        } else {
+                            st4(grad_radial + roff, add4(pend, contrib));
+                        }
+                        go = mul4(go, ld4(radial + roff));
+                    }
+#pragma unroll
+                    for (int b = 0; b < 5; ++b) {
+                        if (b < 2 * l + 1) {
+                            const int idx = wix(L, l * l + b);
+                            g[l * l + b] = fma4(w[idx], go, g[l * l + b]);
+                            dw[idx] += dot4(go, xv[l * l + b]);
+                        }
+                    }
+                }
+#pragma unroll
+                for (int L = 0; L < 9; ++L) st4(g_base + L * channels + c0, g[L]);
+            }
+        }
+        float mine = 0.f, mine2 = 0.f;
+#pragma unroll
+        for (int i = 0; i < FCB200_WIG; ++i) {
+            const float s = warp_sum(dw[i]);
+            if (i < 32) {
+                if (lane == i) mine = s;
+            } else if (lane == i - 32) {
+                mine2 = s;
+            }
+        }
+        grad_wig[e * FCB200_WIG + lane] = mine;
+        if (lane < FCB200_WIG - 32) grad_wig[e * FCB200_WIG + 32 + lane] = mine2;
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// rotate back backward (per edge): grad_msg (M-major) and grad_winv
+// ---------------------------------------------------------------------------------------------
+// MODE 0: full messages.  MODE 1: edge-degree (3 rows), with 1/rescale.
+template <int MODE, bool WANT_DW>
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
+    rotate_back_bwd_kernel(const float* __restrict__ grad_out, const float* __restrict__ msg, const float* __restrict__ winv,
+                           const int32_t* __restrict__ tgt, float* __restrict__ grad_msg, float* __restrict__ grad_winv,
+                           float rescale, int64_t num_edges, int channels) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
+    const int rows_in = MODE == 0 ? 9 : 3;
+    const float inv = MODE == 1 ? 1.0f / rescale : 1.0f;
+    for (int64_t e = warp0; e < num_edges; e += nwarps) {
+        float w[FCB200_WIG], dw[FCB200_WIG];
+        load_wig(winv, e, lane, w);
+#pragma unroll
+        for (int i = 0; i < FCB200_WIG; ++i) dw[i] = 0.f;
+        const float* go_base = grad_out + (int64_t)tgt[e] * 9LL * channels;
+        for (int c0 = lane * 4; c0 < channels; c0 += 128) {
+            float4 go[9];
+#pragma unroll
+            for (int L = 0; L < 9; ++L) go[L] = ld4(go_base + L * channels + c0);
+            if (MODE == 0) {
+                float4 y[9];
+                if (WANT_DW) {
+#pragma unroll
+                    for (int m = 0; m < 9; ++m) y[m] = ld4(msg + e * 9LL * channels + m * channels + c0);
+                }
+#pragma unroll
+                for (int m = 0; m < 9; ++m) {
+                    const int K = m2l(m);  // column of Winv
+                    const int l = deg_of(K);
+                    float4 acc = f4zero();
+#pragma unroll
+                    for (int a = 0; a < 5; ++a) {
+                        if (a < 2 * l + 1) {
+                            const int idx = wix(l * l + a, K);
+                            acc = fma4(w[idx], go[l * l + a], acc);
+                            if (WANT_DW) dw[idx] += dot4(go[l * l + a], y[m]);
+                        }
+                    }
+                    st4(grad_msg + e * 9LL * channels + m * channels + c0, acc);
+                }
+            } else {
+#pragma unroll
+                for (int l = 0; l < 3; ++l) {
+                    const int K = l * l + l;
+                    float4 y = f4zero();
+                    if (WANT_DW) y = ld4(msg + e * 3LL * channels + l * channels + c0);
+                    float4 acc = f4zero();
+#pragma unroll
+                    for (int a = 0; a < 5; ++a) {
+                        if (a < 2 * l + 1) {
+                            const int idx = wix(l * l + a, K);
+                            acc = fma4(w[idx], go[l * l + a], acc);
+                            if (WANT_DW) dw[idx] += dot4(go[l * l + a], y);
+                        }
+                    }
+                    st4(grad_msg + e * 3LL * channels + l * channels + c0, scale4(inv, acc));
+                }
+            }
+        }
+        (void)rows_in;
+        if (WANT_DW) {
+            float mine = 0.f, mine2 = 0.f;
+#pragma unroll
+            for (int i = 0; i < FCB200_WIG; ++i) {
+                const float s = warp_sum(dw[i]) * inv;
+                if (i < 32) {
+                    if (lane == i) mine = s;
+                } else if (lane == i - 32) {
+                    mine2 = s;
+                }
+            }
+            grad_winv[e * FCB200_WIG + lane] = mine;
+            if (lane < FCB200_WIG - 32) grad_winv[e * FCB200_WIG + 32 + lane] = mine2;
+        }
+    }
+}
+
+// ---------------------------------------------------------------------------------------------
+// segmented sum of rows
+// ---------------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
+    segment_sum_vec_kernel(const float* __restrict__ rows, const int32_t* __restrict__ ptr, const int32_t* __restrict__ perm,
+                           const int32_t* __restrict__ out_index, float* __restrict__ out, int accumulate, float scale,
+                           int64_t num_segments, int64_t width) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
+    for (int64_t n = warp0; n < num_segments; n += nwarps) {
+        const int k0 = ptr[n], k1 = ptr[n + 1];
+        for (int64_t c0 = lane * 4; c0 < width; c0 += 128 * 3) {
+            // three float4 per lane per pass (width 1152 = 9*128 is covered in exactly three passes)
+            float4 a0 = f4zero(), a1 = f4zero(), a2 = f4zero();
+            const bool h1 = c0 + 128 < width, h2 = c0 + 256 < width;
+            for (int k = k0; k < k1; ++k) {
+                const int64_t r = perm ? perm[k] : k;
+                const float* p = rows + r * width + c0;
+                a0 = add4(a0, ld4(p));
+                if (h1) a1 = add4(a1, ld4(p + 128));
+                if (h2) a2 = add4(a2, ld4(p + 256));
+            }
+            float* o = out + (out_index ? (int64_t)out_index[n] : n) * width + c0;
+            a0 = scale4(scale, a0); a1 = scale4(scale, a1); a2 = scale4(scale, a2);
+            if (accumulate) {
+                a0 = add4(a0, ld4(o));
+                if (h1) a1 = add4(a1, ld4(o + 128));
+                if (h2) a2 = add4(a2, ld4(o + 256));
+            }
+            st4(o, a0);
+            if (h1) st4(o + 128, a1);
+            if (h2) st4(o + 256, a2);
+        }
+    }
+}
+
+__global__ void segment_sum_scalar_kernel(const float* __restrict__ rows, const int32_t* __restrict__ ptr,
+                                          const int32_t* __restrict__ perm, const int32_t* __restrict__ out_index,
+                                          float* __restrict__ out, int accumulate, float scale, int64_t num_segments,
+                                          int64_t width) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= num_segments * width) return;
+    const int64_t n = i / width, c = i % width;
+    float acc = 0.f;
+    for (int k = ptr[n]; k < ptr[n + 1]; ++k) acc += rows[(int64_t)(perm ? perm[k] : k) * width + c];
+    const int64_t o = (out_index ? (int64_t)out_index[n] : n) * width + c;
+    out[o] = accumulate ? out[o] + scale * acc : scale * acc;
+}
+
+// ---------------------------------------------------------------------------------------------
+// SO(2) glue: complex combine + gate activation
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + __expf(-v)); }
+__device__ __forceinline__ float sigmoid_acc(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float4 sig4(float4 v) {
+    return make_float4(sigmoid_acc(v.x), sigmoid_acc(v.y), sigmoid_acc(v.z), sigmoid_acc(v.w));
+}
+
+// rows of the m>0 blocks from the two GEMM output rows (so2_layers.py:72-80):
+//   real = row0[:half] - row1[half:], imag = row1[:half] + row0[half:]
+template <bool GATE>
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
+    so2_combine_fwd_kernel(const float* __restrict__ y0, const float* __restrict__ y1, const float* __restrict__ y2,
+                           float* __restrict__ out, float* __restrict__ out1, float* __restrict__ out2, int64_t num_edges,
+                           int ch) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
+    const int n0 = GATE ? 5 * ch : 3 * ch;
+    const int goff = GATE ? 2 * ch : 0;
+    for (int64_t e = warp0; e < num_edges; e += nwarps) {
+        const float* p0 = y0 + e * n0;
+        const float* p1 = y1 + e * 8LL * ch;
+        const float* p2 = y2 + e * 4LL * ch;
+        // GATE: rows go to the three planar operands of the next convolution; else one [E,9,ch] tensor
+        auto row = [&](int m) -> float* {
+            return GATE ? packed_row(out, out1, out2, e, m, ch) : out + (e * 9LL + m) * ch;
+        };
+        for (int c = lane * 4; c < ch; c += 128) {
+            float4 gate1 = make_float4(1.f, 1.f, 1.f, 1.f), gate2 = gate1;
+            if (GATE) {
+                gate1 = sig4(ld4(p0 + c));
+                gate2 = sig4(ld4(p0 + ch + c));
+            }
+            float4 v0 = ld4(p0 + goff + c);
+            if (GATE) {
+                float4 s = sig4(v0);
+                v0 = mul4(v0, s);
+            }
+            st4(row(0) + c, v0);
+            st4(row(1) + c, mul4(ld4(p0 + goff + ch + c), gate1));
+            st4(row(2) + c, mul4(ld4(p0 + goff + 2 * ch + c), gate2));
+            // m = 1: half = 2*ch; row0 = p1[0:4ch], row1 = p1[4ch:8ch]
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float4 g = j == 0 ? gate1 : gate2;
+                float4 re = sub4(ld4(p1 + j * ch + c), ld4(p1 + 4 * ch + 2 * ch + j * ch + c));
+                float4 im = add4(ld4(p1 + 4 * ch + j * ch + c), ld4(p1 + 2 * ch + j * ch + c));
+                st4(row(3 + j) + c, mul4(re, g));
+                st4(row(5 + j) + c, mul4(im, g));
+            }
+            // m = 2: half = ch
+            float4 re = sub4(ld4(p2 + c), ld4(p2 + 2 * ch + ch + c));
+            float4 im = add4(ld4(p2 + 2 * ch + c), ld4(p2 + ch + c));
+            st4(row(7) + c, mul4(re, gate2));
+            st4(row(8) + c, mul4(im, gate2));
+        }
+    }
+}
+
+template <bool GATE>
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
+    so2_combine_bwd_kernel(const float* __restrict__ grad_out, const float* __restrict__ grad_out1,
+                           const float* __restrict__ grad_out2, const float* __restrict__ y0, const float* __restrict__ y1,
+                           const float* __restrict__ y2, float* __restrict__ g0, float* __restrict__ g1, float* __restrict__ g2,
+                           int64_t num_edges, int ch) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
+    const int n0 = GATE ? 5 * ch : 3 * ch;
+    const int goff = GATE ? 2 * ch : 0;
+    for (int64_t e = warp0; e < num_edges; e += nwarps) {
+        auto go_row = [&](int m) -> const float* {
+            return GATE ? packed_row(grad_out, grad_out1, grad_out2, e, m, ch) : grad_out + (e * 9LL + m) * ch;
+        };
+        float* q0 = g0 + e * n0;
+        float* q1 = g1 + e * 8LL * ch;
+        float* q2 = g2 + e * 4LL * ch;
+        const float* p0 = GATE ? y0 + e * n0 : nullptr;
+        const float* p1 = GATE ? y1 + e * 8LL * ch : nullptr;
+        const float* p2 = GATE ? y2 + e * 4LL * ch : nullptr;
+        for (int c = lane * 4; c < ch; c += 128) {
+            float4 gate1 = make_float4(1.f, 1.f, 1.f, 1.f), gate2 = gate1;
+            float4 dgate1 = f4zero(), dgate2 = f4zero();  // d/d(sigmoid output)
+            if (GATE) {
+                gate1 = sig4(ld4(p0 + c));
+                gate2 = sig4(ld4(p0 + ch + c));
+            }
+            // row 0
+            float4 d0 = ld4(go_row(0) + c);
+            if (GATE) {
+                const float4 v = ld4(p0 + goff + c);
+                const float4 s = sig4(v);
+                // d silu = s * (1 + v * (1 - s))
+                d0 = make_float4(d0.x * s.x * (1.f + v.x * (1.f - s.x)), d0.y * s.y * (1.f + v.y * (1.f - s.y)),
+                                 d0.z * s.z * (1.f + v.z * (1.f - s.z)), d0.w * s.w * (1.f + v.w * (1.f - s.w)));
+            }
+            st4(q0 + goff + c, d0);
+            // rows 1, 2
+            {
+                const float4 d1 = ld4(go_row(1) + c), d2 = ld4(go_row(2) + c);
+                st4(q0 + goff + ch + c, mul4(d1, gate1));
+                st4(q0 + goff + 2 * ch + c, mul4(d2, gate2));
+                if (GATE) {
+                    dgate1 = add4(dgate1, mul4(d1, ld4(p0 + goff + ch + c)));
+                    dgate2 = add4(dgate2, mul4(d2, ld4(p0 + goff + 2 * ch + c)));
+                }
+            }
+#pragma unroll
+            for (int j = 0; j < 2; ++j) {
+                const float4 g = j == 0 ? gate1 : gate2;
+                const float4 dre_o = ld4(go_row(3 + j) + c), dim_o = ld4(go_row(5 + j) + c);
+                const float4 dre = mul4(dre_o, g), dim = mul4(dim_o, g);
+                st4(q1 + j * ch + c, dre);                                // row0[:half]
+                st4(q1 + 4 * ch + 2 * ch + j * ch + c, scale4(-1.f, dre)); // row1[half:]
+                st4(q1 + 4 * ch + j * ch + c, dim);                       // row1[:half]
+                st4(q1 + 2 * ch + j * ch + c, dim);                       // row0[half:]
+                if (GATE) {
+                    const float4 re = sub4(ld4(p1 + j * ch + c), ld4(p1 + 4 * ch + 2 * ch + j * ch + c));
+                    const float4 im = add4(ld4(p1 + 4 * ch + j * ch + c), ld4(p1 + 2 * ch + j * ch + c));
+                    const float4 t = add4(mul4(dre_o, re), mul4(dim_o, im));
+                    if (j == 0) dgate1 = add4(dgate1, t); else dgate2 = add4(dgate2, t);
+                }
+            }
+            {
+                const float4 dre_o = ld4(go_row(7) + c), dim_o = ld4(go_row(8) + c);
+                const float4 dre = mul4(dre_o, gate2), dim = mul4(dim_o, gate2);
+                st4(q2 + c, dre);
+                st4(q2 + 2 * ch + ch + c, scale4(-1.f, dre));
+                st4(q2 + 2 * ch + c, dim);
+                st4(q2 + ch + c, dim);
+                if (GATE) {
+                    const float4 re = sub4(ld4(p2 + c), ld4(p2 + 2 * ch + ch + c));
+                    const float4 im = add4(ld4(p2 + 2 * ch + c), ld4(p2 + ch + c));
+                    dgate2 = add4(dgate2, add4(mul4(dre_o, re), mul4(dim_o, im)));
+                }
+            }
+            if (GATE) {
+                // d/d(pre-sigmoid) = d/d(gate) * gate * (1 - gate)
+                st4(q0 + c, make_float4(dgate1.x * gate1.x * (1.f - gate1.x), dgate1.y * gate1.y * (1.f - gate1.y),
+                                        dgate1.z * gate1.z * (1.f - gate1.z), dgate1.w * gate1.w * (1.f - gate1.w)));
+                st4(q0 + ch + c, make_float4(dgate2.x * gate2.x * (1.f - gate2.x), dgate2.y * gate2.y * (1.f - gate2.y),
+                                             dgate2.z * gate2.z * (1.f - gate2.z), dgate2.w * gate2.w * (1.f - gate2.w)));
+            }
+        }
+    }
+}
+
+static int check_common(const void* a, const void* b, int64_t n, int32_t channels) {
+    if (a == nullptr || b == nullptr || n < 0) return FCB200_EINVAL;
+    if (channels <= 0 || channels % 128 != 0) return FCB200_EINVAL;
+    if (!aligned16(a) || !aligned16(b)) return FCB200_EALIGN;
+    return FCB200_OK;
+}
+
+}  // namespace fcb200
+
+using namespace fcb200;
+
+extern "C" {
+
+int fcb200_version(void) { return 1000; }
+
+#define FCB_STREAM static_cast<cudaStream_t>(stream)
+#define FCB_LAUNCH(items) warp_grid(items, kWarpsPerBlock), kWarpsPerBlock * kWarp, 0, FCB_STREAM
+
+int fcb200_gather_rotate_fwd(const float* x, const int32_t* src, const int32_t* tgt, const float* wig, const float* radial,
+                             float* out_m0, float* out_m1, float* out_m2, int64_t num_edges, int64_t num_nodes,
+                             int32_t channels, void* stream) {
+    int rc = check_common(x, out_m0, num_edges, channels);
+    if (rc) return rc;
+    if (!src || !tgt || !wig || !out_m1 || !out_m2 || num_nodes < 0) return FCB200_EINVAL;
+    if (!aligned16(out_m1) || !aligned16(out_m2) || (radial && !aligned16(radial))) return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    if (radial)
+        gather_rotate_fwd_kernel<true><<<FCB_LAUNCH(num_edges)>>>(x, src, tgt, wig, radial, out_m0, out_m1, out_m2, num_edges, channels);
+    else
+        gather_rotate_fwd_kernel<false><<<FCB_LAUNCH(num_edges)>>>(x, src, tgt, wig, nullptr, out_m0, out_m1, out_m2, num_edges, channels);
+    return launch_status();
+}
+
+int fcb200_rotate_back_reduce_fwd(const float* msg, const float* winv, const int32_t* row_ptr, float* out, int64_t num_edges,
+                                  int64_t num_nodes, int32_t channels, void* stream) {
+    if (num_nodes == 0) return FCB200_OK;
+    if (!out || !row_ptr || num_edges < 0 || num_nodes < 0 || channels <= 0 || channels % 128) return FCB200_EINVAL;
+    if (num_edges > 0 && (!msg || !winv)) return FCB200_EINVAL;
+    if (!aligned16(out) || (msg && !aligned16(msg))) return FCB200_EALIGN;
+    rotate_back_reduce_kernel<0><<<FCB_LAUNCH(num_nodes)>>>(msg, winv, row_ptr, nullptr, out, 1.0f, num_nodes, channels);
+    return launch_status();
+}
+
+int fcb200_edge_degree_fwd(const float* radial3, const float* winv, const int32_t* row_ptr, const float* x_in, float* out,
+                           float rescale, int64_t num_edges, int64_t num_nodes, int32_t channels, void* stream) {
+    if (num_nodes == 0) return FCB200_OK;
+    if (!out || !row_ptr || num_edges < 0 || num_nodes < 0 || channels <= 0 || channels % 128 || rescale == 0.f)
+        return FCB200_EINVAL;
+    if (num_edges > 0 && (!radial3 || !winv)) return FCB200_EINVAL;
+    if (!aligned16(out) || (radial3 && !aligned16(radial3)) || (x_in && !aligned16(x_in))) return FCB200_EALIGN;
+    rotate_back_reduce_kernel<1><<<FCB_LAUNCH(num_nodes)>>>(radial3, winv, row_ptr, x_in, out, rescale, num_nodes, channels);
+    return launch_status();
+}
+
+int fcb200_gather_rotate_bwd(const float* grad_m0, const float* grad_m1, const float* grad_m2, const float* x, const int32_t* src,
+                             const int32_t* tgt, const float* wig, const float* radial, float* g_src, float* g_tgt,
+                             float* grad_wig, float* grad_radial, int64_t num_edges, int64_t num_nodes, int32_t channels,
+                             void* stream) {
+    int rc = check_common(grad_m0, x, num_edges, channels);
+    if (rc) return rc;
+    if (!grad_m1 || !grad_m2 || !src || !tgt || !wig || !g_src || !g_tgt || !grad_wig || num_nodes < 0) return FCB200_EINVAL;
+    if ((radial == nullptr) != (grad_radial == nullptr)) return FCB200_EINVAL;
+    if (!aligned16(grad_m1) || !aligned16(grad_m2) || !aligned16(g_src) || !aligned16(g_tgt) ||
+        (radial && (!aligned16(radial) || !aligned16(grad_radial))))
+        return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    if (radial)
+        gather_rotate_bwd_kernel<true><<<FCB_LAUNCH(num_edges)>>>(grad_m0, grad_m1, grad_m2, x, src, tgt, wig, radial, g_src, g_tgt,
+                                                                  grad_wig, grad_radial, num_edges, channels);
+    else
+        gather_rotate_bwd_kernel<false><<<FCB_LAUNCH(num_edges)>>>(grad_m0, grad_m1, grad_m2, x, src, tgt, wig, nullptr, g_src,
+                                                                   g_tgt, grad_wig, nullptr, num_edges, channels);
+    return launch_status();
+}
+
+int fcb200_rotate_back_bwd(const float* grad_out, const float* msg, const float* winv, const int32_t* tgt, float* grad_msg,
+                           float* grad_winv, int64_t num_edges, int64_t num_nodes, int32_t channels, void* stream) {
+    int rc = check_common(grad_out, grad_msg, num_edges, channels);
+    if (rc) return rc;
+    if (!winv || !tgt || num_nodes < 0) return FCB200_EINVAL;
+    if ((msg == nullptr) != (grad_winv == nullptr)) return FCB200_EINVAL;
+    if (msg && !aligned16(msg)) return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    if (msg)
+        rotate_back_bwd_kernel<0, true><<<FCB_LAUNCH(num_edges)>>>(grad_out, msg, winv, tgt, grad_msg, grad_winv, 1.f, num_edges, channels);
+    else
+        rotate_back_bwd_kernel<0, false><<<FCB_LAUNCH(num_edges)>>>(grad_out, nullptr, winv, tgt, grad_msg, nullptr, 1.f, num_edges,
+                                                                    channels);
+    return launch_status();
+}
+
+int fcb200_edge_degree_bwd(const float* grad_out, const float* radial3, const float* winv, const int32_t* tgt,
+                           float* grad_radial3, float* grad_winv, float rescale, int64_t num_edges, int64_t num_nodes,
+                           int32_t channels, void* stream) {
+    int rc = check_common(grad_out, grad_radial3, num_edges, channels);
+    if (rc) return rc;
+    if (!radial3 || !winv || !tgt || !grad_winv || num_nodes < 0 || rescale == 0.f) return FCB200_EINVAL;
+    if (!aligned16(radial3)) return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    rotate_back_bwd_kernel<1, true><<<FCB_LAUNCH(num_edges)>>>(grad_out, radial3, winv, tgt, grad_radial3, grad_winv, rescale,
+                                                               num_edges, channels);
+    return launch_status();
+}
+
+int fcb200_segment_sum(const float* rows, const int32_t* ptr, const int32_t* perm, const int32_t* out_index, float* out,
+                       int32_t accumulate, float scale, int64_t num_segments, int64_t width, void* stream) {
+    if (num_segments == 0) return FCB200_OK;
+    if (!ptr || !out || num_segments < 0 || width <= 0) return FCB200_EINVAL;
+    if (width % 4 == 0 && aligned16(rows) && aligned16(out)) {
+        segment_sum_vec_kernel<<<FCB_LAUNCH(num_segments)>>>(rows, ptr, perm, out_index, out, accumulate, scale, num_segments, width);
+    } else {
+        const int64_t total = num_segments * width;
+        segment_sum_scalar_kernel<<<(unsigned)((total + 255) / 256), 256, 0, FCB_STREAM>>>(rows, ptr, perm, out_index, out, accumulate,
+                                                                                        scale, num_segments, width);
+    }
+    return launch_status();
+}
+
+int fcb200_so2_gate_fwd(const float* y0, const float* y1, const float* y2, float* out_m0, float* out_m1, float* out_m2,
+                        int64_t num_edges, int32_t hidden, void* stream) {
+    int rc = check_common(y0, out_m0, num_edges, hidden);
+    if (rc) return rc;
+    if (!y1 || !y2 || !out_m1 || !out_m2) return FCB200_EINVAL;
+    if (!aligned16(y1) || !aligned16(y2) || !aligned16(out_m1) || !aligned16(out_m2)) return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    so2_combine_fwd_kernel<true><<<FCB_LAUNCH(num_edges)>>>(y0, y1, y2, out_m0, out_m1, out_m2, num_edges, hidden);
+    return launch_status();
+}
+
+int fcb200_so2_gate_bwd(const float* grad_m0, const float* grad_m1, const float* grad_m2, const float* y0, const float* y1,
+                        const float* y2, float* g0, float* g1, float* g2, int64_t num_edges, int32_t hidden, void* stream) {
+    int rc = check_common(grad_m0, g0, num_edges, hidden);
+    if (rc) return rc;
+    if (!grad_m1 || !grad_m2 || !y0 || !y1 || !y2 || !g1 || !g2) return FCB200_EINVAL;
+    if (!aligned16(grad_m1) || !aligned16(grad_m2) || !aligned16(y0) || !aligned16(y1) || !aligned16(y2) || !aligned16(g1) ||
+        !aligned16(g2))
+        return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    so2_combine_bwd_kernel<true><<<FCB_LAUNCH(num_edges)>>>(grad_m0, grad_m1, grad_m2, y0, y1, y2, g0, g1, g2, num_edges, hidden);
+    return launch_status();
+}
+
+int fcb200_so2_combine_fwd(const float* z0, const float* z1, const float* z2, float* out, int64_t num_edges, int32_t channels,
+                           void* stream) {
+    int rc = check_common(z0, out, num_edges, channels);
+    if (rc) return rc;
+    if (!z1 || !z2) return FCB200_EINVAL;
+    if (!aligned16(z1) || !aligned16(z2)) return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    so2_combine_fwd_kernel<false><<<FCB_LAUNCH(num_edges)>>>(z0, z1, z2, out, nullptr, nullptr, num_edges, channels);
+    return launch_status();
+}
+
+int fcb200_so2_combine_bwd(const float* grad_out, float* g0, float* g1, float* g2, int64_t num_edges, int32_t channels,
+                           void* stream) {
+    int rc = check_common(grad_out, g0, num_edges, channels);
+    if (rc) return rc;
+    if (!g1 || !g2) return FCB200_EINVAL;
+    if (!aligned16(g1) || !aligned16(g2)) return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    so2_combine_bwd_kernel<false><<<FCB_LAUNCH(num_edges)>>>(grad_out, nullptr, nullptr, nullptr, nullptr, nullptr, g0, g1, g2,
+                                                             num_edges, channels);
+    return launch_status();
+}
+
+}  // extern "C"

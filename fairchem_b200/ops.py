@@ -1,0 +1,402 @@
+"""torch.library custom ops over the C ABI, and the autograd Functions built on them.
+
+Layering mirrors the reference (src/fairchem/core/models/uma/triton/custom_ops.py:8-16): the ops
+registered under ``torch.ops.fairchem_b200`` are kernel-only and write into caller-allocated
+outputs (``mutates_args``); allocation and the chaining of backward kernels live in the
+``torch.autograd.Function`` classes below.  Every op requires CUDA tensors and the compiled
+library; there is no CPU implementation.
+"""
+
+from __future__ import annotations
+
+from ctypes import c_void_p
+from typing import Optional
+
+import torch
+from torch import Tensor
+
+from . import _lib
+
+NS = "fairchem_b200"
+WIG = 35
+
+
+def _p(t: Optional[Tensor]):
+    return None if t is None else c_void_p(t.data_ptr())
+
+
+def _stream():
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _chk(*tensors):
+    for t in tensors:
+        if t is None:
+            continue
+        if not t.is_cuda:
+            raise _lib.FairchemB200Error("fairchem_b200 ops need CUDA tensors (no CPU fallback)")
+        if not t.is_contiguous():
+            raise _lib.FairchemB200Error("fairchem_b200 ops need contiguous tensors")
+
+
+def _f32(*tensors):
+    for t in tensors:
+        if t is not None and t.dtype != torch.float32:
+            raise _lib.FairchemB200Error(f"expected float32, got {t.dtype}")
+
+
+# ------------------------------------------------------------------------------------------
+# kernel-only ops (mutating, no autograd)
+# ------------------------------------------------------------------------------------------
+
+
+@torch.library.custom_op(f"{NS}::gather_rotate_fwd", mutates_args=("m0", "m1", "m2"))
+def gather_rotate_fwd_(x: Tensor, src: Tensor, tgt: Tensor, wig: Tensor, radial: Optional[Tensor], m0: Tensor,
+                       m1: Tensor, m2: Tensor) -> None:
+    _chk(x, src, tgt, wig, radial, m0, m1, m2)
+    _f32(x, wig, radial, m0, m1, m2)
+    _lib.call("fcb200_gather_rotate_fwd", _p(x), _p(src), _p(tgt), _p(wig), _p(radial), _p(m0), _p(m1), _p(m2),
+              src.shape[0], x.shape[0], x.shape[2], _stream())
+
+
+@torch.library.custom_op(f"{NS}::gather_rotate_bwd", mutates_args=("g_src", "g_tgt", "grad_wig", "grad_radial"))
+def gather_rotate_bwd_(gm0: Tensor, gm1: Tensor, gm2: Tensor, x: Tensor, src: Tensor, tgt: Tensor, wig: Tensor,
+                       radial: Optional[Tensor], g_src: Tensor, g_tgt: Tensor, grad_wig: Tensor,
+                       grad_radial: Optional[Tensor]) -> None:
+    _chk(gm0, gm1, gm2, x, src, tgt, wig, radial, g_src, g_tgt, grad_wig, grad_radial)
+    _f32(gm0, gm1, gm2, x, wig, radial, g_src, g_tgt, grad_wig, grad_radial)
+    _lib.call("fcb200_gather_rotate_bwd", _p(gm0), _p(gm1), _p(gm2), _p(x), _p(src), _p(tgt), _p(wig), _p(radial),
+              _p(g_src), _p(g_tgt), _p(grad_wig), _p(grad_radial), src.shape[0], x.shape[0], x.shape[2], _stream())
+
+
+@torch.library.custom_op(f"{NS}::rotate_back_reduce_fwd", mutates_args=("out",))
+def rotate_back_reduce_fwd_(msg: Tensor, winv: Tensor, row_ptr: Tensor, out: Tensor) -> None:
+    _chk(msg, winv, row_ptr, out)
+    _f32(msg, winv, out)
+    _lib.call("fcb200_rotate_back_reduce_fwd", _p(msg), _p(winv), _p(row_ptr), _p(out), msg.shape[0], out.shape[0],
+              out.shape[2], _stream())
+
+
+@torch.library.custom_op(f"{NS}::rotate_back_bwd", mutates_args=("grad_msg", "grad_winv"))
+def rotate_back_bwd_(grad_out: Tensor, msg: Optional[Tensor], winv: Tensor, tgt: Tensor, grad_msg: Tensor,
+                     grad_winv: Optional[Tensor]) -> None:
+    _chk(grad_out, msg, winv, tgt, grad_msg, grad_winv)
+    _f32(grad_out, msg, winv, grad_msg, grad_winv)
+    _lib.call("fcb200_rotate_back_bwd", _p(grad_out), _p(msg), _p(winv), _p(tgt), _p(grad_msg), _p(grad_winv),
+              tgt.shape[0], grad_out.shape[0], grad_out.shape[2], _stream())
+
+
+@torch.library.custom_op(f"{NS}::edge_degree_fwd", mutates_args=("out",))
+def edge_degree_fwd_(radial3: Tensor, winv: Tensor, row_ptr: Tensor, x_in: Optional[Tensor], out: Tensor,
+                     rescale: float) -> None:
+    _chk(radial3, winv, row_ptr, x_in, out)
+    _f32(radial3, winv, x_in, out)
+    _lib.call("fcb200_edge_degree_fwd", _p(radial3), _p(winv), _p(row_ptr), _p(x_in), _p(out), rescale,
+              radial3.shape[0], out.shape[0], out.shape[2], _stream())
+
+
+@torch.library.custom_op(f"{NS}::edge_degree_bwd", mutates_args=("grad_radial3", "grad_winv"))
+def edge_degree_bwd_(grad_out: Tensor, radial3: Tensor, winv: Tensor, tgt: Tensor, grad_radial3: Tensor,
+                     grad_winv: Tensor, rescale: float) -> None:
+    _chk(grad_out, radial3, winv, tgt, grad_radial3, grad_winv)
+    _f32(grad_out, radial3, winv, grad_radial3, grad_winv)
+    _lib.call("fcb200_edge_degree_bwd", _p(grad_out), _p(radial3), _p(winv), _p(tgt), _p(grad_radial3), _p(grad_winv),
+              rescale, tgt.shape[0], grad_out.shape[0], grad_out.shape[2], _stream())
+
+
+@torch.library.custom_op(f"{NS}::segment_sum", mutates_args=("out",))
+def segment_sum_(rows: Tensor, ptr: Tensor, perm: Optional[Tensor], out_index: Optional[Tensor], out: Tensor,
+                 accumulate: bool, scale: float, num_segments: int, width: int) -> None:
+    _chk(rows, ptr, perm, out_index, out)
+    _f32(rows, out)
+    _lib.call("fcb200_segment_sum", _p(rows), _p(ptr), _p(perm), _p(out_index), _p(out), int(accumulate), scale,
+              num_segments, width, _stream())
+
+
+@torch.library.custom_op(f"{NS}::so2_gate_fwd", mutates_args=("a0", "a1", "a2"))
+def so2_gate_fwd_(y0: Tensor, y1: Tensor, y2: Tensor, a0: Tensor, a1: Tensor, a2: Tensor, hidden: int) -> None:
+    _chk(y0, y1, y2, a0, a1, a2)
+    _f32(y0, y1, y2, a0, a1, a2)
+    _lib.call("fcb200_so2_gate_fwd", _p(y0), _p(y1), _p(y2), _p(a0), _p(a1), _p(a2), y0.shape[0], hidden, _stream())
+
+
+@torch.library.custom_op(f"{NS}::so2_gate_bwd", mutates_args=("g0", "g1", "g2"))
+def so2_gate_bwd_(ga0: Tensor, ga1: Tensor, ga2: Tensor, y0: Tensor, y1: Tensor, y2: Tensor, g0: Tensor, g1: Tensor,
+                  g2: Tensor, hidden: int) -> None:
+    _chk(ga0, ga1, ga2, y0, y1, y2, g0, g1, g2)
+    _f32(ga0, ga1, ga2, y0, y1, y2, g0, g1, g2)
+    _lib.call("fcb200_so2_gate_bwd", _p(ga0), _p(ga1), _p(ga2), _p(y0), _p(y1), _p(y2), _p(g0), _p(g1), _p(g2),
+              y0.shape[0], hidden, _stream())
+
+
+@torch.library.custom_op(f"{NS}::so2_combine_fwd", mutates_args=("out",))
+def so2_combine_fwd_(z0: Tensor, z1: Tensor, z2: Tensor, out: Tensor, channels: int) -> None:
+    _chk(z0, z1, z2, out)
+    _f32(z0, z1, z2, out)
+    _lib.call("fcb200_so2_combine_fwd", _p(z0), _p(z1), _p(z2), _p(out), z0.shape[0], channels, _stream())
+
+
+@torch.library.custom_op(f"{NS}::so2_combine_bwd", mutates_args=("g0", "g1", "g2"))
+def so2_combine_bwd_(grad_out: Tensor, g0: Tensor, g1: Tensor, g2: Tensor, channels: int) -> None:
+    _chk(grad_out, g0, g1, g2)
+    _f32(grad_out, g0, g1, g2)
+    _lib.call("fcb200_so2_combine_bwd", _p(grad_out), _p(g0), _p(g1), _p(g2), grad_out.shape[0], channels, _stream())
+
+
+@torch.library.custom_op(f"{NS}::edge_geometry_fwd", mutates_args=("vec", "dist", "env", "wig", "gauss"))
+def edge_geometry_fwd_(pos: Tensor, src: Tensor, tgt: Tensor, shift: Optional[Tensor], gamma: Optional[Tensor],
+                       vec: Optional[Tensor], dist: Optional[Tensor], env: Optional[Tensor], wig: Optional[Tensor],
+                       gauss: Optional[Tensor], cutoff: float, num_basis: int, b_start: float, b_stop: float,
+                       b_width: float) -> None:
+    _chk(pos, src, tgt, shift, gamma, vec, dist, env, wig, gauss)
+    _f32(pos, shift, gamma, vec, dist, env, wig, gauss)
+    _lib.call("fcb200_edge_geometry_fwd", _p(pos), _p(src), _p(tgt), _p(shift), _p(gamma), _p(vec), _p(dist), _p(env),
+              _p(wig), _p(gauss), cutoff, num_basis, b_start, b_stop, b_width, src.shape[0], pos.shape[0], _stream())
+
+
+@torch.library.custom_op(f"{NS}::edge_geometry_bwd", mutates_args=("grad_vec",))
+def edge_geometry_bwd_(pos: Tensor, src: Tensor, tgt: Tensor, shift: Optional[Tensor], gamma: Optional[Tensor],
+                       grad_wig: Optional[Tensor], grad_env: Optional[Tensor], grad_gauss: Optional[Tensor],
+                       grad_dist: Optional[Tensor], grad_vec: Tensor, cutoff: float, num_basis: int, b_start: float,
+                       b_stop: float, b_width: float) -> None:
+    _chk(pos, src, tgt, shift, gamma, grad_wig, grad_env, grad_gauss, grad_dist, grad_vec)
+    _f32(pos, shift, gamma, grad_wig, grad_env, grad_gauss, grad_dist, grad_vec)
+    _lib.call("fcb200_edge_geometry_bwd", _p(pos), _p(src), _p(tgt), _p(shift), _p(gamma), _p(grad_wig), _p(grad_env),
+              _p(grad_gauss), _p(grad_dist), _p(grad_vec), cutoff, num_basis, b_start, b_stop, b_width, src.shape[0],
+              pos.shape[0], _stream())
+
+
+@torch.library.custom_op(f"{NS}::gemm_tf32", mutates_args=("c", "status"))
+def gemm_tf32_(a: Tensor, w: Tensor, bias: Optional[Tensor], c: Tensor, precision: int, status: Tensor) -> None:
+    """c[M,N] = a[M,K] @ w[N,K]^T (+ bias); a, w, c may be row-strided views with unit inner stride."""
+    for t in (a, w, c):
+        if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+            raise _lib.FairchemB200Error("gemm_tf32: need 2-D float32 CUDA operands with unit inner stride")
+    _chk(bias, status)
+    _lib.call("fcb200_gemm_tf32", _p(a), a.stride(0), _p(w), w.stride(0), _p(bias), _p(c), c.stride(0), a.shape[0],
+              w.shape[0], a.shape[1], precision, _p(status), _stream())
+
+
+# ------------------------------------------------------------------------------------------
+# edge graph bookkeeping
+# ------------------------------------------------------------------------------------------
+
+
+class EdgeGraph:
+    """Index structures of one edge list on the device.
+
+    ``src``/``tgt`` are int32 node ids into the full node array (local + halo rows); edges must be
+    sorted by target.  ``row_ptr`` is the CSR over the ``num_targets`` nodes that receive messages
+    (they are the first rows of the node array); ``src_ptr``/``src_perm`` list, for every node of
+    the full array, the edges that leave it (for the atomic-free backward of the gather).
+    """
+
+    def __init__(self, src: Tensor, tgt: Tensor, num_nodes: int, num_targets: Optional[int] = None):
+        if src.dtype != torch.int32:
+            src = src.to(torch.int32)
+        if tgt.dtype != torch.int32:
+            tgt = tgt.to(torch.int32)
+        self.src = src.contiguous()
+        self.tgt = tgt.contiguous()
+        self.num_edges = int(src.shape[0])
+        self.num_nodes = int(num_nodes)
+        self.num_targets = int(num_nodes if num_targets is None else num_targets)
+        dev = src.device
+        tl = self.tgt.long()
+        if self.num_edges > 1 and bool((tl[1:] < tl[:-1]).any()):
+            raise _lib.FairchemB200Error("EdgeGraph: edges must be sorted by target node")
+        counts = torch.bincount(tl, minlength=self.num_targets)
+        self.row_ptr = torch.zeros(self.num_targets + 1, dtype=torch.int32, device=dev)
+        self.row_ptr[1:] = torch.cumsum(counts, 0)
+        sl = self.src.long()
+        order = torch.sort(sl, stable=True).indices
+        self.src_perm = order.to(torch.int32)
+        sc = torch.bincount(sl, minlength=self.num_nodes)
+        self.src_ptr = torch.zeros(self.num_nodes + 1, dtype=torch.int32, device=dev)
+        self.src_ptr[1:] = torch.cumsum(sc, 0)
+
+    @staticmethod
+    def from_edge_index(edge_index: Tensor, num_nodes: int, num_targets: Optional[int] = None) -> "EdgeGraph":
+        return EdgeGraph(edge_index[0], edge_index[1], num_nodes, num_targets)
+
+
+def segment_sum(rows: Tensor, ptr: Tensor, perm: Optional[Tensor], num_segments: int, out: Optional[Tensor] = None,
+                out_index: Optional[Tensor] = None, accumulate: bool = False, scale: float = 1.0) -> Tensor:
+    width = rows[0].numel() if rows.shape[0] else int(torch.tensor(rows.shape[1:]).prod())
+    if out is None:
+        out = torch.empty((num_segments,) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
+    segment_sum_(rows, ptr, perm, out_index, out, accumulate, scale, num_segments, width)
+    return out
+
+
+# ------------------------------------------------------------------------------------------
+# autograd Functions
+# ------------------------------------------------------------------------------------------
+
+
+class GatherRotate(torch.autograd.Function):
+    """x [N,9,C], wig [E,35], radial [E,12C] or None -> (m0 [E,6C], m1 [E,2,4C], m2 [E,2,2C])."""
+
+    @staticmethod
+    def forward(ctx, x, wig, radial, graph: EdgeGraph):
+        e, c = graph.num_edges, x.shape[2]
+        x, wig = x.contiguous(), wig.contiguous()
+        radial = None if radial is None else radial.contiguous()
+        m0 = torch.empty(e, 6 * c, dtype=x.dtype, device=x.device)
+        m1 = torch.empty(e, 2, 4 * c, dtype=x.dtype, device=x.device)
+        m2 = torch.empty(e, 2, 2 * c, dtype=x.dtype, device=x.device)
+        gather_rotate_fwd_(x, graph.src, graph.tgt, wig, radial, m0, m1, m2)
+        ctx.save_for_backward(x, wig, radial)
+        ctx.graph = graph
+        return m0, m1, m2
+
+    @staticmethod
+    def backward(ctx, gm0, gm1, gm2):
+        x, wig, radial = ctx.saved_tensors
+        g = ctx.graph
+        e, c = g.num_edges, x.shape[2]
+        g_src = torch.empty(e, 9, c, dtype=x.dtype, device=x.device)
+        g_tgt = torch.empty(e, 9, c, dtype=x.dtype, device=x.device)
+        grad_wig = torch.empty(e, WIG, dtype=x.dtype, device=x.device)
+        grad_radial = None if radial is None else torch.empty_like(radial)
+        gather_rotate_bwd_(gm0.contiguous(), gm1.contiguous(), gm2.contiguous(), x, g.src, g.tgt, wig, radial, g_src,
+                           g_tgt, grad_wig, grad_radial)
+        grad_x = torch.empty_like(x)
+        segment_sum(g_src, g.src_ptr, g.src_perm, g.num_nodes, out=grad_x)
+        if g.num_targets == g.num_nodes:
+            segment_sum(g_tgt, g.row_ptr, None, g.num_targets, out=grad_x, accumulate=True)
+        else:
+            segment_sum(g_tgt, g.row_ptr, None, g.num_targets, out=grad_x[: g.num_targets], accumulate=True)
+        return grad_x, grad_wig, grad_radial, None
+
+
+class RotateBackReduce(torch.autograd.Function):
+    """msg [E,9,C] (M-major), winv [E,35] -> out [num_targets,9,C]."""
+
+    @staticmethod
+    def forward(ctx, msg, winv, graph: EdgeGraph):
+        msg, winv = msg.contiguous(), winv.contiguous()
+        out = torch.empty(graph.num_targets, 9, msg.shape[2], dtype=msg.dtype, device=msg.device)
+        rotate_back_reduce_fwd_(msg, winv, graph.row_ptr, out)
+        ctx.save_for_backward(msg, winv)
+        ctx.graph = graph
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        msg, winv = ctx.saved_tensors
+        g = ctx.graph
+        grad_msg = torch.empty_like(msg)
+        grad_winv = torch.empty_like(winv)
+        rotate_back_bwd_(grad_out.contiguous(), msg, winv, g.tgt, grad_msg, grad_winv)
+        return grad_msg, grad_winv, None
+
+
+class EdgeDegree(torch.autograd.Function):
+    """x [N,9,C] + segment_sum_tgt(Winv[:, m0 cols] @ radial3 [E,3,C]) / rescale."""
+
+    @staticmethod
+    def forward(ctx, x, radial3, winv, graph: EdgeGraph, rescale: float):
+        radial3, winv, x = radial3.contiguous(), winv.contiguous(), x.contiguous()
+        out = torch.empty_like(x)
+        edge_degree_fwd_(radial3, winv, graph.row_ptr, x, out, float(rescale))
+        ctx.save_for_backward(radial3, winv)
+        ctx.graph, ctx.rescale = graph, float(rescale)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        radial3, winv = ctx.saved_tensors
+        g = ctx.graph
+        grad_out = grad_out.contiguous()
+        grad_r = torch.empty_like(radial3)
+        grad_w = torch.empty_like(winv)
+        edge_degree_bwd_(grad_out, radial3, winv, g.tgt, grad_r, grad_w, ctx.rescale)
+        return grad_out, grad_r, grad_w, None, None
+
+
+class SO2Gate(torch.autograd.Function):
+    """Complex combine + gate: y0 [E,5H], y1 [E,2,4H], y2 [E,2,2H] -> a0 [E,3H], a1 [E,2,2H], a2 [E,2,H]."""
+
+    @staticmethod
+    def forward(ctx, y0, y1, y2):
+        y0, y1, y2 = y0.contiguous(), y1.contiguous(), y2.contiguous()
+        e = y0.shape[0]
+        h = y0.shape[1] // 5
+        a0 = torch.empty(e, 3 * h, dtype=y0.dtype, device=y0.device)
+        a1 = torch.empty(e, 2, 2 * h, dtype=y0.dtype, device=y0.device)
+        a2 = torch.empty(e, 2, h, dtype=y0.dtype, device=y0.device)
+        so2_gate_fwd_(y0, y1, y2, a0, a1, a2, h)
+        ctx.save_for_backward(y0, y1, y2)
+        return a0, a1, a2
+
+    @staticmethod
+    def backward(ctx, ga0, ga1, ga2):
+        y0, y1, y2 = ctx.saved_tensors
+        g0, g1, g2 = torch.empty_like(y0), torch.empty_like(y1), torch.empty_like(y2)
+        so2_gate_bwd_(ga0.contiguous(), ga1.contiguous(), ga2.contiguous(), y0, y1, y2, g0, g1, g2, y0.shape[1] // 5)
+        return g0, g1, g2
+
+
+class SO2Combine(torch.autograd.Function):
+    """Complex combine: z0 [E,3C], z1 [E,2,4C], z2 [E,2,2C] -> msg [E,9,C] (M-major)."""
+
+    @staticmethod
+    def forward(ctx, z0, z1, z2):
+        z0, z1, z2 = z0.contiguous(), z1.contiguous(), z2.contiguous()
+        c = z0.shape[1] // 3
+        out = torch.empty(z0.shape[0], 9, c, dtype=z0.dtype, device=z0.device)
+        so2_combine_fwd_(z0, z1, z2, out, c)
+        ctx.c = c
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        c = ctx.c
+        e = grad_out.shape[0]
+        g0 = torch.empty(e, 3 * c, dtype=grad_out.dtype, device=grad_out.device)
+        g1 = torch.empty(e, 2, 4 * c, dtype=grad_out.dtype, device=grad_out.device)
+        g2 = torch.empty(e, 2, 2 * c, dtype=grad_out.dtype, device=grad_out.device)
+        so2_combine_bwd_(grad_out.contiguous(), g0, g1, g2, c)
+        return g0, g1, g2
+
+
+class EdgeGeometry(torch.autograd.Function):
+    """pos [N,3] -> (vec [E,3], dist [E], env [E], wig [E,35], gauss [E,nb]); differentiable in pos."""
+
+    @staticmethod
+    def forward(ctx, pos, shift, gamma, graph: EdgeGraph, cutoff: float, num_basis: int, b_start: float,
+                b_stop: float, b_width: float):
+        pos = pos.contiguous()
+        e, dev = graph.num_edges, pos.device
+        vec = torch.empty(e, 3, dtype=pos.dtype, device=dev)
+        dist = torch.empty(e, dtype=pos.dtype, device=dev)
+        env = torch.empty(e, dtype=pos.dtype, device=dev)
+        wig = torch.empty(e, WIG, dtype=pos.dtype, device=dev)
+        gauss = torch.empty(e, num_basis, dtype=pos.dtype, device=dev)
+        shift = None if shift is None else shift.contiguous()
+        gamma = None if gamma is None else gamma.contiguous()
+        edge_geometry_fwd_(pos, graph.src, graph.tgt, shift, gamma, vec, dist, env, wig, gauss, cutoff, num_basis,
+                           b_start, b_stop, b_width)
+        ctx.save_for_backward(pos, shift, gamma)
+        ctx.graph = graph
+        ctx.params = (cutoff, num_basis, b_start, b_stop, b_width)
+        ctx.mark_non_differentiable(vec)
+        return vec, dist, env, wig, gauss
+
+    @staticmethod
+    def backward(ctx, _gvec, gdist, genv, gwig, ggauss):
+        pos, shift, gamma = ctx.saved_tensors
+        g = ctx.graph
+
+        def c(t):
+            return None if t is None else t.contiguous()
+
+        grad_vec = torch.empty(g.num_edges, 3, dtype=pos.dtype, device=pos.device)
+        edge_geometry_bwd_(pos, g.src, g.tgt, shift, gamma, c(gwig), c(genv), c(ggauss), c(gdist), grad_vec, *ctx.params)
+        grad_pos = torch.empty_like(pos)
+        segment_sum(grad_vec, g.src_ptr, g.src_perm, pos.shape[0], out=grad_pos)
+        nt = g.num_targets
+        segment_sum(grad_vec, g.row_ptr, None, nt, out=grad_pos if nt == pos.shape[0] else grad_pos[:nt],
+                    accumulate=True, scale=-1.0)
+        return grad_pos, None, None, None, None, None, None, None, None

@@ -1,0 +1,232 @@
+/*
+ * fairchem_b200 -- C ABI of the B200 (sm_100a) edge message-passing path of eSCN-MD / UMA.
+ *
+ * Every entry point is what a binding of fairchem's per-layer edge block would call in place
+ * of the reference's Triton ops / ATen calls.  Citations are paths inside
+ * facebookresearch/fairchem (file:line).
+ *
+ * Conventions
+ *   - all pointers are DEVICE pointers of the current CUDA device unless a name ends in _host;
+ *   - the caller owns every buffer (inputs, outputs and scratch) and the stream; entry points
+ *     neither allocate, free nor synchronise;
+ *   - float tensors are contiguous float32; rows that are read as float4 must be 16-byte aligned;
+ *   - edges are CSR-sorted by target node: row_ptr[n]..row_ptr[n+1] are the edges whose target is n;
+ *   - node features are L-major [N, (lmax+1)^2, C]; edge features are M-major
+ *     (m=0:(l=0..lmax) | m=+1:(l=1..) | m=-1 | m=+2 | m=-2), lmax = mmax = 2, C a multiple of 128;
+ *   - `wig` is the block-diagonal Wigner-D of an edge in compact form [E, 35]:
+ *     entry 0 = l0 block, entries 1..9 = l1 block (3x3 row-major), 10..34 = l2 block (5x5 row-major);
+ *   - return value: 0 on success, a negative FCB200_E* code otherwise (nothing was launched),
+ *     or a positive cudaError_t from the launch.
+ */
+#ifndef FAIRCHEM_B200_H
+#define FAIRCHEM_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define FCB200_OK 0
+#define FCB200_EINVAL (-1)   /* null pointer, negative size or unsupported shape */
+#define FCB200_EALIGN (-2)   /* pointer not 16-byte aligned */
+#define FCB200_ERANGE (-3)   /* size exceeds a documented limit */
+
+#define FCB200_WIG 35        /* compact Wigner entries per edge for lmax = 2 */
+
+/* Library/ABI version (major*1000 + minor). */
+int fcb200_version(void);
+
+/* ---------------------------------------------------------------- edge block, forward */
+
+/*
+ * Gather source and target node rows of every edge, rotate them into the edge frame and emit
+ * the M-major, GEMM-ready operands of the first SO(2) convolution.
+ * Replaces ExecutionBackend.node_to_edge_wigner_permute
+ * (src/fairchem/core/models/uma/nn/execution_backends.py:160-182) and, with `radial` != NULL,
+ * UMASFastGPUBackend.fused_node_to_edge_conv1_pack (execution_backends.py:432-461; Triton kernel
+ * wigner_conv1_fused_fwd_kernel, src/fairchem/core/models/uma/triton/kernels.py:1589).
+ *   x        [N, 9, C]         node features
+ *   src,tgt  [E] int32         node index of the edge's source / target
+ *   wig      [E, 35]           compact Wigner-D (edge frame <- global frame)
+ *   radial   [E, 6*2C] or NULL per-edge radial weights: [3*2C | 2*2C | 2C] for m = 0,1,2
+ *   out_m0   [E, 3*2C]         M-major rows 0-2, the m=0 GEMM operand
+ *   out_m1   [E, 2, 2*2C]      rows 3-4 (real pair) and 5-6 (imaginary pair), the m=1 operand
+ *   out_m2   [E, 2, 2C]        rows 7 and 8, the m=2 operand
+ */
+int fcb200_gather_rotate_fwd(const float* x, const int32_t* src, const int32_t* tgt, const float* wig,
+                             const float* radial, float* out_m0, float* out_m1, float* out_m2, int64_t num_edges,
+                             int64_t num_nodes, int32_t channels, void* stream);
+
+/*
+ * Rotate edge messages back to the global frame and sum them into their target nodes with a
+ * segmented (CSR) reduction: one warp owns one target node, no atomics, fixed summation order.
+ * Replaces ExecutionBackend.permute_wigner_inv_edge_to_node (execution_backends.py:184-215) and
+ * UMASFastGPUBackend.fused_conv2_inv_edge_to_node (execution_backends.py:463-507; Triton kernel
+ * wigner_inv_conv2_fused_fwd_kernel, triton/kernels.py:1964, followed by ATen index_add_).
+ *   msg      [E, 9, C]   M-major edge messages
+ *   winv     [E, 35]     compact inverse rotation with the envelope folded in
+ *   row_ptr  [N+1] int32 CSR offsets by target
+ *   out      [N, 9, C]   L-major node rows (every row is written; empty segments give zeros)
+ */
+int fcb200_rotate_back_reduce_fwd(const float* msg, const float* winv, const int32_t* row_ptr, float* out,
+                                  int64_t num_edges, int64_t num_nodes, int32_t channels, void* stream);
+
+/*
+ * Edge-degree embedding: rotate the m=0 radial coefficients of every edge to the global frame,
+ * segment-sum by target, scale by 1/rescale and add to x_in.
+ * Replaces ExecutionBackend.edge_degree_scatter (execution_backends.py:217-263).
+ *   radial3  [E, 3, C]   m=0 coefficients (l = 0,1,2)
+ *   x_in     [N, 9, C] or NULL
+ *   out      [N, 9, C]   x_in + sum/rescale
+ */
+int fcb200_edge_degree_fwd(const float* radial3, const float* winv, const int32_t* row_ptr, const float* x_in,
+                           float* out, float rescale, int64_t num_edges, int64_t num_nodes, int32_t channels,
+                           void* stream);
+
+/* ---------------------------------------------------------------- edge block, backward */
+
+/*
+ * Backward of fcb200_gather_rotate_fwd w.r.t. x (per edge, before the node reduction), wig and
+ * radial.  Replaces wigner_conv1_fused_bwd_kernel (triton/kernels.py:1697) /
+ * node_to_edge_wigner_permute_bwd_dx_kernel (triton/kernels.py:573) plus the torch.bmm for dW
+ * (src/fairchem/core/models/uma/triton/node_to_edge_wigner_permute.py:148-167).
+ *   grad_m0/1/2  gradients of the three forward outputs (same shapes)
+ *   g_src      [E, 9, C]   out: W^T grad (source half), L-major, to be summed by source node
+ *   g_tgt      [E, 9, C]   out: W^T grad (target half), L-major, to be summed by target node
+ *   grad_wig   [E, 35]     out
+ *   grad_radial[E, 6*2C]   out, or NULL when radial == NULL
+ */
+int fcb200_gather_rotate_bwd(const float* grad_m0, const float* grad_m1, const float* grad_m2, const float* x,
+                             const int32_t* src, const int32_t* tgt, const float* wig, const float* radial,
+                             float* g_src, float* g_tgt, float* grad_wig, float* grad_radial, int64_t num_edges,
+                             int64_t num_nodes, int32_t channels, void* stream);
+
+/*
+ * Backward of fcb200_rotate_back_reduce_fwd: grad_msg = Winv^T grad_out[tgt] (M-major) and
+ * grad_winv = sum_c grad_out[tgt] (x) msg on the block entries.  Replaces
+ * permute_wigner_inv_edge_to_node_bwd_dx/_bwd_dw kernels (triton/kernels.py:1181, 1334) and
+ * wigner_inv_conv2_fused_bwd_kernel (triton/kernels.py:2015).
+ *   msg may be NULL together with grad_winv when only grad_msg is wanted.
+ */
+int fcb200_rotate_back_bwd(const float* grad_out, const float* msg, const float* winv, const int32_t* tgt,
+                           float* grad_msg, float* grad_winv, int64_t num_edges, int64_t num_nodes,
+                           int32_t channels, void* stream);
+
+/* Backward of fcb200_edge_degree_fwd w.r.t. radial3 and winv (grad w.r.t. x_in is grad_out). */
+int fcb200_edge_degree_bwd(const float* grad_out, const float* radial3, const float* winv, const int32_t* tgt,
+                           float* grad_radial3, float* grad_winv, float rescale, int64_t num_edges,
+                           int64_t num_nodes, int32_t channels, void* stream);
+
+/*
+ * Segmented sum of per-edge rows into node rows:
+ *   out[oi(n)] (+)= scale * sum_{k in [ptr[n], ptr[n+1])} rows[perm ? perm[k] : k],  oi(n) = out_index ? out_index[n] : n.
+ * The atomic-free replacement of the index_add_ calls in the reference's backward
+ * (src/fairchem/core/models/uma/triton/fused_wigner.py:228-236).  out_index entries must be distinct;
+ * accumulate != 0 adds to the existing row.  `width` floats per row.
+ */
+int fcb200_segment_sum(const float* rows, const int32_t* ptr, const int32_t* perm, const int32_t* out_index, float* out,
+                       int32_t accumulate, float scale, int64_t num_segments, int64_t width, void* stream);
+
+/* ---------------------------------------------------------------- SO(2) activation glue */
+
+/*
+ * Complex combine of the m>0 GEMM outputs, gate activation and packing for the second SO(2)
+ * convolution, in one pass.  Replaces SO2_m_Conv.forward's combine
+ * (src/fairchem/core/models/uma/nn/so2_layers.py:72-80), torch.cat in SO2_Convolution.forward
+ * (so2_layers.py:642) and GateActivation.forward (src/fairchem/core/models/uma/nn/activation.py:146-165).
+ *   y0 [E, 2H + 3H]  fc_m0 output: [gate scalars 2H | m0 rows 3H]
+ *   y1 [E, 2, 4H]    m=1 GEMM output rows (real-in, imag-in), columns [r(2H) | i(2H)]
+ *   y2 [E, 2, 2H]    m=2 GEMM output
+ *   out_m0 [E,3H], out_m1 [E,2,2H], out_m2 [E,2,H]: gated M-major rows as the operands of the second convolution
+ */
+int fcb200_so2_gate_fwd(const float* y0, const float* y1, const float* y2, float* out_m0, float* out_m1,
+                        float* out_m2, int64_t num_edges, int32_t hidden, void* stream);
+/* Backward of fcb200_so2_gate_fwd: grads of y0, y1, y2 from the output grads (forward inputs are re-read). */
+int fcb200_so2_gate_bwd(const float* grad_m0, const float* grad_m1, const float* grad_m2, const float* y0,
+                        const float* y1, const float* y2, float* g0, float* g1, float* g2, int64_t num_edges,
+                        int32_t hidden, void* stream);
+/*
+ * Complex combine after the second SO(2) convolution: z0 [E,3C], z1 [E,2,4C], z2 [E,2,2C] -> out [E,9,C]
+ * (so2_layers.py:72-80, 642), and its backward.
+ */
+int fcb200_so2_combine_fwd(const float* z0, const float* z1, const float* z2, float* out, int64_t num_edges,
+                           int32_t channels, void* stream);
+int fcb200_so2_combine_bwd(const float* grad_out, float* g0, float* g1, float* g2, int64_t num_edges,
+                           int32_t channels, void* stream);
+
+/* ---------------------------------------------------------------- edge geometry */
+
+/*
+ * Per-edge geometry from positions: edge vector, length, polynomial envelope (p = 5), Gaussian
+ * distance basis and the compact Wigner-D of the rotation edge -> +Y (roll angle gamma).
+ * Replaces get_pbc_distances (src/fairchem/core/graph/compute.py:75-113), axis_angle_wigner_hybrid
+ * for l <= 2 (src/fairchem/core/models/uma/common/quaternion/wigner_d_hybrid.py:134-205),
+ * PolynomialEnvelope and GaussianSmearing (src/fairchem/core/models/uma/nn/radial.py:22-58).
+ *   pos [N,3]; src,tgt [E] int32; shift [E,3] = cell_offsets @ cell (or NULL); gamma [E] or NULL (= 0)
+ *   vec [E,3], dist [E], env [E], wig [E,35], gauss [E, num_basis] (any of the outputs may be NULL)
+ */
+int fcb200_edge_geometry_fwd(const float* pos, const int32_t* src, const int32_t* tgt, const float* shift,
+                             const float* gamma, float* vec, float* dist, float* env, float* wig, float* gauss,
+                             float cutoff, int32_t num_basis, float basis_start, float basis_stop,
+                             float basis_width, int64_t num_edges, int64_t num_nodes, void* stream);
+/*
+ * Backward: d(vec)[E,3] = J^T (grad_wig, grad_env, grad_gauss, grad_dist), by forward-mode
+ * differentiation of the same code in the three components of the edge vector.  The caller
+ * turns grad_vec into forces with two segmented sums (+ by source, - by target).
+ * Replaces the autograd replay of the modules cited above (src/fairchem/core/models/uma/outputs.py:137-162).
+ */
+int fcb200_edge_geometry_bwd(const float* pos, const int32_t* src, const int32_t* tgt, const float* shift,
+                             const float* gamma, const float* grad_wig, const float* grad_env,
+                             const float* grad_gauss, const float* grad_dist, float* grad_vec, float cutoff,
+                             int32_t num_basis, float basis_start, float basis_stop, float basis_width,
+                             int64_t num_edges, int64_t num_nodes, void* stream);
+
+/* ---------------------------------------------------------------- radius graph (cell list) */
+
+/*
+ * Periodic radius graph with the reference's float32 membership rule, as integer cell-list
+ * kernels.  Replaces radius_graph_pbc_v2 and get_max_neighbors_mask
+ * (src/fairchem/core/graph/radius_graph_pbc.py:412-813, 74-189).  The host side
+ * (fairchem_b200/graph.py) sizes the buffers between phases.
+ *
+ * System table `sys` [B, FCB200_SYS_WORDS] int32/float32 words per system:
+ *   0 atom_begin  1 atom_end  2..4 reps (images -rep..rep per lattice vector)  5 num_images
+ *   6 source_begin (exclusive prefix of natoms*num_images)  7 grid_begin (first cell of its grid)
+ *   8..10 grid dims  11..13 grid origin (float bits)  14 inv_cell_size (float bits)
+ *   15..23 cell matrix row-major (float bits)
+ */
+#define FCB200_SYS_WORDS 24
+
+/* Phase 1: count image-replicated source atoms per grid cell (cell_count must be zeroed). */
+int fcb200_rg_count_sources(const float* pos, const int32_t* sys, int32_t num_systems, int64_t num_sources,
+                            int32_t* cell_count, int32_t* source_cell, void* stream);
+/* Exclusive scan of int32 counts into ptr[n+1] (single launch; n <= 2^31-1).  Also usable for CSR offsets. */
+int fcb200_exclusive_scan_i32(const int32_t* counts, int32_t* ptr, int64_t n, void* stream);
+/* Phase 2: place sources in their cell bucket, bucket entries sorted by source id.
+ * bucket [num_kept_sources] float4 = (x, y, z, source id bits); cell_fill must be zeroed. */
+int fcb200_rg_fill_buckets(const float* pos, const int32_t* sys, int32_t num_systems, int64_t num_sources,
+                           const int32_t* source_cell, const int32_t* cell_ptr, int32_t* cell_fill, float* bucket,
+                           int64_t num_cells, void* stream);
+/*
+ * Phase 3 (two passes): candidates of every target within the radius.  Pass A: cand_ptr == NULL,
+ * writes cand_count[t].  Pass B: cand_ptr given, writes cand_id / cand_d2 in a fixed order.
+ *   targets [T] int32 atom ids (or NULL = all atoms), target_sys [T] int32 system of each target
+ */
+int fcb200_rg_search(const float* pos, const int32_t* sys, const int32_t* targets, const int32_t* target_sys,
+                     int64_t num_targets, const int32_t* cell_ptr, const float* bucket, float radius_sq,
+                     int32_t* cand_count, const int32_t* cand_ptr, int32_t* cand_id, float* cand_d2, void* stream);
+/*
+ * Phase 4: max-neighbour rule per target (non-strict: keep d2 <= d2_sorted[k] + 0.01f when a target
+ * has more than k candidates).  Pass A: edge_ptr == NULL, writes keep_count[t].  Pass B: writes the
+ * kept edges: src/tgt atom ids (int64, the reference's edge_index rows), cell offsets [E,3] int32.
+ */
+int fcb200_rg_select(const int32_t* sys, const int32_t* targets, const int32_t* target_sys, int64_t num_targets,
+                     const int32_t* cand_ptr, const int32_t* cand_id, const float* cand_d2, int32_t max_neighbors,
+                     int32_t* keep_count, const int32_t* edge_ptr, int64_t* edge_src, int64_t* edge_tgt,
+                     int32_t* edge_offsets, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FAIRCHEM_B200_H */

@@ -1,0 +1,243 @@
+"""GPU parity of every edge-block kernel against the CPU oracle's dense formulas (through the C ABI)."""
+
+import numpy as np
+import pytest
+import torch
+
+from oracle import escn_md_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+M2L = [0, 2, 6, 3, 7, 1, 5, 8, 4]
+FWD_TOL = dict(rtol=1e-4, atol=1e-4)  # the reference's own kernel-vs-PyTorch tolerance (test_execution_backends.py:435-463)
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from fairchem_b200 import ops as _ops
+
+    return _ops
+
+
+def dense_from_compact(w):
+    """[E,35] -> block-diagonal [E,9,9]."""
+    e = w.shape[0]
+    d = torch.zeros(e, 9, 9, dtype=w.dtype, device=w.device)
+    d[:, 0, 0] = w[:, 0]
+    d[:, 1:4, 1:4] = w[:, 1:10].view(e, 3, 3)
+    d[:, 4:9, 4:9] = w[:, 10:35].view(e, 5, 5)
+    return d
+
+
+def compact_from_dense(d):
+    e = d.shape[0]
+    return torch.cat([d[:, 0, 0].view(e, 1), d[:, 1:4, 1:4].reshape(e, 9), d[:, 4:9, 4:9].reshape(e, 25)], dim=1)
+
+
+def make_case(n, e, c, seed, device="cuda", dtype=torch.float32):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(n, 9, c, generator=g, dtype=dtype)
+    tgt = torch.sort(torch.randint(0, n, (e,), generator=g)).values
+    src = torch.randint(0, n, (e,), generator=g)
+    vec = torch.randn(e, 3, generator=g, dtype=dtype)
+    wig = compact_from_dense(O.wigner_blocks(O.edge_quaternion(vec), 2))
+    return x.to(device), src.to(device), tgt.to(device), wig.to(device), g
+
+
+def ref_gather_rotate(x, src, tgt, wig, radial):
+    """M-major rotate of cat(x[src], x[tgt]) (execution_backends.py:160-182), radial per so2_layers.py:617-638."""
+    d = dense_from_compact(wig)[:, M2L, :]
+    msg = torch.bmm(d, torch.cat([x[src], x[tgt]], dim=2))  # [E,9,2C]
+    e, c2 = msg.shape[0], msg.shape[2]
+    if radial is not None:
+        r0, r1, r2 = radial[:, :3 * c2], radial[:, 3 * c2:5 * c2], radial[:, 5 * c2:]
+        m0 = msg[:, :3].reshape(e, -1) * r0
+        m1 = msg[:, 3:7].reshape(e, 2, -1) * r1.unsqueeze(1)
+        m2 = msg[:, 7:9].reshape(e, 2, -1) * r2.unsqueeze(1)
+    else:
+        m0, m1, m2 = msg[:, :3].reshape(e, -1), msg[:, 3:7].reshape(e, 2, -1), msg[:, 7:9].reshape(e, 2, -1)
+    return m0, m1, m2
+
+
+@pytest.mark.parametrize("n,e,c", [(16, 32, 128), (7, 1, 128), (40, 333, 256), (5, 64, 128)])
+@pytest.mark.parametrize("with_radial", [False, True])
+def test_gather_rotate_forward_backward(ops, n, e, c, with_radial):
+    x, src, tgt, wig, g = make_case(n, e, c, 1)
+    radial = torch.randn(e, 12 * c, generator=g).cuda() if with_radial else None
+    graph = ops.EdgeGraph(src, tgt, n)
+    xa, wa = x.clone().requires_grad_(True), wig.clone().requires_grad_(True)
+    ra = radial.clone().requires_grad_(True) if with_radial else None
+    out = ops.GatherRotate.apply(xa, wa, ra, graph)
+    xb, wb = x.double().requires_grad_(True), wig.double().requires_grad_(True)
+    rb = radial.double().requires_grad_(True) if with_radial else None
+    ref = ref_gather_rotate(xb, src, tgt, wb, rb)
+    cot = [torch.randn(o.shape, generator=g).cuda() for o in out]
+    for o, r in zip(out, ref):
+        torch.testing.assert_close(o, r.float(), **FWD_TOL)
+    ins_a = [xa, wa] + ([ra] if with_radial else [])
+    ins_b = [xb, wb] + ([rb] if with_radial else [])
+    ga = torch.autograd.grad(out, ins_a, cot)
+    gb = torch.autograd.grad(ref, ins_b, [t.double() for t in cot])
+    for a, b in zip(ga, gb):
+        scale = max(1.0, b.abs().max().item())
+        torch.testing.assert_close(a, b.float(), rtol=1e-4, atol=2e-4 * scale)
+
+
+@pytest.mark.parametrize("n,e,c", [(16, 32, 128), (9, 0, 128), (40, 333, 256), (3, 200, 128)])
+def test_rotate_back_reduce_forward_backward(ops, n, e, c):
+    x, src, tgt, wig, g = make_case(n, max(e, 1), c, 2)
+    if e == 0:
+        src, tgt, wig = src[:0], tgt[:0], wig[:0]
+    msg = torch.randn(e, 9, c, generator=g).cuda()
+    env = torch.rand(e, generator=g).cuda()
+    winv = compact_from_dense(dense_from_compact(wig).transpose(1, 2)) * env[:, None] if e else wig
+    graph = ops.EdgeGraph(src, tgt, n)
+    ma, wa = msg.clone().requires_grad_(True), winv.clone().requires_grad_(True)
+    out = ops.RotateBackReduce.apply(ma, wa, graph)
+    mb, wb = msg.double().requires_grad_(True), winv.double().requires_grad_(True)
+    rot = torch.bmm(dense_from_compact(wb)[:, :, M2L], mb)  # [E,9(L),C]
+    ref = torch.zeros(n, 9, c, dtype=torch.float64, device="cuda").index_add(0, tgt, rot)
+    torch.testing.assert_close(out, ref.float(), **FWD_TOL)
+    if e == 0:
+        return
+    cot = torch.randn(n, 9, c, generator=g).cuda()
+    ga = torch.autograd.grad(out, [ma, wa], cot)
+    gb = torch.autograd.grad(ref, [mb, wb], cot.double())
+    for a, b in zip(ga, gb):
+        torch.testing.assert_close(a, b.float(), rtol=1e-4, atol=2e-4 * max(1.0, b.abs().max().item()))
+
+
+@pytest.mark.parametrize("n,e,c", [(16, 32, 128), (40, 333, 256)])
+def test_edge_degree_forward_backward(ops, n, e, c):
+    x, src, tgt, wig, g = make_case(n, e, c, 3)
+    r3 = torch.randn(e, 3, c, generator=g).cuda()
+    winv = compact_from_dense(dense_from_compact(wig).transpose(1, 2)) * torch.rand(e, 1, generator=g).cuda()
+    graph = ops.EdgeGraph(src, tgt, n)
+    xa, ra, wa = x.clone().requires_grad_(True), r3.clone().requires_grad_(True), winv.clone().requires_grad_(True)
+    out = ops.EdgeDegree.apply(xa, ra, wa, graph, 5.0)
+    xb, rb, wb = x.double().requires_grad_(True), r3.double().requires_grad_(True), winv.double().requires_grad_(True)
+    # execution_backends.py:247-263 with the m=0 columns (L indices 0, 2, 6)
+    emb = torch.bmm(dense_from_compact(wb)[:, :, [0, 2, 6]], rb)
+    ref = xb.index_add(0, tgt, emb / 5.0)
+    torch.testing.assert_close(out, ref.float(), **FWD_TOL)
+    cot = torch.randn(n, 9, c, generator=g).cuda()
+    ga = torch.autograd.grad(out, [xa, ra, wa], cot)
+    gb = torch.autograd.grad(ref, [xb, rb, wb], cot.double())
+    for a, b in zip(ga, gb):
+        torch.testing.assert_close(a, b.float(), rtol=1e-4, atol=2e-4 * max(1.0, b.abs().max().item()))
+
+
+def test_backend_ops_match_reference_golden(ops, golden):
+    """Outputs of the reference's ExecutionBackend ops stored by tests/golden/make_golden.py."""
+    g = golden("backend_ops.npz")
+    x = torch.tensor(g["x"]).cuda()
+    ei = torch.tensor(g["edge_index"]).cuda()
+    wig = compact_from_dense(torch.tensor(g["wigner"])).cuda()
+    env = torch.tensor(g["env"]).cuda()
+    graph = ops.EdgeGraph(ei[0], ei[1], x.shape[0])
+    m0, m1, m2 = ops.GatherRotate.apply(x, wig, None, graph)
+    e = ei.shape[1]
+    msg = torch.cat([m0.view(e, 3, -1), m1.view(e, 4, -1), m2.view(e, 2, -1)], dim=1)
+    torch.testing.assert_close(msg.cpu(), torch.tensor(g["msg"]), **FWD_TOL)
+    winv = compact_from_dense(dense_from_compact(wig).transpose(1, 2)) * env[:, None]
+    back = ops.RotateBackReduce.apply(torch.tensor(g["y"]).cuda(), winv, graph)
+    torch.testing.assert_close(back.cpu(), torch.tensor(g["back"]), **FWD_TOL)
+    deg = ops.EdgeDegree.apply(x, torch.tensor(g["rad"]).cuda().view(e, 3, -1), winv, graph, 5.0)
+    torch.testing.assert_close(deg.cpu(), torch.tensor(g["deg"]), **FWD_TOL)
+
+
+@pytest.mark.parametrize("width,nseg", [(1152, 13), (3, 50), (128, 1), (36, 7)])
+def test_segment_sum(ops, width, nseg):
+    g = torch.Generator().manual_seed(4)
+    k = 97
+    rows = torch.randn(k, width, generator=g).cuda()
+    seg = torch.sort(torch.randint(0, nseg, (k,), generator=g)).values.cuda()
+    perm = torch.randperm(k, generator=g).cuda()
+    ptr = torch.zeros(nseg + 1, dtype=torch.int32, device="cuda")
+    ptr[1:] = torch.cumsum(torch.bincount(seg, minlength=nseg), 0)
+    out = ops.segment_sum(rows, ptr, perm.to(torch.int32), nseg)
+    ref = torch.zeros(nseg, width, device="cuda").index_add(0, seg, rows[perm])
+    torch.testing.assert_close(out, ref, rtol=1e-5, atol=1e-5)
+    # indexed + accumulate + scale
+    base = torch.randn(2 * nseg, width, generator=g).cuda()
+    idx = torch.randperm(2 * nseg, generator=g)[:nseg].to(torch.int32).cuda()
+    got = ops.segment_sum(rows, ptr, None, nseg, out=base.clone(), out_index=idx, accumulate=True, scale=-2.0)
+    want = base.clone()
+    want[idx.long()] += -2.0 * torch.zeros(nseg, width, device="cuda").index_add(0, seg, rows)
+    torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-5)
+
+
+def test_so2_middle_matches_oracle_convolutions(ops):
+    """GEMMs + combine + gate + GEMMs + combine == oracle SO2 conv -> gate -> SO2 conv (so2_layers.py:600-647)."""
+    from fairchem_b200 import backbone as B
+
+    torch.manual_seed(0)
+    c, h, e = 128, 128, 77
+    ew = B.Edgewise(c, h, 2, 2, [320, 128, 128]).cuda()
+    g = torch.Generator().manual_seed(5)
+    msg = torch.randn(e, 9, 2 * c, generator=g).cuda()
+    m = [msg[:, :3].reshape(e, -1).clone().requires_grad_(True), msg[:, 3:7].reshape(e, 2, -1).clone().requires_grad_(True),
+         msg[:, 7:9].reshape(e, 2, -1).clone().requires_grad_(True)]
+    out = B._so2_middle(ew, *m)
+    sd = {k: v.detach().double().cpu() for k, v in ew.state_dict().items()}
+    md = msg.double().cpu().requires_grad_(True)
+    y, gating = O.so2_convolution(sd, "so2_conv_1.", md, None, [3, 2, 1], h, 2 * h)
+    y = O.gate_activation(gating, y, [0, 1, 0, 1, 0, 1, 1, 1], 2)
+    ref, _ = O.so2_convolution(sd, "so2_conv_2.", y, None, [3, 2, 1], c, 0)
+    torch.testing.assert_close(out.cpu(), ref.float(), rtol=1e-4, atol=1e-4)
+    cot = torch.randn(e, 9, c, generator=g)
+    ga = torch.autograd.grad(out, m, cot.cuda())
+    (gb,) = torch.autograd.grad(ref, md, cot.double())
+    got = torch.cat([ga[0].view(e, 3, -1), ga[1].view(e, 4, -1), ga[2].view(e, 2, -1)], dim=1).cpu()
+    torch.testing.assert_close(got, gb.float(), rtol=1e-4, atol=1e-4 * max(1.0, gb.abs().max().item()))
+
+
+def _geometry_inputs(golden):
+    g = golden("wigner.npz")
+    vec = torch.tensor(g["vec"])
+    e = vec.shape[0]
+    pos = torch.cat([torch.zeros(1, 3), vec], dim=0)  # edge k: source k+1, target 0
+    src = torch.arange(1, e + 1)
+    tgt = torch.zeros(e, dtype=torch.long)
+    return g, pos, src, tgt
+
+
+@pytest.mark.parametrize("gname", ["g0", "g1"])
+def test_edge_geometry_matches_reference_wigner(ops, golden, gname):
+    g, pos, src, tgt = _geometry_inputs(golden)
+    graph = ops.EdgeGraph(src.cuda(), tgt.cuda(), pos.shape[0])
+    gamma = torch.tensor(g[f"{gname}_gamma"]).cuda()
+    p = pos.cuda().requires_grad_(True)
+    vec, dist, env, wig, gauss = ops.EdgeGeometry.apply(p, None, gamma, graph, 6.0, 64, 0.0, 6.0, 2.0)
+    torch.testing.assert_close(vec.cpu(), torch.tensor(g["vec"]), rtol=0, atol=1e-6)
+    torch.testing.assert_close(dense_from_compact(wig).cpu(), torch.tensor(g[f"{gname}_wigner"]), rtol=0, atol=5e-6)
+    # other outputs against the oracle's formulas
+    d = torch.tensor(g["vec"]).norm(dim=-1)
+    torch.testing.assert_close(dist.cpu(), d, rtol=1e-6, atol=1e-6)
+    torch.testing.assert_close(env.cpu(), O.envelope(d / 6.0), rtol=1e-5, atol=1e-6)
+    torch.testing.assert_close(gauss.cpu(), O.gaussian_smearing(d, 0.0, 6.0, 64, 2.0), rtol=1e-4, atol=1e-6)
+    # backward through the Wigner entries against the reference's autograd
+    cot = compact_from_dense(torch.tensor(g[f"{gname}_cotangent"])).cuda()
+    (gp,) = torch.autograd.grad((wig * cot).sum(), p)
+    ref = torch.tensor(g[f"{gname}_grad_vec"])
+    torch.testing.assert_close(gp[1:].cpu(), ref, rtol=1e-3, atol=2e-4 * ref.abs().max().item())
+    torch.testing.assert_close(gp[0].cpu(), -ref.sum(0), rtol=1e-3, atol=1e-3 * ref.abs().max().item())
+
+
+def test_edge_geometry_backward_scalars(ops, golden):
+    g, pos, src, tgt = _geometry_inputs(golden)
+    graph = ops.EdgeGraph(src.cuda(), tgt.cuda(), pos.shape[0])
+    gen = torch.Generator().manual_seed(6)
+    shift = torch.randn(len(src), 3, generator=gen) * 0.1
+    p = pos.cuda().requires_grad_(True)
+    vec, dist, env, wig, gauss = ops.EdgeGeometry.apply(p, shift.cuda(), None, graph, 6.0, 64, 0.0, 6.0, 2.0)
+    cd, ce, cg = (torch.randn(t.shape, generator=gen) for t in (dist, env, gauss))
+    (gp,) = torch.autograd.grad((dist * cd.cuda()).sum() + (env * ce.cuda()).sum() + (gauss * cg.cuda()).sum(), p)
+    pd = pos.double().requires_grad_(True)
+    v = pd[src] - pd[tgt] + shift.double()
+    d = v.norm(dim=-1)
+    loss = (d * cd).sum() + (O.envelope(d / 6.0) * ce).sum() + (O.gaussian_smearing(d, 0.0, 6.0, 64, 2.0) * cg).sum()
+    (ref,) = torch.autograd.grad(loss, pd)
+    torch.testing.assert_close(gp.cpu(), ref.float(), rtol=1e-3, atol=1e-4 * ref.abs().max().item())

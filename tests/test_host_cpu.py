@@ -1,0 +1,123 @@
+"""CPU-only checks of the host side: the C-ABI library, the chunk plan, the system table, weights."""
+
+import os
+import re
+
+import numpy as np
+import pytest
+import torch
+
+from fairchem_b200 import synthetic, weights
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def test_library_exports_every_declared_symbol():
+    from fairchem_b200 import _lib
+
+    header = open(os.path.join(ROOT, "include", "fairchem_b200.h")).read()
+    declared = sorted(set(re.findall(r"^int\s+(fcb200_\w+)\s*\(", header, flags=re.M)))
+    assert len(declared) >= 19
+    lib = _lib.load()
+    for name in declared:
+        assert hasattr(lib, name), f"{name} declared in the header but missing from the library"
+        assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
+    assert sorted(_lib.SIGNATURES) == declared
+    assert lib.fcb200_version() >= 1000
+
+
+def test_ops_refuse_cpu_tensors():
+    from fairchem_b200 import _lib, ops
+
+    x = torch.zeros(2, 9, 128)
+    with pytest.raises(_lib.FairchemB200Error):
+        ops.rotate_back_reduce_fwd_(torch.zeros(1, 9, 128), torch.zeros(1, 35), torch.zeros(3, dtype=torch.int32), x)
+
+
+def test_edge_graph_and_chunk_plan_cover_every_edge_once():
+    from fairchem_b200.backbone import build_chunks
+    from fairchem_b200.ops import EdgeGraph
+
+    g = torch.Generator().manual_seed(0)
+    n, e = 57, 1000
+    tgt = torch.sort(torch.randint(0, n, (e,), generator=g)).values
+    tgt[tgt == 13] = 14  # an empty segment
+    tgt = torch.sort(tgt).values
+    src = torch.randint(0, n, (e,), generator=g)
+    graph = EdgeGraph(src, tgt, n)
+    assert graph.row_ptr[-1] == e and graph.src_ptr[-1] == e
+    assert torch.equal(graph.src[graph.src_perm.long()].long(), torch.sort(src).values)
+    for chunk_edges in (64, 333, 5000):
+        chunks = build_chunks(graph, chunk_edges)
+        seen = torch.zeros(e, dtype=torch.int32)
+        prev_n = 0
+        for ch in chunks:
+            assert ch.n0 >= prev_n and ch.n1 > ch.n0
+            prev_n = ch.n1
+            assert ch.e0 == int(graph.row_ptr[ch.n0]) and ch.e1 == int(graph.row_ptr[ch.n1])
+            assert torch.equal(ch.row_ptr.long(), graph.row_ptr[ch.n0:ch.n1 + 1].long() - ch.e0)
+            seen[ch.e0:ch.e1] += 1
+            # source grouping: every chunk edge appears once, grouped under its own source node
+            local_src = src[ch.e0:ch.e1]
+            assert sorted(ch.src_perm.tolist()) == list(range(ch.e1 - ch.e0))
+            for u in range(ch.src_nodes.shape[0]):
+                ids = ch.src_perm[ch.src_ptr[u]:ch.src_ptr[u + 1]].long()
+                assert bool((local_src[ids] == ch.src_nodes[u]).all())
+            assert ch.src_nodes.unique().numel() == ch.src_nodes.numel()
+            assert int(ch.src_ptr[-1]) == ch.e1 - ch.e0
+        assert bool((seen == 1).all())
+
+
+def test_edge_graph_rejects_unsorted_targets():
+    from fairchem_b200 import _lib
+    from fairchem_b200.ops import EdgeGraph
+
+    with pytest.raises(_lib.FairchemB200Error):
+        EdgeGraph(torch.tensor([0, 1]), torch.tensor([1, 0]), 2)
+
+
+def test_system_table_matches_reference_image_counts():
+    from fairchem_b200.graph import build_system_table
+    from oracle.radius_graph_oracle import image_repeats
+
+    d = synthetic.fcc_cu((4, 4, 4))
+    table, nsrc, ncell = build_system_table(d.pos, d.cell, d.pbc, d.natoms, 6.0)
+    assert table.shape == (1, 24) and table[0, 2:5].tolist() == [1, 1, 1] and table[0, 5] == 27 and nsrc == 256 * 27
+    dims = table[0, 8:11]
+    assert ncell == int(np.prod(dims))
+    # the grid spans the targets' bounding box padded by the radius
+    origin = table.view(np.float32)[0, 11:14]
+    inv_h = table.view(np.float32)[0, 14]
+    assert np.all(origin < d.pos.numpy().min(0) - 6.0) and np.all((d.pos.numpy().max(0) + 6.0 - origin) * inv_h < dims)
+    m = synthetic.molecule_batch(5, seed=2)
+    table, nsrc, _ = build_system_table(m.pos, m.cell, m.pbc, m.natoms, 6.0)
+    assert table[:, 5].tolist() == [1] * 5 and nsrc == int(m.natoms.sum())
+    assert table[:, 0].tolist() == [0] + np.cumsum(m.natoms.numpy())[:-1].tolist()
+    b = 3.58 / 2
+    cell = np.array([[0, b, b], [b, 0, b], [b, b, 0]], dtype=np.float32)
+    assert image_repeats(cell, np.array([True, True, True]), 6.0).tolist() == [3, 3, 3]
+
+
+def test_weights_follow_the_reference_state_dict_contract():
+    sd = weights.random_init_state_dict(weights.UMA_S, 0)
+    assert sd["blocks.0.edge_wise.so2_conv_1.fc_m0.weight"].shape == (640, 768)
+    assert sd["blocks.3.edge_wise.so2_conv_1.so2_m_conv.0.fc.weight"].shape == (512, 512)
+    assert sd["blocks.0.edge_wise.so2_conv_1.so2_m_conv.1.fc.weight"].shape == (256, 256)
+    assert sd["blocks.0.edge_wise.so2_conv_1.rad_func.net.6.weight"].shape == (1536, 128)
+    assert sd["blocks.0.edge_wise.so2_conv_2.so2_m_conv.0.fc.weight"].shape == (512, 256)
+    assert sd["edge_degree_embedding.rad_func.net.6.weight"].shape == (384, 128)
+    assert sum(v.numel() for k, v in sd.items() if not k.startswith("energy_block")) == 6316288
+    sd2 = weights.random_init_state_dict(weights.UMA_S, 0)
+    assert all(torch.equal(sd[k], sd2[k]) for k in sd)
+
+
+def test_backbone_loads_reference_keys():
+    from fairchem_b200.backbone import MLP_EFS_HeadB200, eSCNMDBackboneB200
+
+    bb = eSCNMDBackboneB200(**weights.UMA_S)
+    sd = weights.random_init_state_dict(weights.UMA_S, 1)
+    bsd, hsd = weights.split_head(sd)
+    assert sorted(bb.state_dict().keys()) == sorted(bsd.keys())
+    bb.load_state_dict(bsd, strict=True)
+    MLP_EFS_HeadB200(bb).energy_block.load_state_dict(hsd, strict=True)
+    assert bb.num_params == 6316288
