@@ -35,7 +35,7 @@ SIGNATURES = {
     "fcb200_exclusive_scan_i32": [P, P, I64, P],
     "fcb200_rg_fill_buckets": [P, P, I32, I64, P, P, P, P, I64, P],
     "fcb200_rg_search": [P, P, P, P, I64, P, P, F32, P, P, P, P, P],
-    "fcb200_rg_select": [P, P, P, P, I64, P, P, P, I32, P, P, P, P, P, P],
+    "fcb200_rg_select": [P, P, P, I64, P, P, P, I32, P, P, P, P, P, P],
 }
 
 ERRORS = {-1: "invalid argument (null pointer, negative size or unsupported shape)",

@@ -23,6 +23,17 @@ def test_library_exports_every_declared_symbol():
         assert hasattr(lib, name), f"{name} declared in the header but missing from the library"
         assert name in _lib.SIGNATURES, f"{name} has no ctypes signature"
     assert sorted(_lib.SIGNATURES) == declared
+    # the ctypes argument lists must agree with the header, parameter by parameter
+    ctype_of = {"float": _lib.F32, "int32_t": _lib.I32, "int64_t": _lib.I64}
+    for name, params in re.findall(r"^int\s+(fcb200_\w+)\s*\(([^;]*?)\)\s*;", header, flags=re.M | re.S):
+        params = [q.strip() for q in params.replace("\n", " ").split(",")]
+        if params == ["void"]:
+            params = []
+        want = []
+        for q in params:
+            base = q.replace("const ", "").split()[0]
+            want.append(_lib.P if "*" in q else ctype_of[base])
+        assert _lib.SIGNATURES[name] == want, name
     assert lib.fcb200_version() >= 1000
 
 
