@@ -271,18 +271,78 @@ class _EdgeCtx:
         self.z_src, self.z_tgt = z_src, z_tgt
 
 
+class _GemmState:
+    """How the dense contractions run: 3 = tcgen05 TF32 with the hi/lo split (float32-level accuracy,
+    default), 1 = single-pass tcgen05 TF32 (the counterpart of the reference's ``tf32`` inference
+    setting, src/fairchem/core/units/mlip_unit/api/inference.py:123-226), 0 = cuBLAS float32 through
+    torch (kept for A/B measurements only)."""
+
+    precision = 3
+    status = None          # device int32 raised by the kernel when a bounded wait expires
+    transposed = {}        # id(weight storage, view) -> (weight ref, transposed contiguous copy)
+
+
+def set_gemm_precision(p: int) -> None:
+    if p not in (0, 1, 3):
+        raise ValueError("gemm precision must be 3 (TF32 x3), 1 (TF32) or 0 (cuBLAS float32)")
+    _GemmState.precision = p
+
+
+def _status(device):
+    if _GemmState.status is None or _GemmState.status.device != device:
+        _GemmState.status = torch.zeros(1, dtype=torch.int32, device=device)
+    return _GemmState.status
+
+
+def check_gemm_status() -> None:
+    if _GemmState.status is not None and int(_GemmState.status.item()) != 0:
+        _GemmState.status.zero_()
+        raise RuntimeError("fcb200_gemm_tf32: a bounded wait expired inside the kernel; results are invalid")
+
+
+def _transposed(w: torch.Tensor) -> torch.Tensor:
+    key = (w.data_ptr(), tuple(w.shape), tuple(w.stride()))
+    hit = _GemmState.transposed.get(key)
+    if hit is None or hit[0]._version != w._version:
+        hit = (w, w.detach().t().contiguous())
+        _GemmState.transposed[key] = hit
+    return hit[1]
+
+
+class _LinearTF32(torch.autograd.Function):
+    """y = x @ w^T + b on the tcgen05 GEMM; backward gives dx = dy @ w only (weights are frozen at inference)."""
+
+    @staticmethod
+    def forward(ctx, x, w, bias, precision):
+        x2 = x if x.stride(-1) == 1 else x.contiguous()
+        y = torch.empty(x2.shape[0], w.shape[0], dtype=x2.dtype, device=x2.device)
+        ops.gemm_tf32_(x2, w, bias, y, precision, _status(x2.device))
+        ctx.w, ctx.precision = w, precision
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        gy = gy if gy.stride(-1) == 1 and gy.stride(0) % 4 == 0 else gy.contiguous()
+        gx = torch.empty(gy.shape[0], ctx.w.shape[1], dtype=gy.dtype, device=gy.device)
+        ops.gemm_tf32_(gy, _transposed(ctx.w), None, gx, ctx.precision, _status(gy.device))
+        return gx, None, None, None
+
+
 def _linear(x2d, weight, bias=None):
-    return F.linear(x2d, weight, bias)
+    if _GemmState.precision == 0:
+        return F.linear(x2d, weight, bias)
+    return _LinearTF32.apply(x2d, weight.detach(), None if bias is None else bias.detach(), _GemmState.precision)
 
 
 def _radial(rad: RadialMLP, tables, gauss_c, zs, zt, nb: int):
     """RadialMLP on [gauss | src_emb[z_s] | tgt_emb[z_t]] with the embedding part of the first Linear
     folded into per-element tables."""
     w0 = rad.net[0]
-    pre = F.linear(gauss_c, w0.weight[:, :nb], w0.bias) + tables[0][zs] + tables[1][zt]
+    pre = _linear(gauss_c, w0.weight[:, :nb], w0.bias) + tables[0][zs] + tables[1][zt]
     h = F.silu(F.layer_norm(pre, pre.shape[-1:], rad.net[1].weight, rad.net[1].bias, rad.net[1].eps))
-    h = F.silu(F.layer_norm(rad.net[3](h), h.shape[-1:], rad.net[4].weight, rad.net[4].bias, rad.net[4].eps))
-    return rad.net[6](h)
+    h = _linear(h, rad.net[3].weight, rad.net[3].bias)
+    h = F.silu(F.layer_norm(h, h.shape[-1:], rad.net[4].weight, rad.net[4].bias, rad.net[4].eps))
+    return _linear(h, rad.net[6].weight, rad.net[6].bias)
 
 
 def _so2_middle(ew: Edgewise, m0, m1, m2):
@@ -584,6 +644,7 @@ class MLP_EFS_HeadB200(nn.Module):
             if self.regress_forces:
                 (grad,) = torch.autograd.grad(energy.sum(), data["pos"], create_graph=False)
                 out["forces"] = -grad
+            check_gemm_status()
         return out
 
 

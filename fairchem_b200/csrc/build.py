@@ -67,7 +67,7 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 fh.write(res.stderr)
             relink = True
     if relink or _stale(LIB_PATH, objs):
-        cmd = [nvcc, "-shared", "-o", LIB_PATH, *objs, "-lcudart", "-lcuda"]
+        cmd = [nvcc, "-shared", "-o", LIB_PATH, *objs]  # static cudart; no link-time libcuda
         res = subprocess.run(cmd, capture_output=True, text=True)
         if res.returncode != 0:
             sys.stderr.write(res.stdout + res.stderr)

@@ -9,7 +9,11 @@
 //               (hi = rna(a), lo = rna(a - hi); same swizzled offsets, so the layout is untouched);
 //               afterwards the epilogue: tcgen05.ld of the accumulator, + bias, float4 stores
 // PRECISION 3 issues lo*hi + hi*lo + hi*hi per k-step, which restores float32-level accuracy; PRECISION 1
-// feeds the float32 bits directly (the tensor core reads them as TF32).
+// feeds the float32 bits directly (the tensor core reads them as TF32).  The tensor core truncates
+// (rounds toward zero) each time it adds into the float32 accumulator, a bias that grows with the
+// number of MMAs into one accumulator; the two small correction products therefore go to a second
+// TMEM accumulator (columns 128..255) and the epilogue adds the two, which cuts the truncating adds
+// into the large accumulator by 3x.
 //
 // Every mbarrier wait is bounded (about one second of SM clock); on expiry the kernel raises a
 // flag in shared memory, all roles leave their loops, TMEM is released and *status is set.
@@ -124,6 +128,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                      int k_total, int tiles_n, int32_t* __restrict__ status) {
     using Cfg = GemmCfg<P>;
     constexpr int S = Cfg::kStages;
+    constexpr int kTmemCols = P == 3 ? 2 * BN : BN;  // main accumulator (+ correction accumulator)
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar_base = base + S * Cfg::kStageBytes;
@@ -155,7 +160,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     }
     if (warp == 0) {
         __syncwarp();
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -188,9 +193,9 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     const uint64_t adv = (uint64_t)(j * 2);  // 32 bytes per k-step, in 16-byte units
                     const uint32_t first = (kb > 0 || j > 0) ? 1u : 0u;
                     if (P == 3) {
-                        umma_tf32(tmem_acc, da_lo + adv, dw + adv, first);
-                        umma_tf32(tmem_acc, da + adv, dw_lo + adv, 1u);
-                        umma_tf32(tmem_acc, da + adv, dw + adv, 1u);
+                        umma_tf32(tmem_acc + BN, da_lo + adv, dw + adv, first);
+                        umma_tf32(tmem_acc + BN, da + adv, dw_lo + adv, 1u);
+                        umma_tf32(tmem_acc, da + adv, dw + adv, first);
                     } else {
                         umma_tf32(tmem_acc, da + adv, dw + adv, first);
                     }
@@ -234,7 +239,24 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                       "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                     : "r"(taddr)
                     : "memory");
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (P == 3) {
+                    uint32_t t[32];
+                    asm volatile(
+                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+                        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+                        : "=r"(t[0]), "=r"(t[1]), "=r"(t[2]), "=r"(t[3]), "=r"(t[4]), "=r"(t[5]), "=r"(t[6]), "=r"(t[7]),
+                          "=r"(t[8]), "=r"(t[9]), "=r"(t[10]), "=r"(t[11]), "=r"(t[12]), "=r"(t[13]), "=r"(t[14]), "=r"(t[15]),
+                          "=r"(t[16]), "=r"(t[17]), "=r"(t[18]), "=r"(t[19]), "=r"(t[20]), "=r"(t[21]), "=r"(t[22]), "=r"(t[23]),
+                          "=r"(t[24]), "=r"(t[25]), "=r"(t[26]), "=r"(t[27]), "=r"(t[28]), "=r"(t[29]), "=r"(t[30]), "=r"(t[31])
+                        : "r"(taddr + (uint32_t)BN)
+                        : "memory");
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(t[i]));
+                } else {
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                }
                 if (row < m_total) {
                     float* crow = c + row * ldc;
 #pragma unroll
@@ -252,11 +274,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         }
     }
 
+    __syncwarp();
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (warp == 0) {
         __syncwarp();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)BN) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)kTmemCols) : "memory");
     }
     if (threadIdx.x == 0 && *abort_flag && status) atomicExch(status, 1);
 }

@@ -21,6 +21,57 @@ NS = "fairchem_b200"
 WIG = 35
 
 
+class LaunchProfiler:
+    """Per-kernel accounting for bench.py: CUDA-event time on the launching stream, launch counts and
+    the algorithmic bytes / FLOPs each launch is responsible for.  Install with ``set_profiler``."""
+
+    def __init__(self, timed: bool = True):
+        self.timed = timed
+        self.records = []  # (name, start, end, nbytes, flops, launches)
+
+    def run(self, name, fn, nbytes, flops, launches):
+        if not self.timed:
+            fn()
+            self.records.append((name, None, None, nbytes, flops, launches))
+            return
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        fn()
+        end.record()
+        self.records.append((name, start, end, nbytes, flops, launches))
+
+    def summary(self) -> dict:
+        torch.cuda.synchronize()
+        out = {}
+        for name, start, end, nbytes, flops, launches in self.records:
+            d = out.setdefault(name, {"ms": 0.0, "bytes": 0, "flops": 0, "launches": 0})
+            if start is not None:
+                d["ms"] += start.elapsed_time(end)
+            d["bytes"] += nbytes
+            d["flops"] += flops
+            d["launches"] += launches
+        return out
+
+    @property
+    def launches(self) -> int:
+        return sum(r[5] for r in self.records)
+
+
+_PROFILER: Optional[LaunchProfiler] = None
+
+
+def set_profiler(p: Optional[LaunchProfiler]) -> None:
+    global _PROFILER
+    _PROFILER = p
+
+
+def _launch(name: str, cname: str, args, nbytes: int = 0, flops: int = 0, launches: int = 1) -> None:
+    if _PROFILER is None:
+        _lib.call(cname, *args)
+    else:
+        _PROFILER.run(name, lambda: _lib.call(cname, *args), nbytes, flops, launches)
+
+
 def _p(t: Optional[Tensor]):
     return None if t is None else c_void_p(t.data_ptr())
 
@@ -55,8 +106,10 @@ def gather_rotate_fwd_(x: Tensor, src: Tensor, tgt: Tensor, wig: Tensor, radial:
                        m1: Tensor, m2: Tensor) -> None:
     _chk(x, src, tgt, wig, radial, m0, m1, m2)
     _f32(x, wig, radial, m0, m1, m2)
-    _lib.call("fcb200_gather_rotate_fwd", _p(x), _p(src), _p(tgt), _p(wig), _p(radial), _p(m0), _p(m1), _p(m2),
-              src.shape[0], x.shape[0], x.shape[2], _stream())
+    e, c = src.shape[0], x.shape[2]
+    _launch("gather_rotate_fwd", "fcb200_gather_rotate_fwd",
+            (_p(x), _p(src), _p(tgt), _p(wig), _p(radial), _p(m0), _p(m1), _p(m2), e, x.shape[0], c, _stream()),
+            nbytes=e * (4 * (18 * c + 18 * c + WIG + (12 * c if radial is not None else 0)) + 8), flops=e * 2 * WIG * 2 * c)
 
 
 @torch.library.custom_op(f"{NS}::gather_rotate_bwd", mutates_args=("g_src", "g_tgt", "grad_wig", "grad_radial"))
@@ -65,16 +118,21 @@ def gather_rotate_bwd_(gm0: Tensor, gm1: Tensor, gm2: Tensor, x: Tensor, src: Te
                        grad_radial: Optional[Tensor]) -> None:
     _chk(gm0, gm1, gm2, x, src, tgt, wig, radial, g_src, g_tgt, grad_wig, grad_radial)
     _f32(gm0, gm1, gm2, x, wig, radial, g_src, g_tgt, grad_wig, grad_radial)
-    _lib.call("fcb200_gather_rotate_bwd", _p(gm0), _p(gm1), _p(gm2), _p(x), _p(src), _p(tgt), _p(wig), _p(radial),
-              _p(g_src), _p(g_tgt), _p(grad_wig), _p(grad_radial), src.shape[0], x.shape[0], x.shape[2], _stream())
+    e, c = src.shape[0], x.shape[2]
+    _launch("gather_rotate_bwd", "fcb200_gather_rotate_bwd",
+            (_p(gm0), _p(gm1), _p(gm2), _p(x), _p(src), _p(tgt), _p(wig), _p(radial), _p(g_src), _p(g_tgt), _p(grad_wig),
+             _p(grad_radial), e, x.shape[0], c, _stream()),
+            nbytes=e * (4 * (18 * c * 3 + 2 * WIG + (24 * c if radial is not None else 0)) + 8), flops=e * 6 * WIG * 2 * c)
 
 
 @torch.library.custom_op(f"{NS}::rotate_back_reduce_fwd", mutates_args=("out",))
 def rotate_back_reduce_fwd_(msg: Tensor, winv: Tensor, row_ptr: Tensor, out: Tensor) -> None:
     _chk(msg, winv, row_ptr, out)
     _f32(msg, winv, out)
-    _lib.call("fcb200_rotate_back_reduce_fwd", _p(msg), _p(winv), _p(row_ptr), _p(out), msg.shape[0], out.shape[0],
-              out.shape[2], _stream())
+    e, n, c = msg.shape[0], out.shape[0], out.shape[2]
+    _launch("rotate_back_reduce_fwd", "fcb200_rotate_back_reduce_fwd",
+            (_p(msg), _p(winv), _p(row_ptr), _p(out), e, n, c, _stream()),
+            nbytes=4 * (e * (9 * c + WIG) + n * (9 * c + 1)), flops=e * 2 * WIG * c)
 
 
 @torch.library.custom_op(f"{NS}::rotate_back_bwd", mutates_args=("grad_msg", "grad_winv"))
@@ -82,8 +140,10 @@ def rotate_back_bwd_(grad_out: Tensor, msg: Optional[Tensor], winv: Tensor, tgt:
                      grad_winv: Optional[Tensor]) -> None:
     _chk(grad_out, msg, winv, tgt, grad_msg, grad_winv)
     _f32(grad_out, msg, winv, grad_msg, grad_winv)
-    _lib.call("fcb200_rotate_back_bwd", _p(grad_out), _p(msg), _p(winv), _p(tgt), _p(grad_msg), _p(grad_winv),
-              tgt.shape[0], grad_out.shape[0], grad_out.shape[2], _stream())
+    e, c = tgt.shape[0], grad_out.shape[2]
+    _launch("rotate_back_bwd", "fcb200_rotate_back_bwd",
+            (_p(grad_out), _p(msg), _p(winv), _p(tgt), _p(grad_msg), _p(grad_winv), e, grad_out.shape[0], c, _stream()),
+            nbytes=e * 4 * (9 * c * (3 if msg is not None else 2) + 2 * WIG + 1), flops=e * 4 * WIG * c)
 
 
 @torch.library.custom_op(f"{NS}::edge_degree_fwd", mutates_args=("out",))
@@ -91,8 +151,10 @@ def edge_degree_fwd_(radial3: Tensor, winv: Tensor, row_ptr: Tensor, x_in: Optio
                      rescale: float) -> None:
     _chk(radial3, winv, row_ptr, x_in, out)
     _f32(radial3, winv, x_in, out)
-    _lib.call("fcb200_edge_degree_fwd", _p(radial3), _p(winv), _p(row_ptr), _p(x_in), _p(out), rescale,
-              radial3.shape[0], out.shape[0], out.shape[2], _stream())
+    e, n, c = radial3.shape[0], out.shape[0], out.shape[2]
+    _launch("edge_degree_fwd", "fcb200_edge_degree_fwd",
+            (_p(radial3), _p(winv), _p(row_ptr), _p(x_in), _p(out), rescale, e, n, c, _stream()),
+            nbytes=4 * (e * (3 * c + WIG) + n * (18 * c + 1)), flops=e * 2 * 9 * c)
 
 
 @torch.library.custom_op(f"{NS}::edge_degree_bwd", mutates_args=("grad_radial3", "grad_winv"))
@@ -100,8 +162,10 @@ def edge_degree_bwd_(grad_out: Tensor, radial3: Tensor, winv: Tensor, tgt: Tenso
                      grad_winv: Tensor, rescale: float) -> None:
     _chk(grad_out, radial3, winv, tgt, grad_radial3, grad_winv)
     _f32(grad_out, radial3, winv, grad_radial3, grad_winv)
-    _lib.call("fcb200_edge_degree_bwd", _p(grad_out), _p(radial3), _p(winv), _p(tgt), _p(grad_radial3), _p(grad_winv),
-              rescale, tgt.shape[0], grad_out.shape[0], grad_out.shape[2], _stream())
+    e, c = tgt.shape[0], grad_out.shape[2]
+    _launch("edge_degree_bwd", "fcb200_edge_degree_bwd",
+            (_p(grad_out), _p(radial3), _p(winv), _p(tgt), _p(grad_radial3), _p(grad_winv), rescale, e, grad_out.shape[0], c,
+             _stream()), nbytes=e * 4 * (9 * c + 6 * c + 2 * WIG + 1), flops=e * 4 * 9 * c)
 
 
 @torch.library.custom_op(f"{NS}::segment_sum", mutates_args=("out",))
@@ -109,15 +173,18 @@ def segment_sum_(rows: Tensor, ptr: Tensor, perm: Optional[Tensor], out_index: O
                  accumulate: bool, scale: float, num_segments: int, width: int) -> None:
     _chk(rows, ptr, perm, out_index, out)
     _f32(rows, out)
-    _lib.call("fcb200_segment_sum", _p(rows), _p(ptr), _p(perm), _p(out_index), _p(out), int(accumulate), scale,
-              num_segments, width, _stream())
+    _launch("segment_sum", "fcb200_segment_sum",
+            (_p(rows), _p(ptr), _p(perm), _p(out_index), _p(out), int(accumulate), scale, num_segments, width, _stream()),
+            nbytes=4 * (rows.shape[0] * width + num_segments * width * (2 if accumulate else 1)))
 
 
 @torch.library.custom_op(f"{NS}::so2_gate_fwd", mutates_args=("a0", "a1", "a2"))
 def so2_gate_fwd_(y0: Tensor, y1: Tensor, y2: Tensor, a0: Tensor, a1: Tensor, a2: Tensor, hidden: int) -> None:
     _chk(y0, y1, y2, a0, a1, a2)
     _f32(y0, y1, y2, a0, a1, a2)
-    _lib.call("fcb200_so2_gate_fwd", _p(y0), _p(y1), _p(y2), _p(a0), _p(a1), _p(a2), y0.shape[0], hidden, _stream())
+    _launch("so2_gate_fwd", "fcb200_so2_gate_fwd",
+            (_p(y0), _p(y1), _p(y2), _p(a0), _p(a1), _p(a2), y0.shape[0], hidden, _stream()),
+            nbytes=y0.shape[0] * 4 * hidden * (5 + 8 + 4 + 9))
 
 
 @torch.library.custom_op(f"{NS}::so2_gate_bwd", mutates_args=("g0", "g1", "g2"))
@@ -125,22 +192,26 @@ def so2_gate_bwd_(ga0: Tensor, ga1: Tensor, ga2: Tensor, y0: Tensor, y1: Tensor,
                   g2: Tensor, hidden: int) -> None:
     _chk(ga0, ga1, ga2, y0, y1, y2, g0, g1, g2)
     _f32(ga0, ga1, ga2, y0, y1, y2, g0, g1, g2)
-    _lib.call("fcb200_so2_gate_bwd", _p(ga0), _p(ga1), _p(ga2), _p(y0), _p(y1), _p(y2), _p(g0), _p(g1), _p(g2),
-              y0.shape[0], hidden, _stream())
+    _launch("so2_gate_bwd", "fcb200_so2_gate_bwd",
+            (_p(ga0), _p(ga1), _p(ga2), _p(y0), _p(y1), _p(y2), _p(g0), _p(g1), _p(g2), y0.shape[0], hidden, _stream()),
+            nbytes=y0.shape[0] * 4 * hidden * (9 + 17 + 17))
 
 
 @torch.library.custom_op(f"{NS}::so2_combine_fwd", mutates_args=("out",))
 def so2_combine_fwd_(z0: Tensor, z1: Tensor, z2: Tensor, out: Tensor, channels: int) -> None:
     _chk(z0, z1, z2, out)
     _f32(z0, z1, z2, out)
-    _lib.call("fcb200_so2_combine_fwd", _p(z0), _p(z1), _p(z2), _p(out), z0.shape[0], channels, _stream())
+    _launch("so2_combine_fwd", "fcb200_so2_combine_fwd",
+            (_p(z0), _p(z1), _p(z2), _p(out), z0.shape[0], channels, _stream()), nbytes=z0.shape[0] * 4 * channels * (15 + 9))
 
 
 @torch.library.custom_op(f"{NS}::so2_combine_bwd", mutates_args=("g0", "g1", "g2"))
 def so2_combine_bwd_(grad_out: Tensor, g0: Tensor, g1: Tensor, g2: Tensor, channels: int) -> None:
     _chk(grad_out, g0, g1, g2)
     _f32(grad_out, g0, g1, g2)
-    _lib.call("fcb200_so2_combine_bwd", _p(grad_out), _p(g0), _p(g1), _p(g2), grad_out.shape[0], channels, _stream())
+    _launch("so2_combine_bwd", "fcb200_so2_combine_bwd",
+            (_p(grad_out), _p(g0), _p(g1), _p(g2), grad_out.shape[0], channels, _stream()),
+            nbytes=grad_out.shape[0] * 4 * channels * (15 + 9))
 
 
 @torch.library.custom_op(f"{NS}::edge_geometry_fwd", mutates_args=("vec", "dist", "env", "wig", "gauss"))
@@ -150,8 +221,11 @@ def edge_geometry_fwd_(pos: Tensor, src: Tensor, tgt: Tensor, shift: Optional[Te
                        b_width: float) -> None:
     _chk(pos, src, tgt, shift, gamma, vec, dist, env, wig, gauss)
     _f32(pos, shift, gamma, vec, dist, env, wig, gauss)
-    _lib.call("fcb200_edge_geometry_fwd", _p(pos), _p(src), _p(tgt), _p(shift), _p(gamma), _p(vec), _p(dist), _p(env),
-              _p(wig), _p(gauss), cutoff, num_basis, b_start, b_stop, b_width, src.shape[0], pos.shape[0], _stream())
+    e = src.shape[0]
+    _launch("edge_geometry_fwd", "fcb200_edge_geometry_fwd",
+            (_p(pos), _p(src), _p(tgt), _p(shift), _p(gamma), _p(vec), _p(dist), _p(env), _p(wig), _p(gauss), cutoff,
+             num_basis, b_start, b_stop, b_width, e, pos.shape[0], _stream()),
+            nbytes=e * 4 * (2 + 6 + 3 + 3 + 2 + WIG + num_basis))
 
 
 @torch.library.custom_op(f"{NS}::edge_geometry_bwd", mutates_args=("grad_vec",))
@@ -161,9 +235,11 @@ def edge_geometry_bwd_(pos: Tensor, src: Tensor, tgt: Tensor, shift: Optional[Te
                        b_stop: float, b_width: float) -> None:
     _chk(pos, src, tgt, shift, gamma, grad_wig, grad_env, grad_gauss, grad_dist, grad_vec)
     _f32(pos, shift, gamma, grad_wig, grad_env, grad_gauss, grad_dist, grad_vec)
-    _lib.call("fcb200_edge_geometry_bwd", _p(pos), _p(src), _p(tgt), _p(shift), _p(gamma), _p(grad_wig), _p(grad_env),
-              _p(grad_gauss), _p(grad_dist), _p(grad_vec), cutoff, num_basis, b_start, b_stop, b_width, src.shape[0],
-              pos.shape[0], _stream())
+    e = src.shape[0]
+    _launch("edge_geometry_bwd", "fcb200_edge_geometry_bwd",
+            (_p(pos), _p(src), _p(tgt), _p(shift), _p(gamma), _p(grad_wig), _p(grad_env), _p(grad_gauss), _p(grad_dist),
+             _p(grad_vec), cutoff, num_basis, b_start, b_stop, b_width, e, pos.shape[0], _stream()),
+            nbytes=e * 4 * (2 + 6 + 3 + 3 + 2 + WIG + num_basis))
 
 
 @torch.library.custom_op(f"{NS}::gemm_tf32", mutates_args=("c", "status"))
@@ -173,8 +249,10 @@ def gemm_tf32_(a: Tensor, w: Tensor, bias: Optional[Tensor], c: Tensor, precisio
         if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
             raise _lib.FairchemB200Error("gemm_tf32: need 2-D float32 CUDA operands with unit inner stride")
     _chk(bias, status)
-    _lib.call("fcb200_gemm_tf32", _p(a), a.stride(0), _p(w), w.stride(0), _p(bias), _p(c), c.stride(0), a.shape[0],
-              w.shape[0], a.shape[1], precision, _p(status), _stream())
+    m, n, k = a.shape[0], w.shape[0], a.shape[1]
+    _launch("gemm_tf32", "fcb200_gemm_tf32",
+            (_p(a), a.stride(0), _p(w), w.stride(0), _p(bias), _p(c), c.stride(0), m, n, k, precision, _p(status), _stream()),
+            nbytes=4 * (m * k + n * k + m * n), flops=2 * m * n * k)
 
 
 # ------------------------------------------------------------------------------------------

@@ -226,6 +226,22 @@ int fcb200_rg_select(const int32_t* sys, const int32_t* targets, const int32_t* 
                      int32_t* keep_count, const int32_t* edge_ptr, int64_t* edge_src, int64_t* edge_tgt,
                      int32_t* edge_offsets, void* stream);
 
+/* ---------------------------------------------------------------- dense contraction */
+
+/*
+ * C[M,N] = A[M,K] * W[N,K]^T (+ bias[N]) in float32 through tcgen05 TF32 tensor-core MMAs with
+ * float32 accumulation in tensor memory.  precision = 1: single TF32 pass; precision = 3: the
+ * operands are split into TF32 high and low parts in shared memory and three MMAs are issued
+ * (hi*hi + lo*hi + hi*lo), which restores float32-level accuracy.
+ * Replaces the cuBLAS calls under SO2_Convolution / SO2_m_Conv (so2_layers.py:67-80, 600-647) and
+ * RadialMLP (radial.py:61-86).  lda/ldw/ldc are row strides in floats (multiples of 4);
+ * K a multiple of 32, N a multiple of 16.  `status` is a device int32 the kernel sets non-zero
+ * if a bounded wait expired (the result is then invalid).
+ */
+int fcb200_gemm_tf32(const float* a, int64_t lda, const float* w, int64_t ldw, const float* bias, float* c,
+                     int64_t ldc, int64_t m, int32_t n, int32_t k, int32_t precision, int32_t* status,
+                     void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,66 @@
+"""tcgen05 TF32 GEMM (C = A W^T + b) against a float64 matmul, through the C ABI."""
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from fairchem_b200 import ops as _ops
+
+    return _ops
+
+
+SHAPES = [  # (M, N, K, lda_pad, bias)
+    (128, 128, 32, 0, False),
+    (128, 128, 128, 0, True),
+    (300, 640, 768, 0, True),      # conv1 m=0
+    (514, 512, 512, 0, False),     # conv1 m=1
+    (1000, 64, 128, 0, False),     # narrow N (radial backward into the distance basis)
+    (77, 1536, 128, 0, True),      # radial output layer
+    (260, 128, 72, 8, True),       # K not a multiple of the 32-wide k-block, strided A
+    (4097, 384, 384, 0, True),
+    (1, 128, 64, 0, False),
+]
+
+
+@pytest.mark.parametrize("m,n,k,pad,with_bias", SHAPES)
+@pytest.mark.parametrize("precision", [3, 1])
+def test_gemm_tf32(ops, m, n, k, pad, with_bias, precision):
+    g = torch.Generator().manual_seed(m * 7 + n * 3 + k)
+    a_full = torch.randn(m, k + pad, generator=g).cuda()
+    a = a_full[:, :k]
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).cuda()
+    bias = torch.randn(n, generator=g).cuda() if with_bias else None
+    c = torch.full((m, n), float("nan"), device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.gemm_tf32_(a, w, bias, c, precision, status)
+    torch.cuda.synchronize()
+    assert int(status.item()) == 0, "a bounded wait inside the kernel expired"
+    ref = a.double() @ w.double().t()
+    if with_bias:
+        ref = ref + bias.double()
+    err = (c.double() - ref).abs().max().item()
+    scale = ref.abs().max().item()
+    # 3-pass split: float32-level accuracy (the tensor core's float32 accumulation costs a few ulps per
+    # k-step, so the bound grows with K); single pass: TF32 (10-bit mantissa) accuracy
+    tol = 1e-5 if precision == 3 else 2e-3
+    assert err <= tol * max(scale, 1.0), (err, scale)
+
+
+def test_gemm_matches_fp32_matmul_closely(ops):
+    """The 3-pass result is as close to float64 as cuBLAS float32 is (within a small factor)."""
+    g = torch.Generator().manual_seed(0)
+    a = torch.randn(2048, 768, generator=g).cuda()
+    w = (torch.randn(640, 768, generator=g) / 768 ** 0.5).cuda()
+    c = torch.empty(2048, 640, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.gemm_tf32_(a, w, None, c, 3, status)
+    ref = a.double() @ w.double().t()
+    e_ours = (c.double() - ref).abs().max().item()
+    e_fp32 = ((a @ w.t()).double() - ref).abs().max().item()
+    assert int(status.item()) == 0 and e_ours < 8 * e_fp32 + 1e-6
