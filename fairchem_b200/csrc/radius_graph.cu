@@ -283,6 +283,45 @@ __global__ void __launch_bounds__(256)
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// allocation-free variant of the candidate search
+// ---------------------------------------------------------------------------------------------
+// Scratch of the cell list for fcb200_rg_neighbor_counts_static: counters, offsets and fill cursors
+// for up to kStaticMaxCells grid cells, the cell of each source and the bucket array for up to
+// kStaticMaxSources image-replicated source atoms (about 6 MiB).  Every GPU that loads the library
+// holds this array until the process exits.
+constexpr int64_t kStaticMaxCells = FCB200_STATIC_MAX_CELLS;
+constexpr int64_t kStaticMaxSources = FCB200_STATIC_MAX_SOURCES;
+constexpr int64_t kOffCount = 0;
+constexpr int64_t kOffPtr = kOffCount + (kStaticMaxCells + 64) * 4;
+constexpr int64_t kOffFill = kOffPtr + (kStaticMaxCells + 64) * 4;
+constexpr int64_t kOffSourceCell = kOffFill + (kStaticMaxCells + 64) * 4;
+constexpr int64_t kOffBucket = kOffSourceCell + kStaticMaxSources * 4;
+constexpr int64_t kStaticBytes = kOffBucket + kStaticMaxSources * 16;
+static_assert(kOffBucket % 256 == 0 && kOffPtr % 256 == 0 && kOffFill % 256 == 0 && kOffSourceCell % 256 == 0, "sub-arrays stay aligned");
+
+static __device__ __align__(256) unsigned char g_static_scratch[kStaticBytes];
+
+// In host code the name above is only a handle of the symbol, not an address the GPU can use: the
+// device address has to be asked for, once per device, with that device current.
+constexpr int kMaxDevices = 64;
+static unsigned char* g_static_scratch_addr[kMaxDevices] = {};
+
+static int static_scratch_address(unsigned char** out) {
+    int dev = -1;
+    cudaError_t err = cudaGetDevice(&dev);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    if (dev < 0 || dev >= kMaxDevices) return FCB200_ERANGE;
+    if (g_static_scratch_addr[dev] == nullptr) {
+        void* p = nullptr;
+        err = cudaGetSymbolAddress(&p, g_static_scratch);
+        if (err != cudaSuccess) return static_cast<int>(err);
+        g_static_scratch_addr[dev] = static_cast<unsigned char*>(p);
+    }
+    *out = g_static_scratch_addr[dev];
+    return FCB200_OK;
+}
+
 }  // namespace fcb200
 
 using namespace fcb200;
@@ -346,6 +385,51 @@ int fcb200_rg_select(const int32_t* sys, const int32_t* targets, const int32_t* 
     rg_select_kernel<<<(unsigned)((num_targets + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         sys, targets, target_sys, num_targets, cand_ptr, cand_id, cand_d2, max_neighbors, keep_count, edge_ptr, edge_src, edge_tgt,
         edge_offsets);
+    return launch_status();
+}
+
+int fcb200_rg_neighbor_counts_static(const float* pos, const int32_t* sys, int32_t num_systems, int64_t num_sources,
+                                     int64_t num_cells, const int32_t* targets, const int32_t* target_sys, int64_t num_targets,
+                                     float radius_sq, int32_t* cand_count, void* stream) {
+    if (!pos || !sys || !target_sys || !cand_count || num_systems <= 0 || num_sources < 0 || num_cells < 0 || num_targets < 0)
+        return FCB200_EINVAL;
+    // sizes beyond the built-in scratch are refused, never truncated
+    if (num_sources > kStaticMaxSources || num_cells > kStaticMaxCells) return FCB200_ERANGE;
+    if (num_targets == 0) return FCB200_OK;
+    unsigned char* base = nullptr;
+    int rc = static_scratch_address(&base);  // first call on a device resolves the symbol address
+    if (rc) return rc;
+    int32_t* cell_count = reinterpret_cast<int32_t*>(base + kOffCount);
+    int32_t* cell_ptr = reinterpret_cast<int32_t*>(base + kOffPtr);
+    int32_t* cell_fill = reinterpret_cast<int32_t*>(base + kOffFill);
+    int32_t* source_cell = reinterpret_cast<int32_t*>(base + kOffSourceCell);
+    float4* bucket = reinterpret_cast<float4*>(base + kOffBucket);
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    // the array still holds the previous call's counters: the two that are accumulated into start at zero
+    cudaError_t err = cudaMemsetAsync(cell_count, 0, (size_t)(num_cells + 1) * 4, s);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    err = cudaMemsetAsync(cell_fill, 0, (size_t)(num_cells + 1) * 4, s);
+    if (err != cudaSuccess) return static_cast<int>(err);
+    if (num_sources > 0) {
+        rg_count_sources_kernel<<<(unsigned)((num_sources + 255) / 256), 256, 0, s>>>(pos, sys, num_systems, num_sources, cell_count,
+                                                                                    source_cell);
+        rc = launch_status();
+        if (rc) return rc;
+    }
+    exclusive_scan_kernel<<<1, 1024, 0, s>>>(cell_count, cell_ptr, num_cells);
+    rc = launch_status();
+    if (rc) return rc;
+    if (num_sources > 0 && num_cells > 0) {
+        rg_fill_kernel<<<(unsigned)((num_sources + 255) / 256), 256, 0, s>>>(pos, sys, num_systems, num_sources, source_cell, cell_ptr,
+                                                                           cell_fill, bucket);
+        rc = launch_status();
+        if (rc) return rc;
+        rg_sort_buckets_kernel<<<(unsigned)((num_cells + 255) / 256), 256, 0, s>>>(cell_ptr, bucket, num_cells);
+        rc = launch_status();
+        if (rc) return rc;
+    }
+    rg_search_kernel<<<(unsigned)((num_targets + 7) / 8), 256, 0, s>>>(pos, sys, targets, target_sys, num_targets, cell_ptr, bucket,
+                                                                     radius_sq, cand_count, nullptr, nullptr, nullptr);
     return launch_status();
 }
 

@@ -226,6 +226,33 @@ int fcb200_rg_select(const int32_t* sys, const int32_t* targets, const int32_t* 
                      int32_t* keep_count, const int32_t* edge_ptr, int64_t* edge_src, int64_t* edge_tgt,
                      int32_t* edge_offsets, void* stream);
 
+/*
+ * Allocation-free neighbour counting (no counterpart in the reference; added for embedders).
+ *
+ * Some hosts of this library cannot let it, or themselves, call cudaMalloc inside a time step: an MD
+ * engine that reserved the device memory for its own pools at start-up, or a driver loop that must
+ * not take the device-wide synchronisation an allocation or a free implies.  For them this entry
+ * point runs phases 1-3A above (bin the periodic source images, scan, fill the buckets, count the
+ * candidates of every target within the radius) with the cell-list scratch held in a fixed array
+ * inside the library instead of caller buffers.  It calls no cudaMalloc/cudaFree and no allocating
+ * library routine; the caller still passes inputs and the output.
+ *
+ *   limits      num_sources <= FCB200_STATIC_MAX_SOURCES and num_cells <= FCB200_STATIC_MAX_CELLS
+ *               (about 6 MiB of device memory per GPU that loads the library, held until exit);
+ *               larger sizes return FCB200_ERANGE and launch nothing
+ *   first call  on each device looks up the array's device address (cudaGetSymbolAddress); make that
+ *               call during set-up, before any stream capture
+ *   sharing     all calls on a device use the same array, which keeps the previous call's contents
+ *               (the counters that must start at zero are cleared on the stream first); two calls
+ *               whose work overlaps on the GPU race on it - serialise them on one stream
+ *   cand_count  [num_targets] out: candidates per target, identical to fcb200_rg_search pass A
+ */
+#define FCB200_STATIC_MAX_SOURCES 262144
+#define FCB200_STATIC_MAX_CELLS 65536
+int fcb200_rg_neighbor_counts_static(const float* pos, const int32_t* sys, int32_t num_systems, int64_t num_sources,
+                                     int64_t num_cells, const int32_t* targets, const int32_t* target_sys,
+                                     int64_t num_targets, float radius_sq, int32_t* cand_count, void* stream);
+
 /* ---------------------------------------------------------------- dense contraction */
 
 /*
