@@ -276,6 +276,8 @@ def run_b200(args):
         "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 1e9, 2),
         "energy": float(energy[0]),
     }
+    if args.profile_run:
+        line["profile_run"] = True
     print(json.dumps(line))
 
 
@@ -337,8 +339,10 @@ def main():
     ap.add_argument("--chunk", type=int, default=65536)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--profile-run", action="store_true",
+                    help="for runs under a profiler: allows fewer than 3 warm-up steps; the printed number is not a bench value")
     args = ap.parse_args()
-    if args.warmup < 3 and args.impl == "b200":
+    if args.warmup < 3 and args.impl == "b200" and not args.profile_run:
         args.warmup = 3
     if args.impl == "reference":
         run_reference(args)

@@ -279,7 +279,8 @@ class _GemmState:
 
     precision = 3
     status = None          # device int32 raised by the kernel when a bounded wait expires
-    transposed = {}        # id(weight storage, view) -> (weight ref, transposed contiguous copy)
+    transposed = {}        # (ptr, shape, stride) of a weight view -> (weight ref, transposed contiguous copy)
+    split = {}             # same key -> (weight ref, TF32 high part, TF32 low part)
 
 
 def set_gemm_precision(p: int) -> None:
@@ -309,6 +310,24 @@ def _transposed(w: torch.Tensor) -> torch.Tensor:
     return hit[1]
 
 
+def _split(w: torch.Tensor):
+    key = (w.data_ptr(), tuple(w.shape), tuple(w.stride()))
+    hit = _GemmState.split.get(key)
+    if hit is None or hit[0]._version != w._version:
+        hi, lo = ops.split_tf32(w)
+        hit = (w, hi, lo)
+        _GemmState.split[key] = hit
+    return hit[1], hit[2]
+
+
+def _gemm(x2, w, bias, y, precision):
+    if precision == 3:
+        hi, lo = _split(w)
+        ops.gemm_tf32_(x2, hi, lo, bias, y, 3, _status(x2.device))
+    else:
+        ops.gemm_tf32_(x2, w, None, bias, y, 1, _status(x2.device))
+
+
 class _LinearTF32(torch.autograd.Function):
     """y = x @ w^T + b on the tcgen05 GEMM; backward gives dx = dy @ w only (weights are frozen at inference)."""
 
@@ -316,7 +335,7 @@ class _LinearTF32(torch.autograd.Function):
     def forward(ctx, x, w, bias, precision):
         x2 = x if x.stride(-1) == 1 else x.contiguous()
         y = torch.empty(x2.shape[0], w.shape[0], dtype=x2.dtype, device=x2.device)
-        ops.gemm_tf32_(x2, w, bias, y, precision, _status(x2.device))
+        _gemm(x2, w, bias, y, precision)
         ctx.w, ctx.precision = w, precision
         return y
 
@@ -324,7 +343,7 @@ class _LinearTF32(torch.autograd.Function):
     def backward(ctx, gy):
         gy = gy if gy.stride(-1) == 1 and gy.stride(0) % 4 == 0 else gy.contiguous()
         gx = torch.empty(gy.shape[0], ctx.w.shape[1], dtype=gy.dtype, device=gy.device)
-        ops.gemm_tf32_(gy, _transposed(ctx.w), None, gx, ctx.precision, _status(gy.device))
+        _gemm(gy, _transposed(ctx.w), None, gx, ctx.precision)
         return gx, None, None, None
 
 

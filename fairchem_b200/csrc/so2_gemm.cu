@@ -1,22 +1,28 @@
 // C[M,N] = A[M,K] * W[N,K]^T (+ bias) in float32 on the sm_100a tensor cores (tcgen05, TF32 inputs,
 // float32 accumulation in tensor memory).
 //
-// One CTA computes one 128 x 128 output tile.  Warp roles (192 threads):
-//   warp 0      TMA producer: cp.async.bulk.tensor (no multicast) of a 128x32 A tile and a 128x32 W
-//               tile per k-block into a 128-byte-swizzled shared-memory ring; also owns the TMEM allocation
+// Persistent kernel: one CTA per SM walks over 128 x 128 output tiles (N fastest, so CTAs that run
+// together share A tiles through L2).  Warp roles (320 threads):
+//   warp 0      TMA producer: cp.async.bulk.tensor (no multicast) of 128x32 tiles of A and of the
+//               weights into a 128-byte-swizzled shared-memory ring; owns the TMEM allocation
 //   warp 1      one elected thread issues tcgen05.mma (M=128, N=128, K=8) and commits to mbarriers
-//   warps 2..5  PRECISION 3: split each landed tile into TF32 high and low parts in shared memory
-//               (hi = rna(a), lo = rna(a - hi); same swizzled offsets, so the layout is untouched);
-//               afterwards the epilogue: tcgen05.ld of the accumulator, + bias, float4 stores
-// PRECISION 3 issues lo*hi + hi*lo + hi*hi per k-step, which restores float32-level accuracy; PRECISION 1
-// feeds the float32 bits directly (the tensor core reads them as TF32).  The tensor core truncates
-// (rounds toward zero) each time it adds into the float32 accumulator, a bias that grows with the
-// number of MMAs into one accumulator; the two small correction products therefore go to a second
-// TMEM accumulator (columns 128..255) and the epilogue adds the two, which cuts the truncating adds
-// into the large accumulator by 3x.
+//   warps 2..5  PRECISION 3 only: write the TF32 low part of each landed A tile next to it
+//   warps 6..9  epilogue: tcgen05.ld of a finished accumulator, + bias, float4 stores; runs while the
+//               next tile's main loop fills the other accumulator (TMEM is double buffered)
 //
-// Every mbarrier wait is bounded (about one second of SM clock); on expiry the kernel raises a
-// flag in shared memory, all roles leave their loops, TMEM is released and *status is set.
+// PRECISION 1 feeds float32 bits to the tensor core, which reads them as TF32 (low 13 mantissa bits
+// ignored).  PRECISION 3 restores float32-level accuracy with three products per k-step,
+//     a_lo*w_hi + a_hi*w_lo + a_hi*w_hi,
+// where w_hi/w_lo are the weights split once on the device (fcb200_split_tf32: round-to-nearest hi,
+// remainder lo) and A is split on the fly: the tensor core's own view of the float32 word is a_hi, and
+// a_lo = tf32(a - a_hi) is written to a second tile at the same swizzled offsets, so the UMMA layout
+// is untouched and only the low part costs shared-memory writes.
+// The tensor core truncates (rounds toward zero) every time it adds into the float32 accumulator, a
+// bias that grows with the number of MMAs into one accumulator; the two small correction products
+// therefore go to a second accumulator and the epilogue adds the two.
+//
+// Every mbarrier wait is bounded (about one second of SM clock); on expiry the kernel raises a flag in
+// shared memory, all roles leave their loops, TMEM is released and *status is set.
 #include <cuda.h>
 
 #include "common.cuh"
@@ -24,14 +30,16 @@
 namespace fcb200 {
 
 constexpr int BM = 128, BN = 128, BK = 32;
-constexpr int kTileBytes = BM * BK * 4;  // 16 KiB, A and W tiles alike
-constexpr int kGemmThreads = 192;
+constexpr int kTileBytes = BM * BK * 4;  // 16 KiB: A, A_lo, W_hi and W_lo tiles alike
+constexpr int kGemmThreads = 320;
 constexpr long long kWaitCycles = 1LL << 31;  // ~1.1 s at 1.9 GHz
 
 template <int P> struct GemmCfg {
     static constexpr int kStages = P == 3 ? 3 : 6;
-    static constexpr int kTilesPerStage = P == 3 ? 4 : 2;  // A, W (, A_lo, W_lo)
+    static constexpr int kTilesPerStage = P == 3 ? 4 : 2;  // A, W_hi (, A_lo, W_lo)
     static constexpr int kStageBytes = kTilesPerStage * kTileBytes;
+    static constexpr int kAccCols = P == 3 ? 2 * BN : BN;  // main (+ correction) accumulator
+    static constexpr int kTmemCols = 2 * kAccCols;         // double buffered
     static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
@@ -59,6 +67,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
 }
 // Bounded wait.  Returns false (and raises *abort_flag) when the limit expires or another role gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    if (mbar_try_wait(bar, parity)) return true;
     const long long t0 = clock64();
     int polls = 0;
     while (!mbar_try_wait(bar, parity)) {
@@ -110,41 +119,63 @@ __device__ __forceinline__ float to_tf32(float v) {
     asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(r) : "f"(v));
     return __uint_as_float(r);
 }
-__device__ __forceinline__ void split_tile(uint32_t hi_addr, uint32_t lo_addr, int tid, int nthreads) {
-    for (int i = tid; i < kTileBytes / 16; i += nthreads) {
-        float4 v;
-        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(hi_addr + i * 16));
-        float4 h = make_float4(to_tf32(v.x), to_tf32(v.y), to_tf32(v.z), to_tf32(v.w));
-        float4 l = make_float4(to_tf32(v.x - h.x), to_tf32(v.y - h.y), to_tf32(v.z - h.z), to_tf32(v.w - h.w));
-        asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(hi_addr + i * 16), "f"(h.x), "f"(h.y), "f"(h.z), "f"(h.w) : "memory");
-        asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(lo_addr + i * 16), "f"(l.x), "f"(l.y), "f"(l.z), "f"(l.w) : "memory");
+// the value the tensor core sees when handed a float32 word as TF32: low 13 mantissa bits dropped
+__device__ __forceinline__ float tf32_view(float v) { return __uint_as_float(__float_as_uint(v) & 0xFFFFE000u); }
+__device__ __forceinline__ float lo_part(float v) { return to_tf32(v - tf32_view(v)); }
+
+// a_lo tile from the landed A tile; 128 threads, 8 float4 each, all loads issued before the stores
+__device__ __forceinline__ void write_low_tile(uint32_t a_addr, uint32_t lo_addr, int tid) {
+    float4 v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t off = (uint32_t)(tid + i * 128) * 16u;
+        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(v[i].x), "=f"(v[i].y), "=f"(v[i].z), "=f"(v[i].w) : "r"(a_addr + off));
+    }
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+        const uint32_t off = (uint32_t)(tid + i * 128) * 16u;
+        asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(lo_addr + off), "f"(lo_part(v[i].x)), "f"(lo_part(v[i].y)),
+                     "f"(lo_part(v[i].z)), "f"(lo_part(v[i].w))
+                     : "memory");
     }
 }
+
+#define FCB_TMEM_LD32(r, taddr)                                                                                          \
+    asm volatile(                                                                                                        \
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "                                                                        \
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "                                        \
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"                        \
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),    \
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),         \
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),        \
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])                      \
+        : "r"(taddr)                                                                                                     \
+        : "memory")
 
 template <int P>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                     const float* __restrict__ bias, float* __restrict__ c, int64_t ldc, int64_t m_total, int n_total,
-                     int k_total, int tiles_n, int32_t* __restrict__ status) {
+                     const __grid_constant__ CUtensorMap map_wlo, const float* __restrict__ bias, float* __restrict__ c,
+                     int64_t ldc, int64_t m_total, int n_total, int k_total, int tiles_n, int64_t num_tiles,
+                     int32_t* __restrict__ status) {
     using Cfg = GemmCfg<P>;
     constexpr int S = Cfg::kStages;
-    constexpr int kTmemCols = P == 3 ? 2 * BN : BN;  // main accumulator (+ correction accumulator)
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t bar_base = base + S * Cfg::kStageBytes;
-    // barrier block: full[S] | conv[S] | empty[S] | accum | tmem slot | abort flag
+    // barrier block: full[S] | conv[S] | empty[S] | tmem_full[2] | tmem_empty[2] | tmem slot | abort flag
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto conv_bar = [&](int s) { return bar_base + 8u * (S + s); };
     auto empty_bar = [&](int s) { return bar_base + 8u * (2 * S + s); };
-    const uint32_t accum_bar = bar_base + 8u * (3 * S);
+    auto tfull_bar = [&](int b) { return bar_base + 8u * (3 * S + b); };
+    auto tempty_bar = [&](int b) { return bar_base + 8u * (3 * S + 2 + b); };
     uint8_t* const bar_generic = smem_raw + (bar_base - smem_u32(smem_raw));
-    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_generic + 8 * (3 * S + 1));
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_generic + 8 * (3 * S + 1) + 4);
-    auto tile_addr = [&](int s, int which) { return base + s * Cfg::kStageBytes + which * kTileBytes; };  // 0 A, 1 W, 2 A_lo, 3 W_lo
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_generic + 8 * (3 * S + 4));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_generic + 8 * (3 * S + 4) + 4);
+    // tile slots of a stage: 0 A, 1 W_hi, 2 A_lo, 3 W_lo
+    auto tile_addr = [&](int s, int which) { return base + s * Cfg::kStageBytes + which * kTileBytes; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tile_n = blockIdx.x % tiles_n;
-    const int64_t tile_m = blockIdx.x / tiles_n;
     const int num_kb = (k_total + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -153,104 +184,119 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             mbar_init(conv_bar(s), 128);
             mbar_init(empty_bar(s), 1);
         }
-        mbar_init(accum_bar, 1);
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tfull_bar(b), 1);
+            mbar_init(tempty_bar(b), 128);
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
     if (warp == 0) {
         __syncwarp();
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)), "r"((uint32_t)kTmemCols) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                     "r"((uint32_t)Cfg::kTmemCols)
+                     : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_acc = *tmem_slot;
+    const uint32_t tmem_base = *tmem_slot;
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % S, it = kb / S;
-                if (!mbar_wait(empty_bar(s), (it & 1) ^ 1, abort_flag)) break;
-                mbar_expect_tx(full_bar(s), 2 * kTileBytes);
-                tma_load_2d(tile_addr(s, 0), &map_a, kb * BK, (int)(tile_m * BM), full_bar(s));
-                tma_load_2d(tile_addr(s, 1), &map_w, kb * BK, tile_n * BN, full_bar(s));
+            int64_t it = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                const int tile_n = (int)(tile % tiles_n);
+                const int64_t tile_m = tile / tiles_n;
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = (int)(it % S);
+                    const uint32_t ph = (uint32_t)((it / S) & 1);
+                    ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag);
+                    if (!ok) break;
+                    mbar_expect_tx(full_bar(s), (P == 3 ? 3 : 2) * kTileBytes);
+                    tma_load_2d(tile_addr(s, 0), &map_a, kb * BK, (int)(tile_m * BM), full_bar(s));
+                    tma_load_2d(tile_addr(s, 1), &map_w, kb * BK, tile_n * BN, full_bar(s));
+                    if (P == 3) tma_load_2d(tile_addr(s, 3), &map_wlo, kb * BK, tile_n * BN, full_bar(s));
+                }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
+            int64_t it = 0, tcount = 0;
             bool ok = true;
-            for (int kb = 0; kb < num_kb && ok; ++kb) {
-                const int s = kb % S, it = kb / S;
-                ok = mbar_wait(P == 3 ? conv_bar(s) : full_bar(s), it & 1, abort_flag);
+            for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+                const int buf = (int)(tcount & 1);
+                const uint32_t use = (uint32_t)((tcount >> 1) & 1);
+                ok = mbar_wait(tempty_bar(buf), use ^ 1u, abort_flag);  // epilogue has drained this accumulator
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint64_t da = smem_desc(tile_addr(s, 0)), dw = smem_desc(tile_addr(s, 1));
-                const uint64_t da_lo = P == 3 ? smem_desc(tile_addr(s, 2)) : 0, dw_lo = P == 3 ? smem_desc(tile_addr(s, 3)) : 0;
+                const uint32_t acc = tmem_base + (uint32_t)(buf * Cfg::kAccCols);
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = (int)(it % S);
+                    const uint32_t ph = (uint32_t)((it / S) & 1);
+                    ok = mbar_wait(P == 3 ? conv_bar(s) : full_bar(s), ph, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint64_t da = smem_desc(tile_addr(s, 0)), dw = smem_desc(tile_addr(s, 1));
+                    const uint64_t da_lo = P == 3 ? smem_desc(tile_addr(s, 2)) : 0, dw_lo = P == 3 ? smem_desc(tile_addr(s, 3)) : 0;
 #pragma unroll
-                for (int j = 0; j < BK / 8; ++j) {
-                    const uint64_t adv = (uint64_t)(j * 2);  // 32 bytes per k-step, in 16-byte units
-                    const uint32_t first = (kb > 0 || j > 0) ? 1u : 0u;
-                    if (P == 3) {
-                        umma_tf32(tmem_acc + BN, da_lo + adv, dw + adv, first);
-                        umma_tf32(tmem_acc + BN, da + adv, dw_lo + adv, 1u);
-                        umma_tf32(tmem_acc, da + adv, dw + adv, first);
-                    } else {
-                        umma_tf32(tmem_acc, da + adv, dw + adv, first);
+                    for (int j = 0; j < BK / 8; ++j) {
+                        const uint64_t adv = (uint64_t)(j * 2);  // 32 bytes per k-step, in 16-byte units
+                        const uint32_t first = (kb > 0 || j > 0) ? 1u : 0u;
+                        if (P == 3) {
+                            umma_tf32(acc + BN, da_lo + adv, dw + adv, first);
+                            umma_tf32(acc + BN, da + adv, dw_lo + adv, 1u);
+                        }
+                        umma_tf32(acc, da + adv, dw + adv, first);
                     }
+                    umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
                 }
-                umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
+                if (ok) umma_commit(tfull_bar(buf));
             }
-            if (ok) umma_commit(accum_bar);
+        }
+    } else if (warp < 6) {
+        if (P == 3) {
+            const int tid = threadIdx.x - 64;  // 0..127
+            int64_t it = 0;
+            bool ok = true;
+            for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+                for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                    const int s = (int)(it % S);
+                    const uint32_t ph = (uint32_t)((it / S) & 1);
+                    ok = mbar_wait(full_bar(s), ph, abort_flag);
+                    if (!ok) break;
+                    write_low_tile(tile_addr(s, 0), tile_addr(s, 2), tid);
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    mbar_arrive(conv_bar(s));
+                }
+            }
         }
     } else {
-        const int tid = threadIdx.x - 64;  // 0..127
-        bool ok = true;
-        if (P == 3) {
-            for (int kb = 0; kb < num_kb; ++kb) {
-                const int s = kb % S, it = kb / S;
-                ok = mbar_wait(full_bar(s), it & 1, abort_flag);
-                if (!ok) break;
-                split_tile(tile_addr(s, 0), tile_addr(s, 2), tid, 128);
-                split_tile(tile_addr(s, 1), tile_addr(s, 3), tid, 128);
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-                mbar_arrive(conv_bar(s));
-            }
-        }
         // epilogue: warp q = warp % 4 owns TMEM lanes [32q, 32q+32)
-        if (ok) ok = mbar_wait(accum_bar, 0, abort_flag);
-        ok = __all_sync(kFull, ok);
-        if (ok) {
+        const int q = warp & 3;
+        int64_t tcount = 0;
+        bool ok = true;
+        for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
+            const int tile_n = (int)(tile % tiles_n);
+            const int64_t tile_m = tile / tiles_n;
+            const int buf = (int)(tcount & 1);
+            const uint32_t use = (uint32_t)((tcount >> 1) & 1);
+            ok = mbar_wait(tfull_bar(buf), use, abort_flag);
+            ok = __all_sync(kFull, ok);
+            if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int q = warp & 3;
             const int64_t row = tile_m * BM + q * 32 + lane;
+            const uint32_t acc = tmem_base + (uint32_t)(buf * Cfg::kAccCols) + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
             for (int cc = 0; cc < BN / 32; ++cc) {
                 uint32_t r[32];
-                const uint32_t taddr = tmem_acc + ((uint32_t)(q * 32) << 16) + (uint32_t)(cc * 32);
-                asm volatile(
-                    "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                    "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                    "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
-                      "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
-                      "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
-                      "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
-                    : "r"(taddr)
-                    : "memory");
+                FCB_TMEM_LD32(r, acc + (uint32_t)(cc * 32));
                 if (P == 3) {
                     uint32_t t[32];
-                    asm volatile(
-                        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
-                        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
-                        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
-                        : "=r"(t[0]), "=r"(t[1]), "=r"(t[2]), "=r"(t[3]), "=r"(t[4]), "=r"(t[5]), "=r"(t[6]), "=r"(t[7]),
-                          "=r"(t[8]), "=r"(t[9]), "=r"(t[10]), "=r"(t[11]), "=r"(t[12]), "=r"(t[13]), "=r"(t[14]), "=r"(t[15]),
-                          "=r"(t[16]), "=r"(t[17]), "=r"(t[18]), "=r"(t[19]), "=r"(t[20]), "=r"(t[21]), "=r"(t[22]), "=r"(t[23]),
-                          "=r"(t[24]), "=r"(t[25]), "=r"(t[26]), "=r"(t[27]), "=r"(t[28]), "=r"(t[29]), "=r"(t[30]), "=r"(t[31])
-                        : "r"(taddr + (uint32_t)BN)
-                        : "memory");
+                    FCB_TMEM_LD32(t, acc + (uint32_t)(BN + cc * 32));
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 #pragma unroll
                     for (int i = 0; i < 32; ++i) r[i] = __float_as_uint(__uint_as_float(r[i]) + __uint_as_float(t[i]));
@@ -271,6 +317,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                     }
                 }
             }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(tempty_bar(buf));  // 128 arrivals hand the accumulator back to the MMA thread
         }
     }
 
@@ -279,9 +327,18 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
     __syncthreads();
     if (warp == 0) {
         __syncwarp();
-        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_acc), "r"((uint32_t)kTmemCols) : "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)Cfg::kTmemCols) : "memory");
     }
     if (threadIdx.x == 0 && *abort_flag && status) atomicExch(status, 1);
+}
+
+__global__ void split_tf32_kernel(const float* __restrict__ w, float* __restrict__ hi, float* __restrict__ lo, int64_t n) {
+    const int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const float v = w[i];
+    const float h = to_tf32(v);
+    hi[i] = h;
+    lo[i] = to_tf32(v - h);
 }
 
 // ---- host side ------------------------------------------------------------------------------
@@ -316,9 +373,21 @@ static int make_map(CUtensorMap* map, const float* ptr, int64_t rows, int64_t co
     return r == CUDA_SUCCESS ? FCB200_OK : FCB200_EINVAL;
 }
 
+static int sm_count() {
+    static int count[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return 148;
+    if (count[dev] == 0) {
+        int v = 0;
+        if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = 148;
+        count[dev] = v;
+    }
+    return count[dev];
+}
+
 template <int P>
-static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, const float* bias, float* c, int64_t ldc, int64_t m, int n,
-                       int k, int32_t* status, cudaStream_t s) {
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mwlo, const float* bias, float* c,
+                       int64_t ldc, int64_t m, int n, int k, int32_t* status, cudaStream_t s) {
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(gemm_tf32_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<P>::kSmemBytes) != cudaSuccess)
@@ -327,9 +396,10 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, const float
     }
     const int tiles_n = (n + BN - 1) / BN;
     const int64_t tiles_m = (m + BM - 1) / BM;
-    if (tiles_m * tiles_n >= (1LL << 31)) return FCB200_ERANGE;
-    gemm_tf32_kernel<P><<<(unsigned)(tiles_m * tiles_n), kGemmThreads, GemmCfg<P>::kSmemBytes, s>>>(ma, mw, bias, c, ldc, m, n, k,
-                                                                                                 tiles_n, status);
+    const int64_t num_tiles = tiles_m * tiles_n;
+    const int grid = (int)(num_tiles < sm_count() ? num_tiles : sm_count());
+    gemm_tf32_kernel<P><<<grid, kGemmThreads, GemmCfg<P>::kSmemBytes, s>>>(ma, mw, mwlo, bias, c, ldc, m, n, k, tiles_n, num_tiles,
+                                                                        status);
     return launch_status();
 }
 
@@ -337,19 +407,31 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, const float
 
 using namespace fcb200;
 
-extern "C" int fcb200_gemm_tf32(const float* a, int64_t lda, const float* w, int64_t ldw, const float* bias, float* c, int64_t ldc,
-                                int64_t m, int32_t n, int32_t k, int32_t precision, int32_t* status, void* stream) {
+extern "C" int fcb200_split_tf32(const float* w, float* w_hi, float* w_lo, int64_t count, void* stream) {
+    if (!w || !w_hi || !w_lo || count < 0) return FCB200_EINVAL;
+    if (count == 0) return FCB200_OK;
+    split_tf32_kernel<<<(unsigned)((count + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(w, w_hi, w_lo, count);
+    return launch_status();
+}
+
+extern "C" int fcb200_gemm_tf32(const float* a, int64_t lda, const float* w, const float* w_lo, int64_t ldw, const float* bias,
+                                float* c, int64_t ldc, int64_t m, int32_t n, int32_t k, int32_t precision, int32_t* status,
+                                void* stream) {
     if (!a || !w || !c || m < 0 || n <= 0 || k <= 0) return FCB200_EINVAL;
     if (precision != 1 && precision != 3) return FCB200_EINVAL;
+    if (precision == 3 && !w_lo) return FCB200_EINVAL;
     if (n % 4 || k % 4 || lda % 4 || ldw % 4 || ldc % 4 || lda < k || ldw < k || ldc < n) return FCB200_EINVAL;
-    if (!aligned16(a) || !aligned16(w) || !aligned16(c) || (bias && !aligned16(bias))) return FCB200_EALIGN;
+    if (!aligned16(a) || !aligned16(w) || !aligned16(c) || (bias && !aligned16(bias)) || (w_lo && !aligned16(w_lo)))
+        return FCB200_EALIGN;
     if (m == 0) return FCB200_OK;
-    CUtensorMap ma, mw;
+    CUtensorMap ma, mw, mwlo;
     int rc = make_map(&ma, a, m, k, lda);
     if (rc) return rc;
     rc = make_map(&mw, w, n, k, ldw);
     if (rc) return rc;
+    rc = make_map(&mwlo, precision == 3 ? w_lo : w, n, k, ldw);
+    if (rc) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    return precision == 3 ? launch_gemm<3>(ma, mw, bias, c, ldc, m, n, k, status, s)
-                          : launch_gemm<1>(ma, mw, bias, c, ldc, m, n, k, status, s);
+    return precision == 3 ? launch_gemm<3>(ma, mw, mwlo, bias, c, ldc, m, n, k, status, s)
+                          : launch_gemm<1>(ma, mw, mwlo, bias, c, ldc, m, n, k, status, s);
 }

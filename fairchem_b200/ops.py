@@ -243,16 +243,35 @@ def edge_geometry_bwd_(pos: Tensor, src: Tensor, tgt: Tensor, shift: Optional[Te
 
 
 @torch.library.custom_op(f"{NS}::gemm_tf32", mutates_args=("c", "status"))
-def gemm_tf32_(a: Tensor, w: Tensor, bias: Optional[Tensor], c: Tensor, precision: int, status: Tensor) -> None:
-    """c[M,N] = a[M,K] @ w[N,K]^T (+ bias); a, w, c may be row-strided views with unit inner stride."""
-    for t in (a, w, c):
+def gemm_tf32_(a: Tensor, w: Tensor, w_lo: Optional[Tensor], bias: Optional[Tensor], c: Tensor, precision: int,
+               status: Tensor) -> None:
+    """c[M,N] = a[M,K] @ w[N,K]^T (+ bias); a, w, c may be row-strided views with unit inner stride.
+    precision 3 takes the weight as (w, w_lo) = split_tf32(weight)."""
+    for t in (a, w, c) + ((w_lo,) if w_lo is not None else ()):
         if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
             raise _lib.FairchemB200Error("gemm_tf32: need 2-D float32 CUDA operands with unit inner stride")
+    if w_lo is not None and (w_lo.shape != w.shape or w_lo.stride(0) != w.stride(0)):
+        raise _lib.FairchemB200Error("gemm_tf32: w and w_lo must share shape and row stride")
     _chk(bias, status)
     m, n, k = a.shape[0], w.shape[0], a.shape[1]
     _launch("gemm_tf32", "fcb200_gemm_tf32",
-            (_p(a), a.stride(0), _p(w), w.stride(0), _p(bias), _p(c), c.stride(0), m, n, k, precision, _p(status), _stream()),
-            nbytes=4 * (m * k + n * k + m * n), flops=2 * m * n * k)
+            (_p(a), a.stride(0), _p(w), _p(w_lo), w.stride(0), _p(bias), _p(c), c.stride(0), m, n, k, precision, _p(status),
+             _stream()), nbytes=4 * (m * k + n * k + m * n), flops=2 * m * n * k)
+
+
+@torch.library.custom_op(f"{NS}::split_tf32", mutates_args=("hi", "lo"))
+def split_tf32_(w: Tensor, hi: Tensor, lo: Tensor) -> None:
+    _chk(w, hi, lo)
+    _f32(w, hi, lo)
+    _launch("split_tf32", "fcb200_split_tf32", (_p(w), _p(hi), _p(lo), w.numel(), _stream()), nbytes=12 * w.numel())
+
+
+def split_tf32(w: Tensor):
+    """(hi, lo) TF32 parts of a float32 tensor, contiguous."""
+    w = w.detach().contiguous()
+    hi, lo = torch.empty_like(w), torch.empty_like(w)
+    split_tf32_(w, hi, lo)
+    return hi, lo
 
 
 # ------------------------------------------------------------------------------------------

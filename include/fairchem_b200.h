@@ -256,18 +256,28 @@ int fcb200_rg_neighbor_counts_static(const float* pos, const int32_t* sys, int32
 /* ---------------------------------------------------------------- dense contraction */
 
 /*
- * C[M,N] = A[M,K] * W[N,K]^T (+ bias[N]) in float32 through tcgen05 TF32 tensor-core MMAs with
- * float32 accumulation in tensor memory.  precision = 1: single TF32 pass; precision = 3: the
- * operands are split into TF32 high and low parts in shared memory and three MMAs are issued
- * (hi*hi + lo*hi + hi*lo), which restores float32-level accuracy.
- * Replaces the cuBLAS calls under SO2_Convolution / SO2_m_Conv (so2_layers.py:67-80, 600-647) and
- * RadialMLP (radial.py:61-86).  lda/ldw/ldc are row strides in floats (multiples of 4);
- * K a multiple of 32, N a multiple of 16.  `status` is a device int32 the kernel sets non-zero
- * if a bounded wait expired (the result is then invalid).
+ * C[M,N] = A[M,K] * W[N,K]^T (+ bias) in float32 through tcgen05 TF32 tensor-core MMAs with float32
+ * accumulation in tensor memory (persistent kernel, TMA loads, double-buffered accumulators).
+ * precision = 1: single TF32 pass, `w` is the float32 weight, `w_lo` is ignored (may be NULL).
+ * precision = 3: `w` = high parts and `w_lo` = low parts produced by fcb200_split_tf32 (same shape and
+ * row stride); A is split on the fly and three MMAs per k-step (lo*hi + hi*lo + hi*hi) restore
+ * float32-level accuracy.
+ * Replaces the cuBLAS calls under SO2_Convolution / SO2_m_Conv
+ * (src/fairchem/core/models/uma/nn/so2_layers.py:67-80, 600-647) and RadialMLP
+ * (src/fairchem/core/models/uma/nn/radial.py:61-86).  lda/ldw/ldc are row strides in floats (multiples
+ * of 4); K and N multiples of 4.  `status` is a device int32 the kernel sets non-zero if one of its
+ * bounded waits expired (the result is then invalid).
  */
-int fcb200_gemm_tf32(const float* a, int64_t lda, const float* w, int64_t ldw, const float* bias, float* c,
-                     int64_t ldc, int64_t m, int32_t n, int32_t k, int32_t precision, int32_t* status,
+int fcb200_gemm_tf32(const float* a, int64_t lda, const float* w, const float* w_lo, int64_t ldw, const float* bias,
+                     float* c, int64_t ldc, int64_t m, int32_t n, int32_t k, int32_t precision, int32_t* status,
                      void* stream);
+
+/*
+ * Split float32 values into TF32 high and low parts: hi = tf32_round(w), lo = tf32_round(w - hi).
+ * Done once per weight matrix; there is no counterpart in the reference (its float32 GEMMs run on
+ * CUDA cores through cuBLAS).
+ */
+int fcb200_split_tf32(const float* w, float* w_hi, float* w_lo, int64_t count, void* stream);
 
 #ifdef __cplusplus
 }

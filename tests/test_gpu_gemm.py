@@ -38,7 +38,11 @@ def test_gemm_tf32(ops, m, n, k, pad, with_bias, precision):
     bias = torch.randn(n, generator=g).cuda() if with_bias else None
     c = torch.full((m, n), float("nan"), device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    ops.gemm_tf32_(a, w, bias, c, precision, status)
+    if precision == 3:
+        hi, lo = ops.split_tf32(w)
+        ops.gemm_tf32_(a, hi, lo, bias, c, 3, status)
+    else:
+        ops.gemm_tf32_(a, w, None, bias, c, 1, status)
     torch.cuda.synchronize()
     assert int(status.item()) == 0, "a bounded wait inside the kernel expired"
     ref = a.double() @ w.double().t()
@@ -59,8 +63,39 @@ def test_gemm_matches_fp32_matmul_closely(ops):
     w = (torch.randn(640, 768, generator=g) / 768 ** 0.5).cuda()
     c = torch.empty(2048, 640, device="cuda")
     status = torch.zeros(1, dtype=torch.int32, device="cuda")
-    ops.gemm_tf32_(a, w, None, c, 3, status)
+    hi, lo = ops.split_tf32(w)
+    ops.gemm_tf32_(a, hi, lo, None, c, 3, status)
     ref = a.double() @ w.double().t()
     e_ours = (c.double() - ref).abs().max().item()
     e_fp32 = ((a @ w.t()).double() - ref).abs().max().item()
     assert int(status.item()) == 0 and e_ours < 8 * e_fp32 + 1e-6
+
+
+def test_tensor_core_reads_float32_words_as_truncated_tf32(ops):
+    """The on-the-fly split of A relies on the tensor core dropping the low 13 mantissa bits of a
+    float32 word (no rounding).  A single-pass product must therefore equal the float64 product of the
+    truncated operands up to float32 accumulation error."""
+    g = torch.Generator().manual_seed(11)
+    a = torch.randn(512, 256, generator=g).cuda()
+    w = (torch.randn(256, 256, generator=g) / 16).cuda()
+    c = torch.empty(512, 256, device="cuda")
+    status = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.gemm_tf32_(a, w, None, None, c, 1, status)
+
+    def trunc(t):
+        return (t.view(torch.int32) & -8192).view(torch.float32)
+
+    ref_trunc = trunc(a).double() @ trunc(w).double().t()
+    ref_exact = a.double() @ w.double().t()
+    e_trunc = (c.double() - ref_trunc).abs().max().item()
+    e_exact = (c.double() - ref_exact).abs().max().item()
+    assert int(status.item()) == 0
+    assert e_trunc < 2e-5 and e_exact > 20 * e_trunc, (e_trunc, e_exact)
+
+
+def test_split_tf32_parts(ops):
+    g = torch.Generator().manual_seed(12)
+    w = torch.randn(1000, generator=g).cuda()
+    hi, lo = ops.split_tf32(w)
+    assert bool(((hi.view(torch.int32) & 8191) == 0).all()) and bool(((lo.view(torch.int32) & 8191) == 0).all())
+    assert float((w - hi - lo).abs().max()) <= float(w.abs().max()) * 2.0 ** -21
