@@ -323,9 +323,9 @@ def _split(w: torch.Tensor):
 def _gemm(x2, w, bias, y, precision):
     if precision == 3:
         hi, lo = _split(w)
-        ops.gemm_tf32_(x2, hi, lo, bias, y, 3, _status(x2.device))
+        ops.gemm_tf32_.raw(x2, hi, lo, bias, y, 3, _status(x2.device))
     else:
-        ops.gemm_tf32_(x2, w, None, bias, y, 1, _status(x2.device))
+        ops.gemm_tf32_.raw(x2, w, None, bias, y, 1, _status(x2.device))
 
 
 class _LinearTF32(torch.autograd.Function):
@@ -395,9 +395,9 @@ class _EdgeBlockFn(torch.autograd.Function):
                 m0 = torch.empty(ec, 6 * c, dtype=x.dtype, device=x.device)
                 m1 = torch.empty(ec, 2, 4 * c, dtype=x.dtype, device=x.device)
                 m2 = torch.empty(ec, 2, 2 * c, dtype=x.dtype, device=x.device)
-                ops.gather_rotate_fwd_(x, g.src[sl], g.tgt[sl], wig[sl], rad, m0, m1, m2)
+                ops.gather_rotate_fwd_.raw(x, g.src[sl], g.tgt[sl], wig[sl], rad, m0, m1, m2)
                 msg = _so2_middle(ew, m0, m1, m2)
-                ops.rotate_back_reduce_fwd_(msg, winv[sl], ch.row_ptr, out[ch.n0:ch.n1])
+                ops.rotate_back_reduce_fwd_.raw(msg, winv[sl], ch.row_ptr, out[ch.n0:ch.n1])
         ctx.save_for_backward(x, wig, winv, gauss)
         ctx.ew, ctx.tables, ctx.ectx, ctx.nb = ew, tables, ectx, nb
         return out
@@ -423,17 +423,17 @@ class _EdgeBlockFn(torch.autograd.Function):
                 m0 = torch.empty(ec, 6 * c, dtype=x.dtype, device=x.device)
                 m1 = torch.empty(ec, 2, 4 * c, dtype=x.dtype, device=x.device)
                 m2 = torch.empty(ec, 2, 2 * c, dtype=x.dtype, device=x.device)
-                ops.gather_rotate_fwd_(x, g.src[sl], g.tgt[sl], wig[sl], rad_d, m0, m1, m2)
+                ops.gather_rotate_fwd_.raw(x, g.src[sl], g.tgt[sl], wig[sl], rad_d, m0, m1, m2)
                 m0.requires_grad_(True), m1.requires_grad_(True), m2.requires_grad_(True)
                 msg = _so2_middle(ew, m0, m1, m2)
             grad_msg = torch.empty_like(msg)
-            ops.rotate_back_bwd_(grad_out, msg.detach(), winv[sl], g.tgt[sl], grad_msg, gwinv[sl])
+            ops.rotate_back_bwd_.raw(grad_out, msg.detach(), winv[sl], g.tgt[sl], grad_msg, gwinv[sl])
             gm0, gm1, gm2 = torch.autograd.grad(msg, (m0, m1, m2), grad_msg)
             del msg, grad_msg
             g_src = torch.empty(ec, 9, c, dtype=x.dtype, device=x.device)
             g_tgt = torch.empty(ec, 9, c, dtype=x.dtype, device=x.device)
             grad_rad = torch.empty_like(rad_d)
-            ops.gather_rotate_bwd_(gm0.contiguous(), gm1.contiguous(), gm2.contiguous(), x, g.src[sl], g.tgt[sl], wig[sl],
+            ops.gather_rotate_bwd_.raw(gm0.contiguous(), gm1.contiguous(), gm2.contiguous(), x, g.src[sl], g.tgt[sl], wig[sl],
                                    rad_d, g_src, g_tgt, gwig[sl], grad_rad)
             del gm0, gm1, gm2, m0, m1, m2
             # node reductions: target rows of the chunk are contiguous; source rows are the chunk's distinct sources
@@ -460,7 +460,7 @@ class _EdgeDegreeFn(torch.autograd.Function):
             for ch in ectx.chunks:
                 sl = slice(ch.e0, ch.e1)
                 r3 = _radial(rad_func, tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb)
-                ops.edge_degree_fwd_(r3, winv[sl], ch.row_ptr, x[ch.n0:ch.n1], out[ch.n0:ch.n1], rescale)
+                ops.edge_degree_fwd_.raw(r3, winv[sl], ch.row_ptr, x[ch.n0:ch.n1], out[ch.n0:ch.n1], rescale)
         ctx.save_for_backward(winv, gauss)
         ctx.rad_func, ctx.tables, ctx.ectx, ctx.nb, ctx.rescale, ctx.c = rad_func, tables, ectx, nb, rescale, c
         return out
@@ -479,7 +479,7 @@ class _EdgeDegreeFn(torch.autograd.Function):
                 g_c = gauss[sl].detach().requires_grad_(True)
                 r3 = _radial(ctx.rad_func, ctx.tables, g_c, ectx.z_src[sl], ectx.z_tgt[sl], nb)
             gr = torch.empty_like(r3)
-            ops.edge_degree_bwd_(grad_out, r3.detach(), winv[sl], g.tgt[sl], gr, gwinv[sl], ctx.rescale)
+            ops.edge_degree_bwd_.raw(grad_out, r3.detach(), winv[sl], g.tgt[sl], gr, gwinv[sl], ctx.rescale)
             (gg,) = torch.autograd.grad(r3, g_c, gr)
             ggauss[sl] = gg
         return grad_out, gwinv, ggauss, None, None, None, None, None
@@ -596,6 +596,8 @@ class eSCNMDBackboneB200(nn.Module):
             return self._forward(data, gamma)
 
     def _forward(self, data, gamma):
+        from .parallel import halo_collect
+
         data["atomic_numbers"] = data["atomic_numbers"].long()
         data["atomic_numbers_full"] = data["atomic_numbers"]
         data["batch_full"] = data["batch"]
@@ -603,12 +605,20 @@ class eSCNMDBackboneB200(nn.Module):
         pos = data["pos"]
         if self.regress_forces and not self.direct_forces:
             pos.requires_grad_(True)
-        n = pos.shape[0]
         c, nb = self.sphere_channels, self.num_distance_basis
         csd = self.csd_embedding(data["charge"], data["spin"], data.get("dataset", None))
-        sys_node = csd[batch]
 
-        edge_index, cell_offsets = self._graph(data)
+        # graph-parallel run: this rank owns plan.node_partition and reads plan.halo_ids from its peers
+        plan = data.get("gp_plan", None)
+        if plan is None:
+            edge_index, cell_offsets = self._graph(data)
+            pos_e, z_e, batch_l = pos, z, batch
+        else:
+            edge_index, cell_offsets = plan.edge_index_local, plan.cell_offsets
+            pos_e = pos.index_select(0, plan.full_ids)
+            z_e, batch_l = z[plan.full_ids], batch[plan.node_partition]
+        n_full, n_local = pos_e.shape[0], batch_l.shape[0]
+        sys_node = csd[batch_l]
         data["scatter_target"] = edge_index[1]
         if edge_index.shape[1] == 0:
             # isolated atoms: one zero-weight self-loop at the cutoff keeps every kernel shape valid
@@ -617,18 +627,18 @@ class eSCNMDBackboneB200(nn.Module):
             cell_offsets = torch.zeros(1, 3, dtype=pos.dtype, device=pos.device)
             shift = torch.tensor([[self.cutoff, 0.0, 0.0]], dtype=pos.dtype, device=pos.device)
         else:
-            edge_sys = None if data["cell"].shape[0] == 1 else batch[edge_index[1]]
+            edge_sys = None if data["cell"].shape[0] == 1 else batch_l[edge_index[1]]
             shift = get_pbc_shifts(data["cell"].to(pos.dtype), cell_offsets, edge_sys).contiguous()
-        graph = EdgeGraph.from_edge_index(edge_index, n)
+        graph = EdgeGraph(edge_index[0], edge_index[1], n_full, n_local)
         self.last_graph = {"edge_index": edge_index, "cell_offsets": cell_offsets}
         chunks = build_chunks(graph, self.edge_chunk_size)
 
-        vec, dist, env, wig, gauss = ops.EdgeGeometry.apply(pos, shift, gamma, graph, self.cutoff, nb, 0.0, self.cutoff, 2.0)
+        vec, dist, env, wig, gauss = ops.EdgeGeometry.apply(pos_e, shift, gamma, graph, self.cutoff, nb, 0.0, self.cutoff, 2.0)
         winv = wig[:, self._wig_transpose] * env.unsqueeze(1)
-        ectx = _EdgeCtx(graph, chunks, wig, winv, gauss, z[edge_index[0]], z[edge_index[1]])
+        ectx = _EdgeCtx(graph, chunks, wig, winv, gauss, z_e[edge_index[0]], z_e[edge_index[1]])
 
-        x = torch.zeros(n, self.sph_feature_size, c, dtype=pos.dtype, device=pos.device)
-        x[:, 0, :] = self.sphere_embedding(z) + sys_node
+        x = torch.zeros(n_local, self.sph_feature_size, c, dtype=pos.dtype, device=pos.device)
+        x[:, 0, :] = self.sphere_embedding(z_e[:n_local]) + sys_node
         ede = self.edge_degree_embedding.rad_func
         x = _EdgeDegreeFn.apply(x, winv, gauss, ede, self._tables(ede), ectx, nb, self.rescale_factor)
 
@@ -636,12 +646,13 @@ class eSCNMDBackboneB200(nn.Module):
             x_res = x
             xn = blk.norm_1(x)
             xn = torch.cat([xn[:, :1] + sys_node.unsqueeze(1), xn[:, 1:]], dim=1)
+            x_full = halo_collect(xn, plan)  # per-layer halo exchange (escn_md_block.py:141-146)
             rad = blk.edge_wise.so2_conv_1.rad_func
-            x = _EdgeBlockFn.apply(xn, wig, winv, gauss, blk.edge_wise, self._tables(rad), ectx, nb) + x_res
+            x = _EdgeBlockFn.apply(x_full, wig, winv, gauss, blk.edge_wise, self._tables(rad), ectx, nb) + x_res
             x_res = x
             x = blk.atom_wise(blk.norm_2(x)) + x_res
         x = self.norm(x)
-        return {"node_embedding": x, "batch": batch}
+        return {"node_embedding": x, "batch": batch_l}
 
 
 class MLP_EFS_HeadB200(nn.Module):
@@ -658,7 +669,7 @@ class MLP_EFS_HeadB200(nn.Module):
         with torch.enable_grad():
             e_node = self.energy_block(emb["node_embedding"][:, 0]).view(-1)
             nsys = len(data["natoms"])
-            energy = torch.zeros(nsys, dtype=torch.float64, device=e_node.device).index_add(0, data["batch"], e_node.double())
+            energy = torch.zeros(nsys, dtype=torch.float64, device=e_node.device).index_add(0, emb["batch"], e_node.double())
             out = {"energy": energy.detach()}
             if self.regress_forces:
                 (grad,) = torch.autograd.grad(energy.sum(), data["pos"], create_graph=False)

@@ -101,7 +101,22 @@ def _f32(*tensors):
 # ------------------------------------------------------------------------------------------
 
 
-@torch.library.custom_op(f"{NS}::gather_rotate_fwd", mutates_args=("m0", "m1", "m2"))
+def _op(name: str, mutates):
+    """Register ``fn`` as ``torch.ops.fairchem_b200.<name>`` and keep the plain function as ``.raw``.
+
+    The registered op is the public, dispatcher-visible entry (what torch.compile and other code see);
+    the module's own inner loops call ``.raw`` to skip the dispatcher's per-call cost, which matters
+    when a step issues thousands of launches."""
+
+    def deco(fn):
+        op = torch.library.custom_op(f"{NS}::{name}", mutates_args=mutates)(fn)
+        op.raw = fn
+        return op
+
+    return deco
+
+
+@_op("gather_rotate_fwd", ("m0", "m1", "m2"))
 def gather_rotate_fwd_(x: Tensor, src: Tensor, tgt: Tensor, wig: Tensor, radial: Optional[Tensor], m0: Tensor,
                        m1: Tensor, m2: Tensor) -> None:
     _chk(x, src, tgt, wig, radial, m0, m1, m2)
@@ -112,7 +127,7 @@ def gather_rotate_fwd_(x: Tensor, src: Tensor, tgt: Tensor, wig: Tensor, radial:
             nbytes=e * (4 * (18 * c + 18 * c + WIG + (12 * c if radial is not None else 0)) + 8), flops=e * 2 * WIG * 2 * c)
 
 
-@torch.library.custom_op(f"{NS}::gather_rotate_bwd", mutates_args=("g_src", "g_tgt", "grad_wig", "grad_radial"))
+@_op("gather_rotate_bwd", ("g_src", "g_tgt", "grad_wig", "grad_radial"))
 def gather_rotate_bwd_(gm0: Tensor, gm1: Tensor, gm2: Tensor, x: Tensor, src: Tensor, tgt: Tensor, wig: Tensor,
                        radial: Optional[Tensor], g_src: Tensor, g_tgt: Tensor, grad_wig: Tensor,
                        grad_radial: Optional[Tensor]) -> None:
@@ -125,7 +140,7 @@ def gather_rotate_bwd_(gm0: Tensor, gm1: Tensor, gm2: Tensor, x: Tensor, src: Te
             nbytes=e * (4 * (18 * c * 3 + 2 * WIG + (24 * c if radial is not None else 0)) + 8), flops=e * 6 * WIG * 2 * c)
 
 
-@torch.library.custom_op(f"{NS}::rotate_back_reduce_fwd", mutates_args=("out",))
+@_op("rotate_back_reduce_fwd", ("out",))
 def rotate_back_reduce_fwd_(msg: Tensor, winv: Tensor, row_ptr: Tensor, out: Tensor) -> None:
     _chk(msg, winv, row_ptr, out)
     _f32(msg, winv, out)
@@ -135,7 +150,7 @@ def rotate_back_reduce_fwd_(msg: Tensor, winv: Tensor, row_ptr: Tensor, out: Ten
             nbytes=4 * (e * (9 * c + WIG) + n * (9 * c + 1)), flops=e * 2 * WIG * c)
 
 
-@torch.library.custom_op(f"{NS}::rotate_back_bwd", mutates_args=("grad_msg", "grad_winv"))
+@_op("rotate_back_bwd", ("grad_msg", "grad_winv"))
 def rotate_back_bwd_(grad_out: Tensor, msg: Optional[Tensor], winv: Tensor, tgt: Tensor, grad_msg: Tensor,
                      grad_winv: Optional[Tensor]) -> None:
     _chk(grad_out, msg, winv, tgt, grad_msg, grad_winv)
@@ -146,7 +161,7 @@ def rotate_back_bwd_(grad_out: Tensor, msg: Optional[Tensor], winv: Tensor, tgt:
             nbytes=e * 4 * (9 * c * (3 if msg is not None else 2) + 2 * WIG + 1), flops=e * 4 * WIG * c)
 
 
-@torch.library.custom_op(f"{NS}::edge_degree_fwd", mutates_args=("out",))
+@_op("edge_degree_fwd", ("out",))
 def edge_degree_fwd_(radial3: Tensor, winv: Tensor, row_ptr: Tensor, x_in: Optional[Tensor], out: Tensor,
                      rescale: float) -> None:
     _chk(radial3, winv, row_ptr, x_in, out)
@@ -157,7 +172,7 @@ def edge_degree_fwd_(radial3: Tensor, winv: Tensor, row_ptr: Tensor, x_in: Optio
             nbytes=4 * (e * (3 * c + WIG) + n * (18 * c + 1)), flops=e * 2 * 9 * c)
 
 
-@torch.library.custom_op(f"{NS}::edge_degree_bwd", mutates_args=("grad_radial3", "grad_winv"))
+@_op("edge_degree_bwd", ("grad_radial3", "grad_winv"))
 def edge_degree_bwd_(grad_out: Tensor, radial3: Tensor, winv: Tensor, tgt: Tensor, grad_radial3: Tensor,
                      grad_winv: Tensor, rescale: float) -> None:
     _chk(grad_out, radial3, winv, tgt, grad_radial3, grad_winv)
@@ -168,7 +183,7 @@ def edge_degree_bwd_(grad_out: Tensor, radial3: Tensor, winv: Tensor, tgt: Tenso
              _stream()), nbytes=e * 4 * (9 * c + 6 * c + 2 * WIG + 1), flops=e * 4 * 9 * c)
 
 
-@torch.library.custom_op(f"{NS}::segment_sum", mutates_args=("out",))
+@_op("segment_sum", ("out",))
 def segment_sum_(rows: Tensor, ptr: Tensor, perm: Optional[Tensor], out_index: Optional[Tensor], out: Tensor,
                  accumulate: bool, scale: float, num_segments: int, width: int) -> None:
     _chk(rows, ptr, perm, out_index, out)
@@ -178,7 +193,7 @@ def segment_sum_(rows: Tensor, ptr: Tensor, perm: Optional[Tensor], out_index: O
             nbytes=4 * (rows.shape[0] * width + num_segments * width * (2 if accumulate else 1)))
 
 
-@torch.library.custom_op(f"{NS}::so2_gate_fwd", mutates_args=("a0", "a1", "a2"))
+@_op("so2_gate_fwd", ("a0", "a1", "a2"))
 def so2_gate_fwd_(y0: Tensor, y1: Tensor, y2: Tensor, a0: Tensor, a1: Tensor, a2: Tensor, hidden: int) -> None:
     _chk(y0, y1, y2, a0, a1, a2)
     _f32(y0, y1, y2, a0, a1, a2)
@@ -187,7 +202,7 @@ def so2_gate_fwd_(y0: Tensor, y1: Tensor, y2: Tensor, a0: Tensor, a1: Tensor, a2
             nbytes=y0.shape[0] * 4 * hidden * (5 + 8 + 4 + 9))
 
 
-@torch.library.custom_op(f"{NS}::so2_gate_bwd", mutates_args=("g0", "g1", "g2"))
+@_op("so2_gate_bwd", ("g0", "g1", "g2"))
 def so2_gate_bwd_(ga0: Tensor, ga1: Tensor, ga2: Tensor, y0: Tensor, y1: Tensor, y2: Tensor, g0: Tensor, g1: Tensor,
                   g2: Tensor, hidden: int) -> None:
     _chk(ga0, ga1, ga2, y0, y1, y2, g0, g1, g2)
@@ -197,7 +212,7 @@ def so2_gate_bwd_(ga0: Tensor, ga1: Tensor, ga2: Tensor, y0: Tensor, y1: Tensor,
             nbytes=y0.shape[0] * 4 * hidden * (9 + 17 + 17))
 
 
-@torch.library.custom_op(f"{NS}::so2_combine_fwd", mutates_args=("out",))
+@_op("so2_combine_fwd", ("out",))
 def so2_combine_fwd_(z0: Tensor, z1: Tensor, z2: Tensor, out: Tensor, channels: int) -> None:
     _chk(z0, z1, z2, out)
     _f32(z0, z1, z2, out)
@@ -205,7 +220,7 @@ def so2_combine_fwd_(z0: Tensor, z1: Tensor, z2: Tensor, out: Tensor, channels: 
             (_p(z0), _p(z1), _p(z2), _p(out), z0.shape[0], channels, _stream()), nbytes=z0.shape[0] * 4 * channels * (15 + 9))
 
 
-@torch.library.custom_op(f"{NS}::so2_combine_bwd", mutates_args=("g0", "g1", "g2"))
+@_op("so2_combine_bwd", ("g0", "g1", "g2"))
 def so2_combine_bwd_(grad_out: Tensor, g0: Tensor, g1: Tensor, g2: Tensor, channels: int) -> None:
     _chk(grad_out, g0, g1, g2)
     _f32(grad_out, g0, g1, g2)
@@ -214,7 +229,7 @@ def so2_combine_bwd_(grad_out: Tensor, g0: Tensor, g1: Tensor, g2: Tensor, chann
             nbytes=grad_out.shape[0] * 4 * channels * (15 + 9))
 
 
-@torch.library.custom_op(f"{NS}::edge_geometry_fwd", mutates_args=("vec", "dist", "env", "wig", "gauss"))
+@_op("edge_geometry_fwd", ("vec", "dist", "env", "wig", "gauss"))
 def edge_geometry_fwd_(pos: Tensor, src: Tensor, tgt: Tensor, shift: Optional[Tensor], gamma: Optional[Tensor],
                        vec: Optional[Tensor], dist: Optional[Tensor], env: Optional[Tensor], wig: Optional[Tensor],
                        gauss: Optional[Tensor], cutoff: float, num_basis: int, b_start: float, b_stop: float,
@@ -228,7 +243,7 @@ def edge_geometry_fwd_(pos: Tensor, src: Tensor, tgt: Tensor, shift: Optional[Te
             nbytes=e * 4 * (2 + 6 + 3 + 3 + 2 + WIG + num_basis))
 
 
-@torch.library.custom_op(f"{NS}::edge_geometry_bwd", mutates_args=("grad_vec",))
+@_op("edge_geometry_bwd", ("grad_vec",))
 def edge_geometry_bwd_(pos: Tensor, src: Tensor, tgt: Tensor, shift: Optional[Tensor], gamma: Optional[Tensor],
                        grad_wig: Optional[Tensor], grad_env: Optional[Tensor], grad_gauss: Optional[Tensor],
                        grad_dist: Optional[Tensor], grad_vec: Tensor, cutoff: float, num_basis: int, b_start: float,
@@ -242,7 +257,7 @@ def edge_geometry_bwd_(pos: Tensor, src: Tensor, tgt: Tensor, shift: Optional[Te
             nbytes=e * 4 * (2 + 6 + 3 + 3 + 2 + WIG + num_basis))
 
 
-@torch.library.custom_op(f"{NS}::gemm_tf32", mutates_args=("c", "status"))
+@_op("gemm_tf32", ("c", "status"))
 def gemm_tf32_(a: Tensor, w: Tensor, w_lo: Optional[Tensor], bias: Optional[Tensor], c: Tensor, precision: int,
                status: Tensor) -> None:
     """c[M,N] = a[M,K] @ w[N,K]^T (+ bias); a, w, c may be row-strided views with unit inner stride.
@@ -259,7 +274,7 @@ def gemm_tf32_(a: Tensor, w: Tensor, w_lo: Optional[Tensor], bias: Optional[Tens
              _stream()), nbytes=4 * (m * k + n * k + m * n), flops=2 * m * n * k)
 
 
-@torch.library.custom_op(f"{NS}::split_tf32", mutates_args=("hi", "lo"))
+@_op("split_tf32", ("hi", "lo"))
 def split_tf32_(w: Tensor, hi: Tensor, lo: Tensor) -> None:
     _chk(w, hi, lo)
     _f32(w, hi, lo)
@@ -270,7 +285,7 @@ def split_tf32(w: Tensor):
     """(hi, lo) TF32 parts of a float32 tensor, contiguous."""
     w = w.detach().contiguous()
     hi, lo = torch.empty_like(w), torch.empty_like(w)
-    split_tf32_(w, hi, lo)
+    split_tf32_.raw(w, hi, lo)
     return hi, lo
 
 
@@ -322,7 +337,7 @@ def segment_sum(rows: Tensor, ptr: Tensor, perm: Optional[Tensor], num_segments:
     width = rows[0].numel() if rows.shape[0] else int(torch.tensor(rows.shape[1:]).prod())
     if out is None:
         out = torch.empty((num_segments,) + tuple(rows.shape[1:]), dtype=rows.dtype, device=rows.device)
-    segment_sum_(rows, ptr, perm, out_index, out, accumulate, scale, num_segments, width)
+    segment_sum_.raw(rows, ptr, perm, out_index, out, accumulate, scale, num_segments, width)
     return out
 
 
@@ -342,7 +357,7 @@ class GatherRotate(torch.autograd.Function):
         m0 = torch.empty(e, 6 * c, dtype=x.dtype, device=x.device)
         m1 = torch.empty(e, 2, 4 * c, dtype=x.dtype, device=x.device)
         m2 = torch.empty(e, 2, 2 * c, dtype=x.dtype, device=x.device)
-        gather_rotate_fwd_(x, graph.src, graph.tgt, wig, radial, m0, m1, m2)
+        gather_rotate_fwd_.raw(x, graph.src, graph.tgt, wig, radial, m0, m1, m2)
         ctx.save_for_backward(x, wig, radial)
         ctx.graph = graph
         return m0, m1, m2
@@ -356,7 +371,7 @@ class GatherRotate(torch.autograd.Function):
         g_tgt = torch.empty(e, 9, c, dtype=x.dtype, device=x.device)
         grad_wig = torch.empty(e, WIG, dtype=x.dtype, device=x.device)
         grad_radial = None if radial is None else torch.empty_like(radial)
-        gather_rotate_bwd_(gm0.contiguous(), gm1.contiguous(), gm2.contiguous(), x, g.src, g.tgt, wig, radial, g_src,
+        gather_rotate_bwd_.raw(gm0.contiguous(), gm1.contiguous(), gm2.contiguous(), x, g.src, g.tgt, wig, radial, g_src,
                            g_tgt, grad_wig, grad_radial)
         grad_x = torch.empty_like(x)
         segment_sum(g_src, g.src_ptr, g.src_perm, g.num_nodes, out=grad_x)
@@ -374,7 +389,7 @@ class RotateBackReduce(torch.autograd.Function):
     def forward(ctx, msg, winv, graph: EdgeGraph):
         msg, winv = msg.contiguous(), winv.contiguous()
         out = torch.empty(graph.num_targets, 9, msg.shape[2], dtype=msg.dtype, device=msg.device)
-        rotate_back_reduce_fwd_(msg, winv, graph.row_ptr, out)
+        rotate_back_reduce_fwd_.raw(msg, winv, graph.row_ptr, out)
         ctx.save_for_backward(msg, winv)
         ctx.graph = graph
         return out
@@ -385,7 +400,7 @@ class RotateBackReduce(torch.autograd.Function):
         g = ctx.graph
         grad_msg = torch.empty_like(msg)
         grad_winv = torch.empty_like(winv)
-        rotate_back_bwd_(grad_out.contiguous(), msg, winv, g.tgt, grad_msg, grad_winv)
+        rotate_back_bwd_.raw(grad_out.contiguous(), msg, winv, g.tgt, grad_msg, grad_winv)
         return grad_msg, grad_winv, None
 
 
@@ -396,7 +411,7 @@ class EdgeDegree(torch.autograd.Function):
     def forward(ctx, x, radial3, winv, graph: EdgeGraph, rescale: float):
         radial3, winv, x = radial3.contiguous(), winv.contiguous(), x.contiguous()
         out = torch.empty_like(x)
-        edge_degree_fwd_(radial3, winv, graph.row_ptr, x, out, float(rescale))
+        edge_degree_fwd_.raw(radial3, winv, graph.row_ptr, x, out, float(rescale))
         ctx.save_for_backward(radial3, winv)
         ctx.graph, ctx.rescale = graph, float(rescale)
         return out
@@ -408,7 +423,7 @@ class EdgeDegree(torch.autograd.Function):
         grad_out = grad_out.contiguous()
         grad_r = torch.empty_like(radial3)
         grad_w = torch.empty_like(winv)
-        edge_degree_bwd_(grad_out, radial3, winv, g.tgt, grad_r, grad_w, ctx.rescale)
+        edge_degree_bwd_.raw(grad_out, radial3, winv, g.tgt, grad_r, grad_w, ctx.rescale)
         return grad_out, grad_r, grad_w, None, None
 
 
@@ -423,7 +438,7 @@ class SO2Gate(torch.autograd.Function):
         a0 = torch.empty(e, 3 * h, dtype=y0.dtype, device=y0.device)
         a1 = torch.empty(e, 2, 2 * h, dtype=y0.dtype, device=y0.device)
         a2 = torch.empty(e, 2, h, dtype=y0.dtype, device=y0.device)
-        so2_gate_fwd_(y0, y1, y2, a0, a1, a2, h)
+        so2_gate_fwd_.raw(y0, y1, y2, a0, a1, a2, h)
         ctx.save_for_backward(y0, y1, y2)
         return a0, a1, a2
 
@@ -431,7 +446,7 @@ class SO2Gate(torch.autograd.Function):
     def backward(ctx, ga0, ga1, ga2):
         y0, y1, y2 = ctx.saved_tensors
         g0, g1, g2 = torch.empty_like(y0), torch.empty_like(y1), torch.empty_like(y2)
-        so2_gate_bwd_(ga0.contiguous(), ga1.contiguous(), ga2.contiguous(), y0, y1, y2, g0, g1, g2, y0.shape[1] // 5)
+        so2_gate_bwd_.raw(ga0.contiguous(), ga1.contiguous(), ga2.contiguous(), y0, y1, y2, g0, g1, g2, y0.shape[1] // 5)
         return g0, g1, g2
 
 
@@ -443,7 +458,7 @@ class SO2Combine(torch.autograd.Function):
         z0, z1, z2 = z0.contiguous(), z1.contiguous(), z2.contiguous()
         c = z0.shape[1] // 3
         out = torch.empty(z0.shape[0], 9, c, dtype=z0.dtype, device=z0.device)
-        so2_combine_fwd_(z0, z1, z2, out, c)
+        so2_combine_fwd_.raw(z0, z1, z2, out, c)
         ctx.c = c
         return out
 
@@ -454,7 +469,7 @@ class SO2Combine(torch.autograd.Function):
         g0 = torch.empty(e, 3 * c, dtype=grad_out.dtype, device=grad_out.device)
         g1 = torch.empty(e, 2, 4 * c, dtype=grad_out.dtype, device=grad_out.device)
         g2 = torch.empty(e, 2, 2 * c, dtype=grad_out.dtype, device=grad_out.device)
-        so2_combine_bwd_(grad_out.contiguous(), g0, g1, g2, c)
+        so2_combine_bwd_.raw(grad_out.contiguous(), g0, g1, g2, c)
         return g0, g1, g2
 
 
@@ -473,7 +488,7 @@ class EdgeGeometry(torch.autograd.Function):
         gauss = torch.empty(e, num_basis, dtype=pos.dtype, device=dev)
         shift = None if shift is None else shift.contiguous()
         gamma = None if gamma is None else gamma.contiguous()
-        edge_geometry_fwd_(pos, graph.src, graph.tgt, shift, gamma, vec, dist, env, wig, gauss, cutoff, num_basis,
+        edge_geometry_fwd_.raw(pos, graph.src, graph.tgt, shift, gamma, vec, dist, env, wig, gauss, cutoff, num_basis,
                            b_start, b_stop, b_width)
         ctx.save_for_backward(pos, shift, gamma)
         ctx.graph = graph
@@ -490,7 +505,7 @@ class EdgeGeometry(torch.autograd.Function):
             return None if t is None else t.contiguous()
 
         grad_vec = torch.empty(g.num_edges, 3, dtype=pos.dtype, device=pos.device)
-        edge_geometry_bwd_(pos, g.src, g.tgt, shift, gamma, c(gwig), c(genv), c(ggauss), c(gdist), grad_vec, *ctx.params)
+        edge_geometry_bwd_.raw(pos, g.src, g.tgt, shift, gamma, c(gwig), c(genv), c(ggauss), c(gdist), grad_vec, *ctx.params)
         grad_pos = torch.empty_like(pos)
         segment_sum(grad_vec, g.src_ptr, g.src_perm, pos.shape[0], out=grad_pos)
         nt = g.num_targets

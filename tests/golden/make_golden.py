@@ -196,8 +196,23 @@ def make_model_golden():
     np.savez_compressed(os.path.join(OUT, "uma_s_energy_forces.npz"), **out)
 
 
+def make_partition_golden():
+    """Rank assignments of the reference's Morton partition (graph_partition.py:38-97)."""
+    ref_shim.load()
+    from fairchem.core.common.parallelism.graph_partition import partition_atoms_spatial
+
+    out = {}
+    for name, d in (("water_600", synthetic.water_box(600, seed=0)), ("molecules_8", synthetic.molecule_batch(8, seed=3)),
+                    ("fcc_cu_256", synthetic.fcc_cu((4, 4, 4), seed=0))):
+        for p in (2, 3, 4, 8):
+            out[f"{name}_p{p}"] = partition_atoms_spatial(d.pos, p).numpy().astype(np.int16)
+    np.savez_compressed(os.path.join(OUT, "partition.npz"), **out)
+
+
 if __name__ == "__main__":
-    which = sys.argv[1:] or ["graph", "wigner", "ops", "model"]
+    which = sys.argv[1:] or ["graph", "wigner", "ops", "model", "partition"]
+    if "partition" in which:
+        make_partition_golden()
     if "graph" in which:
         make_graph_golden()
     if "wigner" in which:
