@@ -268,7 +268,7 @@ class _EdgeCtx:
     def __init__(self, graph, chunks, wig, winv, gauss, z_src, z_tgt):
         self.graph, self.chunks = graph, chunks
         self.wig, self.winv, self.gauss = wig, winv, gauss
-        self.z_src, self.z_tgt = z_src, z_tgt
+        self.z_src, self.z_tgt = z_src.to(torch.int32).contiguous(), z_tgt.to(torch.int32).contiguous()
 
 
 class _GemmState:
@@ -356,11 +356,11 @@ def _linear(x2d, weight, bias=None):
 def _radial(rad: RadialMLP, tables, gauss_c, zs, zt, nb: int):
     """RadialMLP on [gauss | src_emb[z_s] | tgt_emb[z_t]] with the embedding part of the first Linear
     folded into per-element tables."""
-    w0 = rad.net[0]
-    pre = _linear(gauss_c, w0.weight[:, :nb], w0.bias) + tables[0][zs] + tables[1][zt]
-    h = F.silu(F.layer_norm(pre, pre.shape[-1:], rad.net[1].weight, rad.net[1].bias, rad.net[1].eps))
-    h = _linear(h, rad.net[3].weight, rad.net[3].bias)
-    h = F.silu(F.layer_norm(h, h.shape[-1:], rad.net[4].weight, rad.net[4].bias, rad.net[4].eps))
+    w0, ln1, ln2 = rad.net[0], rad.net[1], rad.net[4]
+    pre = _linear(gauss_c, w0.weight[:, :nb], w0.bias)
+    h = ops.RadialAct.apply(pre, tables[0], tables[1], zs, zt, ln1.weight.detach(), ln1.bias.detach(), ln1.eps)
+    pre = _linear(h, rad.net[3].weight, rad.net[3].bias)
+    h = ops.RadialAct.apply(pre, None, None, None, None, ln2.weight.detach(), ln2.bias.detach(), ln2.eps)
     return _linear(h, rad.net[6].weight, rad.net[6].bias)
 
 
@@ -572,7 +572,8 @@ class eSCNMDBackboneB200(nn.Module):
     def _tables(self, rad: RadialMLP):
         nb, ec = self.num_distance_basis, self.edge_channels
         w0 = rad.net[0].weight
-        return (self.source_embedding.weight @ w0[:, nb:nb + ec].t(), self.target_embedding.weight @ w0[:, nb + ec:].t())
+        return ((self.source_embedding.weight @ w0[:, nb:nb + ec].t()).detach().contiguous(),
+                (self.target_embedding.weight @ w0[:, nb + ec:].t()).detach().contiguous())
 
     def csd_embedding(self, charge, spin, dataset):
         emb = torch.cat([self.charge_embedding(charge), self.spin_embedding(spin), self.dataset_embedding(dataset)], dim=1)

@@ -7,8 +7,10 @@
 //               weights into a 128-byte-swizzled shared-memory ring; owns the TMEM allocation
 //   warp 1      one elected thread issues tcgen05.mma (M=128, N=128, K=8) and commits to mbarriers
 //   warps 2..5  PRECISION 3 only: write the TF32 low part of each landed A tile next to it
-//   warps 6..9  epilogue: tcgen05.ld of a finished accumulator, + bias, float4 stores; runs while the
-//               next tile's main loop fills the other accumulator (TMEM is double buffered)
+//   warps 6..9  epilogue: tcgen05.ld of a finished accumulator, + bias, then each warp stages its 32x32
+//               sub-tiles in 128-byte-swizzled shared memory and writes them with TMA stores (coalesced,
+//               clipped at the matrix edge); runs while the next tile's main loop fills the other
+//               accumulator (TMEM is double buffered)
 //
 // PRECISION 1 feeds float32 bits to the tensor core, which reads them as TF32 (low 13 mantissa bits
 // ignored).  PRECISION 3 restores float32-level accuracy with three products per k-step,
@@ -40,7 +42,8 @@ template <int P> struct GemmCfg {
     static constexpr int kStageBytes = kTilesPerStage * kTileBytes;
     static constexpr int kAccCols = P == 3 ? 2 * BN : BN;  // main (+ correction) accumulator
     static constexpr int kTmemCols = 2 * kAccCols;         // double buffered
-    static constexpr int kSmemBytes = kStages * kStageBytes + 1024 /*align*/ + 256 /*barriers*/;
+    static constexpr int kEpiBytes = 4 * 2 * 4096;         // 4 warps x 2 buffers x (32 rows x 128 B)
+    static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*align*/ + 256 /*barriers*/;
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -87,6 +90,12 @@ __device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map
         "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
         ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
         : "memory");
+}
+
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, uint32_t src, int x, int y) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(reinterpret_cast<uint64_t>(map)),
+                 "r"(src), "r"(x), "r"(y)
+                 : "memory");
 }
 
 // K-major, 128-byte swizzle: rows at a 128 B pitch, 8-row groups 1024 B apart, descriptor version 1 (sm_100)
@@ -155,14 +164,15 @@ __device__ __forceinline__ void write_low_tile(uint32_t a_addr, uint32_t lo_addr
 template <int P>
 __global__ void __launch_bounds__(kGemmThreads, 1)
     gemm_tf32_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                     const __grid_constant__ CUtensorMap map_wlo, const float* __restrict__ bias, float* __restrict__ c,
-                     int64_t ldc, int64_t m_total, int n_total, int k_total, int tiles_n, int64_t num_tiles,
+                     const __grid_constant__ CUtensorMap map_wlo, const __grid_constant__ CUtensorMap map_c,
+                     const float* __restrict__ bias, int64_t m_total, int n_total, int k_total, int tiles_n, int64_t num_tiles,
                      int32_t* __restrict__ status) {
     using Cfg = GemmCfg<P>;
     constexpr int S = Cfg::kStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t bar_base = base + S * Cfg::kStageBytes;
+    const uint32_t epi_base = base + S * Cfg::kStageBytes;  // 1024-byte aligned staging buffers of the epilogue warps
+    const uint32_t bar_base = epi_base + Cfg::kEpiBytes;
     // barrier block: full[S] | conv[S] | empty[S] | tmem_full[2] | tmem_empty[2] | tmem slot | abort flag
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto conv_bar = [&](int s) { return bar_base + 8u * (S + s); };
@@ -278,6 +288,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
         // epilogue: warp q = warp % 4 owns TMEM lanes [32q, 32q+32)
         const int q = warp & 3;
         int64_t tcount = 0;
+        int chunk = 0;
         bool ok = true;
         for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++tcount) {
             const int tile_n = (int)(tile % tiles_n);
@@ -288,10 +299,11 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
             ok = __all_sync(kFull, ok);
             if (!ok) break;
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int64_t row = tile_m * BM + q * 32 + lane;
+            const int64_t row0 = tile_m * BM + q * 32;
             const uint32_t acc = tmem_base + (uint32_t)(buf * Cfg::kAccCols) + ((uint32_t)(q * 32) << 16);
 #pragma unroll 1
-            for (int cc = 0; cc < BN / 32; ++cc) {
+            for (int cc = 0; cc < BN / 32; ++cc, ++chunk) {
+                const int col0 = tile_n * BN + cc * 32;
                 uint32_t r[32];
                 FCB_TMEM_LD32(r, acc + (uint32_t)(cc * 32));
                 if (P == 3) {
@@ -303,23 +315,31 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
                 } else {
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 }
-                if (row < m_total) {
-                    float* crow = c + row * ldc;
+                if (row0 >= m_total || col0 >= n_total) continue;  // sub-tile entirely outside the matrix
+                // the store issued two chunks ago read this staging buffer; let it finish before overwriting
+                const uint32_t stage = epi_base + (uint32_t)((q * 2 + (chunk & 1)) * 4096);
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                __syncwarp();
 #pragma unroll
-                    for (int v = 0; v < 8; ++v) {
-                        const int col = tile_n * BN + cc * 32 + v * 4;
-                        if (col < n_total) {
-                            float4 o = make_float4(__uint_as_float(r[v * 4 + 0]), __uint_as_float(r[v * 4 + 1]),
-                                                   __uint_as_float(r[v * 4 + 2]), __uint_as_float(r[v * 4 + 3]));
-                            if (bias) o = add4(o, ld4(bias + col));
-                            st4(crow + col, o);
-                        }
-                    }
+                for (int v = 0; v < 8; ++v) {
+                    float4 o = make_float4(__uint_as_float(r[v * 4 + 0]), __uint_as_float(r[v * 4 + 1]), __uint_as_float(r[v * 4 + 2]),
+                                           __uint_as_float(r[v * 4 + 3]));
+                    if (bias && col0 + v * 4 < n_total) o = add4(o, ld4(bias + col0 + v * 4));
+                    // row `lane` of the 32x32 sub-tile, 16-byte chunk v, 128-byte swizzle: chunk index XOR (row % 8)
+                    const uint32_t dst = stage + (uint32_t)(lane * 128 + ((v ^ (lane & 7)) * 16));
+                    asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "f"(o.x), "f"(o.y), "f"(o.z), "f"(o.w) : "memory");
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    tma_store_2d(&map_c, stage, col0, (int)row0);
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(tempty_bar(buf));  // 128 arrivals hand the accumulator back to the MMA thread
         }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all stores of this warp have landed
     }
 
     __syncwarp();
@@ -359,13 +379,13 @@ static EncodeTiledFn encode_fn() {
     return fn;
 }
 
-// 2-D float32 row-major [rows, cols] with row stride ld (floats); box = 32 columns x 128 rows, 128-byte swizzle
-static int make_map(CUtensorMap* map, const float* ptr, int64_t rows, int64_t cols, int64_t ld) {
+// 2-D float32 row-major [rows, cols] with row stride ld (floats); box = 32 columns x box_rows rows, 128-byte swizzle
+static int make_map(CUtensorMap* map, const float* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows = BM) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return FCB200_EINVAL;
     cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t gstride[1] = {(cuuint64_t)ld * 4};
-    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)BM};
+    cuuint32_t box[2] = {(cuuint32_t)BK, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), gdim, gstride, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
@@ -386,8 +406,8 @@ static int sm_count() {
 }
 
 template <int P>
-static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mwlo, const float* bias, float* c,
-                       int64_t ldc, int64_t m, int n, int k, int32_t* status, cudaStream_t s) {
+static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mwlo, const CUtensorMap& mc,
+                       const float* bias, int64_t m, int n, int k, int32_t* status, cudaStream_t s) {
     static bool attr_set = false;
     if (!attr_set) {
         if (cudaFuncSetAttribute(gemm_tf32_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<P>::kSmemBytes) != cudaSuccess)
@@ -398,8 +418,7 @@ static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, const CUten
     const int64_t tiles_m = (m + BM - 1) / BM;
     const int64_t num_tiles = tiles_m * tiles_n;
     const int grid = (int)(num_tiles < sm_count() ? num_tiles : sm_count());
-    gemm_tf32_kernel<P><<<grid, kGemmThreads, GemmCfg<P>::kSmemBytes, s>>>(ma, mw, mwlo, bias, c, ldc, m, n, k, tiles_n, num_tiles,
-                                                                        status);
+    gemm_tf32_kernel<P><<<grid, kGemmThreads, GemmCfg<P>::kSmemBytes, s>>>(ma, mw, mwlo, mc, bias, m, n, k, tiles_n, num_tiles, status);
     return launch_status();
 }
 
@@ -424,14 +443,16 @@ extern "C" int fcb200_gemm_tf32(const float* a, int64_t lda, const float* w, con
     if (!aligned16(a) || !aligned16(w) || !aligned16(c) || (bias && !aligned16(bias)) || (w_lo && !aligned16(w_lo)))
         return FCB200_EALIGN;
     if (m == 0) return FCB200_OK;
-    CUtensorMap ma, mw, mwlo;
+    CUtensorMap ma, mw, mwlo, mc;
     int rc = make_map(&ma, a, m, k, lda);
     if (rc) return rc;
     rc = make_map(&mw, w, n, k, ldw);
     if (rc) return rc;
     rc = make_map(&mwlo, precision == 3 ? w_lo : w, n, k, ldw);
     if (rc) return rc;
+    rc = make_map(&mc, c, m, n, ldc, 32);
+    if (rc) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    return precision == 3 ? launch_gemm<3>(ma, mw, mwlo, bias, c, ldc, m, n, k, status, s)
-                          : launch_gemm<1>(ma, mw, mwlo, bias, c, ldc, m, n, k, status, s);
+    return precision == 3 ? launch_gemm<3>(ma, mw, mwlo, mc, bias, m, n, k, status, s)
+                          : launch_gemm<1>(ma, mw, mwlo, mc, bias, m, n, k, status, s);
 }

@@ -257,6 +257,29 @@ def edge_geometry_bwd_(pos: Tensor, src: Tensor, tgt: Tensor, shift: Optional[Te
             nbytes=e * 4 * (2 + 6 + 3 + 3 + 2 + WIG + num_basis))
 
 
+@_op("radial_act_fwd", ("out", "stats"))
+def radial_act_fwd_(pre: Tensor, table_src: Optional[Tensor], table_tgt: Optional[Tensor], z_src: Optional[Tensor],
+                    z_tgt: Optional[Tensor], ln_weight: Tensor, ln_bias: Tensor, eps: float, out: Tensor, stats: Tensor) -> None:
+    _chk(pre, table_src, table_tgt, z_src, z_tgt, ln_weight, ln_bias, out, stats)
+    _f32(pre, table_src, table_tgt, ln_weight, ln_bias, out, stats)
+    e, w = pre.shape
+    _launch("radial_act_fwd", "fcb200_radial_act_fwd",
+            (_p(pre), _p(table_src), _p(table_tgt), _p(z_src), _p(z_tgt), _p(ln_weight), _p(ln_bias), eps, _p(out), _p(stats), e,
+             w, _stream()), nbytes=e * (8 * w + 16))
+
+
+@_op("radial_act_bwd", ("grad_pre",))
+def radial_act_bwd_(grad_out: Tensor, pre: Tensor, table_src: Optional[Tensor], table_tgt: Optional[Tensor],
+                    z_src: Optional[Tensor], z_tgt: Optional[Tensor], ln_weight: Tensor, ln_bias: Tensor, stats: Tensor,
+                    grad_pre: Tensor) -> None:
+    _chk(grad_out, pre, table_src, table_tgt, z_src, z_tgt, ln_weight, ln_bias, stats, grad_pre)
+    _f32(grad_out, pre, table_src, table_tgt, ln_weight, ln_bias, stats, grad_pre)
+    e, w = pre.shape
+    _launch("radial_act_bwd", "fcb200_radial_act_bwd",
+            (_p(grad_out), _p(pre), _p(table_src), _p(table_tgt), _p(z_src), _p(z_tgt), _p(ln_weight), _p(ln_bias), _p(stats),
+             _p(grad_pre), e, w, _stream()), nbytes=e * (12 * w + 16))
+
+
 @_op("gemm_tf32", ("c", "status"))
 def gemm_tf32_(a: Tensor, w: Tensor, w_lo: Optional[Tensor], bias: Optional[Tensor], c: Tensor, precision: int,
                status: Tensor) -> None:
@@ -512,3 +535,25 @@ class EdgeGeometry(torch.autograd.Function):
         segment_sum(grad_vec, g.row_ptr, None, nt, out=grad_pos if nt == pos.shape[0] else grad_pos[:nt],
                     accumulate=True, scale=-1.0)
         return grad_pos, None, None, None, None, None, None, None, None
+
+
+class RadialAct(torch.autograd.Function):
+    """SiLU(LayerNorm(pre + table_src[z_src] + table_tgt[z_tgt])) on [E,128] rows; differentiable in ``pre``."""
+
+    @staticmethod
+    def forward(ctx, pre, table_src, table_tgt, z_src, z_tgt, ln_weight, ln_bias, eps: float):
+        pre = pre.contiguous()
+        out = torch.empty_like(pre)
+        stats = torch.empty(pre.shape[0], 2, dtype=pre.dtype, device=pre.device)
+        radial_act_fwd_.raw(pre, table_src, table_tgt, z_src, z_tgt, ln_weight, ln_bias, float(eps), out, stats)
+        ctx.save_for_backward(pre, stats)
+        ctx.consts = (table_src, table_tgt, z_src, z_tgt, ln_weight, ln_bias)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        pre, stats = ctx.saved_tensors
+        table_src, table_tgt, z_src, z_tgt, ln_weight, ln_bias = ctx.consts
+        grad_pre = torch.empty_like(pre)
+        radial_act_bwd_.raw(grad_out.contiguous(), pre, table_src, table_tgt, z_src, z_tgt, ln_weight, ln_bias, stats, grad_pre)
+        return grad_pre, None, None, None, None, None, None, None

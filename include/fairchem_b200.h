@@ -155,6 +155,24 @@ int fcb200_so2_combine_fwd(const float* z0, const float* z1, const float* z2, fl
 int fcb200_so2_combine_bwd(const float* grad_out, float* g0, float* g1, float* g2, int64_t num_edges,
                            int32_t channels, void* stream);
 
+/* ---------------------------------------------------------------- radial MLP hidden activation */
+
+/*
+ * out = SiLU(LayerNorm(pre + table_src[z_src] + table_tgt[z_tgt])) over rows of width 128, with the
+ * row statistics (mean, 1/std) saved for the backward pass.  One pass, one warp per row.
+ * Replaces the LayerNorm + SiLU pairs of RadialMLP (src/fairchem/core/models/uma/nn/radial.py:61-86)
+ * and, through the two tables (embedding @ W^T of the first Linear), the source/target embedding
+ * columns of x_edge (src/fairchem/core/models/uma/escn_md.py:844-853).  Tables may be NULL.
+ *   pre [E,128]; table_* [num_elements,128]; z_* [E] int32; ln_weight, ln_bias [128]; stats [E,2] out
+ */
+int fcb200_radial_act_fwd(const float* pre, const float* table_src, const float* table_tgt, const int32_t* z_src,
+                          const int32_t* z_tgt, const float* ln_weight, const float* ln_bias, float eps, float* out,
+                          float* stats, int64_t num_edges, int32_t width, void* stream);
+/* Backward of fcb200_radial_act_fwd w.r.t. pre (the tables and LayerNorm parameters are frozen). */
+int fcb200_radial_act_bwd(const float* grad_out, const float* pre, const float* table_src, const float* table_tgt,
+                          const int32_t* z_src, const int32_t* z_tgt, const float* ln_weight, const float* ln_bias,
+                          const float* stats, float* grad_pre, int64_t num_edges, int32_t width, void* stream);
+
 /* ---------------------------------------------------------------- edge geometry */
 
 /*

@@ -241,3 +241,27 @@ def test_edge_geometry_backward_scalars(ops, golden):
     loss = (d * cd).sum() + (O.envelope(d / 6.0) * ce).sum() + (O.gaussian_smearing(d, 0.0, 6.0, 64, 2.0) * cg).sum()
     (ref,) = torch.autograd.grad(loss, pd)
     torch.testing.assert_close(gp.cpu(), ref.float(), rtol=1e-3, atol=1e-4 * ref.abs().max().item())
+
+
+@pytest.mark.parametrize("with_tables", [True, False])
+def test_radial_activation_forward_backward(ops, with_tables):
+    """Fused table-add + LayerNorm + SiLU against torch (radial.py:61-86)."""
+    g = torch.Generator().manual_seed(8)
+    e, w, nel = 777, 128, 100
+    pre = torch.randn(e, w, generator=g).cuda()
+    ts, tt = torch.randn(nel, w, generator=g).cuda() * 0.3, torch.randn(nel, w, generator=g).cuda() * 0.3
+    zs, zt = torch.randint(0, nel, (e,), generator=g).cuda(), torch.randint(0, nel, (e,), generator=g).cuda()
+    gamma, beta = torch.randn(w, generator=g).cuda(), torch.randn(w, generator=g).cuda()
+    a = pre.clone().requires_grad_(True)
+    if with_tables:
+        out = ops.RadialAct.apply(a, ts, tt, zs.to(torch.int32), zt.to(torch.int32), gamma, beta, 1e-5)
+    else:
+        out = ops.RadialAct.apply(a, None, None, None, None, gamma, beta, 1e-5)
+    b = pre.double().requires_grad_(True)
+    y = b + (ts.double()[zs] + tt.double()[zt] if with_tables else 0.0)
+    ref = torch.nn.functional.silu(torch.nn.functional.layer_norm(y, (w,), gamma.double(), beta.double(), 1e-5))
+    torch.testing.assert_close(out, ref.float(), rtol=1e-5, atol=1e-5)
+    cot = torch.randn(e, w, generator=g).cuda()
+    (ga,) = torch.autograd.grad(out, a, cot)
+    (gb,) = torch.autograd.grad(ref, b, cot.double())
+    torch.testing.assert_close(ga, gb.float(), rtol=1e-4, atol=1e-5 * max(1.0, gb.abs().max().item()))
