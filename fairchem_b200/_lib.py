@@ -18,17 +18,15 @@ P, I32, I64, F32 = c_void_p, c_int32, c_int64, c_float
 # name -> argtypes (every function returns int)
 SIGNATURES = {
     "fcb200_version": [],
-    "fcb200_gather_rotate_fwd": [P, P, P, P, P, P, P, P, I64, I64, I32, P],
+    "fcb200_gather_rotate_fwd": [P, P, P, P, P, P, I64, I64, I32, P],
     "fcb200_rotate_back_reduce_fwd": [P, P, P, P, I64, I64, I32, P],
     "fcb200_edge_degree_fwd": [P, P, P, P, P, F32, I64, I64, I32, P],
-    "fcb200_gather_rotate_bwd": [P, P, P, P, P, P, P, P, P, P, P, P, I64, I64, I32, P],
+    "fcb200_gather_rotate_bwd": [P, P, P, P, P, P, P, P, P, P, I64, I64, I32, P],
     "fcb200_rotate_back_bwd": [P, P, P, P, P, P, I64, I64, I32, P],
     "fcb200_edge_degree_bwd": [P, P, P, P, P, P, F32, I64, I64, I32, P],
     "fcb200_segment_sum": [P, P, P, P, P, I32, F32, I64, I64, P],
-    "fcb200_so2_gate_fwd": [P, P, P, P, P, P, I64, I32, P],
-    "fcb200_so2_gate_bwd": [P, P, P, P, P, P, P, P, P, I64, I32, P],
-    "fcb200_so2_combine_fwd": [P, P, P, P, I64, I32, P],
-    "fcb200_so2_combine_bwd": [P, P, P, P, I64, I32, P],
+    "fcb200_so2_gate_fwd": [P, P, I64, I32, P],
+    "fcb200_so2_gate_bwd": [P, P, P, I64, I32, P],
     "fcb200_radial_act_fwd": [P, P, P, P, P, P, P, F32, P, P, I64, I32, P],
     "fcb200_radial_act_bwd": [P, P, P, P, P, P, P, P, P, P, I64, I32, P],
     "fcb200_edge_geometry_fwd": [P, P, P, P, P, P, P, P, P, P, F32, I32, F32, F32, F32, I64, I64, P],

@@ -321,7 +321,9 @@ def _split(w: torch.Tensor):
 
 
 def _gemm(x2, w, bias, y, precision):
-    if precision == 3:
+    if precision == 0:  # cuBLAS float32 through torch, for A/B measurements only
+        y.copy_(F.linear(x2, w, bias))
+    elif precision == 3:
         hi, lo = _split(w)
         ops.gemm_tf32_.raw(x2, hi, lo, bias, y, 3, _status(x2.device))
     else:
@@ -364,18 +366,61 @@ def _radial(rad: RadialMLP, tables, gauss_c, zs, zt, nb: int):
     return _linear(h, rad.net[6].weight, rad.net[6].bias)
 
 
-def _so2_middle(ew: Edgewise, m0, m1, m2):
-    """conv1 GEMMs -> combine+gate -> conv2 GEMMs -> combine, on the planar operands."""
-    c1, c2 = ew.so2_conv_1, ew.so2_conv_2
-    e = m0.shape[0]
-    y0 = _linear(m0, c1.fc_m0.weight, c1.fc_m0.bias)
-    y1 = _linear(m1.view(2 * e, -1), c1.so2_m_conv[0].fc.weight).view(e, 2, -1)
-    y2 = _linear(m2.view(2 * e, -1), c1.so2_m_conv[1].fc.weight).view(e, 2, -1)
-    a0, a1, a2 = ops.SO2Gate.apply(y0, y1, y2)
-    z0 = _linear(a0, c2.fc_m0.weight, c2.fc_m0.bias)
-    z1 = _linear(a1.view(2 * e, -1), c2.so2_m_conv[0].fc.weight).view(e, 2, -1)
-    z2 = _linear(a2.view(2 * e, -1), c2.so2_m_conv[1].fc.weight).view(e, 2, -1)
-    return ops.SO2Combine.apply(z0, z1, z2)
+def _block_weight(w: torch.Tensor) -> torch.Tensor:
+    """[[Wa, -Wb], [Wb, Wa]] for an SO(2) m>0 weight W = [Wa; Wb] ([2*half, K] -> [2*half, 2K]): one GEMM on
+    [x_re | x_im] gives [y_re | y_im] (SO2_m_Conv_Block, src/fairchem/core/models/uma/nn/so2_layers.py:83-169)."""
+    key = ("block", w.data_ptr(), tuple(w.shape))
+    hit = _GemmState.transposed.get(key)
+    if hit is None or hit[0]._version != w._version:
+        half = w.shape[0] // 2
+        wa, wb = w.detach()[:half], w.detach()[half:]
+        hit = (w, torch.cat([torch.cat([wa, -wb], dim=1), torch.cat([wb, wa], dim=1)], dim=0).contiguous())
+        _GemmState.transposed[key] = hit
+    return hit[1]
+
+
+class _SO2Conv(torch.autograd.Function):
+    """One SO(2) convolution as three GEMMs on column ranges of the M-major edge matrix.
+
+    x2d [E, 9*Cin] -> y [E, extra + 9*Cout]: the m=0 GEMM writes its (extra + 3*Cout) outputs first, the
+    block-form m=1 and m=2 GEMMs write next to it, so the result is already laid out as
+    [extra | row 0..8] with no concatenation or complex-combine pass."""
+
+    @staticmethod
+    def forward(ctx, x2d, conv: "SO2Convolution", cin: int):
+        e = x2d.shape[0]
+        w0, b0 = conv.fc_m0.weight.detach(), conv.fc_m0.bias.detach()
+        w1, w2 = _block_weight(conv.so2_m_conv[0].fc.weight), _block_weight(conv.so2_m_conv[1].fc.weight)
+        n0, n1, n2 = w0.shape[0], w1.shape[0], w2.shape[0]
+        y = torch.empty(e, n0 + n1 + n2, dtype=x2d.dtype, device=x2d.device)
+        p = _GemmState.precision
+        _gemm(x2d[:, : 3 * cin], w0, b0, y[:, :n0], p)
+        _gemm(x2d[:, 3 * cin: 7 * cin], w1, None, y[:, n0: n0 + n1], p)
+        _gemm(x2d[:, 7 * cin:], w2, None, y[:, n0 + n1:], p)
+        ctx.weights, ctx.cin, ctx.p = (w0, w1, w2), cin, p
+        return y
+
+    @staticmethod
+    def backward(ctx, gy):
+        w0, w1, w2 = ctx.weights
+        cin, p = ctx.cin, ctx.p
+        gy = gy.contiguous()
+        n0, n1 = w0.shape[0], w1.shape[0]
+        gx = torch.empty(gy.shape[0], 9 * cin, dtype=gy.dtype, device=gy.device)
+        _gemm(gy[:, :n0], _transposed(w0), None, gx[:, : 3 * cin], p)
+        _gemm(gy[:, n0: n0 + n1], _transposed(w1), None, gx[:, 3 * cin: 7 * cin], p)
+        _gemm(gy[:, n0 + n1:], _transposed(w2), None, gx[:, 7 * cin:], p)
+        return gx, None, None
+
+
+def _so2_middle(ew: Edgewise, m):
+    """conv 1 -> gate -> conv 2 on the M-major edge rows m [E,9,2C]; returns the messages [E,9,C]."""
+    e, cin = m.shape[0], m.shape[2]
+    y = _SO2Conv.apply(m.view(e, 9 * cin), ew.so2_conv_1, cin)
+    a = ops.SO2Gate.apply(y)
+    h = a.shape[2]
+    z = _SO2Conv.apply(a.view(e, 9 * h), ew.so2_conv_2, h)
+    return z.view(e, 9, -1)
 
 
 class _EdgeBlockFn(torch.autograd.Function):
@@ -392,11 +437,9 @@ class _EdgeBlockFn(torch.autograd.Function):
                 sl = slice(ch.e0, ch.e1)
                 rad = _radial(ew.so2_conv_1.rad_func, tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb)
                 ec = ch.e1 - ch.e0
-                m0 = torch.empty(ec, 6 * c, dtype=x.dtype, device=x.device)
-                m1 = torch.empty(ec, 2, 4 * c, dtype=x.dtype, device=x.device)
-                m2 = torch.empty(ec, 2, 2 * c, dtype=x.dtype, device=x.device)
-                ops.gather_rotate_fwd_.raw(x, g.src[sl], g.tgt[sl], wig[sl], rad, m0, m1, m2)
-                msg = _so2_middle(ew, m0, m1, m2)
+                m = torch.empty(ec, 9, 2 * c, dtype=x.dtype, device=x.device)
+                ops.gather_rotate_fwd_.raw(x, g.src[sl], g.tgt[sl], wig[sl], rad, m)
+                msg = _so2_middle(ew, m)
                 ops.rotate_back_reduce_fwd_.raw(msg, winv[sl], ch.row_ptr, out[ch.n0:ch.n1])
         ctx.save_for_backward(x, wig, winv, gauss)
         ctx.ew, ctx.tables, ctx.ectx, ctx.nb = ew, tables, ectx, nb
@@ -420,22 +463,19 @@ class _EdgeBlockFn(torch.autograd.Function):
                 g_c = gauss[sl].detach().requires_grad_(True)
                 rad = _radial(ew.so2_conv_1.rad_func, tables, g_c, ectx.z_src[sl], ectx.z_tgt[sl], nb)
                 rad_d = rad.detach()
-                m0 = torch.empty(ec, 6 * c, dtype=x.dtype, device=x.device)
-                m1 = torch.empty(ec, 2, 4 * c, dtype=x.dtype, device=x.device)
-                m2 = torch.empty(ec, 2, 2 * c, dtype=x.dtype, device=x.device)
-                ops.gather_rotate_fwd_.raw(x, g.src[sl], g.tgt[sl], wig[sl], rad_d, m0, m1, m2)
-                m0.requires_grad_(True), m1.requires_grad_(True), m2.requires_grad_(True)
-                msg = _so2_middle(ew, m0, m1, m2)
+                m = torch.empty(ec, 9, 2 * c, dtype=x.dtype, device=x.device)
+                ops.gather_rotate_fwd_.raw(x, g.src[sl], g.tgt[sl], wig[sl], rad_d, m)
+                m.requires_grad_(True)
+                msg = _so2_middle(ew, m)
             grad_msg = torch.empty_like(msg)
             ops.rotate_back_bwd_.raw(grad_out, msg.detach(), winv[sl], g.tgt[sl], grad_msg, gwinv[sl])
-            gm0, gm1, gm2 = torch.autograd.grad(msg, (m0, m1, m2), grad_msg)
+            (gm,) = torch.autograd.grad(msg, (m,), grad_msg)
             del msg, grad_msg
             g_src = torch.empty(ec, 9, c, dtype=x.dtype, device=x.device)
             g_tgt = torch.empty(ec, 9, c, dtype=x.dtype, device=x.device)
             grad_rad = torch.empty_like(rad_d)
-            ops.gather_rotate_bwd_.raw(gm0.contiguous(), gm1.contiguous(), gm2.contiguous(), x, g.src[sl], g.tgt[sl], wig[sl],
-                                   rad_d, g_src, g_tgt, gwig[sl], grad_rad)
-            del gm0, gm1, gm2, m0, m1, m2
+            ops.gather_rotate_bwd_.raw(gm.contiguous(), x, g.src[sl], g.tgt[sl], wig[sl], rad_d, g_src, g_tgt, gwig[sl], grad_rad)
+            del gm, m
             # node reductions: target rows of the chunk are contiguous; source rows are the chunk's distinct sources
             ops.segment_sum(g_tgt, ch.row_ptr, None, ch.n1 - ch.n0, out=gx[ch.n0:ch.n1], accumulate=True)
             ops.segment_sum(g_src, ch.src_ptr, ch.src_perm, ch.src_nodes.shape[0], out=gx, out_index=ch.src_nodes,

@@ -11,13 +11,12 @@ namespace fcb200 {
 
 constexpr int kWarpsPerBlock = 8;
 
-// Row m (M-major) of edge e inside the three planar GEMM operands: rows 0-2 -> buf0 [E,3,w],
-// rows 3-6 -> buf1 [E,4,w] (= [E,2,2w]: real pair, imaginary pair), rows 7-8 -> buf2 [E,2,w].
+// Row m (M-major) of edge e inside an [E, 9, w] buffer.  The SO(2) GEMMs read their operands as column
+// ranges of the flattened [E, 9*w] matrix: rows 0-2 (m = 0), rows 3-6 (m = 1: real pair | imaginary
+// pair) and rows 7-8 (m = 2), so nothing is repacked between the rotation kernels and the GEMMs.
 template <class P>
-__device__ __forceinline__ P* packed_row(P* b0, P* b1, P* b2, int64_t e, int m, int w) {
-    if (m < 3) return b0 + (e * 3 + m) * (int64_t)w;
-    if (m < 7) return b1 + (e * 4 + (m - 3)) * (int64_t)w;
-    return b2 + (e * 2 + (m - 7)) * (int64_t)w;
+__device__ __forceinline__ P* edge_row(P* buf, int64_t e, int m, int w) {
+    return buf + (e * 9 + m) * (int64_t)w;
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -26,8 +25,8 @@ __device__ __forceinline__ P* packed_row(P* b0, P* b1, P* b2, int64_t e, int m, 
 template <bool HAS_RAD>
 __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
     gather_rotate_fwd_kernel(const float* __restrict__ x, const int32_t* __restrict__ src, const int32_t* __restrict__ tgt,
-                             const float* __restrict__ wig, const float* __restrict__ radial, float* __restrict__ out0,
-                             float* __restrict__ out1, float* __restrict__ out2, int64_t num_edges, int channels) {
+                             const float* __restrict__ wig, const float* __restrict__ radial, float* __restrict__ out,
+                             int64_t num_edges, int channels) {
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
@@ -63,7 +62,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
                     as = mul4(as, ld4(r));
                     at = mul4(at, ld4(r + channels));
                 }
-                float* o = packed_row(out0, out1, out2, e, m, 2 * channels) + c0;
+                float* o = edge_row(out, e, m, 2 * channels) + c0;
                 st4(o, as);
                 st4(o + channels, at);
             }
@@ -135,8 +134,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
 // ---------------------------------------------------------------------------------------------
 template <bool HAS_RAD>
 __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
-    gather_rotate_bwd_kernel(const float* __restrict__ go0, const float* __restrict__ go1, const float* __restrict__ go2,
-                             const float* __restrict__ x, const int32_t* __restrict__ src,
+    gather_rotate_bwd_kernel(const float* __restrict__ grad_out, const float* __restrict__ x, const int32_t* __restrict__ src,
                              const int32_t* __restrict__ tgt, const float* __restrict__ wig, const float* __restrict__ radial,
                              float* __restrict__ g_src, float* __restrict__ g_tgt, float* __restrict__ grad_wig,
                              float* __restrict__ grad_radial, int64_t num_edges, int channels) {
@@ -169,7 +167,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
                     const int m = order[k];
                     const int L = m2l(m);
                     const int l = deg_of(L);
-                    float4 go = ld4(packed_row(go0, go1, go2, e, m, 2 * channels) + half * channels + c0);
+                    float4 go = ld4(edge_row(grad_out, e, m, 2 * channels) + half * channels + c0);
                     if (HAS_RAD) {
                         float4 rot = f4zero();
 #pragma unroll
@@ -347,149 +345,66 @@ __global__ void segment_sum_scalar_kernel(const float* __restrict__ rows, const 
 }
 
 // ---------------------------------------------------------------------------------------------
-// SO(2) glue: complex combine + gate activation
+// gate activation between the two SO(2) convolutions
 // ---------------------------------------------------------------------------------------------
-__device__ __forceinline__ float sigmoidf_(float v) { return 1.0f / (1.0f + __expf(-v)); }
 __device__ __forceinline__ float sigmoid_acc(float v) { return 1.0f / (1.0f + expf(-v)); }
 __device__ __forceinline__ float4 sig4(float4 v) {
     return make_float4(sigmoid_acc(v.x), sigmoid_acc(v.y), sigmoid_acc(v.z), sigmoid_acc(v.w));
 }
+// gate index (0: l=1 gate, 1: l=2 gate) of M-major rows 1..8: [l1,l2 | l1,l2 | l1,l2 | l2 | l2]
+__host__ __device__ constexpr int gate_of(int m) {
+    constexpr int t[9] = {0, 0, 1, 0, 1, 0, 1, 1, 1};
+    return t[m];
+}
 
-// rows of the m>0 blocks from the two GEMM output rows (so2_layers.py:72-80):
-//   real = row0[:half] - row1[half:], imag = row1[:half] + row0[half:]
-template <bool GATE>
+// y [E, 11H] = [gate scalars 2H | rows 0..8 (9H)] (the three conv-1 GEMMs write it side by side);
+// out [E, 9, H]: row 0 -> SiLU, rows 1..8 -> value * sigmoid(gate of the row's degree).
 __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
-    so2_combine_fwd_kernel(const float* __restrict__ y0, const float* __restrict__ y1, const float* __restrict__ y2,
-                           float* __restrict__ out, float* __restrict__ out1, float* __restrict__ out2, int64_t num_edges,
-                           int ch) {
+    so2_gate_fwd_kernel(const float* __restrict__ y, float* __restrict__ out, int64_t num_edges, int ch) {
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
-    const int n0 = GATE ? 5 * ch : 3 * ch;
-    const int goff = GATE ? 2 * ch : 0;
     for (int64_t e = warp0; e < num_edges; e += nwarps) {
-        const float* p0 = y0 + e * n0;
-        const float* p1 = y1 + e * 8LL * ch;
-        const float* p2 = y2 + e * 4LL * ch;
-        // GATE: rows go to the three planar operands of the next convolution; else one [E,9,ch] tensor
-        auto row = [&](int m) -> float* {
-            return GATE ? packed_row(out, out1, out2, e, m, ch) : out + (e * 9LL + m) * ch;
-        };
+        const float* p = y + e * 11LL * ch;
+        float* o = out + e * 9LL * ch;
         for (int c = lane * 4; c < ch; c += 128) {
-            float4 gate1 = make_float4(1.f, 1.f, 1.f, 1.f), gate2 = gate1;
-            if (GATE) {
-                gate1 = sig4(ld4(p0 + c));
-                gate2 = sig4(ld4(p0 + ch + c));
-            }
-            float4 v0 = ld4(p0 + goff + c);
-            if (GATE) {
-                float4 s = sig4(v0);
-                v0 = mul4(v0, s);
-            }
-            st4(row(0) + c, v0);
-            st4(row(1) + c, mul4(ld4(p0 + goff + ch + c), gate1));
-            st4(row(2) + c, mul4(ld4(p0 + goff + 2 * ch + c), gate2));
-            // m = 1: half = 2*ch; row0 = p1[0:4ch], row1 = p1[4ch:8ch]
+            float4 gate[2] = {sig4(ld4(p + c)), sig4(ld4(p + ch + c))};
+            const float4 v0 = ld4(p + 2 * ch + c);
+            st4(o + c, mul4(v0, sig4(v0)));
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const float4 g = j == 0 ? gate1 : gate2;
-                float4 re = sub4(ld4(p1 + j * ch + c), ld4(p1 + 4 * ch + 2 * ch + j * ch + c));
-                float4 im = add4(ld4(p1 + 4 * ch + j * ch + c), ld4(p1 + 2 * ch + j * ch + c));
-                st4(row(3 + j) + c, mul4(re, g));
-                st4(row(5 + j) + c, mul4(im, g));
-            }
-            // m = 2: half = ch
-            float4 re = sub4(ld4(p2 + c), ld4(p2 + 2 * ch + ch + c));
-            float4 im = add4(ld4(p2 + 2 * ch + c), ld4(p2 + ch + c));
-            st4(row(7) + c, mul4(re, gate2));
-            st4(row(8) + c, mul4(im, gate2));
+            for (int m = 1; m < 9; ++m) st4(o + m * ch + c, mul4(ld4(p + (2 + m) * ch + c), gate[gate_of(m)]));
         }
     }
 }
 
-template <bool GATE>
 __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
-    so2_combine_bwd_kernel(const float* __restrict__ grad_out, const float* __restrict__ grad_out1,
-                           const float* __restrict__ grad_out2, const float* __restrict__ y0, const float* __restrict__ y1,
-                           const float* __restrict__ y2, float* __restrict__ g0, float* __restrict__ g1, float* __restrict__ g2,
-                           int64_t num_edges, int ch) {
+    so2_gate_bwd_kernel(const float* __restrict__ grad_out, const float* __restrict__ y, float* __restrict__ grad_y,
+                        int64_t num_edges, int ch) {
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
-    const int n0 = GATE ? 5 * ch : 3 * ch;
-    const int goff = GATE ? 2 * ch : 0;
     for (int64_t e = warp0; e < num_edges; e += nwarps) {
-        auto go_row = [&](int m) -> const float* {
-            return GATE ? packed_row(grad_out, grad_out1, grad_out2, e, m, ch) : grad_out + (e * 9LL + m) * ch;
-        };
-        float* q0 = g0 + e * n0;
-        float* q1 = g1 + e * 8LL * ch;
-        float* q2 = g2 + e * 4LL * ch;
-        const float* p0 = GATE ? y0 + e * n0 : nullptr;
-        const float* p1 = GATE ? y1 + e * 8LL * ch : nullptr;
-        const float* p2 = GATE ? y2 + e * 4LL * ch : nullptr;
+        const float* p = y + e * 11LL * ch;
+        const float* go = grad_out + e * 9LL * ch;
+        float* q = grad_y + e * 11LL * ch;
         for (int c = lane * 4; c < ch; c += 128) {
-            float4 gate1 = make_float4(1.f, 1.f, 1.f, 1.f), gate2 = gate1;
-            float4 dgate1 = f4zero(), dgate2 = f4zero();  // d/d(sigmoid output)
-            if (GATE) {
-                gate1 = sig4(ld4(p0 + c));
-                gate2 = sig4(ld4(p0 + ch + c));
-            }
-            // row 0
-            float4 d0 = ld4(go_row(0) + c);
-            if (GATE) {
-                const float4 v = ld4(p0 + goff + c);
-                const float4 s = sig4(v);
-                // d silu = s * (1 + v * (1 - s))
-                d0 = make_float4(d0.x * s.x * (1.f + v.x * (1.f - s.x)), d0.y * s.y * (1.f + v.y * (1.f - s.y)),
-                                 d0.z * s.z * (1.f + v.z * (1.f - s.z)), d0.w * s.w * (1.f + v.w * (1.f - s.w)));
-            }
-            st4(q0 + goff + c, d0);
-            // rows 1, 2
+            const float4 gate[2] = {sig4(ld4(p + c)), sig4(ld4(p + ch + c))};
+            float4 dgate[2] = {f4zero(), f4zero()};
             {
-                const float4 d1 = ld4(go_row(1) + c), d2 = ld4(go_row(2) + c);
-                st4(q0 + goff + ch + c, mul4(d1, gate1));
-                st4(q0 + goff + 2 * ch + c, mul4(d2, gate2));
-                if (GATE) {
-                    dgate1 = add4(dgate1, mul4(d1, ld4(p0 + goff + ch + c)));
-                    dgate2 = add4(dgate2, mul4(d2, ld4(p0 + goff + 2 * ch + c)));
-                }
+                const float4 v = ld4(p + 2 * ch + c), s = sig4(v), d = ld4(go + c);
+                st4(q + 2 * ch + c, make_float4(d.x * s.x * (1.f + v.x * (1.f - s.x)), d.y * s.y * (1.f + v.y * (1.f - s.y)),
+                                                d.z * s.z * (1.f + v.z * (1.f - s.z)), d.w * s.w * (1.f + v.w * (1.f - s.w))));
             }
 #pragma unroll
-            for (int j = 0; j < 2; ++j) {
-                const float4 g = j == 0 ? gate1 : gate2;
-                const float4 dre_o = ld4(go_row(3 + j) + c), dim_o = ld4(go_row(5 + j) + c);
-                const float4 dre = mul4(dre_o, g), dim = mul4(dim_o, g);
-                st4(q1 + j * ch + c, dre);                                // row0[:half]
-                st4(q1 + 4 * ch + 2 * ch + j * ch + c, scale4(-1.f, dre)); // row1[half:]
-                st4(q1 + 4 * ch + j * ch + c, dim);                       // row1[:half]
-                st4(q1 + 2 * ch + j * ch + c, dim);                       // row0[half:]
-                if (GATE) {
-                    const float4 re = sub4(ld4(p1 + j * ch + c), ld4(p1 + 4 * ch + 2 * ch + j * ch + c));
-                    const float4 im = add4(ld4(p1 + 4 * ch + j * ch + c), ld4(p1 + 2 * ch + j * ch + c));
-                    const float4 t = add4(mul4(dre_o, re), mul4(dim_o, im));
-                    if (j == 0) dgate1 = add4(dgate1, t); else dgate2 = add4(dgate2, t);
-                }
+            for (int m = 1; m < 9; ++m) {
+                const float4 d = ld4(go + m * ch + c);
+                st4(q + (2 + m) * ch + c, mul4(d, gate[gate_of(m)]));
+                dgate[gate_of(m)] = add4(dgate[gate_of(m)], mul4(d, ld4(p + (2 + m) * ch + c)));
             }
-            {
-                const float4 dre_o = ld4(go_row(7) + c), dim_o = ld4(go_row(8) + c);
-                const float4 dre = mul4(dre_o, gate2), dim = mul4(dim_o, gate2);
-                st4(q2 + c, dre);
-                st4(q2 + 2 * ch + ch + c, scale4(-1.f, dre));
-                st4(q2 + 2 * ch + c, dim);
-                st4(q2 + ch + c, dim);
-                if (GATE) {
-                    const float4 re = sub4(ld4(p2 + c), ld4(p2 + 2 * ch + ch + c));
-                    const float4 im = add4(ld4(p2 + 2 * ch + c), ld4(p2 + ch + c));
-                    dgate2 = add4(dgate2, add4(mul4(dre_o, re), mul4(dim_o, im)));
-                }
-            }
-            if (GATE) {
-                // d/d(pre-sigmoid) = d/d(gate) * gate * (1 - gate)
-                st4(q0 + c, make_float4(dgate1.x * gate1.x * (1.f - gate1.x), dgate1.y * gate1.y * (1.f - gate1.y),
-                                        dgate1.z * gate1.z * (1.f - gate1.z), dgate1.w * gate1.w * (1.f - gate1.w)));
-                st4(q0 + ch + c, make_float4(dgate2.x * gate2.x * (1.f - gate2.x), dgate2.y * gate2.y * (1.f - gate2.y),
-                                             dgate2.z * gate2.z * (1.f - gate2.z), dgate2.w * gate2.w * (1.f - gate2.w)));
+#pragma unroll
+            for (int g = 0; g < 2; ++g) {
+                const float4 s = gate[g], d = dgate[g];
+                st4(q + g * ch + c, make_float4(d.x * s.x * (1.f - s.x), d.y * s.y * (1.f - s.y), d.z * s.z * (1.f - s.z), d.w * s.w * (1.f - s.w)));
             }
         }
     }
@@ -514,17 +429,16 @@ int fcb200_version(void) { return 1000; }
 #define FCB_LAUNCH(items) warp_grid(items, kWarpsPerBlock), kWarpsPerBlock * kWarp, 0, FCB_STREAM
 
 int fcb200_gather_rotate_fwd(const float* x, const int32_t* src, const int32_t* tgt, const float* wig, const float* radial,
-                             float* out_m0, float* out_m1, float* out_m2, int64_t num_edges, int64_t num_nodes,
-                             int32_t channels, void* stream) {
-    int rc = check_common(x, out_m0, num_edges, channels);
+                             float* out, int64_t num_edges, int64_t num_nodes, int32_t channels, void* stream) {
+    int rc = check_common(x, out, num_edges, channels);
     if (rc) return rc;
-    if (!src || !tgt || !wig || !out_m1 || !out_m2 || num_nodes < 0) return FCB200_EINVAL;
-    if (!aligned16(out_m1) || !aligned16(out_m2) || (radial && !aligned16(radial))) return FCB200_EALIGN;
+    if (!src || !tgt || !wig || num_nodes < 0) return FCB200_EINVAL;
+    if (radial && !aligned16(radial)) return FCB200_EALIGN;
     if (num_edges == 0) return FCB200_OK;
     if (radial)
-        gather_rotate_fwd_kernel<true><<<FCB_LAUNCH(num_edges)>>>(x, src, tgt, wig, radial, out_m0, out_m1, out_m2, num_edges, channels);
+        gather_rotate_fwd_kernel<true><<<FCB_LAUNCH(num_edges)>>>(x, src, tgt, wig, radial, out, num_edges, channels);
     else
-        gather_rotate_fwd_kernel<false><<<FCB_LAUNCH(num_edges)>>>(x, src, tgt, wig, nullptr, out_m0, out_m1, out_m2, num_edges, channels);
+        gather_rotate_fwd_kernel<false><<<FCB_LAUNCH(num_edges)>>>(x, src, tgt, wig, nullptr, out, num_edges, channels);
     return launch_status();
 }
 
@@ -549,24 +463,21 @@ int fcb200_edge_degree_fwd(const float* radial3, const float* winv, const int32_
     return launch_status();
 }
 
-int fcb200_gather_rotate_bwd(const float* grad_m0, const float* grad_m1, const float* grad_m2, const float* x, const int32_t* src,
-                             const int32_t* tgt, const float* wig, const float* radial, float* g_src, float* g_tgt,
-                             float* grad_wig, float* grad_radial, int64_t num_edges, int64_t num_nodes, int32_t channels,
-                             void* stream) {
-    int rc = check_common(grad_m0, x, num_edges, channels);
+int fcb200_gather_rotate_bwd(const float* grad_out, const float* x, const int32_t* src, const int32_t* tgt, const float* wig,
+                             const float* radial, float* g_src, float* g_tgt, float* grad_wig, float* grad_radial,
+                             int64_t num_edges, int64_t num_nodes, int32_t channels, void* stream) {
+    int rc = check_common(grad_out, x, num_edges, channels);
     if (rc) return rc;
-    if (!grad_m1 || !grad_m2 || !src || !tgt || !wig || !g_src || !g_tgt || !grad_wig || num_nodes < 0) return FCB200_EINVAL;
+    if (!src || !tgt || !wig || !g_src || !g_tgt || !grad_wig || num_nodes < 0) return FCB200_EINVAL;
     if ((radial == nullptr) != (grad_radial == nullptr)) return FCB200_EINVAL;
-    if (!aligned16(grad_m1) || !aligned16(grad_m2) || !aligned16(g_src) || !aligned16(g_tgt) ||
-        (radial && (!aligned16(radial) || !aligned16(grad_radial))))
-        return FCB200_EALIGN;
+    if (!aligned16(g_src) || !aligned16(g_tgt) || (radial && (!aligned16(radial) || !aligned16(grad_radial)))) return FCB200_EALIGN;
     if (num_edges == 0) return FCB200_OK;
     if (radial)
-        gather_rotate_bwd_kernel<true><<<FCB_LAUNCH(num_edges)>>>(grad_m0, grad_m1, grad_m2, x, src, tgt, wig, radial, g_src, g_tgt,
-                                                                  grad_wig, grad_radial, num_edges, channels);
+        gather_rotate_bwd_kernel<true><<<FCB_LAUNCH(num_edges)>>>(grad_out, x, src, tgt, wig, radial, g_src, g_tgt, grad_wig,
+                                                                  grad_radial, num_edges, channels);
     else
-        gather_rotate_bwd_kernel<false><<<FCB_LAUNCH(num_edges)>>>(grad_m0, grad_m1, grad_m2, x, src, tgt, wig, nullptr, g_src,
-                                                                   g_tgt, grad_wig, nullptr, num_edges, channels);
+        gather_rotate_bwd_kernel<false><<<FCB_LAUNCH(num_edges)>>>(grad_out, x, src, tgt, wig, nullptr, g_src, g_tgt, grad_wig,
+                                                                   nullptr, num_edges, channels);
     return launch_status();
 }
 
@@ -613,50 +524,21 @@ int fcb200_segment_sum(const float* rows, const int32_t* ptr, const int32_t* per
     return launch_status();
 }
 
-int fcb200_so2_gate_fwd(const float* y0, const float* y1, const float* y2, float* out_m0, float* out_m1, float* out_m2,
-                        int64_t num_edges, int32_t hidden, void* stream) {
-    int rc = check_common(y0, out_m0, num_edges, hidden);
+int fcb200_so2_gate_fwd(const float* y, float* out, int64_t num_edges, int32_t hidden, void* stream) {
+    int rc = check_common(y, out, num_edges, hidden);
     if (rc) return rc;
-    if (!y1 || !y2 || !out_m1 || !out_m2) return FCB200_EINVAL;
-    if (!aligned16(y1) || !aligned16(y2) || !aligned16(out_m1) || !aligned16(out_m2)) return FCB200_EALIGN;
     if (num_edges == 0) return FCB200_OK;
-    so2_combine_fwd_kernel<true><<<FCB_LAUNCH(num_edges)>>>(y0, y1, y2, out_m0, out_m1, out_m2, num_edges, hidden);
+    so2_gate_fwd_kernel<<<FCB_LAUNCH(num_edges)>>>(y, out, num_edges, hidden);
     return launch_status();
 }
 
-int fcb200_so2_gate_bwd(const float* grad_m0, const float* grad_m1, const float* grad_m2, const float* y0, const float* y1,
-                        const float* y2, float* g0, float* g1, float* g2, int64_t num_edges, int32_t hidden, void* stream) {
-    int rc = check_common(grad_m0, g0, num_edges, hidden);
+int fcb200_so2_gate_bwd(const float* grad_out, const float* y, float* grad_y, int64_t num_edges, int32_t hidden, void* stream) {
+    int rc = check_common(grad_out, y, num_edges, hidden);
     if (rc) return rc;
-    if (!grad_m1 || !grad_m2 || !y0 || !y1 || !y2 || !g1 || !g2) return FCB200_EINVAL;
-    if (!aligned16(grad_m1) || !aligned16(grad_m2) || !aligned16(y0) || !aligned16(y1) || !aligned16(y2) || !aligned16(g1) ||
-        !aligned16(g2))
-        return FCB200_EALIGN;
+    if (!grad_y) return FCB200_EINVAL;
+    if (!aligned16(grad_y)) return FCB200_EALIGN;
     if (num_edges == 0) return FCB200_OK;
-    so2_combine_bwd_kernel<true><<<FCB_LAUNCH(num_edges)>>>(grad_m0, grad_m1, grad_m2, y0, y1, y2, g0, g1, g2, num_edges, hidden);
-    return launch_status();
-}
-
-int fcb200_so2_combine_fwd(const float* z0, const float* z1, const float* z2, float* out, int64_t num_edges, int32_t channels,
-                           void* stream) {
-    int rc = check_common(z0, out, num_edges, channels);
-    if (rc) return rc;
-    if (!z1 || !z2) return FCB200_EINVAL;
-    if (!aligned16(z1) || !aligned16(z2)) return FCB200_EALIGN;
-    if (num_edges == 0) return FCB200_OK;
-    so2_combine_fwd_kernel<false><<<FCB_LAUNCH(num_edges)>>>(z0, z1, z2, out, nullptr, nullptr, num_edges, channels);
-    return launch_status();
-}
-
-int fcb200_so2_combine_bwd(const float* grad_out, float* g0, float* g1, float* g2, int64_t num_edges, int32_t channels,
-                           void* stream) {
-    int rc = check_common(grad_out, g0, num_edges, channels);
-    if (rc) return rc;
-    if (!g1 || !g2) return FCB200_EINVAL;
-    if (!aligned16(g1) || !aligned16(g2)) return FCB200_EALIGN;
-    if (num_edges == 0) return FCB200_OK;
-    so2_combine_bwd_kernel<false><<<FCB_LAUNCH(num_edges)>>>(grad_out, nullptr, nullptr, nullptr, nullptr, nullptr, g0, g1, g2,
-                                                             num_edges, channels);
+    so2_gate_bwd_kernel<<<FCB_LAUNCH(num_edges)>>>(grad_out, y, grad_y, num_edges, hidden);
     return launch_status();
 }
 

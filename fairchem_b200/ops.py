@@ -116,27 +116,25 @@ def _op(name: str, mutates):
     return deco
 
 
-@_op("gather_rotate_fwd", ("m0", "m1", "m2"))
-def gather_rotate_fwd_(x: Tensor, src: Tensor, tgt: Tensor, wig: Tensor, radial: Optional[Tensor], m0: Tensor,
-                       m1: Tensor, m2: Tensor) -> None:
-    _chk(x, src, tgt, wig, radial, m0, m1, m2)
-    _f32(x, wig, radial, m0, m1, m2)
+@_op("gather_rotate_fwd", ("out",))
+def gather_rotate_fwd_(x: Tensor, src: Tensor, tgt: Tensor, wig: Tensor, radial: Optional[Tensor], out: Tensor) -> None:
+    _chk(x, src, tgt, wig, radial, out)
+    _f32(x, wig, radial, out)
     e, c = src.shape[0], x.shape[2]
     _launch("gather_rotate_fwd", "fcb200_gather_rotate_fwd",
-            (_p(x), _p(src), _p(tgt), _p(wig), _p(radial), _p(m0), _p(m1), _p(m2), e, x.shape[0], c, _stream()),
+            (_p(x), _p(src), _p(tgt), _p(wig), _p(radial), _p(out), e, x.shape[0], c, _stream()),
             nbytes=e * (4 * (18 * c + 18 * c + WIG + (12 * c if radial is not None else 0)) + 8), flops=e * 2 * WIG * 2 * c)
 
 
 @_op("gather_rotate_bwd", ("g_src", "g_tgt", "grad_wig", "grad_radial"))
-def gather_rotate_bwd_(gm0: Tensor, gm1: Tensor, gm2: Tensor, x: Tensor, src: Tensor, tgt: Tensor, wig: Tensor,
-                       radial: Optional[Tensor], g_src: Tensor, g_tgt: Tensor, grad_wig: Tensor,
-                       grad_radial: Optional[Tensor]) -> None:
-    _chk(gm0, gm1, gm2, x, src, tgt, wig, radial, g_src, g_tgt, grad_wig, grad_radial)
-    _f32(gm0, gm1, gm2, x, wig, radial, g_src, g_tgt, grad_wig, grad_radial)
+def gather_rotate_bwd_(grad_out: Tensor, x: Tensor, src: Tensor, tgt: Tensor, wig: Tensor, radial: Optional[Tensor],
+                       g_src: Tensor, g_tgt: Tensor, grad_wig: Tensor, grad_radial: Optional[Tensor]) -> None:
+    _chk(grad_out, x, src, tgt, wig, radial, g_src, g_tgt, grad_wig, grad_radial)
+    _f32(grad_out, x, wig, radial, g_src, g_tgt, grad_wig, grad_radial)
     e, c = src.shape[0], x.shape[2]
     _launch("gather_rotate_bwd", "fcb200_gather_rotate_bwd",
-            (_p(gm0), _p(gm1), _p(gm2), _p(x), _p(src), _p(tgt), _p(wig), _p(radial), _p(g_src), _p(g_tgt), _p(grad_wig),
-             _p(grad_radial), e, x.shape[0], c, _stream()),
+            (_p(grad_out), _p(x), _p(src), _p(tgt), _p(wig), _p(radial), _p(g_src), _p(g_tgt), _p(grad_wig), _p(grad_radial), e,
+             x.shape[0], c, _stream()),
             nbytes=e * (4 * (18 * c * 3 + 2 * WIG + (24 * c if radial is not None else 0)) + 8), flops=e * 6 * WIG * 2 * c)
 
 
@@ -193,40 +191,20 @@ def segment_sum_(rows: Tensor, ptr: Tensor, perm: Optional[Tensor], out_index: O
             nbytes=4 * (rows.shape[0] * width + num_segments * width * (2 if accumulate else 1)))
 
 
-@_op("so2_gate_fwd", ("a0", "a1", "a2"))
-def so2_gate_fwd_(y0: Tensor, y1: Tensor, y2: Tensor, a0: Tensor, a1: Tensor, a2: Tensor, hidden: int) -> None:
-    _chk(y0, y1, y2, a0, a1, a2)
-    _f32(y0, y1, y2, a0, a1, a2)
-    _launch("so2_gate_fwd", "fcb200_so2_gate_fwd",
-            (_p(y0), _p(y1), _p(y2), _p(a0), _p(a1), _p(a2), y0.shape[0], hidden, _stream()),
-            nbytes=y0.shape[0] * 4 * hidden * (5 + 8 + 4 + 9))
+@_op("so2_gate_fwd", ("out",))
+def so2_gate_fwd_(y: Tensor, out: Tensor, hidden: int) -> None:
+    _chk(y, out)
+    _f32(y, out)
+    _launch("so2_gate_fwd", "fcb200_so2_gate_fwd", (_p(y), _p(out), y.shape[0], hidden, _stream()),
+            nbytes=y.shape[0] * 4 * hidden * (11 + 9))
 
 
-@_op("so2_gate_bwd", ("g0", "g1", "g2"))
-def so2_gate_bwd_(ga0: Tensor, ga1: Tensor, ga2: Tensor, y0: Tensor, y1: Tensor, y2: Tensor, g0: Tensor, g1: Tensor,
-                  g2: Tensor, hidden: int) -> None:
-    _chk(ga0, ga1, ga2, y0, y1, y2, g0, g1, g2)
-    _f32(ga0, ga1, ga2, y0, y1, y2, g0, g1, g2)
-    _launch("so2_gate_bwd", "fcb200_so2_gate_bwd",
-            (_p(ga0), _p(ga1), _p(ga2), _p(y0), _p(y1), _p(y2), _p(g0), _p(g1), _p(g2), y0.shape[0], hidden, _stream()),
-            nbytes=y0.shape[0] * 4 * hidden * (9 + 17 + 17))
-
-
-@_op("so2_combine_fwd", ("out",))
-def so2_combine_fwd_(z0: Tensor, z1: Tensor, z2: Tensor, out: Tensor, channels: int) -> None:
-    _chk(z0, z1, z2, out)
-    _f32(z0, z1, z2, out)
-    _launch("so2_combine_fwd", "fcb200_so2_combine_fwd",
-            (_p(z0), _p(z1), _p(z2), _p(out), z0.shape[0], channels, _stream()), nbytes=z0.shape[0] * 4 * channels * (15 + 9))
-
-
-@_op("so2_combine_bwd", ("g0", "g1", "g2"))
-def so2_combine_bwd_(grad_out: Tensor, g0: Tensor, g1: Tensor, g2: Tensor, channels: int) -> None:
-    _chk(grad_out, g0, g1, g2)
-    _f32(grad_out, g0, g1, g2)
-    _launch("so2_combine_bwd", "fcb200_so2_combine_bwd",
-            (_p(grad_out), _p(g0), _p(g1), _p(g2), grad_out.shape[0], channels, _stream()),
-            nbytes=grad_out.shape[0] * 4 * channels * (15 + 9))
+@_op("so2_gate_bwd", ("grad_y",))
+def so2_gate_bwd_(grad_out: Tensor, y: Tensor, grad_y: Tensor, hidden: int) -> None:
+    _chk(grad_out, y, grad_y)
+    _f32(grad_out, y, grad_y)
+    _launch("so2_gate_bwd", "fcb200_so2_gate_bwd", (_p(grad_out), _p(y), _p(grad_y), y.shape[0], hidden, _stream()),
+            nbytes=y.shape[0] * 4 * hidden * (9 + 11 + 11))
 
 
 @_op("edge_geometry_fwd", ("vec", "dist", "env", "wig", "gauss"))
@@ -370,23 +348,21 @@ def segment_sum(rows: Tensor, ptr: Tensor, perm: Optional[Tensor], num_segments:
 
 
 class GatherRotate(torch.autograd.Function):
-    """x [N,9,C], wig [E,35], radial [E,12C] or None -> (m0 [E,6C], m1 [E,2,4C], m2 [E,2,2C])."""
+    """x [N,9,C], wig [E,35], radial [E,12C] or None -> M-major edge rows [E,9,2C]."""
 
     @staticmethod
     def forward(ctx, x, wig, radial, graph: EdgeGraph):
         e, c = graph.num_edges, x.shape[2]
         x, wig = x.contiguous(), wig.contiguous()
         radial = None if radial is None else radial.contiguous()
-        m0 = torch.empty(e, 6 * c, dtype=x.dtype, device=x.device)
-        m1 = torch.empty(e, 2, 4 * c, dtype=x.dtype, device=x.device)
-        m2 = torch.empty(e, 2, 2 * c, dtype=x.dtype, device=x.device)
-        gather_rotate_fwd_.raw(x, graph.src, graph.tgt, wig, radial, m0, m1, m2)
+        out = torch.empty(e, 9, 2 * c, dtype=x.dtype, device=x.device)
+        gather_rotate_fwd_.raw(x, graph.src, graph.tgt, wig, radial, out)
         ctx.save_for_backward(x, wig, radial)
         ctx.graph = graph
-        return m0, m1, m2
+        return out
 
     @staticmethod
-    def backward(ctx, gm0, gm1, gm2):
+    def backward(ctx, grad_out):
         x, wig, radial = ctx.saved_tensors
         g = ctx.graph
         e, c = g.num_edges, x.shape[2]
@@ -394,8 +370,7 @@ class GatherRotate(torch.autograd.Function):
         g_tgt = torch.empty(e, 9, c, dtype=x.dtype, device=x.device)
         grad_wig = torch.empty(e, WIG, dtype=x.dtype, device=x.device)
         grad_radial = None if radial is None else torch.empty_like(radial)
-        gather_rotate_bwd_.raw(gm0.contiguous(), gm1.contiguous(), gm2.contiguous(), x, g.src, g.tgt, wig, radial, g_src,
-                           g_tgt, grad_wig, grad_radial)
+        gather_rotate_bwd_.raw(grad_out.contiguous(), x, g.src, g.tgt, wig, radial, g_src, g_tgt, grad_wig, grad_radial)
         grad_x = torch.empty_like(x)
         segment_sum(g_src, g.src_ptr, g.src_perm, g.num_nodes, out=grad_x)
         if g.num_targets == g.num_nodes:
@@ -451,49 +426,23 @@ class EdgeDegree(torch.autograd.Function):
 
 
 class SO2Gate(torch.autograd.Function):
-    """Complex combine + gate: y0 [E,5H], y1 [E,2,4H], y2 [E,2,2H] -> a0 [E,3H], a1 [E,2,2H], a2 [E,2,H]."""
+    """Gate activation: y [E,11H] = [gate scalars 2H | 9 M-major rows] -> [E,9,H]."""
 
     @staticmethod
-    def forward(ctx, y0, y1, y2):
-        y0, y1, y2 = y0.contiguous(), y1.contiguous(), y2.contiguous()
-        e = y0.shape[0]
-        h = y0.shape[1] // 5
-        a0 = torch.empty(e, 3 * h, dtype=y0.dtype, device=y0.device)
-        a1 = torch.empty(e, 2, 2 * h, dtype=y0.dtype, device=y0.device)
-        a2 = torch.empty(e, 2, h, dtype=y0.dtype, device=y0.device)
-        so2_gate_fwd_.raw(y0, y1, y2, a0, a1, a2, h)
-        ctx.save_for_backward(y0, y1, y2)
-        return a0, a1, a2
-
-    @staticmethod
-    def backward(ctx, ga0, ga1, ga2):
-        y0, y1, y2 = ctx.saved_tensors
-        g0, g1, g2 = torch.empty_like(y0), torch.empty_like(y1), torch.empty_like(y2)
-        so2_gate_bwd_.raw(ga0.contiguous(), ga1.contiguous(), ga2.contiguous(), y0, y1, y2, g0, g1, g2, y0.shape[1] // 5)
-        return g0, g1, g2
-
-
-class SO2Combine(torch.autograd.Function):
-    """Complex combine: z0 [E,3C], z1 [E,2,4C], z2 [E,2,2C] -> msg [E,9,C] (M-major)."""
-
-    @staticmethod
-    def forward(ctx, z0, z1, z2):
-        z0, z1, z2 = z0.contiguous(), z1.contiguous(), z2.contiguous()
-        c = z0.shape[1] // 3
-        out = torch.empty(z0.shape[0], 9, c, dtype=z0.dtype, device=z0.device)
-        so2_combine_fwd_.raw(z0, z1, z2, out, c)
-        ctx.c = c
+    def forward(ctx, y):
+        y = y.contiguous()
+        h = y.shape[1] // 11
+        out = torch.empty(y.shape[0], 9, h, dtype=y.dtype, device=y.device)
+        so2_gate_fwd_.raw(y, out, h)
+        ctx.save_for_backward(y)
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
-        c = ctx.c
-        e = grad_out.shape[0]
-        g0 = torch.empty(e, 3 * c, dtype=grad_out.dtype, device=grad_out.device)
-        g1 = torch.empty(e, 2, 4 * c, dtype=grad_out.dtype, device=grad_out.device)
-        g2 = torch.empty(e, 2, 2 * c, dtype=grad_out.dtype, device=grad_out.device)
-        so2_combine_bwd_.raw(grad_out.contiguous(), g0, g1, g2, c)
-        return g0, g1, g2
+        (y,) = ctx.saved_tensors
+        grad_y = torch.empty_like(y)
+        so2_gate_bwd_.raw(grad_out.contiguous(), y, grad_y, y.shape[1] // 11)
+        return grad_y
 
 
 class EdgeGeometry(torch.autograd.Function):

@@ -50,13 +50,13 @@ int fcb200_version(void);
  *   src,tgt  [E] int32         node index of the edge's source / target
  *   wig      [E, 35]           compact Wigner-D (edge frame <- global frame)
  *   radial   [E, 6*2C] or NULL per-edge radial weights: [3*2C | 2*2C | 2C] for m = 0,1,2
- *   out_m0   [E, 3*2C]         M-major rows 0-2, the m=0 GEMM operand
- *   out_m1   [E, 2, 2*2C]      rows 3-4 (real pair) and 5-6 (imaginary pair), the m=1 operand
- *   out_m2   [E, 2, 2C]        rows 7 and 8, the m=2 operand
+ *   out      [E, 9, 2C]        M-major rows; the SO(2) GEMMs read their operands as column ranges of the
+ *                              flattened [E, 9*2C] matrix: rows 0-2 (m=0), rows 3-6 (m=1: real pair |
+ *                              imaginary pair, the operand of the block-form GEMM), rows 7-8 (m=2)
  */
 int fcb200_gather_rotate_fwd(const float* x, const int32_t* src, const int32_t* tgt, const float* wig,
-                             const float* radial, float* out_m0, float* out_m1, float* out_m2, int64_t num_edges,
-                             int64_t num_nodes, int32_t channels, void* stream);
+                             const float* radial, float* out, int64_t num_edges, int64_t num_nodes, int32_t channels,
+                             void* stream);
 
 /*
  * Rotate edge messages back to the global frame and sum them into their target nodes with a
@@ -91,16 +91,16 @@ int fcb200_edge_degree_fwd(const float* radial3, const float* winv, const int32_
  * radial.  Replaces wigner_conv1_fused_bwd_kernel (triton/kernels.py:1697) /
  * node_to_edge_wigner_permute_bwd_dx_kernel (triton/kernels.py:573) plus the torch.bmm for dW
  * (src/fairchem/core/models/uma/triton/node_to_edge_wigner_permute.py:148-167).
- *   grad_m0/1/2  gradients of the three forward outputs (same shapes)
+ *   grad_out   [E, 9, 2C]
  *   g_src      [E, 9, C]   out: W^T grad (source half), L-major, to be summed by source node
  *   g_tgt      [E, 9, C]   out: W^T grad (target half), L-major, to be summed by target node
  *   grad_wig   [E, 35]     out
  *   grad_radial[E, 6*2C]   out, or NULL when radial == NULL
  */
-int fcb200_gather_rotate_bwd(const float* grad_m0, const float* grad_m1, const float* grad_m2, const float* x,
-                             const int32_t* src, const int32_t* tgt, const float* wig, const float* radial,
-                             float* g_src, float* g_tgt, float* grad_wig, float* grad_radial, int64_t num_edges,
-                             int64_t num_nodes, int32_t channels, void* stream);
+int fcb200_gather_rotate_bwd(const float* grad_out, const float* x, const int32_t* src, const int32_t* tgt,
+                             const float* wig, const float* radial, float* g_src, float* g_tgt, float* grad_wig,
+                             float* grad_radial, int64_t num_edges, int64_t num_nodes, int32_t channels,
+                             void* stream);
 
 /*
  * Backward of fcb200_rotate_back_reduce_fwd: grad_msg = Winv^T grad_out[tgt] (M-major) and
@@ -131,29 +131,18 @@ int fcb200_segment_sum(const float* rows, const int32_t* ptr, const int32_t* per
 /* ---------------------------------------------------------------- SO(2) activation glue */
 
 /*
- * Complex combine of the m>0 GEMM outputs, gate activation and packing for the second SO(2)
- * convolution, in one pass.  Replaces SO2_m_Conv.forward's combine
- * (src/fairchem/core/models/uma/nn/so2_layers.py:72-80), torch.cat in SO2_Convolution.forward
- * (so2_layers.py:642) and GateActivation.forward (src/fairchem/core/models/uma/nn/activation.py:146-165).
- *   y0 [E, 2H + 3H]  fc_m0 output: [gate scalars 2H | m0 rows 3H]
- *   y1 [E, 2, 4H]    m=1 GEMM output rows (real-in, imag-in), columns [r(2H) | i(2H)]
- *   y2 [E, 2, 2H]    m=2 GEMM output
- *   out_m0 [E,3H], out_m1 [E,2,2H], out_m2 [E,2,H]: gated M-major rows as the operands of the second convolution
+ * Gate activation between the two SO(2) convolutions, one pass.
+ * The m>0 convolutions run in block form ([x_re | x_im] @ [[Wa, -Wb], [Wb, Wa]]^T, the reference's
+ * SO2_m_Conv_Block, src/fairchem/core/models/uma/nn/so2_layers.py:83-169), so the three conv-1 GEMMs
+ * write one matrix y [E, 11H] = [gate scalars 2H | m=0 rows 3H | m=1 rows 4H | m=2 rows 2H] side by side
+ * and no separate complex-combine or concatenation pass exists (so2_layers.py:72-80, 642).
+ * Replaces GateActivation.forward (src/fairchem/core/models/uma/nn/activation.py:146-165):
+ *   out [E, 9, H]: row 0 = SiLU(row 0), rows 1..8 = row * sigmoid(gate of the row's degree).
  */
-int fcb200_so2_gate_fwd(const float* y0, const float* y1, const float* y2, float* out_m0, float* out_m1,
-                        float* out_m2, int64_t num_edges, int32_t hidden, void* stream);
-/* Backward of fcb200_so2_gate_fwd: grads of y0, y1, y2 from the output grads (forward inputs are re-read). */
-int fcb200_so2_gate_bwd(const float* grad_m0, const float* grad_m1, const float* grad_m2, const float* y0,
-                        const float* y1, const float* y2, float* g0, float* g1, float* g2, int64_t num_edges,
-                        int32_t hidden, void* stream);
-/*
- * Complex combine after the second SO(2) convolution: z0 [E,3C], z1 [E,2,4C], z2 [E,2,2C] -> out [E,9,C]
- * (so2_layers.py:72-80, 642), and its backward.
- */
-int fcb200_so2_combine_fwd(const float* z0, const float* z1, const float* z2, float* out, int64_t num_edges,
-                           int32_t channels, void* stream);
-int fcb200_so2_combine_bwd(const float* grad_out, float* g0, float* g1, float* g2, int64_t num_edges,
-                           int32_t channels, void* stream);
+int fcb200_so2_gate_fwd(const float* y, float* out, int64_t num_edges, int32_t hidden, void* stream);
+/* Backward of fcb200_so2_gate_fwd: grad_y [E, 11H] from grad_out [E, 9, H] (y is re-read). */
+int fcb200_so2_gate_bwd(const float* grad_out, const float* y, float* grad_y, int64_t num_edges, int32_t hidden,
+                        void* stream);
 
 /* ---------------------------------------------------------------- radial MLP hidden activation */
 

@@ -56,9 +56,8 @@ def ref_gather_rotate(x, src, tgt, wig, radial):
         m0 = msg[:, :3].reshape(e, -1) * r0
         m1 = msg[:, 3:7].reshape(e, 2, -1) * r1.unsqueeze(1)
         m2 = msg[:, 7:9].reshape(e, 2, -1) * r2.unsqueeze(1)
-    else:
-        m0, m1, m2 = msg[:, :3].reshape(e, -1), msg[:, 3:7].reshape(e, 2, -1), msg[:, 7:9].reshape(e, 2, -1)
-    return m0, m1, m2
+        msg = torch.cat([m0.view(e, 3, c2), m1.view(e, 4, c2), m2.view(e, 2, c2)], dim=1)
+    return msg
 
 
 @pytest.mark.parametrize("n,e,c", [(16, 32, 128), (7, 1, 128), (40, 333, 256), (5, 64, 128)])
@@ -73,13 +72,12 @@ def test_gather_rotate_forward_backward(ops, n, e, c, with_radial):
     xb, wb = x.double().requires_grad_(True), wig.double().requires_grad_(True)
     rb = radial.double().requires_grad_(True) if with_radial else None
     ref = ref_gather_rotate(xb, src, tgt, wb, rb)
-    cot = [torch.randn(o.shape, generator=g).cuda() for o in out]
-    for o, r in zip(out, ref):
-        torch.testing.assert_close(o, r.float(), **FWD_TOL)
+    cot = torch.randn(out.shape, generator=g).cuda()
+    torch.testing.assert_close(out, ref.float(), **FWD_TOL)
     ins_a = [xa, wa] + ([ra] if with_radial else [])
     ins_b = [xb, wb] + ([rb] if with_radial else [])
     ga = torch.autograd.grad(out, ins_a, cot)
-    gb = torch.autograd.grad(ref, ins_b, [t.double() for t in cot])
+    gb = torch.autograd.grad(ref, ins_b, cot.double())
     for a, b in zip(ga, gb):
         scale = max(1.0, b.abs().max().item())
         torch.testing.assert_close(a, b.float(), rtol=1e-4, atol=2e-4 * scale)
@@ -137,9 +135,8 @@ def test_backend_ops_match_reference_golden(ops, golden):
     wig = compact_from_dense(torch.tensor(g["wigner"])).cuda()
     env = torch.tensor(g["env"]).cuda()
     graph = ops.EdgeGraph(ei[0], ei[1], x.shape[0])
-    m0, m1, m2 = ops.GatherRotate.apply(x, wig, None, graph)
+    msg = ops.GatherRotate.apply(x, wig, None, graph)
     e = ei.shape[1]
-    msg = torch.cat([m0.view(e, 3, -1), m1.view(e, 4, -1), m2.view(e, 2, -1)], dim=1)
     torch.testing.assert_close(msg.cpu(), torch.tensor(g["msg"]), **FWD_TOL)
     winv = compact_from_dense(dense_from_compact(wig).transpose(1, 2)) * env[:, None]
     back = ops.RotateBackReduce.apply(torch.tensor(g["y"]).cuda(), winv, graph)
@@ -170,7 +167,7 @@ def test_segment_sum(ops, width, nseg):
 
 
 def test_so2_middle_matches_oracle_convolutions(ops):
-    """GEMMs + combine + gate + GEMMs + combine == oracle SO2 conv -> gate -> SO2 conv (so2_layers.py:600-647)."""
+    """Block-form GEMMs + gate + block-form GEMMs == oracle SO2 conv -> gate -> SO2 conv (so2_layers.py:600-647)."""
     from fairchem_b200 import backbone as B
 
     torch.manual_seed(0)
@@ -178,9 +175,8 @@ def test_so2_middle_matches_oracle_convolutions(ops):
     ew = B.Edgewise(c, h, 2, 2, [320, 128, 128]).cuda()
     g = torch.Generator().manual_seed(5)
     msg = torch.randn(e, 9, 2 * c, generator=g).cuda()
-    m = [msg[:, :3].reshape(e, -1).clone().requires_grad_(True), msg[:, 3:7].reshape(e, 2, -1).clone().requires_grad_(True),
-         msg[:, 7:9].reshape(e, 2, -1).clone().requires_grad_(True)]
-    out = B._so2_middle(ew, *m)
+    m = msg.clone().requires_grad_(True)
+    out = B._so2_middle(ew, m)
     sd = {k: v.detach().double().cpu() for k, v in ew.state_dict().items()}
     md = msg.double().cpu().requires_grad_(True)
     y, gating = O.so2_convolution(sd, "so2_conv_1.", md, None, [3, 2, 1], h, 2 * h)
@@ -188,10 +184,25 @@ def test_so2_middle_matches_oracle_convolutions(ops):
     ref, _ = O.so2_convolution(sd, "so2_conv_2.", y, None, [3, 2, 1], c, 0)
     torch.testing.assert_close(out.cpu(), ref.float(), rtol=1e-4, atol=1e-4)
     cot = torch.randn(e, 9, c, generator=g)
-    ga = torch.autograd.grad(out, m, cot.cuda())
+    (ga,) = torch.autograd.grad(out, m, cot.cuda())
     (gb,) = torch.autograd.grad(ref, md, cot.double())
-    got = torch.cat([ga[0].view(e, 3, -1), ga[1].view(e, 4, -1), ga[2].view(e, 2, -1)], dim=1).cpu()
-    torch.testing.assert_close(got, gb.float(), rtol=1e-4, atol=1e-4 * max(1.0, gb.abs().max().item()))
+    torch.testing.assert_close(ga.cpu(), gb.float(), rtol=1e-4, atol=1e-4 * max(1.0, gb.abs().max().item()))
+
+
+def test_gate_activation_forward_backward(ops):
+    """Gate kernel against activation.py:146-165 on y = [gate scalars | M-major rows]."""
+    g = torch.Generator().manual_seed(9)
+    e, h = 130, 128
+    y = torch.randn(e, 11 * h, generator=g).cuda()
+    a = y.clone().requires_grad_(True)
+    out = ops.SO2Gate.apply(a)
+    b = y.double().requires_grad_(True)
+    ref = O.gate_activation(b[:, :2 * h], b[:, 2 * h:].reshape(e, 9, h), [0, 1, 0, 1, 0, 1, 1, 1], 2)
+    torch.testing.assert_close(out, ref.float(), rtol=1e-5, atol=1e-5)
+    cot = torch.randn(e, 9, h, generator=g).cuda()
+    (ga,) = torch.autograd.grad(out, a, cot)
+    (gb,) = torch.autograd.grad(ref, b, cot.double())
+    torch.testing.assert_close(ga, gb.float(), rtol=1e-4, atol=1e-5)
 
 
 def _geometry_inputs(golden):
