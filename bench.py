@@ -197,6 +197,10 @@ def run_b200(args):
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         ms = float(t.item())
     edges = int(bb.last_graph["edge_index"].shape[1]) if bb.last_graph else 0
+    if world > 1:  # every rank holds the edges of its own targets only
+        t = torch.tensor([edges], device=dev, dtype=torch.int64)
+        torch.distributed.all_reduce(t)
+        edges = int(t.item())
 
     # end to end through the module interface with host buffers
     pin_pos = data["pos"].detach().cpu().pin_memory()
@@ -229,6 +233,9 @@ def run_b200(args):
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
         e2e_ms = float(t.item())
 
+    if world > 1:
+        torch.distributed.barrier()
+        torch.distributed.destroy_process_group()
     if rank != 0:
         return
     peaks = load_peaks()

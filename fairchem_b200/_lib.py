@@ -29,6 +29,8 @@ SIGNATURES = {
     "fcb200_so2_gate_bwd": [P, P, P, I64, I32, P],
     "fcb200_radial_act_fwd": [P, P, P, P, P, P, P, F32, P, P, I64, I32, P],
     "fcb200_radial_act_bwd": [P, P, P, P, P, P, P, P, P, P, I64, I32, P],
+    "fcb200_rms_norm_sh_fwd": [P, P, P, P, P, P, F32, I64, I32, P],
+    "fcb200_rms_norm_sh_bwd": [P, P, P, P, P, I64, I32, P],
     "fcb200_edge_geometry_fwd": [P, P, P, P, P, P, P, P, P, P, F32, I32, F32, F32, F32, I64, I64, P],
     "fcb200_edge_geometry_bwd": [P, P, P, P, P, P, P, P, P, P, F32, I32, F32, F32, F32, I64, I64, P],
     "fcb200_rg_count_sources": [P, P, I32, I64, P, P, P],

@@ -122,6 +122,8 @@ class SO3Linear(nn.Module):
         self.lmax = lmax
 
     def forward(self, x):  # x [N,(lmax+1)^2,Cin]
+        if x.is_cuda and _GemmState.precision != 0:
+            return _SO3LinearFn.apply(x, self.weight.detach(), self.bias.detach())
         outs = []
         for l in range(self.lmax + 1):
             y = torch.matmul(x[:, l * l:(l + 1) * (l + 1)], self.weight[l].t())
@@ -129,6 +131,32 @@ class SO3Linear(nn.Module):
                 y = y + self.bias
             outs.append(y)
         return torch.cat(outs, dim=1)
+
+
+class _SO3LinearFn(torch.autograd.Function):
+    """Per-degree linear map on the tcgen05 GEMM: row i of every node is one [N, Cin] x [Cin, Cout] product
+    on a strided view (row stride 9*Cin), with the weight of the row's degree; bias on row 0."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias):
+        x = x.contiguous()
+        n, rows, cin = x.shape
+        cout = weight.shape[1]
+        out = torch.empty(n, rows, cout, dtype=x.dtype, device=x.device)
+        p = _GemmState.precision
+        for i in range(rows):
+            _gemm(x[:, i, :], weight[_L_OF[i]], bias if i == 0 else None, out[:, i, :], p)
+        ctx.weight, ctx.p, ctx.cin = weight, p, cin
+        return out
+
+    @staticmethod
+    def backward(ctx, gy):
+        gy = gy.contiguous()
+        n, rows, _ = gy.shape
+        gx = torch.empty(n, rows, ctx.cin, dtype=gy.dtype, device=gy.device)
+        for i in range(rows):
+            _gemm(gy[:, i, :], _transposed(ctx.weight[_L_OF[i]]), None, gx[:, i, :], ctx.p)
+        return gx, None, None
 
 
 class SpectralAtomwise(nn.Module):
@@ -142,7 +170,8 @@ class SpectralAtomwise(nn.Module):
         self.lmax, self.h = lmax, h
 
     def forward(self, x):
-        gates = torch.sigmoid(self.scalar_mlp(x[:, 0])).view(x.shape[0], self.lmax, self.h)
+        lin = self.scalar_mlp[0]
+        gates = torch.sigmoid(F.silu(_linear(x[:, 0], lin.weight, lin.bias))).view(x.shape[0], self.lmax, self.h)
         y = self.so3_linear_1(x)
         parts = [F.silu(y[:, :1])]
         for l in range(1, self.lmax + 1):
@@ -163,7 +192,13 @@ class RMSNormSH(nn.Module):
         self.register_buffer("balance", torch.tensor([1.0 / ((2 * l + 1) * (lmax + 1)) for l in l_of]).view(1, -1, 1),
                              persistent=False)
 
-    def forward(self, x):
+    def forward(self, x, extra=None):
+        if x.is_cuda and self.lmax == 2:
+            return ops.RMSNormSH.apply(x, self.affine_weight.detach(), self.affine_bias.detach(), extra, self.eps)
+        out = self._forward_torch(x)
+        return out if extra is None else torch.cat([out[:, :1] + extra.unsqueeze(1), out[:, 1:]], dim=1)
+
+    def _forward_torch(self, x):
         x0 = x[:, :1] - x[:, :1].mean(dim=2, keepdim=True)
         feat = torch.cat([x0, x[:, 1:]], dim=1)
         nrm = (feat.square() * self.balance).sum(dim=1, keepdim=True).mean(dim=2, keepdim=True)
@@ -260,6 +295,20 @@ def build_chunks(graph: EdgeGraph, chunk_edges: int) -> list[_Chunk]:
 # ------------------------------------------------------------------------------------------
 # the edge block
 # ------------------------------------------------------------------------------------------
+
+
+class _PermuteColumns(torch.autograd.Function):
+    """x[:, perm] for an involutive column permutation (block transpose of the compact Wigner): the
+    backward is the same gather, instead of an index_put with accumulation."""
+
+    @staticmethod
+    def forward(ctx, x, perm):
+        ctx.perm = perm
+        return x.index_select(1, perm)
+
+    @staticmethod
+    def backward(ctx, g):
+        return g.index_select(1, ctx.perm), None
 
 
 class _EdgeCtx:
@@ -675,7 +724,7 @@ class eSCNMDBackboneB200(nn.Module):
         chunks = build_chunks(graph, self.edge_chunk_size)
 
         vec, dist, env, wig, gauss = ops.EdgeGeometry.apply(pos_e, shift, gamma, graph, self.cutoff, nb, 0.0, self.cutoff, 2.0)
-        winv = wig[:, self._wig_transpose] * env.unsqueeze(1)
+        winv = _PermuteColumns.apply(wig, self._wig_transpose) * env.unsqueeze(1)
         ectx = _EdgeCtx(graph, chunks, wig, winv, gauss, z_e[edge_index[0]], z_e[edge_index[1]])
 
         x = torch.zeros(n_local, self.sph_feature_size, c, dtype=pos.dtype, device=pos.device)
@@ -685,8 +734,7 @@ class eSCNMDBackboneB200(nn.Module):
 
         for blk in self.blocks:
             x_res = x
-            xn = blk.norm_1(x)
-            xn = torch.cat([xn[:, :1] + sys_node.unsqueeze(1), xn[:, 1:]], dim=1)
+            xn = blk.norm_1(x, sys_node)
             x_full = halo_collect(xn, plan)  # per-layer halo exchange (escn_md_block.py:141-146)
             rad = blk.edge_wise.so2_conv_1.rad_func
             x = _EdgeBlockFn.apply(x_full, wig, winv, gauss, blk.edge_wise, self._tables(rad), ectx, nb) + x_res
@@ -708,7 +756,11 @@ class MLP_EFS_HeadB200(nn.Module):
 
     def forward(self, data, emb):
         with torch.enable_grad():
-            e_node = self.energy_block(emb["node_embedding"][:, 0]).view(-1)
+            eb = self.energy_block
+            h = emb["node_embedding"][:, 0]
+            h = F.silu(_linear(h, eb[0].weight, eb[0].bias))
+            h = F.silu(_linear(h, eb[2].weight, eb[2].bias))
+            e_node = F.linear(h, eb[4].weight, eb[4].bias).view(-1)
             nsys = len(data["natoms"])
             energy = torch.zeros(nsys, dtype=torch.float64, device=e_node.device).index_add(0, emb["batch"], e_node.double())
             out = {"energy": energy.detach()}

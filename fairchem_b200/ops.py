@@ -258,6 +258,25 @@ def radial_act_bwd_(grad_out: Tensor, pre: Tensor, table_src: Optional[Tensor], 
              _p(grad_pre), e, w, _stream()), nbytes=e * (12 * w + 16))
 
 
+@_op("rms_norm_sh_fwd", ("out", "stats"))
+def rms_norm_sh_fwd_(x: Tensor, weight: Tensor, bias: Tensor, extra: Optional[Tensor], out: Tensor, stats: Tensor,
+                     eps: float) -> None:
+    _chk(x, weight, bias, extra, out, stats)
+    _f32(x, weight, bias, extra, out, stats)
+    n, _, c = x.shape
+    _launch("rms_norm_sh_fwd", "fcb200_rms_norm_sh_fwd",
+            (_p(x), _p(weight), _p(bias), _p(extra), _p(out), _p(stats), eps, n, c, _stream()), nbytes=n * 4 * (18 * c + 2))
+
+
+@_op("rms_norm_sh_bwd", ("grad_x",))
+def rms_norm_sh_bwd_(grad_out: Tensor, x: Tensor, weight: Tensor, stats: Tensor, grad_x: Tensor) -> None:
+    _chk(grad_out, x, weight, stats, grad_x)
+    _f32(grad_out, x, weight, stats, grad_x)
+    n, _, c = x.shape
+    _launch("rms_norm_sh_bwd", "fcb200_rms_norm_sh_bwd",
+            (_p(grad_out), _p(x), _p(weight), _p(stats), _p(grad_x), n, c, _stream()), nbytes=n * 4 * (27 * c + 2))
+
+
 @_op("gemm_tf32", ("c", "status"))
 def gemm_tf32_(a: Tensor, w: Tensor, w_lo: Optional[Tensor], bias: Optional[Tensor], c: Tensor, precision: int,
                status: Tensor) -> None:
@@ -506,3 +525,25 @@ class RadialAct(torch.autograd.Function):
         grad_pre = torch.empty_like(pre)
         radial_act_bwd_.raw(grad_out.contiguous(), pre, table_src, table_tgt, z_src, z_tgt, ln_weight, ln_bias, stats, grad_pre)
         return grad_pre, None, None, None, None, None, None, None
+
+
+class RMSNormSH(torch.autograd.Function):
+    """Degree-balanced RMS norm of [N,9,C] node features (+ optional per-node vector on row 0); differentiable in x."""
+
+    @staticmethod
+    def forward(ctx, x, weight, bias, extra, eps: float):
+        x = x.contiguous()
+        out = torch.empty_like(x)
+        stats = torch.empty(x.shape[0], 2, dtype=x.dtype, device=x.device)
+        extra = None if extra is None else extra.contiguous()
+        rms_norm_sh_fwd_.raw(x, weight, bias, extra, out, stats, float(eps))
+        ctx.save_for_backward(x, stats)
+        ctx.weight = weight
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        x, stats = ctx.saved_tensors
+        grad_x = torch.empty_like(x)
+        rms_norm_sh_bwd_.raw(grad_out.contiguous(), x, ctx.weight, stats, grad_x)
+        return grad_x, None, None, None, None

@@ -162,6 +162,22 @@ int fcb200_radial_act_bwd(const float* grad_out, const float* pre, const float* 
                           const int32_t* z_src, const int32_t* z_tgt, const float* ln_weight, const float* ln_bias,
                           const float* stats, float* grad_pre, int64_t num_edges, int32_t width, void* stream);
 
+/* ---------------------------------------------------------------- node-wise norm */
+
+/*
+ * Degree-balanced RMS norm of node features x [N, 9, C] (lmax = 2), one pass:
+ *   y_0 = x_0 - mean_c(x_0), y_i = x_i (i > 0);  s = rsqrt(mean_c sum_i y_i^2 / ((2 l_i + 1) * 3) + eps);
+ *   out_i = y_i * s * weight[l_i] ; out_0 += bias (+ extra[n], the per-system embedding added after the
+ *   first norm of a layer, src/fairchem/core/models/uma/escn_md_block.py:440-443).
+ * Replaces EquivariantRMSNormArraySphericalHarmonicsV2.forward
+ * (src/fairchem/core/models/uma/nn/layer_norm.py:372-419).  stats [N,2] = (mean_c x_0, s) for the backward.
+ */
+int fcb200_rms_norm_sh_fwd(const float* x, const float* weight, const float* bias, const float* extra, float* out,
+                           float* stats, float eps, int64_t num_nodes, int32_t channels, void* stream);
+/* Backward of fcb200_rms_norm_sh_fwd w.r.t. x (affine parameters are frozen; grad of extra is grad_out row 0). */
+int fcb200_rms_norm_sh_bwd(const float* grad_out, const float* x, const float* weight, const float* stats,
+                           float* grad_x, int64_t num_nodes, int32_t channels, void* stream);
+
 /* ---------------------------------------------------------------- edge geometry */
 
 /*

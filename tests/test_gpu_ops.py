@@ -276,3 +276,24 @@ def test_radial_activation_forward_backward(ops, with_tables):
     (ga,) = torch.autograd.grad(out, a, cot)
     (gb,) = torch.autograd.grad(ref, b, cot.double())
     torch.testing.assert_close(ga, gb.float(), rtol=1e-4, atol=1e-5 * max(1.0, gb.abs().max().item()))
+
+
+@pytest.mark.parametrize("with_extra", [True, False])
+def test_rms_norm_sh_forward_backward(ops, with_extra):
+    """Fused node norm against the oracle's restatement of layer_norm.py:372-419."""
+    g = torch.Generator().manual_seed(10)
+    n, c = 333, 128
+    x = torch.randn(n, 9, c, generator=g).cuda() * 2 + 0.3
+    w, b = torch.randn(3, c, generator=g).cuda(), torch.randn(c, generator=g).cuda()
+    extra = torch.randn(n, c, generator=g).cuda() if with_extra else None
+    a = x.clone().requires_grad_(True)
+    out = ops.RMSNormSH.apply(a, w, b, extra, 1e-5)
+    xd = x.double().cpu().requires_grad_(True)
+    ref = O.rms_norm_sh(xd, w.double().cpu(), b.double().cpu(), 2)
+    if with_extra:
+        ref = torch.cat([ref[:, :1] + extra.double().cpu().unsqueeze(1), ref[:, 1:]], dim=1)
+    torch.testing.assert_close(out.cpu(), ref.float(), rtol=1e-5, atol=1e-5)
+    cot = torch.randn(n, 9, c, generator=g)
+    (ga,) = torch.autograd.grad(out, a, cot.cuda())
+    (gb,) = torch.autograd.grad(ref, xd, cot.double())
+    torch.testing.assert_close(ga.cpu(), gb.float(), rtol=1e-4, atol=1e-5 * max(1.0, gb.abs().max().item()))
