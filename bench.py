@@ -289,7 +289,7 @@ def run_b200(args):
     }
     if args.profile_run:
         line["profile_run"] = True
-    print(json.dumps(line))
+    _emit(line)
 
 
 def cpu_baseline(args, quiet=False):
@@ -336,10 +336,32 @@ def run_reference(args):
         "cpu_baseline": cpu,
         "e2e": {"value": cpu["value"], "unit": "atom-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
-    print(json.dumps(line))
+    _emit(line)
+
+
+_JSON_FD = None
+
+
+def _claim_stdout():
+    """Keep the process's stdout for the one JSON line: libraries that print banners on fd 1 (NCCL's
+    version line) are pointed at stderr instead."""
+    global _JSON_FD
+    sys.stdout.flush()
+    _JSON_FD = os.dup(1)
+    os.dup2(2, 1)
+
+
+def _emit(line: dict):
+    data = (json.dumps(line) + "\n").encode()
+    if _JSON_FD is None:
+        sys.stdout.write(data.decode())
+        sys.stdout.flush()
+    else:
+        os.write(_JSON_FD, data)
 
 
 def main():
+    _claim_stdout()
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=5)
