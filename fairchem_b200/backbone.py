@@ -462,25 +462,50 @@ class _SO2Conv(torch.autograd.Function):
         return gx, None, None
 
 
-def _so2_middle(ew: Edgewise, m):
-    """conv 1 -> gate -> conv 2 on the M-major edge rows m [E,9,2C]; returns the messages [E,9,C]."""
+def _so2_conv1(ew: Edgewise, m):
+    """First SO(2) convolution on the M-major edge rows m [E,9,2C] -> y [E, 11H] (gate scalars | 9 rows)."""
     e, cin = m.shape[0], m.shape[2]
-    y = _SO2Conv.apply(m.view(e, 9 * cin), ew.so2_conv_1, cin)
+    return _SO2Conv.apply(m.view(e, 9 * cin), ew.so2_conv_1, cin)
+
+
+def _so2_tail(ew: Edgewise, y):
+    """gate -> second SO(2) convolution: y [E,11H] -> messages [E,9,C]."""
     a = ops.SO2Gate.apply(y)
-    h = a.shape[2]
+    e, h = a.shape[0], a.shape[2]
     z = _SO2Conv.apply(a.view(e, 9 * h), ew.so2_conv_2, h)
     return z.view(e, 9, -1)
+
+
+def _so2_middle(ew: Edgewise, m):
+    """conv 1 -> gate -> conv 2 on the M-major edge rows m [E,9,2C]; returns the messages [E,9,C]."""
+    return _so2_tail(ew, _so2_conv1(ew, m))
+
+
+def _so2_conv1_input_grad(ew: Edgewise, gy, cin: int):
+    """d(conv-1 input) from d(conv-1 output): three GEMMs with the transposed weights."""
+    conv = ew.so2_conv_1
+    w0 = conv.fc_m0.weight.detach()
+    w1, w2 = _block_weight(conv.so2_m_conv[0].fc.weight), _block_weight(conv.so2_m_conv[1].fc.weight)
+    n0, n1 = w0.shape[0], w1.shape[0]
+    p = _GemmState.precision
+    gy = gy.contiguous()
+    gx = torch.empty(gy.shape[0], 9 * cin, dtype=gy.dtype, device=gy.device)
+    _gemm(gy[:, :n0], _transposed(w0), None, gx[:, : 3 * cin], p)
+    _gemm(gy[:, n0: n0 + n1], _transposed(w1), None, gx[:, 3 * cin: 7 * cin], p)
+    _gemm(gy[:, n0 + n1:], _transposed(w2), None, gx[:, 7 * cin:], p)
+    return gx
 
 
 class _EdgeBlockFn(torch.autograd.Function):
     """One layer's edge block over all chunks; differentiable in x, wig, winv and gauss."""
 
     @staticmethod
-    def forward(ctx, x, wig, winv, gauss, ew: Edgewise, tables, ectx: _EdgeCtx, nb: int):
+    def forward(ctx, x, wig, winv, gauss, ew: Edgewise, tables, ectx: _EdgeCtx, nb: int, keep_conv1: bool):
         g = ectx.graph
         c = x.shape[2]
         x = x.contiguous()
         out = torch.zeros(g.num_targets, 9, c, dtype=x.dtype, device=x.device)
+        kept = []
         with torch.no_grad():
             for ch in ectx.chunks:
                 sl = slice(ch.e0, ch.e1)
@@ -488,10 +513,14 @@ class _EdgeBlockFn(torch.autograd.Function):
                 ec = ch.e1 - ch.e0
                 m = torch.empty(ec, 9, 2 * c, dtype=x.dtype, device=x.device)
                 ops.gather_rotate_fwd_.raw(x, g.src[sl], g.tgt[sl], wig[sl], rad, m)
-                msg = _so2_middle(ew, m)
+                y = _so2_conv1(ew, m)
+                del m, rad
+                msg = _so2_tail(ew, y)
                 ops.rotate_back_reduce_fwd_.raw(msg, winv[sl], ch.row_ptr, out[ch.n0:ch.n1])
+                if keep_conv1:
+                    kept.append(y)  # the backward then skips the gather+rotate and the conv-1 GEMMs
         ctx.save_for_backward(x, wig, winv, gauss)
-        ctx.ew, ctx.tables, ctx.ectx, ctx.nb = ew, tables, ectx, nb
+        ctx.ew, ctx.tables, ctx.ectx, ctx.nb, ctx.kept = ew, tables, ectx, nb, kept
         return out
 
     @staticmethod
@@ -505,20 +534,34 @@ class _EdgeBlockFn(torch.autograd.Function):
         gwig = torch.empty_like(wig)
         gwinv = torch.empty_like(winv)
         ggauss = torch.empty_like(gauss)
-        for ch in ectx.chunks:
+        kept = ctx.kept
+        ctx.kept = None
+        for ci, ch in enumerate(ectx.chunks):
             sl = slice(ch.e0, ch.e1)
             ec = ch.e1 - ch.e0
             with torch.enable_grad():
                 g_c = gauss[sl].detach().requires_grad_(True)
                 rad = _radial(ew.so2_conv_1.rad_func, tables, g_c, ectx.z_src[sl], ectx.z_tgt[sl], nb)
                 rad_d = rad.detach()
-                m = torch.empty(ec, 9, 2 * c, dtype=x.dtype, device=x.device)
-                ops.gather_rotate_fwd_.raw(x, g.src[sl], g.tgt[sl], wig[sl], rad_d, m)
-                m.requires_grad_(True)
-                msg = _so2_middle(ew, m)
+                if kept:
+                    y = kept[ci].requires_grad_(True)
+                    kept[ci] = None
+                    m = None
+                    msg = _so2_tail(ew, y)
+                else:
+                    m = torch.empty(ec, 9, 2 * c, dtype=x.dtype, device=x.device)
+                    ops.gather_rotate_fwd_.raw(x, g.src[sl], g.tgt[sl], wig[sl], rad_d, m)
+                    m.requires_grad_(True)
+                    msg = _so2_middle(ew, m)
             grad_msg = torch.empty_like(msg)
             ops.rotate_back_bwd_.raw(grad_out, msg.detach(), winv[sl], g.tgt[sl], grad_msg, gwinv[sl])
-            (gm,) = torch.autograd.grad(msg, (m,), grad_msg)
+            if m is None:
+                (gy,) = torch.autograd.grad(msg, (y,), grad_msg)
+                del y
+                gm = _so2_conv1_input_grad(ew, gy, 2 * c)
+                del gy
+            else:
+                (gm,) = torch.autograd.grad(msg, (m,), grad_msg)
             del msg, grad_msg
             g_src = torch.empty(ec, 9, c, dtype=x.dtype, device=x.device)
             g_tgt = torch.empty(ec, 9, c, dtype=x.dtype, device=x.device)
@@ -533,7 +576,7 @@ class _EdgeBlockFn(torch.autograd.Function):
             (gg,) = torch.autograd.grad(rad, g_c, grad_rad)
             ggauss[sl] = gg
             del rad, rad_d, grad_rad, gg
-        return gx, gwig, gwinv, ggauss, None, None, None, None
+        return gx, gwig, gwinv, ggauss, None, None, None, None, None
 
 
 class _EdgeDegreeFn(torch.autograd.Function):
@@ -608,6 +651,7 @@ class eSCNMDBackboneB200(nn.Module):
         always_use_pbc: bool = False,
         execution_mode: str = "b200",
         edge_chunk_size: int = 65536,
+        keep_conv1: Optional[bool] = None,
         **unused,
     ) -> None:
         super().__init__()
@@ -626,6 +670,8 @@ class eSCNMDBackboneB200(nn.Module):
         self.always_use_pbc, self.radius_pbc_version = always_use_pbc, radius_pbc_version
         self.regress_forces, self.direct_forces = regress_forces, direct_forces
         self.edge_chunk_size = int(edge_chunk_size)
+        # keep the conv-1 outputs of every layer for the backward pass (None: when they fit in free memory)
+        self.keep_conv1 = keep_conv1
         self.dataset_mapping = dict(dataset_mapping or {"omat": "omat", "omol": "omol"})
         self.sph_feature_size = (lmax + 1) ** 2
         c, h = sphere_channels, hidden_channels
@@ -732,12 +778,17 @@ class eSCNMDBackboneB200(nn.Module):
         ede = self.edge_degree_embedding.rad_func
         x = _EdgeDegreeFn.apply(x, winv, gauss, ede, self._tables(ede), ectx, nb, self.rescale_factor)
 
+        keep = self.keep_conv1
+        if keep is None:
+            # [E, 11H] float32 per layer; used only while it leaves half of the free device memory untouched
+            need = graph.num_edges * 11 * self.hidden_channels * 4 * self.num_layers
+            keep = pos.is_cuda and need < 0.5 * torch.cuda.mem_get_info(pos.device)[0]
         for blk in self.blocks:
             x_res = x
             xn = blk.norm_1(x, sys_node)
             x_full = halo_collect(xn, plan)  # per-layer halo exchange (escn_md_block.py:141-146)
             rad = blk.edge_wise.so2_conv_1.rad_func
-            x = _EdgeBlockFn.apply(x_full, wig, winv, gauss, blk.edge_wise, self._tables(rad), ectx, nb) + x_res
+            x = _EdgeBlockFn.apply(x_full, wig, winv, gauss, blk.edge_wise, self._tables(rad), ectx, nb, keep) + x_res
             x_res = x
             x = blk.atom_wise(blk.norm_2(x)) + x_res
         x = self.norm(x)

@@ -61,6 +61,30 @@ __device__ __forceinline__ int warp_sum_i(int v) {
     return v;
 }
 
+// Sum each of 35 per-lane partial values over the warp.  The first 32 go through a transposed butterfly
+// (at offset h every lane hands over the half it will not own: 16+8+4+2+1 = 31 shuffles, after which
+// lane l holds the total of value l); the last 3 use plain warp sums.  46 shuffles instead of 175.
+__device__ __forceinline__ void warp_reduce_wig(float (&v)[FCB200_WIG], int lane, float& first32, float& last3) {
+#pragma unroll
+    for (int h = 16; h >= 1; h >>= 1) {
+        const bool upper = (lane & h) != 0;
+#pragma unroll
+        for (int i = 0; i < h; ++i) {
+            const float a = v[i], b = v[i + h];
+            const float send = upper ? a : b;
+            const float keep = upper ? b : a;
+            v[i] = keep + __shfl_xor_sync(kFull, send, h);
+        }
+    }
+    first32 = v[0];
+    last3 = 0.f;
+#pragma unroll
+    for (int j = 0; j < FCB200_WIG - 32; ++j) {
+        const float t = warp_sum(v[32 + j]);
+        if (lane == j) last3 = t;
+    }
+}
+
 // Load the 35 compact Wigner entries of one edge into registers, identical in every lane.
 __device__ __forceinline__ void load_wig(const float* __restrict__ wig, int64_t e, int lane, float (&w)[FCB200_WIG]) {
     const float* p = wig + e * FCB200_WIG;

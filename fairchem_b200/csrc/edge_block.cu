@@ -197,16 +197,8 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
                 for (int L = 0; L < 9; ++L) st4(g_base + L * channels + c0, g[L]);
             }
         }
-        float mine = 0.f, mine2 = 0.f;
-#pragma unroll
-        for (int i = 0; i < FCB200_WIG; ++i) {
-            const float s = warp_sum(dw[i]);
-            if (i < 32) {
-                if (lane == i) mine = s;
-            } else if (lane == i - 32) {
-                mine2 = s;
-            }
-        }
+        float mine, mine2;
+        warp_reduce_wig(dw, lane, mine, mine2);
         grad_wig[e * FCB200_WIG + lane] = mine;
         if (lane < FCB200_WIG - 32) grad_wig[e * FCB200_WIG + 32 + lane] = mine2;
     }
@@ -278,16 +270,10 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
         }
         (void)rows_in;
         if (WANT_DW) {
-            float mine = 0.f, mine2 = 0.f;
-#pragma unroll
-            for (int i = 0; i < FCB200_WIG; ++i) {
-                const float s = warp_sum(dw[i]) * inv;
-                if (i < 32) {
-                    if (lane == i) mine = s;
-                } else if (lane == i - 32) {
-                    mine2 = s;
-                }
-            }
+            float mine, mine2;
+            warp_reduce_wig(dw, lane, mine, mine2);
+            mine *= inv;
+            mine2 *= inv;
             grad_winv[e * FCB200_WIG + lane] = mine;
             if (lane < FCB200_WIG - 32) grad_winv[e * FCB200_WIG + 32 + lane] = mine2;
         }
