@@ -782,7 +782,13 @@ class eSCNMDBackboneB200(nn.Module):
         if keep is None:
             # [E, 11H] float32 per layer; used only while it leaves half of the free device memory untouched
             need = graph.num_edges * 11 * self.hidden_channels * 4 * self.num_layers
-            keep = pos.is_cuda and need < 0.5 * torch.cuda.mem_get_info(pos.device)[0]
+            if pos.is_cuda:
+                # memory the caching allocator already holds but is not using counts as available
+                avail = (torch.cuda.mem_get_info(pos.device)[0] + torch.cuda.memory_reserved(pos.device)
+                         - torch.cuda.memory_allocated(pos.device))
+                keep = need < 0.5 * avail
+            else:
+                keep = False
         for blk in self.blocks:
             x_res = x
             xn = blk.norm_1(x, sys_node)
