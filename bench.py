@@ -369,7 +369,7 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="water_100k", choices=sorted(synthetic.WORKLOADS))
     ap.add_argument("--precision", type=int, default=3, choices=[0, 1, 3])
-    ap.add_argument("--chunk", type=int, default=65536)
+    ap.add_argument("--chunk", type=int, default=131072)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--profile-run", action="store_true",

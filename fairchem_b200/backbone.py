@@ -481,9 +481,8 @@ def _so2_middle(ew: Edgewise, m):
     return _so2_tail(ew, _so2_conv1(ew, m))
 
 
-def _so2_conv1_input_grad(ew: Edgewise, gy, cin: int):
-    """d(conv-1 input) from d(conv-1 output): three GEMMs with the transposed weights."""
-    conv = ew.so2_conv_1
+def _so2_conv_input_grad(conv: "SO2Convolution", gy, cin: int):
+    """d(convolution input) from d(convolution output): three GEMMs with the transposed weights."""
     w0 = conv.fc_m0.weight.detach()
     w1, w2 = _block_weight(conv.so2_m_conv[0].fc.weight), _block_weight(conv.so2_m_conv[1].fc.weight)
     n0, n1 = w0.shape[0], w1.shape[0]
@@ -500,7 +499,7 @@ class _EdgeBlockFn(torch.autograd.Function):
     """One layer's edge block over all chunks; differentiable in x, wig, winv and gauss."""
 
     @staticmethod
-    def forward(ctx, x, wig, winv, gauss, ew: Edgewise, tables, ectx: _EdgeCtx, nb: int, keep_conv1: bool):
+    def forward(ctx, x, wig, winv, gauss, ew: Edgewise, tables, ectx: _EdgeCtx, nb: int, keep_level: int):
         g = ectx.graph
         c = x.shape[2]
         x = x.contiguous()
@@ -517,8 +516,10 @@ class _EdgeBlockFn(torch.autograd.Function):
                 del m, rad
                 msg = _so2_tail(ew, y)
                 ops.rotate_back_reduce_fwd_.raw(msg, winv[sl], ch.row_ptr, out[ch.n0:ch.n1])
-                if keep_conv1:
-                    kept.append(y)  # the backward then skips the gather+rotate and the conv-1 GEMMs
+                if keep_level >= 2:
+                    kept.append((y, msg))  # the backward is then free of any recomputation but the radial MLP
+                elif keep_level == 1:
+                    kept.append((y, None))  # the backward skips the gather+rotate and the conv-1 GEMMs
         ctx.save_for_backward(x, wig, winv, gauss)
         ctx.ew, ctx.tables, ctx.ectx, ctx.nb, ctx.kept = ew, tables, ectx, nb, kept
         return out
@@ -543,11 +544,13 @@ class _EdgeBlockFn(torch.autograd.Function):
                 g_c = gauss[sl].detach().requires_grad_(True)
                 rad = _radial(ew.so2_conv_1.rad_func, tables, g_c, ectx.z_src[sl], ectx.z_tgt[sl], nb)
                 rad_d = rad.detach()
+                y = msg = m = None
                 if kept:
-                    y = kept[ci].requires_grad_(True)
+                    y, msg = kept[ci]
                     kept[ci] = None
-                    m = None
-                    msg = _so2_tail(ew, y)
+                    if msg is None:
+                        y.requires_grad_(True)
+                        msg = _so2_tail(ew, y)
                 else:
                     m = torch.empty(ec, 9, 2 * c, dtype=x.dtype, device=x.device)
                     ops.gather_rotate_fwd_.raw(x, g.src[sl], g.tgt[sl], wig[sl], rad_d, m)
@@ -555,13 +558,19 @@ class _EdgeBlockFn(torch.autograd.Function):
                     msg = _so2_middle(ew, m)
             grad_msg = torch.empty_like(msg)
             ops.rotate_back_bwd_.raw(grad_out, msg.detach(), winv[sl], g.tgt[sl], grad_msg, gwinv[sl])
-            if m is None:
-                (gy,) = torch.autograd.grad(msg, (y,), grad_msg)
-                del y
-                gm = _so2_conv1_input_grad(ew, gy, 2 * c)
-                del gy
-            else:
+            if m is not None:
                 (gm,) = torch.autograd.grad(msg, (m,), grad_msg)
+            else:
+                if msg.requires_grad:
+                    (gy,) = torch.autograd.grad(msg, (y,), grad_msg)
+                else:  # both kept: manual chain conv-2 input grad -> gate backward
+                    h = y.shape[1] // 11
+                    ga = _so2_conv_input_grad(ew.so2_conv_2, grad_msg.view(ec, -1), h)
+                    gy = torch.empty_like(y)
+                    ops.so2_gate_bwd_.raw(ga, y, gy, h)
+                    del ga
+                gm = _so2_conv_input_grad(ew.so2_conv_1, gy, 2 * c)
+                del gy, y
             del msg, grad_msg
             g_src = torch.empty(ec, 9, c, dtype=x.dtype, device=x.device)
             g_tgt = torch.empty(ec, 9, c, dtype=x.dtype, device=x.device)
@@ -650,8 +659,8 @@ class eSCNMDBackboneB200(nn.Module):
         radius_pbc_version: int = 200,
         always_use_pbc: bool = False,
         execution_mode: str = "b200",
-        edge_chunk_size: int = 65536,
-        keep_conv1: Optional[bool] = None,
+        edge_chunk_size: int = 131072,
+        keep_level: Optional[int] = None,
         **unused,
     ) -> None:
         super().__init__()
@@ -670,8 +679,9 @@ class eSCNMDBackboneB200(nn.Module):
         self.always_use_pbc, self.radius_pbc_version = always_use_pbc, radius_pbc_version
         self.regress_forces, self.direct_forces = regress_forces, direct_forces
         self.edge_chunk_size = int(edge_chunk_size)
-        # keep the conv-1 outputs of every layer for the backward pass (None: when they fit in free memory)
-        self.keep_conv1 = keep_conv1
+        # what every layer keeps per edge for its backward pass: 0 nothing (recompute the chunk), 1 the conv-1
+        # output [E,11H], 2 also the messages [E,9C]; None picks the highest level that fits in free memory
+        self.keep_level = keep_level
         self.dataset_mapping = dict(dataset_mapping or {"omat": "omat", "omol": "omol"})
         self.sph_feature_size = (lmax + 1) ** 2
         c, h = sphere_channels, hidden_channels
@@ -778,17 +788,19 @@ class eSCNMDBackboneB200(nn.Module):
         ede = self.edge_degree_embedding.rad_func
         x = _EdgeDegreeFn.apply(x, winv, gauss, ede, self._tables(ede), ectx, nb, self.rescale_factor)
 
-        keep = self.keep_conv1
+        keep = self.keep_level
         if keep is None:
-            # [E, 11H] float32 per layer; used only while it leaves half of the free device memory untouched
-            need = graph.num_edges * 11 * self.hidden_channels * 4 * self.num_layers
+            keep = 0
             if pos.is_cuda:
                 # memory the caching allocator already holds but is not using counts as available
                 avail = (torch.cuda.mem_get_info(pos.device)[0] + torch.cuda.memory_reserved(pos.device)
                          - torch.cuda.memory_allocated(pos.device))
-                keep = need < 0.5 * avail
-            else:
-                keep = False
+                per_layer_1 = graph.num_edges * 11 * self.hidden_channels * 4
+                per_layer_2 = per_layer_1 + graph.num_edges * 9 * c * 4
+                if per_layer_2 * self.num_layers < 0.5 * avail:
+                    keep = 2
+                elif per_layer_1 * self.num_layers < 0.5 * avail:
+                    keep = 1
         for blk in self.blocks:
             x_res = x
             xn = blk.norm_1(x, sys_node)
