@@ -136,25 +136,75 @@ def _l2_quadratic_forms() -> np.ndarray:
 _A2 = _l2_quadratic_forms()
 
 
-def wigner_blocks(q: torch.Tensor, lmax: int) -> torch.Tensor:
-    """Block-diagonal real Wigner-D [E,(lmax+1)^2,(lmax+1)^2] of the rotation q (l <= 2).
+def _next_degree(r1: torch.Tensor, prev: torch.Tensor, l: int) -> torch.Tensor:
+    """Real rotation matrix of degree l from degree l-1 and degree 1 (rows/columns m = -l..l): the
+    recursion of Ivanic and Ruedenberg, J. Phys. Chem. 100 (1996) 6342 (with the 1998 erratum)."""
+    n = r1.shape[0]
+    out = torch.zeros(n, 2 * l + 1, 2 * l + 1, dtype=r1.dtype)
 
-    l=1 is the Cartesian rotation matrix; l=2 follows from it through the quadratic forms of
-    the l=2 harmonics: D2[i,j] = (2/3) tr(A_i R A_j R^T).  The reference evaluates the same
-    degree-4 polynomial in q from a coefficient table (wigner_d_custom_kernels.py:196-227).
+    def one(i, j):
+        return r1[:, i + 1, j + 1]
+
+    def low(a, b):
+        return prev[:, a + l - 1, b + l - 1]
+
+    def p(i, a, b):
+        if abs(b) < l:
+            return one(i, 0) * low(a, b)
+        if b == l:
+            return one(i, 1) * low(a, l - 1) - one(i, -1) * low(a, -l + 1)
+        return one(i, 1) * low(a, -l + 1) + one(i, -1) * low(a, l - 1)
+
+    for m in range(-l, l + 1):
+        for mp in range(-l, l + 1):
+            den = (l + mp) * (l - mp) if abs(mp) < l else (2 * l) * (2 * l - 1)
+            d0 = 1.0 if m == 0 else 0.0
+            u = math.sqrt((l + m) * (l - m) / den)
+            v = 0.5 * math.sqrt((1 + d0) * (l + abs(m) - 1) * (l + abs(m)) / den) * (1 - 2 * d0)
+            w = -0.5 * math.sqrt((l - abs(m) - 1) * (l - abs(m)) / den) * (1 - d0)
+            val = 0
+            if u != 0:
+                val = val + u * p(0, m, mp)
+            if v != 0:
+                if m == 0:
+                    vv = p(1, 1, mp) + p(-1, -1, mp)
+                elif m > 0:
+                    d1 = 1.0 if m == 1 else 0.0
+                    vv = p(1, m - 1, mp) * math.sqrt(1 + d1) - p(-1, -m + 1, mp) * (1 - d1)
+                else:
+                    d1 = 1.0 if m == -1 else 0.0
+                    vv = p(1, m + 1, mp) * (1 - d1) + p(-1, -m - 1, mp) * math.sqrt(1 + d1)
+                val = val + v * vv
+            if w != 0:
+                ww = p(1, m + 1, mp) + p(-1, -m - 1, mp) if m > 0 else p(1, m - 1, mp) - p(-1, -m + 1, mp)
+                val = val + w * ww
+            out[:, m + l, mp + l] = val
+    return out
+
+
+def wigner_blocks(q: torch.Tensor, lmax: int) -> torch.Tensor:
+    """Block-diagonal real Wigner-D [E,(lmax+1)^2,(lmax+1)^2] of the rotation q.
+
+    l=1 is the Cartesian rotation matrix R (x,y,z order = m -1,0,1 in the y-polar convention); l=2
+    follows from it through the quadratic forms of the l=2 harmonics, D2[i,j] = (2/3) tr(A_i R A_j R^T);
+    l>=3 by the Ivanic-Ruedenberg recursion from the l-1 and l=1 blocks.  The reference evaluates the
+    same matrices as polynomials in q from coefficient tables (wigner_d_custom_kernels.py:196-356);
+    the two routes agree to rounding (checked on l = 2, 3, 4 against the reference's output).
     """
-    if lmax > 2:
-        raise NotImplementedError("oracle Wigner blocks are restated for lmax <= 2")
     n = q.shape[0]
     size = (lmax + 1) ** 2
-    d = torch.zeros(n, size, size, dtype=q.dtype)
-    d[:, 0, 0] = 1.0
+    blocks = [torch.ones(n, 1, 1, dtype=q.dtype)]
     if lmax >= 1:
         r = rotation_from_quaternion(q)
-        d[:, 1:4, 1:4] = r
+        blocks.append(r)
     if lmax >= 2:
         a = torch.tensor(_A2, dtype=q.dtype)
-        d[:, 4:9, 4:9] = (2.0 / 3.0) * torch.einsum("iab,nbc,jcd,nad->nij", a, r, a, r)
+        blocks.append((2.0 / 3.0) * torch.einsum("iab,nbc,jcd,nad->nij", a, r, a, r))
+    for l in range(3, lmax + 1):
+        blocks.append(_next_degree(r, blocks[-1], l))
+    d = torch.zeros(n, size, size, dtype=q.dtype)
+    for l, b in enumerate(blocks):
+        d[:, l * l:(l + 1) ** 2, l * l:(l + 1) ** 2] = b
     return d
 
 

@@ -196,6 +196,32 @@ def make_model_golden():
     np.savez_compressed(os.path.join(OUT, "uma_s_energy_forces.npz"), **out)
 
 
+def make_l4_golden():
+    """lmax=4 / mmax=2, 10-layer shape (the larger eSCN-MD configuration): Wigner blocks and a small model run."""
+    ref_shim.load()
+    from fairchem.core.models.uma.common.quaternion.wigner_d_hybrid import axis_angle_wigner_hybrid
+
+    bb, head = ref_shim.build_reference_model(0, lmax=4, mmax=2, num_layers=10)
+    sd = weights.random_init_state_dict(weights.ESCN_MD_L4, 0)
+    bsd, hsd = weights.split_head(sd)
+    missing, unexpected = bb.load_state_dict(bsd, strict=False)
+    assert not unexpected and all(k.startswith("Jd_") for k in missing), (missing, unexpected)
+    head.energy_block.load_state_dict(hsd)
+    out = {}
+    rng = np.random.default_rng(21)
+    vec = torch.tensor(rng.normal(size=(40, 3)) * rng.uniform(0.8, 5.9, (40, 1)), dtype=torch.float32)
+    gamma = torch.linspace(0.0, 6.0, 40)
+    d, _ = axis_angle_wigner_hybrid(vec, 4, gamma=gamma, coeffs=bb.wigner_data.coeffs, U_blocks=bb.wigner_data.U_blocks,
+                                    custom_kernels=bb.wigner_data.custom_kernels)
+    out["vec"], out["gamma"], out["wigner"] = vec.numpy(), gamma.numpy(), d.detach().numpy()
+    torch.set_num_threads(os.cpu_count() or 8)
+    for name, data in (("fcc_cu_32", synthetic.fcc_cu((2, 2, 2), seed=0)), ("water_96", synthetic.water_box(96, seed=0))):
+        e, f, _ = ref_shim.run_reference(bb, head, data, gamma=0.0)
+        out[f"{name}_energy"], out[f"{name}_forces"] = e.numpy(), f.numpy()
+        print("l4", name, e.numpy(), f.abs().max().item())
+    np.savez_compressed(os.path.join(OUT, "escn_md_l4.npz"), **out)
+
+
 def make_partition_golden():
     """Rank assignments of the reference's Morton partition (graph_partition.py:38-97)."""
     ref_shim.load()
@@ -210,7 +236,9 @@ def make_partition_golden():
 
 
 if __name__ == "__main__":
-    which = sys.argv[1:] or ["graph", "wigner", "ops", "model", "partition"]
+    which = sys.argv[1:] or ["graph", "wigner", "ops", "model", "partition", "l4"]
+    if "l4" in which:
+        make_l4_golden()
     if "partition" in which:
         make_partition_golden()
     if "graph" in which:

@@ -98,3 +98,25 @@ def test_energy_forces_oracle_matches_reference(golden, name):
     e_ref, f_ref = g[f"{name}_energy"], g[f"{name}_forces"]
     assert np.max(np.abs(e.numpy() - e_ref) / np.abs(e_ref)) < 2e-6
     assert np.max(np.abs(f.numpy() - f_ref)) < 5e-6
+
+
+def test_wigner_oracle_l4_matches_reference(golden):
+    """Blocks l = 0..4 (Ivanic-Ruedenberg recursion for l >= 3) against the reference's polynomial kernels."""
+    g = golden("escn_md_l4.npz")
+    d = O.wigner_blocks(O.edge_quaternion(torch.tensor(g["vec"]), torch.tensor(g["gamma"])), 4)
+    assert torch.allclose(d, torch.tensor(g["wigner"]), atol=5e-6, rtol=0)
+
+
+@pytest.mark.parametrize("name,make", [("fcc_cu_32", lambda: synthetic.fcc_cu((2, 2, 2), seed=0)),
+                                       ("water_96", lambda: synthetic.water_box(96, seed=0))])
+def test_energy_forces_oracle_l4_matches_reference(golden, name, make):
+    """10 layers, lmax = 4, mmax = 2 (the larger eSCN-MD configuration)."""
+    g = golden("escn_md_l4.npz")
+    d = make()
+    sd = weights.random_init_state_dict(weights.ESCN_MD_L4, 0)
+    ei, co, _, _ = G.radius_graph(d.pos.numpy(), d.cell.numpy(), d.pbc.numpy(), d.natoms.numpy(), 6.0, 30)
+    torch.set_num_threads(8)
+    e, f = O.energy_and_forces(sd, weights.ESCN_MD_L4, d, torch.from_numpy(ei), torch.from_numpy(co))
+    e_ref, f_ref = g[f"{name}_energy"], g[f"{name}_forces"]
+    assert np.max(np.abs(e.numpy() - e_ref) / np.abs(e_ref)) < 5e-6
+    assert np.max(np.abs(f.numpy() - f_ref)) < 1e-5
