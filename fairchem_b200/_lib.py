@@ -33,6 +33,18 @@ SIGNATURES = {
     "fcb200_rms_norm_sh_bwd": [P, P, P, P, P, I64, I32, P],
     "fcb200_edge_geometry_fwd": [P, P, P, P, P, P, P, P, P, P, F32, I32, F32, F32, F32, I64, I64, P],
     "fcb200_edge_geometry_bwd": [P, P, P, P, P, P, P, P, P, P, F32, I32, F32, F32, F32, I64, I64, P],
+    "fcb200_lx_gather_rotate_fwd": [P, P, P, P, P, P, I64, I64, I32, I32, P],
+    "fcb200_lx_gather_rotate_bwd": [P, P, P, P, P, P, P, P, P, P, I64, I64, I32, I32, P],
+    "fcb200_lx_rotate_back_reduce_fwd": [P, P, P, P, I64, I64, I32, I32, P],
+    "fcb200_lx_edge_degree_fwd": [P, P, P, P, P, F32, I64, I64, I32, I32, P],
+    "fcb200_lx_rotate_back_bwd": [P, P, P, P, P, P, I64, I64, I32, I32, P],
+    "fcb200_lx_edge_degree_bwd": [P, P, P, P, P, P, F32, I64, I64, I32, I32, P],
+    "fcb200_lx_so2_gate_fwd": [P, P, I64, I32, I32, P],
+    "fcb200_lx_so2_gate_bwd": [P, P, P, I64, I32, I32, P],
+    "fcb200_lx_rms_norm_sh_fwd": [P, P, P, P, P, P, F32, I64, I32, I32, P],
+    "fcb200_lx_rms_norm_sh_bwd": [P, P, P, P, P, I64, I32, I32, P],
+    "fcb200_lx_edge_geometry_fwd": [P, P, P, P, P, P, P, P, P, P, F32, I32, F32, F32, F32, I64, I64, I32, P],
+    "fcb200_lx_edge_geometry_bwd": [P, P, P, P, P, P, P, P, P, P, F32, I32, F32, F32, F32, I64, I64, I32, P],
     "fcb200_rg_count_sources": [P, P, I32, I64, P, P, P],
     "fcb200_exclusive_scan_i32": [P, P, I64, P],
     "fcb200_rg_fill_buckets": [P, P, I32, I64, P, P, P, P, I64, P],

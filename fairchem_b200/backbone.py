@@ -4,7 +4,7 @@
 "batch"}`` contract, attributes and ``state_dict`` keys of fairchem's ``eSCNMDBackbone``
 (src/fairchem/core/models/uma/escn_md.py:280-905) for the configuration the UMA models use
 (``norm_type="rms_norm_sh"``, ``act_type="gate"``, ``ff_type="spectral"``,
-``chg_spin_emb_type="rand_emb"``, lmax = mmax = 2), and ``MLP_EFS_HeadB200`` mirrors
+``chg_spin_emb_type="rand_emb"``, mmax = 2 with lmax = 2 or 4), and ``MLP_EFS_HeadB200`` mirrors
 ``MLP_EFS_Head`` (escn_md.py:1062-1168).  Reference weights load unchanged.
 
 What differs from the reference is how the edge block runs.  Edges are CSR-sorted by target and
@@ -31,8 +31,8 @@ from . import ops
 from .graph import generate_graph, get_pbc_shifts
 from .ops import EdgeGraph
 
-# compact-Wigner index of the transposed entry, and of the m=0 column entries
-_L_OF = [0, 1, 1, 1, 2, 2, 2, 2, 2]
+# degree of L-major row i (the lmax = 2 list is a prefix of the lmax = 4 one)
+_L_OF = ops.SHAPES[4].l_of
 
 
 def _compact_index(row: int, col: int) -> int:
@@ -50,13 +50,19 @@ def _transpose_index() -> list[int]:
     return idx
 
 
-def dense_to_compact_index() -> list[int]:
-    """Flat index into a dense [9,9] matrix of each compact Wigner entry."""
-    flat = [0] * ops.WIG
-    for row in range(9):
-        for col in range(9):
-            if _L_OF[row] == _L_OF[col]:
-                flat[_compact_index(row, col)] = row * 9 + col
+def dense_to_compact_index(lmax: int = 2, transposed: bool = False) -> list[int]:
+    """Flat index into a dense [NL,NL] block-diagonal matrix of each compact Wigner entry (block l: rows
+    m = -min(l,2)..min(l,2), all 2l+1 columns).  ``transposed`` reads entry (col, row) instead, which turns a
+    dense inverse D^T into the compact layout of D."""
+    sh = ops.SHAPES[lmax]
+    flat = [0] * sh.nw
+    for l in range(lmax + 1):
+        mm = min(l, 2)
+        for k in range(2 * mm + 1):
+            row = l * l + l + (k - mm)
+            for j in range(2 * l + 1):
+                col = l * l + j
+                flat[sh.woff[l] + k * (2 * l + 1) + j] = col * sh.nl + row if transposed else row * sh.nl + col
     return flat
 
 
@@ -107,6 +113,7 @@ class SO2Convolution(nn.Module):
 class Edgewise(nn.Module):
     def __init__(self, c, h, lmax, mmax, edge_widths):
         super().__init__()
+        self.lmax, self.hidden = lmax, h
         self.so2_conv_1 = SO2Convolution(2 * c, h, lmax, mmax, edge_widths, extra_m0=lmax * h)
         self.so2_conv_2 = SO2Convolution(h, c, lmax, mmax, None, 0)
 
@@ -135,7 +142,7 @@ class SO3Linear(nn.Module):
 
 class _SO3LinearFn(torch.autograd.Function):
     """Per-degree linear map on the tcgen05 GEMM: row i of every node is one [N, Cin] x [Cin, Cout] product
-    on a strided view (row stride 9*Cin), with the weight of the row's degree; bias on row 0."""
+    on a strided view (row stride NL*Cin), with the weight of the row's degree; bias on row 0."""
 
     @staticmethod
     def forward(ctx, x, weight, bias):
@@ -193,7 +200,7 @@ class RMSNormSH(nn.Module):
                              persistent=False)
 
     def forward(self, x, extra=None):
-        if x.is_cuda and self.lmax == 2:
+        if x.is_cuda and self.lmax in ops.SHAPES:
             return ops.RMSNormSH.apply(x, self.affine_weight.detach(), self.affine_bias.detach(), extra, self.eps)
         out = self._forward_torch(x)
         return out if extra is None else torch.cat([out[:, :1] + extra.unsqueeze(1), out[:, 1:]], dim=1)
@@ -431,9 +438,9 @@ def _block_weight(w: torch.Tensor) -> torch.Tensor:
 class _SO2Conv(torch.autograd.Function):
     """One SO(2) convolution as three GEMMs on column ranges of the M-major edge matrix.
 
-    x2d [E, 9*Cin] -> y [E, extra + 9*Cout]: the m=0 GEMM writes its (extra + 3*Cout) outputs first, the
-    block-form m=1 and m=2 GEMMs write next to it, so the result is already laid out as
-    [extra | row 0..8] with no concatenation or complex-combine pass."""
+    x2d [E, NM*Cin] -> y [E, extra + NM*Cout]: the m=0 GEMM writes its (extra + (lmax+1)*Cout) outputs first,
+    the block-form m=1 and m=2 GEMMs write next to it, so the result is already laid out as
+    [extra | row 0..NM-1] with no concatenation or complex-combine pass (NM = 9 for lmax 2, 19 for lmax 4)."""
 
     @staticmethod
     def forward(ctx, x2d, conv: "SO2Convolution", cin: int):
@@ -443,9 +450,10 @@ class _SO2Conv(torch.autograd.Function):
         n0, n1, n2 = w0.shape[0], w1.shape[0], w2.shape[0]
         y = torch.empty(e, n0 + n1 + n2, dtype=x2d.dtype, device=x2d.device)
         p = _GemmState.precision
-        _gemm(x2d[:, : 3 * cin], w0, b0, y[:, :n0], p)
-        _gemm(x2d[:, 3 * cin: 7 * cin], w1, None, y[:, n0: n0 + n1], p)
-        _gemm(x2d[:, 7 * cin:], w2, None, y[:, n0 + n1:], p)
+        k0, k1 = w0.shape[1], w1.shape[1]
+        _gemm(x2d[:, :k0], w0, b0, y[:, :n0], p)
+        _gemm(x2d[:, k0: k0 + k1], w1, None, y[:, n0: n0 + n1], p)
+        _gemm(x2d[:, k0 + k1:], w2, None, y[:, n0 + n1:], p)
         ctx.weights, ctx.cin, ctx.p = (w0, w1, w2), cin, p
         return y
 
@@ -455,29 +463,30 @@ class _SO2Conv(torch.autograd.Function):
         cin, p = ctx.cin, ctx.p
         gy = gy.contiguous()
         n0, n1 = w0.shape[0], w1.shape[0]
-        gx = torch.empty(gy.shape[0], 9 * cin, dtype=gy.dtype, device=gy.device)
-        _gemm(gy[:, :n0], _transposed(w0), None, gx[:, : 3 * cin], p)
-        _gemm(gy[:, n0: n0 + n1], _transposed(w1), None, gx[:, 3 * cin: 7 * cin], p)
-        _gemm(gy[:, n0 + n1:], _transposed(w2), None, gx[:, 7 * cin:], p)
+        k0, k1, k2 = w0.shape[1], w1.shape[1], w2.shape[1]
+        gx = torch.empty(gy.shape[0], k0 + k1 + k2, dtype=gy.dtype, device=gy.device)
+        _gemm(gy[:, :n0], _transposed(w0), None, gx[:, :k0], p)
+        _gemm(gy[:, n0: n0 + n1], _transposed(w1), None, gx[:, k0: k0 + k1], p)
+        _gemm(gy[:, n0 + n1:], _transposed(w2), None, gx[:, k0 + k1:], p)
         return gx, None, None
 
 
 def _so2_conv1(ew: Edgewise, m):
-    """First SO(2) convolution on the M-major edge rows m [E,9,2C] -> y [E, 11H] (gate scalars | 9 rows)."""
+    """First SO(2) convolution on the M-major edge rows m [E,NM,2C] -> y [E,(lmax+NM)H] (gate scalars | NM rows)."""
     e, cin = m.shape[0], m.shape[2]
-    return _SO2Conv.apply(m.view(e, 9 * cin), ew.so2_conv_1, cin)
+    return _SO2Conv.apply(m.view(e, -1), ew.so2_conv_1, cin)
 
 
 def _so2_tail(ew: Edgewise, y):
-    """gate -> second SO(2) convolution: y [E,11H] -> messages [E,9,C]."""
-    a = ops.SO2Gate.apply(y)
-    e, h = a.shape[0], a.shape[2]
-    z = _SO2Conv.apply(a.view(e, 9 * h), ew.so2_conv_2, h)
-    return z.view(e, 9, -1)
+    """gate -> second SO(2) convolution: y [E,(lmax+NM)H] -> messages [E,NM,C]."""
+    a = ops.SO2Gate.apply(y, ew.hidden)
+    e, nm, h = a.shape
+    z = _SO2Conv.apply(a.view(e, nm * h), ew.so2_conv_2, h)
+    return z.view(e, nm, -1)
 
 
 def _so2_middle(ew: Edgewise, m):
-    """conv 1 -> gate -> conv 2 on the M-major edge rows m [E,9,2C]; returns the messages [E,9,C]."""
+    """conv 1 -> gate -> conv 2 on the M-major edge rows m [E,NM,2C]; returns the messages [E,NM,C]."""
     return _so2_tail(ew, _so2_conv1(ew, m))
 
 
@@ -488,10 +497,11 @@ def _so2_conv_input_grad(conv: "SO2Convolution", gy, cin: int):
     n0, n1 = w0.shape[0], w1.shape[0]
     p = _GemmState.precision
     gy = gy.contiguous()
-    gx = torch.empty(gy.shape[0], 9 * cin, dtype=gy.dtype, device=gy.device)
-    _gemm(gy[:, :n0], _transposed(w0), None, gx[:, : 3 * cin], p)
-    _gemm(gy[:, n0: n0 + n1], _transposed(w1), None, gx[:, 3 * cin: 7 * cin], p)
-    _gemm(gy[:, n0 + n1:], _transposed(w2), None, gx[:, 7 * cin:], p)
+    k0, k1, k2 = w0.shape[1], w1.shape[1], w2.shape[1]
+    gx = torch.empty(gy.shape[0], k0 + k1 + k2, dtype=gy.dtype, device=gy.device)
+    _gemm(gy[:, :n0], _transposed(w0), None, gx[:, :k0], p)
+    _gemm(gy[:, n0: n0 + n1], _transposed(w1), None, gx[:, k0: k0 + k1], p)
+    _gemm(gy[:, n0 + n1:], _transposed(w2), None, gx[:, k0 + k1:], p)
     return gx
 
 
@@ -503,14 +513,16 @@ class _EdgeBlockFn(torch.autograd.Function):
         g = ectx.graph
         c = x.shape[2]
         x = x.contiguous()
-        out = torch.zeros(g.num_targets, 9, c, dtype=x.dtype, device=x.device)
+        nl = x.shape[1]
+        nm = ops.SHAPES[ew.lmax].nm
+        out = torch.zeros(g.num_targets, nl, c, dtype=x.dtype, device=x.device)
         kept = []
         with torch.no_grad():
             for ch in ectx.chunks:
                 sl = slice(ch.e0, ch.e1)
                 rad = _radial(ew.so2_conv_1.rad_func, tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb)
                 ec = ch.e1 - ch.e0
-                m = torch.empty(ec, 9, 2 * c, dtype=x.dtype, device=x.device)
+                m = torch.empty(ec, nm, 2 * c, dtype=x.dtype, device=x.device)
                 ops.gather_rotate_fwd_.raw(x, g.src[sl], g.tgt[sl], wig[sl], rad, m)
                 y = _so2_conv1(ew, m)
                 del m, rad
@@ -529,7 +541,8 @@ class _EdgeBlockFn(torch.autograd.Function):
         x, wig, winv, gauss = ctx.saved_tensors
         ew, tables, ectx, nb = ctx.ew, ctx.tables, ctx.ectx, ctx.nb
         g = ectx.graph
-        c = x.shape[2]
+        nl, c = x.shape[1], x.shape[2]
+        nm = ops.SHAPES[ew.lmax].nm
         grad_out = grad_out.contiguous()
         gx = torch.zeros_like(x)
         gwig = torch.empty_like(wig)
@@ -552,7 +565,7 @@ class _EdgeBlockFn(torch.autograd.Function):
                         y.requires_grad_(True)
                         msg = _so2_tail(ew, y)
                 else:
-                    m = torch.empty(ec, 9, 2 * c, dtype=x.dtype, device=x.device)
+                    m = torch.empty(ec, nm, 2 * c, dtype=x.dtype, device=x.device)
                     ops.gather_rotate_fwd_.raw(x, g.src[sl], g.tgt[sl], wig[sl], rad_d, m)
                     m.requires_grad_(True)
                     msg = _so2_middle(ew, m)
@@ -564,7 +577,7 @@ class _EdgeBlockFn(torch.autograd.Function):
                 if msg.requires_grad:
                     (gy,) = torch.autograd.grad(msg, (y,), grad_msg)
                 else:  # both kept: manual chain conv-2 input grad -> gate backward
-                    h = y.shape[1] // 11
+                    h = ew.hidden
                     ga = _so2_conv_input_grad(ew.so2_conv_2, grad_msg.view(ec, -1), h)
                     gy = torch.empty_like(y)
                     ops.so2_gate_bwd_.raw(ga, y, gy, h)
@@ -572,8 +585,8 @@ class _EdgeBlockFn(torch.autograd.Function):
                 gm = _so2_conv_input_grad(ew.so2_conv_1, gy, 2 * c)
                 del gy, y
             del msg, grad_msg
-            g_src = torch.empty(ec, 9, c, dtype=x.dtype, device=x.device)
-            g_tgt = torch.empty(ec, 9, c, dtype=x.dtype, device=x.device)
+            g_src = torch.empty(ec, nl, c, dtype=x.dtype, device=x.device)
+            g_tgt = torch.empty(ec, nl, c, dtype=x.dtype, device=x.device)
             grad_rad = torch.empty_like(rad_d)
             ops.gather_rotate_bwd_.raw(gm.contiguous(), x, g.src[sl], g.tgt[sl], wig[sl], rad_d, g_src, g_tgt, gwig[sl], grad_rad)
             del gm, m
@@ -664,8 +677,8 @@ class eSCNMDBackboneB200(nn.Module):
         **unused,
     ) -> None:
         super().__init__()
-        if (lmax, mmax) != (2, 2):
-            raise ValueError("the sm_100a edge-block kernels are built for lmax = mmax = 2")
+        if mmax != 2 or lmax not in ops.SHAPES:
+            raise ValueError("the sm_100a edge-block kernels are built for mmax = 2 with lmax = 2 or 4")
         if norm_type != "rms_norm_sh" or act_type != "gate" or ff_type != "spectral" or chg_spin_emb_type != "rand_emb":
             raise ValueError("only the UMA configuration (rms_norm_sh / gate / spectral / rand_emb) is implemented")
         if direct_forces or regress_stress or distance_function != "gaussian" or not use_dataset_embedding:
@@ -680,7 +693,7 @@ class eSCNMDBackboneB200(nn.Module):
         self.regress_forces, self.direct_forces = regress_forces, direct_forces
         self.edge_chunk_size = int(edge_chunk_size)
         # what every layer keeps per edge for its backward pass: 0 nothing (recompute the chunk), 1 the conv-1
-        # output [E,11H], 2 also the messages [E,9C]; None picks the highest level that fits in free memory
+        # output [E,(lmax+NM)H], 2 also the messages [E,NM*C]; None picks the highest level that fits in free memory
         self.keep_level = keep_level
         self.dataset_mapping = dict(dataset_mapping or {"omat": "omat", "omol": "omol"})
         self.sph_feature_size = (lmax + 1) ** 2
@@ -779,8 +792,12 @@ class eSCNMDBackboneB200(nn.Module):
         self.last_graph = {"edge_index": edge_index, "cell_offsets": cell_offsets}
         chunks = build_chunks(graph, self.edge_chunk_size)
 
-        vec, dist, env, wig, gauss = ops.EdgeGeometry.apply(pos_e, shift, gamma, graph, self.cutoff, nb, 0.0, self.cutoff, 2.0)
-        winv = _PermuteColumns.apply(wig, self._wig_transpose) * env.unsqueeze(1)
+        vec, dist, env, wig, gauss = ops.EdgeGeometry.apply(pos_e, shift, gamma, graph, self.cutoff, nb, 0.0, self.cutoff, 2.0,
+                                                            self.lmax)
+        if ops.uses_transposed_inverse(self.lmax):
+            winv = _PermuteColumns.apply(wig, self._wig_transpose) * env.unsqueeze(1)
+        else:  # the any-lmax kernels read the inverse from the same compact layout (D is orthogonal)
+            winv = wig * env.unsqueeze(1)
         ectx = _EdgeCtx(graph, chunks, wig, winv, gauss, z_e[edge_index[0]], z_e[edge_index[1]])
 
         x = torch.zeros(n_local, self.sph_feature_size, c, dtype=pos.dtype, device=pos.device)
@@ -795,8 +812,9 @@ class eSCNMDBackboneB200(nn.Module):
                 # memory the caching allocator already holds but is not using counts as available
                 avail = (torch.cuda.mem_get_info(pos.device)[0] + torch.cuda.memory_reserved(pos.device)
                          - torch.cuda.memory_allocated(pos.device))
-                per_layer_1 = graph.num_edges * 11 * self.hidden_channels * 4
-                per_layer_2 = per_layer_1 + graph.num_edges * 9 * c * 4
+                sh = ops.SHAPES[self.lmax]
+                per_layer_1 = graph.num_edges * (sh.lmax + sh.nm) * self.hidden_channels * 4
+                per_layer_2 = per_layer_1 + graph.num_edges * sh.nm * c * 4
                 if per_layer_2 * self.num_layers < 0.5 * avail:
                     keep = 2
                 elif per_layer_1 * self.num_layers < 0.5 * avail:

@@ -19,16 +19,23 @@ from . import ops
 from .backbone import dense_to_compact_index
 from .ops import EdgeGraph
 
-_FLAT = None
+_FLAT: dict = {}
 _GRAPH_CACHE: dict = {}
+_LMAX_OF_NL = {s.nl: l for l, s in ops.SHAPES.items()}
 
 
-def _compact(wigner: torch.Tensor) -> torch.Tensor:
-    """Dense [E,9,9] block-diagonal matrix -> compact [E,35] (differentiable gather)."""
-    global _FLAT
-    if _FLAT is None or _FLAT.device != wigner.device:
-        _FLAT = torch.tensor(dense_to_compact_index(), device=wigner.device)
-    return wigner.reshape(wigner.shape[0], 81).index_select(1, _FLAT)
+def _compact(wigner: torch.Tensor, inverse: bool = False) -> torch.Tensor:
+    """Dense [E,NL,NL] block-diagonal matrix -> compact [E,NW] (differentiable gather).  An inverse
+    rotation goes to the layout the rotate-back kernels of its lmax expect."""
+    nl = wigner.shape[1]
+    lmax = _LMAX_OF_NL.get(nl)
+    if lmax is None or wigner.shape[2] != nl:
+        raise ValueError("B200Backend takes square block-diagonal Wigner matrices of lmax = 2 or 4")
+    transposed = inverse and not ops.uses_transposed_inverse(lmax)
+    key = (lmax, transposed, wigner.device)
+    if key not in _FLAT:
+        _FLAT[key] = torch.tensor(dense_to_compact_index(lmax, transposed), device=wigner.device)
+    return wigner.reshape(wigner.shape[0], nl * nl).index_select(1, _FLAT[key])
 
 
 def _graph_for(src: torch.Tensor, tgt: torch.Tensor, num_nodes: int, num_targets: int):
@@ -57,8 +64,8 @@ class B200Backend:
 
     @staticmethod
     def validate(lmax: int, mmax: int, settings=None) -> None:
-        if lmax != 2 or mmax != 2:
-            raise ValueError("B200Backend kernels are built for lmax = mmax = 2")
+        if mmax != 2 or lmax not in ops.SHAPES:
+            raise ValueError("B200Backend kernels are built for mmax = 2 with lmax = 2 or 4")
         if settings is not None and getattr(settings, "activation_checkpointing", False):
             raise ValueError("B200Backend chunks and recomputes inside its own edge block; "
                              "turn activation_checkpointing off")
@@ -75,8 +82,7 @@ class B200Backend:
 
     @staticmethod
     def prepare_wigner(wigner, wigner_inv, mappingReduced=None, coefficient_index=None):
-        if coefficient_index is not None:
-            raise ValueError("B200Backend needs mmax == lmax (no coefficient selection)")
+        # the kernels select the |m| <= 2 coefficients themselves: they take the square block-diagonal matrices
         return wigner, wigner_inv
 
     @staticmethod
@@ -91,7 +97,7 @@ class B200Backend:
     def permute_wigner_inv_edge_to_node(x_message, wigner_inv, scatter_target, num_nodes):
         """[E,9,C] (M-major), [E,9,9], [E] -> [num_nodes,9,C]."""
         graph, perm, _ = _graph_for(scatter_target, scatter_target, num_nodes, num_nodes)
-        w = _compact(wigner_inv)
+        w = _compact(wigner_inv, inverse=True)
         if perm is not None:
             x_message, w = x_message[perm], w[perm]
         return ops.RotateBackReduce.apply(x_message, w, graph)
@@ -101,15 +107,15 @@ class B200Backend:
                             rescale_factor):
         graph, perm, _ = _graph_for(scatter_target, scatter_target, x.shape[0], x.shape[0])
         radial = radial_output.reshape(-1, m_0_num_coefficients, sphere_channels)
-        w = _compact(wigner_inv)
+        w = _compact(wigner_inv, inverse=True)
         if perm is not None:
             radial, w = radial[perm], w[perm]
         return ops.EdgeDegree.apply(x, radial, w, graph, float(rescale_factor))
 
     @staticmethod
     def fused_node_to_edge_conv1_pack(x_full, edge_index, wigner, radial, sphere_channels):
-        """Gather + rotate + radial scale; returns the three GEMM operands m0 [E,3*2C], m1 [E,4*2C],
-        m2 [E,2*2C] as column ranges of one [E, 9*2C] buffer."""
+        """Gather + rotate + radial scale; returns the three GEMM operands m0 [E,(lmax+1)*2C], m1 [E,2*lmax*2C],
+        m2 [E,2*(lmax-1)*2C] as column ranges of one [E, NM*2C] buffer."""
         graph, perm, inv = _graph_for(edge_index[0], edge_index[1], x_full.shape[0], x_full.shape[0])
         w = _compact(wigner)
         if perm is not None:
@@ -119,10 +125,13 @@ class B200Backend:
             out = out[inv]
         flat = out.reshape(out.shape[0], -1)
         c2 = 2 * sphere_channels
-        return flat[:, : 3 * c2], flat[:, 3 * c2: 7 * c2], flat[:, 7 * c2:]
+        ms = ops.SHAPES[_LMAX_OF_NL[x_full.shape[1]]].m_size
+        a, b = ms[0] * c2, (ms[0] + 2 * ms[1]) * c2
+        return flat[:, :a], flat[:, a:b], flat[:, b:]
 
     @staticmethod
     def fused_conv2_inv_edge_to_node(g0, g1, g2, wigner_inv_envelope, scatter_target, num_nodes, sphere_channels):
-        """Block-GEMM outputs g0 [E,3C], g1 [E,4C], g2 [E,2C] -> rotate back and sum into [num_nodes,9,C]."""
-        msg = torch.cat([g0, g1, g2], dim=1).view(g0.shape[0], 9, sphere_channels)
+        """Block-GEMM outputs g0 [E,(lmax+1)C], g1 [E,2*lmax*C], g2 [E,2*(lmax-1)C] -> rotate back and sum into
+        [num_nodes,NL,C]."""
+        msg = torch.cat([g0, g1, g2], dim=1).view(g0.shape[0], -1, sphere_channels)
         return B200Backend.permute_wigner_inv_edge_to_node(msg, wigner_inv_envelope, scatter_target, num_nodes)

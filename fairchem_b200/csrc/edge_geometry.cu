@@ -1,11 +1,12 @@
 // Per-edge geometry: edge vector, length, envelope, Gaussian basis and the compact Wigner-D of the
-// rotation that takes the edge direction to +Y (l <= 2), forward and backward.
+// rotation that takes the edge direction to +Y (l <= 2, or l <= 4 with rows |m| <= 2), forward and backward.
 //
 // The rotation code is written once as a template over the scalar type.  Instantiated with
 // float it is the forward pass; instantiated with Dual3 (value + three tangents, one per component
 // of the edge vector) it yields d(wigner)/d(vec) exactly, which the backward kernel contracts with
 // the incoming gradient.  35 outputs against 3 inputs makes forward mode the cheap direction.
 #include "common.cuh"
+#include "shape_lx.cuh"
 
 namespace fcb200 {
 
@@ -148,6 +149,100 @@ __device__ __forceinline__ void wigner_from_quaternion(const T (&q)[4], F&& emit
     }
 }
 
+// ---- degrees l >= 3: the recursion of Ivanic and Ruedenberg (J. Phys. Chem. 100 (1996) 6342, erratum 1998) ----
+// R^l[m][m'] = u P(0,m,m') + v V(m,m') + w W(m,m'), built from R^(l-1) and the l = 1 block; rows and
+// columns run m = -l..l.  All coefficients are compile-time constants.
+constexpr double csqrt(double x) {
+    if (x <= 0.0) return 0.0;
+    double g = x > 1.0 ? x : 1.0;
+    for (int i = 0; i < 64; ++i) g = 0.5 * (g + x / g);
+    return g;
+}
+
+template <int L> struct IR {
+    static constexpr int P = 2 * L - 1;  // side of the degree l-1 block
+    // P(i, a, b) of the paper: i indexes the l = 1 row (-1, 0, 1), a the row of R^(l-1), b the target column
+    template <class T, int I, int A, int B>
+    static __device__ __forceinline__ T p(const T (&r)[3][3], const T (&prev)[P][P]) {
+        if constexpr (B < L && B > -L) {
+            return r[I + 1][1] * prev[A + L - 1][B + L - 1];
+        } else if constexpr (B == L) {
+            return r[I + 1][2] * prev[A + L - 1][2 * L - 2] - r[I + 1][0] * prev[A + L - 1][0];
+        } else {
+            return r[I + 1][2] * prev[A + L - 1][0] + r[I + 1][0] * prev[A + L - 1][2 * L - 2];
+        }
+    }
+    template <class T, int M, int MP>
+    static __device__ __forceinline__ T entry(const T (&r)[3][3], const T (&prev)[P][P]) {
+        constexpr int am = M < 0 ? -M : M;
+        constexpr double den = (MP < L && MP > -L) ? (double)((L + MP) * (L - MP)) : (double)((2 * L) * (2 * L - 1));
+        constexpr double d0 = M == 0 ? 1.0 : 0.0;
+        constexpr float u = (float)csqrt((double)((L + M) * (L - M)) / den);
+        constexpr float v = (float)(0.5 * csqrt((1.0 + d0) * (double)((L + am - 1) * (L + am)) / den) * (1.0 - 2.0 * d0));
+        constexpr float w = (float)(-0.5 * csqrt((double)((L - am - 1) * (L - am)) / den) * (1.0 - d0));
+        constexpr float s2 = 1.41421356237309504880f;
+        T val = Ops<T>::lit(0.f);
+        if constexpr (u != 0.f) val = u * p<T, 0, M, MP>(r, prev);
+        if constexpr (v != 0.f) {
+            if constexpr (M == 0) {
+                val = val + v * (p<T, 1, 1, MP>(r, prev) + p<T, -1, -1, MP>(r, prev));
+            } else if constexpr (M == 1) {
+                val = val + (v * s2) * p<T, 1, 0, MP>(r, prev);
+            } else if constexpr (M > 1) {
+                val = val + v * (p<T, 1, M - 1, MP>(r, prev) - p<T, -1, -M + 1, MP>(r, prev));
+            } else if constexpr (M == -1) {
+                val = val + (v * s2) * p<T, -1, 0, MP>(r, prev);
+            } else {
+                val = val + v * (p<T, 1, M + 1, MP>(r, prev) + p<T, -1, -M - 1, MP>(r, prev));
+            }
+        }
+        if constexpr (w != 0.f) {
+            if constexpr (M > 0) {
+                val = val + w * (p<T, 1, M + 1, MP>(r, prev) + p<T, -1, -M - 1, MP>(r, prev));
+            } else {
+                val = val + w * (p<T, 1, M - 1, MP>(r, prev) - p<T, -1, -M + 1, MP>(r, prev));
+            }
+        }
+        return val;
+    }
+    template <class T, int M, int MP, class F>
+    static __device__ __forceinline__ void cols(const T (&r)[3][3], const T (&prev)[P][P], F&& f) {
+        f(M, MP, entry<T, M, MP>(r, prev));
+        if constexpr (MP < L) cols<T, M, MP + 1>(r, prev, f);
+    }
+    // f(m, m', value) for rows m = MLO..MHI, all columns
+    template <class T, int MLO, int MHI, class F>
+    static __device__ __forceinline__ void rows(const T (&r)[3][3], const T (&prev)[P][P], F&& f) {
+        cols<T, MLO, -L>(r, prev, f);
+        if constexpr (MLO < MHI) rows<T, MLO + 1, MHI>(r, prev, f);
+    }
+};
+
+// Compact Wigner entries for lmax = 4 (rows |m| <= 2 of every block): degrees 0..2 as above, then
+// the full degree-3 block and rows -2..2 of degree 4 by the recursion.
+template <class T, class F>
+__device__ __forceinline__ void wigner_from_quaternion_l4(const T (&q)[4], F&& emit) {
+    using S = Shape<4>;
+    T r[3][3], d2[5][5];
+    wigner_from_quaternion<T>(q, [&](int i, T v) {
+        if (i >= 1 && i < 10) r[(i - 1) / 3][(i - 1) % 3] = v;
+        if (i >= 10) d2[(i - 10) / 5][(i - 10) % 5] = v;
+        emit(i, v);
+    });
+    T d3[7][7];
+    IR<3>::template rows<T, -3, 3>(r, d2, [&](int m, int mp, T v) {
+        d3[m + 3][mp + 3] = v;
+        if (m >= -2 && m <= 2) emit(S::woff(3) + (m + 2) * 7 + (mp + 3), v);
+    });
+    IR<4>::template rows<T, -2, 2>(r, d3, [&](int m, int mp, T v) { emit(S::woff(4) + (m + 2) * 9 + (mp + 4), v); });
+}
+
+template <int LMAX, class T, class F>
+__device__ __forceinline__ void wigner_compact(const T (&q)[4], F&& emit) {
+    if constexpr (LMAX == 2) wigner_from_quaternion<T>(q, emit);
+    else wigner_from_quaternion_l4<T>(q, emit);
+}
+
 __device__ __forceinline__ void edge_vector(const float* __restrict__ pos, const int32_t* __restrict__ src,
                                             const int32_t* __restrict__ tgt, const float* __restrict__ shift, int64_t e,
                                             float& vx, float& vy, float& vz) {
@@ -167,6 +262,7 @@ struct BasisParams {
     int num;
 };
 
+template <int LMAX>
 __global__ void __launch_bounds__(128)
     edge_geometry_fwd_kernel(const float* __restrict__ pos, const int32_t* __restrict__ src, const int32_t* __restrict__ tgt,
                              const float* __restrict__ shift, const float* __restrict__ gamma, float* __restrict__ vec,
@@ -194,11 +290,12 @@ __global__ void __launch_bounds__(128)
     if (wig) {
         float q[4];
         edge_quaternion<float>(vx, vy, vz, gamma ? gamma[e] : 0.f, q);
-        float* w = wig + e * FCB200_WIG;
-        wigner_from_quaternion<float>(q, [&](int i, float v) { w[i] = v; });
+        float* w = wig + e * Shape<LMAX>::kW;
+        wigner_compact<LMAX, float>(q, [&](int i, float v) { w[i] = v; });
     }
 }
 
+template <int LMAX>
 __global__ void __launch_bounds__(128)
     edge_geometry_bwd_kernel(const float* __restrict__ pos, const int32_t* __restrict__ src, const int32_t* __restrict__ tgt,
                              const float* __restrict__ shift, const float* __restrict__ gamma,
@@ -235,8 +332,8 @@ __global__ void __launch_bounds__(128)
         Dual3 q[4];
         const Dual3 dx{vx, 1.f, 0.f, 0.f}, dy{vy, 0.f, 1.f, 0.f}, dz{vz, 0.f, 0.f, 1.f};
         edge_quaternion<Dual3>(dx, dy, dz, gamma ? gamma[e] : 0.f, q);
-        const float* gw = grad_wig + e * FCB200_WIG;
-        wigner_from_quaternion<Dual3>(q, [&](int i, Dual3 v) {
+        const float* gw = grad_wig + e * Shape<LMAX>::kW;
+        wigner_compact<LMAX, Dual3>(q, [&](int i, Dual3 v) {
             const float g = gw[i];
             gx = fmaf(g, v.a, gx);
             gy = fmaf(g, v.b, gy);
@@ -265,30 +362,58 @@ using namespace fcb200;
 
 extern "C" {
 
+int fcb200_lx_edge_geometry_fwd(const float* pos, const int32_t* src, const int32_t* tgt, const float* shift, const float* gamma,
+                                float* vec, float* dist, float* env, float* wig, float* gauss, float cutoff, int32_t num_basis,
+                                float basis_start, float basis_stop, float basis_width, int64_t num_edges, int64_t num_nodes,
+                                int32_t lmax, void* stream) {
+    if (!pos || !src || !tgt || num_edges < 0 || num_nodes < 0 || cutoff <= 0.f) return FCB200_EINVAL;
+    if (gauss && num_basis < 2) return FCB200_EINVAL;
+    if (lmax != 2 && lmax != 4) return FCB200_EINVAL;
+    if (num_edges == 0) return FCB200_OK;
+    const BasisParams bp = make_basis(cutoff, num_basis, basis_start, basis_stop, basis_width);
+    const unsigned grid = (unsigned)((num_edges + 127) / 128);
+    if (lmax == 2)
+        edge_geometry_fwd_kernel<2><<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(pos, src, tgt, shift, gamma, vec, dist, env,
+                                                                                         wig, gauss, bp, num_edges);
+    else
+        edge_geometry_fwd_kernel<4><<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(pos, src, tgt, shift, gamma, vec, dist, env,
+                                                                                         wig, gauss, bp, num_edges);
+    return launch_status();
+}
+
+int fcb200_lx_edge_geometry_bwd(const float* pos, const int32_t* src, const int32_t* tgt, const float* shift, const float* gamma,
+                                const float* grad_wig, const float* grad_env, const float* grad_gauss, const float* grad_dist,
+                                float* grad_vec, float cutoff, int32_t num_basis, float basis_start, float basis_stop,
+                                float basis_width, int64_t num_edges, int64_t num_nodes, int32_t lmax, void* stream) {
+    if (!pos || !src || !tgt || !grad_vec || num_edges < 0 || num_nodes < 0 || cutoff <= 0.f) return FCB200_EINVAL;
+    if (grad_gauss && num_basis < 2) return FCB200_EINVAL;
+    if (lmax != 2 && lmax != 4) return FCB200_EINVAL;
+    if (num_edges == 0) return FCB200_OK;
+    const BasisParams bp = make_basis(cutoff, num_basis, basis_start, basis_stop, basis_width);
+    const unsigned grid = (unsigned)((num_edges + 127) / 128);
+    if (lmax == 2)
+        edge_geometry_bwd_kernel<2><<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+            pos, src, tgt, shift, gamma, grad_wig, grad_env, grad_gauss, grad_dist, grad_vec, bp, num_edges);
+    else
+        edge_geometry_bwd_kernel<4><<<grid, 128, 0, static_cast<cudaStream_t>(stream)>>>(
+            pos, src, tgt, shift, gamma, grad_wig, grad_env, grad_gauss, grad_dist, grad_vec, bp, num_edges);
+    return launch_status();
+}
+
 int fcb200_edge_geometry_fwd(const float* pos, const int32_t* src, const int32_t* tgt, const float* shift, const float* gamma,
                              float* vec, float* dist, float* env, float* wig, float* gauss, float cutoff, int32_t num_basis,
                              float basis_start, float basis_stop, float basis_width, int64_t num_edges, int64_t num_nodes,
                              void* stream) {
-    if (!pos || !src || !tgt || num_edges < 0 || num_nodes < 0 || cutoff <= 0.f) return FCB200_EINVAL;
-    if (gauss && num_basis < 2) return FCB200_EINVAL;
-    if (num_edges == 0) return FCB200_OK;
-    const BasisParams bp = make_basis(cutoff, num_basis, basis_start, basis_stop, basis_width);
-    edge_geometry_fwd_kernel<<<(unsigned)((num_edges + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        pos, src, tgt, shift, gamma, vec, dist, env, wig, gauss, bp, num_edges);
-    return launch_status();
+    return fcb200_lx_edge_geometry_fwd(pos, src, tgt, shift, gamma, vec, dist, env, wig, gauss, cutoff, num_basis, basis_start,
+                                       basis_stop, basis_width, num_edges, num_nodes, 2, stream);
 }
 
 int fcb200_edge_geometry_bwd(const float* pos, const int32_t* src, const int32_t* tgt, const float* shift, const float* gamma,
                              const float* grad_wig, const float* grad_env, const float* grad_gauss, const float* grad_dist,
                              float* grad_vec, float cutoff, int32_t num_basis, float basis_start, float basis_stop,
                              float basis_width, int64_t num_edges, int64_t num_nodes, void* stream) {
-    if (!pos || !src || !tgt || !grad_vec || num_edges < 0 || num_nodes < 0 || cutoff <= 0.f) return FCB200_EINVAL;
-    if (grad_gauss && num_basis < 2) return FCB200_EINVAL;
-    if (num_edges == 0) return FCB200_OK;
-    const BasisParams bp = make_basis(cutoff, num_basis, basis_start, basis_stop, basis_width);
-    edge_geometry_bwd_kernel<<<(unsigned)((num_edges + 127) / 128), 128, 0, static_cast<cudaStream_t>(stream)>>>(
-        pos, src, tgt, shift, gamma, grad_wig, grad_env, grad_gauss, grad_dist, grad_vec, bp, num_edges);
-    return launch_status();
+    return fcb200_lx_edge_geometry_bwd(pos, src, tgt, shift, gamma, grad_wig, grad_env, grad_gauss, grad_dist, grad_vec, cutoff,
+                                       num_basis, basis_start, basis_stop, basis_width, num_edges, num_nodes, 2, stream);
 }
 
 }  // extern "C"

@@ -1,18 +1,27 @@
-// Node-wise kernels that bracket the edge block: the degree-balanced RMS norm over a node's 9 x C
+// Node-wise kernels that bracket the edge block: the degree-balanced RMS norm over a node's (lmax+1)^2 x C
 // spherical-harmonic coefficients (forward and backward), one warp per node, a lane owns one float4 of
-// each of the 9 rows.  HBM-bound: one read and one write of the node tensor per pass.
+// each of the rows.  HBM-bound: one read and one write of the node tensor per pass.
 #include "common.cuh"
 
 namespace fcb200 {
 
 constexpr int kNodeWarps = 8;
 
-// weight of row i in the norm: 1 / ((2l+1) * (lmax+1)), lmax = 2
-__host__ __device__ constexpr float balance_of(int L) { return L == 0 ? 1.0f / 3.0f : (L < 4 ? 1.0f / 9.0f : 1.0f / 15.0f); }
+// degree of L-major row L
+__host__ __device__ constexpr int degree_of(int L) {
+    int l = 0;
+    while ((l + 1) * (l + 1) <= L) ++l;
+    return l;
+}
+// weight of row L in the norm: 1 / ((2l+1) * (lmax+1))
+template <int LMAX> __host__ __device__ constexpr float balance_of(int L) {
+    return 1.0f / (float)((2 * degree_of(L) + 1) * (LMAX + 1));
+}
 
 __device__ __forceinline__ float hsum4(float4 v) { return v.x + v.y + v.z + v.w; }
 
 // out_i = y_i * rsqrt(mean_c sum_i bal_i y_i^2 + eps) * w[l_i] (+ bias, + extra on row 0), y_0 = x_0 - mean_c x_0
+template <int LMAX>
 __global__ void __launch_bounds__(kNodeWarps* kWarp)
     rms_norm_fwd_kernel(const float* __restrict__ x, const float* __restrict__ weight, const float* __restrict__ bias,
                         const float* __restrict__ extra, float* __restrict__ out, float* __restrict__ stats, float eps,
@@ -21,9 +30,10 @@ __global__ void __launch_bounds__(kNodeWarps* kWarp)
     const int64_t warp0 = (int64_t)blockIdx.x * kNodeWarps + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kNodeWarps;
     const float inv_c = 1.0f / (float)channels;
+    constexpr int kL = (LMAX + 1) * (LMAX + 1);
     for (int64_t n = warp0; n < num_nodes; n += nwarps) {
-        const float* xb = x + n * 9LL * channels;
-        float* ob = out + n * 9LL * channels;
+        const float* xb = x + n * (int64_t)kL * channels;
+        float* ob = out + n * (int64_t)kL * channels;
         // pass 1: mean of row 0 and the balanced sum of squares (channels > 128 loop over tiles)
         float s0 = 0.f;
         for (int c = lane * 4; c < channels; c += 128) s0 += hsum4(ld4(xb + c));
@@ -31,19 +41,19 @@ __global__ void __launch_bounds__(kNodeWarps* kWarp)
         float acc = 0.f;
         for (int c = lane * 4; c < channels; c += 128) {
 #pragma unroll
-            for (int L = 0; L < 9; ++L) {
+            for (int L = 0; L < kL; ++L) {
                 float4 v = ld4(xb + L * channels + c);
                 if (L == 0) v = make_float4(v.x - mean0, v.y - mean0, v.z - mean0, v.w - mean0);
-                acc = fmaf(balance_of(L), dot4(v, v), acc);
+                acc = fmaf(balance_of<LMAX>(L), dot4(v, v), acc);
             }
         }
         const float scale = rsqrtf(warp_sum(acc) * inv_c + eps);
         for (int c = lane * 4; c < channels; c += 128) {
 #pragma unroll
-            for (int L = 0; L < 9; ++L) {
+            for (int L = 0; L < kL; ++L) {
                 float4 v = ld4(xb + L * channels + c);
                 if (L == 0) v = make_float4(v.x - mean0, v.y - mean0, v.z - mean0, v.w - mean0);
-                float4 o = mul4(scale4(scale, v), ld4(weight + deg_of(L) * channels + c));
+                float4 o = mul4(scale4(scale, v), ld4(weight + degree_of(L) * channels + c));
                 if (L == 0) {
                     o = add4(o, ld4(bias + c));
                     if (extra) o = add4(o, ld4(extra + n * channels + c));
@@ -58,6 +68,7 @@ __global__ void __launch_bounds__(kNodeWarps* kWarp)
     }
 }
 
+template <int LMAX>
 __global__ void __launch_bounds__(kNodeWarps* kWarp)
     rms_norm_bwd_kernel(const float* __restrict__ grad_out, const float* __restrict__ x, const float* __restrict__ weight,
                         const float* __restrict__ stats, float* __restrict__ grad_x, int64_t num_nodes, int channels) {
@@ -65,19 +76,20 @@ __global__ void __launch_bounds__(kNodeWarps* kWarp)
     const int64_t warp0 = (int64_t)blockIdx.x * kNodeWarps + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kNodeWarps;
     const float inv_c = 1.0f / (float)channels;
+    constexpr int kL = (LMAX + 1) * (LMAX + 1);
     for (int64_t n = warp0; n < num_nodes; n += nwarps) {
-        const float* xb = x + n * 9LL * channels;
-        const float* gb = grad_out + n * 9LL * channels;
-        float* qb = grad_x + n * 9LL * channels;
+        const float* xb = x + n * (int64_t)kL * channels;
+        const float* gb = grad_out + n * (int64_t)kL * channels;
+        float* qb = grad_x + n * (int64_t)kL * channels;
         const float mean0 = stats[n * 2 + 0], scale = stats[n * 2 + 1];
         // dL/dscale = sum_{i,c} g_i w_i y_i ; also sum_c g_0 w_0 for the centering term
         float ds = 0.f, g0w = 0.f, y0b = 0.f;
         for (int c = lane * 4; c < channels; c += 128) {
 #pragma unroll
-            for (int L = 0; L < 9; ++L) {
+            for (int L = 0; L < kL; ++L) {
                 float4 v = ld4(xb + L * channels + c);
                 if (L == 0) v = make_float4(v.x - mean0, v.y - mean0, v.z - mean0, v.w - mean0);
-                const float4 gw = mul4(ld4(gb + L * channels + c), ld4(weight + deg_of(L) * channels + c));
+                const float4 gw = mul4(ld4(gb + L * channels + c), ld4(weight + degree_of(L) * channels + c));
                 ds += dot4(gw, v);
                 if (L == 0) {
                     g0w += hsum4(gw);
@@ -90,14 +102,14 @@ __global__ void __launch_bounds__(kNodeWarps* kWarp)
         y0b = warp_sum(y0b);
         // dL/dy_i = g_i w_i scale - scale^3 * ds * bal_i * y_i / C ; dL/dx_0 = dL/dy_0 - mean_c dL/dy_0
         const float k = scale * scale * scale * ds * inv_c;
-        const float mean_dy0 = (g0w * scale - k * balance_of(0) * y0b) * inv_c;
+        const float mean_dy0 = (g0w * scale - k * balance_of<LMAX>(0) * y0b) * inv_c;
         for (int c = lane * 4; c < channels; c += 128) {
 #pragma unroll
-            for (int L = 0; L < 9; ++L) {
+            for (int L = 0; L < kL; ++L) {
                 float4 v = ld4(xb + L * channels + c);
                 if (L == 0) v = make_float4(v.x - mean0, v.y - mean0, v.z - mean0, v.w - mean0);
-                const float4 gw = mul4(ld4(gb + L * channels + c), ld4(weight + deg_of(L) * channels + c));
-                const float kb = k * balance_of(L);
+                const float4 gw = mul4(ld4(gb + L * channels + c), ld4(weight + degree_of(L) * channels + c));
+                const float kb = k * balance_of<LMAX>(L);
                 float4 d = make_float4(fmaf(gw.x, scale, -kb * v.x), fmaf(gw.y, scale, -kb * v.y), fmaf(gw.z, scale, -kb * v.z),
                                        fmaf(gw.w, scale, -kb * v.w));
                 if (L == 0) d = make_float4(d.x - mean_dy0, d.y - mean_dy0, d.z - mean_dy0, d.w - mean_dy0);
@@ -113,24 +125,45 @@ using namespace fcb200;
 
 extern "C" {
 
-int fcb200_rms_norm_sh_fwd(const float* x, const float* weight, const float* bias, const float* extra, float* out, float* stats,
-                           float eps, int64_t num_nodes, int32_t channels, void* stream) {
+#define FCB_NODE_LAUNCH(kernel, ...)                                                                                          \
+    do {                                                                                                                      \
+        const int grid = warp_grid(num_nodes, kNodeWarps);                                                                    \
+        if (lmax == 2)                                                                                                        \
+            kernel<2><<<grid, kNodeWarps * kWarp, 0, static_cast<cudaStream_t>(stream)>>>(__VA_ARGS__);                       \
+        else if (lmax == 4)                                                                                                   \
+            kernel<4><<<grid, kNodeWarps * kWarp, 0, static_cast<cudaStream_t>(stream)>>>(__VA_ARGS__);                       \
+        else                                                                                                                  \
+            return FCB200_EINVAL;                                                                                             \
+    } while (0)
+
+int fcb200_lx_rms_norm_sh_fwd(const float* x, const float* weight, const float* bias, const float* extra, float* out, float* stats,
+                              float eps, int64_t num_nodes, int32_t channels, int32_t lmax, void* stream) {
     if (!x || !weight || !bias || !out || !stats || num_nodes < 0 || channels <= 0 || channels % 128) return FCB200_EINVAL;
     if (!aligned16(x) || !aligned16(weight) || !aligned16(bias) || !aligned16(out) || (extra && !aligned16(extra))) return FCB200_EALIGN;
+    if (lmax != 2 && lmax != 4) return FCB200_EINVAL;
     if (num_nodes == 0) return FCB200_OK;
-    rms_norm_fwd_kernel<<<warp_grid(num_nodes, kNodeWarps), kNodeWarps * kWarp, 0, static_cast<cudaStream_t>(stream)>>>(
-        x, weight, bias, extra, out, stats, eps, num_nodes, channels);
+    FCB_NODE_LAUNCH(rms_norm_fwd_kernel, x, weight, bias, extra, out, stats, eps, num_nodes, channels);
     return launch_status();
+}
+
+int fcb200_lx_rms_norm_sh_bwd(const float* grad_out, const float* x, const float* weight, const float* stats, float* grad_x,
+                              int64_t num_nodes, int32_t channels, int32_t lmax, void* stream) {
+    if (!grad_out || !x || !weight || !stats || !grad_x || num_nodes < 0 || channels <= 0 || channels % 128) return FCB200_EINVAL;
+    if (!aligned16(grad_out) || !aligned16(x) || !aligned16(weight) || !aligned16(grad_x)) return FCB200_EALIGN;
+    if (lmax != 2 && lmax != 4) return FCB200_EINVAL;
+    if (num_nodes == 0) return FCB200_OK;
+    FCB_NODE_LAUNCH(rms_norm_bwd_kernel, grad_out, x, weight, stats, grad_x, num_nodes, channels);
+    return launch_status();
+}
+
+int fcb200_rms_norm_sh_fwd(const float* x, const float* weight, const float* bias, const float* extra, float* out, float* stats,
+                           float eps, int64_t num_nodes, int32_t channels, void* stream) {
+    return fcb200_lx_rms_norm_sh_fwd(x, weight, bias, extra, out, stats, eps, num_nodes, channels, 2, stream);
 }
 
 int fcb200_rms_norm_sh_bwd(const float* grad_out, const float* x, const float* weight, const float* stats, float* grad_x,
                            int64_t num_nodes, int32_t channels, void* stream) {
-    if (!grad_out || !x || !weight || !stats || !grad_x || num_nodes < 0 || channels <= 0 || channels % 128) return FCB200_EINVAL;
-    if (!aligned16(grad_out) || !aligned16(x) || !aligned16(weight) || !aligned16(grad_x)) return FCB200_EALIGN;
-    if (num_nodes == 0) return FCB200_OK;
-    rms_norm_bwd_kernel<<<warp_grid(num_nodes, kNodeWarps), kNodeWarps * kWarp, 0, static_cast<cudaStream_t>(stream)>>>(
-        grad_out, x, weight, stats, grad_x, num_nodes, channels);
-    return launch_status();
+    return fcb200_lx_rms_norm_sh_bwd(grad_out, x, weight, stats, grad_x, num_nodes, channels, 2, stream);
 }
 
 }  // extern "C"

@@ -21,6 +21,61 @@ NS = "fairchem_b200"
 WIG = 35
 
 
+class SHShape:
+    """Coefficient layouts for one lmax with mmax = 2 (the reference's CoefficientMapping,
+    src/fairchem/core/models/uma/common/so3.py:19-160, restricted to |m| <= 2).
+
+    nl: L-major rows per node; m_size: rows per |m| block (m=0, 1, 2); nm: M-major rows per edge;
+    nw: compact Wigner entries per edge; nrad: radial slots of width 2C; m2l[i]: L-major index of M-major row i;
+    l_of_m[i]: degree of M-major row i."""
+
+    def __init__(self, lmax: int):
+        self.lmax = lmax
+        self.nl = (lmax + 1) ** 2
+        self.m_size = [lmax + 1, lmax, lmax - 1]
+        self.nm = self.m_size[0] + 2 * self.m_size[1] + 2 * self.m_size[2]
+        self.nw = sum((2 * min(l, 2) + 1) * (2 * l + 1) for l in range(lmax + 1))
+        self.nrad = 3 * lmax
+        self.l_of = [l for l in range(lmax + 1) for _ in range(2 * l + 1)]
+        order = [(l, 0) for l in range(lmax + 1)]
+        for m in (1, 2):
+            order += [(l, m) for l in range(m, lmax + 1)] + [(l, -m) for l in range(m, lmax + 1)]
+        self.m2l = [l * l + l + m for l, m in order]
+        self.l_of_m = [l for l, _ in order]
+        self.woff = [sum((2 * min(i, 2) + 1) * (2 * i + 1) for i in range(l)) for l in range(lmax + 2)]
+
+
+SHAPES = {2: SHShape(2), 4: SHShape(4)}
+_BY_NL = {s.nl: s for s in SHAPES.values()}
+_BY_NW = {s.nw: s for s in SHAPES.values()}
+_BY_NM = {s.nm: s for s in SHAPES.values()}
+_BY_GATE = {s.lmax + s.nm: s for s in SHAPES.values()}
+_GENERIC = False
+
+
+def _shape(table: dict, key: int, what: str) -> SHShape:
+    s = table.get(int(key))
+    if s is None:
+        raise _lib.FairchemB200Error(f"{what} = {key} matches neither lmax = 2 nor lmax = 4 (mmax = 2)")
+    return s
+
+
+def set_generic_kernels(flag: bool) -> None:
+    """Route lmax = 2 shapes through the any-lmax kernels too (they are the only ones for lmax = 4)."""
+    global _GENERIC
+    _GENERIC = bool(flag)
+
+
+def uses_transposed_inverse(lmax: int) -> bool:
+    """Layout of the inverse rotation the rotate-back ops expect: the tuned lmax = 2 kernels take the
+    compact entries of D^T (wig[:, transpose index] * envelope); the any-lmax kernels take wig * envelope."""
+    return lmax == 2 and not _GENERIC
+
+
+def _lx(s: SHShape) -> bool:
+    return s.lmax != 2 or _GENERIC
+
+
 class LaunchProfiler:
     """Per-kernel accounting for bench.py: CUDA-event time on the launching stream, launch counts and
     the algorithmic bytes / FLOPs each launch is responsible for.  Install with ``set_profiler``."""
@@ -121,9 +176,16 @@ def gather_rotate_fwd_(x: Tensor, src: Tensor, tgt: Tensor, wig: Tensor, radial:
     _chk(x, src, tgt, wig, radial, out)
     _f32(x, wig, radial, out)
     e, c = src.shape[0], x.shape[2]
-    _launch("gather_rotate_fwd", "fcb200_gather_rotate_fwd",
-            (_p(x), _p(src), _p(tgt), _p(wig), _p(radial), _p(out), e, x.shape[0], c, _stream()),
-            nbytes=e * (4 * (18 * c + 18 * c + WIG + (12 * c if radial is not None else 0)) + 8), flops=e * 2 * WIG * 2 * c)
+    s = _shape(_BY_NL, x.shape[1], "rows per node")
+    nbytes = e * (4 * (2 * s.nl * c + 2 * s.nm * c + s.nw + (2 * s.nrad * c if radial is not None else 0)) + 8)
+    if _lx(s):
+        _launch("gather_rotate_fwd", "fcb200_lx_gather_rotate_fwd",
+                (_p(x), _p(src), _p(tgt), _p(wig), _p(radial), _p(out), e, x.shape[0], c, s.lmax, _stream()),
+                nbytes=nbytes, flops=e * 2 * s.nw * 2 * c)
+    else:
+        _launch("gather_rotate_fwd", "fcb200_gather_rotate_fwd",
+                (_p(x), _p(src), _p(tgt), _p(wig), _p(radial), _p(out), e, x.shape[0], c, _stream()),
+                nbytes=nbytes, flops=e * 2 * s.nw * 2 * c)
 
 
 @_op("gather_rotate_bwd", ("g_src", "g_tgt", "grad_wig", "grad_radial"))
@@ -132,10 +194,15 @@ def gather_rotate_bwd_(grad_out: Tensor, x: Tensor, src: Tensor, tgt: Tensor, wi
     _chk(grad_out, x, src, tgt, wig, radial, g_src, g_tgt, grad_wig, grad_radial)
     _f32(grad_out, x, wig, radial, g_src, g_tgt, grad_wig, grad_radial)
     e, c = src.shape[0], x.shape[2]
-    _launch("gather_rotate_bwd", "fcb200_gather_rotate_bwd",
-            (_p(grad_out), _p(x), _p(src), _p(tgt), _p(wig), _p(radial), _p(g_src), _p(g_tgt), _p(grad_wig), _p(grad_radial), e,
-             x.shape[0], c, _stream()),
-            nbytes=e * (4 * (18 * c * 3 + 2 * WIG + (24 * c if radial is not None else 0)) + 8), flops=e * 6 * WIG * 2 * c)
+    s = _shape(_BY_NL, x.shape[1], "rows per node")
+    nbytes = e * (4 * (2 * s.nm * c + 4 * s.nl * c + 2 * s.nw + (4 * s.nrad * c if radial is not None else 0)) + 8)
+    args = (_p(grad_out), _p(x), _p(src), _p(tgt), _p(wig), _p(radial), _p(g_src), _p(g_tgt), _p(grad_wig), _p(grad_radial), e,
+            x.shape[0], c)
+    if _lx(s):
+        _launch("gather_rotate_bwd", "fcb200_lx_gather_rotate_bwd", args + (s.lmax, _stream()), nbytes=nbytes,
+                flops=e * 6 * s.nw * 2 * c)
+    else:
+        _launch("gather_rotate_bwd", "fcb200_gather_rotate_bwd", args + (_stream(),), nbytes=nbytes, flops=e * 6 * s.nw * 2 * c)
 
 
 @_op("rotate_back_reduce_fwd", ("out",))
@@ -143,9 +210,15 @@ def rotate_back_reduce_fwd_(msg: Tensor, winv: Tensor, row_ptr: Tensor, out: Ten
     _chk(msg, winv, row_ptr, out)
     _f32(msg, winv, out)
     e, n, c = msg.shape[0], out.shape[0], out.shape[2]
-    _launch("rotate_back_reduce_fwd", "fcb200_rotate_back_reduce_fwd",
-            (_p(msg), _p(winv), _p(row_ptr), _p(out), e, n, c, _stream()),
-            nbytes=4 * (e * (9 * c + WIG) + n * (9 * c + 1)), flops=e * 2 * WIG * c)
+    s = _shape(_BY_NL, out.shape[1], "rows per node")
+    nbytes = 4 * (e * (s.nm * c + s.nw) + n * (s.nl * c + 1))
+    args = (_p(msg), _p(winv), _p(row_ptr), _p(out), e, n, c)
+    if _lx(s):
+        _launch("rotate_back_reduce_fwd", "fcb200_lx_rotate_back_reduce_fwd", args + (s.lmax, _stream()), nbytes=nbytes,
+                flops=e * 2 * s.nw * c)
+    else:
+        _launch("rotate_back_reduce_fwd", "fcb200_rotate_back_reduce_fwd", args + (_stream(),), nbytes=nbytes,
+                flops=e * 2 * s.nw * c)
 
 
 @_op("rotate_back_bwd", ("grad_msg", "grad_winv"))
@@ -154,9 +227,13 @@ def rotate_back_bwd_(grad_out: Tensor, msg: Optional[Tensor], winv: Tensor, tgt:
     _chk(grad_out, msg, winv, tgt, grad_msg, grad_winv)
     _f32(grad_out, msg, winv, grad_msg, grad_winv)
     e, c = tgt.shape[0], grad_out.shape[2]
-    _launch("rotate_back_bwd", "fcb200_rotate_back_bwd",
-            (_p(grad_out), _p(msg), _p(winv), _p(tgt), _p(grad_msg), _p(grad_winv), e, grad_out.shape[0], c, _stream()),
-            nbytes=e * 4 * (9 * c * (3 if msg is not None else 2) + 2 * WIG + 1), flops=e * 4 * WIG * c)
+    s = _shape(_BY_NL, grad_out.shape[1], "rows per node")
+    nbytes = e * 4 * (s.nl * c + s.nm * c * (2 if msg is not None else 1) + 2 * s.nw + 1)
+    args = (_p(grad_out), _p(msg), _p(winv), _p(tgt), _p(grad_msg), _p(grad_winv), e, grad_out.shape[0], c)
+    if _lx(s):
+        _launch("rotate_back_bwd", "fcb200_lx_rotate_back_bwd", args + (s.lmax, _stream()), nbytes=nbytes, flops=e * 4 * s.nw * c)
+    else:
+        _launch("rotate_back_bwd", "fcb200_rotate_back_bwd", args + (_stream(),), nbytes=nbytes, flops=e * 4 * s.nw * c)
 
 
 @_op("edge_degree_fwd", ("out",))
@@ -165,9 +242,13 @@ def edge_degree_fwd_(radial3: Tensor, winv: Tensor, row_ptr: Tensor, x_in: Optio
     _chk(radial3, winv, row_ptr, x_in, out)
     _f32(radial3, winv, x_in, out)
     e, n, c = radial3.shape[0], out.shape[0], out.shape[2]
-    _launch("edge_degree_fwd", "fcb200_edge_degree_fwd",
-            (_p(radial3), _p(winv), _p(row_ptr), _p(x_in), _p(out), rescale, e, n, c, _stream()),
-            nbytes=4 * (e * (3 * c + WIG) + n * (18 * c + 1)), flops=e * 2 * 9 * c)
+    s = _shape(_BY_NL, out.shape[1], "rows per node")
+    nbytes = 4 * (e * ((s.lmax + 1) * c + s.nw) + n * (2 * s.nl * c + 1))
+    args = (_p(radial3), _p(winv), _p(row_ptr), _p(x_in), _p(out), rescale, e, n, c)
+    if _lx(s):
+        _launch("edge_degree_fwd", "fcb200_lx_edge_degree_fwd", args + (s.lmax, _stream()), nbytes=nbytes, flops=e * 2 * s.nl * c)
+    else:
+        _launch("edge_degree_fwd", "fcb200_edge_degree_fwd", args + (_stream(),), nbytes=nbytes, flops=e * 2 * s.nl * c)
 
 
 @_op("edge_degree_bwd", ("grad_radial3", "grad_winv"))
@@ -176,9 +257,13 @@ def edge_degree_bwd_(grad_out: Tensor, radial3: Tensor, winv: Tensor, tgt: Tenso
     _chk(grad_out, radial3, winv, tgt, grad_radial3, grad_winv)
     _f32(grad_out, radial3, winv, grad_radial3, grad_winv)
     e, c = tgt.shape[0], grad_out.shape[2]
-    _launch("edge_degree_bwd", "fcb200_edge_degree_bwd",
-            (_p(grad_out), _p(radial3), _p(winv), _p(tgt), _p(grad_radial3), _p(grad_winv), rescale, e, grad_out.shape[0], c,
-             _stream()), nbytes=e * 4 * (9 * c + 6 * c + 2 * WIG + 1), flops=e * 4 * 9 * c)
+    s = _shape(_BY_NL, grad_out.shape[1], "rows per node")
+    nbytes = e * 4 * (s.nl * c + 2 * (s.lmax + 1) * c + 2 * s.nw + 1)
+    args = (_p(grad_out), _p(radial3), _p(winv), _p(tgt), _p(grad_radial3), _p(grad_winv), rescale, e, grad_out.shape[0], c)
+    if _lx(s):
+        _launch("edge_degree_bwd", "fcb200_lx_edge_degree_bwd", args + (s.lmax, _stream()), nbytes=nbytes, flops=e * 4 * s.nl * c)
+    else:
+        _launch("edge_degree_bwd", "fcb200_edge_degree_bwd", args + (_stream(),), nbytes=nbytes, flops=e * 4 * s.nl * c)
 
 
 @_op("segment_sum", ("out",))
@@ -195,16 +280,26 @@ def segment_sum_(rows: Tensor, ptr: Tensor, perm: Optional[Tensor], out_index: O
 def so2_gate_fwd_(y: Tensor, out: Tensor, hidden: int) -> None:
     _chk(y, out)
     _f32(y, out)
-    _launch("so2_gate_fwd", "fcb200_so2_gate_fwd", (_p(y), _p(out), y.shape[0], hidden, _stream()),
-            nbytes=y.shape[0] * 4 * hidden * (11 + 9))
+    s = _shape(_BY_GATE, y.shape[1] // hidden, "gate input rows")
+    nbytes = y.shape[0] * 4 * hidden * (s.lmax + 2 * s.nm)
+    if _lx(s):
+        _launch("so2_gate_fwd", "fcb200_lx_so2_gate_fwd", (_p(y), _p(out), y.shape[0], hidden, s.lmax, _stream()), nbytes=nbytes)
+    else:
+        _launch("so2_gate_fwd", "fcb200_so2_gate_fwd", (_p(y), _p(out), y.shape[0], hidden, _stream()), nbytes=nbytes)
 
 
 @_op("so2_gate_bwd", ("grad_y",))
 def so2_gate_bwd_(grad_out: Tensor, y: Tensor, grad_y: Tensor, hidden: int) -> None:
     _chk(grad_out, y, grad_y)
     _f32(grad_out, y, grad_y)
-    _launch("so2_gate_bwd", "fcb200_so2_gate_bwd", (_p(grad_out), _p(y), _p(grad_y), y.shape[0], hidden, _stream()),
-            nbytes=y.shape[0] * 4 * hidden * (9 + 11 + 11))
+    s = _shape(_BY_GATE, y.shape[1] // hidden, "gate input rows")
+    nbytes = y.shape[0] * 4 * hidden * (2 * s.lmax + 3 * s.nm)
+    if _lx(s):
+        _launch("so2_gate_bwd", "fcb200_lx_so2_gate_bwd", (_p(grad_out), _p(y), _p(grad_y), y.shape[0], hidden, s.lmax, _stream()),
+                nbytes=nbytes)
+    else:
+        _launch("so2_gate_bwd", "fcb200_so2_gate_bwd", (_p(grad_out), _p(y), _p(grad_y), y.shape[0], hidden, _stream()),
+                nbytes=nbytes)
 
 
 @_op("edge_geometry_fwd", ("vec", "dist", "env", "wig", "gauss"))
@@ -215,10 +310,14 @@ def edge_geometry_fwd_(pos: Tensor, src: Tensor, tgt: Tensor, shift: Optional[Te
     _chk(pos, src, tgt, shift, gamma, vec, dist, env, wig, gauss)
     _f32(pos, shift, gamma, vec, dist, env, wig, gauss)
     e = src.shape[0]
-    _launch("edge_geometry_fwd", "fcb200_edge_geometry_fwd",
-            (_p(pos), _p(src), _p(tgt), _p(shift), _p(gamma), _p(vec), _p(dist), _p(env), _p(wig), _p(gauss), cutoff,
-             num_basis, b_start, b_stop, b_width, e, pos.shape[0], _stream()),
-            nbytes=e * 4 * (2 + 6 + 3 + 3 + 2 + WIG + num_basis))
+    s = SHAPES[2] if wig is None else _shape(_BY_NW, wig.shape[1], "compact Wigner entries")
+    args = (_p(pos), _p(src), _p(tgt), _p(shift), _p(gamma), _p(vec), _p(dist), _p(env), _p(wig), _p(gauss), cutoff,
+            num_basis, b_start, b_stop, b_width, e, pos.shape[0])
+    nbytes = e * 4 * (2 + 6 + 3 + 3 + 2 + s.nw + num_basis)
+    if _lx(s):
+        _launch("edge_geometry_fwd", "fcb200_lx_edge_geometry_fwd", args + (s.lmax, _stream()), nbytes=nbytes)
+    else:
+        _launch("edge_geometry_fwd", "fcb200_edge_geometry_fwd", args + (_stream(),), nbytes=nbytes)
 
 
 @_op("edge_geometry_bwd", ("grad_vec",))
@@ -229,10 +328,14 @@ def edge_geometry_bwd_(pos: Tensor, src: Tensor, tgt: Tensor, shift: Optional[Te
     _chk(pos, src, tgt, shift, gamma, grad_wig, grad_env, grad_gauss, grad_dist, grad_vec)
     _f32(pos, shift, gamma, grad_wig, grad_env, grad_gauss, grad_dist, grad_vec)
     e = src.shape[0]
-    _launch("edge_geometry_bwd", "fcb200_edge_geometry_bwd",
-            (_p(pos), _p(src), _p(tgt), _p(shift), _p(gamma), _p(grad_wig), _p(grad_env), _p(grad_gauss), _p(grad_dist),
-             _p(grad_vec), cutoff, num_basis, b_start, b_stop, b_width, e, pos.shape[0], _stream()),
-            nbytes=e * 4 * (2 + 6 + 3 + 3 + 2 + WIG + num_basis))
+    s = SHAPES[2] if grad_wig is None else _shape(_BY_NW, grad_wig.shape[1], "compact Wigner entries")
+    args = (_p(pos), _p(src), _p(tgt), _p(shift), _p(gamma), _p(grad_wig), _p(grad_env), _p(grad_gauss), _p(grad_dist),
+            _p(grad_vec), cutoff, num_basis, b_start, b_stop, b_width, e, pos.shape[0])
+    nbytes = e * 4 * (2 + 6 + 3 + 3 + 2 + s.nw + num_basis)
+    if _lx(s):
+        _launch("edge_geometry_bwd", "fcb200_lx_edge_geometry_bwd", args + (s.lmax, _stream()), nbytes=nbytes)
+    else:
+        _launch("edge_geometry_bwd", "fcb200_edge_geometry_bwd", args + (_stream(),), nbytes=nbytes)
 
 
 @_op("radial_act_fwd", ("out", "stats"))
@@ -263,18 +366,21 @@ def rms_norm_sh_fwd_(x: Tensor, weight: Tensor, bias: Tensor, extra: Optional[Te
                      eps: float) -> None:
     _chk(x, weight, bias, extra, out, stats)
     _f32(x, weight, bias, extra, out, stats)
-    n, _, c = x.shape
-    _launch("rms_norm_sh_fwd", "fcb200_rms_norm_sh_fwd",
-            (_p(x), _p(weight), _p(bias), _p(extra), _p(out), _p(stats), eps, n, c, _stream()), nbytes=n * 4 * (18 * c + 2))
+    n, nl, c = x.shape
+    s = _shape(_BY_NL, nl, "rows per node")
+    _launch("rms_norm_sh_fwd", "fcb200_lx_rms_norm_sh_fwd",
+            (_p(x), _p(weight), _p(bias), _p(extra), _p(out), _p(stats), eps, n, c, s.lmax, _stream()),
+            nbytes=n * 4 * (2 * nl * c + 2))
 
 
 @_op("rms_norm_sh_bwd", ("grad_x",))
 def rms_norm_sh_bwd_(grad_out: Tensor, x: Tensor, weight: Tensor, stats: Tensor, grad_x: Tensor) -> None:
     _chk(grad_out, x, weight, stats, grad_x)
     _f32(grad_out, x, weight, stats, grad_x)
-    n, _, c = x.shape
-    _launch("rms_norm_sh_bwd", "fcb200_rms_norm_sh_bwd",
-            (_p(grad_out), _p(x), _p(weight), _p(stats), _p(grad_x), n, c, _stream()), nbytes=n * 4 * (27 * c + 2))
+    n, nl, c = x.shape
+    s = _shape(_BY_NL, nl, "rows per node")
+    _launch("rms_norm_sh_bwd", "fcb200_lx_rms_norm_sh_bwd",
+            (_p(grad_out), _p(x), _p(weight), _p(stats), _p(grad_x), n, c, s.lmax, _stream()), nbytes=n * 4 * (3 * nl * c + 2))
 
 
 @_op("gemm_tf32", ("c", "status"))
@@ -367,14 +473,14 @@ def segment_sum(rows: Tensor, ptr: Tensor, perm: Optional[Tensor], num_segments:
 
 
 class GatherRotate(torch.autograd.Function):
-    """x [N,9,C], wig [E,35], radial [E,12C] or None -> M-major edge rows [E,9,2C]."""
+    """x [N,NL,C], wig [E,NW], radial [E,NRAD*2C] or None -> M-major edge rows [E,NM,2C] (9/35/6/9 for lmax 2)."""
 
     @staticmethod
     def forward(ctx, x, wig, radial, graph: EdgeGraph):
         e, c = graph.num_edges, x.shape[2]
         x, wig = x.contiguous(), wig.contiguous()
         radial = None if radial is None else radial.contiguous()
-        out = torch.empty(e, 9, 2 * c, dtype=x.dtype, device=x.device)
+        out = torch.empty(e, _shape(_BY_NL, x.shape[1], "rows per node").nm, 2 * c, dtype=x.dtype, device=x.device)
         gather_rotate_fwd_.raw(x, graph.src, graph.tgt, wig, radial, out)
         ctx.save_for_backward(x, wig, radial)
         ctx.graph = graph
@@ -385,9 +491,9 @@ class GatherRotate(torch.autograd.Function):
         x, wig, radial = ctx.saved_tensors
         g = ctx.graph
         e, c = g.num_edges, x.shape[2]
-        g_src = torch.empty(e, 9, c, dtype=x.dtype, device=x.device)
-        g_tgt = torch.empty(e, 9, c, dtype=x.dtype, device=x.device)
-        grad_wig = torch.empty(e, WIG, dtype=x.dtype, device=x.device)
+        g_src = torch.empty(e, x.shape[1], c, dtype=x.dtype, device=x.device)
+        g_tgt = torch.empty(e, x.shape[1], c, dtype=x.dtype, device=x.device)
+        grad_wig = torch.empty_like(wig)
         grad_radial = None if radial is None else torch.empty_like(radial)
         gather_rotate_bwd_.raw(grad_out.contiguous(), x, g.src, g.tgt, wig, radial, g_src, g_tgt, grad_wig, grad_radial)
         grad_x = torch.empty_like(x)
@@ -400,12 +506,13 @@ class GatherRotate(torch.autograd.Function):
 
 
 class RotateBackReduce(torch.autograd.Function):
-    """msg [E,9,C] (M-major), winv [E,35] -> out [num_targets,9,C]."""
+    """msg [E,NM,C] (M-major), winv [E,NW] -> out [num_targets,NL,C]."""
 
     @staticmethod
     def forward(ctx, msg, winv, graph: EdgeGraph):
         msg, winv = msg.contiguous(), winv.contiguous()
-        out = torch.empty(graph.num_targets, 9, msg.shape[2], dtype=msg.dtype, device=msg.device)
+        nl = _shape(_BY_NM, msg.shape[1], "rows per edge").nl
+        out = torch.empty(graph.num_targets, nl, msg.shape[2], dtype=msg.dtype, device=msg.device)
         rotate_back_reduce_fwd_.raw(msg, winv, graph.row_ptr, out)
         ctx.save_for_backward(msg, winv)
         ctx.graph = graph
@@ -422,7 +529,7 @@ class RotateBackReduce(torch.autograd.Function):
 
 
 class EdgeDegree(torch.autograd.Function):
-    """x [N,9,C] + segment_sum_tgt(Winv[:, m0 cols] @ radial3 [E,3,C]) / rescale."""
+    """x [N,NL,C] + segment_sum_tgt(Winv[:, m0 cols] @ radial3 [E,lmax+1,C]) / rescale."""
 
     @staticmethod
     def forward(ctx, x, radial3, winv, graph: EdgeGraph, rescale: float):
@@ -445,37 +552,38 @@ class EdgeDegree(torch.autograd.Function):
 
 
 class SO2Gate(torch.autograd.Function):
-    """Gate activation: y [E,11H] = [gate scalars 2H | 9 M-major rows] -> [E,9,H]."""
+    """Gate activation: y [E,(lmax+NM)H] = [gate scalars lmax*H | NM M-major rows] -> [E,NM,H]."""
 
     @staticmethod
-    def forward(ctx, y):
+    def forward(ctx, y, hidden: int):
         y = y.contiguous()
-        h = y.shape[1] // 11
-        out = torch.empty(y.shape[0], 9, h, dtype=y.dtype, device=y.device)
-        so2_gate_fwd_.raw(y, out, h)
+        s = _shape(_BY_GATE, y.shape[1] // hidden, "gate input rows")
+        out = torch.empty(y.shape[0], s.nm, hidden, dtype=y.dtype, device=y.device)
+        so2_gate_fwd_.raw(y, out, hidden)
         ctx.save_for_backward(y)
+        ctx.hidden = hidden
         return out
 
     @staticmethod
     def backward(ctx, grad_out):
         (y,) = ctx.saved_tensors
         grad_y = torch.empty_like(y)
-        so2_gate_bwd_.raw(grad_out.contiguous(), y, grad_y, y.shape[1] // 11)
-        return grad_y
+        so2_gate_bwd_.raw(grad_out.contiguous(), y, grad_y, ctx.hidden)
+        return grad_y, None
 
 
 class EdgeGeometry(torch.autograd.Function):
-    """pos [N,3] -> (vec [E,3], dist [E], env [E], wig [E,35], gauss [E,nb]); differentiable in pos."""
+    """pos [N,3] -> (vec [E,3], dist [E], env [E], wig [E,NW], gauss [E,nb]); differentiable in pos."""
 
     @staticmethod
     def forward(ctx, pos, shift, gamma, graph: EdgeGraph, cutoff: float, num_basis: int, b_start: float,
-                b_stop: float, b_width: float):
+                b_stop: float, b_width: float, lmax: int = 2):
         pos = pos.contiguous()
         e, dev = graph.num_edges, pos.device
         vec = torch.empty(e, 3, dtype=pos.dtype, device=dev)
         dist = torch.empty(e, dtype=pos.dtype, device=dev)
         env = torch.empty(e, dtype=pos.dtype, device=dev)
-        wig = torch.empty(e, WIG, dtype=pos.dtype, device=dev)
+        wig = torch.empty(e, SHAPES[lmax].nw, dtype=pos.dtype, device=dev)
         gauss = torch.empty(e, num_basis, dtype=pos.dtype, device=dev)
         shift = None if shift is None else shift.contiguous()
         gamma = None if gamma is None else gamma.contiguous()
@@ -502,7 +610,7 @@ class EdgeGeometry(torch.autograd.Function):
         nt = g.num_targets
         segment_sum(grad_vec, g.row_ptr, None, nt, out=grad_pos if nt == pos.shape[0] else grad_pos[:nt],
                     accumulate=True, scale=-1.0)
-        return grad_pos, None, None, None, None, None, None, None, None
+        return grad_pos, None, None, None, None, None, None, None, None, None
 
 
 class RadialAct(torch.autograd.Function):
@@ -528,7 +636,7 @@ class RadialAct(torch.autograd.Function):
 
 
 class RMSNormSH(torch.autograd.Function):
-    """Degree-balanced RMS norm of [N,9,C] node features (+ optional per-node vector on row 0); differentiable in x."""
+    """Degree-balanced RMS norm of [N,NL,C] node features (+ optional per-node vector on row 0); differentiable in x."""
 
     @staticmethod
     def forward(ctx, x, weight, bias, extra, eps: float):

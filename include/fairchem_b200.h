@@ -302,6 +302,80 @@ int fcb200_gemm_tf32(const float* a, int64_t lda, const float* w, const float* w
  */
 int fcb200_split_tf32(const float* w, float* w_hi, float* w_lo, int64_t count, void* stream);
 
+/* ---------------------------------------------------------------- any lmax with mmax = 2 (lmax = 2 or 4) */
+
+/*
+ * The `fcb200_lx_*` family is the same set of operations for the 10-layer lmax = 4, mmax = 2
+ * configuration of the backbone (src/fairchem/core/models/uma/escn_md.py:76-160 with lmax=4, mmax=2;
+ * coefficient selection as CoefficientMapping, src/fairchem/core/models/uma/common/so3.py:19-160); `lmax` is
+ * 2 or 4 (FCB200_EINVAL otherwise).  With NL = (lmax+1)^2, NM = sum_l min(2l+1, 5) (9 / 19):
+ *   - node features [N, NL, C] L-major; edge features [E, NM, w] M-major
+ *     (m=0: l=0..lmax | m=+1: l=1.. | m=-1 | m=+2: l=2.. | m=-2);
+ *   - compact Wigner [E, NW], NW = FCB200_WIG (35) / FCB200_WIG_L4 (115): block l stores the rows
+ *     m = -min(l,2)..min(l,2) of D^l, each with its 2l+1 columns, row-major, blocks in order of l
+ *     (for lmax = 2 this is the layout described at the top of this file);
+ *   - the inverse rotation is passed in the SAME layout (entry (l,m,m') of D times the envelope), not
+ *     transposed: D is orthogonal, so the kernels read D^-1[m',m] = D[m,m'];
+ *   - radial weights [E, 3*lmax * 2C]: slots of width 2C, (lmax+1) for m=0 (l=0..), lmax for |m|=1
+ *     (l=1.., shared by +1 and -1), lmax-1 for |m|=2;
+ *   - gate input y [E, (lmax + NM) H] = [lmax gate scalars (degree 1..lmax) | NM rows].
+ * Argument meaning otherwise follows the entry point of the same name without `lx_`.
+ */
+#define FCB200_WIG_L4 115
+
+int fcb200_lx_gather_rotate_fwd(const float* x, const int32_t* src, const int32_t* tgt, const float* wig,
+                                const float* radial, float* out, int64_t num_edges, int64_t num_nodes,
+                                int32_t channels, int32_t lmax, void* stream);
+
+int fcb200_lx_gather_rotate_bwd(const float* grad_out, const float* x, const int32_t* src, const int32_t* tgt,
+                                const float* wig, const float* radial, float* g_src, float* g_tgt, float* grad_wig,
+                                float* grad_radial, int64_t num_edges, int64_t num_nodes, int32_t channels,
+                                int32_t lmax, void* stream);
+
+int fcb200_lx_rotate_back_reduce_fwd(const float* msg, const float* winv, const int32_t* row_ptr, float* out,
+                                     int64_t num_edges, int64_t num_nodes, int32_t channels, int32_t lmax,
+                                     void* stream);
+
+/* radial0 [E, lmax+1, C]: the m = 0 rows of the edge-degree embedding (nn/embedding.py:77-94) */
+int fcb200_lx_edge_degree_fwd(const float* radial0, const float* winv, const int32_t* row_ptr, const float* x_in,
+                              float* out, float rescale, int64_t num_edges, int64_t num_nodes, int32_t channels,
+                              int32_t lmax, void* stream);
+
+int fcb200_lx_rotate_back_bwd(const float* grad_out, const float* msg, const float* winv, const int32_t* tgt,
+                              float* grad_msg, float* grad_winv, int64_t num_edges, int64_t num_nodes,
+                              int32_t channels, int32_t lmax, void* stream);
+
+int fcb200_lx_edge_degree_bwd(const float* grad_out, const float* radial0, const float* winv, const int32_t* tgt,
+                              float* grad_radial0, float* grad_winv, float rescale, int64_t num_edges,
+                              int64_t num_nodes, int32_t channels, int32_t lmax, void* stream);
+
+int fcb200_lx_so2_gate_fwd(const float* y, float* out, int64_t num_edges, int32_t hidden, int32_t lmax, void* stream);
+
+int fcb200_lx_so2_gate_bwd(const float* grad_out, const float* y, float* grad_y, int64_t num_edges, int32_t hidden,
+                           int32_t lmax, void* stream);
+
+int fcb200_lx_rms_norm_sh_fwd(const float* x, const float* weight, const float* bias, const float* extra, float* out,
+                              float* stats, float eps, int64_t num_nodes, int32_t channels, int32_t lmax, void* stream);
+
+int fcb200_lx_rms_norm_sh_bwd(const float* grad_out, const float* x, const float* weight, const float* stats,
+                              float* grad_x, int64_t num_nodes, int32_t channels, int32_t lmax, void* stream);
+
+/*
+ * Edge geometry with the compact Wigner-D of the given lmax [E, NW].  Degrees 3 and 4 follow from the
+ * degree-1 and degree-(l-1) blocks by the recursion of Ivanic and Ruedenberg; the reference evaluates the
+ * same matrices as polynomials of the quaternion (src/fairchem/core/models/uma/common/wigner_d_custom_kernels.py:196-356).
+ */
+int fcb200_lx_edge_geometry_fwd(const float* pos, const int32_t* src, const int32_t* tgt, const float* shift,
+                                const float* gamma, float* vec, float* dist, float* env, float* wig, float* gauss,
+                                float cutoff, int32_t num_basis, float basis_start, float basis_stop,
+                                float basis_width, int64_t num_edges, int64_t num_nodes, int32_t lmax, void* stream);
+
+int fcb200_lx_edge_geometry_bwd(const float* pos, const int32_t* src, const int32_t* tgt, const float* shift,
+                                const float* gamma, const float* grad_wig, const float* grad_env,
+                                const float* grad_gauss, const float* grad_dist, float* grad_vec, float cutoff,
+                                int32_t num_basis, float basis_start, float basis_stop, float basis_width,
+                                int64_t num_edges, int64_t num_nodes, int32_t lmax, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

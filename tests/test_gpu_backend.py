@@ -33,8 +33,10 @@ def test_op_table_matches_reference_outputs(backend, golden, shuffle):
     d_inv_env = d.transpose(1, 2).contiguous() * env.view(-1, 1, 1)
     w, winv = backend.prepare_wigner(d, d_inv_env, None, None)
     backend.validate(2, 2, None)
-    with pytest.raises(ValueError):
-        backend.validate(4, 2, None)
+    backend.validate(4, 2, None)
+    for bad in ((3, 2), (4, 4), (2, 1)):
+        with pytest.raises(ValueError):
+            backend.validate(*bad, None)
 
     msg = backend.node_to_edge_wigner_permute(x, ei, w)
     torch.testing.assert_close(msg, msg_ref, **TOL)

@@ -195,7 +195,7 @@ def test_gate_activation_forward_backward(ops):
     e, h = 130, 128
     y = torch.randn(e, 11 * h, generator=g).cuda()
     a = y.clone().requires_grad_(True)
-    out = ops.SO2Gate.apply(a)
+    out = ops.SO2Gate.apply(a, h)
     b = y.double().requires_grad_(True)
     ref = O.gate_activation(b[:, :2 * h], b[:, 2 * h:].reshape(e, 9, h), [0, 1, 0, 1, 0, 1, 1, 1], 2)
     torch.testing.assert_close(out, ref.float(), rtol=1e-5, atol=1e-5)
