@@ -144,8 +144,9 @@ def run_b200(args):
 
         dist.init_process_group("nccl", device_id=dev)
     B.set_gemm_precision(args.precision)
-    sd = weights.random_init_state_dict(weights.UMA_S, args.seed)
-    bb, head = B.build_model(weights.UMA_S, sd, device=dev, edge_chunk_size=args.chunk)
+    cfg, model_name = MODELS[args.model]
+    sd = weights.random_init_state_dict(cfg, args.seed)
+    bb, head = B.build_model(cfg, sd, device=dev, edge_chunk_size=args.chunk)
     host = synthetic.WORKLOADS[args.workload](args.seed)
     n_atoms = int(host["pos"].shape[0])
     if world > 1:
@@ -272,7 +273,7 @@ def run_b200(args):
         "metric": "atom_steps_per_s", "value": n_atoms * args.steps / (ms * 1e-3), "unit": "atom-steps/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
         "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "atoms": n_atoms, "edges": edges, "model": "UMA-s shape (4 layers, C=128, lmax=mmax=2)",
+        "config": {"workload": args.workload, "atoms": n_atoms, "edges": edges, "model": model_name,
                    "cutoff": 6.0, "max_neighbors": 30, "gemm_precision": {3: "tf32x3", 1: "tf32", 0: "cublas_fp32"}[args.precision],
                    "edge_chunk": args.chunk, "l2": "inputs larger than L2 (node and edge arrays of 0.4-2 GB per pass)",
                    "parallelism": f"gp{world}"},
@@ -292,6 +293,24 @@ def run_b200(args):
     _emit(line)
 
 
+MODELS = {
+    "uma_s": (weights.UMA_S, "UMA-s shape (4 layers, C=128, lmax=mmax=2)"),
+    "escn_md_l4": (weights.ESCN_MD_L4, "eSCN-MD shape (10 layers, C=128, lmax=4, mmax=2)"),
+}
+
+
+def _cpu_sample(args):
+    """A bounded sample of the workload for the host: the same material at the same density with fewer atoms."""
+    if args.workload.startswith("water"):
+        return (synthetic.water_box(CPU_SAMPLE_ATOMS, seed=args.seed),
+                f"{CPU_SAMPLE_ATOMS}-atom water box of the same density (graph + energy + forces)")
+    if args.workload == "fcc_cu_20000":
+        cells = (6, 6, 6) if args.model == "escn_md_l4" else (7, 7, 7)
+        d = synthetic.fcc_cu(cells, seed=args.seed)
+        return d, f"{int(d['pos'].shape[0])}-atom FCC Cu supercell of the same lattice (graph + energy + forces)"
+    return synthetic.WORKLOADS[args.workload](args.seed), f"full {args.workload}"
+
+
 def cpu_baseline(args, quiet=False):
     """The CPU oracle on a bounded sample of the workload: a box of the same density with fewer atoms."""
     from oracle import escn_md_oracle as oracle_model
@@ -299,20 +318,16 @@ def cpu_baseline(args, quiet=False):
 
     threads = os.cpu_count() or 1
     torch.set_num_threads(threads)
-    if args.workload.startswith("water"):
-        sample = synthetic.water_box(CPU_SAMPLE_ATOMS, seed=args.seed)
-        what = f"{CPU_SAMPLE_ATOMS}-atom water box of the same density (graph + energy + forces)"
-    else:
-        sample = synthetic.WORKLOADS[args.workload](args.seed)
-        what = f"full {args.workload}"
-    sd = weights.random_init_state_dict(weights.UMA_S, args.seed)
+    sample, what = _cpu_sample(args)
+    cfg = MODELS[args.model][0]
+    sd = weights.random_init_state_dict(cfg, args.seed)
     times = []
     reps = max(1, min(args.steps, 3))
     for i in range(reps + 1):
         t = time.perf_counter()
         ei, co, _, _ = oracle_graph.radius_graph(sample.pos.numpy(), sample.cell.numpy(), sample.pbc.numpy(),
                                                  sample.natoms.numpy(), 6.0, 30)
-        oracle_model.energy_and_forces(sd, weights.UMA_S, sample, torch.from_numpy(ei), torch.from_numpy(co))
+        oracle_model.energy_and_forces(sd, cfg, sample, torch.from_numpy(ei), torch.from_numpy(co))
         if i:  # the first pass warms the allocator and thread pool
             times.append(time.perf_counter() - t)
     sec = statistics.median(times)
@@ -326,13 +341,13 @@ def run_reference(args):
     if rank != 0:
         return
     cpu = cpu_baseline(args)
-    n = CPU_SAMPLE_ATOMS if args.workload.startswith("water") else int(synthetic.WORKLOADS[args.workload](args.seed)["pos"].shape[0])
+    n = int(_cpu_sample(args)[0]["pos"].shape[0])
     line = {
         "impl": "reference", "metric": "atom_steps_per_s", "value": cpu["value"], "unit": "atom-steps/s",
         "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": cpu["s_per_step"] * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
-        "config": {"workload": args.workload, "sample_atoms": n, "model": "UMA-s shape (4 layers, C=128, lmax=mmax=2)"},
+        "config": {"workload": args.workload, "sample_atoms": n, "model": MODELS[args.model][1]},
         "cpu_baseline": cpu,
         "e2e": {"value": cpu["value"], "unit": "atom-steps/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -368,6 +383,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="water_100k", choices=sorted(synthetic.WORKLOADS))
+    ap.add_argument("--model", default="uma_s", choices=sorted(MODELS),
+                    help="uma_s: the configuration the metric is quoted on; escn_md_l4: the 10-layer lmax=4/mmax=2 shape")
     ap.add_argument("--precision", type=int, default=3, choices=[0, 1, 3])
     ap.add_argument("--chunk", type=int, default=131072)
     ap.add_argument("--seed", type=int, default=0)
