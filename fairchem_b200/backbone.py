@@ -19,6 +19,7 @@ per-element tables (``embedding @ W^T``), which removes the [E,320] edge-feature
 
 from __future__ import annotations
 
+import contextlib
 import math
 from dataclasses import dataclass
 from typing import Optional
@@ -161,8 +162,9 @@ class _SO3LinearFn(torch.autograd.Function):
         gy = gy.contiguous()
         n, rows, _ = gy.shape
         gx = torch.empty(n, rows, ctx.cin, dtype=gy.dtype, device=gy.device)
-        for i in range(rows):
-            _gemm(gy[:, i, :], _transposed(ctx.weight[_L_OF[i]]), None, gx[:, i, :], ctx.p)
+        with _GradScale.ensure(gy):
+            for i in range(rows):
+                _gemm(gy[:, i, :], _transposed(ctx.weight[_L_OF[i]]), None, gx[:, i, :], ctx.p, grad=gy)
         return gx, None, None
 
 
@@ -329,19 +331,23 @@ class _EdgeCtx:
 
 class _GemmState:
     """How the dense contractions run: 3 = tcgen05 TF32 with the hi/lo split (float32-level accuracy,
-    default), 1 = single-pass tcgen05 TF32 (the counterpart of the reference's ``tf32`` inference
-    setting, src/fairchem/core/units/mlip_unit/api/inference.py:123-226), 0 = cuBLAS float32 through
-    torch (kept for A/B measurements only)."""
+    default), 2 = tcgen05 half-precision hi/lo split (float32-level accuracy at twice the TF32 issue rate;
+    operands must fit the half range after a power-of-two scale), 1 = single-pass tcgen05 TF32 (the
+    counterpart of the reference's ``tf32`` inference setting,
+    src/fairchem/core/units/mlip_unit/api/inference.py:123-226), 0 = cuBLAS float32 through torch (kept
+    for A/B measurements only)."""
 
     precision = 3
-    status = None          # device int32 raised by the kernel when a bounded wait expires
+    status = None          # device int32 raised by the kernel when a bounded wait expires or a value leaves the half range
     transposed = {}        # (ptr, shape, stride) of a weight view -> (weight ref, transposed contiguous copy)
     split = {}             # same key -> (weight ref, TF32 high part, TF32 low part)
+    split16 = {}           # same key -> (weight ref, half high part, half low part, scale)
+    a_scale = None         # precision 2: one-element device tensor, the power of two A operands are scaled by (None = 1)
 
 
 def set_gemm_precision(p: int) -> None:
-    if p not in (0, 1, 3):
-        raise ValueError("gemm precision must be 3 (TF32 x3), 1 (TF32) or 0 (cuBLAS float32)")
+    if p not in (0, 1, 2, 3):
+        raise ValueError("gemm precision must be 3 (TF32 x3), 2 (half x3), 1 (TF32) or 0 (cuBLAS float32)")
     _GemmState.precision = p
 
 
@@ -354,7 +360,8 @@ def _status(device):
 def check_gemm_status() -> None:
     if _GemmState.status is not None and int(_GemmState.status.item()) != 0:
         _GemmState.status.zero_()
-        raise RuntimeError("fcb200_gemm_tf32: a bounded wait expired inside the kernel; results are invalid")
+        raise RuntimeError("tcgen05 GEMM: a bounded wait expired inside the kernel, or an operand left the half range "
+                           "(precision 2); results are invalid")
 
 
 def _transposed(w: torch.Tensor) -> torch.Tensor:
@@ -376,10 +383,59 @@ def _split(w: torch.Tensor):
     return hit[1], hit[2]
 
 
-def _gemm(x2, w, bias, y, precision):
+def _split16(w: torch.Tensor):
+    key = (w.data_ptr(), tuple(w.shape), tuple(w.stride()))
+    hit = _GemmState.split16.get(key)
+    if hit is None or hit[0]._version != w._version:
+        hit = (w,) + ops.split_f16(w)
+        _GemmState.split16[key] = hit
+    return hit[1], hit[2], hit[3]
+
+
+def _pow2_scale(magnitude: torch.Tensor) -> torch.Tensor:
+    """One-element device tensor: the power of two that maps ``magnitude`` to [2^6, 2^7)."""
+    return torch.exp2(torch.floor(6.0 - torch.log2(magnitude.float().clamp_min(1e-30)))).reshape(1).contiguous()
+
+
+class _GradScale:
+    """Precision 2: gradients are usually far below the half range, so the backward contractions issued inside
+    the block scale their A operand by the power of two that maps ``magnitude`` (a device scalar: the largest
+    incoming gradient of the block) to about 2^6; 2^9 of headroom remain above it and values down to 2^-20
+    of it stay normal halves."""
+
+    def __init__(self, magnitude: torch.Tensor):
+        self.scale = _pow2_scale(magnitude) if _GemmState.precision == 2 else None
+
+    @staticmethod
+    def ensure(grad: torch.Tensor):
+        """The enclosing scale if there is one, else one derived from ``grad`` itself."""
+        if _GemmState.precision != 2 or _GemmState.a_scale is not None:
+            return contextlib.nullcontext()
+        return _GradScale(grad.abs().amax())
+
+    def __enter__(self):
+        self.saved = _GemmState.a_scale
+        _GemmState.a_scale = self.scale
+        return self
+
+    def __exit__(self, *exc):
+        _GemmState.a_scale = self.saved
+        return False
+
+
+def _gemm(x2, w, bias, y, precision, grad=None):
+    """y = x2 @ w^T + bias.  ``grad`` marks a backward contraction (x2 is a gradient, w a transposed weight)
+    and names the full gradient tensor x2 is a view of: in precision 2 such operands are scaled into the half
+    range by the enclosing _GradScale, or by their own largest magnitude when there is none."""
     if precision == 0:  # cuBLAS float32 through torch, for A/B measurements only
         y.copy_(F.linear(x2, w, bias))
-    elif precision == 3:
+    elif precision == 2 and w.shape[1] % 8 == 0:
+        hi, lo, sc = _split16(w)
+        a_scale = None
+        if grad is not None:
+            a_scale = _GemmState.a_scale if _GemmState.a_scale is not None else _pow2_scale(grad.abs().amax())
+        ops.gemm_f16x2_.raw(x2, hi, lo, sc, a_scale, bias, y, _status(x2.device))
+    elif precision >= 2:
         hi, lo = _split(w)
         ops.gemm_tf32_.raw(x2, hi, lo, bias, y, 3, _status(x2.device))
     else:
@@ -401,7 +457,7 @@ class _LinearTF32(torch.autograd.Function):
     def backward(ctx, gy):
         gy = gy if gy.stride(-1) == 1 and gy.stride(0) % 4 == 0 else gy.contiguous()
         gx = torch.empty(gy.shape[0], ctx.w.shape[1], dtype=gy.dtype, device=gy.device)
-        _gemm(gy, _transposed(ctx.w), None, gx, ctx.precision)
+        _gemm(gy, _transposed(ctx.w), None, gx, ctx.precision, grad=gy)
         return gx, None, None, None
 
 
@@ -465,9 +521,9 @@ class _SO2Conv(torch.autograd.Function):
         n0, n1 = w0.shape[0], w1.shape[0]
         k0, k1, k2 = w0.shape[1], w1.shape[1], w2.shape[1]
         gx = torch.empty(gy.shape[0], k0 + k1 + k2, dtype=gy.dtype, device=gy.device)
-        _gemm(gy[:, :n0], _transposed(w0), None, gx[:, :k0], p)
-        _gemm(gy[:, n0: n0 + n1], _transposed(w1), None, gx[:, k0: k0 + k1], p)
-        _gemm(gy[:, n0 + n1:], _transposed(w2), None, gx[:, k0 + k1:], p)
+        _gemm(gy[:, :n0], _transposed(w0), None, gx[:, :k0], p, grad=gy)
+        _gemm(gy[:, n0: n0 + n1], _transposed(w1), None, gx[:, k0: k0 + k1], p, grad=gy)
+        _gemm(gy[:, n0 + n1:], _transposed(w2), None, gx[:, k0 + k1:], p, grad=gy)
         return gx, None, None
 
 
@@ -499,9 +555,9 @@ def _so2_conv_input_grad(conv: "SO2Convolution", gy, cin: int):
     gy = gy.contiguous()
     k0, k1, k2 = w0.shape[1], w1.shape[1], w2.shape[1]
     gx = torch.empty(gy.shape[0], k0 + k1 + k2, dtype=gy.dtype, device=gy.device)
-    _gemm(gy[:, :n0], _transposed(w0), None, gx[:, :k0], p)
-    _gemm(gy[:, n0: n0 + n1], _transposed(w1), None, gx[:, k0: k0 + k1], p)
-    _gemm(gy[:, n0 + n1:], _transposed(w2), None, gx[:, k0 + k1:], p)
+    _gemm(gy[:, :n0], _transposed(w0), None, gx[:, :k0], p, grad=gy)
+    _gemm(gy[:, n0: n0 + n1], _transposed(w1), None, gx[:, k0: k0 + k1], p, grad=gy)
+    _gemm(gy[:, n0 + n1:], _transposed(w2), None, gx[:, k0 + k1:], p, grad=gy)
     return gx
 
 
@@ -550,6 +606,13 @@ class _EdgeBlockFn(torch.autograd.Function):
         ggauss = torch.empty_like(gauss)
         kept = ctx.kept
         ctx.kept = None
+        with _GradScale(grad_out.abs().amax()):
+            return _EdgeBlockFn._backward_chunks(ctx, x, wig, winv, gauss, grad_out, gx, gwig, gwinv, ggauss, kept, nl, nm, c)
+
+    @staticmethod
+    def _backward_chunks(ctx, x, wig, winv, gauss, grad_out, gx, gwig, gwinv, ggauss, kept, nl, nm, c):
+        ew, tables, ectx, nb = ctx.ew, ctx.tables, ctx.ectx, ctx.nb
+        g = ectx.graph
         for ci, ch in enumerate(ectx.chunks):
             sl = slice(ch.e0, ch.e1)
             ec = ch.e1 - ch.e0
@@ -627,15 +690,16 @@ class _EdgeDegreeFn(torch.autograd.Function):
         grad_out = grad_out.contiguous()
         gwinv = torch.empty_like(winv)
         ggauss = torch.empty_like(gauss)
-        for ch in ectx.chunks:
-            sl = slice(ch.e0, ch.e1)
-            with torch.enable_grad():
-                g_c = gauss[sl].detach().requires_grad_(True)
-                r3 = _radial(ctx.rad_func, ctx.tables, g_c, ectx.z_src[sl], ectx.z_tgt[sl], nb)
-            gr = torch.empty_like(r3)
-            ops.edge_degree_bwd_.raw(grad_out, r3.detach(), winv[sl], g.tgt[sl], gr, gwinv[sl], ctx.rescale)
-            (gg,) = torch.autograd.grad(r3, g_c, gr)
-            ggauss[sl] = gg
+        with _GradScale(grad_out.abs().amax()):
+            for ch in ectx.chunks:
+                sl = slice(ch.e0, ch.e1)
+                with torch.enable_grad():
+                    g_c = gauss[sl].detach().requires_grad_(True)
+                    r3 = _radial(ctx.rad_func, ctx.tables, g_c, ectx.z_src[sl], ectx.z_tgt[sl], nb)
+                gr = torch.empty_like(r3)
+                ops.edge_degree_bwd_.raw(grad_out, r3.detach(), winv[sl], g.tgt[sl], gr, gwinv[sl], ctx.rescale)
+                (gg,) = torch.autograd.grad(r3, g_c, gr)
+                ggauss[sl] = gg
         return grad_out, gwinv, ggauss, None, None, None, None, None
 
 

@@ -9,6 +9,7 @@ library; there is no CPU implementation.
 
 from __future__ import annotations
 
+import math
 from ctypes import c_void_p
 from typing import Optional
 
@@ -398,6 +399,39 @@ def gemm_tf32_(a: Tensor, w: Tensor, w_lo: Optional[Tensor], bias: Optional[Tens
     _launch("gemm_tf32", "fcb200_gemm_tf32",
             (_p(a), a.stride(0), _p(w), _p(w_lo), w.stride(0), _p(bias), _p(c), c.stride(0), m, n, k, precision, _p(status),
              _stream()), nbytes=4 * (m * k + n * k + m * n), flops=2 * m * n * k)
+
+
+@_op("gemm_f16x2", ("c", "status"))
+def gemm_f16x2_(a: Tensor, w_hi: Tensor, w_lo: Tensor, w_scale: float, a_scale: Optional[Tensor], bias: Optional[Tensor],
+                c: Tensor, status: Tensor) -> None:
+    """c[M,N] = a[M,K] @ w[N,K]^T (+ bias) with half-precision split operands; (w_hi, w_lo, w_scale) = split_f16(w);
+    ``a_scale`` is a one-element float32 device tensor (a power of two) or None for 1."""
+    for t in (a, c):
+        if not t.is_cuda or t.dtype != torch.float32 or t.dim() != 2 or t.stride(1) != 1:
+            raise _lib.FairchemB200Error("gemm_f16x2: need 2-D float32 CUDA a and c with unit inner stride")
+    for t in (w_hi, w_lo):
+        if not t.is_cuda or t.dtype != torch.float16 or t.dim() != 2 or not t.is_contiguous() or t.shape != w_hi.shape:
+            raise _lib.FairchemB200Error("gemm_f16x2: need contiguous 2-D float16 CUDA weight parts of one shape")
+    _chk(bias, status, a_scale)
+    m, n, k = a.shape[0], w_hi.shape[0], a.shape[1]
+    if w_hi.shape[1] != k:
+        raise _lib.FairchemB200Error("gemm_f16x2: inner dimensions differ")
+    _launch("gemm_f16x2", "fcb200_gemm_f16x2",
+            (_p(a), a.stride(0), _p(w_hi), _p(w_lo), k, w_scale, _p(a_scale), _p(bias), _p(c), c.stride(0), m, n, k, _p(status),
+             _stream()), nbytes=4 * (m * k + n * k + m * n), flops=2 * m * n * k)
+
+
+def split_f16(w: Tensor):
+    """(hi, lo, scale): half-precision parts of w * scale, scale = the power of two that puts max|w| in [2^13, 2^14)."""
+    w = w.detach().contiguous()
+    amax = float(w.abs().max())
+    scale = 2.0 ** (13 - math.floor(math.log2(amax))) if amax > 0.0 else 1.0
+    hi = torch.empty(w.shape, dtype=torch.float16, device=w.device)
+    lo = torch.empty_like(hi)
+    _chk(w, hi, lo)
+    _launch("split_f16", "fcb200_split_f16", (_p(w), w.stride(0), _p(hi), _p(lo), scale, w.shape[0], w.shape[1], _stream()),
+            nbytes=8 * w.numel())
+    return hi, lo, scale
 
 
 @_op("split_tf32", ("hi", "lo"))

@@ -302,6 +302,26 @@ int fcb200_gemm_tf32(const float* a, int64_t lda, const float* w, const float* w
  */
 int fcb200_split_tf32(const float* w, float* w_hi, float* w_lo, int64_t count, void* stream);
 
+/*
+ * The same contraction with half-precision split operands (three kind::f16 tcgen05 MMAs per product,
+ * twice the TF32 issue rate, float32 accumulation): every value v is carried as hi + lo * 2^-11 with
+ * hi = half(v * scale), lo = half((v * scale - hi) * 2^11), 22 significant bits as long as v * scale lies in
+ * the normal half range (6.1e-5 .. 65504); smaller values keep an absolute accuracy of 3e-11 / scale.
+ *   w_hi, w_lo  [N, K] half, row stride ldw (halves, multiple of 8): fcb200_split_f16 of the float32 weight
+ *   w_scale     the power of two the weight was multiplied by before the split
+ *   a_scale     DEVICE pointer to the power of two A is multiplied by before its split, or NULL for 1;
+ *               choose it so that max|A| * a_scale stays well below 65504
+ *   status      set to 1 if a bounded wait expired, to 2 if a scaled A value left the half range
+ * K a multiple of 8, N a multiple of 4.  Same role in the reference as fcb200_gemm_tf32.
+ */
+int fcb200_gemm_f16x2(const float* a, int64_t lda, const void* w_hi, const void* w_lo, int64_t ldw, float w_scale,
+                      const float* a_scale, const float* bias, float* c, int64_t ldc, int64_t m, int32_t n, int32_t k,
+                      int32_t* status, void* stream);
+
+/* w [rows, cols] float32 (row stride ldw) -> contiguous half hi / lo parts of w * scale (see fcb200_gemm_f16x2). */
+int fcb200_split_f16(const float* w, int64_t ldw, void* w_hi, void* w_lo, float scale, int64_t rows, int64_t cols,
+                     void* stream);
+
 /* ---------------------------------------------------------------- any lmax with mmax = 2 (lmax = 2 or 4) */
 
 /*

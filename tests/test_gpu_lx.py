@@ -353,3 +353,19 @@ def test_backend_ops_lmax4(ops):
     back = B200Backend.permute_wigner_inv_edge_to_node(msg, dense_inv, edge_index[1], n)
     ref_back = torch.zeros(n, sh.nl, c, device="cuda").index_add(0, edge_index[1], torch.bmm(dense_inv[:, :, sh.m2l], msg))
     torch.testing.assert_close(back, ref_back, **FWD_TOL)
+
+
+def test_l4_half_split_gemm_mode_matches_reference_golden(ops, golden):
+    from fairchem_b200 import backbone as B
+
+    g = golden("escn_md_l4.npz")
+    sd = weights.random_init_state_dict(weights.ESCN_MD_L4, 0)
+    B.set_gemm_precision(2)
+    try:
+        model = B.build_model(weights.ESCN_MD_L4, sd, edge_chunk_size=1024)
+        for name in sorted(L4_CASES):
+            e, f = run(model, L4_CASES[name]())
+            assert np.max(np.abs(e - g[f"{name}_energy"]) / np.abs(g[f"{name}_energy"])) < E_RTOL, name
+            assert np.max(np.abs(f - g[f"{name}_forces"])) < F_ATOL, name
+    finally:
+        B.set_gemm_precision(3)

@@ -100,3 +100,21 @@ def test_isolated_atom_and_empty_graph(model):
     d = synthetic._pack(np.array([[0, 0, 0], [20, 0, 0]], np.float32), [8, 1], np.eye(3)[None], [[False] * 3], [2], "omol", 0, 1)
     e, f, _ = run(model, d)
     assert np.isfinite(e).all() and np.abs(f).max() < 1e-6
+
+
+def test_half_split_gemm_mode_matches_reference_golden(golden):
+    """Precision 2 (half-precision hi/lo operands, gradients scaled into the half range) meets the same bars."""
+    from fairchem_b200 import backbone as B
+
+    g = golden("uma_s_energy_forces.npz")
+    sd = weights.random_init_state_dict(weights.UMA_S, 0)
+    B.set_gemm_precision(2)
+    try:
+        model = (B.build_model(weights.UMA_S, sd, edge_chunk_size=4096), sd)
+        for name in sorted(CASES):
+            e, f, _ = run(model, CASES[name]())
+            e_ref, f_ref = g[f"{name}_energy"], g[f"{name}_forces"]
+            assert np.max(np.abs(e - e_ref) / np.abs(e_ref)) < E_RTOL, name
+            assert np.max(np.abs(f - f_ref)) < F_ATOL, name
+    finally:
+        B.set_gemm_precision(3)
