@@ -144,6 +144,10 @@ def run_b200(args):
 
         dist.init_process_group("nccl", device_id=dev)
     B.set_gemm_precision(args.precision)
+    if args.generic_kernels:
+        from fairchem_b200 import ops as _ops
+
+        _ops.set_generic_kernels(True)
     cfg, model_name = MODELS[args.model]
     sd = weights.random_init_state_dict(cfg, args.seed)
     bb, head = B.build_model(cfg, sd, device=dev, edge_chunk_size=args.chunk)
@@ -397,6 +401,8 @@ def main():
     ap.add_argument("--chunk", type=int, default=131072)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--generic-kernels", action="store_true",
+                    help="route the lmax=2 model through the any-lmax edge-block kernels (A/B measurement)")
     ap.add_argument("--profile-run", action="store_true",
                     help="for runs under a profiler: allows fewer than 3 warm-up steps; the printed number is not a bench value")
     args = ap.parse_args()

@@ -34,6 +34,15 @@ SIGNATURES = {
     "fcb200_edge_geometry_fwd": [P, P, P, P, P, P, P, P, P, P, F32, I32, F32, F32, F32, I64, I64, P],
     "fcb200_edge_geometry_bwd": [P, P, P, P, P, P, P, P, P, P, F32, I32, F32, F32, F32, I64, I64, P],
     "fcb200_gemm_f16x2": [P, I64, P, P, I64, F32, P, P, P, I64, I64, I32, I32, P, P],
+    "fcb200_gemm_f16x2_presplit": [P, P, I64, P, P, I64, F32, P, P, P, I64, I64, I32, I32, P, P],
+    "fcb200_gather_rotate_fwd_h": [P, P, P, P, P, P, P, P, I64, I64, I32, P],
+    "fcb200_rotate_back_bwd_h": [P, P, P, P, P, P, P, P, I64, I64, I32, P],
+    "fcb200_so2_gate_fwd_h": [P, P, P, P, I64, I32, P],
+    "fcb200_so2_gate_bwd_h": [P, P, P, P, P, I64, I32, P],
+    "fcb200_lx_gather_rotate_fwd_h": [P, P, P, P, P, P, P, P, I64, I64, I32, I32, P],
+    "fcb200_lx_rotate_back_bwd_h": [P, P, P, P, P, P, P, P, I64, I64, I32, I32, P],
+    "fcb200_lx_so2_gate_fwd_h": [P, P, P, P, I64, I32, I32, P],
+    "fcb200_lx_so2_gate_bwd_h": [P, P, P, P, P, I64, I32, I32, P],
     "fcb200_split_f16": [P, I64, P, P, F32, I64, I64, P],
     "fcb200_lx_gather_rotate_fwd": [P, P, P, P, P, P, I64, I64, I32, I32, P],
     "fcb200_lx_gather_rotate_bwd": [P, P, P, P, P, P, P, P, P, P, I64, I64, I32, I32, P],

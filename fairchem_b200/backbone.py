@@ -561,8 +561,98 @@ def _so2_conv_input_grad(conv: "SO2Convolution", gy, cin: int):
     return gx
 
 
+# ---- the chunk pipeline, written out by hand (no autograd inside a chunk) ------------------------
+# A tensor that only feeds a contraction is either float32 or, in precision 2, the pair of half planes
+# (hi, lo) its producer kernel writes so that the tensor cores read it without a conversion pass.
+
+
+def _presplit() -> bool:
+    return _GemmState.precision == 2
+
+
+def _new_operand(rows: int, width: int, device):
+    if _presplit():
+        t = torch.empty(2, rows, width, dtype=torch.float16, device=device)
+        return t[0], t[1]
+    return torch.empty(rows, width, dtype=torch.float32, device=device)
+
+
+def _cols(x, a: int, b: int):
+    return (x[0][:, a:b], x[1][:, a:b]) if isinstance(x, tuple) else x[:, a:b]
+
+
+def _contract(x, w, bias, y, scale):
+    """y = x @ w^T + bias for a float32 or pre-split x; ``scale`` is the power of two a pre-split x was written with."""
+    if isinstance(x, tuple):
+        hi, lo, sc = _split16(w)
+        ops.gemm_f16x2_presplit_.raw(x[0], x[1], hi, lo, sc, scale, bias, y, _status(y.device))
+    else:
+        _gemm(x, w, bias, y, _GemmState.precision)
+
+
+def _conv_weights(conv: "SO2Convolution"):
+    return (conv.fc_m0.weight.detach(), _block_weight(conv.so2_m_conv[0].fc.weight), _block_weight(conv.so2_m_conv[1].fc.weight))
+
+
+def _conv_forward(conv: "SO2Convolution", x):
+    """SO(2) convolution of M-major rows x [E, NM*Cin] (float32 or pre-split) -> float32 [E, extra + NM*Cout]."""
+    w0, w1, w2 = _conv_weights(conv)
+    n0, n1, n2 = w0.shape[0], w1.shape[0], w2.shape[0]
+    k0, k1 = w0.shape[1], w1.shape[1]
+    ref = x[0] if isinstance(x, tuple) else x
+    y = torch.empty(ref.shape[0], n0 + n1 + n2, dtype=torch.float32, device=ref.device)
+    _contract(_cols(x, 0, k0), w0, conv.fc_m0.bias.detach(), y[:, :n0], None)
+    _contract(_cols(x, k0, k0 + k1), w1, None, y[:, n0:n0 + n1], None)
+    _contract(_cols(x, k0 + k1, ref.shape[1]), w2, None, y[:, n0 + n1:], None)
+    return y
+
+
+def _conv_backward(conv: "SO2Convolution", gy):
+    """Gradient of the convolution input from the gradient of its output gy [E, extra + NM*Cout] (float32 or pre-split)."""
+    w0, w1, w2 = _conv_weights(conv)
+    n0, n1 = w0.shape[0], w1.shape[0]
+    k0, k1, k2 = w0.shape[1], w1.shape[1], w2.shape[1]
+    ref = gy[0] if isinstance(gy, tuple) else gy
+    gx = torch.empty(ref.shape[0], k0 + k1 + k2, dtype=torch.float32, device=ref.device)
+    scale = _GemmState.a_scale
+    if isinstance(gy, tuple):
+        _contract(_cols(gy, 0, n0), _transposed(w0), None, gx[:, :k0], scale)
+        _contract(_cols(gy, n0, n0 + n1), _transposed(w1), None, gx[:, k0:k0 + k1], scale)
+        _contract(_cols(gy, n0 + n1, ref.shape[1]), _transposed(w2), None, gx[:, k0 + k1:], scale)
+    else:
+        p = _GemmState.precision
+        _gemm(gy[:, :n0], _transposed(w0), None, gx[:, :k0], p, grad=gy)
+        _gemm(gy[:, n0:n0 + n1], _transposed(w1), None, gx[:, k0:k0 + k1], p, grad=gy)
+        _gemm(gy[:, n0 + n1:], _transposed(w2), None, gx[:, k0 + k1:], p, grad=gy)
+    return gx
+
+
+def _gather_rotate(x, g, sl, wig, rad, nm: int):
+    ec, c = sl.stop - sl.start, x.shape[2]
+    m = _new_operand(ec, nm * 2 * c, x.device)
+    if isinstance(m, tuple):
+        ops.gather_rotate_fwd_h_.raw(x, g.src[sl], g.tgt[sl], wig[sl], rad, m[0], m[1], None)
+    else:
+        ops.gather_rotate_fwd_.raw(x, g.src[sl], g.tgt[sl], wig[sl], rad, m.view(ec, nm, 2 * c))
+    return m
+
+
+def _gate(y, hidden: int, nm: int):
+    a = _new_operand(y.shape[0], nm * hidden, y.device)
+    if isinstance(a, tuple):
+        ops.so2_gate_fwd_h_.raw(y, a[0], a[1], None, hidden)
+    else:
+        ops.so2_gate_fwd_.raw(y, a.view(y.shape[0], nm, hidden), hidden)
+    return a
+
+
 class _EdgeBlockFn(torch.autograd.Function):
-    """One layer's edge block over all chunks; differentiable in x, wig, winv and gauss."""
+    """One layer's edge block over all chunks; differentiable in x, wig, winv and gauss.
+
+    Per chunk: radial MLP -> gather + rotate + radial scale -> SO(2) conv 1 -> gate -> SO(2) conv 2 -> rotate back
+    + segmented reduce.  The backward pass walks the same chain in reverse with explicit kernels; what it needs
+    of the forward pass (the conv-1 output for the gate derivative, the messages for the Wigner gradient) is
+    kept or recomputed according to ``keep_level``."""
 
     @staticmethod
     def forward(ctx, x, wig, winv, gauss, ew: Edgewise, tables, ectx: _EdgeCtx, nb: int, keep_level: int):
@@ -576,13 +666,13 @@ class _EdgeBlockFn(torch.autograd.Function):
         with torch.no_grad():
             for ch in ectx.chunks:
                 sl = slice(ch.e0, ch.e1)
-                rad = _radial(ew.so2_conv_1.rad_func, tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb)
                 ec = ch.e1 - ch.e0
-                m = torch.empty(ec, nm, 2 * c, dtype=x.dtype, device=x.device)
-                ops.gather_rotate_fwd_.raw(x, g.src[sl], g.tgt[sl], wig[sl], rad, m)
-                y = _so2_conv1(ew, m)
-                del m, rad
-                msg = _so2_tail(ew, y)
+                rad = _radial(ew.so2_conv_1.rad_func, tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb)
+                m = _gather_rotate(x, g, sl, wig, rad, nm)
+                del rad
+                y = _conv_forward(ew.so2_conv_1, m)
+                del m
+                msg = _conv_forward(ew.so2_conv_2, _gate(y, ew.hidden, nm)).view(ec, nm, c)
                 ops.rotate_back_reduce_fwd_.raw(msg, winv[sl], ch.row_ptr, out[ch.n0:ch.n1])
                 if keep_level >= 2:
                     kept.append((y, msg))  # the backward is then free of any recomputation but the radial MLP
@@ -595,64 +685,60 @@ class _EdgeBlockFn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, grad_out):
         x, wig, winv, gauss = ctx.saved_tensors
+        grad_out = grad_out.contiguous()
+        with _GradScale(grad_out.abs().amax()):
+            return _EdgeBlockFn._backward_chunks(ctx, x, wig, winv, gauss, grad_out)
+
+    @staticmethod
+    def _backward_chunks(ctx, x, wig, winv, gauss, grad_out):
         ew, tables, ectx, nb = ctx.ew, ctx.tables, ctx.ectx, ctx.nb
         g = ectx.graph
         nl, c = x.shape[1], x.shape[2]
-        nm = ops.SHAPES[ew.lmax].nm
-        grad_out = grad_out.contiguous()
+        nm, h = ops.SHAPES[ew.lmax].nm, ew.hidden
         gx = torch.zeros_like(x)
         gwig = torch.empty_like(wig)
         gwinv = torch.empty_like(winv)
         ggauss = torch.empty_like(gauss)
         kept = ctx.kept
         ctx.kept = None
-        with _GradScale(grad_out.abs().amax()):
-            return _EdgeBlockFn._backward_chunks(ctx, x, wig, winv, gauss, grad_out, gx, gwig, gwinv, ggauss, kept, nl, nm, c)
-
-    @staticmethod
-    def _backward_chunks(ctx, x, wig, winv, gauss, grad_out, gx, gwig, gwinv, ggauss, kept, nl, nm, c):
-        ew, tables, ectx, nb = ctx.ew, ctx.tables, ctx.ectx, ctx.nb
-        g = ectx.graph
+        scale = _GemmState.a_scale  # the power of two the gradient operands of this block are written with
         for ci, ch in enumerate(ectx.chunks):
             sl = slice(ch.e0, ch.e1)
             ec = ch.e1 - ch.e0
             with torch.enable_grad():
                 g_c = gauss[sl].detach().requires_grad_(True)
                 rad = _radial(ew.so2_conv_1.rad_func, tables, g_c, ectx.z_src[sl], ectx.z_tgt[sl], nb)
-                rad_d = rad.detach()
-                y = msg = m = None
-                if kept:
-                    y, msg = kept[ci]
-                    kept[ci] = None
-                    if msg is None:
-                        y.requires_grad_(True)
-                        msg = _so2_tail(ew, y)
-                else:
-                    m = torch.empty(ec, nm, 2 * c, dtype=x.dtype, device=x.device)
-                    ops.gather_rotate_fwd_.raw(x, g.src[sl], g.tgt[sl], wig[sl], rad_d, m)
-                    m.requires_grad_(True)
-                    msg = _so2_middle(ew, m)
-            grad_msg = torch.empty_like(msg)
-            ops.rotate_back_bwd_.raw(grad_out, msg.detach(), winv[sl], g.tgt[sl], grad_msg, gwinv[sl])
-            if m is not None:
-                (gm,) = torch.autograd.grad(msg, (m,), grad_msg)
+            rad_d = rad.detach()
+            y = msg = None
+            if kept:
+                y, msg = kept[ci]
+                kept[ci] = None
+            if y is None:
+                y = _conv_forward(ew.so2_conv_1, _gather_rotate(x, g, sl, wig, rad_d, nm))
+            if msg is None:
+                msg = _conv_forward(ew.so2_conv_2, _gate(y, h, nm)).view(ec, nm, c)
+            # rotate back: gradient of the messages (and of the inverse Wigner entries)
+            grad_msg = _new_operand(ec, nm * c, x.device)
+            if isinstance(grad_msg, tuple):
+                ops.rotate_back_bwd_h_.raw(grad_out, msg, winv[sl], g.tgt[sl], grad_msg[0], grad_msg[1], scale, gwinv[sl])
             else:
-                if msg.requires_grad:
-                    (gy,) = torch.autograd.grad(msg, (y,), grad_msg)
-                else:  # both kept: manual chain conv-2 input grad -> gate backward
-                    h = ew.hidden
-                    ga = _so2_conv_input_grad(ew.so2_conv_2, grad_msg.view(ec, -1), h)
-                    gy = torch.empty_like(y)
-                    ops.so2_gate_bwd_.raw(ga, y, gy, h)
-                    del ga
-                gm = _so2_conv_input_grad(ew.so2_conv_1, gy, 2 * c)
-                del gy, y
-            del msg, grad_msg
+                ops.rotate_back_bwd_.raw(grad_out, msg, winv[sl], g.tgt[sl], grad_msg.view(ec, nm, c), gwinv[sl])
+            del msg
+            ga = _conv_backward(ew.so2_conv_2, grad_msg)
+            del grad_msg
+            gy = _new_operand(ec, y.shape[1], x.device)
+            if isinstance(gy, tuple):
+                ops.so2_gate_bwd_h_.raw(ga, y, gy[0], gy[1], scale, h)
+            else:
+                ops.so2_gate_bwd_.raw(ga, y, gy, h)
+            del ga, y
+            gm = _conv_backward(ew.so2_conv_1, gy)
+            del gy
             g_src = torch.empty(ec, nl, c, dtype=x.dtype, device=x.device)
             g_tgt = torch.empty(ec, nl, c, dtype=x.dtype, device=x.device)
             grad_rad = torch.empty_like(rad_d)
-            ops.gather_rotate_bwd_.raw(gm.contiguous(), x, g.src[sl], g.tgt[sl], wig[sl], rad_d, g_src, g_tgt, gwig[sl], grad_rad)
-            del gm, m
+            ops.gather_rotate_bwd_.raw(gm, x, g.src[sl], g.tgt[sl], wig[sl], rad_d, g_src, g_tgt, gwig[sl], grad_rad)
+            del gm
             # node reductions: target rows of the chunk are contiguous; source rows are the chunk's distinct sources
             ops.segment_sum(g_tgt, ch.row_ptr, None, ch.n1 - ch.n0, out=gx[ch.n0:ch.n1], accumulate=True)
             ops.segment_sum(g_src, ch.src_ptr, ch.src_perm, ch.src_nodes.shape[0], out=gx, out_index=ch.src_nodes,

@@ -1,6 +1,7 @@
 // Shared helpers for the fairchem_b200 kernels (sm_100a).
 #pragma once
 
+#include <cuda_fp16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -93,6 +94,36 @@ __device__ __forceinline__ void load_wig(const float* __restrict__ wig, int64_t 
 #pragma unroll
     for (int i = 0; i < FCB200_WIG; ++i) w[i] = i < 32 ? __shfl_sync(kFull, a, i) : __shfl_sync(kFull, b, i - 32);
 }
+
+// ---- output policies of the kernels that feed the dense contractions ---------------------------
+// OutF32 stores float32.  OutSplit stores the half-precision split the tensor cores consume directly:
+// hi = half(v * s), lo = half((v * s - hi) * 2^11), in two planes of the same shape (same bytes as float32).
+struct OutF32 {
+    float* p;
+    __device__ __forceinline__ void load_scale(const float*) {}
+    __device__ __forceinline__ void st(int64_t off, float4 v) const { st4(p + off, v); }
+};
+struct OutSplit {
+    __half* hi;
+    __half* lo;
+    float s;
+    __device__ __forceinline__ void load_scale(const float* sp) { s = sp ? *sp : 1.0f; }
+    __device__ __forceinline__ void st(int64_t off, float4 v) const {
+        v = scale4(s, v);
+        const __half2 h0 = __floats2half2_rn(v.x, v.y), h1 = __floats2half2_rn(v.z, v.w);
+        const float2 f0 = __half22float2(h0), f1 = __half22float2(h1);
+        const __half2 l0 = __floats2half2_rn((v.x - f0.x) * 2048.0f, (v.y - f0.y) * 2048.0f);
+        const __half2 l1 = __floats2half2_rn((v.z - f1.x) * 2048.0f, (v.w - f1.y) * 2048.0f);
+        uint2 ph, pl;
+        ph.x = *reinterpret_cast<const uint32_t*>(&h0);
+        ph.y = *reinterpret_cast<const uint32_t*>(&h1);
+        pl.x = *reinterpret_cast<const uint32_t*>(&l0);
+        pl.y = *reinterpret_cast<const uint32_t*>(&l1);
+        *reinterpret_cast<uint2*>(hi + off) = ph;
+        *reinterpret_cast<uint2*>(lo + off) = pl;
+    }
+};
+inline bool aligned8(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 7u) == 0; }
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 

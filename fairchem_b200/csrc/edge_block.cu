@@ -22,11 +22,12 @@ __device__ __forceinline__ P* edge_row(P* buf, int64_t e, int m, int w) {
 // ---------------------------------------------------------------------------------------------
 // gather + rotate (+ radial scale) forward
 // ---------------------------------------------------------------------------------------------
-template <bool HAS_RAD>
+template <bool HAS_RAD, class Out>
 __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
     gather_rotate_fwd_kernel(const float* __restrict__ x, const int32_t* __restrict__ src, const int32_t* __restrict__ tgt,
-                             const float* __restrict__ wig, const float* __restrict__ radial, float* __restrict__ out,
-                             int64_t num_edges, int channels) {
+                             const float* __restrict__ wig, const float* __restrict__ radial, Out out,
+                             const float* __restrict__ scale_ptr, int64_t num_edges, int channels) {
+    out.load_scale(scale_ptr);
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
@@ -62,9 +63,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
                     as = mul4(as, ld4(r));
                     at = mul4(at, ld4(r + channels));
                 }
-                float* o = edge_row(out, e, m, 2 * channels) + c0;
-                st4(o, as);
-                st4(o + channels, at);
+                const int64_t o = (e * 9 + m) * 2LL * channels + c0;
+                out.st(o, as);
+                out.st(o + channels, at);
             }
         }
     }
@@ -208,11 +209,12 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
 // rotate back backward (per edge): grad_msg (M-major) and grad_winv
 // ---------------------------------------------------------------------------------------------
 // MODE 0: full messages.  MODE 1: edge-degree (3 rows), with 1/rescale.
-template <int MODE, bool WANT_DW>
+template <int MODE, bool WANT_DW, class Out>
 __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
     rotate_back_bwd_kernel(const float* __restrict__ grad_out, const float* __restrict__ msg, const float* __restrict__ winv,
-                           const int32_t* __restrict__ tgt, float* __restrict__ grad_msg, float* __restrict__ grad_winv,
-                           float rescale, int64_t num_edges, int channels) {
+                           const int32_t* __restrict__ tgt, Out grad_msg, const float* __restrict__ scale_ptr,
+                           float* __restrict__ grad_winv, float rescale, int64_t num_edges, int channels) {
+    grad_msg.load_scale(scale_ptr);
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
@@ -247,7 +249,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
                             if (WANT_DW) dw[idx] += dot4(go[l * l + a], y[m]);
                         }
                     }
-                    st4(grad_msg + e * 9LL * channels + m * channels + c0, acc);
+                    grad_msg.st(e * 9LL * channels + m * channels + c0, acc);
                 }
             } else {
 #pragma unroll
@@ -264,7 +266,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
                             if (WANT_DW) dw[idx] += dot4(go[l * l + a], y);
                         }
                     }
-                    st4(grad_msg + e * 3LL * channels + l * channels + c0, scale4(inv, acc));
+                    grad_msg.st(e * 3LL * channels + l * channels + c0, scale4(inv, acc));
                 }
             }
         }
@@ -345,52 +347,56 @@ __host__ __device__ constexpr int gate_of(int m) {
 
 // y [E, 11H] = [gate scalars 2H | rows 0..8 (9H)] (the three conv-1 GEMMs write it side by side);
 // out [E, 9, H]: row 0 -> SiLU, rows 1..8 -> value * sigmoid(gate of the row's degree).
+template <class Out>
 __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
-    so2_gate_fwd_kernel(const float* __restrict__ y, float* __restrict__ out, int64_t num_edges, int ch) {
+    so2_gate_fwd_kernel(const float* __restrict__ y, Out out, const float* __restrict__ scale_ptr, int64_t num_edges, int ch) {
+    out.load_scale(scale_ptr);
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
     for (int64_t e = warp0; e < num_edges; e += nwarps) {
         const float* p = y + e * 11LL * ch;
-        float* o = out + e * 9LL * ch;
+        const int64_t o = e * 9LL * ch;
         for (int c = lane * 4; c < ch; c += 128) {
             float4 gate[2] = {sig4(ld4(p + c)), sig4(ld4(p + ch + c))};
             const float4 v0 = ld4(p + 2 * ch + c);
-            st4(o + c, mul4(v0, sig4(v0)));
+            out.st(o + c, mul4(v0, sig4(v0)));
 #pragma unroll
-            for (int m = 1; m < 9; ++m) st4(o + m * ch + c, mul4(ld4(p + (2 + m) * ch + c), gate[gate_of(m)]));
+            for (int m = 1; m < 9; ++m) out.st(o + m * ch + c, mul4(ld4(p + (2 + m) * ch + c), gate[gate_of(m)]));
         }
     }
 }
 
+template <class Out>
 __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
-    so2_gate_bwd_kernel(const float* __restrict__ grad_out, const float* __restrict__ y, float* __restrict__ grad_y,
-                        int64_t num_edges, int ch) {
+    so2_gate_bwd_kernel(const float* __restrict__ grad_out, const float* __restrict__ y, Out grad_y,
+                        const float* __restrict__ scale_ptr, int64_t num_edges, int ch) {
+    grad_y.load_scale(scale_ptr);
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
     for (int64_t e = warp0; e < num_edges; e += nwarps) {
         const float* p = y + e * 11LL * ch;
         const float* go = grad_out + e * 9LL * ch;
-        float* q = grad_y + e * 11LL * ch;
+        const int64_t q = e * 11LL * ch;
         for (int c = lane * 4; c < ch; c += 128) {
             const float4 gate[2] = {sig4(ld4(p + c)), sig4(ld4(p + ch + c))};
             float4 dgate[2] = {f4zero(), f4zero()};
             {
                 const float4 v = ld4(p + 2 * ch + c), s = sig4(v), d = ld4(go + c);
-                st4(q + 2 * ch + c, make_float4(d.x * s.x * (1.f + v.x * (1.f - s.x)), d.y * s.y * (1.f + v.y * (1.f - s.y)),
-                                                d.z * s.z * (1.f + v.z * (1.f - s.z)), d.w * s.w * (1.f + v.w * (1.f - s.w))));
+                grad_y.st(q + 2 * ch + c, make_float4(d.x * s.x * (1.f + v.x * (1.f - s.x)), d.y * s.y * (1.f + v.y * (1.f - s.y)),
+                                                      d.z * s.z * (1.f + v.z * (1.f - s.z)), d.w * s.w * (1.f + v.w * (1.f - s.w))));
             }
 #pragma unroll
             for (int m = 1; m < 9; ++m) {
                 const float4 d = ld4(go + m * ch + c);
-                st4(q + (2 + m) * ch + c, mul4(d, gate[gate_of(m)]));
+                grad_y.st(q + (2 + m) * ch + c, mul4(d, gate[gate_of(m)]));
                 dgate[gate_of(m)] = add4(dgate[gate_of(m)], mul4(d, ld4(p + (2 + m) * ch + c)));
             }
 #pragma unroll
             for (int g = 0; g < 2; ++g) {
                 const float4 s = gate[g], d = dgate[g];
-                st4(q + g * ch + c, make_float4(d.x * s.x * (1.f - s.x), d.y * s.y * (1.f - s.y), d.z * s.z * (1.f - s.z), d.w * s.w * (1.f - s.w)));
+                grad_y.st(q + g * ch + c, make_float4(d.x * s.x * (1.f - s.x), d.y * s.y * (1.f - s.y), d.z * s.z * (1.f - s.z), d.w * s.w * (1.f - s.w)));
             }
         }
     }
@@ -422,9 +428,9 @@ int fcb200_gather_rotate_fwd(const float* x, const int32_t* src, const int32_t* 
     if (radial && !aligned16(radial)) return FCB200_EALIGN;
     if (num_edges == 0) return FCB200_OK;
     if (radial)
-        gather_rotate_fwd_kernel<true><<<FCB_LAUNCH(num_edges)>>>(x, src, tgt, wig, radial, out, num_edges, channels);
+        gather_rotate_fwd_kernel<true, OutF32><<<FCB_LAUNCH(num_edges)>>>(x, src, tgt, wig, radial, OutF32{out}, nullptr, num_edges, channels);
     else
-        gather_rotate_fwd_kernel<false><<<FCB_LAUNCH(num_edges)>>>(x, src, tgt, wig, nullptr, out, num_edges, channels);
+        gather_rotate_fwd_kernel<false, OutF32><<<FCB_LAUNCH(num_edges)>>>(x, src, tgt, wig, nullptr, OutF32{out}, nullptr, num_edges, channels);
     return launch_status();
 }
 
@@ -476,9 +482,9 @@ int fcb200_rotate_back_bwd(const float* grad_out, const float* msg, const float*
     if (msg && !aligned16(msg)) return FCB200_EALIGN;
     if (num_edges == 0) return FCB200_OK;
     if (msg)
-        rotate_back_bwd_kernel<0, true><<<FCB_LAUNCH(num_edges)>>>(grad_out, msg, winv, tgt, grad_msg, grad_winv, 1.f, num_edges, channels);
+        rotate_back_bwd_kernel<0, true, OutF32><<<FCB_LAUNCH(num_edges)>>>(grad_out, msg, winv, tgt, OutF32{grad_msg}, nullptr, grad_winv, 1.f, num_edges, channels);
     else
-        rotate_back_bwd_kernel<0, false><<<FCB_LAUNCH(num_edges)>>>(grad_out, nullptr, winv, tgt, grad_msg, nullptr, 1.f, num_edges,
+        rotate_back_bwd_kernel<0, false, OutF32><<<FCB_LAUNCH(num_edges)>>>(grad_out, nullptr, winv, tgt, OutF32{grad_msg}, nullptr, nullptr, 1.f, num_edges,
                                                                     channels);
     return launch_status();
 }
@@ -491,7 +497,7 @@ int fcb200_edge_degree_bwd(const float* grad_out, const float* radial3, const fl
     if (!radial3 || !winv || !tgt || !grad_winv || num_nodes < 0 || rescale == 0.f) return FCB200_EINVAL;
     if (!aligned16(radial3)) return FCB200_EALIGN;
     if (num_edges == 0) return FCB200_OK;
-    rotate_back_bwd_kernel<1, true><<<FCB_LAUNCH(num_edges)>>>(grad_out, radial3, winv, tgt, grad_radial3, grad_winv, rescale,
+    rotate_back_bwd_kernel<1, true, OutF32><<<FCB_LAUNCH(num_edges)>>>(grad_out, radial3, winv, tgt, OutF32{grad_radial3}, nullptr, grad_winv, rescale,
                                                                num_edges, channels);
     return launch_status();
 }
@@ -514,7 +520,7 @@ int fcb200_so2_gate_fwd(const float* y, float* out, int64_t num_edges, int32_t h
     int rc = check_common(y, out, num_edges, hidden);
     if (rc) return rc;
     if (num_edges == 0) return FCB200_OK;
-    so2_gate_fwd_kernel<<<FCB_LAUNCH(num_edges)>>>(y, out, num_edges, hidden);
+    so2_gate_fwd_kernel<OutF32><<<FCB_LAUNCH(num_edges)>>>(y, OutF32{out}, nullptr, num_edges, hidden);
     return launch_status();
 }
 
@@ -524,7 +530,62 @@ int fcb200_so2_gate_bwd(const float* grad_out, const float* y, float* grad_y, in
     if (!grad_y) return FCB200_EINVAL;
     if (!aligned16(grad_y)) return FCB200_EALIGN;
     if (num_edges == 0) return FCB200_OK;
-    so2_gate_bwd_kernel<<<FCB_LAUNCH(num_edges)>>>(grad_out, y, grad_y, num_edges, hidden);
+    so2_gate_bwd_kernel<OutF32><<<FCB_LAUNCH(num_edges)>>>(grad_out, y, OutF32{grad_y}, nullptr, num_edges, hidden);
+    return launch_status();
+}
+
+// ---- the same four producers writing the half-precision split the tensor-core contraction reads directly ----
+
+int fcb200_gather_rotate_fwd_h(const float* x, const int32_t* src, const int32_t* tgt, const float* wig, const float* radial,
+                               void* out_hi, void* out_lo, const float* scale, int64_t num_edges, int64_t num_nodes,
+                               int32_t channels, void* stream) {
+    if (!x || !out_hi || !out_lo || !src || !tgt || !wig || num_edges < 0 || num_nodes < 0) return FCB200_EINVAL;
+    if (channels <= 0 || channels % 128 != 0) return FCB200_EINVAL;
+    if (!aligned16(x) || !aligned8(out_hi) || !aligned8(out_lo) || (radial && !aligned16(radial))) return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    const OutSplit out{static_cast<__half*>(out_hi), static_cast<__half*>(out_lo), 1.0f};
+    if (radial)
+        gather_rotate_fwd_kernel<true, OutSplit><<<FCB_LAUNCH(num_edges)>>>(x, src, tgt, wig, radial, out, scale, num_edges, channels);
+    else
+        gather_rotate_fwd_kernel<false, OutSplit><<<FCB_LAUNCH(num_edges)>>>(x, src, tgt, wig, nullptr, out, scale, num_edges, channels);
+    return launch_status();
+}
+
+int fcb200_rotate_back_bwd_h(const float* grad_out, const float* msg, const float* winv, const int32_t* tgt, void* grad_msg_hi,
+                             void* grad_msg_lo, const float* scale, float* grad_winv, int64_t num_edges, int64_t num_nodes,
+                             int32_t channels, void* stream) {
+    if (!grad_out || !winv || !tgt || !grad_msg_hi || !grad_msg_lo || num_edges < 0 || num_nodes < 0) return FCB200_EINVAL;
+    if (channels <= 0 || channels % 128 != 0) return FCB200_EINVAL;
+    if ((grad_winv != nullptr) && (msg == nullptr)) return FCB200_EINVAL;
+    if (!aligned16(grad_out) || !aligned8(grad_msg_hi) || !aligned8(grad_msg_lo) || (msg && !aligned16(msg))) return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    const OutSplit out{static_cast<__half*>(grad_msg_hi), static_cast<__half*>(grad_msg_lo), 1.0f};
+    if (grad_winv)
+        rotate_back_bwd_kernel<0, true, OutSplit><<<FCB_LAUNCH(num_edges)>>>(grad_out, msg, winv, tgt, out, scale, grad_winv, 1.f,
+                                                                             num_edges, channels);
+    else
+        rotate_back_bwd_kernel<0, false, OutSplit><<<FCB_LAUNCH(num_edges)>>>(grad_out, nullptr, winv, tgt, out, scale, nullptr, 1.f,
+                                                                              num_edges, channels);
+    return launch_status();
+}
+
+int fcb200_so2_gate_fwd_h(const float* y, void* out_hi, void* out_lo, const float* scale, int64_t num_edges, int32_t hidden,
+                          void* stream) {
+    if (!y || !out_hi || !out_lo || num_edges < 0 || hidden <= 0 || hidden % 128) return FCB200_EINVAL;
+    if (!aligned16(y) || !aligned8(out_hi) || !aligned8(out_lo)) return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    so2_gate_fwd_kernel<OutSplit><<<FCB_LAUNCH(num_edges)>>>(
+        y, OutSplit{static_cast<__half*>(out_hi), static_cast<__half*>(out_lo), 1.0f}, scale, num_edges, hidden);
+    return launch_status();
+}
+
+int fcb200_so2_gate_bwd_h(const float* grad_out, const float* y, void* grad_y_hi, void* grad_y_lo, const float* scale,
+                          int64_t num_edges, int32_t hidden, void* stream) {
+    if (!grad_out || !y || !grad_y_hi || !grad_y_lo || num_edges < 0 || hidden <= 0 || hidden % 128) return FCB200_EINVAL;
+    if (!aligned16(grad_out) || !aligned16(y) || !aligned8(grad_y_hi) || !aligned8(grad_y_lo)) return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    so2_gate_bwd_kernel<OutSplit><<<FCB_LAUNCH(num_edges)>>>(
+        grad_out, y, OutSplit{static_cast<__half*>(grad_y_hi), static_cast<__half*>(grad_y_lo), 1.0f}, scale, num_edges, hidden);
     return launch_status();
 }
 

@@ -31,12 +31,13 @@ __device__ __forceinline__ void stage_wig(const float* __restrict__ wig, int64_t
 // ---------------------------------------------------------------------------------------------
 // gather + rotate (+ radial) forward: out[e, mrow(l,m), :] = rad * sum_j D[(l,m), j] * cat(x[src], x[tgt])[l^2 + j]
 // ---------------------------------------------------------------------------------------------
-template <int LMAX, bool HAS_RAD>
+template <int LMAX, bool HAS_RAD, class Out>
 __global__ void __launch_bounds__(kLxWarps* kWarp)
     lx_gather_rotate_fwd_kernel(const float* __restrict__ x, const int32_t* __restrict__ src, const int32_t* __restrict__ tgt,
-                                const float* __restrict__ wig, const float* __restrict__ radial, float* __restrict__ out,
-                                int64_t num_edges, int channels) {
+                                const float* __restrict__ wig, const float* __restrict__ radial, Out out,
+                                const float* __restrict__ scale_ptr, int64_t num_edges, int channels) {
     using S = Shape<LMAX>;
+    out.load_scale(scale_ptr);
     __shared__ float sw[kLxWarps][kWigSlot];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int64_t warp0 = (int64_t)blockIdx.x * kLxWarps + wid;
@@ -46,7 +47,7 @@ __global__ void __launch_bounds__(kLxWarps* kWarp)
         stage_wig<S::kW>(wig, e, lane, w);
         const float* xs_base = x + (int64_t)src[e] * S::kL * channels;
         const float* xt_base = x + (int64_t)tgt[e] * S::kL * channels;
-        float* o_base = out + e * (int64_t)S::kM * 2 * channels;
+        const int64_t o_base = e * (int64_t)S::kM * 2 * channels;
         const float* r_base = HAS_RAD ? radial + e * (int64_t)S::kRad * 2 * channels : nullptr;
         for (int c0 = lane * 4; c0 < channels; c0 += 128) {
 #pragma unroll
@@ -72,9 +73,9 @@ __global__ void __launch_bounds__(kLxWarps* kWarp)
                         as = mul4(as, ld4(r));
                         at = mul4(at, ld4(r + channels));
                     }
-                    float* o = o_base + S::mrow(l, m) * 2 * channels + c0;
-                    st4(o, as);
-                    st4(o + channels, at);
+                    const int64_t o = o_base + S::mrow(l, m) * 2 * channels + c0;
+                    out.st(o, as);
+                    out.st(o + channels, at);
                 }
             }
         }
@@ -211,12 +212,13 @@ __global__ void __launch_bounds__(kLxWarps* kWarp)
 }
 
 // backward per edge: grad_msg[e, mrow(l,m)] = sum_j winv[(l,k,j)] * go[tgt, l^2+j];  grad_winv[(l,k,j)] = <go[l^2+j], y[mrow]>
-template <int LMAX, int MODE, bool WANT_DW>
+template <int LMAX, int MODE, bool WANT_DW, class Out>
 __global__ void __launch_bounds__(kLxWarps* kWarp)
     lx_rotate_back_bwd_kernel(const float* __restrict__ grad_out, const float* __restrict__ msg, const float* __restrict__ winv,
-                              const int32_t* __restrict__ tgt, float* __restrict__ grad_msg, float* __restrict__ grad_winv,
-                              float rescale, int64_t num_edges, int channels) {
+                              const int32_t* __restrict__ tgt, Out grad_msg, const float* __restrict__ scale_ptr,
+                              float* __restrict__ grad_winv, float rescale, int64_t num_edges, int channels) {
     using S = Shape<LMAX>;
+    grad_msg.load_scale(scale_ptr);
     __shared__ float sw[kLxWarps][kWigSlot];
     const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
     const int64_t warp0 = (int64_t)blockIdx.x * kLxWarps + wid;
@@ -228,7 +230,7 @@ __global__ void __launch_bounds__(kLxWarps* kWarp)
         stage_wig<S::kW>(winv, e, lane, w);
         const float* go_base = grad_out + (int64_t)tgt[e] * S::kL * channels;
         const float* y_base = msg + e * (int64_t)rows_in * channels;
-        float* gm_base = grad_msg + e * (int64_t)rows_in * channels;
+        const int64_t gm_base = e * (int64_t)rows_in * channels;
 #pragma unroll
         for (int l = 0; l <= LMAX; ++l) {
             constexpr int kmax = 5 * (2 * LMAX + 1);
@@ -251,7 +253,7 @@ __global__ void __launch_bounds__(kLxWarps* kWarp)
                         acc = fma4(w[S::woff(l) + k * (2 * l + 1) + j], go[j], acc);
                         if (WANT_DW) dw[k * (2 * l + 1) + j] += dot4(go[j], y);
                     }
-                    st4(gm_base + row * channels + c0, scale4(inv, acc));
+                    grad_msg.st(gm_base + row * channels + c0, scale4(inv, acc));
                 }
             }
             if (WANT_DW) {
@@ -275,48 +277,50 @@ __device__ __forceinline__ float4 lx_sig4(float4 v) {
     return make_float4(lx_sigmoid(v.x), lx_sigmoid(v.y), lx_sigmoid(v.z), lx_sigmoid(v.w));
 }
 
-template <int LMAX>
+template <int LMAX, class Out>
 __global__ void __launch_bounds__(kLxWarps* kWarp)
-    lx_so2_gate_fwd_kernel(const float* __restrict__ y, float* __restrict__ out, int64_t num_edges, int ch) {
+    lx_so2_gate_fwd_kernel(const float* __restrict__ y, Out out, const float* __restrict__ scale_ptr, int64_t num_edges, int ch) {
     using S = Shape<LMAX>;
+    out.load_scale(scale_ptr);
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (int64_t)blockIdx.x * kLxWarps + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kLxWarps;
     for (int64_t e = warp0; e < num_edges; e += nwarps) {
         const float* p = y + e * (int64_t)(LMAX + S::kM) * ch;
-        float* o = out + e * (int64_t)S::kM * ch;
+        const int64_t o = e * (int64_t)S::kM * ch;
         for (int c = lane * 4; c < ch; c += 128) {
             const float4 v0 = ld4(p + LMAX * ch + c);
-            st4(o + c, mul4(v0, lx_sig4(v0)));
+            out.st(o + c, mul4(v0, lx_sig4(v0)));
 #pragma unroll
             for (int l = 1; l <= LMAX; ++l) {
                 const float4 gate = lx_sig4(ld4(p + (l - 1) * ch + c));
 #pragma unroll
                 for (int k = 0; k < S::rows(l); ++k) {
                     const int row = S::mrow(l, k - S::mm(l));
-                    st4(o + row * ch + c, mul4(ld4(p + (LMAX + row) * ch + c), gate));
+                    out.st(o + row * ch + c, mul4(ld4(p + (LMAX + row) * ch + c), gate));
                 }
             }
         }
     }
 }
 
-template <int LMAX>
+template <int LMAX, class Out>
 __global__ void __launch_bounds__(kLxWarps* kWarp)
-    lx_so2_gate_bwd_kernel(const float* __restrict__ grad_out, const float* __restrict__ y, float* __restrict__ grad_y,
-                           int64_t num_edges, int ch) {
+    lx_so2_gate_bwd_kernel(const float* __restrict__ grad_out, const float* __restrict__ y, Out grad_y,
+                           const float* __restrict__ scale_ptr, int64_t num_edges, int ch) {
     using S = Shape<LMAX>;
+    grad_y.load_scale(scale_ptr);
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (int64_t)blockIdx.x * kLxWarps + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kLxWarps;
     for (int64_t e = warp0; e < num_edges; e += nwarps) {
         const float* p = y + e * (int64_t)(LMAX + S::kM) * ch;
         const float* go = grad_out + e * (int64_t)S::kM * ch;
-        float* q = grad_y + e * (int64_t)(LMAX + S::kM) * ch;
+        const int64_t q = e * (int64_t)(LMAX + S::kM) * ch;
         for (int c = lane * 4; c < ch; c += 128) {
             {
                 const float4 v = ld4(p + LMAX * ch + c), s = lx_sig4(v), d = ld4(go + c);
-                st4(q + LMAX * ch + c, make_float4(d.x * s.x * (1.f + v.x * (1.f - s.x)), d.y * s.y * (1.f + v.y * (1.f - s.y)),
+                grad_y.st(q + LMAX * ch + c, make_float4(d.x * s.x * (1.f + v.x * (1.f - s.x)), d.y * s.y * (1.f + v.y * (1.f - s.y)),
                                                    d.z * s.z * (1.f + v.z * (1.f - s.z)), d.w * s.w * (1.f + v.w * (1.f - s.w))));
             }
 #pragma unroll
@@ -327,10 +331,10 @@ __global__ void __launch_bounds__(kLxWarps* kWarp)
                 for (int k = 0; k < S::rows(l); ++k) {
                     const int row = S::mrow(l, k - S::mm(l));
                     const float4 d = ld4(go + row * ch + c);
-                    st4(q + (LMAX + row) * ch + c, mul4(d, s));
+                    grad_y.st(q + (LMAX + row) * ch + c, mul4(d, s));
                     dg = add4(dg, mul4(d, ld4(p + (LMAX + row) * ch + c)));
                 }
-                st4(q + (l - 1) * ch + c,
+                grad_y.st(q + (l - 1) * ch + c,
                     make_float4(dg.x * s.x * (1.f - s.x), dg.y * s.y * (1.f - s.y), dg.z * s.z * (1.f - s.z), dg.w * s.w * (1.f - s.w)));
             }
         }
@@ -374,9 +378,11 @@ int fcb200_lx_gather_rotate_fwd(const float* x, const int32_t* src, const int32_
     if (radial && !aligned16(radial)) return FCB200_EALIGN;
     if (num_edges == 0) return FCB200_OK;
     if (radial)
-        LX_DISPATCH(num_edges, lx_gather_rotate_fwd_kernel, LX_COMMA true, x, src, tgt, wig, radial, out, num_edges, channels);
+        LX_DISPATCH(num_edges, lx_gather_rotate_fwd_kernel, LX_COMMA true LX_COMMA OutF32, x, src, tgt, wig, radial, OutF32{out},
+                    nullptr, num_edges, channels);
     else
-        LX_DISPATCH(num_edges, lx_gather_rotate_fwd_kernel, LX_COMMA false, x, src, tgt, wig, nullptr, out, num_edges, channels);
+        LX_DISPATCH(num_edges, lx_gather_rotate_fwd_kernel, LX_COMMA false LX_COMMA OutF32, x, src, tgt, wig, nullptr, OutF32{out},
+                    nullptr, num_edges, channels);
     return launch_status();
 }
 
@@ -429,11 +435,11 @@ int fcb200_lx_rotate_back_bwd(const float* grad_out, const float* msg, const flo
     if (msg && !aligned16(msg)) return FCB200_EALIGN;
     if (num_edges == 0) return FCB200_OK;
     if (grad_winv)
-        LX_DISPATCH(num_edges, lx_rotate_back_bwd_kernel, LX_COMMA 0 LX_COMMA true, grad_out, msg, winv, tgt, grad_msg, grad_winv,
-                    1.f, num_edges, channels);
+        LX_DISPATCH(num_edges, lx_rotate_back_bwd_kernel, LX_COMMA 0 LX_COMMA true LX_COMMA OutF32, grad_out, msg, winv, tgt,
+                    OutF32{grad_msg}, nullptr, grad_winv, 1.f, num_edges, channels);
     else
-        LX_DISPATCH(num_edges, lx_rotate_back_bwd_kernel, LX_COMMA 0 LX_COMMA false, grad_out, nullptr, winv, tgt, grad_msg, nullptr,
-                    1.f, num_edges, channels);
+        LX_DISPATCH(num_edges, lx_rotate_back_bwd_kernel, LX_COMMA 0 LX_COMMA false LX_COMMA OutF32, grad_out, nullptr, winv, tgt,
+                    OutF32{grad_msg}, nullptr, nullptr, 1.f, num_edges, channels);
     return launch_status();
 }
 
@@ -446,8 +452,8 @@ int fcb200_lx_edge_degree_bwd(const float* grad_out, const float* radial0, const
     if (!aligned16(radial0)) return FCB200_EALIGN;
     if (num_edges == 0) return FCB200_OK;
     // every entry of grad_winv is written (zeros in the rows m != 0, which this op does not read)
-    LX_DISPATCH(num_edges, lx_rotate_back_bwd_kernel, LX_COMMA 1 LX_COMMA true, grad_out, radial0, winv, tgt, grad_radial0,
-                grad_winv, rescale, num_edges, channels);
+    LX_DISPATCH(num_edges, lx_rotate_back_bwd_kernel, LX_COMMA 1 LX_COMMA true LX_COMMA OutF32, grad_out, radial0, winv, tgt,
+                OutF32{grad_radial0}, nullptr, grad_winv, rescale, num_edges, channels);
     return launch_status();
 }
 
@@ -455,7 +461,7 @@ int fcb200_lx_so2_gate_fwd(const float* y, float* out, int64_t num_edges, int32_
     int rc = lx_check(y, out, num_edges, hidden, lmax);
     if (rc != FCB200_OK) return rc;
     if (num_edges == 0) return FCB200_OK;
-    LX_DISPATCH(num_edges, lx_so2_gate_fwd_kernel, , y, out, num_edges, hidden);
+    LX_DISPATCH(num_edges, lx_so2_gate_fwd_kernel, LX_COMMA OutF32, y, OutF32{out}, nullptr, num_edges, hidden);
     return launch_status();
 }
 
@@ -466,7 +472,70 @@ int fcb200_lx_so2_gate_bwd(const float* grad_out, const float* y, float* grad_y,
     if (!grad_y) return FCB200_EINVAL;
     if (!aligned16(grad_y)) return FCB200_EALIGN;
     if (num_edges == 0) return FCB200_OK;
-    LX_DISPATCH(num_edges, lx_so2_gate_bwd_kernel, , grad_out, y, grad_y, num_edges, hidden);
+    LX_DISPATCH(num_edges, lx_so2_gate_bwd_kernel, LX_COMMA OutF32, grad_out, y, OutF32{grad_y}, nullptr, num_edges, hidden);
+    return launch_status();
+}
+
+// ---- the same four producers writing the half-precision split the tensor-core contraction reads directly ----
+
+int fcb200_lx_gather_rotate_fwd_h(const float* x, const int32_t* src, const int32_t* tgt, const float* wig, const float* radial,
+                                  void* out_hi, void* out_lo, const float* scale, int64_t num_edges, int64_t num_nodes,
+                                  int32_t channels, int32_t lmax, void* stream) {
+    int rc = lx_check(x, x, num_edges, channels, lmax);
+    if (rc != FCB200_OK) return rc;
+    if (!out_hi || !out_lo || !src || !tgt || !wig || num_nodes < 0) return FCB200_EINVAL;
+    if (!aligned8(out_hi) || !aligned8(out_lo) || (radial && !aligned16(radial))) return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    const OutSplit out{static_cast<__half*>(out_hi), static_cast<__half*>(out_lo), 1.0f};
+    if (radial)
+        LX_DISPATCH(num_edges, lx_gather_rotate_fwd_kernel, LX_COMMA true LX_COMMA OutSplit, x, src, tgt, wig, radial, out, scale,
+                    num_edges, channels);
+    else
+        LX_DISPATCH(num_edges, lx_gather_rotate_fwd_kernel, LX_COMMA false LX_COMMA OutSplit, x, src, tgt, wig, nullptr, out, scale,
+                    num_edges, channels);
+    return launch_status();
+}
+
+int fcb200_lx_rotate_back_bwd_h(const float* grad_out, const float* msg, const float* winv, const int32_t* tgt, void* grad_msg_hi,
+                                void* grad_msg_lo, const float* scale, float* grad_winv, int64_t num_edges, int64_t num_nodes,
+                                int32_t channels, int32_t lmax, void* stream) {
+    int rc = lx_check(grad_out, grad_out, num_edges, channels, lmax);
+    if (rc != FCB200_OK) return rc;
+    if (!winv || !tgt || !grad_msg_hi || !grad_msg_lo || num_nodes < 0) return FCB200_EINVAL;
+    if ((grad_winv != nullptr) && (msg == nullptr)) return FCB200_EINVAL;
+    if (!aligned8(grad_msg_hi) || !aligned8(grad_msg_lo) || (msg && !aligned16(msg))) return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    const OutSplit out{static_cast<__half*>(grad_msg_hi), static_cast<__half*>(grad_msg_lo), 1.0f};
+    if (grad_winv)
+        LX_DISPATCH(num_edges, lx_rotate_back_bwd_kernel, LX_COMMA 0 LX_COMMA true LX_COMMA OutSplit, grad_out, msg, winv, tgt, out,
+                    scale, grad_winv, 1.f, num_edges, channels);
+    else
+        LX_DISPATCH(num_edges, lx_rotate_back_bwd_kernel, LX_COMMA 0 LX_COMMA false LX_COMMA OutSplit, grad_out, nullptr, winv, tgt,
+                    out, scale, nullptr, 1.f, num_edges, channels);
+    return launch_status();
+}
+
+int fcb200_lx_so2_gate_fwd_h(const float* y, void* out_hi, void* out_lo, const float* scale, int64_t num_edges, int32_t hidden,
+                             int32_t lmax, void* stream) {
+    int rc = lx_check(y, y, num_edges, hidden, lmax);
+    if (rc != FCB200_OK) return rc;
+    if (!out_hi || !out_lo) return FCB200_EINVAL;
+    if (!aligned8(out_hi) || !aligned8(out_lo)) return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    const OutSplit out{static_cast<__half*>(out_hi), static_cast<__half*>(out_lo), 1.0f};
+    LX_DISPATCH(num_edges, lx_so2_gate_fwd_kernel, LX_COMMA OutSplit, y, out, scale, num_edges, hidden);
+    return launch_status();
+}
+
+int fcb200_lx_so2_gate_bwd_h(const float* grad_out, const float* y, void* grad_y_hi, void* grad_y_lo, const float* scale,
+                             int64_t num_edges, int32_t hidden, int32_t lmax, void* stream) {
+    int rc = lx_check(grad_out, y, num_edges, hidden, lmax);
+    if (rc != FCB200_OK) return rc;
+    if (!grad_y_hi || !grad_y_lo) return FCB200_EINVAL;
+    if (!aligned8(grad_y_hi) || !aligned8(grad_y_lo)) return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    const OutSplit out{static_cast<__half*>(grad_y_hi), static_cast<__half*>(grad_y_lo), 1.0f};
+    LX_DISPATCH(num_edges, lx_so2_gate_bwd_kernel, LX_COMMA OutSplit, grad_out, y, out, scale, num_edges, hidden);
     return launch_status();
 }
 

@@ -11,7 +11,7 @@
 // index, a thread converts one 32-byte unit in place: same unit index, half the pitch.
 //
 // Structure is that of the TF32 kernel (persistent CTAs, 128 x 128 tiles, N fastest; warp 0 TMA producer
-// and TMEM owner, warp 1 MMA issue, warps 2..5 split A, warps 6..9 epilogue with TMA stores; main and
+// and TMEM owner, warp 1 MMA issue, two groups of four warps split A tiles in turn, four epilogue warps with TMA stores; main and
 // correction accumulators, both double buffered = 512 TMEM columns).  Every mbarrier wait is bounded; on
 // expiry the roles leave their loops, TMEM is released and *status is set to 1.  *status is set to 2 when
 // a scaled A value leaves the finite half range (the result is then invalid).
@@ -26,13 +26,21 @@ namespace f16 {
 constexpr int BM = 128, BN = 128, BK = 32;
 constexpr int kA32Bytes = BM * BK * 4;   // 16 KiB float32 A tile as landed by TMA
 constexpr int kHalfBytes = BM * BK * 2;  // 8 KiB: A_hi, A_lo, W_hi, W_lo tiles
-constexpr int kStageBytes = kA32Bytes + 4 * kHalfBytes;  // 48 KiB
-constexpr int kStages = 4;
-constexpr int kThreads = 320;
+constexpr int kSplitGroups = 2;  // groups of four warps that split A tiles, taking k-steps in turn
 constexpr int kAccCols = 2 * BN;         // main + correction
 constexpr int kTmemCols = 2 * kAccCols;  // double buffered
 constexpr int kEpiBytes = 4 * 2 * 4096;  // 4 warps x 2 buffers x (32 rows x 128 B)
-constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*align*/ + 256 /*barriers*/;
+
+// PRESPLIT: A arrives already split (two half planes written by the producing kernel); no float32 staging
+// tile and no split warps, so a stage is 32 KiB and the ring is deeper.
+template <bool PRESPLIT> struct Cfg {
+    static constexpr int kA32 = PRESPLIT ? 0 : kA32Bytes;
+    static constexpr int kStageBytes = kA32 + 4 * kHalfBytes;  // 32 or 48 KiB
+    static constexpr int kStages = PRESPLIT ? 6 : 4;
+    static constexpr int kSplitWarps = PRESPLIT ? 0 : 4 * kSplitGroups;
+    static constexpr int kThreads = 64 + 32 * kSplitWarps + 128;
+    static constexpr int kSmemBytes = kStages * kStageBytes + kEpiBytes + 1024 /*align*/ + 256 /*barriers*/;
+};
 constexpr float kLoScale = 2048.0f;      // 2^11
 constexpr float kHalfMax = 65504.0f;
 
@@ -105,12 +113,16 @@ __device__ __forceinline__ float split_tile(uint32_t a32, uint32_t a_hi, uint32_
 }
 
 
-__global__ void __launch_bounds__(kThreads, 1)
-    gemm_f16x2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_whi,
-                      const __grid_constant__ CUtensorMap map_wlo, const __grid_constant__ CUtensorMap map_c,
-                      const float* __restrict__ bias, const float* __restrict__ a_scale_ptr, float w_scale, int64_t m_total,
-                      int n_total, int k_total, int tiles_n, int64_t num_tiles, int32_t* __restrict__ status) {
-    constexpr int S = kStages;
+template <bool PRESPLIT>
+__global__ void __launch_bounds__(Cfg<PRESPLIT>::kThreads, 1)
+    gemm_f16x2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_alo,
+                      const __grid_constant__ CUtensorMap map_whi, const __grid_constant__ CUtensorMap map_wlo,
+                      const __grid_constant__ CUtensorMap map_c, const float* __restrict__ bias,
+                      const float* __restrict__ a_scale_ptr, float w_scale, int64_t m_total, int n_total, int k_total, int tiles_n,
+                      int64_t num_tiles, int32_t* __restrict__ status) {
+    using C = Cfg<PRESPLIT>;
+    constexpr int S = C::kStages;
+    constexpr int kStageBytes = C::kStageBytes;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t epi_base = base + S * kStageBytes;
@@ -127,7 +139,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     volatile int* range_flag = reinterpret_cast<volatile int*>(bar_generic + 8 * (3 * S + 4) + 8);
     // a stage: float32 A tile | A_hi | A_lo | W_hi | W_lo
     auto a32_addr = [&](int s) { return base + s * kStageBytes; };
-    auto half_addr = [&](int s, int which) { return base + s * kStageBytes + kA32Bytes + which * kHalfBytes; };
+    auto half_addr = [&](int s, int which) { return base + s * kStageBytes + C::kA32 + which * kHalfBytes; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int num_kb = (k_total + BK - 1) / BK;
@@ -172,8 +184,14 @@ __global__ void __launch_bounds__(kThreads, 1)
                     const uint32_t ph = (uint32_t)((it / S) & 1);
                     ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag);
                     if (!ok) break;
-                    mbar_expect_tx(full_bar(s), kA32Bytes + 2 * kHalfBytes);
-                    tma_load_2d(a32_addr(s), &map_a, kb * BK, (int)(tile_m * BM), full_bar(s));
+                    if (PRESPLIT) {
+                        mbar_expect_tx(full_bar(s), 4 * kHalfBytes);
+                        tma_load_2d(half_addr(s, 0), &map_a, kb * BK, (int)(tile_m * BM), full_bar(s));
+                        tma_load_2d(half_addr(s, 1), &map_alo, kb * BK, (int)(tile_m * BM), full_bar(s));
+                    } else {
+                        mbar_expect_tx(full_bar(s), kA32Bytes + 2 * kHalfBytes);
+                        tma_load_2d(a32_addr(s), &map_a, kb * BK, (int)(tile_m * BM), full_bar(s));
+                    }
                     tma_load_2d(half_addr(s, 2), &map_whi, kb * BK, tile_n * BN, full_bar(s));
                     tma_load_2d(half_addr(s, 3), &map_wlo, kb * BK, tile_n * BN, full_bar(s));
                 }
@@ -193,7 +211,8 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int kb = 0; kb < num_kb; ++kb, ++it) {
                     const int s = (int)(it % S);
                     const uint32_t ph = (uint32_t)((it / S) & 1);
-                    ok = mbar_wait(conv_bar(s), ph, abort_flag);  // A split done (which implies the TMA data landed)
+                    // A split done (which implies the TMA data landed), or just the TMA data when A came split
+                    ok = mbar_wait(PRESPLIT ? full_bar(s) : conv_bar(s), ph, abort_flag);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const uint64_t da_hi = smem_desc64(half_addr(s, 0)), da_lo = smem_desc64(half_addr(s, 1));
@@ -211,13 +230,15 @@ __global__ void __launch_bounds__(kThreads, 1)
                 if (ok) umma_commit(tfull_bar(buf));
             }
         }
-    } else if (warp < 6) {
-        const int tid = threadIdx.x - 64;  // 0..127
+    } else if (warp < 2 + C::kSplitWarps) {
+        const int group = (warp - 2) >> 2;
+        const int tid = (threadIdx.x - 64) & 127;  // 0..127 within the group
         int64_t it = 0;
         bool ok = true;
         float amax = 0.f;
         for (int64_t tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
             for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                if ((int)(it % kSplitGroups) != group) continue;
                 const int s = (int)(it % S);
                 const uint32_t ph = (uint32_t)((it / S) & 1);
                 ok = mbar_wait(full_bar(s), ph, abort_flag);
@@ -258,6 +279,12 @@ __global__ void __launch_bounds__(kThreads, 1)
                 for (int i = 0; i < 32; ++i)
                     r[i] = __float_as_uint(fmaf(__uint_as_float(t[i]), corr_scale, __uint_as_float(r[i]) * out_scale));
                 if (row0 >= m_total || col0 >= n_total) continue;  // sub-tile entirely outside the matrix
+                {  // a half that overflowed upstream shows up here as inf or NaN (exponent bits all set)
+                    uint32_t bad = 0;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) bad |= (uint32_t)((r[i] & 0x7f800000u) == 0x7f800000u);
+                    if (bad) *range_flag = 1;
+                }
                 // the store issued two chunks ago read this staging buffer; let it finish before overwriting
                 const uint32_t stage = epi_base + (uint32_t)((q * 2 + (chunk & 1)) * 4096);
                 if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
@@ -350,6 +377,30 @@ extern "C" int fcb200_split_f16(const float* w, int64_t ldw, void* w_hi, void* w
     return launch_status();
 }
 
+namespace {
+
+template <bool PRESPLIT>
+int launch_f16(const CUtensorMap& ma, const CUtensorMap& malo, const CUtensorMap& mh, const CUtensorMap& ml, const CUtensorMap& mc,
+               const float* bias, const float* a_scale, float w_scale, int64_t m, int n, int k, int32_t* status, cudaStream_t s) {
+    using C = f16::Cfg<PRESPLIT>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        if (cudaFuncSetAttribute(f16::gemm_f16x2_kernel<PRESPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) !=
+            cudaSuccess)
+            return static_cast<int>(cudaGetLastError());
+        attr_set = true;
+    }
+    const int tiles_n = (n + f16::BN - 1) / f16::BN;
+    const int64_t tiles_m = (m + f16::BM - 1) / f16::BM;
+    const int64_t num_tiles = tiles_m * tiles_n;
+    const int grid = (int)(num_tiles < sm_count() ? num_tiles : sm_count());
+    f16::gemm_f16x2_kernel<PRESPLIT><<<grid, C::kThreads, C::kSmemBytes, s>>>(ma, malo, mh, ml, mc, bias, a_scale, w_scale, m, n, k,
+                                                                             tiles_n, num_tiles, status);
+    return launch_status();
+}
+
+}  // namespace
+
 extern "C" int fcb200_gemm_f16x2(const float* a, int64_t lda, const void* w_hi, const void* w_lo, int64_t ldw, float w_scale,
                                  const float* a_scale, const float* bias, float* c, int64_t ldc, int64_t m, int32_t n, int32_t k,
                                  int32_t* status, void* stream) {
@@ -366,17 +417,27 @@ extern "C" int fcb200_gemm_f16x2(const float* a, int64_t lda, const void* w_hi, 
     if (rc) return rc;
     rc = f16::make_map_f32(&mc, c, m, n, ldc, 32);
     if (rc) return rc;
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(f16::gemm_f16x2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, f16::kSmemBytes) != cudaSuccess)
-            return static_cast<int>(cudaGetLastError());
-        attr_set = true;
-    }
-    const int tiles_n = (n + f16::BN - 1) / f16::BN;
-    const int64_t tiles_m = (m + f16::BM - 1) / f16::BM;
-    const int64_t num_tiles = tiles_m * tiles_n;
-    const int grid = (int)(num_tiles < sm_count() ? num_tiles : sm_count());
-    f16::gemm_f16x2_kernel<<<grid, f16::kThreads, f16::kSmemBytes, static_cast<cudaStream_t>(stream)>>>(
-        ma, mh, ml, mc, bias, a_scale, w_scale, m, n, k, tiles_n, num_tiles, status);
-    return launch_status();
+    return launch_f16<false>(ma, ma, mh, ml, mc, bias, a_scale, w_scale, m, n, k, status, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int fcb200_gemm_f16x2_presplit(const void* a_hi, const void* a_lo, int64_t lda, const void* w_hi, const void* w_lo,
+                                          int64_t ldw, float w_scale, const float* a_scale, const float* bias, float* c,
+                                          int64_t ldc, int64_t m, int32_t n, int32_t k, int32_t* status, void* stream) {
+    if (!a_hi || !a_lo || !w_hi || !w_lo || !c || m < 0 || n <= 0 || k <= 0 || !(w_scale > 0.f)) return FCB200_EINVAL;
+    if (n % 4 || k % 8 || lda % 8 || ldw % 8 || ldc % 4 || lda < k || ldw < k || ldc < n) return FCB200_EINVAL;
+    if (!aligned16(a_hi) || !aligned16(a_lo) || !aligned16(w_hi) || !aligned16(w_lo) || !aligned16(c) || (bias && !aligned16(bias)))
+        return FCB200_EALIGN;
+    if (m == 0) return FCB200_OK;
+    CUtensorMap mah, mal, mh, ml, mc;
+    int rc = f16::make_map_f16(&mah, a_hi, m, k, lda);
+    if (rc) return rc;
+    rc = f16::make_map_f16(&mal, a_lo, m, k, lda);
+    if (rc) return rc;
+    rc = f16::make_map_f16(&mh, w_hi, n, k, ldw);
+    if (rc) return rc;
+    rc = f16::make_map_f16(&ml, w_lo, n, k, ldw);
+    if (rc) return rc;
+    rc = f16::make_map_f32(&mc, c, m, n, ldc, 32);
+    if (rc) return rc;
+    return launch_f16<true>(mah, mal, mh, ml, mc, bias, a_scale, w_scale, m, n, k, status, static_cast<cudaStream_t>(stream));
 }

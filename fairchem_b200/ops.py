@@ -421,6 +421,98 @@ def gemm_f16x2_(a: Tensor, w_hi: Tensor, w_lo: Tensor, w_scale: float, a_scale: 
              _stream()), nbytes=4 * (m * k + n * k + m * n), flops=2 * m * n * k)
 
 
+def _h16(*tensors):
+    for t in tensors:
+        if not t.is_cuda or t.dtype != torch.float16 or not t.is_contiguous():
+            raise _lib.FairchemB200Error("split outputs must be contiguous float16 CUDA tensors")
+
+
+@_op("gather_rotate_fwd_h", ("out_hi", "out_lo"))
+def gather_rotate_fwd_h_(x: Tensor, src: Tensor, tgt: Tensor, wig: Tensor, radial: Optional[Tensor], out_hi: Tensor,
+                         out_lo: Tensor, scale: Optional[Tensor]) -> None:
+    """gather_rotate_fwd_ writing the half-precision split (two planes of the output's shape) the contraction reads."""
+    _chk(x, src, tgt, wig, radial, scale)
+    _f32(x, wig, radial, scale)
+    _h16(out_hi, out_lo)
+    e, c = src.shape[0], x.shape[2]
+    s = _shape(_BY_NL, x.shape[1], "rows per node")
+    nbytes = e * (4 * (2 * s.nl * c + 2 * s.nm * c + s.nw + (2 * s.nrad * c if radial is not None else 0)) + 8)
+    args = (_p(x), _p(src), _p(tgt), _p(wig), _p(radial), _p(out_hi), _p(out_lo), _p(scale), e, x.shape[0], c)
+    if _lx(s):
+        _launch("gather_rotate_fwd", "fcb200_lx_gather_rotate_fwd_h", args + (s.lmax, _stream()), nbytes=nbytes,
+                flops=e * 2 * s.nw * 2 * c)
+    else:
+        _launch("gather_rotate_fwd", "fcb200_gather_rotate_fwd_h", args + (_stream(),), nbytes=nbytes, flops=e * 2 * s.nw * 2 * c)
+
+
+@_op("rotate_back_bwd_h", ("grad_msg_hi", "grad_msg_lo", "grad_winv"))
+def rotate_back_bwd_h_(grad_out: Tensor, msg: Optional[Tensor], winv: Tensor, tgt: Tensor, grad_msg_hi: Tensor,
+                       grad_msg_lo: Tensor, scale: Optional[Tensor], grad_winv: Optional[Tensor]) -> None:
+    _chk(grad_out, msg, winv, tgt, grad_winv, scale)
+    _f32(grad_out, msg, winv, grad_winv, scale)
+    _h16(grad_msg_hi, grad_msg_lo)
+    e, c = tgt.shape[0], grad_out.shape[2]
+    s = _shape(_BY_NL, grad_out.shape[1], "rows per node")
+    nbytes = e * 4 * (s.nl * c + s.nm * c * (2 if msg is not None else 1) + 2 * s.nw + 1)
+    args = (_p(grad_out), _p(msg), _p(winv), _p(tgt), _p(grad_msg_hi), _p(grad_msg_lo), _p(scale), _p(grad_winv), e,
+            grad_out.shape[0], c)
+    if _lx(s):
+        _launch("rotate_back_bwd", "fcb200_lx_rotate_back_bwd_h", args + (s.lmax, _stream()), nbytes=nbytes, flops=e * 4 * s.nw * c)
+    else:
+        _launch("rotate_back_bwd", "fcb200_rotate_back_bwd_h", args + (_stream(),), nbytes=nbytes, flops=e * 4 * s.nw * c)
+
+
+@_op("so2_gate_fwd_h", ("out_hi", "out_lo"))
+def so2_gate_fwd_h_(y: Tensor, out_hi: Tensor, out_lo: Tensor, scale: Optional[Tensor], hidden: int) -> None:
+    _chk(y, scale)
+    _f32(y, scale)
+    _h16(out_hi, out_lo)
+    s = _shape(_BY_GATE, y.shape[1] // hidden, "gate input rows")
+    nbytes = y.shape[0] * 4 * hidden * (s.lmax + 2 * s.nm)
+    args = (_p(y), _p(out_hi), _p(out_lo), _p(scale), y.shape[0], hidden)
+    if _lx(s):
+        _launch("so2_gate_fwd", "fcb200_lx_so2_gate_fwd_h", args + (s.lmax, _stream()), nbytes=nbytes)
+    else:
+        _launch("so2_gate_fwd", "fcb200_so2_gate_fwd_h", args + (_stream(),), nbytes=nbytes)
+
+
+@_op("so2_gate_bwd_h", ("grad_y_hi", "grad_y_lo"))
+def so2_gate_bwd_h_(grad_out: Tensor, y: Tensor, grad_y_hi: Tensor, grad_y_lo: Tensor, scale: Optional[Tensor],
+                    hidden: int) -> None:
+    _chk(grad_out, y, scale)
+    _f32(grad_out, y, scale)
+    _h16(grad_y_hi, grad_y_lo)
+    s = _shape(_BY_GATE, y.shape[1] // hidden, "gate input rows")
+    nbytes = y.shape[0] * 4 * hidden * (2 * s.lmax + 3 * s.nm)
+    args = (_p(grad_out), _p(y), _p(grad_y_hi), _p(grad_y_lo), _p(scale), y.shape[0], hidden)
+    if _lx(s):
+        _launch("so2_gate_bwd", "fcb200_lx_so2_gate_bwd_h", args + (s.lmax, _stream()), nbytes=nbytes)
+    else:
+        _launch("so2_gate_bwd", "fcb200_so2_gate_bwd_h", args + (_stream(),), nbytes=nbytes)
+
+
+@_op("gemm_f16x2_presplit", ("c", "status"))
+def gemm_f16x2_presplit_(a_hi: Tensor, a_lo: Tensor, w_hi: Tensor, w_lo: Tensor, w_scale: float, a_scale: Optional[Tensor],
+                         bias: Optional[Tensor], c: Tensor, status: Tensor) -> None:
+    """gemm_f16x2_ with A given as the two half planes a producer kernel wrote (row-strided views allowed)."""
+    for t in (a_hi, a_lo):
+        if not t.is_cuda or t.dtype != torch.float16 or t.dim() != 2 or t.stride(1) != 1 or t.shape != a_hi.shape \
+                or t.stride(0) != a_hi.stride(0):
+            raise _lib.FairchemB200Error("gemm_f16x2_presplit: need 2-D float16 CUDA planes of one shape and row stride")
+    if not c.is_cuda or c.dtype != torch.float32 or c.dim() != 2 or c.stride(1) != 1:
+        raise _lib.FairchemB200Error("gemm_f16x2_presplit: need a 2-D float32 CUDA c with unit inner stride")
+    for t in (w_hi, w_lo):
+        if not t.is_cuda or t.dtype != torch.float16 or t.dim() != 2 or not t.is_contiguous() or t.shape != w_hi.shape:
+            raise _lib.FairchemB200Error("gemm_f16x2_presplit: need contiguous 2-D float16 CUDA weight parts of one shape")
+    _chk(bias, status, a_scale)
+    m, n, k = a_hi.shape[0], w_hi.shape[0], a_hi.shape[1]
+    if w_hi.shape[1] != k:
+        raise _lib.FairchemB200Error("gemm_f16x2_presplit: inner dimensions differ")
+    _launch("gemm_f16x2", "fcb200_gemm_f16x2_presplit",
+            (_p(a_hi), _p(a_lo), a_hi.stride(0), _p(w_hi), _p(w_lo), k, w_scale, _p(a_scale), _p(bias), _p(c), c.stride(0), m, n, k,
+             _p(status), _stream()), nbytes=4 * (m * k + n * k + m * n), flops=2 * m * n * k)
+
+
 def split_f16(w: Tensor):
     """(hi, lo, scale): half-precision parts of w * scale, scale = the power of two that puts max|w| in [2^13, 2^14)."""
     w = w.detach().contiguous()

@@ -318,6 +318,45 @@ int fcb200_gemm_f16x2(const float* a, int64_t lda, const void* w_hi, const void*
                       const float* a_scale, const float* bias, float* c, int64_t ldc, int64_t m, int32_t n, int32_t k,
                       int32_t* status, void* stream);
 
+/*
+ * fcb200_gemm_f16x2 with A already split by the kernel that produced it: a_hi / a_lo [M, K] half, row stride
+ * lda (halves, multiple of 8), both of (A * *a_scale).  The contraction then needs no conversion pass over A
+ * in shared memory; `a_scale` is only used to undo the scale in the epilogue.  *status = 2 also when an
+ * output is not finite (a producer's half overflowed).
+ */
+int fcb200_gemm_f16x2_presplit(const void* a_hi, const void* a_lo, int64_t lda, const void* w_hi, const void* w_lo,
+                               int64_t ldw, float w_scale, const float* a_scale, const float* bias, float* c, int64_t ldc,
+                               int64_t m, int32_t n, int32_t k, int32_t* status, void* stream);
+
+/*
+ * The four kernels whose output is consumed only by an SO(2) contraction, writing that output as the
+ * half-precision split (two planes `*_hi`, `*_lo` of the float32 tensor's shape, values times *scale; scale
+ * is a DEVICE pointer to a power of two, or NULL for 1) instead of float32: same bytes written, and the
+ * contraction reads them with fcb200_gemm_f16x2_presplit.  Arguments otherwise as in the float32 versions
+ * (fcb200_gather_rotate_fwd, fcb200_rotate_back_bwd, fcb200_so2_gate_fwd, fcb200_so2_gate_bwd and their
+ * fcb200_lx_* counterparts).
+ */
+int fcb200_gather_rotate_fwd_h(const float* x, const int32_t* src, const int32_t* tgt, const float* wig, const float* radial,
+                               void* out_hi, void* out_lo, const float* scale, int64_t num_edges, int64_t num_nodes,
+                               int32_t channels, void* stream);
+int fcb200_rotate_back_bwd_h(const float* grad_out, const float* msg, const float* winv, const int32_t* tgt, void* grad_msg_hi,
+                             void* grad_msg_lo, const float* scale, float* grad_winv, int64_t num_edges, int64_t num_nodes,
+                             int32_t channels, void* stream);
+int fcb200_so2_gate_fwd_h(const float* y, void* out_hi, void* out_lo, const float* scale, int64_t num_edges, int32_t hidden,
+                          void* stream);
+int fcb200_so2_gate_bwd_h(const float* grad_out, const float* y, void* grad_y_hi, void* grad_y_lo, const float* scale,
+                          int64_t num_edges, int32_t hidden, void* stream);
+int fcb200_lx_gather_rotate_fwd_h(const float* x, const int32_t* src, const int32_t* tgt, const float* wig,
+                                  const float* radial, void* out_hi, void* out_lo, const float* scale, int64_t num_edges,
+                                  int64_t num_nodes, int32_t channels, int32_t lmax, void* stream);
+int fcb200_lx_rotate_back_bwd_h(const float* grad_out, const float* msg, const float* winv, const int32_t* tgt,
+                                void* grad_msg_hi, void* grad_msg_lo, const float* scale, float* grad_winv, int64_t num_edges,
+                                int64_t num_nodes, int32_t channels, int32_t lmax, void* stream);
+int fcb200_lx_so2_gate_fwd_h(const float* y, void* out_hi, void* out_lo, const float* scale, int64_t num_edges, int32_t hidden,
+                             int32_t lmax, void* stream);
+int fcb200_lx_so2_gate_bwd_h(const float* grad_out, const float* y, void* grad_y_hi, void* grad_y_lo, const float* scale,
+                             int64_t num_edges, int32_t hidden, int32_t lmax, void* stream);
+
 /* w [rows, cols] float32 (row stride ldw) -> contiguous half hi / lo parts of w * scale (see fcb200_gemm_f16x2). */
 int fcb200_split_f16(const float* w, int64_t ldw, void* w_hi, void* w_lo, float scale, int64_t rows, int64_t cols,
                      void* stream);
