@@ -397,7 +397,7 @@ def main():
     ap.add_argument("--workload", default="water_100k", choices=sorted(synthetic.WORKLOADS))
     ap.add_argument("--model", default="uma_s", choices=sorted(MODELS),
                     help="uma_s: the configuration the metric is quoted on; escn_md_l4: the 10-layer lmax=4/mmax=2 shape")
-    ap.add_argument("--precision", type=int, default=3, choices=[0, 1, 2, 3])
+    ap.add_argument("--precision", type=int, default=2, choices=[0, 1, 2, 3])
     ap.add_argument("--chunk", type=int, default=131072)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--skip-cpu", action="store_true")

@@ -330,14 +330,14 @@ class _EdgeCtx:
 
 
 class _GemmState:
-    """How the dense contractions run: 3 = tcgen05 TF32 with the hi/lo split (float32-level accuracy,
-    default), 2 = tcgen05 half-precision hi/lo split (float32-level accuracy at twice the TF32 issue rate;
-    operands must fit the half range after a power-of-two scale), 1 = single-pass tcgen05 TF32 (the
+    """How the dense contractions run: 2 = tcgen05 half-precision hi/lo split (default: float32-level accuracy
+    at twice the TF32 issue rate; operands must fit the half range after a power-of-two scale, which the kernels
+    check), 3 = tcgen05 TF32 with the hi/lo split (float32-level accuracy, no range condition), 1 = single-pass tcgen05 TF32 (the
     counterpart of the reference's ``tf32`` inference setting,
     src/fairchem/core/units/mlip_unit/api/inference.py:123-226), 0 = cuBLAS float32 through torch (kept
     for A/B measurements only)."""
 
-    precision = 3
+    precision = 2
     status = None          # device int32 raised by the kernel when a bounded wait expires or a value leaves the half range
     transposed = {}        # (ptr, shape, stride) of a weight view -> (weight ref, transposed contiguous copy)
     split = {}             # same key -> (weight ref, TF32 high part, TF32 low part)

@@ -355,12 +355,12 @@ def test_backend_ops_lmax4(ops):
     torch.testing.assert_close(back, ref_back, **FWD_TOL)
 
 
-def test_l4_half_split_gemm_mode_matches_reference_golden(ops, golden):
+def test_l4_tf32_split_gemm_mode_matches_reference_golden(ops, golden):
     from fairchem_b200 import backbone as B
 
     g = golden("escn_md_l4.npz")
     sd = weights.random_init_state_dict(weights.ESCN_MD_L4, 0)
-    B.set_gemm_precision(2)
+    B.set_gemm_precision(3)
     try:
         model = B.build_model(weights.ESCN_MD_L4, sd, edge_chunk_size=1024)
         for name in sorted(L4_CASES):
@@ -368,4 +368,4 @@ def test_l4_half_split_gemm_mode_matches_reference_golden(ops, golden):
             assert np.max(np.abs(e - g[f"{name}_energy"]) / np.abs(g[f"{name}_energy"])) < E_RTOL, name
             assert np.max(np.abs(f - g[f"{name}_forces"])) < F_ATOL, name
     finally:
-        B.set_gemm_precision(3)
+        B.set_gemm_precision(2)

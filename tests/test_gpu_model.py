@@ -102,13 +102,13 @@ def test_isolated_atom_and_empty_graph(model):
     assert np.isfinite(e).all() and np.abs(f).max() < 1e-6
 
 
-def test_half_split_gemm_mode_matches_reference_golden(golden):
-    """Precision 2 (half-precision hi/lo operands, gradients scaled into the half range) meets the same bars."""
+def test_tf32_split_gemm_mode_matches_reference_golden(golden):
+    """Precision 3 (TF32 hi/lo operands; the default is the half-precision split) meets the same bars."""
     from fairchem_b200 import backbone as B
 
     g = golden("uma_s_energy_forces.npz")
     sd = weights.random_init_state_dict(weights.UMA_S, 0)
-    B.set_gemm_precision(2)
+    B.set_gemm_precision(3)
     try:
         model = (B.build_model(weights.UMA_S, sd, edge_chunk_size=4096), sd)
         for name in sorted(CASES):
@@ -117,4 +117,4 @@ def test_half_split_gemm_mode_matches_reference_golden(golden):
             assert np.max(np.abs(e - e_ref) / np.abs(e_ref)) < E_RTOL, name
             assert np.max(np.abs(f - f_ref)) < F_ATOL, name
     finally:
-        B.set_gemm_precision(3)
+        B.set_gemm_precision(2)
