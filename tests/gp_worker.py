@@ -1,6 +1,6 @@
 """Worker for tests/test_gpu_multi.py: one rank of a graph-parallel energy+force evaluation.
 
-Launched with ``python -m torch.distributed.run --nproc-per-node N tests/gp_worker.py OUT.pt [natoms]``.
+Launched with ``python -m torch.distributed.run --nproc-per-node N tests/gp_worker.py OUT.pt [natoms] [uma_s|escn_md_l4]``.
 """
 
 import os
@@ -19,12 +19,13 @@ from fairchem_b200.backbone import build_model  # noqa: E402
 def main():
     out_path = sys.argv[1]
     natoms = int(sys.argv[2]) if len(sys.argv) > 2 else 3000
+    cfg = weights.ESCN_MD_L4 if len(sys.argv) > 3 and sys.argv[3] == "escn_md_l4" else weights.UMA_S
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
-    sd = weights.random_init_state_dict(weights.UMA_S, 0)
-    bb, head = build_model(weights.UMA_S, sd, device=dev, edge_chunk_size=8192)
+    sd = weights.random_init_state_dict(cfg, 0)
+    bb, head = build_model(cfg, sd, device=dev, edge_chunk_size=8192)
     host = synthetic.water_box(natoms, seed=1)
     data = host.to(dev)
     stepper = parallel.PartitionedStepper(bb, head, host, dev, rank, world)

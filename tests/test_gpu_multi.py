@@ -15,15 +15,15 @@ pytestmark = pytest.mark.gpu
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-@pytest.mark.parametrize("world", [2, 4])
-def test_partitioned_run_matches_single_gpu(world):
+@pytest.mark.parametrize("world,model,natoms", [(2, "uma_s", 3000), (4, "uma_s", 3000), (2, "escn_md_l4", 1200)])
+def test_partitioned_run_matches_single_gpu(world, model, natoms):
     if not torch.cuda.is_available() or torch.cuda.device_count() < world:
         pytest.skip(f"needs {world} CUDA devices")
     from fairchem_b200.backbone import build_model
 
-    natoms = 3000
-    sd = weights.random_init_state_dict(weights.UMA_S, 0)
-    bb, head = build_model(weights.UMA_S, sd, edge_chunk_size=8192)
+    cfg = weights.ESCN_MD_L4 if model == "escn_md_l4" else weights.UMA_S
+    sd = weights.random_init_state_dict(cfg, 0)
+    bb, head = build_model(cfg, sd, edge_chunk_size=8192)
     d = synthetic.water_box(natoms, seed=1).to("cuda")
     out = head(d, bb(d))
     e1, f1 = out["energy"].cpu().numpy(), out["forces"].cpu().numpy()
@@ -32,7 +32,7 @@ def test_partitioned_run_matches_single_gpu(world):
         env = dict(os.environ, NCCL_NVLS_ENABLE="0")
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={world}",
                "--master-addr", "127.0.0.1", "--master-port", str(29500 + world), os.path.join(ROOT, "tests", "gp_worker.py"),
-               path, str(natoms)]
+               path, str(natoms), model]
         res = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
         assert res.returncode == 0, res.stdout[-2000:] + res.stderr[-4000:]
         got = torch.load(path)
