@@ -114,12 +114,11 @@ __device__ __forceinline__ float split_tile(uint32_t a32, uint32_t a_hi, uint32_
 
 
 template <bool PRESPLIT>
-__global__ void __launch_bounds__(Cfg<PRESPLIT>::kThreads, 1)
-    gemm_f16x2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_alo,
-                      const __grid_constant__ CUtensorMap map_whi, const __grid_constant__ CUtensorMap map_wlo,
-                      const __grid_constant__ CUtensorMap map_c, const float* __restrict__ bias,
-                      const float* __restrict__ a_scale_ptr, float w_scale, int64_t m_total, int n_total, int k_total, int tiles_n,
-                      int64_t num_tiles, int32_t* __restrict__ status) {
+__device__ __forceinline__ void gemm_f16x2_body(const CUtensorMap& map_a, const CUtensorMap& map_alo, const CUtensorMap& map_whi,
+                                                const CUtensorMap& map_wlo, const CUtensorMap& map_c,
+                                                const float* __restrict__ bias, const float* __restrict__ a_scale_ptr,
+                                                float w_scale, int64_t m_total, int n_total, int k_total, int tiles_n,
+                                                int64_t num_tiles, int32_t* __restrict__ status) {
     using C = Cfg<PRESPLIT>;
     constexpr int S = C::kStages;
     constexpr int kStageBytes = C::kStageBytes;
@@ -324,6 +323,27 @@ __global__ void __launch_bounds__(Cfg<PRESPLIT>::kThreads, 1)
     }
 }
 
+// A as float32, split by the kernel
+__global__ void __launch_bounds__(Cfg<false>::kThreads, 1)
+    gemm_f16x2_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_whi,
+                      const __grid_constant__ CUtensorMap map_wlo, const __grid_constant__ CUtensorMap map_c,
+                      const float* __restrict__ bias, const float* __restrict__ a_scale_ptr, float w_scale, int64_t m_total,
+                      int n_total, int k_total, int tiles_n, int64_t num_tiles, int32_t* __restrict__ status) {
+    gemm_f16x2_body<false>(map_a, map_a, map_whi, map_wlo, map_c, bias, a_scale_ptr, w_scale, m_total, n_total, k_total, tiles_n,
+                           num_tiles, status);
+}
+
+// A as the two half planes its producer wrote
+__global__ void __launch_bounds__(Cfg<true>::kThreads, 1)
+    gemm_f16x2_presplit_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
+                               const __grid_constant__ CUtensorMap map_whi, const __grid_constant__ CUtensorMap map_wlo,
+                               const __grid_constant__ CUtensorMap map_c, const float* __restrict__ bias,
+                               const float* __restrict__ a_scale_ptr, float w_scale, int64_t m_total, int n_total, int k_total,
+                               int tiles_n, int64_t num_tiles, int32_t* __restrict__ status) {
+    gemm_f16x2_body<true>(map_ahi, map_alo, map_whi, map_wlo, map_c, bias, a_scale_ptr, w_scale, m_total, n_total, k_total, tiles_n,
+                          num_tiles, status);
+}
+
 // w [rows, cols] float32 with row stride ldw -> contiguous half hi / lo [rows, cols], both of (w * scale)
 __global__ void split_f16_kernel(const float* __restrict__ w, int64_t ldw, __half* __restrict__ hi, __half* __restrict__ lo,
                                  float scale, int64_t rows, int64_t cols) {
@@ -385,17 +405,23 @@ int launch_f16(const CUtensorMap& ma, const CUtensorMap& malo, const CUtensorMap
     using C = f16::Cfg<PRESPLIT>;
     static bool attr_set = false;
     if (!attr_set) {
-        if (cudaFuncSetAttribute(f16::gemm_f16x2_kernel<PRESPLIT>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes) !=
-            cudaSuccess)
-            return static_cast<int>(cudaGetLastError());
+        const cudaError_t err = PRESPLIT ? cudaFuncSetAttribute(f16::gemm_f16x2_presplit_kernel,
+                                                                cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)
+                                         : cudaFuncSetAttribute(f16::gemm_f16x2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                                                C::kSmemBytes);
+        if (err != cudaSuccess) return static_cast<int>(cudaGetLastError());
         attr_set = true;
     }
     const int tiles_n = (n + f16::BN - 1) / f16::BN;
     const int64_t tiles_m = (m + f16::BM - 1) / f16::BM;
     const int64_t num_tiles = tiles_m * tiles_n;
     const int grid = (int)(num_tiles < sm_count() ? num_tiles : sm_count());
-    f16::gemm_f16x2_kernel<PRESPLIT><<<grid, C::kThreads, C::kSmemBytes, s>>>(ma, malo, mh, ml, mc, bias, a_scale, w_scale, m, n, k,
-                                                                             tiles_n, num_tiles, status);
+    if (PRESPLIT)
+        f16::gemm_f16x2_presplit_kernel<<<grid, C::kThreads, C::kSmemBytes, s>>>(ma, malo, mh, ml, mc, bias, a_scale, w_scale, m, n, k,
+                                                                                tiles_n, num_tiles, status);
+    else
+        f16::gemm_f16x2_kernel<<<grid, C::kThreads, C::kSmemBytes, s>>>(ma, mh, ml, mc, bias, a_scale, w_scale, m, n, k, tiles_n,
+                                                                       num_tiles, status);
     return launch_status();
 }
 

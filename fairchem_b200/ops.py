@@ -508,7 +508,7 @@ def gemm_f16x2_presplit_(a_hi: Tensor, a_lo: Tensor, w_hi: Tensor, w_lo: Tensor,
     m, n, k = a_hi.shape[0], w_hi.shape[0], a_hi.shape[1]
     if w_hi.shape[1] != k:
         raise _lib.FairchemB200Error("gemm_f16x2_presplit: inner dimensions differ")
-    _launch("gemm_f16x2", "fcb200_gemm_f16x2_presplit",
+    _launch("gemm_f16x2_presplit", "fcb200_gemm_f16x2_presplit",
             (_p(a_hi), _p(a_lo), a_hi.stride(0), _p(w_hi), _p(w_lo), k, w_scale, _p(a_scale), _p(bias), _p(c), c.stride(0), m, n, k,
              _p(status), _stream()), nbytes=4 * (m * k + n * k + m * n), flops=2 * m * n * k)
 
