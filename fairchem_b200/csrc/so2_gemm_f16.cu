@@ -55,15 +55,16 @@ __device__ __forceinline__ uint64_t smem_desc64(uint32_t addr) {
     return d;
 }
 
-// tcgen05 instruction descriptor: D=f32, A=B=f16 (format 0), both K-major, N=BN, M=BM
-constexpr uint32_t kInstrDesc = (1u << 4) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+// tcgen05 instruction descriptor: D=f32, A=B=f16 (format 0), both K-major, M=BM, N = BN or 2*BN
+constexpr uint32_t instr_desc(int n) { return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(BM >> 4) << 24); }
 
+template <int N>
 __device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
         "setp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8}, p;\n\t}"
-        ::"r"(tmem_d), "l"(da), "l"(db), "r"(kInstrDesc), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(instr_desc(N)), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u)
         : "memory");
 }
 
@@ -214,15 +215,17 @@ __device__ __forceinline__ void gemm_f16x2_body(const CUtensorMap& map_a, const 
                     ok = mbar_wait(PRESPLIT ? full_bar(s) : conv_bar(s), ph, abort_flag);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    // The W_hi and W_lo tiles are adjacent in shared memory, so one 256-wide MMA on a_hi yields
+                    // a_hi*w_hi in the main accumulator and a_hi*w_lo in the correction accumulator beside it (a_hi is
+                    // read once for both); a 128-wide MMA then adds a_lo*w_hi to the correction accumulator.
                     const uint64_t da_hi = smem_desc64(half_addr(s, 0)), da_lo = smem_desc64(half_addr(s, 1));
-                    const uint64_t dw_hi = smem_desc64(half_addr(s, 2)), dw_lo = smem_desc64(half_addr(s, 3));
+                    const uint64_t dw = smem_desc64(half_addr(s, 2));
 #pragma unroll
                     for (int j = 0; j < BK / 16; ++j) {
                         const uint64_t adv = (uint64_t)(j * 2);  // 16 halves = 32 bytes per MMA, in 16-byte units
                         const uint32_t first = (kb > 0 || j > 0) ? 1u : 0u;
-                        umma_f16(acc + BN, da_lo + adv, dw_hi + adv, first);
-                        umma_f16(acc + BN, da_hi + adv, dw_lo + adv, 1u);
-                        umma_f16(acc, da_hi + adv, dw_hi + adv, first);
+                        umma_f16<2 * BN>(acc, da_hi + adv, dw + adv, first);
+                        umma_f16<BN>(acc + BN, da_lo + adv, dw + adv, 1u);
                     }
                     umma_commit(empty_bar(s));  // frees the stage once these MMAs have read it
                 }
