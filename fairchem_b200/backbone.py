@@ -594,13 +594,14 @@ def _conv_weights(conv: "SO2Convolution"):
     return (conv.fc_m0.weight.detach(), _block_weight(conv.so2_m_conv[0].fc.weight), _block_weight(conv.so2_m_conv[1].fc.weight))
 
 
-def _conv_forward(conv: "SO2Convolution", x):
-    """SO(2) convolution of M-major rows x [E, NM*Cin] (float32 or pre-split) -> float32 [E, extra + NM*Cout]."""
+def _conv_forward(conv: "SO2Convolution", x, out=None):
+    """SO(2) convolution of M-major rows x [E, NM*Cin] (float32 or pre-split) -> float32 [E, extra + NM*Cout]
+    (written into ``out`` when given)."""
     w0, w1, w2 = _conv_weights(conv)
     n0, n1, n2 = w0.shape[0], w1.shape[0], w2.shape[0]
     k0, k1 = w0.shape[1], w1.shape[1]
     ref = x[0] if isinstance(x, tuple) else x
-    y = torch.empty(ref.shape[0], n0 + n1 + n2, dtype=torch.float32, device=ref.device)
+    y = out if out is not None else torch.empty(ref.shape[0], n0 + n1 + n2, dtype=torch.float32, device=ref.device)
     _contract(_cols(x, 0, k0), w0, conv.fc_m0.bias.detach(), y[:, :n0], None)
     _contract(_cols(x, k0, k0 + k1), w1, None, y[:, n0:n0 + n1], None)
     _contract(_cols(x, k0 + k1, ref.shape[1]), w2, None, y[:, n0 + n1:], None)
@@ -662,7 +663,11 @@ class _EdgeBlockFn(torch.autograd.Function):
         nl = x.shape[1]
         nm = ops.SHAPES[ew.lmax].nm
         out = torch.zeros(g.num_targets, nl, c, dtype=x.dtype, device=x.device)
-        kept = []
+        # level 1 keeps the conv-1 outputs (the backward then skips the gather+rotate and the conv-1 GEMMs), level 2
+        # also the messages (no recomputation but the radial MLP); one buffer per layer, chunks write their slices
+        h = ew.hidden
+        y_all = torch.empty(g.num_edges, (ew.lmax + nm) * h, dtype=x.dtype, device=x.device) if keep_level >= 1 else None
+        msg_all = torch.empty(g.num_edges, nm, c, dtype=x.dtype, device=x.device) if keep_level >= 2 else None
         with torch.no_grad():
             for ch in ectx.chunks:
                 sl = slice(ch.e0, ch.e1)
@@ -670,16 +675,13 @@ class _EdgeBlockFn(torch.autograd.Function):
                 rad = _radial(ew.so2_conv_1.rad_func, tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb)
                 m = _gather_rotate(x, g, sl, wig, rad, nm)
                 del rad
-                y = _conv_forward(ew.so2_conv_1, m)
+                y = _conv_forward(ew.so2_conv_1, m, out=None if y_all is None else y_all[sl])
                 del m
-                msg = _conv_forward(ew.so2_conv_2, _gate(y, ew.hidden, nm)).view(ec, nm, c)
+                msg = _conv_forward(ew.so2_conv_2, _gate(y, h, nm),
+                                    out=None if msg_all is None else msg_all[sl].view(ec, nm * c)).view(ec, nm, c)
                 ops.rotate_back_reduce_fwd_.raw(msg, winv[sl], ch.row_ptr, out[ch.n0:ch.n1])
-                if keep_level >= 2:
-                    kept.append((y, msg))  # the backward is then free of any recomputation but the radial MLP
-                elif keep_level == 1:
-                    kept.append((y, None))  # the backward skips the gather+rotate and the conv-1 GEMMs
         ctx.save_for_backward(x, wig, winv, gauss)
-        ctx.ew, ctx.tables, ctx.ectx, ctx.nb, ctx.kept = ew, tables, ectx, nb, kept
+        ctx.ew, ctx.tables, ctx.ectx, ctx.nb, ctx.kept = ew, tables, ectx, nb, (y_all, msg_all)
         return out
 
     @staticmethod
@@ -699,7 +701,7 @@ class _EdgeBlockFn(torch.autograd.Function):
         gwig = torch.empty_like(wig)
         gwinv = torch.empty_like(winv)
         ggauss = torch.empty_like(gauss)
-        kept = ctx.kept
+        y_all, msg_all = ctx.kept
         ctx.kept = None
         scale = _GemmState.a_scale  # the power of two the gradient operands of this block are written with
         for ci, ch in enumerate(ectx.chunks):
@@ -709,10 +711,8 @@ class _EdgeBlockFn(torch.autograd.Function):
                 g_c = gauss[sl].detach().requires_grad_(True)
                 rad = _radial(ew.so2_conv_1.rad_func, tables, g_c, ectx.z_src[sl], ectx.z_tgt[sl], nb)
             rad_d = rad.detach()
-            y = msg = None
-            if kept:
-                y, msg = kept[ci]
-                kept[ci] = None
+            y = None if y_all is None else y_all[sl]
+            msg = None if msg_all is None else msg_all[sl]
             if y is None:
                 y = _conv_forward(ew.so2_conv_1, _gather_rotate(x, g, sl, wig, rad_d, nm))
             if msg is None:
@@ -877,6 +877,29 @@ class eSCNMDBackboneB200(nn.Module):
         return self
 
     # -- forward -----------------------------------------------------------------------------
+    def _keep_level_for_next_layer(self, num_edges: int, device) -> int:
+        """What the next layer keeps per edge for its backward pass, decided from the memory that is free now
+        (earlier layers' kept buffers are already allocated): the highest level that leaves a reserve for the
+        per-chunk temporaries of both passes."""
+        if self.keep_level is not None:
+            return self.keep_level
+        if device.type != "cuda":
+            return 0
+        free, total = torch.cuda.mem_get_info(device)
+        # memory the caching allocator already holds but is not using counts as available
+        avail = free + torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
+        sh = ops.SHAPES[self.lmax]
+        need_1 = num_edges * (sh.lmax + sh.nm) * self.hidden_channels * 4
+        need_2 = need_1 + num_edges * sh.nm * self.sphere_channels * 4
+        # a chunk's temporaries measure about 5 operand buffers [E_c, NM*2C] in the backward pass; allow 10
+        chunk = min(num_edges, int(1.25 * self.edge_chunk_size))
+        reserve = 0.06 * total + 10 * chunk * sh.nm * 2 * self.sphere_channels * 4
+        if need_2 + reserve < avail:
+            return 2
+        if need_1 + reserve < avail:
+            return 1
+        return 0
+
     def _tables(self, rad: RadialMLP):
         nb, ec = self.num_distance_basis, self.edge_channels
         w0 = rad.net[0].weight
@@ -955,21 +978,8 @@ class eSCNMDBackboneB200(nn.Module):
         ede = self.edge_degree_embedding.rad_func
         x = _EdgeDegreeFn.apply(x, winv, gauss, ede, self._tables(ede), ectx, nb, self.rescale_factor)
 
-        keep = self.keep_level
-        if keep is None:
-            keep = 0
-            if pos.is_cuda:
-                # memory the caching allocator already holds but is not using counts as available
-                avail = (torch.cuda.mem_get_info(pos.device)[0] + torch.cuda.memory_reserved(pos.device)
-                         - torch.cuda.memory_allocated(pos.device))
-                sh = ops.SHAPES[self.lmax]
-                per_layer_1 = graph.num_edges * (sh.lmax + sh.nm) * self.hidden_channels * 4
-                per_layer_2 = per_layer_1 + graph.num_edges * sh.nm * c * 4
-                if per_layer_2 * self.num_layers < 0.5 * avail:
-                    keep = 2
-                elif per_layer_1 * self.num_layers < 0.5 * avail:
-                    keep = 1
         for blk in self.blocks:
+            keep = self._keep_level_for_next_layer(graph.num_edges, pos.device)
             x_res = x
             xn = blk.norm_1(x, sys_node)
             x_full = halo_collect(xn, plan)  # per-layer halo exchange (escn_md_block.py:141-146)
