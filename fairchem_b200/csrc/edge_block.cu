@@ -348,7 +348,7 @@ __host__ __device__ constexpr int gate_of(int m) {
 // y [E, 11H] = [gate scalars 2H | rows 0..8 (9H)] (the three conv-1 GEMMs write it side by side);
 // out [E, 9, H]: row 0 -> SiLU, rows 1..8 -> value * sigmoid(gate of the row's degree).
 template <class Out>
-__global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp, 3)
     so2_gate_fwd_kernel(const float* __restrict__ y, Out out, const float* __restrict__ scale_ptr, int64_t num_edges, int ch) {
     out.load_scale(scale_ptr);
     const int lane = threadIdx.x & 31;
@@ -368,7 +368,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
 }
 
 template <class Out>
-__global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp, 3)
     so2_gate_bwd_kernel(const float* __restrict__ grad_out, const float* __restrict__ y, Out grad_y,
                         const float* __restrict__ scale_ptr, int64_t num_edges, int ch) {
     grad_y.load_scale(scale_ptr);

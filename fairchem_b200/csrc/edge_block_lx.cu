@@ -278,7 +278,7 @@ __device__ __forceinline__ float4 lx_sig4(float4 v) {
 }
 
 template <int LMAX, class Out>
-__global__ void __launch_bounds__(kLxWarps* kWarp)
+__global__ void __launch_bounds__(kLxWarps* kWarp, 6)
     lx_so2_gate_fwd_kernel(const float* __restrict__ y, Out out, const float* __restrict__ scale_ptr, int64_t num_edges, int ch) {
     using S = Shape<LMAX>;
     out.load_scale(scale_ptr);
@@ -305,7 +305,7 @@ __global__ void __launch_bounds__(kLxWarps* kWarp)
 }
 
 template <int LMAX, class Out>
-__global__ void __launch_bounds__(kLxWarps* kWarp)
+__global__ void __launch_bounds__(kLxWarps* kWarp, 6)
     lx_so2_gate_bwd_kernel(const float* __restrict__ grad_out, const float* __restrict__ y, Out grad_y,
                            const float* __restrict__ scale_ptr, int64_t num_edges, int ch) {
     using S = Shape<LMAX>;
