@@ -666,8 +666,10 @@ class _EdgeBlockFn(torch.autograd.Function):
         # level 1 keeps the conv-1 outputs (the backward then skips the gather+rotate and the conv-1 GEMMs), level 2
         # also the messages (no recomputation but the radial MLP); one buffer per layer, chunks write their slices
         h = ew.hidden
-        y_all = torch.empty(g.num_edges, (ew.lmax + nm) * h, dtype=x.dtype, device=x.device) if keep_level >= 1 else None
-        msg_all = torch.empty(g.num_edges, nm, c, dtype=x.dtype, device=x.device) if keep_level >= 2 else None
+        # rows rounded up so that a slowly changing edge count (MD) asks the allocator for the same block every step
+        rows = -(-g.num_edges // 65536) * 65536
+        y_all = torch.empty(rows, (ew.lmax + nm) * h, dtype=x.dtype, device=x.device)[: g.num_edges] if keep_level >= 1 else None
+        msg_all = torch.empty(rows, nm, c, dtype=x.dtype, device=x.device)[: g.num_edges] if keep_level >= 2 else None
         with torch.no_grad():
             for ch in ectx.chunks:
                 sl = slice(ch.e0, ch.e1)
@@ -889,8 +891,9 @@ class eSCNMDBackboneB200(nn.Module):
         # memory the caching allocator already holds but is not using counts as available
         avail = free + torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
         sh = ops.SHAPES[self.lmax]
-        need_1 = num_edges * (sh.lmax + sh.nm) * self.hidden_channels * 4
-        need_2 = need_1 + num_edges * sh.nm * self.sphere_channels * 4
+        rows = -(-num_edges // 65536) * 65536
+        need_1 = rows * (sh.lmax + sh.nm) * self.hidden_channels * 4
+        need_2 = need_1 + rows * sh.nm * self.sphere_channels * 4
         # a chunk's temporaries measure about 5 operand buffers [E_c, NM*2C] in the backward pass; allow 10
         chunk = min(num_edges, int(1.25 * self.edge_chunk_size))
         reserve = 0.06 * total + 10 * chunk * sh.nm * 2 * self.sphere_channels * 4

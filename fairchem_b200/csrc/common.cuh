@@ -86,6 +86,31 @@ __device__ __forceinline__ void warp_reduce_wig(float (&v)[FCB200_WIG], int lane
     }
 }
 
+// Sum each of N per-lane partial values over the warp and store total i at out[i].  Values are taken in groups
+// of 32 through the transposed butterfly of warp_reduce_wig (31 shuffles per group, a short group is padded with
+// zeros), after which lane l holds the total of value 32 g + l and stores it.
+template <int N>
+__device__ __forceinline__ void warp_reduce_store(const float (&v)[N], int lane, float* __restrict__ out, float scale = 1.0f) {
+#pragma unroll
+    for (int g = 0; g < (N + 31) / 32; ++g) {
+        float t[32];
+#pragma unroll
+        for (int i = 0; i < 32; ++i) t[i] = (g * 32 + i < N) ? v[g * 32 + i] : 0.f;
+#pragma unroll
+        for (int h = 16; h >= 1; h >>= 1) {
+            const bool upper = (lane & h) != 0;
+#pragma unroll
+            for (int i = 0; i < h; ++i) {
+                const float a = t[i], b = t[i + h];
+                const float send = upper ? a : b;
+                const float keep = upper ? b : a;
+                t[i] = keep + __shfl_xor_sync(kFull, send, h);
+            }
+        }
+        if (g * 32 + lane < N) out[g * 32 + lane] = t[0] * scale;
+    }
+}
+
 // Load the 35 compact Wigner entries of one edge into registers, identical in every lane.
 __device__ __forceinline__ void load_wig(const float* __restrict__ wig, int64_t e, int lane, float (&w)[FCB200_WIG]) {
     const float* p = wig + e * FCB200_WIG;

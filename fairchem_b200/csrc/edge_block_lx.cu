@@ -11,6 +11,8 @@
 //   edge features   [E, NM, w]          M-major rows: m=0 (l=0..lmax) | m=+1 (l=1..) | m=-1 | m=+2 (l=2..) | m=-2
 //   compact Wigner  [E, NW]             block l holds rows m = -mm..mm (mm = min(l,2)) x columns m' = -l..l of D^l
 //   inverse         same layout as the compact Wigner, times the envelope (D is orthogonal: D^-1 = D^T)
+#include <type_traits>
+
 #include "common.cuh"
 #include "shape_lx.cuh"
 
@@ -26,6 +28,27 @@ __device__ __forceinline__ void stage_wig(const float* __restrict__ wig, int64_t
 #pragma unroll
     for (int i = lane; i < KW; i += 32) slot[i] = wig[e * KW + i];
     __syncwarp();
+}
+
+// Warp-reduce the first rows(l) * (2l+1) entries of a per-lane block gradient and store them.  `l` is a compile-time
+// constant at every call site (the degree loops are fully unrolled), so the switch folds away.
+template <int LMAX, int KMAX>
+__device__ __forceinline__ void reduce_block(const float (&dw)[KMAX], int l, int lane, float* __restrict__ out, float scale) {
+    using S = Shape<LMAX>;
+    auto run = [&](auto tag) {
+        constexpr int n = decltype(tag)::value;
+        float v[n];
+#pragma unroll
+        for (int i = 0; i < n; ++i) v[i] = dw[i];
+        warp_reduce_store<n>(v, lane, out, scale);
+    };
+    switch (l) {
+        case 0: run(std::integral_constant<int, S::rows(0) * 1>{}); break;
+        case 1: run(std::integral_constant<int, S::rows(1) * 3>{}); break;
+        case 2: run(std::integral_constant<int, S::rows(2) * 5>{}); break;
+        case 3: if constexpr (LMAX >= 3) run(std::integral_constant<int, S::rows(3) * 7>{}); break;
+        default: if constexpr (LMAX >= 4) run(std::integral_constant<int, S::rows(4) * 9>{}); break;
+    }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -144,11 +167,8 @@ __global__ void __launch_bounds__(kLxWarps* kWarp)
                     }
                 }
             }
-#pragma unroll
-            for (int i = 0; i < S::rows(l) * (2 * l + 1); ++i) {
-                const float s = warp_sum(dw[i]);
-                if (lane == (i & 31)) grad_wig[e * S::kW + S::woff(l) + i] = s;
-            }
+            // entries past rows(l) * (2l+1) are zero and not stored
+            reduce_block<LMAX>(dw, l, lane, grad_wig + e * S::kW + S::woff(l), 1.0f);
         }
     }
 }
@@ -256,13 +276,7 @@ __global__ void __launch_bounds__(kLxWarps* kWarp)
                     grad_msg.st(gm_base + row * channels + c0, scale4(inv, acc));
                 }
             }
-            if (WANT_DW) {
-#pragma unroll
-                for (int i = 0; i < S::rows(l) * (2 * l + 1); ++i) {
-                    const float s = warp_sum(dw[i]);
-                    if (lane == (i & 31)) grad_winv[e * S::kW + S::woff(l) + i] = s * inv;
-                }
-            }
+            if (WANT_DW) reduce_block<LMAX>(dw, l, lane, grad_winv + e * S::kW + S::woff(l), inv);
         }
     }
 }
