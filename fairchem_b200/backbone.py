@@ -833,7 +833,7 @@ class eSCNMDBackboneB200(nn.Module):
             raise ValueError("the sm_100a edge-block kernels are built for mmax = 2 with lmax = 2 or 4")
         if norm_type != "rms_norm_sh" or act_type != "gate" or ff_type != "spectral" or chg_spin_emb_type != "rand_emb":
             raise ValueError("only the UMA configuration (rms_norm_sh / gate / spectral / rand_emb) is implemented")
-        if direct_forces or regress_stress or distance_function != "gaussian" or not use_dataset_embedding:
+        if direct_forces or distance_function != "gaussian" or not use_dataset_embedding:
             raise ValueError("unsupported option for the B200 backbone")
         if sphere_channels % 128 or hidden_channels % 128:
             raise ValueError("sphere_channels and hidden_channels must be multiples of 128")
@@ -842,7 +842,7 @@ class eSCNMDBackboneB200(nn.Module):
         self.cutoff, self.max_neighbors, self.otf_graph = float(cutoff), max_neighbors, otf_graph
         self.edge_channels, self.num_distance_basis = edge_channels, num_distance_basis
         self.always_use_pbc, self.radius_pbc_version = always_use_pbc, radius_pbc_version
-        self.regress_forces, self.direct_forces = regress_forces, direct_forces
+        self.regress_forces, self.direct_forces, self.regress_stress = regress_forces, direct_forces, regress_stress
         self.edge_chunk_size = int(edge_chunk_size)
         # what every layer keeps per edge for its backward pass: 0 nothing (recompute the chunk), 1 the conv-1
         # output [E,(lmax+NM)H], 2 also the messages [E,NM*C]; None picks the highest level that fits in free memory
@@ -938,7 +938,7 @@ class eSCNMDBackboneB200(nn.Module):
         data["batch_full"] = data["batch"]
         z, batch = data["atomic_numbers"], data["batch"]
         pos = data["pos"]
-        if self.regress_forces and not self.direct_forces:
+        if (self.regress_forces or self.regress_stress) and not self.direct_forces:
             pos.requires_grad_(True)
         c, nb = self.sphere_channels, self.num_distance_basis
         csd = self.csd_embedding(data["charge"], data["spin"], data.get("dataset", None))
@@ -968,8 +968,12 @@ class eSCNMDBackboneB200(nn.Module):
         self.last_graph = {"edge_index": edge_index, "cell_offsets": cell_offsets}
         chunks = build_chunks(graph, self.edge_chunk_size)
 
+        virial = None
+        if self.regress_stress:
+            nsys = len(data["natoms"])
+            virial = {"num_systems": nsys, "edge_system": None if nsys == 1 else batch_l[edge_index[1]]}
         vec, dist, env, wig, gauss = ops.EdgeGeometry.apply(pos_e, shift, gamma, graph, self.cutoff, nb, 0.0, self.cutoff, 2.0,
-                                                            self.lmax)
+                                                            self.lmax, virial)
         if ops.uses_transposed_inverse(self.lmax):
             winv = _PermuteColumns.apply(wig, self._wig_transpose) * env.unsqueeze(1)
         else:  # the any-lmax kernels read the inverse from the same compact layout (D is orthogonal)
@@ -991,7 +995,7 @@ class eSCNMDBackboneB200(nn.Module):
             x_res = x
             x = blk.atom_wise(blk.norm_2(x)) + x_res
         x = self.norm(x)
-        return {"node_embedding": x, "batch": batch_l}
+        return {"node_embedding": x, "batch": batch_l, "virial": virial}
 
 
 class MLP_EFS_HeadB200(nn.Module):
@@ -1002,7 +1006,7 @@ class MLP_EFS_HeadB200(nn.Module):
         super().__init__()
         c, h = backbone.sphere_channels, backbone.hidden_channels
         self.energy_block = nn.Sequential(nn.Linear(c, h), nn.SiLU(), nn.Linear(h, h), nn.SiLU(), nn.Linear(h, 1))
-        self.regress_forces = backbone.regress_forces
+        self.regress_forces, self.regress_stress = backbone.regress_forces, backbone.regress_stress
 
     def forward(self, data, emb):
         with torch.enable_grad():
@@ -1014,9 +1018,14 @@ class MLP_EFS_HeadB200(nn.Module):
             nsys = len(data["natoms"])
             energy = torch.zeros(nsys, dtype=torch.float64, device=e_node.device).index_add(0, emb["batch"], e_node.double())
             out = {"energy": energy.detach()}
-            if self.regress_forces:
+            if self.regress_forces or self.regress_stress:
                 (grad,) = torch.autograd.grad(energy.sum(), data["pos"], create_graph=False)
                 out["forces"] = -grad
+            if self.regress_stress:
+                # stress = sym(sum_e dE/dvec_e (x) vec_e) / volume, flattened [B,9] as the reference returns it
+                w = emb["virial"]["virial"]
+                volume = torch.det(data["cell"].double()).abs().view(-1, 1, 1)
+                out["stress"] = ((w + w.transpose(1, 2)) / 2 / volume).reshape(-1, 9)
             check_gemm_status()
         return out
 

@@ -699,11 +699,16 @@ class SO2Gate(torch.autograd.Function):
 
 
 class EdgeGeometry(torch.autograd.Function):
-    """pos [N,3] -> (vec [E,3], dist [E], env [E], wig [E,NW], gauss [E,nb]); differentiable in pos."""
+    """pos [N,3] -> (vec [E,3], dist [E], env [E], wig [E,NW], gauss [E,nb]); differentiable in pos.
+
+    ``virial``: optional dict with ``num_systems`` (and ``edge_system`` [E] for batches); the backward pass then
+    also leaves ``virial["virial"]`` [B,3,3] (float64) = sum over edges of dE/dvec (x) vec, the strain derivative of
+    the energy: positions and cell enter the energy only through the edge vectors, so this is what the
+    reference's position and cell gradients combine to (src/fairchem/core/models/uma/outputs.py:165-226)."""
 
     @staticmethod
     def forward(ctx, pos, shift, gamma, graph: EdgeGraph, cutoff: float, num_basis: int, b_start: float,
-                b_stop: float, b_width: float, lmax: int = 2):
+                b_stop: float, b_width: float, lmax: int = 2, virial: Optional[dict] = None):
         pos = pos.contiguous()
         e, dev = graph.num_edges, pos.device
         vec = torch.empty(e, 3, dtype=pos.dtype, device=dev)
@@ -718,6 +723,7 @@ class EdgeGeometry(torch.autograd.Function):
         ctx.save_for_backward(pos, shift, gamma)
         ctx.graph = graph
         ctx.params = (cutoff, num_basis, b_start, b_stop, b_width)
+        ctx.virial, ctx.vec = virial, (vec if virial is not None else None)
         ctx.mark_non_differentiable(vec)
         return vec, dist, env, wig, gauss
 
@@ -731,12 +737,19 @@ class EdgeGeometry(torch.autograd.Function):
 
         grad_vec = torch.empty(g.num_edges, 3, dtype=pos.dtype, device=pos.device)
         edge_geometry_bwd_.raw(pos, g.src, g.tgt, shift, gamma, c(gwig), c(genv), c(ggauss), c(gdist), grad_vec, *ctx.params)
+        if ctx.virial is not None:
+            outer = grad_vec.double().unsqueeze(2) * ctx.vec.double().unsqueeze(1)  # [E,3,3]: dE/dvec_i * vec_j
+            nsys, esys = int(ctx.virial["num_systems"]), ctx.virial.get("edge_system")
+            if esys is None:
+                ctx.virial["virial"] = outer.sum(dim=0, keepdim=True)
+            else:
+                ctx.virial["virial"] = torch.zeros(nsys, 3, 3, dtype=torch.float64, device=pos.device).index_add_(0, esys, outer)
         grad_pos = torch.empty_like(pos)
         segment_sum(grad_vec, g.src_ptr, g.src_perm, pos.shape[0], out=grad_pos)
         nt = g.num_targets
         segment_sum(grad_vec, g.row_ptr, None, nt, out=grad_pos if nt == pos.shape[0] else grad_pos[:nt],
                     accumulate=True, scale=-1.0)
-        return grad_pos, None, None, None, None, None, None, None, None, None
+        return grad_pos, None, None, None, None, None, None, None, None, None, None
 
 
 class RadialAct(torch.autograd.Function):

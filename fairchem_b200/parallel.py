@@ -195,4 +195,7 @@ class PartitionedStepper:
         energy, forces = out["energy"], out["forces"]
         dist.all_reduce(energy, group=self.group)
         dist.all_reduce(forces, group=self.group)
+        if "stress" in out:  # every rank holds the virial of its own targets' edges
+            dist.all_reduce(out["stress"], group=self.group)
+            self.last_stress = out["stress"]
         return energy, forces

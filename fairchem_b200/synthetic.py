@@ -76,6 +76,21 @@ def _pack(pos32, z, cell, pbc, natoms, task, charge, spin) -> AtomicDataLike:
     )
 
 
+def merge(systems) -> AtomicDataLike:
+    """One batch out of several single- or multi-system inputs (what the reference's collater does for these fields)."""
+    systems = list(systems)
+    out = AtomicDataLike()
+    for key in ("pos", "atomic_numbers", "cell", "pbc", "natoms", "charge", "spin"):
+        out[key] = torch.cat([s[key] for s in systems], dim=0)
+    offsets, batches = 0, []
+    for s in systems:
+        batches.append(s["batch"] + offsets)
+        offsets += len(s["natoms"])
+    out["batch"] = torch.cat(batches, dim=0)
+    out["dataset"] = [t for s in systems for t in s["dataset"]]
+    return out
+
+
 def _lattice(basis: np.ndarray, a: float, reps: tuple[int, int, int]) -> np.ndarray:
     ii, jj, kk = np.meshgrid(np.arange(reps[0]), np.arange(reps[1]), np.arange(reps[2]), indexing="ij")
     origins = np.stack([ii.ravel(), jj.ravel(), kk.ravel()], axis=1).astype(np.float64)

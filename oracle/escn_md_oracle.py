@@ -301,7 +301,7 @@ def edge_vectors(pos, cell, edge_index, cell_offsets, edge_system):
 
 
 def energy_and_forces(sd, cfg: dict, data, edge_index, cell_offsets, gamma=None, want_forces=True,
-                      return_intermediates=False):
+                      return_intermediates=False, want_stress=False):
     """Energy [B] (float64) and forces [N,3] for one batch, given the edge list.
 
     ``sd``: backbone state_dict plus head entries under ``energy_block.*``; ``cfg``: dict with
@@ -318,6 +318,7 @@ def energy_and_forces(sd, cfg: dict, data, edge_index, cell_offsets, gamma=None,
     n_full = (lmax + 1) ** 2
 
     pos = data["pos"].detach().to(dtype).clone().requires_grad_(want_forces)
+    cell = data["cell"].detach().to(dtype).clone().requires_grad_(want_stress)
     z = data["atomic_numbers"].long()
     batch = data["batch"].long()
     n = pos.shape[0]
@@ -334,7 +335,7 @@ def energy_and_forces(sd, cfg: dict, data, edge_index, cell_offsets, gamma=None,
     sys_node = csd[batch]
 
     # geometry
-    vec = edge_vectors(pos, data["cell"].to(dtype), edge_index, cell_offsets, batch[tgt])
+    vec = edge_vectors(pos, cell, edge_index, cell_offsets, batch[tgt])
     dist = vec.norm(dim=-1)
     q = edge_quaternion(vec, gamma)
     d_full = wigner_blocks(q, lmax)  # [E,L2,L2]
@@ -393,6 +394,15 @@ def energy_and_forces(sd, cfg: dict, data, edge_index, cell_offsets, gamma=None,
         sd["energy_block.4.weight"], sd["energy_block.4.bias"]).view(-1)
     energy = torch.zeros(nsys, dtype=torch.float64).index_add(0, batch, e_node.double())
     forces = None
+    if want_stress:
+        # virial from the position and cell gradients, stress = virial / volume, flattened [B,9] (outputs.py:165-226)
+        g_r, g_h = torch.autograd.grad(energy.sum(), [pos, cell])
+        forces = -g_r
+        pos_virial = torch.zeros(nsys, 3, 3, dtype=dtype).index_add(0, batch, g_r.unsqueeze(2) * pos.detach().unsqueeze(1))
+        cell_virial = cell.detach().transpose(1, 2) @ g_h
+        virial = (pos_virial + pos_virial.transpose(1, 2) + cell_virial + cell_virial.transpose(1, 2)) / 2
+        stress = (virial / torch.det(cell.detach()).abs().view(-1, 1, 1)).reshape(-1, 9)
+        return energy.detach(), forces, stress
     if want_forces:
         (grad,) = torch.autograd.grad(energy.sum(), pos)
         forces = -grad

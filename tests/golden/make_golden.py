@@ -222,6 +222,29 @@ def make_l4_golden():
     np.savez_compressed(os.path.join(OUT, "escn_md_l4.npz"), **out)
 
 
+def make_stress_golden():
+    """Energy, forces and stress (virial / volume, outputs.py:165-226) of the reference with regress_stress=True."""
+    bb, head = ref_shim.build_reference_model(0, regress_stress=True)
+    sd = weights.random_init_state_dict(weights.UMA_S, 0)
+    bsd, hsd = weights.split_head(sd)
+    missing, unexpected = bb.load_state_dict(bsd, strict=False)
+    assert not unexpected and all(k.startswith("Jd_") for k in missing), (missing, unexpected)
+    head.energy_block.load_state_dict(hsd)
+    out = {}
+    torch.set_num_threads(os.cpu_count() or 8)
+    cases = (("fcc_cu_32", synthetic.fcc_cu((2, 2, 2), seed=0)), ("bcc_alloy_72", synthetic.bcc_alloy((3, 3, 4), seed=9)),
+             ("water_96", synthetic.water_box(96, seed=0)))
+    for name, data in cases:
+        d = data.clone()
+        with ref_shim.fixed_gamma(0.0):
+            res = head(d, bb(d))
+        out[f"{name}_energy"] = res["energy"].detach().numpy()
+        out[f"{name}_forces"] = res["forces"].detach().numpy()
+        out[f"{name}_stress"] = res["stress"].detach().numpy()
+        print("stress", name, out[f"{name}_energy"], out[f"{name}_stress"])
+    np.savez_compressed(os.path.join(OUT, "uma_s_stress.npz"), **out)
+
+
 def make_partition_golden():
     """Rank assignments of the reference's Morton partition (graph_partition.py:38-97)."""
     ref_shim.load()
@@ -236,7 +259,9 @@ def make_partition_golden():
 
 
 if __name__ == "__main__":
-    which = sys.argv[1:] or ["graph", "wigner", "ops", "model", "partition", "l4"]
+    which = sys.argv[1:] or ["graph", "wigner", "ops", "model", "partition", "l4", "stress"]
+    if "stress" in which:
+        make_stress_golden()
     if "l4" in which:
         make_l4_golden()
     if "partition" in which:

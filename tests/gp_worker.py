@@ -25,18 +25,19 @@ def main():
     dev = torch.device("cuda", local)
     dist.init_process_group("nccl", device_id=dev)
     sd = weights.random_init_state_dict(cfg, 0)
-    bb, head = build_model(cfg, sd, device=dev, edge_chunk_size=8192)
+    bb, head = build_model(cfg, sd, device=dev, edge_chunk_size=8192, regress_stress=True)
     host = synthetic.water_box(natoms, seed=1)
     data = host.to(dev)
     stepper = parallel.PartitionedStepper(bb, head, host, dev, rank, world)
     energy, forces = stepper.step(data)
+    stress = stepper.last_stress.clone()
     energy2, forces2 = stepper.step(data)  # a second step reuses nothing stale
     plan = stepper.last_plan
     stats = torch.tensor([plan.n_local, plan.n_halo, plan.edge_index_local.shape[1]], device=dev)
     gathered = [torch.zeros_like(stats) for _ in range(world)]
     dist.all_gather(gathered, stats)
     if rank == 0:
-        torch.save({"energy": energy.cpu(), "forces": forces.cpu(), "energy2": energy2.cpu(), "forces2": forces2.cpu(),
+        torch.save({"energy": energy.cpu(), "forces": forces.cpu(), "energy2": energy2.cpu(), "forces2": forces2.cpu(), "stress": stress.cpu(),
                     "stats": torch.stack(gathered).cpu()}, out_path)
     dist.barrier()
     dist.destroy_process_group()

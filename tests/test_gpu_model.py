@@ -118,3 +118,36 @@ def test_tf32_split_gemm_mode_matches_reference_golden(golden):
             assert np.max(np.abs(f - f_ref)) < F_ATOL, name
     finally:
         B.set_gemm_precision(2)
+
+
+@pytest.mark.parametrize("name,make", [("fcc_cu_32", lambda: synthetic.fcc_cu((2, 2, 2), seed=0)),
+                                       ("bcc_alloy_72", lambda: synthetic.bcc_alloy((3, 3, 4), seed=9)),
+                                       ("water_96", lambda: synthetic.water_box(96, seed=0))])
+def test_stress_matches_reference_golden(golden, name, make):
+    """regress_stress=True: virial from the per-edge gradients against the reference's stress (outputs.py:165-226)."""
+    from fairchem_b200.backbone import build_model
+
+    g = golden("uma_s_stress.npz")
+    sd = weights.random_init_state_dict(weights.UMA_S, 0)
+    bb, head = build_model(weights.UMA_S, sd, edge_chunk_size=4096, regress_stress=True)
+    d = make().to("cuda")
+    out = head(d, bb(d))
+    e, f, s = out["energy"].cpu().numpy(), out["forces"].cpu().numpy(), out["stress"].cpu().numpy()
+    assert np.max(np.abs(e - g[f"{name}_energy"]) / np.abs(g[f"{name}_energy"])) < E_RTOL
+    assert np.max(np.abs(f - g[f"{name}_forces"])) < F_ATOL
+    assert s.shape == (1, 9) and np.max(np.abs(s - g[f"{name}_stress"])) < 1e-6
+
+
+def test_stress_of_a_batch_is_per_system():
+    from fairchem_b200.backbone import build_model
+
+    sd = weights.random_init_state_dict(weights.UMA_S, 0)
+    bb, head = build_model(weights.UMA_S, sd, edge_chunk_size=4096, regress_stress=True)
+    a, b = synthetic.fcc_cu((2, 2, 2), seed=0), synthetic.bcc_alloy((3, 3, 4), seed=9)
+    singles = []
+    for d in (a, b):
+        dd = d.to("cuda")
+        singles.append(head(dd, bb(dd))["stress"].cpu().numpy())
+    both = synthetic.merge([a, b]).to("cuda")
+    got = head(both, bb(both))["stress"].cpu().numpy()
+    assert got.shape == (2, 9) and np.max(np.abs(got - np.concatenate(singles))) < 1e-6

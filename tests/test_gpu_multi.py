@@ -23,10 +23,10 @@ def test_partitioned_run_matches_single_gpu(world, model, natoms):
 
     cfg = weights.ESCN_MD_L4 if model == "escn_md_l4" else weights.UMA_S
     sd = weights.random_init_state_dict(cfg, 0)
-    bb, head = build_model(cfg, sd, edge_chunk_size=8192)
+    bb, head = build_model(cfg, sd, edge_chunk_size=8192, regress_stress=True)
     d = synthetic.water_box(natoms, seed=1).to("cuda")
     out = head(d, bb(d))
-    e1, f1 = out["energy"].cpu().numpy(), out["forces"].cpu().numpy()
+    e1, f1, s1 = out["energy"].cpu().numpy(), out["forces"].cpu().numpy(), out["stress"].cpu().numpy()
     with tempfile.TemporaryDirectory() as tmp:
         path = os.path.join(tmp, "gp.pt")
         env = dict(os.environ, NCCL_NVLS_ENABLE="0")
@@ -39,6 +39,7 @@ def test_partitioned_run_matches_single_gpu(world, model, natoms):
     e, f = got["energy"].numpy(), got["forces"].numpy()
     assert np.max(np.abs(e - e1) / np.abs(e1)) < 1e-5
     assert np.max(np.abs(f - f1)) < 1e-4
+    assert np.max(np.abs(got["stress"].numpy() - s1)) < 1e-6   # partial virials of the ranks add up
     assert np.max(np.abs(got["energy2"].numpy() - e)) < 1e-6 * np.abs(e).max() and np.max(np.abs(got["forces2"].numpy() - f)) < 2e-6
     stats = got["stats"].numpy()
     assert stats[:, 0].sum() == natoms and stats[:, 0].max() - stats[:, 0].min() <= 1   # balanced ownership
