@@ -796,6 +796,15 @@ class _EdgeDegreeFn(torch.autograd.Function):
 # ------------------------------------------------------------------------------------------
 
 
+@dataclass
+class _RegressConfig:
+    forces: bool = True
+    stress: bool = False
+    direct_forces: bool = False
+    direct_stress: bool = False
+    hessian: bool = False
+
+
 class eSCNMDBackboneB200(nn.Module):
     def __init__(
         self,
@@ -873,10 +882,95 @@ class eSCNMDBackboneB200(nn.Module):
     def num_params(self) -> int:
         return sum(p.numel() for p in self.parameters())
 
-    def prepare_for_inference(self, *a, **k):
-        for p in self.parameters():
-            p.requires_grad_(False)
+    registry_name = "escnmd_backbone"  # the name the reference registers its backbone under (escn_md.py:280)
+
+    @property
+    def regress_config(self):
+        """What the heads may derive from the energy (the reference's RegressConfig, escn_md.py:340-352)."""
+        return _RegressConfig(forces=self.regress_forces, stress=self.regress_stress, direct_forces=self.direct_forces)
+
+    def no_weight_decay(self) -> set:
+        """Names of the parameters a trainer should not decay: everything but Linear / SO3Linear weights inside the
+        linear, SO3-linear and normalisation modules (the reference's rule, escn_md.py:911-937)."""
+        names = set()
+        for mod_name, mod in self.named_modules():
+            if isinstance(mod, (nn.Linear, SO3Linear, nn.LayerNorm, RMSNormSH)):
+                for pname, _ in mod.named_parameters(recurse=False):
+                    if isinstance(mod, (nn.Linear, SO3Linear)) and "weight" in pname:
+                        continue
+                    names.add(f"{mod_name}.{pname}")
+        return names
+
+    @classmethod
+    def build_inference_settings(cls, settings) -> dict:
+        """Constructor overrides from an inference-settings object (escn_md.py:939-961); unset fields are skipped."""
+        overrides = {"always_use_pbc": False}
+        for field, key in (("activation_checkpointing", "activation_checkpointing"), ("edge_chunk_size", "edge_chunk_size"),
+                           ("internal_graph_gen_version", "radius_pbc_version"), ("execution_mode", "execution_mode")):
+            value = getattr(settings, field, None)
+            if value is not None:
+                overrides[key] = value
+        if getattr(settings, "external_graph_gen", None) is not None:
+            overrides["otf_graph"] = not settings.external_graph_gen
+        return overrides
+
+    def get_default_untrained_tasks(self, checkpoint_tasks: dict, inference_settings) -> list:
+        """Stress tasks for every dataset that has an energy task but no stress task (escn_md.py:963-1027): the
+        stress follows from the energy by differentiation.  Tasks are built with fairchem's ``Task`` / ``OutputSpec``
+        when that package is importable, else as plain namespaces with the same fields."""
+        if self.direct_forces:
+            return []
+        try:
+            from fairchem.core.units.mlip_unit.mlip_unit import OutputSpec, Task
+        except Exception:  # fairchem is not installed next to this package
+            from types import SimpleNamespace as OutputSpec
+            from types import SimpleNamespace as Task
+        energy_task, with_stress = {}, set(getattr(inference_settings, "predict_untrained_stress", ()) or ())
+        for task in checkpoint_tasks.values():
+            if task.property == "energy":
+                energy_task.update({ds: task for ds in task.datasets})
+            elif task.property == "stress":
+                with_stress.update(task.datasets)
+        tasks = []
+        for ds in sorted(set(energy_task) - with_stress):
+            et = energy_task[ds]
+            tasks.append(Task(name=("" if et.name == "energy" else f"{ds}_") + "stress", level="system", property="stress",
+                              out_spec=OutputSpec(dim=[1, 9], dtype=getattr(inference_settings, "base_precision_dtype", None)),
+                              normalizer=et.normalizer, datasets=[ds], loss_fn=None, element_references=None, metrics=[],
+                              train_on_free_atoms=True, eval_on_free_atoms=True, inference_only=True))
+        return tasks
+
+    def validate_tasks(self, dataset_to_tasks: dict) -> None:
+        assert set(dataset_to_tasks).issubset(set(self.dataset_mapping)), \
+            "Datasets in tasks is not a strict subset of datasets in backbone."
+
+    def prepare_for_inference(self, data=None, settings=None):
+        """Called once before the first prediction (escn_md.py:1037-1044): validate the kernel shapes, freeze weights."""
+        from .backend import B200Backend
+
+        self._inference_settings = settings
+        B200Backend.validate(self.lmax, self.mmax, settings)
+        B200Backend.prepare_model_for_inference(self)
         return self
+
+    def on_predict_check(self, data) -> None:
+        """Called before each prediction; nothing to check."""
+
+    def validate_atoms_data(self, atoms, task_name: str) -> None:
+        """Default and range-check total charge and spin multiplicity in ``atoms.info`` (the reference's
+        ``validate_uma_atoms_data``, src/fairchem/core/units/mlip_unit/api/inference.py:39-100): charge 0; spin 1 for
+        the ``omol`` task and 0 otherwise; charge within [-100, 100], spin within [0, 100]."""
+        info = atoms.info
+        info.setdefault("charge", 0)
+        info.setdefault("spin", 1 if task_name == "omol" else 0)
+        import numbers
+
+        for key, lo, hi in (("charge", -100, 100), ("spin", 0, 100)):
+            value = info[key]
+            if not isinstance(value, numbers.Integral) or isinstance(value, bool):
+                raise TypeError(f"Invalid type for {key}: {type(value)}; it must be an integer.")
+            if not lo <= value <= hi:
+                raise ValueError(f"Invalid value for {key}: {value}; it must be within the range {lo} to {hi}.")
 
     # -- forward -----------------------------------------------------------------------------
     def _keep_level_for_next_layer(self, num_edges: int, device) -> int:

@@ -132,3 +132,46 @@ def test_backbone_loads_reference_keys():
     bb.load_state_dict(bsd, strict=True)
     MLP_EFS_HeadB200(bb).energy_block.load_state_dict(hsd, strict=True)
     assert bb.num_params == 6316288
+
+
+def test_backbone_mirrors_the_reference_module_interface():
+    """Members MLIPPredictUnit and the trainer call on the backbone (escn_md.py:907-1059), checked without a GPU."""
+    from types import SimpleNamespace as NS
+
+    import pytest
+
+    from fairchem_b200 import weights
+    from fairchem_b200.backbone import eSCNMDBackboneB200
+
+    bb = eSCNMDBackboneB200(**weights.UMA_S)
+    assert bb.registry_name == "escnmd_backbone" and bb.num_params == 6_316_288
+    cfg = bb.regress_config
+    assert cfg.forces and not cfg.stress and not cfg.direct_forces
+    no_wd = bb.no_weight_decay()
+    names = dict(bb.named_parameters())
+    assert no_wd <= set(names) and "mix_csd.bias" in no_wd and "mix_csd.weight" not in no_wd
+    assert "norm.affine_weight" in no_wd and "blocks.0.atom_wise.so3_linear_1.weight" not in no_wd
+    over = eSCNMDBackboneB200.build_inference_settings(
+        NS(activation_checkpointing=False, edge_chunk_size=None, external_graph_gen=True, internal_graph_gen_version=2,
+           execution_mode=None))
+    assert over == {"always_use_pbc": False, "activation_checkpointing": False, "radius_pbc_version": 2, "otf_graph": False}
+    energy = NS(property="energy", datasets=["omat", "omol"], name="energy", normalizer="n")
+    have = NS(property="stress", datasets=["omat"], name="stress", normalizer="n")
+    tasks = bb.get_default_untrained_tasks({"a": energy, "b": have}, NS(predict_untrained_stress=[], base_precision_dtype=None))
+    assert [t.name for t in tasks] == ["stress"] and tasks[0].datasets == ["omol"] and tasks[0].out_spec.dim == [1, 9]
+    bb.validate_tasks({"omat": []})
+    with pytest.raises(AssertionError):
+        bb.validate_tasks({"unknown": []})
+    atoms = NS(info={})
+    bb.validate_atoms_data(atoms, "omol")
+    assert atoms.info == {"charge": 0, "spin": 1}
+    with pytest.raises(ValueError):
+        bb.validate_atoms_data(NS(info={"charge": 101}), "omat")
+    with pytest.raises(TypeError):
+        bb.validate_atoms_data(NS(info={"spin": 0.5}), "omat")
+    assert bb.prepare_for_inference(None, NS(activation_checkpointing=False)) is bb
+    assert not any(p.requires_grad for p in bb.parameters())
+    with pytest.raises(ValueError):
+        bb.prepare_for_inference(None, NS(activation_checkpointing=True))
+    with pytest.raises(ValueError):
+        eSCNMDBackboneB200(**dict(weights.UMA_S, lmax=3))
