@@ -54,6 +54,8 @@ SIGNATURES = {
     "fcb200_lx_so2_gate_bwd": [P, P, P, I64, I32, I32, P],
     "fcb200_lx_rms_norm_sh_fwd": [P, P, P, P, P, P, F32, I64, I32, I32, P],
     "fcb200_lx_rms_norm_sh_bwd": [P, P, P, P, P, I64, I32, I32, P],
+    "fcb200_node_gate_fwd": [P, P, P, I64, I32, I32, P],
+    "fcb200_node_gate_bwd": [P, P, P, P, P, I64, I32, I32, P],
     "fcb200_lx_edge_geometry_fwd": [P, P, P, P, P, P, P, P, P, P, F32, I32, F32, F32, F32, I64, I64, I32, P],
     "fcb200_lx_edge_geometry_bwd": [P, P, P, P, P, P, P, P, P, P, F32, I32, F32, F32, F32, I64, I64, I32, P],
     "fcb200_rg_count_sources": [P, P, I32, I64, P, P, P],

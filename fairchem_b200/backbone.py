@@ -180,6 +180,9 @@ class SpectralAtomwise(nn.Module):
 
     def forward(self, x):
         lin = self.scalar_mlp[0]
+        if x.is_cuda and self.lmax in ops.SHAPES and self.h % 128 == 0:
+            gate_pre = _linear(x[:, 0], lin.weight, lin.bias)
+            return self.so3_linear_2(ops.NodeGate.apply(self.so3_linear_1(x), gate_pre))
         gates = torch.sigmoid(F.silu(_linear(x[:, 0], lin.weight, lin.bias))).view(x.shape[0], self.lmax, self.h)
         y = self.so3_linear_1(x)
         parts = [F.silu(y[:, :1])]

@@ -119,6 +119,74 @@ __global__ void __launch_bounds__(kNodeWarps* kWarp)
     }
 }
 
+// ---------------------------------------------------------------------------------------------
+// gate of the node-wise feed-forward (SpectralAtomwise): y [N, NL, H] L-major, gate_pre [N, LMAX*H] (the
+// scalar Linear's output); out row 0 = SiLU(y_0), rows of degree l >= 1 = y * sigmoid(SiLU(gate_pre[l-1]))
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ float sigm(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float silu_f(float v) { return v * sigm(v); }
+__device__ __forceinline__ float dsilu_f(float v) {
+    const float s = sigm(v);
+    return s * (1.0f + v * (1.0f - s));
+}
+template <class F> __device__ __forceinline__ float4 map4(float4 v, F f) { return make_float4(f(v.x), f(v.y), f(v.z), f(v.w)); }
+
+template <int LMAX>
+__global__ void __launch_bounds__(kNodeWarps* kWarp)
+    node_gate_fwd_kernel(const float* __restrict__ y, const float* __restrict__ gate_pre, float* __restrict__ out,
+                         int64_t num_nodes, int ch) {
+    constexpr int kL = (LMAX + 1) * (LMAX + 1);
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = (int64_t)blockIdx.x * kNodeWarps + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * kNodeWarps;
+    for (int64_t n = warp0; n < num_nodes; n += nwarps) {
+        const float* yb = y + n * (int64_t)kL * ch;
+        float* ob = out + n * (int64_t)kL * ch;
+        for (int c = lane * 4; c < ch; c += 128) {
+            st4(ob + c, map4(ld4(yb + c), silu_f));
+#pragma unroll
+            for (int l = 1; l <= LMAX; ++l) {
+                const float4 g = map4(ld4(gate_pre + n * (int64_t)LMAX * ch + (l - 1) * ch + c), [](float v) { return sigm(silu_f(v)); });
+#pragma unroll
+                for (int j = 0; j < 2 * l + 1; ++j) st4(ob + (l * l + j) * ch + c, mul4(ld4(yb + (l * l + j) * ch + c), g));
+            }
+        }
+    }
+}
+
+template <int LMAX>
+__global__ void __launch_bounds__(kNodeWarps* kWarp)
+    node_gate_bwd_kernel(const float* __restrict__ grad_out, const float* __restrict__ y, const float* __restrict__ gate_pre,
+                         float* __restrict__ grad_y, float* __restrict__ grad_gate_pre, int64_t num_nodes, int ch) {
+    constexpr int kL = (LMAX + 1) * (LMAX + 1);
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = (int64_t)blockIdx.x * kNodeWarps + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * kNodeWarps;
+    for (int64_t n = warp0; n < num_nodes; n += nwarps) {
+        const float* yb = y + n * (int64_t)kL * ch;
+        const float* gb = grad_out + n * (int64_t)kL * ch;
+        float* qb = grad_y + n * (int64_t)kL * ch;
+        for (int c = lane * 4; c < ch; c += 128) {
+            st4(qb + c, mul4(ld4(gb + c), map4(ld4(yb + c), dsilu_f)));
+#pragma unroll
+            for (int l = 1; l <= LMAX; ++l) {
+                const float4 pre = ld4(gate_pre + n * (int64_t)LMAX * ch + (l - 1) * ch + c);
+                const float4 g = map4(pre, [](float v) { return sigm(silu_f(v)); });
+                float4 dg = f4zero();
+#pragma unroll
+                for (int j = 0; j < 2 * l + 1; ++j) {
+                    const float4 d = ld4(gb + (l * l + j) * ch + c);
+                    st4(qb + (l * l + j) * ch + c, mul4(d, g));
+                    dg = add4(dg, mul4(d, ld4(yb + (l * l + j) * ch + c)));
+                }
+                // d/dpre sigmoid(SiLU(pre)) = g (1 - g) SiLU'(pre)
+                const float4 chain = mul4(mul4(g, make_float4(1.f - g.x, 1.f - g.y, 1.f - g.z, 1.f - g.w)), map4(pre, dsilu_f));
+                st4(grad_gate_pre + n * (int64_t)LMAX * ch + (l - 1) * ch + c, mul4(dg, chain));
+            }
+        }
+    }
+}
+
 }  // namespace fcb200
 
 using namespace fcb200;
@@ -153,6 +221,27 @@ int fcb200_lx_rms_norm_sh_bwd(const float* grad_out, const float* x, const float
     if (lmax != 2 && lmax != 4) return FCB200_EINVAL;
     if (num_nodes == 0) return FCB200_OK;
     FCB_NODE_LAUNCH(rms_norm_bwd_kernel, grad_out, x, weight, stats, grad_x, num_nodes, channels);
+    return launch_status();
+}
+
+int fcb200_node_gate_fwd(const float* y, const float* gate_pre, float* out, int64_t num_nodes, int32_t hidden, int32_t lmax,
+                         void* stream) {
+    if (!y || !gate_pre || !out || num_nodes < 0 || hidden <= 0 || hidden % 128) return FCB200_EINVAL;
+    if (!aligned16(y) || !aligned16(gate_pre) || !aligned16(out)) return FCB200_EALIGN;
+    if (lmax != 2 && lmax != 4) return FCB200_EINVAL;
+    if (num_nodes == 0) return FCB200_OK;
+    FCB_NODE_LAUNCH(node_gate_fwd_kernel, y, gate_pre, out, num_nodes, hidden);
+    return launch_status();
+}
+
+int fcb200_node_gate_bwd(const float* grad_out, const float* y, const float* gate_pre, float* grad_y, float* grad_gate_pre,
+                         int64_t num_nodes, int32_t hidden, int32_t lmax, void* stream) {
+    if (!grad_out || !y || !gate_pre || !grad_y || !grad_gate_pre || num_nodes < 0 || hidden <= 0 || hidden % 128) return FCB200_EINVAL;
+    if (!aligned16(grad_out) || !aligned16(y) || !aligned16(gate_pre) || !aligned16(grad_y) || !aligned16(grad_gate_pre))
+        return FCB200_EALIGN;
+    if (lmax != 2 && lmax != 4) return FCB200_EINVAL;
+    if (num_nodes == 0) return FCB200_OK;
+    FCB_NODE_LAUNCH(node_gate_bwd_kernel, grad_out, y, gate_pre, grad_y, grad_gate_pre, num_nodes, hidden);
     return launch_status();
 }
 

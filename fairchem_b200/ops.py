@@ -384,6 +384,27 @@ def rms_norm_sh_bwd_(grad_out: Tensor, x: Tensor, weight: Tensor, stats: Tensor,
             (_p(grad_out), _p(x), _p(weight), _p(stats), _p(grad_x), n, c, s.lmax, _stream()), nbytes=n * 4 * (3 * nl * c + 2))
 
 
+@_op("node_gate_fwd", ("out",))
+def node_gate_fwd_(y: Tensor, gate_pre: Tensor, out: Tensor) -> None:
+    _chk(y, gate_pre, out)
+    _f32(y, gate_pre, out)
+    n, nl, h = y.shape
+    s = _shape(_BY_NL, nl, "rows per node")
+    _launch("node_gate_fwd", "fcb200_node_gate_fwd", (_p(y), _p(gate_pre), _p(out), n, h, s.lmax, _stream()),
+            nbytes=n * 4 * h * (2 * nl + s.lmax))
+
+
+@_op("node_gate_bwd", ("grad_y", "grad_gate_pre"))
+def node_gate_bwd_(grad_out: Tensor, y: Tensor, gate_pre: Tensor, grad_y: Tensor, grad_gate_pre: Tensor) -> None:
+    _chk(grad_out, y, gate_pre, grad_y, grad_gate_pre)
+    _f32(grad_out, y, gate_pre, grad_y, grad_gate_pre)
+    n, nl, h = y.shape
+    s = _shape(_BY_NL, nl, "rows per node")
+    _launch("node_gate_bwd", "fcb200_node_gate_bwd",
+            (_p(grad_out), _p(y), _p(gate_pre), _p(grad_y), _p(grad_gate_pre), n, h, s.lmax, _stream()),
+            nbytes=n * 4 * h * (3 * nl + 2 * s.lmax))
+
+
 @_op("gemm_tf32", ("c", "status"))
 def gemm_tf32_(a: Tensor, w: Tensor, w_lo: Optional[Tensor], bias: Optional[Tensor], c: Tensor, precision: int,
                status: Tensor) -> None:
@@ -794,3 +815,23 @@ class RMSNormSH(torch.autograd.Function):
         grad_x = torch.empty_like(x)
         rms_norm_sh_bwd_.raw(grad_out.contiguous(), x, ctx.weight, stats, grad_x)
         return grad_x, None, None, None, None
+
+
+class NodeGate(torch.autograd.Function):
+    """Gate of the node-wise feed-forward: y [N,NL,H], gate_pre [N,lmax*H] -> [N,NL,H]; row 0 SiLU, rows of degree
+    l times sigmoid(SiLU(gate_pre[l-1])); differentiable in both."""
+
+    @staticmethod
+    def forward(ctx, y, gate_pre):
+        y, gate_pre = y.contiguous(), gate_pre.contiguous()
+        out = torch.empty_like(y)
+        node_gate_fwd_.raw(y, gate_pre, out)
+        ctx.save_for_backward(y, gate_pre)
+        return out
+
+    @staticmethod
+    def backward(ctx, grad_out):
+        y, gate_pre = ctx.saved_tensors
+        grad_y, grad_g = torch.empty_like(y), torch.empty_like(gate_pre)
+        node_gate_bwd_.raw(grad_out.contiguous(), y, gate_pre, grad_y, grad_g)
+        return grad_y, grad_g

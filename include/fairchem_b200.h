@@ -420,6 +420,17 @@ int fcb200_lx_rms_norm_sh_bwd(const float* grad_out, const float* x, const float
                               float* grad_x, int64_t num_nodes, int32_t channels, int32_t lmax, void* stream);
 
 /*
+ * Gate of the node-wise feed-forward (SpectralAtomwise, src/fairchem/core/models/uma/escn_md_block.py:288-328 with
+ * GateActivation, src/fairchem/core/models/uma/nn/activation.py:146-165), fused: y [N, NL, H] L-major, gate_pre
+ * [N, lmax*H] the scalar Linear's output; out row 0 = SiLU(y_0), rows of degree l = y * sigmoid(SiLU(gate_pre[l-1])).
+ * The backward writes grad_y [N, NL, H] and grad_gate_pre [N, lmax*H].
+ */
+int fcb200_node_gate_fwd(const float* y, const float* gate_pre, float* out, int64_t num_nodes, int32_t hidden, int32_t lmax,
+                         void* stream);
+int fcb200_node_gate_bwd(const float* grad_out, const float* y, const float* gate_pre, float* grad_y, float* grad_gate_pre,
+                         int64_t num_nodes, int32_t hidden, int32_t lmax, void* stream);
+
+/*
  * Edge geometry with the compact Wigner-D of the given lmax [E, NW].  Degrees 3 and 4 follow from the
  * degree-1 and degree-(l-1) blocks by the recursion of Ivanic and Ruedenberg; the reference evaluates the
  * same matrices as polynomials of the quaternion (src/fairchem/core/models/uma/common/wigner_d_custom_kernels.py:196-356).

@@ -369,3 +369,24 @@ def test_l4_tf32_split_gemm_mode_matches_reference_golden(ops, golden):
             assert np.max(np.abs(f - g[f"{name}_forces"])) < F_ATOL, name
     finally:
         B.set_gemm_precision(2)
+
+
+def test_node_gate_forward_backward(ops, lmax):
+    """Fused gate of the node-wise feed-forward against SiLU / sigmoid(SiLU(.)) in float64 (escn_md_block.py:323-328)."""
+    sh = ops.SHAPES[lmax]
+    g = torch.Generator().manual_seed(13)
+    n, h = 77, 128
+    y = torch.randn(n, sh.nl, h, generator=g).cuda()
+    pre = torch.randn(n, sh.lmax * h, generator=g).cuda()
+    ya, pa = y.clone().requires_grad_(True), pre.clone().requires_grad_(True)
+    out = ops.NodeGate.apply(ya, pa)
+    yb, pb = y.double().requires_grad_(True), pre.double().requires_grad_(True)
+    gates = torch.sigmoid(torch.nn.functional.silu(pb)).view(n, sh.lmax, h)
+    ref = torch.cat([torch.nn.functional.silu(yb[:, :1])] + [yb[:, l * l:(l + 1) ** 2] * gates[:, l - 1:l]
+                                                           for l in range(1, sh.lmax + 1)], dim=1)
+    torch.testing.assert_close(out, ref.float(), rtol=1e-5, atol=1e-5)
+    cot = torch.randn(out.shape, generator=g).cuda()
+    ga = torch.autograd.grad(out, [ya, pa], cot)
+    gb = torch.autograd.grad(ref, [yb, pb], cot.double())
+    for a, b in zip(ga, gb):
+        torch.testing.assert_close(a, b.float(), rtol=1e-4, atol=1e-5)
