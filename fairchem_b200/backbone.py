@@ -130,9 +130,11 @@ class SO3Linear(nn.Module):
         self.lmax = lmax
 
     def forward(self, x):  # x [N,(lmax+1)^2,Cin]
-        if x.is_cuda and _GemmState.precision != 0:
+        if not x.is_cuda:
+            raise ops._lib.FairchemB200Error("fairchem_b200 modules need CUDA tensors (no CPU fallback)")
+        if _GemmState.precision != 0:
             return _SO3LinearFn.apply(x, self.weight.detach(), self.bias.detach())
-        outs = []
+        outs = []  # precision 0: cuBLAS float32 through torch, for A/B measurements only
         for l in range(self.lmax + 1):
             y = torch.matmul(x[:, l * l:(l + 1) * (l + 1)], self.weight[l].t())
             if l == 0:
@@ -180,15 +182,8 @@ class SpectralAtomwise(nn.Module):
 
     def forward(self, x):
         lin = self.scalar_mlp[0]
-        if x.is_cuda and self.lmax in ops.SHAPES and self.h % 128 == 0:
-            gate_pre = _linear(x[:, 0], lin.weight, lin.bias)
-            return self.so3_linear_2(ops.NodeGate.apply(self.so3_linear_1(x), gate_pre))
-        gates = torch.sigmoid(F.silu(_linear(x[:, 0], lin.weight, lin.bias))).view(x.shape[0], self.lmax, self.h)
-        y = self.so3_linear_1(x)
-        parts = [F.silu(y[:, :1])]
-        for l in range(1, self.lmax + 1):
-            parts.append(y[:, l * l:(l + 1) * (l + 1)] * gates[:, l - 1:l])
-        return self.so3_linear_2(torch.cat(parts, dim=1))
+        gate_pre = _linear(x[:, 0], lin.weight, lin.bias)
+        return self.so3_linear_2(ops.NodeGate.apply(self.so3_linear_1(x), gate_pre))
 
 
 class RMSNormSH(nn.Module):
@@ -199,23 +194,9 @@ class RMSNormSH(nn.Module):
         self.affine_weight = nn.Parameter(torch.ones(lmax + 1, c))
         self.affine_bias = nn.Parameter(torch.zeros(c))
         self.lmax, self.eps = lmax, eps
-        l_of = [l for l in range(lmax + 1) for _ in range(2 * l + 1)]
-        self.register_buffer("l_index", torch.tensor(l_of), persistent=False)
-        self.register_buffer("balance", torch.tensor([1.0 / ((2 * l + 1) * (lmax + 1)) for l in l_of]).view(1, -1, 1),
-                             persistent=False)
 
     def forward(self, x, extra=None):
-        if x.is_cuda and self.lmax in ops.SHAPES:
-            return ops.RMSNormSH.apply(x, self.affine_weight.detach(), self.affine_bias.detach(), extra, self.eps)
-        out = self._forward_torch(x)
-        return out if extra is None else torch.cat([out[:, :1] + extra.unsqueeze(1), out[:, 1:]], dim=1)
-
-    def _forward_torch(self, x):
-        x0 = x[:, :1] - x[:, :1].mean(dim=2, keepdim=True)
-        feat = torch.cat([x0, x[:, 1:]], dim=1)
-        nrm = (feat.square() * self.balance).sum(dim=1, keepdim=True).mean(dim=2, keepdim=True)
-        out = feat * ((nrm + self.eps).rsqrt() * self.affine_weight[self.l_index].unsqueeze(0))
-        return torch.cat([out[:, :1] + self.affine_bias, out[:, 1:]], dim=1)
+        return ops.RMSNormSH.apply(x, self.affine_weight.detach(), self.affine_bias.detach(), extra, self.eps)
 
 
 class _Block(nn.Module):
