@@ -376,6 +376,12 @@ def _split16(w: torch.Tensor):
     return hit[1], hit[2], hit[3]
 
 
+def _absmax(t: torch.Tensor) -> torch.Tensor:
+    """max |t| as a device scalar in one pass over t (no |t| temporary)."""
+    lo, hi = torch.aminmax(t)
+    return torch.maximum(-lo, hi)
+
+
 def _pow2_scale(magnitude: torch.Tensor) -> torch.Tensor:
     """One-element device tensor: the power of two that maps ``magnitude`` to [2^6, 2^7)."""
     return torch.exp2(torch.floor(6.0 - torch.log2(magnitude.float().clamp_min(1e-30)))).reshape(1).contiguous()
@@ -395,7 +401,7 @@ class _GradScale:
         """The enclosing scale if there is one, else one derived from ``grad`` itself."""
         if _GemmState.precision != 2 or _GemmState.a_scale is not None:
             return contextlib.nullcontext()
-        return _GradScale(grad.abs().amax())
+        return _GradScale(_absmax(grad))
 
     def __enter__(self):
         self.saved = _GemmState.a_scale
@@ -417,7 +423,7 @@ def _gemm(x2, w, bias, y, precision, grad=None):
         hi, lo, sc = _split16(w)
         a_scale = None
         if grad is not None:
-            a_scale = _GemmState.a_scale if _GemmState.a_scale is not None else _pow2_scale(grad.abs().amax())
+            a_scale = _GemmState.a_scale if _GemmState.a_scale is not None else _pow2_scale(_absmax(grad))
         ops.gemm_f16x2_.raw(x2, hi, lo, sc, a_scale, bias, y, _status(x2.device))
     elif precision >= 2:
         hi, lo = _split(w)
@@ -674,7 +680,7 @@ class _EdgeBlockFn(torch.autograd.Function):
     def backward(ctx, grad_out):
         x, wig, winv, gauss = ctx.saved_tensors
         grad_out = grad_out.contiguous()
-        with _GradScale(grad_out.abs().amax()):
+        with _GradScale(_absmax(grad_out)):
             return _EdgeBlockFn._backward_chunks(ctx, x, wig, winv, gauss, grad_out)
 
     @staticmethod
@@ -762,7 +768,7 @@ class _EdgeDegreeFn(torch.autograd.Function):
         grad_out = grad_out.contiguous()
         gwinv = torch.empty_like(winv)
         ggauss = torch.empty_like(gauss)
-        with _GradScale(grad_out.abs().amax()):
+        with _GradScale(_absmax(grad_out)):
             for ch in ectx.chunks:
                 sl = slice(ch.e0, ch.e1)
                 with torch.enable_grad():
