@@ -142,6 +142,9 @@ def run_b200(args):
     if world > 1:
         import torch.distributed as dist
 
+        # the per-layer exchanges are small all-to-alls and the reductions move 1.2 MB: nothing here gains from
+        # in-switch reduction, and without it a rank that fails cannot fault its peers through a multicast binding
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
     B.set_gemm_precision(args.precision)
     if args.generic_kernels:
