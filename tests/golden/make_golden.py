@@ -1,7 +1,7 @@
 """Generate the golden vectors under tests/golden/ by running the UNMODIFIED fairchem reference.
 
-Run once on a machine that has the reference checkout (default /root/reference, override with
-FAIRCHEM_REF_ROOT):
+Run once on a machine that has a checkout of the reference (its location is ``oracle.ref_shim.REF_ROOT``,
+set with the environment variable FAIRCHEM_REF_ROOT):
 
     python tests/golden/make_golden.py
 
