@@ -63,8 +63,8 @@ def build(force: bool = False, verbose: bool = False) -> str:
                 sys.stderr.write(res.stdout + res.stderr)
             if res.returncode != 0:
                 raise RuntimeError(f"nvcc failed on {src}")
-            with open(obj + ".ptxas.txt", "w") as fh:
-                fh.write(res.stderr)
+            with open(obj + ".ptxas.txt", "w") as fh:  # registers / spills / shared memory per kernel, without the timings
+                fh.write("".join(ln for ln in res.stderr.splitlines(keepends=True) if "Compile time" not in ln))
             relink = True
     if relink or _stale(LIB_PATH, objs):
         cmd = [nvcc, "-shared", "-o", LIB_PATH, *objs]  # static cudart; no link-time libcuda
