@@ -383,14 +383,14 @@ def _absmax(t: torch.Tensor) -> torch.Tensor:
 
 
 def _pow2_scale(magnitude: torch.Tensor) -> torch.Tensor:
-    """One-element device tensor: the power of two that maps ``magnitude`` to [2^6, 2^7)."""
+    """One-element device tensor: the power of two that maps ``magnitude`` into (2^5, 2^6]."""
     return torch.exp2(torch.floor(6.0 - torch.log2(magnitude.float().clamp_min(1e-30)))).reshape(1).contiguous()
 
 
 class _GradScale:
     """Precision 2: gradients are usually far below the half range, so the backward contractions issued inside
     the block scale their A operand by the power of two that maps ``magnitude`` (a device scalar: the largest
-    incoming gradient of the block) to about 2^6; 2^9 of headroom remain above it and values down to 2^-20
+    incoming gradient of the block) into (2^5, 2^6]; 2^10 of headroom remain above it and values down to 2^-19
     of it stay normal halves."""
 
     def __init__(self, magnitude: torch.Tensor):
