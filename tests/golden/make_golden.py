@@ -176,6 +176,34 @@ def make_backend_op_golden():
                         rad=rad.numpy(), deg=deg.numpy())
 
 
+def make_backend_op_l4_golden():
+    """The same ops with lmax=4, mmax=2: the reference selects the |m| <= 2 coefficients (coefficient_idx) and composes
+    with the reduced to_m mapping (execution_backends.py:122-158); N=10 nodes, E=36 edges, C=128."""
+    ref_shim.load()
+    from fairchem.core.models.uma.common.so3 import CoefficientMapping
+    from fairchem.core.models.uma.nn.execution_backends import ExecutionBackend
+    from oracle.escn_md_oracle import edge_quaternion, wigner_blocks
+
+    g = torch.Generator().manual_seed(17)
+    n, e, c = 10, 36, 128
+    x = torch.randn(n, 25, c, generator=g)
+    edge_index = torch.stack([torch.randint(0, n, (e,), generator=g), torch.sort(torch.randint(0, n, (e,), generator=g))[0]])
+    d = wigner_blocks(edge_quaternion(torch.randn(e, 3, generator=g)), 4)
+    env = torch.rand(e, 1, 1, generator=g)
+    coefficient_index = CoefficientMapping(4, 4).coefficient_idx(4, 2)
+    reduced = CoefficientMapping(4, 2)
+    w, winv = ExecutionBackend.prepare_wigner(d, d.transpose(1, 2).contiguous() * env, reduced, coefficient_index)
+    msg = ExecutionBackend.node_to_edge_wigner_permute(x, edge_index, w)
+    y = torch.randn(e, 19, c, generator=g)
+    back = ExecutionBackend.permute_wigner_inv_edge_to_node(y, winv, edge_index[1], n)
+    rad = torch.randn(e, 5 * c, generator=g)
+    deg = ExecutionBackend.edge_degree_scatter(x, rad, winv, edge_index[1], 5, c, 5.0)
+    np.savez_compressed(os.path.join(OUT, "backend_ops_l4.npz"), x=x.numpy(), edge_index=edge_index.numpy(),
+                        wigner=d.numpy(), env=env.view(-1).numpy(), msg=msg.numpy(), y=y.numpy(), back=back.numpy(),
+                        rad=rad.numpy(), deg=deg.numpy())
+    print("ops l4", msg.shape, back.shape, deg.shape)
+
+
 def make_model_golden():
     bb, head = ref_model(0)
     cases = {
@@ -259,9 +287,11 @@ def make_partition_golden():
 
 
 if __name__ == "__main__":
-    which = sys.argv[1:] or ["graph", "wigner", "ops", "model", "partition", "l4", "stress"]
+    which = sys.argv[1:] or ["graph", "wigner", "ops", "model", "partition", "l4", "stress", "ops_l4"]
     if "stress" in which:
         make_stress_golden()
+    if "ops_l4" in which:
+        make_backend_op_l4_golden()
     if "l4" in which:
         make_l4_golden()
     if "partition" in which:

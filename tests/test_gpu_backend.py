@@ -75,3 +75,36 @@ def test_op_table_gradients_flow_to_dense_wigner(backend):
     mask = (w.detach() != 0).float()  # only the block-diagonal entries exist for the kernels
     torch.testing.assert_close(ga[0], gb[0], rtol=1e-4, atol=2e-4 * gb[0].abs().max().item())
     torch.testing.assert_close(ga[1], gb[1] * mask, rtol=1e-4, atol=2e-4 * gb[1].abs().max().item())
+
+
+@pytest.mark.parametrize("shuffle", [False, True])
+def test_op_table_lmax4_matches_reference_outputs(backend, golden, shuffle):
+    """lmax = 4, mmax = 2: the reference selects the |m| <= 2 coefficients and applies the reduced M-mapping in
+    prepare_wigner (execution_backends.py:122-158); this backend takes the square matrices and selects in the kernels."""
+    g = golden("backend_ops_l4.npz")
+    x = torch.tensor(g["x"]).cuda()
+    ei = torch.tensor(g["edge_index"]).cuda()
+    d = torch.tensor(g["wigner"]).cuda()
+    env = torch.tensor(g["env"]).cuda()
+    y = torch.tensor(g["y"]).cuda()
+    rad = torch.tensor(g["rad"]).cuda()
+    msg_ref = torch.tensor(g["msg"]).cuda()
+    e, n, c = ei.shape[1], x.shape[0], x.shape[2]
+    if shuffle:
+        p = torch.randperm(e, generator=torch.Generator().manual_seed(0)).cuda()
+        ei, d, env, y, rad, msg_ref = ei[:, p].contiguous(), d[p], env[p], y[p], rad[p], msg_ref[p]
+    w, winv = backend.prepare_wigner(d, d.transpose(1, 2).contiguous() * env.view(-1, 1, 1), None, None)
+    msg = backend.node_to_edge_wigner_permute(x, ei, w)
+    assert msg.shape == (e, 19, 2 * c)
+    torch.testing.assert_close(msg, msg_ref, **TOL)
+    back = backend.permute_wigner_inv_edge_to_node(y, winv, ei[1], n)
+    torch.testing.assert_close(back.cpu(), torch.tensor(g["back"]), **TOL)
+    deg = backend.edge_degree_scatter(x, rad, winv, ei[1], 5, c, 5.0)
+    torch.testing.assert_close(deg.cpu(), torch.tensor(g["deg"]), **TOL)
+    ones = torch.ones(e, 12 * 2 * c, device="cuda")
+    m0, m1, m2 = backend.fused_node_to_edge_conv1_pack(x, ei, w, ones, c)
+    assert m0.shape == (e, 10 * c) and m1.shape == (e, 16 * c) and m2.shape == (e, 12 * c)
+    torch.testing.assert_close(torch.cat([m0, m1, m2], dim=1).view(e, 19, 2 * c), msg_ref, **TOL)
+    flat = y.reshape(e, -1)
+    back2 = backend.fused_conv2_inv_edge_to_node(flat[:, : 5 * c], flat[:, 5 * c: 13 * c], flat[:, 13 * c:], winv, ei[1], n, c)
+    torch.testing.assert_close(back2.cpu(), torch.tensor(g["back"]), **TOL)

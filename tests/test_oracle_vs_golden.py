@@ -144,3 +144,18 @@ def test_stress_oracle_matches_reference(golden, name):
     # the same number as the edge sum sym(sum_e dE/dvec_e (x) vec_e) / V, checked here through its symmetry and trace
     s33 = s.numpy().reshape(3, 3)
     assert np.allclose(s33, s33.T, atol=1e-9)
+
+
+def test_reference_lmax4_backend_ops_are_the_dense_formulas(golden):
+    """The reference's lmax=4/mmax=2 gather-rotate and rotate-back outputs equal the M-major rows of the block-diagonal
+    matrix applied to the node rows, which is what the GPU parity tests of the any-lmax kernels compare against."""
+    g = golden("backend_ops_l4.npz")
+    x, ei, d = torch.tensor(g["x"]), torch.tensor(g["edge_index"]), torch.tensor(g["wigner"])
+    l_of, m_of, m_order, m_size = O.lm_tables(4, 2)
+    kept = O.kept_full_indices(4, 2)
+    rows = [kept[i] for i in m_order]
+    msg = torch.bmm(d[:, rows, :], torch.cat([x[ei[0]], x[ei[1]]], dim=2))
+    assert torch.allclose(msg, torch.tensor(g["msg"]), atol=2e-5, rtol=0)
+    winv = d.transpose(1, 2)[:, :, rows] * torch.tensor(g["env"]).view(-1, 1, 1)
+    back = torch.zeros(x.shape[0], 25, x.shape[2]).index_add(0, ei[1], torch.bmm(winv, torch.tensor(g["y"])))
+    assert torch.allclose(back, torch.tensor(g["back"]), atol=2e-5, rtol=0)
