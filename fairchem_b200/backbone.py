@@ -468,6 +468,63 @@ def _radial(rad: RadialMLP, tables, gauss_c, zs, zt, nb: int):
     return _linear(h, rad.net[6].weight, rad.net[6].bias)
 
 
+def _dense(x2d, weight, bias, out=None, grad=None):
+    """out = x2d @ weight^T + bias on the contraction kernels, without autograd."""
+    y = out if out is not None else torch.empty(x2d.shape[0], weight.shape[0], dtype=x2d.dtype, device=x2d.device)
+    _gemm(x2d, weight, bias, y, _GemmState.precision, grad=grad)
+    return y
+
+
+class _RadialKeep:
+    """Per-edge activations of one layer's radial MLP that its backward pass reuses instead of recomputing: the
+    pre-activations and LayerNorm statistics of both hidden layers ([E,128] + [E,2] each) and, when memory allows,
+    the radial weights themselves ([E, NRAD*2C])."""
+
+    def __init__(self, num_edges: int, hidden: int, out_width: int, keep_output: bool, device):
+        rows = -(-num_edges // 65536) * 65536
+        f32 = dict(dtype=torch.float32, device=device)
+        self.pre1, self.pre2 = torch.empty(rows, hidden, **f32)[:num_edges], torch.empty(rows, hidden, **f32)[:num_edges]
+        self.st1, self.st2 = torch.empty(rows, 2, **f32)[:num_edges], torch.empty(rows, 2, **f32)[:num_edges]
+        self.out = torch.empty(rows, out_width, **f32)[:num_edges] if keep_output else None
+
+
+def _radial_forward(rad: RadialMLP, tables, gauss_c, zs, zt, nb: int, keep: Optional[_RadialKeep] = None, sl=None,
+                    from_kept: bool = False):
+    """The radial MLP of `_radial` written out on the kernels (no autograd).  With ``keep`` the hidden pre-activations
+    and LayerNorm statistics (and the output, if the keeper holds it) are written into / read from its slice ``sl``;
+    ``from_kept`` skips the layers whose results are already there.  Returns (rad, (pre1, st1, pre2, st2))."""
+    w0, ln1, w1, ln2, w2 = rad.net[0], rad.net[1], rad.net[3], rad.net[4], rad.net[6]
+    e, dev = gauss_c.shape[0], gauss_c.device
+    if keep is not None:
+        pre1, st1, pre2, st2 = keep.pre1[sl], keep.st1[sl], keep.pre2[sl], keep.st2[sl]
+    else:
+        pre1 = torch.empty(e, w0.weight.shape[0], dtype=torch.float32, device=dev)
+        pre2 = torch.empty(e, w1.weight.shape[0], dtype=torch.float32, device=dev)
+        st1, st2 = torch.empty(e, 2, dtype=torch.float32, device=dev), torch.empty(e, 2, dtype=torch.float32, device=dev)
+    if from_kept and keep is not None and keep.out is not None:
+        return keep.out[sl], (pre1, st1, pre2, st2)
+    h = torch.empty_like(pre1)
+    if not (from_kept and keep is not None):
+        _dense(gauss_c, w0.weight.detach()[:, :nb], w0.bias.detach(), out=pre1)
+        ops.radial_act_fwd_.raw(pre1, tables[0], tables[1], zs, zt, ln1.weight.detach(), ln1.bias.detach(), float(ln1.eps), h, st1)
+        _dense(h, w1.weight.detach(), w1.bias.detach(), out=pre2)
+    ops.radial_act_fwd_.raw(pre2, None, None, None, None, ln2.weight.detach(), ln2.bias.detach(), float(ln2.eps), h, st2)
+    out = keep.out[sl] if keep is not None and keep.out is not None else None
+    return _dense(h, w2.weight.detach(), w2.bias.detach(), out=out), (pre1, st1, pre2, st2)
+
+
+def _radial_backward(rad: RadialMLP, tables, grad_rad, acts, zs, zt, nb: int, out):
+    """Gradient of the radial weights' loss with respect to the distance basis, into ``out`` [E, nb]."""
+    w0, ln1, w1, ln2, w2 = rad.net[0], rad.net[1], rad.net[3], rad.net[4], rad.net[6]
+    pre1, st1, pre2, st2 = acts
+    g = _dense(grad_rad, _transposed(w2.weight.detach()), None, grad=grad_rad)
+    gp = torch.empty_like(g)
+    ops.radial_act_bwd_.raw(g, pre2, None, None, None, None, ln2.weight.detach(), ln2.bias.detach(), st2, gp)
+    _dense(gp, _transposed(w1.weight.detach()), None, out=g, grad=gp)
+    ops.radial_act_bwd_.raw(g, pre1, tables[0], tables[1], zs, zt, ln1.weight.detach(), ln1.bias.detach(), st1, gp)
+    return _dense(gp, _transposed(w0.weight.detach()[:, :nb]), None, out=out, grad=gp)
+
+
 def _block_weight(w: torch.Tensor) -> torch.Tensor:
     """[[Wa, -Wb], [Wb, Wa]] for an SO(2) m>0 weight W = [Wa; Wb] ([2*half, K] -> [2*half, 2K]): one GEMM on
     [x_re | x_im] gives [y_re | y_im] (SO2_m_Conv_Block, src/fairchem/core/models/uma/nn/so2_layers.py:83-169)."""
@@ -660,11 +717,15 @@ class _EdgeBlockFn(torch.autograd.Function):
         rows = -(-g.num_edges // 65536) * 65536
         y_all = torch.empty(rows, (ew.lmax + nm) * h, dtype=x.dtype, device=x.device)[: g.num_edges] if keep_level >= 1 else None
         msg_all = torch.empty(rows, nm, c, dtype=x.dtype, device=x.device)[: g.num_edges] if keep_level >= 2 else None
+        rfn = ew.so2_conv_1.rad_func
+        rkeep = None
+        if keep_level >= 1:  # level 3 also keeps the radial weights
+            rkeep = _RadialKeep(g.num_edges, rfn.net[0].weight.shape[0], rfn.net[6].weight.shape[0], keep_level >= 3, x.device)
         with torch.no_grad():
             for ch in ectx.chunks:
                 sl = slice(ch.e0, ch.e1)
                 ec = ch.e1 - ch.e0
-                rad = _radial(ew.so2_conv_1.rad_func, tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb)
+                rad, _ = _radial_forward(rfn, tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb, rkeep, sl)
                 m = _gather_rotate(x, g, sl, wig, rad, nm)
                 del rad
                 y = _conv_forward(ew.so2_conv_1, m, out=None if y_all is None else y_all[sl])
@@ -673,7 +734,7 @@ class _EdgeBlockFn(torch.autograd.Function):
                                     out=None if msg_all is None else msg_all[sl].view(ec, nm * c)).view(ec, nm, c)
                 ops.rotate_back_reduce_fwd_.raw(msg, winv[sl], ch.row_ptr, out[ch.n0:ch.n1])
         ctx.save_for_backward(x, wig, winv, gauss)
-        ctx.ew, ctx.tables, ctx.ectx, ctx.nb, ctx.kept = ew, tables, ectx, nb, (y_all, msg_all)
+        ctx.ew, ctx.tables, ctx.ectx, ctx.nb, ctx.kept = ew, tables, ectx, nb, (y_all, msg_all, rkeep)
         return out
 
     @staticmethod
@@ -693,16 +754,15 @@ class _EdgeBlockFn(torch.autograd.Function):
         gwig = torch.empty_like(wig)
         gwinv = torch.empty_like(winv)
         ggauss = torch.empty_like(gauss)
-        y_all, msg_all = ctx.kept
+        y_all, msg_all, rkeep = ctx.kept
         ctx.kept = None
+        rfn = ew.so2_conv_1.rad_func
         scale = _GemmState.a_scale  # the power of two the gradient operands of this block are written with
         for ci, ch in enumerate(ectx.chunks):
             sl = slice(ch.e0, ch.e1)
             ec = ch.e1 - ch.e0
-            with torch.enable_grad():
-                g_c = gauss[sl].detach().requires_grad_(True)
-                rad = _radial(ew.so2_conv_1.rad_func, tables, g_c, ectx.z_src[sl], ectx.z_tgt[sl], nb)
-            rad_d = rad.detach()
+            rad_d, acts = _radial_forward(rfn, tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb, rkeep, sl,
+                                          from_kept=rkeep is not None)
             y = None if y_all is None else y_all[sl]
             msg = None if msg_all is None else msg_all[sl]
             if y is None:
@@ -736,9 +796,8 @@ class _EdgeBlockFn(torch.autograd.Function):
             ops.segment_sum(g_src, ch.src_ptr, ch.src_perm, ch.src_nodes.shape[0], out=gx, out_index=ch.src_nodes,
                             accumulate=True)
             del g_src, g_tgt
-            (gg,) = torch.autograd.grad(rad, g_c, grad_rad)
-            ggauss[sl] = gg
-            del rad, rad_d, grad_rad, gg
+            _radial_backward(rfn, tables, grad_rad, acts, ectx.z_src[sl], ectx.z_tgt[sl], nb, ggauss[sl])
+            del rad_d, grad_rad, acts
         return gx, gwig, gwinv, ggauss, None, None, None, None, None
 
 
@@ -844,7 +903,8 @@ class eSCNMDBackboneB200(nn.Module):
         self.regress_forces, self.direct_forces, self.regress_stress = regress_forces, direct_forces, regress_stress
         self.edge_chunk_size = int(edge_chunk_size)
         # what every layer keeps per edge for its backward pass: 0 nothing (recompute the chunk), 1 the conv-1
-        # output [E,(lmax+NM)H], 2 also the messages [E,NM*C]; None picks the highest level that fits in free memory
+        # output [E,(lmax+NM)H] and the radial MLP's hidden pre-activations, 2 also the messages [E,NM*C], 3 also the
+        # radial weights [E,NRAD*2C]; None picks the highest level that fits in free memory
         self.keep_level = keep_level
         self.dataset_mapping = dict(dataset_mapping or {"omat": "omat", "omol": "omol"})
         self.sph_feature_size = (lmax + 1) ** 2
@@ -976,11 +1036,15 @@ class eSCNMDBackboneB200(nn.Module):
         avail = free + torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
         sh = ops.SHAPES[self.lmax]
         rows = -(-num_edges // 65536) * 65536
-        need_1 = rows * (sh.lmax + sh.nm) * self.hidden_channels * 4
+        need_1 = rows * ((sh.lmax + sh.nm) * self.hidden_channels + 2 * self.edge_channels + 4) * 4
         need_2 = need_1 + rows * sh.nm * self.sphere_channels * 4
+        need_3 = need_2 + rows * sh.nrad * 2 * self.sphere_channels * 4
         # a chunk's temporaries measure about 5 operand buffers [E_c, NM*2C] in the backward pass; allow 10
         chunk = min(num_edges, int(1.25 * self.edge_chunk_size))
         reserve = 0.06 * total + 10 * chunk * sh.nm * 2 * self.sphere_channels * 4
+        # level 3 only when every layer can have it with room to spare (a partitioned run, a smaller system)
+        if self.num_layers * need_3 + 1.5 * reserve < avail:
+            return 3
         if need_2 + reserve < avail:
             return 2
         if need_1 + reserve < avail:

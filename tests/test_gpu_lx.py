@@ -287,7 +287,7 @@ def test_l4_keep_levels_and_chunking_agree(model_l4):
 
     d = synthetic.water_box(96, seed=0)
     e1, f1 = run(model_l4[0], d)
-    for level, chunk in ((0, 1 << 20), (1, 512), (2, 4096)):
+    for level, chunk in ((0, 1 << 20), (1, 512), (2, 4096), (3, 700)):
         m = build_model(weights.ESCN_MD_L4, model_l4[1], edge_chunk_size=chunk, keep_level=level)
         e2, f2 = run(m, d)
         assert np.max(np.abs(e1 - e2) / np.abs(e2)) < 1e-6 and np.max(np.abs(f1 - f2)) < 2e-6, (level, chunk)

@@ -63,7 +63,7 @@ def test_chunking_does_not_change_results(model):
     e2, f2, _ = run((big, sd), d)
     assert np.max(np.abs(e1 - e2) / np.abs(e2)) < 1e-6 and np.max(np.abs(f1 - f2)) < 2e-6
     # recomputing the first convolution in the backward pass instead of keeping its output changes nothing
-    for level in (0, 1, 2):
+    for level in (0, 1, 2, 3):
         m = build_model(weights.UMA_S, sd, edge_chunk_size=4096, keep_level=level)
         e3, f3, _ = run((m, sd), d)
         assert np.max(np.abs(e1 - e3) / np.abs(e3)) < 1e-6 and np.max(np.abs(f1 - f3)) < 2e-6, level

@@ -51,18 +51,22 @@ def test_keep_level_policy(monkeypatch):
     dev = torch.device("cuda", 0)
     total = 183 * 2 ** 30
     edges = 3_100_000
-    need_1 = -(-edges // 65536) * 65536 * 11 * 128 * 4
-    need_2 = need_1 + -(-edges // 65536) * 65536 * 9 * 128 * 4
+    rows = -(-edges // 65536) * 65536
+    need_1 = rows * (11 * 128 + 2 * 128 + 4) * 4        # conv-1 output + radial pre-activations and statistics
+    need_2 = need_1 + rows * 9 * 128 * 4                # + messages
+    need_3 = need_2 + rows * 6 * 256 * 4                # + radial weights
 
-    def with_free(free):
+    def with_free(free, num_edges=edges):
         monkeypatch.setattr(torch.cuda, "mem_get_info", lambda device=None: (free, total))
         monkeypatch.setattr(torch.cuda, "memory_reserved", lambda device=None: 0)
         monkeypatch.setattr(torch.cuda, "memory_allocated", lambda device=None: 0)
-        return bb._keep_level_for_next_layer(edges, dev)
+        return bb._keep_level_for_next_layer(num_edges, dev)
 
     # reserve for the per-chunk temporaries of both passes: 6 % of the device + 10 operand buffers of one chunk
     reserve = 0.06 * total + 10 * int(1.25 * bb.edge_chunk_size) * 9 * 2 * 128 * 4
-    assert with_free(175 * 2 ** 30) == 2
+    assert with_free(175 * 2 ** 30) == 2                     # the 100k-atom box: level 3 would not fit in all four layers
+    assert with_free(int(4 * need_3 + 1.5 * reserve) + 2 ** 20) == 3
+    assert with_free(175 * 2 ** 30, num_edges=edges // 4) == 3   # a quarter of the edges (4 ranks): everything is kept
     assert with_free(int(need_2 + reserve) + 2 ** 20) == 2
     assert with_free(int(need_2 + reserve) - 2 ** 20) == 1   # the reserve no longer fits beside level 2
     assert with_free(int(need_1 + reserve) - 2 ** 20) == 0
