@@ -1029,8 +1029,8 @@ class eSCNMDBackboneB200(nn.Module):
         per-chunk temporaries of both passes."""
         if self.keep_level is not None:
             return self.keep_level
-        if device.type != "cuda":
-            return 0
+        if device.type != "cuda" or not (self.regress_forces or self.regress_stress) or not torch.is_grad_enabled():
+            return 0  # nothing will be differentiated: keep nothing
         free, total = torch.cuda.mem_get_info(device)
         # memory the caching allocator already holds but is not using counts as available
         avail = free + torch.cuda.memory_reserved(device) - torch.cuda.memory_allocated(device)
