@@ -538,76 +538,6 @@ def _block_weight(w: torch.Tensor) -> torch.Tensor:
     return hit[1]
 
 
-class _SO2Conv(torch.autograd.Function):
-    """One SO(2) convolution as three GEMMs on column ranges of the M-major edge matrix.
-
-    x2d [E, NM*Cin] -> y [E, extra + NM*Cout]: the m=0 GEMM writes its (extra + (lmax+1)*Cout) outputs first,
-    the block-form m=1 and m=2 GEMMs write next to it, so the result is already laid out as
-    [extra | row 0..NM-1] with no concatenation or complex-combine pass (NM = 9 for lmax 2, 19 for lmax 4)."""
-
-    @staticmethod
-    def forward(ctx, x2d, conv: "SO2Convolution", cin: int):
-        e = x2d.shape[0]
-        w0, b0 = conv.fc_m0.weight.detach(), conv.fc_m0.bias.detach()
-        w1, w2 = _block_weight(conv.so2_m_conv[0].fc.weight), _block_weight(conv.so2_m_conv[1].fc.weight)
-        n0, n1, n2 = w0.shape[0], w1.shape[0], w2.shape[0]
-        y = torch.empty(e, n0 + n1 + n2, dtype=x2d.dtype, device=x2d.device)
-        p = _GemmState.precision
-        k0, k1 = w0.shape[1], w1.shape[1]
-        _gemm(x2d[:, :k0], w0, b0, y[:, :n0], p)
-        _gemm(x2d[:, k0: k0 + k1], w1, None, y[:, n0: n0 + n1], p)
-        _gemm(x2d[:, k0 + k1:], w2, None, y[:, n0 + n1:], p)
-        ctx.weights, ctx.cin, ctx.p = (w0, w1, w2), cin, p
-        return y
-
-    @staticmethod
-    def backward(ctx, gy):
-        w0, w1, w2 = ctx.weights
-        cin, p = ctx.cin, ctx.p
-        gy = gy.contiguous()
-        n0, n1 = w0.shape[0], w1.shape[0]
-        k0, k1, k2 = w0.shape[1], w1.shape[1], w2.shape[1]
-        gx = torch.empty(gy.shape[0], k0 + k1 + k2, dtype=gy.dtype, device=gy.device)
-        _gemm(gy[:, :n0], _transposed(w0), None, gx[:, :k0], p, grad=gy)
-        _gemm(gy[:, n0: n0 + n1], _transposed(w1), None, gx[:, k0: k0 + k1], p, grad=gy)
-        _gemm(gy[:, n0 + n1:], _transposed(w2), None, gx[:, k0 + k1:], p, grad=gy)
-        return gx, None, None
-
-
-def _so2_conv1(ew: Edgewise, m):
-    """First SO(2) convolution on the M-major edge rows m [E,NM,2C] -> y [E,(lmax+NM)H] (gate scalars | NM rows)."""
-    e, cin = m.shape[0], m.shape[2]
-    return _SO2Conv.apply(m.view(e, -1), ew.so2_conv_1, cin)
-
-
-def _so2_tail(ew: Edgewise, y):
-    """gate -> second SO(2) convolution: y [E,(lmax+NM)H] -> messages [E,NM,C]."""
-    a = ops.SO2Gate.apply(y, ew.hidden)
-    e, nm, h = a.shape
-    z = _SO2Conv.apply(a.view(e, nm * h), ew.so2_conv_2, h)
-    return z.view(e, nm, -1)
-
-
-def _so2_middle(ew: Edgewise, m):
-    """conv 1 -> gate -> conv 2 on the M-major edge rows m [E,NM,2C]; returns the messages [E,NM,C]."""
-    return _so2_tail(ew, _so2_conv1(ew, m))
-
-
-def _so2_conv_input_grad(conv: "SO2Convolution", gy, cin: int):
-    """d(convolution input) from d(convolution output): three GEMMs with the transposed weights."""
-    w0 = conv.fc_m0.weight.detach()
-    w1, w2 = _block_weight(conv.so2_m_conv[0].fc.weight), _block_weight(conv.so2_m_conv[1].fc.weight)
-    n0, n1 = w0.shape[0], w1.shape[0]
-    p = _GemmState.precision
-    gy = gy.contiguous()
-    k0, k1, k2 = w0.shape[1], w1.shape[1], w2.shape[1]
-    gx = torch.empty(gy.shape[0], k0 + k1 + k2, dtype=gy.dtype, device=gy.device)
-    _gemm(gy[:, :n0], _transposed(w0), None, gx[:, :k0], p, grad=gy)
-    _gemm(gy[:, n0: n0 + n1], _transposed(w1), None, gx[:, k0: k0 + k1], p, grad=gy)
-    _gemm(gy[:, n0 + n1:], _transposed(w2), None, gx[:, k0 + k1:], p, grad=gy)
-    return gx
-
-
 # ---- the chunk pipeline, written out by hand (no autograd inside a chunk) ------------------------
 # A tensor that only feeds a contraction is either float32 or, in precision 2, the pair of half planes
 # (hi, lo) its producer kernel writes so that the tensor cores read it without a conversion pass.

@@ -166,8 +166,10 @@ def test_segment_sum(ops, width, nseg):
     torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-5)
 
 
-def test_so2_middle_matches_oracle_convolutions(ops):
-    """Block-form GEMMs + gate + block-form GEMMs == oracle SO2 conv -> gate -> SO2 conv (so2_layers.py:600-647)."""
+@pytest.mark.parametrize("precision", [2, 3])
+def test_so2_middle_matches_oracle_convolutions(ops, precision):
+    """Block-form GEMMs + gate + block-form GEMMs == oracle SO2 conv -> gate -> SO2 conv (so2_layers.py:600-647),
+    forward and input gradient, on float32 operands (precision 3) and on the pre-split half planes (precision 2)."""
     from fairchem_b200 import backbone as B
 
     torch.manual_seed(0)
@@ -175,18 +177,40 @@ def test_so2_middle_matches_oracle_convolutions(ops):
     ew = B.Edgewise(c, h, 2, 2, [320, 128, 128]).cuda()
     g = torch.Generator().manual_seed(5)
     msg = torch.randn(e, 9, 2 * c, generator=g).cuda()
-    m = msg.clone().requires_grad_(True)
-    out = B._so2_middle(ew, m)
+    cot = torch.randn(e, 9, c, generator=g)
+    B.set_gemm_precision(precision)
+    try:
+        with torch.no_grad():
+            if precision == 2:
+                hi = msg.view(e, -1).half()
+                m = (hi, ((msg.view(e, -1) - hi.float()) * 2048.0).half())
+            else:
+                m = msg.view(e, -1)
+            y = B._conv_forward(ew.so2_conv_1, m)
+            out = B._conv_forward(ew.so2_conv_2, B._gate(y, h, 9)).view(e, 9, c)
+            # input gradient by the explicit chain the edge block uses
+            gmsg = cot.cuda().view(e, -1)
+            if precision == 2:
+                ghi = gmsg.half()
+                gmsg = (ghi, ((gmsg - ghi.float()) * 2048.0).half())
+            ga = B._conv_backward(ew.so2_conv_2, gmsg)
+            gy = B._new_operand(e, y.shape[1], y.device)
+            if isinstance(gy, tuple):
+                ops.so2_gate_bwd_h_(ga, y, gy[0], gy[1], None, h)
+            else:
+                ops.so2_gate_bwd_(ga, y, gy, h)
+            gm = B._conv_backward(ew.so2_conv_1, gy).view(e, 9, 2 * c)
+        B.check_gemm_status()
+    finally:
+        B.set_gemm_precision(2)
     sd = {k: v.detach().double().cpu() for k, v in ew.state_dict().items()}
     md = msg.double().cpu().requires_grad_(True)
-    y, gating = O.so2_convolution(sd, "so2_conv_1.", md, None, [3, 2, 1], h, 2 * h)
-    y = O.gate_activation(gating, y, [0, 1, 0, 1, 0, 1, 1, 1], 2)
-    ref, _ = O.so2_convolution(sd, "so2_conv_2.", y, None, [3, 2, 1], c, 0)
+    yr, gating = O.so2_convolution(sd, "so2_conv_1.", md, None, [3, 2, 1], h, 2 * h)
+    yr = O.gate_activation(gating, yr, [0, 1, 0, 1, 0, 1, 1, 1], 2)
+    ref, _ = O.so2_convolution(sd, "so2_conv_2.", yr, None, [3, 2, 1], c, 0)
     torch.testing.assert_close(out.cpu(), ref.float(), rtol=1e-4, atol=1e-4)
-    cot = torch.randn(e, 9, c, generator=g)
-    (ga,) = torch.autograd.grad(out, m, cot.cuda())
     (gb,) = torch.autograd.grad(ref, md, cot.double())
-    torch.testing.assert_close(ga.cpu(), gb.float(), rtol=1e-4, atol=1e-4 * max(1.0, gb.abs().max().item()))
+    torch.testing.assert_close(gm.cpu(), gb.float(), rtol=1e-4, atol=1e-4 * max(1.0, gb.abs().max().item()))
 
 
 def test_gate_activation_forward_backward(ops):
