@@ -41,9 +41,10 @@ def _compact(wigner: torch.Tensor, inverse: bool = False) -> torch.Tensor:
 def _graph_for(src: torch.Tensor, tgt: torch.Tensor, num_nodes: int, num_targets: int):
     """(EdgeGraph over target-sorted edges, permutation or None, inverse permutation or None), cached per edge list."""
     key = (src.data_ptr(), tgt.data_ptr(), int(src.shape[0]), num_nodes, num_targets, src._version, tgt._version)
+    key_tensors = (src, tgt)
     hit = _GRAPH_CACHE.get(key)
     if hit is not None:
-        return hit
+        return hit[:3]
     if len(_GRAPH_CACHE) > 8:
         _GRAPH_CACHE.clear()
     perm = inv = None
@@ -53,7 +54,8 @@ def _graph_for(src: torch.Tensor, tgt: torch.Tensor, num_nodes: int, num_targets
         inv[perm] = torch.arange(perm.shape[0], device=perm.device)
         src, tgt = src[perm], tgt[perm]
     hit = (EdgeGraph(src, tgt, num_nodes, num_targets), perm, inv)
-    _GRAPH_CACHE[key] = hit
+    # the entry keeps the caller's tensors alive: their addresses (the key) cannot be reused by other edge lists
+    _GRAPH_CACHE[key] = hit + (key_tensors,)
     return hit
 
 
