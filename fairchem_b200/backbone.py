@@ -640,8 +640,9 @@ class _EdgeBlockFn(torch.autograd.Function):
         nl = x.shape[1]
         nm = ops.SHAPES[ew.lmax].nm
         out = torch.zeros(g.num_targets, nl, c, dtype=x.dtype, device=x.device)
-        # level 1 keeps the conv-1 outputs (the backward then skips the gather+rotate and the conv-1 GEMMs), level 2
-        # also the messages (no recomputation but the radial MLP); one buffer per layer, chunks write their slices
+        # level 1 keeps the conv-1 outputs and the radial MLP's hidden pre-activations (the backward then skips the
+        # gather+rotate, the conv-1 GEMMs and two radial layers), level 2 also the messages, level 3 also the radial
+        # weights (nothing is recomputed); one buffer per layer and kind, chunks write their slices
         h = ew.hidden
         # rows rounded up so that a slowly changing edge count (MD) asks the allocator for the same block every step
         rows = -(-g.num_edges // 65536) * 65536
@@ -688,7 +689,7 @@ class _EdgeBlockFn(torch.autograd.Function):
         ctx.kept = None
         rfn = ew.so2_conv_1.rad_func
         scale = _GemmState.a_scale  # the power of two the gradient operands of this block are written with
-        for ci, ch in enumerate(ectx.chunks):
+        for ch in ectx.chunks:
             sl = slice(ch.e0, ch.e1)
             ec = ch.e1 - ch.e0
             rad_d, acts = _radial_forward(rfn, tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb, rkeep, sl,
