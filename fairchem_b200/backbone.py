@@ -970,9 +970,10 @@ class eSCNMDBackboneB200(nn.Module):
         need_1 = rows * ((sh.lmax + sh.nm) * self.hidden_channels + 2 * self.edge_channels + 4) * 4
         need_2 = need_1 + rows * sh.nm * self.sphere_channels * 4
         need_3 = need_2 + rows * sh.nrad * 2 * self.sphere_channels * 4
-        # a chunk's temporaries measure about 5 operand buffers [E_c, NM*2C] in the backward pass; allow 10
+        # a chunk's temporaries measure 4 to 5 operand buffers [E_c, NM*2C] in the backward pass; allow 6 and 6 % of
+        # the device for everything that is not per edge
         chunk = min(num_edges, int(1.25 * self.edge_chunk_size))
-        reserve = 0.06 * total + 10 * chunk * sh.nm * 2 * self.sphere_channels * 4
+        reserve = 0.06 * total + 6 * chunk * sh.nm * 2 * self.sphere_channels * 4
         # level 3 only when every layer can have it with room to spare (a partitioned run, a smaller system)
         if self.num_layers * need_3 + 1.5 * reserve < avail:
             return 3

@@ -62,8 +62,8 @@ def test_keep_level_policy(monkeypatch):
         monkeypatch.setattr(torch.cuda, "memory_allocated", lambda device=None: 0)
         return bb._keep_level_for_next_layer(num_edges, dev)
 
-    # reserve for the per-chunk temporaries of both passes: 6 % of the device + 10 operand buffers of one chunk
-    reserve = 0.06 * total + 10 * int(1.25 * bb.edge_chunk_size) * 9 * 2 * 128 * 4
+    # reserve for the per-chunk temporaries of both passes: 6 % of the device + 6 operand buffers of one chunk
+    reserve = 0.06 * total + 6 * int(1.25 * bb.edge_chunk_size) * 9 * 2 * 128 * 4
     assert with_free(175 * 2 ** 30) == 2                     # the 100k-atom box: level 3 would not fit in all four layers
     assert with_free(int(4 * need_3 + 1.5 * reserve) + 2 ** 20) == 3
     assert with_free(175 * 2 ** 30, num_edges=edges // 4) == 3   # a quarter of the edges (4 ranks): everything is kept
