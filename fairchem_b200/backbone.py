@@ -341,11 +341,23 @@ def _status(device):
     return _GemmState.status
 
 
+class HalfRangeError(RuntimeError):
+    """A value left the half-precision range inside a precision-2 contraction; the step's results are invalid."""
+
+
 def check_gemm_status() -> None:
-    if _GemmState.status is not None and int(_GemmState.status.item()) != 0:
-        _GemmState.status.zero_()
-        raise RuntimeError("tcgen05 GEMM: a bounded wait expired inside the kernel, or an operand left the half range "
-                           "(precision 2); results are invalid")
+    """Turn the contraction kernels' device status word into an exception (and clear it): 1 = a bounded wait expired
+    inside a kernel, 2 = an operand or output left the half-precision range (precision 2 only)."""
+    if _GemmState.status is None:
+        return
+    code = int(_GemmState.status.item())
+    if code == 0:
+        return
+    _GemmState.status.zero_()
+    if code == 2:
+        raise HalfRangeError("tcgen05 GEMM: an operand left the half-precision range; results are invalid "
+                             "(use set_gemm_precision(3), or energy_forces(), which falls back by itself)")
+    raise RuntimeError("tcgen05 GEMM: a bounded wait expired inside the kernel; results are invalid")
 
 
 def _transposed(w: torch.Tensor) -> torch.Tensor:
@@ -1108,6 +1120,24 @@ class MLP_EFS_HeadB200(nn.Module):
                 out["stress"] = ((w + w.transpose(1, 2)) / 2 / volume).reshape(-1, 9)
             check_gemm_status()
         return out
+
+
+def energy_forces(backbone, head, data, gamma: Optional[torch.Tensor] = None) -> dict:
+    """``head(data, backbone(data))`` that survives activations or gradients outside the half-precision range: when the
+    default contraction mode reports one (HalfRangeError), the step is repeated with the TF32 split (precision 3),
+    which has no range condition, and the mode is restored."""
+    try:
+        return head(data, backbone(data, gamma=gamma))
+    except HalfRangeError:
+        if _GemmState.precision != 2:
+            raise
+    set_gemm_precision(3)
+    try:
+        if data["pos"].grad is not None:
+            data["pos"].grad = None
+        return head(data, backbone(data, gamma=gamma))
+    finally:
+        set_gemm_precision(2)
 
 
 def build_model(cfg: dict, state_dict: Optional[dict] = None, device="cuda", **overrides):

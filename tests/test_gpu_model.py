@@ -151,3 +151,27 @@ def test_stress_of_a_batch_is_per_system():
     both = synthetic.merge([a, b]).to("cuda")
     got = head(both, bb(both))["stress"].cpu().numpy()
     assert got.shape == (2, 9) and np.max(np.abs(got - np.concatenate(singles))) < 1e-6
+
+
+def test_half_range_overflow_is_reported_and_survivable():
+    """Activations beyond the half-precision range raise HalfRangeError in the default mode; energy_forces() repeats
+    the step with the TF32 split and returns the same numbers a precision-3 model gives."""
+    from fairchem_b200 import backbone as B
+
+    sd = {k: v.clone() for k, v in weights.random_init_state_dict(weights.UMA_S, 0).items()}
+    sd["blocks.0.edge_wise.so2_conv_1.rad_func.net.6.weight"] *= 3.0e5   # radial weights of layer 1 blow up the operand
+    sd["blocks.0.edge_wise.so2_conv_1.rad_func.net.6.bias"] *= 3.0e5
+    bb, head = B.build_model(weights.UMA_S, sd, edge_chunk_size=4096)
+    d = synthetic.fcc_cu((2, 2, 2), seed=0).to("cuda")
+    with pytest.raises(B.HalfRangeError):
+        head(d, bb(d))
+    out = B.energy_forces(bb, head, d)
+    assert B._GemmState.precision == 2
+    B.set_gemm_precision(3)
+    try:
+        ref = head(d, bb(d))
+    finally:
+        B.set_gemm_precision(2)
+    assert torch.isfinite(out["energy"]).all() and torch.isfinite(out["forces"]).all()
+    torch.testing.assert_close(out["energy"], ref["energy"], rtol=1e-6, atol=0)
+    torch.testing.assert_close(out["forces"], ref["forces"], rtol=1e-4, atol=1e-6 * float(ref["forces"].abs().max()))
