@@ -469,17 +469,6 @@ def _linear(x2d, weight, bias=None):
     return _LinearTF32.apply(x2d, weight.detach(), None if bias is None else bias.detach(), _GemmState.precision)
 
 
-def _radial(rad: RadialMLP, tables, gauss_c, zs, zt, nb: int):
-    """RadialMLP on [gauss | src_emb[z_s] | tgt_emb[z_t]] with the embedding part of the first Linear
-    folded into per-element tables."""
-    w0, ln1, ln2 = rad.net[0], rad.net[1], rad.net[4]
-    pre = _linear(gauss_c, w0.weight[:, :nb], w0.bias)
-    h = ops.RadialAct.apply(pre, tables[0], tables[1], zs, zt, ln1.weight.detach(), ln1.bias.detach(), ln1.eps)
-    pre = _linear(h, rad.net[3].weight, rad.net[3].bias)
-    h = ops.RadialAct.apply(pre, None, None, None, None, ln2.weight.detach(), ln2.bias.detach(), ln2.eps)
-    return _linear(h, rad.net[6].weight, rad.net[6].bias)
-
-
 def _dense(x2d, weight, bias, out=None, grad=None):
     """out = x2d @ weight^T + bias on the contraction kernels, without autograd."""
     y = out if out is not None else torch.empty(x2d.shape[0], weight.shape[0], dtype=x2d.dtype, device=x2d.device)
@@ -502,7 +491,8 @@ class _RadialKeep:
 
 def _radial_forward(rad: RadialMLP, tables, gauss_c, zs, zt, nb: int, keep: Optional[_RadialKeep] = None, sl=None,
                     from_kept: bool = False):
-    """The radial MLP of `_radial` written out on the kernels (no autograd).  With ``keep`` the hidden pre-activations
+    """RadialMLP on [gauss | src_emb[z_s] | tgt_emb[z_t]] with the embedding part of the first Linear folded into
+    per-element tables, written out on the kernels (no autograd).  With ``keep`` the hidden pre-activations
     and LayerNorm statistics (and the output, if the keeper holds it) are written into / read from its slice ``sl``;
     ``from_kept`` skips the layers whose results are already there.  Returns (rad, (pre1, st1, pre2, st2))."""
     w0, ln1, w1, ln2, w2 = rad.net[0], rad.net[1], rad.net[3], rad.net[4], rad.net[6]
@@ -756,7 +746,7 @@ class _EdgeDegreeFn(torch.autograd.Function):
         with torch.no_grad():
             for ch in ectx.chunks:
                 sl = slice(ch.e0, ch.e1)
-                r3 = _radial(rad_func, tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb)
+                r3, _ = _radial_forward(rad_func, tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb)
                 ops.edge_degree_fwd_.raw(r3, winv[sl], ch.row_ptr, x[ch.n0:ch.n1], out[ch.n0:ch.n1], rescale)
         ctx.save_for_backward(winv, gauss)
         ctx.rad_func, ctx.tables, ctx.ectx, ctx.nb, ctx.rescale, ctx.c = rad_func, tables, ectx, nb, rescale, c
@@ -773,13 +763,10 @@ class _EdgeDegreeFn(torch.autograd.Function):
         with _GradScale(_absmax(grad_out)):
             for ch in ectx.chunks:
                 sl = slice(ch.e0, ch.e1)
-                with torch.enable_grad():
-                    g_c = gauss[sl].detach().requires_grad_(True)
-                    r3 = _radial(ctx.rad_func, ctx.tables, g_c, ectx.z_src[sl], ectx.z_tgt[sl], nb)
+                r3, acts = _radial_forward(ctx.rad_func, ctx.tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb)
                 gr = torch.empty_like(r3)
-                ops.edge_degree_bwd_.raw(grad_out, r3.detach(), winv[sl], g.tgt[sl], gr, gwinv[sl], ctx.rescale)
-                (gg,) = torch.autograd.grad(r3, g_c, gr)
-                ggauss[sl] = gg
+                ops.edge_degree_bwd_.raw(grad_out, r3, winv[sl], g.tgt[sl], gr, gwinv[sl], ctx.rescale)
+                _radial_backward(ctx.rad_func, ctx.tables, gr, acts, ectx.z_src[sl], ectx.z_tgt[sl], nb, ggauss[sl])
         return grad_out, gwinv, ggauss, None, None, None, None, None
 
 
