@@ -8,13 +8,15 @@
 ``MLP_EFS_Head`` (escn_md.py:1062-1168).  Reference weights load unchanged.
 
 What differs from the reference is how the edge block runs.  Edges are CSR-sorted by target and
-cut into chunks on target boundaries; a chunk runs gather+rotate+radial-scale -> SO(2) GEMMs ->
-gate -> SO(2) GEMMs -> rotate-back + segmented reduce with the chunk's [E_c, *] intermediates
-living only inside the chunk.  The backward pass recomputes a chunk before differentiating it
-(the role ``activation_checkpointing`` plays in escn_md_block.py:157-202), so memory is
-O(nodes) + O(chunk) instead of O(edges * layers), which is what lets a 100k-atom system run on
-one GPU.  The first radial Linear is split into a distance part (a [E,64] GEMM) and two
-per-element tables (``embedding @ W^T``), which removes the [E,320] edge-feature tensor.
+cut into chunks on target boundaries; a chunk runs radial MLP -> gather+rotate+radial-scale -> SO(2) GEMMs ->
+gate -> SO(2) GEMMs -> rotate-back + segmented reduce, written out on the kernels for both passes (no autograd
+inside a chunk).  Tensors that only feed a contraction are written by their producers as half-precision (hi, lo)
+planes the tensor cores read directly.  For its backward pass a layer keeps per-edge outputs as memory allows
+(``keep_level``: nothing / conv-1 output and radial hidden layers / also the messages / also the radial
+weights) and recomputes the rest per chunk - the role ``activation_checkpointing`` plays in
+escn_md_block.py:157-202 - which is what lets a 100k-atom system run on one GPU.  The first radial Linear is
+split into a distance part (a [E,64] GEMM) and two per-element tables (``embedding @ W^T``), which removes the
+[E,320] edge-feature tensor.
 """
 
 from __future__ import annotations
