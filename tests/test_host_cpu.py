@@ -175,3 +175,30 @@ def test_backbone_mirrors_the_reference_module_interface():
         bb.prepare_for_inference(None, NS(activation_checkpointing=True))
     with pytest.raises(ValueError):
         eSCNMDBackboneB200(**dict(weights.UMA_S, lmax=3))
+
+
+def test_bench_reference_arm_prints_one_contract_line():
+    """`bench.py --impl reference` (the CPU oracle on the host cores) prints exactly one JSON line with the keys the
+    bench contract names; non-zero ranks of a multi-rank launch print nothing."""
+    import json
+    import os
+    import subprocess
+    import sys
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, os.path.join(root, "bench.py"), "--impl", "reference", "--workload", "fcc_cu_256", "--steps", "1",
+           "--warmup", "1"]
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=root)
+    assert res.returncode == 0, res.stderr[-2000:]
+    lines = [ln for ln in res.stdout.splitlines() if ln.strip()]
+    assert len(lines) == 1
+    line = json.loads(lines[0])
+    for key in ("impl", "metric", "value", "unit", "n_gpus", "steps", "warmup", "ms_per_step", "higher_is_better", "scaling",
+                "vs_baseline", "dtype", "data", "config", "cpu_baseline", "e2e"):
+        assert key in line, key
+    assert line["impl"] == "reference" and line["unit"] == "atom-steps/s" and line["value"] > 0
+    assert line["cpu_baseline"]["kind"] == "port" and line["cpu_baseline"]["cores"] >= 1
+    assert line["e2e"]["h2d_bytes_per_step"] == 0 and line["e2e"]["value"] == line["value"]
+    env = dict(os.environ, RANK="1", WORLD_SIZE="2", LOCAL_RANK="1")
+    res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=root, env=env)
+    assert res.returncode == 0 and res.stdout.strip() == ""
