@@ -87,7 +87,15 @@ class RadialMLP(nn.Module):
         self.net = nn.Sequential(*mods)
 
     def forward(self, x):
-        return self.net(x)
+        """The MLP on a full edge-feature matrix [E, in] (what ``ExecutionBackend.get_layer_radial_emb`` evaluates,
+        execution_backends.py:96-119): contractions on the tcgen05 GEMM, LayerNorm + SiLU in the fused kernel."""
+        n_hidden = (len(self.net) - 1) // 3
+        h = x
+        for i in range(n_hidden):
+            lin, ln = self.net[3 * i], self.net[3 * i + 1]
+            h = ops.RadialAct.apply(_linear(h, lin.weight, lin.bias), None, None, None, None, ln.weight.detach(),
+                                    ln.bias.detach(), ln.eps)
+        return _linear(h, self.net[-1].weight, self.net[-1].bias)
 
 
 class _SO2mConv(nn.Module):

@@ -108,3 +108,21 @@ def test_op_table_lmax4_matches_reference_outputs(backend, golden, shuffle):
     flat = y.reshape(e, -1)
     back2 = backend.fused_conv2_inv_edge_to_node(flat[:, : 5 * c], flat[:, 5 * c: 13 * c], flat[:, 13 * c:], winv, ei[1], n, c)
     torch.testing.assert_close(back2.cpu(), torch.tensor(g["back"]), **TOL)
+
+
+def test_layer_radial_embeddings_match_torch_layers(backend):
+    """get_layer_radial_emb evaluates every layer's radial MLP on the kernels; against the same weights in plain torch."""
+    import copy
+
+    from fairchem_b200 import weights
+    from fairchem_b200.backbone import build_model
+
+    sd = weights.random_init_state_dict(weights.UMA_S, 0)
+    bb, _ = build_model(weights.UMA_S, sd)
+    g = torch.Generator().manual_seed(2)
+    x_edge = torch.randn(300, 64 + 2 * 128, generator=g).cuda()
+    got = backend.get_layer_radial_emb(x_edge, bb)
+    assert len(got) == 4 and got[0].shape == (300, 1536)
+    for blk, out in zip(bb.blocks, got):
+        ref = copy.deepcopy(blk.edge_wise.so2_conv_1.rad_func.net).double()(x_edge.double())
+        torch.testing.assert_close(out, ref.float(), rtol=1e-4, atol=1e-5)
