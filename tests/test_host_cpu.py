@@ -202,3 +202,37 @@ def test_bench_reference_arm_prints_one_contract_line():
     env = dict(os.environ, RANK="1", WORLD_SIZE="2", LOCAL_RANK="1")
     res = subprocess.run(cmd, capture_output=True, text=True, timeout=300, cwd=root, env=env)
     assert res.returncode == 0 and res.stdout.strip() == ""
+
+
+def test_entry_points_reject_bad_arguments_before_touching_the_device():
+    """Every entry point validates its arguments first and returns a negative FCB200_E* code without launching
+    (so these calls are safe without a GPU): null pointers, unsupported shapes, misaligned pointers."""
+    from fairchem_b200 import _lib
+
+    lib = _lib.load()
+    EINVAL, EALIGN = -1, -2
+    p, q = 4096, 4096 + 4  # a 16-byte aligned and a misaligned stand-in address (never dereferenced)
+    f = lambda name: getattr(lib, name)  # noqa: E731
+
+    # null pointers
+    assert f("fcb200_gather_rotate_fwd")(None, p, p, p, None, p, 10, 10, 128, None) == EINVAL
+    assert f("fcb200_gemm_f16x2")(None, 128, p, p, 128, 1.0, None, None, p, 128, 10, 128, 128, None, None) == EINVAL
+    assert f("fcb200_node_gate_fwd")(p, None, p, 10, 128, 2, None) == EINVAL
+    # unsupported shapes: channels not a multiple of 128, lmax not 2 or 4, K not a multiple of 8, scale not positive
+    assert f("fcb200_gather_rotate_fwd")(p, p, p, p, None, p, 10, 10, 100, None) == EINVAL
+    assert f("fcb200_lx_gather_rotate_fwd")(p, p, p, p, None, p, 10, 10, 128, 3, None) == EINVAL
+    assert f("fcb200_lx_rms_norm_sh_fwd")(p, p, p, None, p, p, 1e-5, 10, 128, 5, None) == EINVAL
+    assert f("fcb200_lx_edge_geometry_fwd")(p, p, p, None, None, p, p, p, p, p, 6.0, 64, 0.0, 6.0, 2.0, 10, 10, 3, None) == EINVAL
+    assert f("fcb200_gemm_f16x2")(p, 128, p, p, 132, 1.0, None, None, p, 128, 10, 128, 132, None, None) == EINVAL
+    assert f("fcb200_gemm_f16x2_presplit")(p, p, 128, p, p, 128, 0.0, None, None, p, 128, 10, 128, 128, None, None) == EINVAL
+    assert f("fcb200_split_f16")(p, 64, p, p, 0.0, 4, 64, None) == EINVAL
+    assert f("fcb200_gemm_tf32")(p, 128, p, None, 128, None, p, 128, 10, 128, 128, 3, None, None) == EINVAL  # precision 3 needs w_lo
+    assert f("fcb200_node_gate_bwd")(p, p, p, p, p, 10, 100, 2, None) == EINVAL
+    # misaligned pointers
+    assert f("fcb200_gather_rotate_fwd")(q, p, p, p, None, p, 10, 10, 128, None) == EALIGN
+    assert f("fcb200_gemm_f16x2")(q, 128, p, p, 128, 1.0, None, None, p, 128, 10, 128, 128, None, None) == EALIGN
+    assert f("fcb200_so2_gate_fwd_h")(p, q, p, None, 10, 128, None) == EALIGN
+    assert f("fcb200_lx_so2_gate_bwd_h")(p, p, p, q, None, 10, 128, 4, None) == EALIGN
+    # empty problems are fine and launch nothing
+    assert f("fcb200_gather_rotate_fwd")(p, p, p, p, None, p, 0, 10, 128, None) == 0
+    assert f("fcb200_gemm_f16x2")(p, 128, p, p, 128, 1.0, None, None, p, 128, 0, 128, 128, None, None) == 0
