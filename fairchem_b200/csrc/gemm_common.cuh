@@ -108,4 +108,18 @@ inline int sm_count() {
     return count[dev];
 }
 
+// cudaFuncSetAttribute(MaxDynamicSharedMemorySize) applies to the current device only: remember per device
+// (one flag array per kernel, owned by the caller) whether it has been raised there.
+template <typename Kernel>
+inline int ensure_dynamic_smem(Kernel kernel, int bytes, bool (&done)[64]) {
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return static_cast<int>(cudaGetLastError());
+    const bool cached = dev >= 0 && dev < 64;
+    if (cached && done[dev]) return 0;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes) != cudaSuccess)
+        return static_cast<int>(cudaGetLastError());
+    if (cached) done[dev] = true;
+    return 0;
+}
+
 }  // namespace fcb200

@@ -310,12 +310,8 @@ static int make_map(CUtensorMap* map, const float* ptr, int64_t rows, int64_t co
 template <int P>
 static int launch_gemm(const CUtensorMap& ma, const CUtensorMap& mw, const CUtensorMap& mwlo, const CUtensorMap& mc,
                        const float* bias, int64_t m, int n, int k, int32_t* status, cudaStream_t s) {
-    static bool attr_set = false;
-    if (!attr_set) {
-        if (cudaFuncSetAttribute(gemm_tf32_kernel<P>, cudaFuncAttributeMaxDynamicSharedMemorySize, GemmCfg<P>::kSmemBytes) != cudaSuccess)
-            return static_cast<int>(cudaGetLastError());
-        attr_set = true;
-    }
+    static bool attr_done[64] = {};
+    if (const int rc = ensure_dynamic_smem(gemm_tf32_kernel<P>, GemmCfg<P>::kSmemBytes, attr_done)) return rc;
     const int tiles_n = (n + BN - 1) / BN;
     const int64_t tiles_m = (m + BM - 1) / BM;
     const int64_t num_tiles = tiles_m * tiles_n;

@@ -406,15 +406,10 @@ template <bool PRESPLIT>
 int launch_f16(const CUtensorMap& ma, const CUtensorMap& malo, const CUtensorMap& mh, const CUtensorMap& ml, const CUtensorMap& mc,
                const float* bias, const float* a_scale, float w_scale, int64_t m, int n, int k, int32_t* status, cudaStream_t s) {
     using C = f16::Cfg<PRESPLIT>;
-    static bool attr_set = false;
-    if (!attr_set) {
-        const cudaError_t err = PRESPLIT ? cudaFuncSetAttribute(f16::gemm_f16x2_presplit_kernel,
-                                                                cudaFuncAttributeMaxDynamicSharedMemorySize, C::kSmemBytes)
-                                         : cudaFuncSetAttribute(f16::gemm_f16x2_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                                                C::kSmemBytes);
-        if (err != cudaSuccess) return static_cast<int>(cudaGetLastError());
-        attr_set = true;
-    }
+    static bool attr_done[64] = {};
+    const int arc = PRESPLIT ? ensure_dynamic_smem(f16::gemm_f16x2_presplit_kernel, C::kSmemBytes, attr_done)
+                             : ensure_dynamic_smem(f16::gemm_f16x2_kernel, C::kSmemBytes, attr_done);
+    if (arc) return arc;
     const int tiles_n = (n + f16::BN - 1) / f16::BN;
     const int64_t tiles_m = (m + f16::BM - 1) / f16::BM;
     const int64_t num_tiles = tiles_m * tiles_n;

@@ -21,12 +21,13 @@ import types
 
 import torch
 
-REF_ROOT = os.environ.get("FAIRCHEM_REF_ROOT", "/root/reference")
-_REF_SRC = os.path.join(REF_ROOT, "src")
+# The checkout's location comes from the environment only (no default path): unset means "no reference here".
+REF_ROOT = os.environ.get("FAIRCHEM_REF_ROOT", "")
+_REF_SRC = os.path.join(REF_ROOT, "src") if REF_ROOT else ""
 
 
 def available() -> bool:
-    return os.path.isdir(os.path.join(_REF_SRC, "fairchem", "core", "models", "uma"))
+    return bool(_REF_SRC) and os.path.isdir(os.path.join(_REF_SRC, "fairchem", "core", "models", "uma"))
 
 
 class _Any:
@@ -70,7 +71,7 @@ def load():
     if _loaded is not None:
         return _loaded
     if not available():
-        raise RuntimeError(f"fairchem reference checkout not found under {REF_ROOT}")
+        raise RuntimeError("fairchem reference checkout not found: set FAIRCHEM_REF_ROOT to its root")
     if "omegaconf" not in sys.modules:
         _stub("omegaconf", DictConfig=type("DictConfig", (dict,), {}), ListConfig=type("ListConfig", (list,), {}),
               OmegaConf=_Any())
