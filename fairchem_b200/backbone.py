@@ -355,19 +355,29 @@ class HalfRangeError(RuntimeError):
     """A value left the half-precision range inside a precision-2 contraction; the step's results are invalid."""
 
 
-def check_gemm_status() -> None:
-    """Turn the contraction kernels' device status word into an exception (and clear it): 1 = a bounded wait expired
-    inside a kernel, 2 = an operand or output left the half-precision range (precision 2 only)."""
+def read_gemm_status() -> int:
+    """The contraction kernels' device status word, read and cleared: 0 = fine, 1 = a bounded wait expired inside a
+    kernel, 2 = an operand or output left the half-precision range (precision 2 only)."""
     if _GemmState.status is None:
-        return
+        return 0
     code = int(_GemmState.status.item())
+    if code:
+        _GemmState.status.zero_()
+    return code
+
+
+def raise_gemm_status(code: int) -> None:
     if code == 0:
         return
-    _GemmState.status.zero_()
     if code == 2:
         raise HalfRangeError("tcgen05 GEMM: an operand left the half-precision range; results are invalid "
                              "(use set_gemm_precision(3), or energy_forces(), which falls back by itself)")
     raise RuntimeError("tcgen05 GEMM: a bounded wait expired inside the kernel; results are invalid")
+
+
+def check_gemm_status() -> None:
+    """Turn the contraction kernels' device status word into an exception (and clear it)."""
+    raise_gemm_status(read_gemm_status())
 
 
 def _transposed(w: torch.Tensor) -> torch.Tensor:
@@ -697,7 +707,8 @@ class _EdgeBlockFn(torch.autograd.Function):
         gwig = torch.empty_like(wig)
         gwinv = torch.empty_like(winv)
         ggauss = torch.empty_like(gauss)
-        y_all, msg_all, rkeep = ctx.kept
+        # the kept buffers are released after their first use; a repeated backward recomputes (keep level 0)
+        y_all, msg_all, rkeep = ctx.kept or (None, None, None)
         ctx.kept = None
         rfn = ew.so2_conv_1.rad_func
         scale = _GemmState.a_scale  # the power of two the gradient operands of this block are written with
@@ -1100,7 +1111,9 @@ class MLP_EFS_HeadB200(nn.Module):
         self.energy_block = nn.Sequential(nn.Linear(c, h), nn.SiLU(), nn.Linear(h, h), nn.SiLU(), nn.Linear(h, 1))
         self.regress_forces, self.regress_stress = backbone.regress_forces, backbone.regress_stress
 
-    def forward(self, data, emb):
+    def forward(self, data, emb, check_status: bool = True):
+        """``check_status=False`` leaves the contraction status word unread: a graph-parallel caller must first agree
+        on it with its peers (a rank that raised alone would leave the others waiting in the next collective)."""
         with torch.enable_grad():
             eb = self.energy_block
             h = emb["node_embedding"][:, 0]
@@ -1118,7 +1131,8 @@ class MLP_EFS_HeadB200(nn.Module):
                 w = emb["virial"]["virial"]
                 volume = torch.det(data["cell"].double()).abs().view(-1, 1, 1)
                 out["stress"] = ((w + w.transpose(1, 2)) / 2 / volume).reshape(-1, 9)
-            check_gemm_status()
+            if check_status:
+                check_gemm_status()
         return out
 
 

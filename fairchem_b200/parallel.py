@@ -173,8 +173,19 @@ class PartitionedStepper:
         self.last_plan: Optional[GPPlan] = None
 
     def step(self, data):
+        """One energy+forces evaluation.  The contraction status word is agreed on by all ranks before anyone acts on
+        it: either every rank repeats the step with the TF32 split (half-range overflow on any rank) or every rank
+        raises (expired wait on any rank), so no rank is left waiting in a collective its peers never enter."""
+        from . import backbone as B
+
+        return run_agreed(lambda: self._step_once(data), self.group, B.read_gemm_status, B.raise_gemm_status,
+                          lambda: B._GemmState.precision, B.set_gemm_precision, self.device)
+
+    def _step_once(self, data):
         from .graph import radius_graph_pbc_b200
 
+        if data["pos"].grad is not None:
+            data["pos"].grad = None
         pos = data["pos"].detach()
         # every rank must see the same positions: rank 0's are authoritative (predict.py:828-833)
         dist.broadcast(pos, src=dist.get_global_rank(self.group, 0) if self.group is not None else 0, group=self.group)
@@ -190,7 +201,7 @@ class PartitionedStepper:
         self.last_plan = plan
         data["gp_plan"] = plan
         emb = self.bb(data)
-        out = self.head(data, emb)
+        out = self.head(data, emb, check_status=False)
         del data["gp_plan"]
         energy, forces = out["energy"], out["forces"]
         dist.all_reduce(energy, group=self.group)
@@ -199,3 +210,29 @@ class PartitionedStepper:
             dist.all_reduce(out["stress"], group=self.group)
             self.last_stress = out["stress"]
         return energy, forces
+
+
+def agree_on_status(code: int, group, device) -> int:
+    """The largest status code any rank of ``group`` holds (one small all-reduce)."""
+    t = torch.tensor([int(code)], dtype=torch.int32, device=device)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX, group=group)
+    return int(t.item())
+
+
+def run_agreed(step_once, group, read_status, raise_status, get_precision, set_precision, device):
+    """Run ``step_once`` on every rank, then act on the ranks' *common* status: 0 returns the result, 2 (half-range
+    overflow somewhere) repeats the step on all ranks with precision 3 and restores the mode, anything else raises on
+    all ranks.  The step's collectives all complete before the status is looked at."""
+    result = step_once()
+    code = agree_on_status(read_status(), group, device)
+    if code == 0:
+        return result
+    if code != 2 or get_precision() != 2:
+        raise_status(code)
+    set_precision(3)
+    try:
+        result = step_once()
+        raise_status(agree_on_status(read_status(), group, device))
+        return result
+    finally:
+        set_precision(2)

@@ -88,3 +88,50 @@ def test_halo_collect_and_plan_reproduce_the_single_process_result(world):
             e, g = result[rank]
             assert abs(e - e_ref.item()) < 1e-9 * abs(e_ref.item())
             assert np.max(np.abs(g - g_ref.numpy())) < 1e-9 * float(g_ref.abs().max())
+
+
+def _status_worker(rank, world, init_file, result, fault_code):
+    """Every rank runs the agreed-step helper with a fake step; only rank 1 holds a non-zero status after the first pass."""
+    dist.init_process_group("gloo", init_method=f"file://{init_file}", rank=rank, world_size=world)
+    try:
+        state = {"precision": 2, "calls": 0, "pending": fault_code if rank == 1 else 0}
+
+        def step_once():
+            state["calls"] += 1
+            t = torch.ones(1)
+            dist.all_reduce(t)  # the step's own collective: every rank must reach it on every pass
+            return float(t.item()), state["precision"]
+
+        def read_status():
+            code, state["pending"] = state["pending"], 0
+            return code
+
+        def raise_status(code):
+            if code:
+                raise RuntimeError(f"status {code}")
+
+        try:
+            value = parallel.run_agreed(step_once, None, read_status, raise_status, lambda: state["precision"],
+                                        lambda p: state.__setitem__("precision", p), torch.device("cpu"))
+            result[rank] = ("ok", value, state["calls"], state["precision"])
+        except RuntimeError as err:
+            result[rank] = ("raised", str(err), state["calls"], state["precision"])
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("fault_code,expect", [(0, "ok"), (2, "retry"), (1, "raised")])
+def test_status_of_one_rank_is_acted_on_by_all_ranks(fault_code, expect):
+    world = 2
+    with tempfile.TemporaryDirectory() as tmp:
+        result = mp.Manager().dict()
+        mp.spawn(_status_worker, args=(world, os.path.join(tmp, "pg"), result, fault_code), nprocs=world, join=True)
+        for rank in range(world):
+            kind, value, calls, precision = result[rank]
+            assert precision == 2                       # the mode is restored on every path
+            if expect == "ok":
+                assert kind == "ok" and calls == 1 and value == (2.0, 2)
+            elif expect == "retry":                     # both ranks repeated the step with the TF32 split
+                assert kind == "ok" and calls == 2 and value == (2.0, 3)
+            else:                                       # both ranks raise, none is left in a collective
+                assert kind == "raised" and calls == 1 and "status 1" in value
