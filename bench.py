@@ -183,8 +183,6 @@ def run_b200(args):
         one_step()
     barrier()
     torch.cuda.reset_peak_memory_stats()
-    prof = ops.LaunchProfiler(timed=True)
-    ops.set_profiler(prof)
     sampler = ClockSampler(local)
     if rank == 0:
         sampler.start()
@@ -197,9 +195,18 @@ def run_b200(args):
     barrier()
     ms = t0.elapsed_time(t1)
     clocks = sampler.stop() if rank == 0 else None
+    # second pass, not part of `value`: the same steps with two CUDA events around every launch of this library's
+    # kernels, for the per-kernel table and the roofline of the dominant kernel
+    prof_steps = max(1, min(args.steps, 3))
+    prof = ops.LaunchProfiler(timed=True)
+    ops.set_profiler(prof)
+    barrier()
+    for _ in range(prof_steps):
+        one_step()
+    barrier()
     summary = prof.summary()
     ops.set_profiler(None)
-    launches = prof.launches
+    launches = prof.launches // prof_steps * args.steps  # launches inside the timed region (same steps, counted here)
     if world > 1:
         t = torch.tensor([ms], device=dev, dtype=torch.float64)
         torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
@@ -287,11 +294,11 @@ def run_b200(args):
     for k, v in summary.items():
         if not v["ms"]:
             continue
-        per_kernel[k] = {"ms_per_step": round(v["ms"] / args.steps, 3), "launches_per_step": v["launches"] // args.steps,
+        per_kernel[k] = {"ms_per_step": round(v["ms"] / prof_steps, 3), "launches_per_step": v["launches"] // prof_steps,
                          "GBps": round(v["bytes"] / (v["ms"] * 1e-3) / 1e9, 1)}
         if v["flops"]:
             per_kernel[k]["TFLOPps"] = round(v["flops"] / (v["ms"] * 1e-3) / 1e12, 2)
-    cpu = cpu_baseline(args, quiet=True) if world == 1 and not args.skip_cpu else None
+    cpu = cpu_baseline(args, reps=3, warmup=1) if world == 1 and not args.skip_cpu else None
     line = {
         "metric": "atom_steps_per_s", "value": n_atoms * args.steps / (ms * 1e-3), "unit": "atom-steps/s",
         "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": ms / args.steps,
@@ -299,7 +306,11 @@ def run_b200(args):
         "config": {"workload": args.workload, "atoms": n_atoms, "edges": edges, "model": model_name,
                    "cutoff": 6.0, "max_neighbors": 30, "gemm_precision": {3: "tf32x3", 2: "f16x3", 1: "tf32", 0: "cublas_fp32"}[args.precision],
                    "edge_chunk": args.chunk, "l2": "inputs larger than L2 (node and edge arrays of 0.4-2 GB per pass)",
-                   "parallelism": f"gp{world}"},
+                   "parallelism": f"gp{world}", "energy": float(energy[0]),
+                   "peak_mem_gb": round(torch.cuda.max_memory_allocated() / 1e9, 2),
+                   "arithmetic": "float32 results; contractions as 3 half-precision tensor-core products per float32 "
+                                 "product (22-bit operands, float32 accumulation), not IEEE float32"
+                                 if args.precision == 2 else "float32"},
         "clocks": clocks,
         "e2e": {"value": n_atoms * args.steps / (e2e_ms * 1e-3), "unit": "atom-steps/s", "h2d_bytes_per_step": h2d,
                 "d2h_bytes_per_step": d2h},
@@ -334,8 +345,27 @@ def _cpu_sample(args):
     return synthetic.WORKLOADS[args.workload](args.seed), f"full {args.workload}"
 
 
-def cpu_baseline(args, quiet=False):
-    """The CPU oracle on a bounded sample of the workload: a box of the same density with fewer atoms."""
+def _reference_modules(cfg, sd):
+    """The reference's own backbone + head on the CPU when a checkout is present (its location comes from the
+    environment, see oracle/ref_shim.py); None otherwise."""
+    try:
+        from oracle import ref_shim
+        if not ref_shim.available():
+            return None
+        overrides = {k: cfg[k] for k in cfg if k in ("lmax", "mmax", "num_layers", "sphere_channels", "hidden_channels")}
+        bb, head = ref_shim.build_reference_model(0, **overrides)
+        bsd, hsd = weights.split_head(sd)
+        bb.load_state_dict(bsd, strict=False)
+        head.energy_block.load_state_dict(hsd)
+        return lambda sample: ref_shim.run_reference(bb, head, sample)
+    except Exception:
+        return None
+
+
+def cpu_baseline(args, reps: int = 3, warmup: int = 1):
+    """The reference's CPU path on a bounded sample of the workload (a box of the same density with fewer atoms):
+    the reference's own modules when a checkout is importable (kind "reference"), else the CPU oracle, its pinned
+    restatement (kind "port").  ``warmup`` untimed passes, then exactly ``reps`` timed ones."""
     from oracle import escn_md_oracle as oracle_model
     from oracle import radius_graph_oracle as oracle_graph
 
@@ -344,30 +374,39 @@ def cpu_baseline(args, quiet=False):
     sample, what = _cpu_sample(args)
     cfg = MODELS[args.model][0]
     sd = weights.random_init_state_dict(cfg, args.seed)
-    times = []
-    reps = max(1, min(args.steps, 3))
-    for i in range(reps + 1):
-        t = time.perf_counter()
+    ref_step = _reference_modules(cfg, sd)
+
+    def port_step(sample):
         ei, co, _, _ = oracle_graph.radius_graph(sample.pos.numpy(), sample.cell.numpy(), sample.pbc.numpy(),
                                                  sample.natoms.numpy(), 6.0, 30)
         oracle_model.energy_and_forces(sd, cfg, sample, torch.from_numpy(ei), torch.from_numpy(co))
-        if i:  # the first pass warms the allocator and thread pool
+
+    step = ref_step or port_step
+    times = []
+    for i in range(warmup + reps):
+        t = time.perf_counter()
+        step(sample)
+        if i >= warmup:  # the first passes warm the allocator and thread pool
             times.append(time.perf_counter() - t)
-    sec = statistics.median(times)
     n = int(sample["pos"].shape[0])
-    return {"value": n / sec, "unit": "atom-steps/s", "cores": threads, "kind": "port", "sample": what,
-            "s_per_step": sec}
+    total = sum(times)
+    return {"value": n * len(times) / total, "unit": "atom-steps/s", "cores": threads,
+            "kind": "reference" if ref_step else "port", "sample": what, "s_per_step": total / len(times),
+            "s_per_step_min": min(times), "s_per_step_median": statistics.median(times), "timed_steps": len(times),
+            "warmup_steps": warmup}
 
 
 def run_reference(args):
+    """Reference arm: exactly ``--steps`` timed CPU steps after ``--warmup`` untimed ones; ``value`` is the mean rate over
+    the timed steps (steps x atoms / total time), min and median are reported beside it."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    cpu = cpu_baseline(args)
+    cpu = cpu_baseline(args, reps=max(1, args.steps), warmup=max(0, args.warmup))
     n = int(_cpu_sample(args)[0]["pos"].shape[0])
     line = {
         "impl": "reference", "metric": "atom_steps_per_s", "value": cpu["value"], "unit": "atom-steps/s",
-        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": args.steps, "warmup": args.warmup,
+        "n_gpus": int(os.environ.get("WORLD_SIZE", "1")), "steps": cpu["timed_steps"], "warmup": cpu["warmup_steps"],
         "ms_per_step": cpu["s_per_step"] * 1e3, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "f32", "data": "synthetic",
         "config": {"workload": args.workload, "sample_atoms": n, "model": MODELS[args.model][1]},
