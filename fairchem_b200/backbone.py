@@ -337,6 +337,7 @@ class _GemmState:
     split = {}             # same key -> (weight ref, TF32 high part, TF32 low part)
     split16 = {}           # same key -> (weight ref, half high part, half low part, scale)
     a_scale = None         # precision 2: one-element device tensor, the power of two A operands are scaled by (None = 1)
+    fused_conv = True      # precision 2: one launch per SO(2) convolution with the gate in the epilogue
 
 
 def set_gemm_precision(p: int) -> None:
@@ -627,6 +628,130 @@ def _conv_backward(conv: "SO2Convolution", gy):
     return gx
 
 
+# ---- one launch per convolution, gate in the epilogue (precision 2) ----------------------------------
+
+
+def _row_degrees(lmax: int) -> list:
+    """Degree l of every M-major edge row: m=0 (l=0..lmax) | m=+1 (l=1..) | m=-1 | m=+2 (l=2..) | m=-2."""
+    return list(range(lmax + 1)) + 2 * list(range(1, lmax + 1)) + 2 * list(range(2, lmax + 1))
+
+
+def _fused_tiles(shapes, transposed: bool, describe) -> list:
+    """Flat tile list for ops.so2_conv_fused_: the m-blocks ``shapes`` = [(n_i, k_i)] side by side, one tile per 128
+    output columns in column order.  ``describe(c)`` -> (out_col, mode, y_col, gate_col, flags) for output column c."""
+    tiles, a_off, out_off = [], 0, 0
+    for wi, (n, k) in enumerate(shapes):
+        n_out, k_in = (k, n) if transposed else (n, k)
+        for r0 in range(0, n_out, 128):
+            out_col, mode, y_col, gate_col, flags = describe(out_off + r0)
+            tiles += [a_off, k_in, wi, r0, out_col, mode, y_col, gate_col, flags]
+        a_off += k_in
+        out_off += n_out
+    return tiles
+
+
+class _FusedConvPlan:
+    """Tile lists and split weights of one Edgewise module's two convolutions for the fused launches."""
+
+    def __init__(self, ew: "Edgewise"):
+        h, lmax = ew.hidden, ew.lmax
+        deg = _row_degrees(lmax)
+        gates = lmax * h
+        w1, w2 = _conv_weights(ew.so2_conv_1), _conv_weights(ew.so2_conv_2)
+        s1, s2 = [tuple(w.shape) for w in w1], [tuple(w.shape) for w in w2]
+        self.gates, self.y_width = gates, gates + len(deg) * h
+        self.versions = _conv_versions(ew)
+
+        def fwd1(keep):
+            def describe(c):
+                if c < gates:
+                    return c, ops.CONV_GATE_RAW, 0, 0, 0
+                r, j = divmod(c - gates, h)
+                flags = ops.CONV_KEEP if keep else 0
+                if r == 0:
+                    return c - gates, ops.CONV_SILU, c, 0, flags
+                return c - gates, ops.CONV_GATED, c, (deg[r] - 1) * h + j, flags
+            return _fused_tiles(s1, False, describe)
+
+        rows_of = {l: [r for r, d in enumerate(deg) if d == l] for l in range(1, lmax + 1)}
+
+        def bwd2(c):
+            r, j = divmod(c, h)
+            if r == 0:
+                return gates + c, ops.CONV_SILU_BWD, gates + c, 0, 0
+            rows = rows_of[deg[r]]
+            flags = (ops.CONV_FIRST if r == rows[0] else 0) | (ops.CONV_LAST if r == rows[-1] else 0)
+            return gates + c, ops.CONV_GATED_BWD, gates + c, (deg[r] - 1) * h + j, flags
+
+        plain = lambda c: (c, ops.CONV_PLAIN, 0, 0, 0)  # noqa: E731
+        self.fwd1 = {False: fwd1(False), True: fwd1(True)}
+        self.fwd2 = _fused_tiles(s2, False, plain)
+        self.bwd2 = _fused_tiles(s2, True, bwd2)
+        self.bwd1 = _fused_tiles(s1, True, plain)
+        self.ok = max(len(t) // 9 for t in (self.fwd1[True], self.fwd2, self.bwd2, self.bwd1)) <= ops.CONV_MAX_TILES and h % 128 == 0
+        split = lambda ws: tuple(zip(*[_split16(w) for w in ws]))  # noqa: E731
+        self.w1, self.w2 = split(w1), split(w2)
+        self.w1t, self.w2t = split([_transposed(w) for w in w1]), split([_transposed(w) for w in w2])
+        self.bias1, self.bias2 = ew.so2_conv_1.fc_m0.bias.detach(), ew.so2_conv_2.fc_m0.bias.detach()
+
+
+def _conv_versions(ew: "Edgewise") -> tuple:
+    ws = [p for conv in (ew.so2_conv_1, ew.so2_conv_2)
+          for p in (conv.fc_m0.weight, conv.fc_m0.bias, conv.so2_m_conv[0].fc.weight, conv.so2_m_conv[1].fc.weight)]
+    return tuple((w.data_ptr(), w._version) for w in ws)
+
+
+def _fused_plan(ew: "Edgewise") -> "_FusedConvPlan":
+    plan = getattr(ew, "_fused_plan", None)
+    if plan is None or plan.versions != _conv_versions(ew):
+        plan = _FusedConvPlan(ew)
+        ew._fused_plan = plan
+    return plan
+
+
+def _use_fused(ew: "Edgewise") -> bool:
+    return _presplit() and _GemmState.fused_conv and _fused_plan(ew).ok
+
+
+def _fused_conv1_gate(ew, m, y_keep):
+    """conv 1 + gate in one launch: planes m [Ec, NM*2C] -> planes a [Ec, NM*H].  ``y_keep`` [Ec, gates + NM*H] receives
+    the raw conv-1 output when given; otherwise only the gate scalars pass through a narrow scratch."""
+    p = _fused_plan(ew)
+    ec, dev = m[0].shape[0], m[0].device
+    y = y_keep if y_keep is not None else torch.empty(ec, p.gates, dtype=torch.float32, device=dev)
+    a = _new_operand(ec, p.y_width - p.gates, dev)
+    ops.so2_conv_fused_.raw(m[0], m[1], list(p.w1[0]), list(p.w1[1]), list(p.w1[2]), p.bias1, p.fwd1[y_keep is not None], y,
+                            a[0], a[1], None, None, None, _status(dev))
+    return a
+
+
+def _fused_conv2(ew, a, out):
+    p = _fused_plan(ew)
+    ops.so2_conv_fused_.raw(a[0], a[1], list(p.w2[0]), list(p.w2[1]), list(p.w2[2]), p.bias2, p.fwd2, out, None, None, None,
+                            None, None, _status(out.device))
+    return out
+
+
+def _fused_conv2_gate_backward(ew, grad_msg, y, scale):
+    """Gradient of the conv-1 output (planes, written with ``scale``) from the message-gradient planes and the kept y."""
+    p = _fused_plan(ew)
+    ec, dev = y.shape[0], y.device
+    gy = _new_operand(ec, p.y_width, dev)
+    gacc = torch.empty(ec, p.gates, dtype=torch.float32, device=dev)
+    ops.so2_conv_fused_.raw(grad_msg[0], grad_msg[1], list(p.w2t[0]), list(p.w2t[1]), list(p.w2t[2]), None, p.bwd2, y,
+                            gy[0], gy[1], gacc, scale, scale, _status(dev))
+    return gy
+
+
+def _fused_conv1_backward(ew, gy, scale):
+    p = _fused_plan(ew)
+    ec, dev = gy[0].shape[0], gy[0].device
+    gm = torch.empty(ec, sum(w.shape[1] for w in p.w1[0]), dtype=torch.float32, device=dev)
+    ops.so2_conv_fused_.raw(gy[0], gy[1], list(p.w1t[0]), list(p.w1t[1]), list(p.w1t[2]), None, p.bwd1, gm, None, None, None,
+                            scale, None, _status(dev))
+    return gm
+
+
 def _gather_rotate(x, g, sl, wig, rad, nm: int):
     ec, c = sl.stop - sl.start, x.shape[2]
     m = _new_operand(ec, nm * 2 * c, x.device)
@@ -674,6 +799,7 @@ class _EdgeBlockFn(torch.autograd.Function):
         rkeep = None
         if keep_level >= 1:  # level 3 also keeps the radial weights
             rkeep = _RadialKeep(g.num_edges, rfn.net[0].weight.shape[0], rfn.net[6].weight.shape[0], keep_level >= 3, x.device)
+        fused = _use_fused(ew)
         with torch.no_grad():
             for ch in ectx.chunks:
                 sl = slice(ch.e0, ch.e1)
@@ -681,10 +807,16 @@ class _EdgeBlockFn(torch.autograd.Function):
                 rad, _ = _radial_forward(rfn, tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb, rkeep, sl)
                 m = _gather_rotate(x, g, sl, wig, rad, nm)
                 del rad
-                y = _conv_forward(ew.so2_conv_1, m, out=None if y_all is None else y_all[sl])
-                del m
-                msg = _conv_forward(ew.so2_conv_2, _gate(y, h, nm),
-                                    out=None if msg_all is None else msg_all[sl].view(ec, nm * c)).view(ec, nm, c)
+                msg_out = torch.empty(ec, nm * c, dtype=x.dtype, device=x.device) if msg_all is None else msg_all[sl].view(ec, nm * c)
+                if fused:
+                    a = _fused_conv1_gate(ew, m, None if y_all is None else y_all[sl])
+                    del m
+                    msg = _fused_conv2(ew, a, msg_out).view(ec, nm, c)
+                    del a
+                else:
+                    y = _conv_forward(ew.so2_conv_1, m, out=None if y_all is None else y_all[sl])
+                    del m
+                    msg = _conv_forward(ew.so2_conv_2, _gate(y, h, nm), out=msg_out).view(ec, nm, c)
                 ops.rotate_back_reduce_fwd_.raw(msg, winv[sl], ch.row_ptr, out[ch.n0:ch.n1])
         ctx.save_for_backward(x, wig, winv, gauss)
         ctx.ew, ctx.tables, ctx.ectx, ctx.nb, ctx.kept = ew, tables, ectx, nb, (y_all, msg_all, rkeep)
@@ -712,6 +844,7 @@ class _EdgeBlockFn(torch.autograd.Function):
         ctx.kept = None
         rfn = ew.so2_conv_1.rad_func
         scale = _GemmState.a_scale  # the power of two the gradient operands of this block are written with
+        fused = _use_fused(ew)
         for ch in ectx.chunks:
             sl = slice(ch.e0, ch.e1)
             ec = ch.e1 - ch.e0
@@ -719,6 +852,16 @@ class _EdgeBlockFn(torch.autograd.Function):
                                           from_kept=rkeep is not None)
             y = None if y_all is None else y_all[sl]
             msg = None if msg_all is None else msg_all[sl]
+            if fused and (y is None or msg is None):
+                a = None
+                if y is None:
+                    y = torch.empty(ec, (ew.lmax + nm) * h, dtype=x.dtype, device=x.device)
+                    a = _fused_conv1_gate(ew, _gather_rotate(x, g, sl, wig, rad_d, nm), y)
+                if msg is None:
+                    if a is None:
+                        a = _gate(y, h, nm)
+                    msg = _fused_conv2(ew, a, torch.empty(ec, nm * c, dtype=x.dtype, device=x.device)).view(ec, nm, c)
+                del a
             if y is None:
                 y = _conv_forward(ew.so2_conv_1, _gather_rotate(x, g, sl, wig, rad_d, nm))
             if msg is None:
@@ -730,15 +873,20 @@ class _EdgeBlockFn(torch.autograd.Function):
             else:
                 ops.rotate_back_bwd_.raw(grad_out, msg, winv[sl], g.tgt[sl], grad_msg.view(ec, nm, c), gwinv[sl])
             del msg
-            ga = _conv_backward(ew.so2_conv_2, grad_msg)
-            del grad_msg
-            gy = _new_operand(ec, y.shape[1], x.device)
-            if isinstance(gy, tuple):
-                ops.so2_gate_bwd_h_.raw(ga, y, gy[0], gy[1], scale, h)
+            if fused:
+                gy = _fused_conv2_gate_backward(ew, grad_msg, y, scale)
+                del grad_msg, y
+                gm = _fused_conv1_backward(ew, gy, scale)
             else:
-                ops.so2_gate_bwd_.raw(ga, y, gy, h)
-            del ga, y
-            gm = _conv_backward(ew.so2_conv_1, gy)
+                ga = _conv_backward(ew.so2_conv_2, grad_msg)
+                del grad_msg
+                gy = _new_operand(ec, y.shape[1], x.device)
+                if isinstance(gy, tuple):
+                    ops.so2_gate_bwd_h_.raw(ga, y, gy[0], gy[1], scale, h)
+                else:
+                    ops.so2_gate_bwd_.raw(ga, y, gy, h)
+                del ga, y
+                gm = _conv_backward(ew.so2_conv_1, gy)
             del gy
             g_src = torch.empty(ec, nl, c, dtype=x.dtype, device=x.device)
             g_tgt = torch.empty(ec, nl, c, dtype=x.dtype, device=x.device)

@@ -20,8 +20,8 @@ LIB_DIR = os.path.join(PKG, "lib")
 LIB_PATH = os.path.join(LIB_DIR, "libfairchem_b200.so")
 OBJ_DIR = os.path.join(HERE, "_obj")
 
-SOURCES = ["edge_block.cu", "edge_block_lx.cu", "edge_geometry.cu", "radius_graph.cu", "so2_gemm.cu", "so2_gemm_f16.cu", "radial_act.cu", "node_ops.cu"]
-HEADERS = ["common.cuh", "shape_lx.cuh", "gemm_common.cuh", os.path.join("..", "..", "include", "fairchem_b200.h")]
+SOURCES = ["edge_block.cu", "edge_block_lx.cu", "edge_geometry.cu", "radius_graph.cu", "so2_gemm.cu", "so2_gemm_f16.cu", "so2_conv_fused.cu", "radial_act.cu", "node_ops.cu"]
+HEADERS = ["common.cuh", "shape_lx.cuh", "gemm_common.cuh", "gemm_f16_common.cuh", os.path.join("..", "..", "include", "fairchem_b200.h")]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",

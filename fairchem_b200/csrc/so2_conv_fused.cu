@@ -1,0 +1,511 @@
+// One launch per SO(2) convolution: a persistent CTA owns a 128-edge row tile and walks the output column
+// tiles of all m-blocks of the convolution in turn (each with its own slice of the input columns, weight
+// matrix and K extent), with the gate activation -- or its derivative -- applied in the epilogue, so that
+// the convolution output never makes a round trip through memory as float32 just to be gated:
+//
+//   conv 1 forward : A = rotated+radial-scaled rows (hi, lo planes)  ->  tiles [gate scalars | rows]
+//                    gate tiles  : raw float32 into y (a later tile of the same thread reads them back)
+//                    row tiles   : row 0 -> v * sigmoid(v); row (l, m) -> v * sigmoid(gate[l-1]); written as the
+//                                  (hi, lo) half planes conv 2 reads; raw y rows are stored only when the backward
+//                                  pass will want them
+//   conv 2 forward : plain float32 output (messages)
+//   conv 2 backward: A = message gradient planes -> tiles = rows of the gate output's gradient; the epilogue
+//                    reads the kept y, writes the gradient of the conv-1 output as (hi, lo) planes and accumulates
+//                    the gate-scalar gradients over the rows of a degree in a float32 scratch row that the same
+//                    thread revisits (first tile of a degree writes, last tile finalises into the planes)
+//   conv 1 backward: plain float32 output (gradient of the rotated rows)
+//
+// Replaces SO2_Convolution.forward + GateActivation.forward of the reference
+// (src/fairchem/core/models/uma/nn/so2_layers.py:600-647, src/fairchem/core/models/uma/nn/activation.py:146-165)
+// and their autograd twins.  Arithmetic, tile shape, operand format, accumulators and the bounded waits are those
+// of gemm_f16x2_presplit_kernel; what differs is the tile schedule (row tile outermost, so the gate scalars and
+// all rows of an edge pass through one thread), eight epilogue warps (two per TMEM lane quarter, each taking
+// half of the tile's columns) and the epilogue modes.
+#include "gemm_f16_common.cuh"
+
+namespace fcb200 {
+namespace fused {
+
+using namespace f16;
+
+enum Mode : int32_t {
+    kPlain = 0,     // float32 tile -> y[:, out_col ...] through TMA
+    kGateRaw = 1,   // float32 tile -> y[:, out_col ...] with plain stores (read back by this thread in kGated tiles)
+    kSilu = 2,      // planes[:, out_col ...] = split(v * sigmoid(v));                       keep: y[:, y_col ...] = v
+    kGated = 3,     // planes[:, out_col ...] = split(v * sigmoid(y[:, gate_col ...]));      keep: y[:, y_col ...] = v
+    kSiluBwd = 4,   // planes[:, out_col ...] = split(v * d/dy silu(y[:, y_col ...]))
+    kGatedBwd = 5,  // planes[:, out_col ...] = split(v * sigmoid(gate)); gate gradient accumulated over rows
+};
+enum Flags : int32_t { kFirst = 1, kLast = 2, kKeep = 4 };
+
+struct Tile {
+    int32_t a_col;     // first input column of this tile's K range
+    int32_t k;         // K extent (multiple of 32)
+    int32_t w;         // weight matrix 0..2
+    int32_t w_row;     // first output row of the weight matrix (multiple of 128)
+    int32_t out_col;   // where the result goes (column of y for float32 modes, of the planes for split modes)
+    int32_t mode;
+    int32_t y_col;     // column of y holding this row's raw value (kSilu/kGated keep, kSiluBwd/kGatedBwd read)
+    int32_t gate_col;  // column of y (and of the gradient planes / scratch) of the gate scalars of this row's degree
+    int32_t flags;
+    int32_t pad;
+};
+constexpr int kMaxTiles = 40;  // lmax 4: 19 rows x 2C = 38 column tiles in the conv-1 backward
+struct Plan {
+    int32_t ntiles;
+    int32_t pad[3];
+    Tile t[kMaxTiles];
+};
+
+constexpr int kStages = 5;
+constexpr int kStageBytes = 4 * BM * BK * 2;           // A_hi | A_lo | W_hi | W_lo, 8 KiB each
+constexpr int kHalfTile = BM * BK * 2;
+constexpr int kEpiWarps = 8;
+constexpr int kEpiWarpBytes = 4096 + 2048 + 2048;      // float32 32x32 | hi 32x32 | lo 32x32 staging per warp
+constexpr int kThreads = 128 + 32 * kEpiWarps;         // warp 0 TMA, warp 1 MMA, warps 2-3 idle, warps 4-11 epilogue
+constexpr int kAccCols = 2 * BN, kTmemCols = 2 * kAccCols;
+constexpr int kSmemBytes = kStages * kStageBytes + kEpiWarps * kEpiWarpBytes + 1024 + 256;
+
+struct Params {
+    const float* bias[3];
+    float w_scale[3];
+    float* y;          // raw conv-1 output / float32 output
+    int64_t ldy;
+    float* gacc;       // [M, ldg] float32 scratch for the gate-gradient sums (kGatedBwd only)
+    int64_t ldg;
+    const float* a_scale;  // power of two the A planes were written with (null = 1)
+    const float* o_scale;  // power of two the output planes are written with (null = 1)
+    int64_t m_total;
+    int32_t* status;
+};
+
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
+
+// pack (a, b) * already-applied scale into hi and lo half pairs; track the largest magnitude
+__device__ __forceinline__ void pack2(float a, float b, uint32_t& hi, uint32_t& lo, float& amax) {
+    amax = fmaxf(amax, fmaxf(fabsf(a), fabsf(b)));
+    const __half2 h = __floats2half2_rn(a, b);
+    const float2 hf = __half22float2(h);
+    const __half2 l = __floats2half2_rn((a - hf.x) * kLoScale, (b - hf.y) * kLoScale);
+    hi = *reinterpret_cast<const uint32_t*>(&h);
+    lo = *reinterpret_cast<const uint32_t*>(&l);
+}
+
+// 8 consecutive values -> one 16-byte unit of the hi staging tile and one of the lo staging tile.
+// Row `lane` of a 32-row x 64-byte tile with the 64-byte swizzle: unit index XOR ((row >> 1) & 3).
+__device__ __forceinline__ void stage_split8(uint32_t hi_base, uint32_t lo_base, int lane, int unit, const float (&v)[8], float& amax) {
+    uint32_t h[4], l[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) pack2(v[2 * i], v[2 * i + 1], h[i], l[i], amax);
+    const uint32_t off = (uint32_t)(lane * 64 + ((unit ^ ((lane >> 1) & 3)) * 16));
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(hi_base + off), "r"(h[0]), "r"(h[1]), "r"(h[2]), "r"(h[3]) : "memory");
+    asm volatile("st.shared.v4.b32 [%0], {%1,%2,%3,%4};" ::"r"(lo_base + off), "r"(l[0]), "r"(l[1]), "r"(l[2]), "r"(l[3]) : "memory");
+}
+
+// 4 consecutive float32 -> 16-byte chunk `v4` of row `lane` of a 32-row x 128-byte tile with the 128-byte swizzle
+__device__ __forceinline__ void stage_f32x4(uint32_t base, int lane, int v4, float a, float b, float c, float d) {
+    const uint32_t dst = base + (uint32_t)(lane * 128 + ((v4 ^ (lane & 7)) * 16));
+    asm volatile("st.shared.v4.f32 [%0], {%1,%2,%3,%4};" ::"r"(dst), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+
+
+__device__ __forceinline__ void ld8(const float* p, bool valid, float (&o)[8]) {
+    if (valid) {
+        const float4 a = ld4(p), b = ld4(p + 4);
+        o[0] = a.x, o[1] = a.y, o[2] = a.z, o[3] = a.w, o[4] = b.x, o[5] = b.y, o[6] = b.z, o[7] = b.w;
+    } else {
+#pragma unroll
+        for (int i = 0; i < 8; ++i) o[i] = 0.f;
+    }
+}
+
+// Epilogue warps 4..11: warp w reads TMEM lanes [32 (w % 4), +32) -- one accumulator row per thread -- and takes
+// the 64 columns [64 h, 64 h + 64) of every tile, h = (w - 4) / 4, in two chunks of 32.
+__device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtensorMap& map_ohi, const CUtensorMap& map_olo,
+                                         const Plan& plan, const Params& prm, int64_t tiles_m, uint32_t tmem_base,
+                                         uint32_t epi_base, uint32_t tfull0, uint32_t tempty0, volatile int* abort_flag,
+                                         volatile int* range_flag) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int q = warp & 3;
+    const int half = (warp - 4) >> 2;
+    const uint32_t st_f32 = epi_base + (uint32_t)((warp - 4) * kEpiWarpBytes), st_hi = st_f32 + 4096u, st_lo = st_hi + 2048u;
+    const float a_scale = prm.a_scale ? *prm.a_scale : 1.0f;
+    const float o_scale = prm.o_scale ? *prm.o_scale : 1.0f;
+    const int ntiles = plan.ntiles;
+    float amax = 0.f;
+    int64_t tcount = 0;
+    bool ok = true;
+    for (int64_t mt = blockIdx.x; mt < tiles_m && ok; mt += gridDim.x) {
+        const int64_t row0 = mt * BM + q * 32;
+        const int64_t row = row0 + lane;
+        const bool valid = row < prm.m_total;
+        float* const yrow = prm.y + row * prm.ldy;
+        for (int ti = 0; ti < ntiles; ++ti, ++tcount) {
+            const Tile& t = plan.t[ti];
+            const int buf = (int)(tcount & 1);
+            const uint32_t use = (uint32_t)((tcount >> 1) & 1);
+            ok = mbar_wait(tfull0 + 8u * buf, use, abort_flag);
+            ok = __all_sync(kFull, ok);
+            if (!ok) break;
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const float out_scale = 1.0f / (a_scale * prm.w_scale[t.w]);
+            const float corr_scale = out_scale / kLoScale;
+            const float* bias = prm.bias[t.w];
+            const uint32_t acc = tmem_base + (uint32_t)(buf * kAccCols) + ((uint32_t)(q * 32) << 16);
+            const int mode = t.mode;
+#pragma unroll 1
+            for (int c2 = 0; c2 < 2; ++c2) {
+                const int col = (half * 2 + c2) * 32;  // within the tile
+                float v[32];
+                {
+                    uint32_t r[32], c[32];
+                    FCB_TMEM_LD32(r, acc + (uint32_t)col);
+                    FCB_TMEM_LD32(c, acc + (uint32_t)(BN + col));
+                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    uint32_t bad = 0;
+#pragma unroll
+                    for (int i = 0; i < 32; ++i) {
+                        v[i] = fmaf(__uint_as_float(c[i]), corr_scale, __uint_as_float(r[i]) * out_scale);
+                        bad |= (uint32_t)((__float_as_uint(v[i]) & 0x7f800000u) == 0x7f800000u);  // inf or NaN: an overflowed half upstream
+                    }
+                    if (bad && valid) *range_flag = 1;
+                }
+                if (row0 >= prm.m_total) continue;  // this warp's 32 rows lie entirely below the matrix
+                if (bias) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) {
+                        const float4 b = ld4(bias + t.w_row + col + 4 * i);
+                        v[4 * i] += b.x, v[4 * i + 1] += b.y, v[4 * i + 2] += b.z, v[4 * i + 3] += b.w;
+                    }
+                }
+                if (mode == kGateRaw) {
+                    if (valid) {
+#pragma unroll
+                        for (int i = 0; i < 8; ++i)
+                            st4(yrow + t.out_col + col + 4 * i, make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
+                    }
+                    continue;
+                }
+                // the stores issued for the previous chunk read the staging tiles: let them finish before overwriting
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                __syncwarp();
+                const bool keep = (t.flags & kKeep) != 0;
+                if (mode == kPlain || ((mode == kSilu || mode == kGated) && keep)) {
+#pragma unroll
+                    for (int i = 0; i < 8; ++i) stage_f32x4(st_f32, lane, i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+                }
+                bool fin = false;  // kGatedBwd, last row of a degree: gate gradient staged in the float32 area as two planes
+                if (mode != kPlain) {
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) {
+                        float o[8];
+                        if (mode == kSilu) {
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) o[i] = v[8 * u + i] * sigmoid_f(v[8 * u + i]) * o_scale;
+                        } else if (mode == kGated) {
+                            float g[8];
+                            ld8(yrow + t.gate_col + col + 8 * u, valid, g);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) o[i] = v[8 * u + i] * sigmoid_f(g[i]) * o_scale;
+                        } else if (mode == kSiluBwd) {
+                            float y0[8];
+                            ld8(yrow + t.y_col + col + 8 * u, valid, y0);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                const float sg = sigmoid_f(y0[i]);
+                                o[i] = v[8 * u + i] * sg * (1.f + y0[i] * (1.f - sg)) * o_scale;
+                            }
+                        } else {  // kGatedBwd
+                            float g[8], yr[8], a[8];
+                            ld8(yrow + t.gate_col + col + 8 * u, valid, g);
+                            ld8(yrow + t.y_col + col + 8 * u, valid, yr);
+                            float* const gp = prm.gacc + row * prm.ldg + t.gate_col + col + 8 * u;
+                            ld8(gp, valid && !(t.flags & kFirst), a);
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) {
+                                g[i] = sigmoid_f(g[i]);
+                                o[i] = v[8 * u + i] * g[i] * o_scale;
+                                a[i] = fmaf(v[8 * u + i], yr[i], a[i]);
+                            }
+                            if (t.flags & kLast) {
+                                fin = true;
+#pragma unroll
+                                for (int i = 0; i < 8; ++i) a[i] = a[i] * g[i] * (1.f - g[i]) * o_scale;
+                                stage_split8(st_f32, st_f32 + 2048u, lane, u, a, amax);
+                            } else if (valid) {
+                                st4(gp, make_float4(a[0], a[1], a[2], a[3]));
+                                st4(gp + 4, make_float4(a[4], a[5], a[6], a[7]));
+                            }
+                        }
+                        stage_split8(st_hi, st_lo, lane, u, o, amax);
+                    }
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                __syncwarp();
+                if (lane == 0) {
+                    if (mode == kPlain) {
+                        tma_store_2d(&map_y, st_f32, t.out_col + col, (int)row0);
+                    } else {
+                        if (keep && (mode == kSilu || mode == kGated)) tma_store_2d(&map_y, st_f32, t.y_col + col, (int)row0);
+                        tma_store_2d(&map_ohi, st_hi, t.out_col + col, (int)row0);
+                        tma_store_2d(&map_olo, st_lo, t.out_col + col, (int)row0);
+                        if (fin) {
+                            tma_store_2d(&map_ohi, st_f32, t.gate_col + col, (int)row0);
+                            tma_store_2d(&map_olo, st_f32 + 2048u, t.gate_col + col, (int)row0);
+                        }
+                    }
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            mbar_arrive(tempty0 + 8u * buf);  // 256 arrivals hand the accumulator back to the MMA thread
+        }
+    }
+    if (!(amax <= kHalfMax)) *range_flag = 1;  // also catches NaN
+    if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all stores of this warp have landed
+}
+
+__global__ void __launch_bounds__(kThreads, 1)
+    so2_conv_fused_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
+                          const __grid_constant__ CUtensorMap map_whi0, const __grid_constant__ CUtensorMap map_wlo0,
+                          const __grid_constant__ CUtensorMap map_whi1, const __grid_constant__ CUtensorMap map_wlo1,
+                          const __grid_constant__ CUtensorMap map_whi2, const __grid_constant__ CUtensorMap map_wlo2,
+                          const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_ohi,
+                          const __grid_constant__ CUtensorMap map_olo, const __grid_constant__ Plan plan,
+                          const __grid_constant__ Params prm, int64_t tiles_m) {
+    constexpr int S = kStages;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t epi_base = base + S * kStageBytes;
+    const uint32_t bar_base = epi_base + kEpiWarps * kEpiWarpBytes;
+    // barrier block: full[S] | empty[S] | tmem_full[2] | tmem_empty[2] | tmem slot | abort flag | range flag
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
+    auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * S + b); };
+    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * S + 2 + b); };
+    uint8_t* const bar_generic = smem_raw + (bar_base - smem_u32(smem_raw));
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_generic + 8 * (2 * S + 4));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_generic + 8 * (2 * S + 4) + 4);
+    volatile int* range_flag = reinterpret_cast<volatile int*>(bar_generic + 8 * (2 * S + 4) + 8);
+    auto half_addr = [&](int s, int which) { return base + s * kStageBytes + which * kHalfTile; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ntiles = plan.ntiles;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(full_bar(s), 1);
+            mbar_init(empty_bar(s), 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tfull_bar(b), 1);
+            mbar_init(tempty_bar(b), 32 * kEpiWarps);
+        }
+        *abort_flag = 0;
+        *range_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                     "r"((uint32_t)kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int64_t it = 0;
+            bool ok = true;
+            for (int64_t mt = blockIdx.x; mt < tiles_m && ok; mt += gridDim.x) {
+                for (int ti = 0; ti < ntiles && ok; ++ti) {
+                    const Tile& t = plan.t[ti];
+                    const CUtensorMap* whi = t.w == 0 ? &map_whi0 : (t.w == 1 ? &map_whi1 : &map_whi2);
+                    const CUtensorMap* wlo = t.w == 0 ? &map_wlo0 : (t.w == 1 ? &map_wlo1 : &map_wlo2);
+                    const int num_kb = t.k / BK;
+                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                        const int s = (int)(it % S);
+                        const uint32_t ph = (uint32_t)((it / S) & 1);
+                        ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag);
+                        if (!ok) break;
+                        mbar_expect_tx(full_bar(s), kStageBytes);
+                        tma_load_2d(half_addr(s, 0), &map_ahi, t.a_col + kb * BK, (int)(mt * BM), full_bar(s));
+                        tma_load_2d(half_addr(s, 1), &map_alo, t.a_col + kb * BK, (int)(mt * BM), full_bar(s));
+                        tma_load_2d(half_addr(s, 2), whi, kb * BK, t.w_row, full_bar(s));
+                        tma_load_2d(half_addr(s, 3), wlo, kb * BK, t.w_row, full_bar(s));
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            int64_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int64_t mt = blockIdx.x; mt < tiles_m && ok; mt += gridDim.x) {
+                for (int ti = 0; ti < ntiles && ok; ++ti, ++tcount) {
+                    const int num_kb = plan.t[ti].k / BK;
+                    const int buf = (int)(tcount & 1);
+                    const uint32_t use = (uint32_t)((tcount >> 1) & 1);
+                    ok = mbar_wait(tempty_bar(buf), use ^ 1u, abort_flag);  // epilogue has drained this accumulator
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t acc = tmem_base + (uint32_t)(buf * kAccCols);
+                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                        const int s = (int)(it % S);
+                        const uint32_t ph = (uint32_t)((it / S) & 1);
+                        ok = mbar_wait(full_bar(s), ph, abort_flag);
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        // W_hi | W_lo are adjacent: one 256-wide MMA on a_hi gives a_hi*w_hi (main accumulator) and
+                        // a_hi*w_lo (correction accumulator); a 128-wide MMA adds a_lo*w_hi to the correction
+                        const uint64_t da_hi = smem_desc64(half_addr(s, 0)), da_lo = smem_desc64(half_addr(s, 1));
+                        const uint64_t dw = smem_desc64(half_addr(s, 2));
+#pragma unroll
+                        for (int j = 0; j < BK / 16; ++j) {
+                            const uint64_t adv = (uint64_t)(j * 2);
+                            const uint32_t first = (kb > 0 || j > 0) ? 1u : 0u;
+                            umma_f16<2 * BN>(acc, da_hi + adv, dw + adv, first);
+                            umma_f16<BN>(acc + BN, da_lo + adv, dw + adv, 1u);
+                        }
+                        umma_commit(empty_bar(s));
+                    }
+                    if (ok) umma_commit(tfull_bar(buf));
+                }
+            }
+        }
+    } else if (warp >= 4) {
+        epilogue(map_y, map_ohi, map_olo, plan, prm, tiles_m, tmem_base, epi_base, tfull_bar(0), tempty_bar(0), abort_flag,
+                 range_flag);
+    }
+
+    __syncwarp();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols) : "memory");
+    }
+    if (threadIdx.x == 0 && prm.status) {
+        if (*abort_flag) atomicExch(prm.status, 1);
+        else if (*range_flag) atomicCAS(prm.status, 0, 2);
+    }
+}
+
+
+// 2-D row-major half matrix [rows, cols], row stride ld elements; box = 32 columns x box_rows rows, 64-byte swizzle
+static int map_half(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return FCB200_EINVAL;
+    cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t gstride[1] = {(cuuint64_t)ld * 2};
+    cuuint32_t box[2] = {32u, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? FCB200_OK : FCB200_EINVAL;
+}
+
+// float32 [rows, cols] with row stride ld; box = 32 x 32, 128-byte swizzle
+static int map_f32(CUtensorMap* map, const float* ptr, int64_t rows, int64_t cols, int64_t ld) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return FCB200_EINVAL;
+    cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t gstride[1] = {(cuuint64_t)ld * 4};
+    cuuint32_t box[2] = {32u, 32u};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT32, 2, const_cast<float*>(ptr), gdim, gstride, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? FCB200_OK : FCB200_EINVAL;
+}
+
+}  // namespace fused
+}  // namespace fcb200
+
+using namespace fcb200;
+
+extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t lda, int64_t a_cols, const void* const* w_hi,
+                                     const void* const* w_lo, const int64_t* w_rows, const int64_t* w_cols,
+                                     const float* w_scale, const float* const* bias, const int32_t* tiles, int32_t num_tiles,
+                                     float* y, int64_t ldy, int64_t y_cols, void* o_hi, void* o_lo, int64_t ldo, int64_t o_cols,
+                                     float* gacc, int64_t ldg, const float* a_scale, const float* o_scale, int64_t m,
+                                     int32_t* status, void* stream) {
+    using namespace fused;
+    if (!a_hi || !a_lo || !w_hi || !w_lo || !w_rows || !w_cols || !w_scale || !tiles || !y || m < 0) return FCB200_EINVAL;
+    if (num_tiles <= 0 || num_tiles > kMaxTiles) return FCB200_ERANGE;
+    if (lda % 8 || lda < a_cols || ldy % 4 || ldy < y_cols) return FCB200_EINVAL;
+    if (!aligned16(a_hi) || !aligned16(a_lo) || !aligned16(y)) return FCB200_EALIGN;
+    if (o_hi || o_lo) {
+        if (!o_hi || !o_lo || ldo % 8 || ldo < o_cols) return FCB200_EINVAL;
+        if (!aligned16(o_hi) || !aligned16(o_lo)) return FCB200_EALIGN;
+    }
+    if (gacc && (ldg % 4 || !aligned16(gacc))) return FCB200_EINVAL;
+    Plan plan{};
+    Params prm{};
+    plan.ntiles = num_tiles;
+    bool used[3] = {false, false, false};
+    for (int i = 0; i < num_tiles; ++i) {
+        Tile& t = plan.t[i];
+        const int32_t* d = tiles + 9 * i;
+        t.a_col = d[0], t.k = d[1], t.w = d[2], t.w_row = d[3], t.out_col = d[4], t.mode = d[5], t.y_col = d[6], t.gate_col = d[7];
+        t.flags = d[8];
+        if (t.w < 0 || t.w > 2 || !w_hi[t.w] || !w_lo[t.w]) return FCB200_EINVAL;
+        if (t.k <= 0 || t.k % BK || t.k > w_cols[t.w] || t.a_col < 0 || t.a_col % 8 || t.a_col + t.k > a_cols) return FCB200_EINVAL;
+        if (t.w_row < 0 || t.w_row % BN || t.w_row + BN > w_rows[t.w]) return FCB200_EINVAL;
+        if (t.mode < kPlain || t.mode > kGatedBwd || t.out_col < 0 || t.out_col % 8) return FCB200_EINVAL;
+        const bool split = t.mode >= kSilu;
+        if (split && (!o_hi || t.out_col + BN > o_cols)) return FCB200_EINVAL;
+        if (!split && t.out_col + BN > y_cols) return FCB200_EINVAL;
+        const bool reads_gate = t.mode == kGated || t.mode == kGatedBwd;
+        if (reads_gate && (t.gate_col < 0 || t.gate_col % 4 || t.gate_col + BN > y_cols)) return FCB200_EINVAL;
+        const bool uses_y = t.mode == kSiluBwd || t.mode == kGatedBwd || ((t.mode == kSilu || t.mode == kGated) && (t.flags & kKeep));
+        if (uses_y && (t.y_col < 0 || t.y_col % 4 || t.y_col + BN > y_cols)) return FCB200_EINVAL;
+        if (t.mode == kGatedBwd && (!gacc || t.gate_col + BN > ldg || t.gate_col + BN > o_cols)) return FCB200_EINVAL;
+        used[t.w] = true;
+    }
+    if (m == 0) return FCB200_OK;
+    CUtensorMap mah, mal, mw[6], my, moh, mol;
+    int rc = map_half(&mah, a_hi, m, a_cols, lda, BM);
+    if (!rc) rc = map_half(&mal, a_lo, m, a_cols, lda, BM);
+    int first = -1;
+    for (int i = 0; i < 3 && !rc; ++i) {
+        if (!used[i]) continue;
+        if (first < 0) first = i;
+        if (w_cols[i] % 8 || !aligned16(w_hi[i]) || !aligned16(w_lo[i]) || !(w_scale[i] > 0.f)) return FCB200_EINVAL;
+        rc = map_half(&mw[2 * i], w_hi[i], w_rows[i], w_cols[i], w_cols[i], BN);
+        if (!rc) rc = map_half(&mw[2 * i + 1], w_lo[i], w_rows[i], w_cols[i], w_cols[i], BN);
+        prm.w_scale[i] = w_scale[i];
+        prm.bias[i] = bias ? bias[i] : nullptr;
+        if (prm.bias[i] && !aligned16(prm.bias[i])) return FCB200_EALIGN;
+    }
+    if (rc) return rc;
+    for (int i = 0; i < 3; ++i)
+        if (!used[i]) {  // never dereferenced; keep the parameter block initialised
+            mw[2 * i] = mw[2 * first], mw[2 * i + 1] = mw[2 * first + 1];
+            prm.w_scale[i] = 1.f;
+        }
+    rc = map_f32(&my, y, m, y_cols, ldy);
+    if (rc) return rc;
+    if (o_hi) {
+        rc = map_half(&moh, o_hi, m, o_cols, ldo, 32);
+        if (!rc) rc = map_half(&mol, o_lo, m, o_cols, ldo, 32);
+        if (rc) return rc;
+    } else {
+        moh = mah, mol = mal;  // no split-output tile exists (checked above)
+    }
+    prm.y = y, prm.ldy = ldy, prm.gacc = gacc, prm.ldg = ldg, prm.a_scale = a_scale, prm.o_scale = o_scale;
+    prm.m_total = m, prm.status = status;
+    static bool attr_done[64] = {};
+    if (const int arc = ensure_dynamic_smem(so2_conv_fused_kernel, kSmemBytes, attr_done)) return arc;
+    const int64_t tiles_m = (m + BM - 1) / BM;
+    const int grid = (int)(tiles_m < sm_count() ? tiles_m : sm_count());
+    so2_conv_fused_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(
+        mah, mal, mw[0], mw[1], mw[2], mw[3], mw[4], mw[5], my, moh, mol, plan, prm, tiles_m);
+    return launch_status();
+}

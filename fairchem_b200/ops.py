@@ -10,8 +10,8 @@ library; there is no CPU implementation.
 from __future__ import annotations
 
 import math
-from ctypes import c_void_p
-from typing import Optional
+from ctypes import c_float, c_int32, c_int64, c_void_p
+from typing import List, Optional
 
 import torch
 from torch import Tensor
@@ -532,6 +532,61 @@ def gemm_f16x2_presplit_(a_hi: Tensor, a_lo: Tensor, w_hi: Tensor, w_lo: Tensor,
     _launch("gemm_f16x2_presplit", "fcb200_gemm_f16x2_presplit",
             (_p(a_hi), _p(a_lo), a_hi.stride(0), _p(w_hi), _p(w_lo), k, w_scale, _p(a_scale), _p(bias), _p(c), c.stride(0), m, n, k,
              _p(status), _stream()), nbytes=4 * (m * k + n * k + m * n), flops=2 * m * n * k)
+
+
+# epilogue modes and flags of so2_conv_fused_ (csrc/so2_conv_fused.cu)
+CONV_PLAIN, CONV_GATE_RAW, CONV_SILU, CONV_GATED, CONV_SILU_BWD, CONV_GATED_BWD = range(6)
+CONV_FIRST, CONV_LAST, CONV_KEEP = 1, 2, 4
+CONV_MAX_TILES = 40
+
+
+@_op("so2_conv_fused", ("y", "o_hi", "o_lo", "gacc", "status"))
+def so2_conv_fused_(a_hi: Tensor, a_lo: Tensor, w_hi: List[Tensor], w_lo: List[Tensor], w_scale: List[float],
+                    bias0: Optional[Tensor], tiles: List[int], y: Tensor, o_hi: Optional[Tensor], o_lo: Optional[Tensor],
+                    gacc: Optional[Tensor], a_scale: Optional[Tensor], o_scale: Optional[Tensor], status: Tensor) -> None:
+    """One launch for all m-blocks of an SO(2) convolution with the gate (or its derivative) in the epilogue.
+
+    ``a_hi/a_lo`` [E, Ka] are the input planes, ``w_*`` the (up to three) half-split weight matrices, ``tiles`` a flat
+    list of 9 integers per 128-column output tile (a_col, k, w, w_row, out_col, mode, y_col, gate_col, flags).  ``y``
+    [E, >=gates] float32 receives the float32 modes and the raw gate scalars and is read by the gated modes; ``o_hi/o_lo``
+    receive the split modes; ``gacc`` is float32 scratch [E, >=gates] for the gate-gradient sums."""
+    for t in (a_hi, a_lo):
+        if not t.is_cuda or t.dtype != torch.float16 or t.dim() != 2 or t.stride(1) != 1 or t.shape != a_hi.shape \
+                or t.stride(0) != a_hi.stride(0):
+            raise _lib.FairchemB200Error("so2_conv_fused: need 2-D float16 CUDA planes of one shape and row stride")
+    if not y.is_cuda or y.dtype != torch.float32 or y.dim() != 2 or y.stride(1) != 1:
+        raise _lib.FairchemB200Error("so2_conv_fused: need a 2-D float32 CUDA y with unit inner stride")
+    if (o_hi is None) != (o_lo is None):
+        raise _lib.FairchemB200Error("so2_conv_fused: output planes come in pairs")
+    if o_hi is not None:
+        for t in (o_hi, o_lo):
+            if not t.is_cuda or t.dtype != torch.float16 or t.dim() != 2 or t.stride(1) != 1 or t.shape != o_hi.shape \
+                    or t.stride(0) != o_hi.stride(0) or t.shape[0] != a_hi.shape[0]:
+                raise _lib.FairchemB200Error("so2_conv_fused: need 2-D float16 CUDA output planes of one shape and row stride")
+    if gacc is not None and (not gacc.is_cuda or gacc.dtype != torch.float32 or gacc.dim() != 2 or gacc.stride(1) != 1):
+        raise _lib.FairchemB200Error("so2_conv_fused: need a 2-D float32 CUDA scratch")
+    if len(w_hi) != len(w_lo) or len(w_hi) != len(w_scale) or not 1 <= len(w_hi) <= 3 or len(tiles) % 9:
+        raise _lib.FairchemB200Error("so2_conv_fused: malformed weight or tile lists")
+    for t in list(w_hi) + list(w_lo):
+        if not t.is_cuda or t.dtype != torch.float16 or t.dim() != 2 or not t.is_contiguous():
+            raise _lib.FairchemB200Error("so2_conv_fused: need contiguous 2-D float16 CUDA weight parts")
+    _chk(bias0, status, a_scale, o_scale)
+    nw, nt, m = len(w_hi), len(tiles) // 9, a_hi.shape[0]
+    pad = [None] * (3 - nw)
+    whi = (c_void_p * 3)(*([t.data_ptr() for t in w_hi] + pad))
+    wlo = (c_void_p * 3)(*([t.data_ptr() for t in w_lo] + pad))
+    rows = (c_int64 * 3)(*([t.shape[0] for t in w_hi] + [0] * (3 - nw)))
+    cols = (c_int64 * 3)(*([t.shape[1] for t in w_hi] + [0] * (3 - nw)))
+    scales = (c_float * 3)(*(list(w_scale) + [1.0] * (3 - nw)))
+    biases = (c_void_p * 3)(None if bias0 is None else bias0.data_ptr(), None, None)
+    tl = (c_int32 * len(tiles))(*tiles)
+    flops = 2 * m * 128 * sum(tiles[9 * i + 1] for i in range(nt))
+    nbytes = 4 * m * (a_hi.shape[1] + 128 * nt)
+    _launch("so2_conv_fused", "fcb200_so2_conv_fused",
+            (_p(a_hi), _p(a_lo), a_hi.stride(0), a_hi.shape[1], whi, wlo, rows, cols, scales, biases, tl, nt,
+             _p(y), y.stride(0), y.shape[1], _p(o_hi), _p(o_lo), 0 if o_hi is None else o_hi.stride(0),
+             0 if o_hi is None else o_hi.shape[1], _p(gacc), 0 if gacc is None else gacc.stride(0), _p(a_scale), _p(o_scale), m,
+             _p(status), _stream()), nbytes=nbytes, flops=flops)
 
 
 def split_f16(w: Tensor):

@@ -329,6 +329,36 @@ int fcb200_gemm_f16x2_presplit(const void* a_hi, const void* a_lo, int64_t lda, 
                                int64_t m, int32_t n, int32_t k, int32_t* status, void* stream);
 
 /*
+ * One launch for a whole SO(2) convolution (all m-blocks) with the gate activation, or its derivative, applied
+ * in the epilogue: replaces SO2_Convolution.forward (uma/nn/so2_layers.py:600-647; block form :83-169) followed by
+ * GateActivation.forward (uma/nn/activation.py:146-165), and their autograd twins, which the reference runs as
+ * separate cuBLAS GEMMs, elementwise kernels and concatenations.  A CTA owns 128 edges and walks the listed
+ * 128-column output tiles in order; the float32 convolution output between GEMM and gate never exists in memory
+ * unless the caller asks to keep it for the backward pass.
+ *   a_hi, a_lo   [M, a_cols] half planes (row stride lda halves), both of (A * *a_scale)
+ *   w_hi, w_lo   HOST arrays of 3 device pointers: half-split weights [w_rows[i], w_cols[i]] contiguous (unused: NULL)
+ *   w_scale      HOST array of 3 floats; bias: HOST array of 3 device pointers (or NULL entries / NULL array)
+ *   tiles        HOST array, 9 int32 per tile: a_col, k, w, w_row, out_col, mode, y_col, gate_col, flags
+ *                mode 0  float32 tile -> y[:, out_col..]
+ *                mode 1  float32 tile -> y[:, out_col..] with plain stores (gate scalars; must precede mode-3 tiles)
+ *                mode 2  planes[:, out_col..] = split(v * sigmoid(v));                    flag 4: also y[:, y_col..] = v
+ *                mode 3  planes[:, out_col..] = split(v * sigmoid(y[:, gate_col..]));     flag 4: also y[:, y_col..] = v
+ *                mode 4  planes[:, out_col..] = split(v * silu'(y[:, y_col..]))
+ *                mode 5  planes[:, out_col..] = split(v * sigmoid(y[:, gate_col..])) and the gate gradient
+ *                        sum_rows v * y[:, y_col..] accumulated in gacc[:, gate_col..] (flag 1: first row of the
+ *                        degree, flag 2: last row -> planes[:, gate_col..] = split(sum * s * (1 - s)))
+ *   y            [M, y_cols] float32, row stride ldy; o_hi/o_lo [M, o_cols] half planes, row stride ldo, written
+ *                times *o_scale (device pointers to powers of two, NULL = 1); gacc [M, ldg] float32 SCRATCH
+ *   status       as in fcb200_gemm_f16x2_presplit
+ * At most 40 tiles; every k a multiple of 32, w_row a multiple of 128.
+ */
+int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t lda, int64_t a_cols, const void* const* w_hi,
+                          const void* const* w_lo, const int64_t* w_rows, const int64_t* w_cols, const float* w_scale,
+                          const float* const* bias, const int32_t* tiles, int32_t num_tiles, float* y, int64_t ldy,
+                          int64_t y_cols, void* o_hi, void* o_lo, int64_t ldo, int64_t o_cols, float* gacc, int64_t ldg,
+                          const float* a_scale, const float* o_scale, int64_t m, int32_t* status, void* stream);
+
+/*
  * The four kernels whose output is consumed only by an SO(2) contraction, writing that output as the
  * half-precision split (two planes `*_hi`, `*_lo` of the float32 tensor's shape, values times *scale; scale
  * is a DEVICE pointer to a power of two, or NULL for 1) instead of float32: same bytes written, and the
