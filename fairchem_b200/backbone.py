@@ -721,14 +721,14 @@ def _fused_conv1_gate(ew, m, y_keep):
     y = y_keep if y_keep is not None else torch.empty(ec, p.gates, dtype=torch.float32, device=dev)
     a = _new_operand(ec, p.y_width - p.gates, dev)
     ops.so2_conv_fused_.raw(m[0], m[1], list(p.w1[0]), list(p.w1[1]), list(p.w1[2]), p.bias1, p.fwd1[y_keep is not None], y,
-                            a[0], a[1], None, None, None, _status(dev))
+                            a[0], a[1], None, None, None, _status(dev), "_conv1_gate")
     return a
 
 
 def _fused_conv2(ew, a, out):
     p = _fused_plan(ew)
     ops.so2_conv_fused_.raw(a[0], a[1], list(p.w2[0]), list(p.w2[1]), list(p.w2[2]), p.bias2, p.fwd2, out, None, None, None,
-                            None, None, _status(out.device))
+                            None, None, _status(out.device), "_conv2")
     return out
 
 
@@ -739,7 +739,7 @@ def _fused_conv2_gate_backward(ew, grad_msg, y, scale):
     gy = _new_operand(ec, p.y_width, dev)
     gacc = torch.empty(ec, p.gates, dtype=torch.float32, device=dev)
     ops.so2_conv_fused_.raw(grad_msg[0], grad_msg[1], list(p.w2t[0]), list(p.w2t[1]), list(p.w2t[2]), None, p.bwd2, y,
-                            gy[0], gy[1], gacc, scale, scale, _status(dev))
+                            gy[0], gy[1], gacc, scale, scale, _status(dev), "_conv2_gate_bwd")
     return gy
 
 
@@ -748,7 +748,7 @@ def _fused_conv1_backward(ew, gy, scale):
     ec, dev = gy[0].shape[0], gy[0].device
     gm = torch.empty(ec, sum(w.shape[1] for w in p.w1[0]), dtype=torch.float32, device=dev)
     ops.so2_conv_fused_.raw(gy[0], gy[1], list(p.w1t[0]), list(p.w1t[1]), list(p.w1t[2]), None, p.bwd1, gm, None, None, None,
-                            scale, None, _status(dev))
+                            scale, None, _status(dev), "_conv1_bwd")
     return gm
 
 
@@ -1092,6 +1092,12 @@ class eSCNMDBackboneB200(nn.Module):
                               train_on_free_atoms=True, eval_on_free_atoms=True, inference_only=True))
         return tasks
 
+    def merge_MOLE_model(self, data):
+        """The reference's hook for folding routed experts into plain weights before inference (MOLEInterface,
+        src/fairchem/core/models/uma/nn/mole_utils.py:30-44).  This backbone only ever holds merged weights --
+        fairchem_b200.mole.merge_mole_state_dict does the folding on the checkpoint -- so there is nothing left to do."""
+        return self
+
     def validate_tasks(self, dataset_to_tasks: dict) -> None:
         assert set(dataset_to_tasks).issubset(set(self.dataset_mapping)), \
             "Datasets in tasks is not a strict subset of datasets in backbone."
@@ -1302,12 +1308,18 @@ def energy_forces(backbone, head, data, gamma: Optional[torch.Tensor] = None) ->
         set_gemm_precision(2)
 
 
-def build_model(cfg: dict, state_dict: Optional[dict] = None, device="cuda", **overrides):
-    """Backbone + head from a config dict (fairchem_b200.weights.UMA_S keys) and an optional combined state_dict."""
+def build_model(cfg: dict, state_dict: Optional[dict] = None, device="cuda", mole_data=None, **overrides):
+    """Backbone + head from a config dict (fairchem_b200.weights.UMA_S keys) and an optional combined state_dict.
+    A routed-expert (MOLE) state_dict is merged for the system in ``mole_data`` first (fairchem_b200.mole)."""
+    from . import mole
     from .weights import split_head
 
     kw = dict(cfg)
     kw.update(overrides)
+    if state_dict is not None and mole.is_mole_state_dict(state_dict):
+        if mole_data is None:
+            raise ValueError("a routed-expert state_dict needs mole_data: the system its experts are merged for")
+        state_dict = mole.merge_mole_state_dict(state_dict, mole_data, kw.get("dataset_mapping"))
     bb = eSCNMDBackboneB200(otf_graph=True, **kw)
     head = MLP_EFS_HeadB200(bb)
     if state_dict is not None:

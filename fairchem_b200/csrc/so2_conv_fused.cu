@@ -61,7 +61,7 @@ constexpr int kStages = 5;
 constexpr int kStageBytes = 4 * BM * BK * 2;           // A_hi | A_lo | W_hi | W_lo, 8 KiB each
 constexpr int kHalfTile = BM * BK * 2;
 constexpr int kEpiWarps = 8;
-constexpr int kEpiWarpBytes = 4096 + 2048 + 2048;      // float32 32x32 | hi 32x32 | lo 32x32 staging per warp
+constexpr int kEpiWarpBytes = 2 * 4096;                // two staging buffers per warp: a float32 32x32 tile or hi|lo 32x32 tiles
 constexpr int kThreads = 128 + 32 * kEpiWarps;         // warp 0 TMA, warp 1 MMA, warps 2-3 idle, warps 4-11 epilogue
 constexpr int kAccCols = 2 * BN, kTmemCols = 2 * kAccCols;
 constexpr int kSmemBytes = kStages * kStageBytes + kEpiWarps * kEpiWarpBytes + 1024 + 256;
@@ -79,7 +79,9 @@ struct Params {
     int32_t* status;
 };
 
-__device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
+// 1 / (1 + e^-v) on the special-function unit (ex2.approx, rcp.approx): relative error ~2^-22, a few instructions
+// instead of the ~20 of expf and an IEEE division -- the epilogue evaluates it for every output element
+__device__ __forceinline__ float sigmoid_f(float v) { return __fdividef(1.0f, 1.0f + __expf(-v)); }
 
 // pack (a, b) * already-applied scale into hi and lo half pairs; track the largest magnitude
 __device__ __forceinline__ void pack2(float a, float b, uint32_t& hi, uint32_t& lo, float& amax) {
@@ -128,7 +130,9 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q = warp & 3;
     const int half = (warp - 4) >> 2;
-    const uint32_t st_f32 = epi_base + (uint32_t)((warp - 4) * kEpiWarpBytes), st_hi = st_f32 + 4096u, st_lo = st_hi + 2048u;
+    const uint32_t st_base = epi_base + (uint32_t)((warp - 4) * kEpiWarpBytes);
+    int nst = 0;            // staged chunks so far: single-buffer chunks alternate between the two buffers
+    bool both_busy = false;  // the previous chunk used both buffers
     const float a_scale = prm.a_scale ? *prm.a_scale : 1.0f;
     const float o_scale = prm.o_scale ? *prm.o_scale : 1.0f;
     const int ntiles = plan.ntiles;
@@ -162,13 +166,13 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
                     FCB_TMEM_LD32(r, acc + (uint32_t)col);
                     FCB_TMEM_LD32(c, acc + (uint32_t)(BN + col));
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    uint32_t bad = 0;
+                    float poison = 0.f;  // becomes NaN if any value is inf or NaN (an overflowed half upstream)
 #pragma unroll
                     for (int i = 0; i < 32; ++i) {
                         v[i] = fmaf(__uint_as_float(c[i]), corr_scale, __uint_as_float(r[i]) * out_scale);
-                        bad |= (uint32_t)((__float_as_uint(v[i]) & 0x7f800000u) == 0x7f800000u);  // inf or NaN: an overflowed half upstream
+                        poison = fmaf(v[i], 0.f, poison);
                     }
-                    if (bad && valid) *range_flag = 1;
+                    if (poison != poison && valid) *range_flag = 1;
                 }
                 if (row0 >= prm.m_total) continue;  // this warp's 32 rows lie entirely below the matrix
                 if (bias) {
@@ -186,15 +190,25 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
                     }
                     continue;
                 }
-                // the stores issued for the previous chunk read the staging tiles: let them finish before overwriting
-                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                const bool keep = (t.flags & kKeep) != 0 && (mode == kSilu || mode == kGated);
+                const bool fin = mode == kGatedBwd && (t.flags & kLast) != 0;  // gate gradient finalised in this tile
+                const bool two = keep || fin;
+                // a chunk stages into one buffer (float32 tile, or hi|lo tiles) unless it also keeps y or finalises a
+                // gate gradient; the stores issued earlier must have read a buffer before it is overwritten
+                if (lane == 0) {
+                    if (two || both_busy) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                }
                 __syncwarp();
-                const bool keep = (t.flags & kKeep) != 0;
-                if (mode == kPlain || ((mode == kSilu || mode == kGated) && keep)) {
+                const uint32_t buf_a = st_base + (two ? 0u : (uint32_t)((nst & 1) * 4096));  // float32 tile / extra planes
+                const uint32_t buf_b = two ? st_base + 4096u : buf_a;                         // hi | lo tiles
+                const uint32_t st_f32 = buf_a, st_hi = buf_b, st_lo = buf_b + 2048u;
+                both_busy = two;
+                nst += two ? 0 : 1;
+                if (mode == kPlain || keep) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) stage_f32x4(st_f32, lane, i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
                 }
-                bool fin = false;  // kGatedBwd, last row of a degree: gate gradient staged in the float32 area as two planes
                 if (mode != kPlain) {
 #pragma unroll
                     for (int u = 0; u < 4; ++u) {
@@ -227,8 +241,7 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
                                 o[i] = v[8 * u + i] * g[i] * o_scale;
                                 a[i] = fmaf(v[8 * u + i], yr[i], a[i]);
                             }
-                            if (t.flags & kLast) {
-                                fin = true;
+                            if (fin) {
 #pragma unroll
                                 for (int i = 0; i < 8; ++i) a[i] = a[i] * g[i] * (1.f - g[i]) * o_scale;
                                 stage_split8(st_f32, st_f32 + 2048u, lane, u, a, amax);
@@ -246,7 +259,7 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
                     if (mode == kPlain) {
                         tma_store_2d(&map_y, st_f32, t.out_col + col, (int)row0);
                     } else {
-                        if (keep && (mode == kSilu || mode == kGated)) tma_store_2d(&map_y, st_f32, t.y_col + col, (int)row0);
+                        if (keep) tma_store_2d(&map_y, st_f32, t.y_col + col, (int)row0);
                         tma_store_2d(&map_ohi, st_hi, t.out_col + col, (int)row0);
                         tma_store_2d(&map_olo, st_lo, t.out_col + col, (int)row0);
                         if (fin) {

@@ -543,7 +543,8 @@ CONV_MAX_TILES = 40
 @_op("so2_conv_fused", ("y", "o_hi", "o_lo", "gacc", "status"))
 def so2_conv_fused_(a_hi: Tensor, a_lo: Tensor, w_hi: List[Tensor], w_lo: List[Tensor], w_scale: List[float],
                     bias0: Optional[Tensor], tiles: List[int], y: Tensor, o_hi: Optional[Tensor], o_lo: Optional[Tensor],
-                    gacc: Optional[Tensor], a_scale: Optional[Tensor], o_scale: Optional[Tensor], status: Tensor) -> None:
+                    gacc: Optional[Tensor], a_scale: Optional[Tensor], o_scale: Optional[Tensor], status: Tensor,
+                    label: str = "") -> None:
     """One launch for all m-blocks of an SO(2) convolution with the gate (or its derivative) in the epilogue.
 
     ``a_hi/a_lo`` [E, Ka] are the input planes, ``w_*`` the (up to three) half-split weight matrices, ``tiles`` a flat
@@ -582,7 +583,7 @@ def so2_conv_fused_(a_hi: Tensor, a_lo: Tensor, w_hi: List[Tensor], w_lo: List[T
     tl = (c_int32 * len(tiles))(*tiles)
     flops = 2 * m * 128 * sum(tiles[9 * i + 1] for i in range(nt))
     nbytes = 4 * m * (a_hi.shape[1] + 128 * nt)
-    _launch("so2_conv_fused", "fcb200_so2_conv_fused",
+    _launch("so2_conv_fused" + label, "fcb200_so2_conv_fused",
             (_p(a_hi), _p(a_lo), a_hi.stride(0), a_hi.shape[1], whi, wlo, rows, cols, scales, biases, tl, nt,
              _p(y), y.stride(0), y.shape[1], _p(o_hi), _p(o_lo), 0 if o_hi is None else o_hi.stride(0),
              0 if o_hi is None else o_hi.shape[1], _p(gacc), 0 if gacc is None else gacc.stride(0), _p(a_scale), _p(o_scale), m,

@@ -2,7 +2,7 @@
 
 Imports ``fairchem.core.models.uma.escn_md`` from a read-only checkout of
 facebookresearch/fairchem without installing it: packages the checkout needs but this
-image lacks (omegaconf, hydra, monty, e3nn, ase, ray, torchtnt) are replaced by inert
+image lacks (omegaconf, hydra, monty, e3nn, matplotlib, ase, ray, torchtnt) are replaced by inert
 stand-ins, and the heavy ``__init__`` files are skipped by pre-registering namespace
 modules.  Nothing of the reference is copied; its sources run where they lie.
 
@@ -83,6 +83,11 @@ def load():
     if "e3nn" not in sys.modules:
         _stub("e3nn")
         _stub("e3nn.o3", ToS2Grid=_ToS2Grid, FromS2Grid=_FromS2Grid)
+    if "matplotlib" not in sys.modules:  # escn_moe.py imports pyplot for a training-time plot only
+        try:
+            import matplotlib  # noqa: F401
+        except ModuleNotFoundError:
+            _stub("matplotlib").pyplot = _stub("matplotlib.pyplot")
     if _REF_SRC not in sys.path:
         sys.path.insert(0, _REF_SRC)
     for pkg in ("fairchem", "fairchem.core", "fairchem.core.units", "fairchem.core.units.mlip_unit"):

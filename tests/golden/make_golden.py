@@ -286,8 +286,47 @@ def make_partition_golden():
     np.savez_compressed(os.path.join(OUT, "partition.npz"), **out)
 
 
+def make_mole_golden():
+    """A small routed-expert backbone (3 experts, 16 channels, 1 layer, with and without the composition embedding)
+    merged by the reference for one system (escn_moe.py:92-123): its state_dict before and after, the mixing
+    coefficients and the system's fields."""
+    import importlib
+
+    ref_shim.load()
+    moe = importlib.import_module("fairchem.core.models.uma.escn_moe")
+    data = synthetic.molecule_batch(1, seed=11)
+    data["charge"] = torch.tensor([-1])
+    data["spin"] = torch.tensor([2])
+    out = {"atomic_numbers": data["atomic_numbers"].numpy(), "batch": data["batch"].numpy(), "charge": data["charge"].numpy(),
+           "spin": data["spin"].numpy(), "dataset": np.array(data["dataset"])}
+    for tag, comp in (("comp", True), ("nocomp", False)):
+        torch.manual_seed(7)
+        bb = moe.eSCNMDMoeBackbone(
+            num_experts=3, use_composition_embedding=comp, max_num_elements=100, otf_graph=True, direct_forces=False,
+            regress_forces=True, norm_type="rms_norm_sh", act_type="gate", ff_type="spectral", chg_spin_emb_type="rand_emb",
+            dataset_mapping={"omat": "omat", "omol": "omol"}, always_use_pbc=False, radius_pbc_version=2,
+            execution_mode="general", sphere_channels=16, lmax=2, mmax=2, num_layers=1, hidden_channels=16, edge_channels=16,
+            num_distance_basis=8, cutoff=6.0, max_neighbors=30)
+        bb.eval()
+        with torch.no_grad():  # routing weights are tiny at init: spread the coefficients
+            for p in bb.routing_mlp.parameters():
+                p.mul_(8.0)
+        for k, v in bb.state_dict().items():
+            if not k.startswith("Jd_"):
+                out[f"{tag}/in/{k}"] = v.numpy().copy()
+        merged = bb.merge_MOLE_model(data.clone())
+        out[f"{tag}/coeff"] = bb.global_mole_tensors.expert_mixing_coefficients.detach().numpy().copy()
+        for k, v in merged.state_dict().items():
+            if not k.startswith("Jd_"):
+                out[f"{tag}/out/{k}"] = v.numpy().copy()
+    np.savez_compressed(os.path.join(OUT, "mole_merge.npz"), **out)
+    print("mole_merge.npz", len(out), "arrays")
+
+
 if __name__ == "__main__":
-    which = sys.argv[1:] or ["graph", "wigner", "ops", "model", "partition", "l4", "stress", "ops_l4"]
+    which = sys.argv[1:] or ["graph", "wigner", "ops", "model", "partition", "l4", "stress", "ops_l4", "mole"]
+    if "mole" in which:
+        make_mole_golden()
     if "stress" in which:
         make_stress_golden()
     if "ops_l4" in which:
