@@ -665,12 +665,14 @@ class _FusedConvPlan:
         def fwd1(keep):
             def describe(c):
                 if c < gates:
-                    return c, ops.CONV_GATE_RAW, 0, 0, 0
+                    return c, ops.CONV_PLAIN, 0, 0, 0
                 r, j = divmod(c - gates, h)
                 flags = ops.CONV_KEEP if keep else 0
                 if r == 0:
                     return c - gates, ops.CONV_SILU, c, 0, flags
-                return c - gates, ops.CONV_GATED, c, (deg[r] - 1) * h + j, flags
+                # the first gated tile waits for this warp's stores of the gate scalars before reading them back
+                sync = ops.CONV_SYNC if (r == 1 and j == 0) else 0
+                return c - gates, ops.CONV_GATED, c, (deg[r] - 1) * h + j, flags | sync
             return _fused_tiles(s1, False, describe)
 
         rows_of = {l: [r for r, d in enumerate(deg) if d == l] for l in range(1, lmax + 1)}
@@ -686,7 +688,11 @@ class _FusedConvPlan:
         plain = lambda c: (c, ops.CONV_PLAIN, 0, 0, 0)  # noqa: E731
         self.fwd1 = {False: fwd1(False), True: fwd1(True)}
         self.fwd2 = _fused_tiles(s2, False, plain)
-        self.bwd2 = _fused_tiles(s2, True, bwd2)
+        # the rows of one degree (and column tile) back to back: their gate-gradient sum stays in registers
+        t2 = _fused_tiles(s2, True, bwd2)
+        t2 = [t2[i:i + 9] for i in range(0, len(t2), 9)]
+        t2.sort(key=lambda t: (t[5] != ops.CONV_SILU_BWD, t[7], t[4]))
+        self.bwd2 = [v for t in t2 for v in t]
         self.bwd1 = _fused_tiles(s1, True, plain)
         self.ok = max(len(t) // 9 for t in (self.fwd1[True], self.fwd2, self.bwd2, self.bwd1)) <= ops.CONV_MAX_TILES and h % 128 == 0
         split = lambda ws: tuple(zip(*[_split16(w) for w in ws]))  # noqa: E731
@@ -721,13 +727,13 @@ def _fused_conv1_gate(ew, m, y_keep):
     y = y_keep if y_keep is not None else torch.empty(ec, p.gates, dtype=torch.float32, device=dev)
     a = _new_operand(ec, p.y_width - p.gates, dev)
     ops.so2_conv_fused_.raw(m[0], m[1], list(p.w1[0]), list(p.w1[1]), list(p.w1[2]), p.bias1, p.fwd1[y_keep is not None], y,
-                            a[0], a[1], None, None, None, _status(dev), "_conv1_gate")
+                            a[0], a[1], None, None, _status(dev), "_conv1_gate")
     return a
 
 
 def _fused_conv2(ew, a, out):
     p = _fused_plan(ew)
-    ops.so2_conv_fused_.raw(a[0], a[1], list(p.w2[0]), list(p.w2[1]), list(p.w2[2]), p.bias2, p.fwd2, out, None, None, None,
+    ops.so2_conv_fused_.raw(a[0], a[1], list(p.w2[0]), list(p.w2[1]), list(p.w2[2]), p.bias2, p.fwd2, out, None, None,
                             None, None, _status(out.device), "_conv2")
     return out
 
@@ -737,9 +743,8 @@ def _fused_conv2_gate_backward(ew, grad_msg, y, scale):
     p = _fused_plan(ew)
     ec, dev = y.shape[0], y.device
     gy = _new_operand(ec, p.y_width, dev)
-    gacc = torch.empty(ec, p.gates, dtype=torch.float32, device=dev)
     ops.so2_conv_fused_.raw(grad_msg[0], grad_msg[1], list(p.w2t[0]), list(p.w2t[1]), list(p.w2t[2]), None, p.bwd2, y,
-                            gy[0], gy[1], gacc, scale, scale, _status(dev), "_conv2_gate_bwd")
+                            gy[0], gy[1], scale, scale, _status(dev), "_conv2_gate_bwd")
     return gy
 
 
@@ -747,7 +752,7 @@ def _fused_conv1_backward(ew, gy, scale):
     p = _fused_plan(ew)
     ec, dev = gy[0].shape[0], gy[0].device
     gm = torch.empty(ec, sum(w.shape[1] for w in p.w1[0]), dtype=torch.float32, device=dev)
-    ops.so2_conv_fused_.raw(gy[0], gy[1], list(p.w1t[0]), list(p.w1t[1]), list(p.w1t[2]), None, p.bwd1, gm, None, None, None,
+    ops.so2_conv_fused_.raw(gy[0], gy[1], list(p.w1t[0]), list(p.w1t[1]), list(p.w1t[2]), None, p.bwd1, gm, None, None,
                             scale, None, _status(dev), "_conv1_bwd")
     return gm
 

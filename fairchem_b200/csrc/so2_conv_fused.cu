@@ -4,15 +4,15 @@
 // the convolution output never makes a round trip through memory as float32 just to be gated:
 //
 //   conv 1 forward : A = rotated+radial-scaled rows (hi, lo planes)  ->  tiles [gate scalars | rows]
-//                    gate tiles  : raw float32 into y (a later tile of the same thread reads them back)
+//                    gate tiles  : raw float32 into y (later tiles of the same warp read them back through TMA)
 //                    row tiles   : row 0 -> v * sigmoid(v); row (l, m) -> v * sigmoid(gate[l-1]); written as the
 //                                  (hi, lo) half planes conv 2 reads; raw y rows are stored only when the backward
 //                                  pass will want them
 //   conv 2 forward : plain float32 output (messages)
 //   conv 2 backward: A = message gradient planes -> tiles = rows of the gate output's gradient; the epilogue
-//                    reads the kept y, writes the gradient of the conv-1 output as (hi, lo) planes and accumulates
-//                    the gate-scalar gradients over the rows of a degree in a float32 scratch row that the same
-//                    thread revisits (first tile of a degree writes, last tile finalises into the planes)
+//                    reads the kept y, writes the gradient of the conv-1 output as (hi, lo) planes and sums the
+//                    gate-scalar gradients over the rows of a degree in registers (the tiles of a degree are
+//                    consecutive: the first resets the sums, the last writes them into the planes)
 //   conv 1 backward: plain float32 output (gradient of the rotated rows)
 //
 // Replaces SO2_Convolution.forward + GateActivation.forward of the reference
@@ -30,13 +30,13 @@ using namespace f16;
 
 enum Mode : int32_t {
     kPlain = 0,     // float32 tile -> y[:, out_col ...] through TMA
-    kGateRaw = 1,   // float32 tile -> y[:, out_col ...] with plain stores (read back by this thread in kGated tiles)
+    kGateRaw = 1,   // (unused: gate scalars are kPlain tiles; the first kGated tile after them carries kSync)
     kSilu = 2,      // planes[:, out_col ...] = split(v * sigmoid(v));                       keep: y[:, y_col ...] = v
     kGated = 3,     // planes[:, out_col ...] = split(v * sigmoid(y[:, gate_col ...]));      keep: y[:, y_col ...] = v
     kSiluBwd = 4,   // planes[:, out_col ...] = split(v * d/dy silu(y[:, y_col ...]))
-    kGatedBwd = 5,  // planes[:, out_col ...] = split(v * sigmoid(gate)); gate gradient accumulated over rows
+    kGatedBwd = 5,  // planes[:, out_col ...] = split(v * sigmoid(gate)); gate gradient summed over consecutive tiles
 };
-enum Flags : int32_t { kFirst = 1, kLast = 2, kKeep = 4 };
+enum Flags : int32_t { kFirst = 1, kLast = 2, kKeep = 4, kSync = 8 };
 
 struct Tile {
     int32_t a_col;     // first input column of this tile's K range
@@ -57,12 +57,12 @@ struct Plan {
     Tile t[kMaxTiles];
 };
 
-constexpr int kStages = 5;
+constexpr int kStages = 4;
 constexpr int kStageBytes = 4 * BM * BK * 2;           // A_hi | A_lo | W_hi | W_lo, 8 KiB each
 constexpr int kHalfTile = BM * BK * 2;
 constexpr int kEpiWarps = 8;
-constexpr int kEpiWarpBytes = 2 * 4096;                // two staging buffers per warp: a float32 32x32 tile or hi|lo 32x32 tiles
-constexpr int kThreads = 128 + 32 * kEpiWarps;         // warp 0 TMA, warp 1 MMA, warps 2-3 idle, warps 4-11 epilogue
+constexpr int kEpiWarpBytes = 3 * 4096;                // three 32 x 32 float32 (or hi|lo half) tiles per epilogue warp
+constexpr int kThreads = 64 + 32 * kEpiWarps;          // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
 constexpr int kAccCols = 2 * BN, kTmemCols = 2 * kAccCols;
 constexpr int kSmemBytes = kStages * kStageBytes + kEpiWarps * kEpiWarpBytes + 1024 + 256;
 
@@ -71,8 +71,6 @@ struct Params {
     float w_scale[3];
     float* y;          // raw conv-1 output / float32 output
     int64_t ldy;
-    float* gacc;       // [M, ldg] float32 scratch for the gate-gradient sums (kGatedBwd only)
-    int64_t ldg;
     const float* a_scale;  // power of two the A planes were written with (null = 1)
     const float* o_scale;  // power of two the output planes are written with (null = 1)
     int64_t m_total;
@@ -111,39 +109,45 @@ __device__ __forceinline__ void stage_f32x4(uint32_t base, int lane, int v4, flo
 }
 
 
-__device__ __forceinline__ void ld8(const float* p, bool valid, float (&o)[8]) {
-    if (valid) {
-        const float4 a = ld4(p), b = ld4(p + 4);
-        o[0] = a.x, o[1] = a.y, o[2] = a.z, o[3] = a.w, o[4] = b.x, o[5] = b.y, o[6] = b.z, o[7] = b.w;
-    } else {
+// own row (`lane`) of a 32 x 32 float32 tile that TMA landed with the 128-byte swizzle: values [8u, 8u + 8)
+__device__ __forceinline__ void ld_row8(uint32_t base, int lane, int u, float (&o)[8]) {
 #pragma unroll
-        for (int i = 0; i < 8; ++i) o[i] = 0.f;
+    for (int h = 0; h < 2; ++h) {
+        const uint32_t src = base + (uint32_t)(lane * 128 + (((2 * u + h) ^ (lane & 7)) * 16));
+        asm volatile("ld.shared.v4.f32 {%0,%1,%2,%3}, [%4];" : "=f"(o[4 * h]), "=f"(o[4 * h + 1]), "=f"(o[4 * h + 2]), "=f"(o[4 * h + 3]) : "r"(src));
     }
 }
 
-// Epilogue warps 4..11: warp w reads TMEM lanes [32 (w % 4), +32) -- one accumulator row per thread -- and takes
-// the 64 columns [64 h, 64 h + 64) of every tile, h = (w - 4) / 4, in two chunks of 32.
+// Epilogue warps 2..9: warp w reads TMEM lanes [32 (w % 4), +32) -- one accumulator row per thread -- and takes the
+// 64 columns [64 h, 64 h + 64) of every tile, h = (w - 2) / 4, in two chunks of 32.  Per warp three 4 KiB
+// shared-memory tiles: B0 and B1 receive the 32 x 32 float32 tiles of y a gated mode reads (TMA loads, so the
+// global reads are whole lines and each thread then takes its own row from shared memory), B2 stages the output;
+// B1 doubles as the staging tile of a kept y row or of a finished gate gradient.  Launches of plain tiles rotate
+// the output over all three.
 __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtensorMap& map_ohi, const CUtensorMap& map_olo,
                                          const Plan& plan, const Params& prm, int64_t tiles_m, uint32_t tmem_base,
-                                         uint32_t epi_base, uint32_t tfull0, uint32_t tempty0, volatile int* abort_flag,
-                                         volatile int* range_flag) {
+                                         uint32_t epi_base, uint32_t tfull0, uint32_t tempty0, uint32_t ld_bar0,
+                                         volatile int* abort_flag, volatile int* range_flag) {
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q = warp & 3;
-    const int half = (warp - 4) >> 2;
-    const uint32_t st_base = epi_base + (uint32_t)((warp - 4) * kEpiWarpBytes);
-    int nst = 0;            // staged chunks so far: single-buffer chunks alternate between the two buffers
-    bool both_busy = false;  // the previous chunk used both buffers
+    const int ew = warp - 2;
+    const int half = ew >> 2;
+    const uint32_t b0 = epi_base + (uint32_t)(ew * kEpiWarpBytes), b1 = b0 + 4096u, b2 = b0 + 8192u;
+    const uint32_t ld_bar = ld_bar0 + 8u * ew;
+    uint32_t ld_phase = 0;
+    int rot = 0;             // plain chunks staged so far (output buffer = rot % 3)
+    int last_kind = -1;      // 0 plain, 1 anything else
+    bool b1_stored = false;  // the previous chunk issued a store that reads B1
     const float a_scale = prm.a_scale ? *prm.a_scale : 1.0f;
     const float o_scale = prm.o_scale ? *prm.o_scale : 1.0f;
     const int ntiles = plan.ntiles;
     float amax = 0.f;
+    float acc[2][32];  // gate-gradient sums over the rows of a degree (kGatedBwd), per chunk
     int64_t tcount = 0;
     bool ok = true;
     for (int64_t mt = blockIdx.x; mt < tiles_m && ok; mt += gridDim.x) {
         const int64_t row0 = mt * BM + q * 32;
-        const int64_t row = row0 + lane;
-        const bool valid = row < prm.m_total;
-        float* const yrow = prm.y + row * prm.ldy;
+        const bool live = row0 < prm.m_total;  // else this warp's 32 rows lie entirely below the matrix
         for (int ti = 0; ti < ntiles; ++ti, ++tcount) {
             const Tile& t = plan.t[ti];
             const int buf = (int)(tcount & 1);
@@ -155,16 +159,30 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
             const float out_scale = 1.0f / (a_scale * prm.w_scale[t.w]);
             const float corr_scale = out_scale / kLoScale;
             const float* bias = prm.bias[t.w];
-            const uint32_t acc = tmem_base + (uint32_t)(buf * kAccCols) + ((uint32_t)(q * 32) << 16);
+            const uint32_t acc_t = tmem_base + (uint32_t)(buf * kAccCols) + ((uint32_t)(q * 32) << 16);
             const int mode = t.mode;
-#pragma unroll 1
+            const bool keep = (t.flags & kKeep) != 0 && (mode == kSilu || mode == kGated);
+            const bool fin = mode == kGatedBwd && (t.flags & kLast) != 0;
+            const int n_in = mode == kGatedBwd ? 2 : ((mode == kGated || mode == kSiluBwd) ? 1 : 0);
+#pragma unroll
             for (int c2 = 0; c2 < 2; ++c2) {
                 const int col = (half * 2 + c2) * 32;  // within the tile
+                // 1. inputs of the gated modes, fetched while the accumulator is read
+                if (live && n_in > 0) {
+                    if (lane == 0) {
+                        if (last_kind == 0 || (n_in == 2 && b1_stored)) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                        if (t.flags & kSync) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // gate tiles stored by this thread have landed
+                        mbar_expect_tx(ld_bar, (uint32_t)(n_in * 4096));
+                        tma_load_2d(b0, &map_y, (mode == kSiluBwd ? t.y_col : t.gate_col) + col, (int)row0, ld_bar);
+                        if (n_in == 2) tma_load_2d(b1, &map_y, t.y_col + col, (int)row0, ld_bar);
+                    }
+                }
+                // 2. accumulator -> registers
                 float v[32];
                 {
                     uint32_t r[32], c[32];
-                    FCB_TMEM_LD32(r, acc + (uint32_t)col);
-                    FCB_TMEM_LD32(c, acc + (uint32_t)(BN + col));
+                    FCB_TMEM_LD32(r, acc_t + (uint32_t)col);
+                    FCB_TMEM_LD32(c, acc_t + (uint32_t)(BN + col));
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     float poison = 0.f;  // becomes NaN if any value is inf or NaN (an overflowed half upstream)
 #pragma unroll
@@ -172,9 +190,9 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
                         v[i] = fmaf(__uint_as_float(c[i]), corr_scale, __uint_as_float(r[i]) * out_scale);
                         poison = fmaf(v[i], 0.f, poison);
                     }
-                    if (poison != poison && valid) *range_flag = 1;
+                    if (poison != poison && row0 + lane < prm.m_total) *range_flag = 1;
                 }
-                if (row0 >= prm.m_total) continue;  // this warp's 32 rows lie entirely below the matrix
+                if (!live) continue;
                 if (bias) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
@@ -182,30 +200,30 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
                         v[4 * i] += b.x, v[4 * i + 1] += b.y, v[4 * i + 2] += b.z, v[4 * i + 3] += b.w;
                     }
                 }
-                if (mode == kGateRaw) {
-                    if (valid) {
-#pragma unroll
-                        for (int i = 0; i < 8; ++i)
-                            st4(yrow + t.out_col + col + 4 * i, make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]));
+                // 3. staging tiles free, inputs landed
+                uint32_t st_out;
+                if (mode == kPlain) {
+                    if (lane == 0) {
+                        if (last_kind != 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                        else asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory");
                     }
-                    continue;
+                    st_out = b0 + (uint32_t)((rot % 3) * 4096);
+                    ++rot;
+                    last_kind = 0;
+                } else {
+                    if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
+                    st_out = b2;
+                    last_kind = 1;
                 }
-                const bool keep = (t.flags & kKeep) != 0 && (mode == kSilu || mode == kGated);
-                const bool fin = mode == kGatedBwd && (t.flags & kLast) != 0;  // gate gradient finalised in this tile
-                const bool two = keep || fin;
-                // a chunk stages into one buffer (float32 tile, or hi|lo tiles) unless it also keeps y or finalises a
-                // gate gradient; the stores issued earlier must have read a buffer before it is overwritten
-                if (lane == 0) {
-                    if (two || both_busy) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                    else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                if (n_in > 0) {
+                    ok = mbar_wait(ld_bar, ld_phase, abort_flag);
+                    ld_phase ^= 1u;
                 }
-                __syncwarp();
-                const uint32_t buf_a = st_base + (two ? 0u : (uint32_t)((nst & 1) * 4096));  // float32 tile / extra planes
-                const uint32_t buf_b = two ? st_base + 4096u : buf_a;                         // hi | lo tiles
-                const uint32_t st_f32 = buf_a, st_hi = buf_b, st_lo = buf_b + 2048u;
-                both_busy = two;
-                nst += two ? 0 : 1;
+                ok = __all_sync(kFull, ok);  // also orders lane 0's wait before everybody's staging writes
+                if (!ok) break;
+                // 4. the mode's arithmetic, staged for the stores
                 if (mode == kPlain || keep) {
+                    const uint32_t st_f32 = mode == kPlain ? st_out : b1;
 #pragma unroll
                     for (int i = 0; i < 8; ++i) stage_f32x4(st_f32, lane, i, v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
                 }
@@ -218,58 +236,62 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
                             for (int i = 0; i < 8; ++i) o[i] = v[8 * u + i] * sigmoid_f(v[8 * u + i]) * o_scale;
                         } else if (mode == kGated) {
                             float g[8];
-                            ld8(yrow + t.gate_col + col + 8 * u, valid, g);
+                            ld_row8(b0, lane, u, g);
 #pragma unroll
                             for (int i = 0; i < 8; ++i) o[i] = v[8 * u + i] * sigmoid_f(g[i]) * o_scale;
                         } else if (mode == kSiluBwd) {
                             float y0[8];
-                            ld8(yrow + t.y_col + col + 8 * u, valid, y0);
+                            ld_row8(b0, lane, u, y0);
 #pragma unroll
                             for (int i = 0; i < 8; ++i) {
                                 const float sg = sigmoid_f(y0[i]);
                                 o[i] = v[8 * u + i] * sg * (1.f + y0[i] * (1.f - sg)) * o_scale;
                             }
                         } else {  // kGatedBwd
-                            float g[8], yr[8], a[8];
-                            ld8(yrow + t.gate_col + col + 8 * u, valid, g);
-                            ld8(yrow + t.y_col + col + 8 * u, valid, yr);
-                            float* const gp = prm.gacc + row * prm.ldg + t.gate_col + col + 8 * u;
-                            ld8(gp, valid && !(t.flags & kFirst), a);
+                            float g[8], yr[8];
+                            ld_row8(b0, lane, u, g);
+                            ld_row8(b1, lane, u, yr);
 #pragma unroll
                             for (int i = 0; i < 8; ++i) {
                                 g[i] = sigmoid_f(g[i]);
                                 o[i] = v[8 * u + i] * g[i] * o_scale;
-                                a[i] = fmaf(v[8 * u + i], yr[i], a[i]);
-                            }
-                            if (fin) {
-#pragma unroll
-                                for (int i = 0; i < 8; ++i) a[i] = a[i] * g[i] * (1.f - g[i]) * o_scale;
-                                stage_split8(st_f32, st_f32 + 2048u, lane, u, a, amax);
-                            } else if (valid) {
-                                st4(gp, make_float4(a[0], a[1], a[2], a[3]));
-                                st4(gp + 4, make_float4(a[4], a[5], a[6], a[7]));
+                                const float prev = (t.flags & kFirst) ? 0.f : acc[c2][8 * u + i];
+                                acc[c2][8 * u + i] = fmaf(v[8 * u + i], yr[i], prev);
+                                if (fin) acc[c2][8 * u + i] *= g[i] * (1.f - g[i]) * o_scale;
                             }
                         }
-                        stage_split8(st_hi, st_lo, lane, u, o, amax);
+                        stage_split8(st_out, st_out + 2048u, lane, u, o, amax);
+                    }
+                    if (fin) {  // every thread has read its y row out of B1: stage the finished gate gradient there
+                        __syncwarp();
+#pragma unroll
+                        for (int u = 0; u < 4; ++u) {
+                            float a[8];
+#pragma unroll
+                            for (int i = 0; i < 8; ++i) a[i] = acc[c2][8 * u + i];
+                            stage_split8(b1, b1 + 2048u, lane, u, a, amax);
+                        }
                     }
                 }
                 asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                 __syncwarp();
                 if (lane == 0) {
                     if (mode == kPlain) {
-                        tma_store_2d(&map_y, st_f32, t.out_col + col, (int)row0);
+                        tma_store_2d(&map_y, st_out, t.out_col + col, (int)row0);
                     } else {
-                        if (keep) tma_store_2d(&map_y, st_f32, t.y_col + col, (int)row0);
-                        tma_store_2d(&map_ohi, st_hi, t.out_col + col, (int)row0);
-                        tma_store_2d(&map_olo, st_lo, t.out_col + col, (int)row0);
+                        if (keep) tma_store_2d(&map_y, b1, t.y_col + col, (int)row0);
+                        tma_store_2d(&map_ohi, st_out, t.out_col + col, (int)row0);
+                        tma_store_2d(&map_olo, st_out + 2048u, t.out_col + col, (int)row0);
                         if (fin) {
-                            tma_store_2d(&map_ohi, st_f32, t.gate_col + col, (int)row0);
-                            tma_store_2d(&map_olo, st_f32 + 2048u, t.gate_col + col, (int)row0);
+                            tma_store_2d(&map_ohi, b1, t.gate_col + col, (int)row0);
+                            tma_store_2d(&map_olo, b1 + 2048u, t.gate_col + col, (int)row0);
                         }
                     }
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
+                b1_stored = keep || fin;
             }
+            if (!ok) break;
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             mbar_arrive(tempty0 + 8u * buf);  // 256 arrivals hand the accumulator back to the MMA thread
         }
@@ -291,11 +313,12 @@ __global__ void __launch_bounds__(kThreads, 1)
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t epi_base = base + S * kStageBytes;
     const uint32_t bar_base = epi_base + kEpiWarps * kEpiWarpBytes;
-    // barrier block: full[S] | empty[S] | tmem_full[2] | tmem_empty[2] | tmem slot | abort flag | range flag
+    // barrier block: full[S] | empty[S] | tmem_full[2] | tmem_empty[2] | tmem slot, abort flag, range flag, pad | ld[8]
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
     auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * S + b); };
     auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * S + 2 + b); };
+    auto ld_bar = [&](int w) { return bar_base + 8u * (2 * S + 6 + w); };  // one per epilogue warp, after the flag words
     uint8_t* const bar_generic = smem_raw + (bar_base - smem_u32(smem_raw));
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_generic + 8 * (2 * S + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_generic + 8 * (2 * S + 4) + 4);
@@ -314,6 +337,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             mbar_init(tfull_bar(b), 1);
             mbar_init(tempty_bar(b), 32 * kEpiWarps);
         }
+        for (int w = 0; w < kEpiWarps; ++w) mbar_init(ld_bar(w), 1);
         *abort_flag = 0;
         *range_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -391,9 +415,9 @@ __global__ void __launch_bounds__(kThreads, 1)
                 }
             }
         }
-    } else if (warp >= 4) {
-        epilogue(map_y, map_ohi, map_olo, plan, prm, tiles_m, tmem_base, epi_base, tfull_bar(0), tempty_bar(0), abort_flag,
-                 range_flag);
+    } else {
+        epilogue(map_y, map_ohi, map_olo, plan, prm, tiles_m, tmem_base, epi_base, tfull_bar(0), tempty_bar(0), ld_bar(0),
+                 abort_flag, range_flag);
     }
 
     __syncwarp();
@@ -447,8 +471,7 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
                                      const void* const* w_lo, const int64_t* w_rows, const int64_t* w_cols,
                                      const float* w_scale, const float* const* bias, const int32_t* tiles, int32_t num_tiles,
                                      float* y, int64_t ldy, int64_t y_cols, void* o_hi, void* o_lo, int64_t ldo, int64_t o_cols,
-                                     float* gacc, int64_t ldg, const float* a_scale, const float* o_scale, int64_t m,
-                                     int32_t* status, void* stream) {
+                                     const float* a_scale, const float* o_scale, int64_t m, int32_t* status, void* stream) {
     using namespace fused;
     if (!a_hi || !a_lo || !w_hi || !w_lo || !w_rows || !w_cols || !w_scale || !tiles || !y || m < 0) return FCB200_EINVAL;
     if (num_tiles <= 0 || num_tiles > kMaxTiles) return FCB200_ERANGE;
@@ -458,7 +481,6 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
         if (!o_hi || !o_lo || ldo % 8 || ldo < o_cols) return FCB200_EINVAL;
         if (!aligned16(o_hi) || !aligned16(o_lo)) return FCB200_EALIGN;
     }
-    if (gacc && (ldg % 4 || !aligned16(gacc))) return FCB200_EINVAL;
     Plan plan{};
     Params prm{};
     plan.ntiles = num_tiles;
@@ -471,7 +493,7 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
         if (t.w < 0 || t.w > 2 || !w_hi[t.w] || !w_lo[t.w]) return FCB200_EINVAL;
         if (t.k <= 0 || t.k % BK || t.k > w_cols[t.w] || t.a_col < 0 || t.a_col % 8 || t.a_col + t.k > a_cols) return FCB200_EINVAL;
         if (t.w_row < 0 || t.w_row % BN || t.w_row + BN > w_rows[t.w]) return FCB200_EINVAL;
-        if (t.mode < kPlain || t.mode > kGatedBwd || t.out_col < 0 || t.out_col % 8) return FCB200_EINVAL;
+        if (t.mode < kPlain || t.mode > kGatedBwd || t.mode == kGateRaw || t.out_col < 0 || t.out_col % 8) return FCB200_EINVAL;
         const bool split = t.mode >= kSilu;
         if (split && (!o_hi || t.out_col + BN > o_cols)) return FCB200_EINVAL;
         if (!split && t.out_col + BN > y_cols) return FCB200_EINVAL;
@@ -479,7 +501,7 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
         if (reads_gate && (t.gate_col < 0 || t.gate_col % 4 || t.gate_col + BN > y_cols)) return FCB200_EINVAL;
         const bool uses_y = t.mode == kSiluBwd || t.mode == kGatedBwd || ((t.mode == kSilu || t.mode == kGated) && (t.flags & kKeep));
         if (uses_y && (t.y_col < 0 || t.y_col % 4 || t.y_col + BN > y_cols)) return FCB200_EINVAL;
-        if (t.mode == kGatedBwd && (!gacc || t.gate_col + BN > ldg || t.gate_col + BN > o_cols)) return FCB200_EINVAL;
+        if (t.mode == kGatedBwd && t.gate_col + BN > o_cols) return FCB200_EINVAL;
         used[t.w] = true;
     }
     if (m == 0) return FCB200_OK;
@@ -512,7 +534,7 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
     } else {
         moh = mah, mol = mal;  // no split-output tile exists (checked above)
     }
-    prm.y = y, prm.ldy = ldy, prm.gacc = gacc, prm.ldg = ldg, prm.a_scale = a_scale, prm.o_scale = o_scale;
+    prm.y = y, prm.ldy = ldy, prm.a_scale = a_scale, prm.o_scale = o_scale;
     prm.m_total = m, prm.status = status;
     static bool attr_done[64] = {};
     if (const int arc = ensure_dynamic_smem(so2_conv_fused_kernel, kSmemBytes, attr_done)) return arc;

@@ -536,21 +536,20 @@ def gemm_f16x2_presplit_(a_hi: Tensor, a_lo: Tensor, w_hi: Tensor, w_lo: Tensor,
 
 # epilogue modes and flags of so2_conv_fused_ (csrc/so2_conv_fused.cu)
 CONV_PLAIN, CONV_GATE_RAW, CONV_SILU, CONV_GATED, CONV_SILU_BWD, CONV_GATED_BWD = range(6)
-CONV_FIRST, CONV_LAST, CONV_KEEP = 1, 2, 4
+CONV_FIRST, CONV_LAST, CONV_KEEP, CONV_SYNC = 1, 2, 4, 8
 CONV_MAX_TILES = 40
 
 
-@_op("so2_conv_fused", ("y", "o_hi", "o_lo", "gacc", "status"))
+@_op("so2_conv_fused", ("y", "o_hi", "o_lo", "status"))
 def so2_conv_fused_(a_hi: Tensor, a_lo: Tensor, w_hi: List[Tensor], w_lo: List[Tensor], w_scale: List[float],
                     bias0: Optional[Tensor], tiles: List[int], y: Tensor, o_hi: Optional[Tensor], o_lo: Optional[Tensor],
-                    gacc: Optional[Tensor], a_scale: Optional[Tensor], o_scale: Optional[Tensor], status: Tensor,
-                    label: str = "") -> None:
+                    a_scale: Optional[Tensor], o_scale: Optional[Tensor], status: Tensor, label: str = "") -> None:
     """One launch for all m-blocks of an SO(2) convolution with the gate (or its derivative) in the epilogue.
 
     ``a_hi/a_lo`` [E, Ka] are the input planes, ``w_*`` the (up to three) half-split weight matrices, ``tiles`` a flat
     list of 9 integers per 128-column output tile (a_col, k, w, w_row, out_col, mode, y_col, gate_col, flags).  ``y``
     [E, >=gates] float32 receives the float32 modes and the raw gate scalars and is read by the gated modes; ``o_hi/o_lo``
-    receive the split modes; ``gacc`` is float32 scratch [E, >=gates] for the gate-gradient sums."""
+    receive the split modes."""
     for t in (a_hi, a_lo):
         if not t.is_cuda or t.dtype != torch.float16 or t.dim() != 2 or t.stride(1) != 1 or t.shape != a_hi.shape \
                 or t.stride(0) != a_hi.stride(0):
@@ -564,8 +563,6 @@ def so2_conv_fused_(a_hi: Tensor, a_lo: Tensor, w_hi: List[Tensor], w_lo: List[T
             if not t.is_cuda or t.dtype != torch.float16 or t.dim() != 2 or t.stride(1) != 1 or t.shape != o_hi.shape \
                     or t.stride(0) != o_hi.stride(0) or t.shape[0] != a_hi.shape[0]:
                 raise _lib.FairchemB200Error("so2_conv_fused: need 2-D float16 CUDA output planes of one shape and row stride")
-    if gacc is not None and (not gacc.is_cuda or gacc.dtype != torch.float32 or gacc.dim() != 2 or gacc.stride(1) != 1):
-        raise _lib.FairchemB200Error("so2_conv_fused: need a 2-D float32 CUDA scratch")
     if len(w_hi) != len(w_lo) or len(w_hi) != len(w_scale) or not 1 <= len(w_hi) <= 3 or len(tiles) % 9:
         raise _lib.FairchemB200Error("so2_conv_fused: malformed weight or tile lists")
     for t in list(w_hi) + list(w_lo):
@@ -586,8 +583,7 @@ def so2_conv_fused_(a_hi: Tensor, a_lo: Tensor, w_hi: List[Tensor], w_lo: List[T
     _launch("so2_conv_fused" + label, "fcb200_so2_conv_fused",
             (_p(a_hi), _p(a_lo), a_hi.stride(0), a_hi.shape[1], whi, wlo, rows, cols, scales, biases, tl, nt,
              _p(y), y.stride(0), y.shape[1], _p(o_hi), _p(o_lo), 0 if o_hi is None else o_hi.stride(0),
-             0 if o_hi is None else o_hi.shape[1], _p(gacc), 0 if gacc is None else gacc.stride(0), _p(a_scale), _p(o_scale), m,
-             _p(status), _stream()), nbytes=nbytes, flops=flops)
+             0 if o_hi is None else o_hi.shape[1], _p(a_scale), _p(o_scale), m, _p(status), _stream()), nbytes=nbytes, flops=flops)
 
 
 def split_f16(w: Tensor):

@@ -340,23 +340,23 @@ int fcb200_gemm_f16x2_presplit(const void* a_hi, const void* a_lo, int64_t lda, 
  *   w_scale      HOST array of 3 floats; bias: HOST array of 3 device pointers (or NULL entries / NULL array)
  *   tiles        HOST array, 9 int32 per tile: a_col, k, w, w_row, out_col, mode, y_col, gate_col, flags
  *                mode 0  float32 tile -> y[:, out_col..]
- *                mode 1  float32 tile -> y[:, out_col..] with plain stores (gate scalars; must precede mode-3 tiles)
  *                mode 2  planes[:, out_col..] = split(v * sigmoid(v));                    flag 4: also y[:, y_col..] = v
  *                mode 3  planes[:, out_col..] = split(v * sigmoid(y[:, gate_col..]));     flag 4: also y[:, y_col..] = v
  *                mode 4  planes[:, out_col..] = split(v * silu'(y[:, y_col..]))
  *                mode 5  planes[:, out_col..] = split(v * sigmoid(y[:, gate_col..])) and the gate gradient
- *                        sum_rows v * y[:, y_col..] accumulated in gacc[:, gate_col..] (flag 1: first row of the
+ *                        sum_rows v * y[:, y_col..] summed over CONSECUTIVE tiles (flag 1: first row of the
  *                        degree, flag 2: last row -> planes[:, gate_col..] = split(sum * s * (1 - s)))
+ *                flag 8 on the first mode-3 tile after the mode-0 tiles that wrote the gate scalars it reads
  *   y            [M, y_cols] float32, row stride ldy; o_hi/o_lo [M, o_cols] half planes, row stride ldo, written
- *                times *o_scale (device pointers to powers of two, NULL = 1); gacc [M, ldg] float32 SCRATCH
+ *                times *o_scale (device pointers to powers of two, NULL = 1)
  *   status       as in fcb200_gemm_f16x2_presplit
  * At most 40 tiles; every k a multiple of 32, w_row a multiple of 128.
  */
 int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t lda, int64_t a_cols, const void* const* w_hi,
                           const void* const* w_lo, const int64_t* w_rows, const int64_t* w_cols, const float* w_scale,
                           const float* const* bias, const int32_t* tiles, int32_t num_tiles, float* y, int64_t ldy,
-                          int64_t y_cols, void* o_hi, void* o_lo, int64_t ldo, int64_t o_cols, float* gacc, int64_t ldg,
-                          const float* a_scale, const float* o_scale, int64_t m, int32_t* status, void* stream);
+                          int64_t y_cols, void* o_hi, void* o_lo, int64_t ldo, int64_t o_cols, const float* a_scale,
+                          const float* o_scale, int64_t m, int32_t* status, void* stream);
 
 /*
  * The four kernels whose output is consumed only by an SO(2) contraction, writing that output as the
