@@ -526,14 +526,41 @@ def _radial_forward(rad: RadialMLP, tables, gauss_c, zs, zt, nb: int, keep: Opti
         st1, st2 = torch.empty(e, 2, dtype=torch.float32, device=dev), torch.empty(e, 2, dtype=torch.float32, device=dev)
     if from_kept and keep is not None and keep.out is not None:
         return keep.out[sl], (pre1, st1, pre2, st2)
+    out = keep.out[sl] if keep is not None and keep.out is not None else None
+    if _presplit() and _GemmState.fused_conv and pre1.shape[1] == 128:
+        # the hidden activations only feed the next Linear: written as half planes, read by the tensor cores directly
+        h = _new_operand(e, pre1.shape[1], dev)
+        if not (from_kept and keep is not None):
+            _dense(gauss_c, w0.weight.detach()[:, :nb], w0.bias.detach(), out=pre1)
+            ops.radial_act_fwd_h_.raw(pre1, tables[0], tables[1], zs, zt, ln1.weight.detach(), ln1.bias.detach(), float(ln1.eps),
+                                      h[0], h[1], st1)
+            _contract(h, w1.weight.detach(), w1.bias.detach(), pre2, None)
+        ops.radial_act_fwd_h_.raw(pre2, None, None, None, None, ln2.weight.detach(), ln2.bias.detach(), float(ln2.eps), h[0], h[1], st2)
+        if out is None:
+            out = torch.empty(e, w2.weight.shape[0], dtype=torch.float32, device=dev)
+        return _fused_linear(h, w2.weight.detach(), w2.bias.detach(), out, "_radial_out"), (pre1, st1, pre2, st2)
     h = torch.empty_like(pre1)
     if not (from_kept and keep is not None):
         _dense(gauss_c, w0.weight.detach()[:, :nb], w0.bias.detach(), out=pre1)
         ops.radial_act_fwd_.raw(pre1, tables[0], tables[1], zs, zt, ln1.weight.detach(), ln1.bias.detach(), float(ln1.eps), h, st1)
         _dense(h, w1.weight.detach(), w1.bias.detach(), out=pre2)
     ops.radial_act_fwd_.raw(pre2, None, None, None, None, ln2.weight.detach(), ln2.bias.detach(), float(ln2.eps), h, st2)
-    out = keep.out[sl] if keep is not None and keep.out is not None else None
     return _dense(h, w2.weight.detach(), w2.bias.detach(), out=out), (pre1, st1, pre2, st2)
+
+
+def _fused_linear(x, w: torch.Tensor, bias, out: torch.Tensor, label: str = "_linear"):
+    """out = x @ w^T + bias for pre-split x [E, K] through the row-tile-major fused kernel (eight epilogue warps): the
+    form for wide outputs over a short K, where storing the result is the bound.  N a multiple of 128, at most 40 tiles."""
+    n, k = w.shape
+    if n % 128 or n // 128 > ops.CONV_MAX_TILES or k % 32:
+        _contract(x, w, bias, out, None)
+        return out
+    hi, lo, sc = _split16(w)
+    tiles = []
+    for r0 in range(0, n, 128):
+        tiles += [0, k, 0, r0, r0, ops.CONV_PLAIN, 0, 0, 0]
+    ops.so2_conv_fused_.raw(x[0], x[1], [hi], [lo], [sc], bias, tiles, out, None, None, None, None, _status(out.device), label)
+    return out
 
 
 def _radial_backward(rad: RadialMLP, tables, grad_rad, acts, zs, zt, nb: int, out):

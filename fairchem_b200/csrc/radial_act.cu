@@ -1,6 +1,8 @@
 // Hidden-layer activation of the radial MLP, fused: add the two per-element embedding tables, LayerNorm
 // over the row, SiLU -- one pass over a [E, W] tensor (W = 128), one warp per row, a lane owns a float4.
 // HBM-bound: reads 4W (+ two L2-resident table rows), writes 4W + 8 bytes per edge.
+#include <cuda_fp16.h>
+
 #include "common.cuh"
 
 namespace fcb200 {
@@ -17,11 +19,14 @@ __device__ __forceinline__ float4 load_row(const float* __restrict__ pre, const 
     return y;
 }
 
+// Out = OutF32 (float32 rows) or OutSplit (the half-precision hi / lo planes the next contraction reads directly)
+template <class Out>
 __global__ void __launch_bounds__(kActWarps* kWarp)
     radial_act_fwd_kernel(const float* __restrict__ pre, const float* __restrict__ ts, const float* __restrict__ tt,
                           const int32_t* __restrict__ zs, const int32_t* __restrict__ zt, const float* __restrict__ gamma,
-                          const float* __restrict__ beta, float eps, float* __restrict__ out, float* __restrict__ stats,
+                          const float* __restrict__ beta, float eps, Out out, float* __restrict__ stats,
                           int64_t num_edges, int w) {
+    out.load_scale(nullptr);
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (int64_t)blockIdx.x * kActWarps + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kActWarps;
@@ -36,7 +41,7 @@ __global__ void __launch_bounds__(kActWarps* kWarp)
         const float rstd = rsqrtf(var + eps);
         float4 v = make_float4(fmaf(d.x * rstd, g.x, b.x), fmaf(d.y * rstd, g.y, b.y), fmaf(d.z * rstd, g.z, b.z),
                                fmaf(d.w * rstd, g.w, b.w));
-        st4(out + e * w + c, make_float4(v.x * sigmoid_f(v.x), v.y * sigmoid_f(v.y), v.z * sigmoid_f(v.z), v.w * sigmoid_f(v.w)));
+        out.st(e * w + c, make_float4(v.x * sigmoid_f(v.x), v.y * sigmoid_f(v.y), v.z * sigmoid_f(v.z), v.w * sigmoid_f(v.w)));
         if (lane == 0) {
             stats[e * 2 + 0] = mean;
             stats[e * 2 + 1] = rstd;
@@ -95,8 +100,23 @@ int fcb200_radial_act_fwd(const float* pre, const float* table_src, const float*
         (table_tgt && !aligned16(table_tgt)))
         return FCB200_EALIGN;
     if (num_edges == 0) return FCB200_OK;
-    radial_act_fwd_kernel<<<warp_grid(num_edges, kActWarps), kActWarps * kWarp, 0, static_cast<cudaStream_t>(stream)>>>(
-        pre, table_src, table_tgt, z_src, z_tgt, ln_weight, ln_bias, eps, out, stats, num_edges, width);
+    radial_act_fwd_kernel<OutF32><<<warp_grid(num_edges, kActWarps), kActWarps * kWarp, 0, static_cast<cudaStream_t>(stream)>>>(
+        pre, table_src, table_tgt, z_src, z_tgt, ln_weight, ln_bias, eps, OutF32{out}, stats, num_edges, width);
+    return launch_status();
+}
+
+int fcb200_radial_act_fwd_h(const float* pre, const float* table_src, const float* table_tgt, const int32_t* z_src,
+                            const int32_t* z_tgt, const float* ln_weight, const float* ln_bias, float eps, void* out_hi,
+                            void* out_lo, float* stats, int64_t num_edges, int32_t width, void* stream) {
+    if (!pre || !ln_weight || !ln_bias || !out_hi || !out_lo || !stats || num_edges < 0 || width != 128) return FCB200_EINVAL;
+    if ((table_src && !z_src) || (table_tgt && !z_tgt)) return FCB200_EINVAL;
+    if (!aligned16(pre) || !aligned16(out_hi) || !aligned16(out_lo) || !aligned16(ln_weight) || !aligned16(ln_bias) ||
+        (table_src && !aligned16(table_src)) || (table_tgt && !aligned16(table_tgt)))
+        return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    radial_act_fwd_kernel<OutSplit><<<warp_grid(num_edges, kActWarps), kActWarps * kWarp, 0, static_cast<cudaStream_t>(stream)>>>(
+        pre, table_src, table_tgt, z_src, z_tgt, ln_weight, ln_bias, eps,
+        OutSplit{static_cast<__half*>(out_hi), static_cast<__half*>(out_lo), 1.0f}, stats, num_edges, width);
     return launch_status();
 }
 

@@ -109,6 +109,54 @@ __device__ __forceinline__ void stage_f32x4(uint32_t base, int lane, int v4, flo
 }
 
 
+
+// ---- CTA pairs (cta_group::2): two CTAs of a cluster share a 256-row tile and each holds half of the B operand ----
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t bar) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx_cluster(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.release.cluster.shared::cluster.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+// TMA load whose completion is signalled on a barrier that may live in the peer CTA (no multicast: the data lands in
+// this CTA's own shared memory only)
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+        : "memory");
+}
+// arrive on the barrier at this offset in both CTAs of the pair once the MMAs issued so far have completed
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(bar),
+                 "h"((uint16_t)3)
+                 : "memory");
+}
+// instruction descriptor of the pair MMA: M = 256 (128 rows in each CTA), N columns
+constexpr uint32_t instr_desc_pair(int n) { return (1u << 4) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(256 >> 4) << 24); }
+template <int N>
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, {%5, %6, %7, %8, %9, %10, %11, %12}, p;\n\t}"
+        ::"r"(tmem_d), "l"(da), "l"(db), "r"(instr_desc_pair(N)), "r"(accumulate), "r"(0u), "r"(0u), "r"(0u), "r"(0u), "r"(0u),
+          "r"(0u), "r"(0u), "r"(0u)
+        : "memory");
+}
+
 // own row (`lane`) of a 32 x 32 float32 tile that TMA landed with the 128-byte swizzle: values [8u, 8u + 8)
 __device__ __forceinline__ void ld_row8(uint32_t base, int lane, int u, float (&o)[8]) {
 #pragma unroll
@@ -124,10 +172,16 @@ __device__ __forceinline__ void ld_row8(uint32_t base, int lane, int u, float (&
 // global reads are whole lines and each thread then takes its own row from shared memory), B2 stages the output;
 // B1 doubles as the staging tile of a kept y row or of a finished gate gradient.  Launches of plain tiles rotate
 // the output over all three.
+// PAIR: the CTA is one of a pair that shares 256-row tiles; `unit` is the tile stride owner (CTA or pair index),
+// `units` their number, `row_off` this CTA's first row inside a tile, and `tempty0` a shared::cluster address of the
+// leader's accumulator-free barriers.
+template <bool PAIR>
 __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtensorMap& map_ohi, const CUtensorMap& map_olo,
                                          const Plan& plan, const Params& prm, int64_t tiles_m, uint32_t tmem_base,
                                          uint32_t epi_base, uint32_t tfull0, uint32_t tempty0, uint32_t ld_bar0,
-                                         volatile int* abort_flag, volatile int* range_flag) {
+                                         volatile int* abort_flag, volatile int* range_flag, int64_t unit, int64_t units,
+                                         int row_off) {
+    constexpr int kTileRows = PAIR ? 2 * BM : BM;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int q = warp & 3;
     const int ew = warp - 2;
@@ -145,8 +199,8 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
     float acc[2][32];  // gate-gradient sums over the rows of a degree (kGatedBwd), per chunk
     int64_t tcount = 0;
     bool ok = true;
-    for (int64_t mt = blockIdx.x; mt < tiles_m && ok; mt += gridDim.x) {
-        const int64_t row0 = mt * BM + q * 32;
+    for (int64_t mt = unit; mt < tiles_m && ok; mt += units) {
+        const int64_t row0 = mt * kTileRows + row_off + q * 32;
         const bool live = row0 < prm.m_total;  // else this warp's 32 rows lie entirely below the matrix
         for (int ti = 0; ti < ntiles; ++ti, ++tcount) {
             const Tile& t = plan.t[ti];
@@ -293,7 +347,9 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
             }
             if (!ok) break;
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            mbar_arrive(tempty0 + 8u * buf);  // 256 arrivals hand the accumulator back to the MMA thread
+            // 256 arrivals (per CTA) hand the accumulator back to the MMA thread
+            if (PAIR) mbar_arrive_cluster(tempty0 + 8u * buf);
+            else mbar_arrive(tempty0 + 8u * buf);
         }
     }
     if (!(amax <= kHalfMax)) *range_flag = 1;  // also catches NaN
@@ -416,8 +472,8 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         }
     } else {
-        epilogue(map_y, map_ohi, map_olo, plan, prm, tiles_m, tmem_base, epi_base, tfull_bar(0), tempty_bar(0), ld_bar(0),
-                 abort_flag, range_flag);
+        epilogue<false>(map_y, map_ohi, map_olo, plan, prm, tiles_m, tmem_base, epi_base, tfull_bar(0), tempty_bar(0), ld_bar(0),
+                        abort_flag, range_flag, blockIdx.x, gridDim.x, 0);
     }
 
     __syncwarp();
@@ -433,6 +489,161 @@ __global__ void __launch_bounds__(kThreads, 1)
     }
 }
 
+
+// ---------------------------------------------------------------------------------------------------------------
+// The same schedule on CTA pairs.  Two CTAs of a cluster own a 256-edge row tile (128 rows each); one thread of
+// the leader CTA issues tcgen05.mma.cta_group::2 (M = 256), which reads each CTA's A rows from that CTA's shared
+// memory and the B operand half from each: the 128-wide MMAs of a single CTA are bound by shared-memory bandwidth,
+// and the pair halves the B bytes each CTA streams per MMA.  Per stage a CTA holds
+//     A_hi | A_lo (its 128 rows) | X = W_hi[n0, n0+128) in the leader, W_lo[n0, n0+128) in the peer
+//                                | Y = W_hi[n0, n0+64) in the leader, W_hi[n0+64, n0+128) in the peer
+// so that  a_hi x [X_leader ; X_peer] = [a_hi w_hi | a_hi w_lo]  (one N = 256 MMA into main | correction) and
+//          a_lo x [Y_leader ; Y_peer] = a_lo w_hi                (one N = 128 MMA into the correction columns).
+// TMA loads carry no multicast: every CTA fetches what lands in its own shared memory; their completion is counted
+// on the leader's barrier.  tcgen05.commit with the pair mask frees a stage / publishes an accumulator in both CTAs.
+// ---------------------------------------------------------------------------------------------------------------
+constexpr int kPairStageBytes = 3 * kHalfTile + kHalfTile / 2;  // 28 KiB
+constexpr int kPairStages = 4;
+constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kEpiWarps * kEpiWarpBytes + 1024 + 256;
+
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+    so2_conv_pair_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
+                         const __grid_constant__ CUtensorMap map_whi0, const __grid_constant__ CUtensorMap map_wlo0,
+                         const __grid_constant__ CUtensorMap map_whi1, const __grid_constant__ CUtensorMap map_wlo1,
+                         const __grid_constant__ CUtensorMap map_whi2, const __grid_constant__ CUtensorMap map_wlo2,
+                         const __grid_constant__ CUtensorMap map_wy0, const __grid_constant__ CUtensorMap map_wy1,
+                         const __grid_constant__ CUtensorMap map_wy2, const __grid_constant__ CUtensorMap map_y,
+                         const __grid_constant__ CUtensorMap map_ohi, const __grid_constant__ CUtensorMap map_olo,
+                         const __grid_constant__ Plan plan, const __grid_constant__ Params prm, int64_t tiles_m) {
+    constexpr int S = kPairStages;
+    extern __shared__ uint8_t smem_raw[];
+    const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const uint32_t epi_base = base + S * kPairStageBytes;
+    const uint32_t bar_base = epi_base + kEpiWarps * kEpiWarpBytes;
+    // barrier block as in the single-CTA kernel; full[] and tmem_empty[] are used in the leader only
+    auto full_bar = [&](int s) { return bar_base + 8u * s; };
+    auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
+    auto tfull_bar = [&](int b) { return bar_base + 8u * (2 * S + b); };
+    auto tempty_bar = [&](int b) { return bar_base + 8u * (2 * S + 2 + b); };
+    auto ld_bar = [&](int w) { return bar_base + 8u * (2 * S + 6 + w); };
+    uint8_t* const bar_generic = smem_raw + (bar_base - smem_u32(smem_raw));
+    volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_generic + 8 * (2 * S + 4));
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_generic + 8 * (2 * S + 4) + 4);
+    volatile int* range_flag = reinterpret_cast<volatile int*>(bar_generic + 8 * (2 * S + 4) + 8);
+    // a stage: A_hi | A_lo | X | Y
+    auto part_addr = [&](int s, int which) { return base + s * kPairStageBytes + which * kHalfTile; };
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int ntiles = plan.ntiles;
+    const uint32_t rank = cluster_ctarank();
+    const bool leader = rank == 0;
+    const int64_t pair = blockIdx.x >> 1, pairs = gridDim.x >> 1;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S; ++s) {
+            mbar_init(full_bar(s), 2);   // one arrive.expect_tx from each CTA's producer
+            mbar_init(empty_bar(s), 1);  // the leader's commit, delivered to both CTAs
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(tfull_bar(b), 1);
+            mbar_init(tempty_bar(b), 2 * 32 * kEpiWarps);  // both CTAs' epilogue threads
+        }
+        for (int w = 0; w < kEpiWarps; ++w) mbar_init(ld_bar(w), 1);
+        *abort_flag = 0;
+        *range_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32((const void*)tmem_slot)),
+                     "r"((uint32_t)kTmemCols)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    cluster_sync_all();  // both CTAs' barriers are initialised before either signals the other
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = *tmem_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int64_t it = 0;
+            bool ok = true;
+            for (int64_t mt = pair; mt < tiles_m && ok; mt += pairs) {
+                const int row = (int)(mt * 2 * BM + rank * BM);
+                for (int ti = 0; ti < ntiles && ok; ++ti) {
+                    const Tile& t = plan.t[ti];
+                    const CUtensorMap* wx = leader ? (t.w == 0 ? &map_whi0 : (t.w == 1 ? &map_whi1 : &map_whi2))
+                                                   : (t.w == 0 ? &map_wlo0 : (t.w == 1 ? &map_wlo1 : &map_wlo2));
+                    const CUtensorMap* wy = t.w == 0 ? &map_wy0 : (t.w == 1 ? &map_wy1 : &map_wy2);
+                    const int num_kb = t.k / BK;
+                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                        const int s = (int)(it % S);
+                        const uint32_t ph = (uint32_t)((it / S) & 1);
+                        ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag);
+                        if (!ok) break;
+                        const uint32_t lead_full = map_to_cta(full_bar(s), 0);
+                        mbar_expect_tx_cluster(lead_full, kPairStageBytes);
+                        tma_load_2d_pair(part_addr(s, 0), &map_ahi, t.a_col + kb * BK, row, lead_full);
+                        tma_load_2d_pair(part_addr(s, 1), &map_alo, t.a_col + kb * BK, row, lead_full);
+                        tma_load_2d_pair(part_addr(s, 2), wx, kb * BK, t.w_row, lead_full);
+                        tma_load_2d_pair(part_addr(s, 3), wy, kb * BK, t.w_row + (int)rank * (BN / 2), lead_full);
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && leader) {
+            int64_t it = 0, tcount = 0;
+            bool ok = true;
+            for (int64_t mt = pair; mt < tiles_m && ok; mt += pairs) {
+                for (int ti = 0; ti < ntiles && ok; ++ti, ++tcount) {
+                    const int num_kb = plan.t[ti].k / BK;
+                    const int buf = (int)(tcount & 1);
+                    const uint32_t use = (uint32_t)((tcount >> 1) & 1);
+                    ok = mbar_wait(tempty_bar(buf), use ^ 1u, abort_flag);  // both epilogues have drained this accumulator
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t acc = tmem_base + (uint32_t)(buf * kAccCols);
+                    for (int kb = 0; kb < num_kb; ++kb, ++it) {
+                        const int s = (int)(it % S);
+                        const uint32_t ph = (uint32_t)((it / S) & 1);
+                        ok = mbar_wait(full_bar(s), ph, abort_flag);  // both CTAs' tiles have landed
+                        if (!ok) break;
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const uint64_t da_hi = smem_desc64(part_addr(s, 0)), da_lo = smem_desc64(part_addr(s, 1));
+                        const uint64_t dx = smem_desc64(part_addr(s, 2)), dy = smem_desc64(part_addr(s, 3));
+#pragma unroll
+                        for (int j = 0; j < BK / 16; ++j) {
+                            const uint64_t adv = (uint64_t)(j * 2);
+                            const uint32_t first = (kb > 0 || j > 0) ? 1u : 0u;
+                            umma_f16_pair<2 * BN>(acc, da_hi + adv, dx + adv, first);
+                            umma_f16_pair<BN>(acc + BN, da_lo + adv, dy + adv, 1u);
+                        }
+                        umma_commit_pair(empty_bar(s));
+                    }
+                    if (ok) umma_commit_pair(tfull_bar(buf));
+                }
+            }
+        }
+    } else {
+        epilogue<true>(map_y, map_ohi, map_olo, plan, prm, tiles_m, tmem_base, epi_base, tfull_bar(0), map_to_cta(tempty_bar(0), 0),
+                       ld_bar(0), abort_flag, range_flag, pair, pairs, (int)rank * BM);
+    }
+
+    __syncwarp();
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    cluster_sync_all();  // neither CTA leaves, nor frees tensor memory, while its peer can still reach it
+    if (warp == 0) {
+        __syncwarp();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)kTmemCols) : "memory");
+    }
+    if (threadIdx.x == 0 && prm.status) {
+        if (*abort_flag) atomicExch(prm.status, 1);
+        else if (*range_flag) atomicCAS(prm.status, 0, 2);
+    }
+}
 
 // 2-D row-major half matrix [rows, cols], row stride ld elements; box = 32 columns x box_rows rows, 64-byte swizzle
 static int map_half(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
@@ -462,6 +673,33 @@ static int map_f32(CUtensorMap* map, const float* ptr, int64_t rows, int64_t col
     return r == CUDA_SUCCESS ? FCB200_OK : FCB200_EINVAL;
 }
 
+// How many CTA pairs the device runs at once with this kernel's resources (cached per device); 0 on failure.
+static int pair_capacity() {
+    static int cap[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return 0;
+    const bool cached = dev >= 0 && dev < 64;
+    if (cached && cap[dev] > 0) return cap[dev];
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * 74, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = kPairSmemBytes;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, so2_conv_pair_kernel, &cfg) != cudaSuccess || n <= 0) {
+        cudaGetLastError();
+        n = sm_count() / 2;
+    }
+    if (cached) cap[dev] = n;
+    return n;
+}
+
 }  // namespace fused
 }  // namespace fcb200
 
@@ -471,10 +709,12 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
                                      const void* const* w_lo, const int64_t* w_rows, const int64_t* w_cols,
                                      const float* w_scale, const float* const* bias, const int32_t* tiles, int32_t num_tiles,
                                      float* y, int64_t ldy, int64_t y_cols, void* o_hi, void* o_lo, int64_t ldo, int64_t o_cols,
-                                     const float* a_scale, const float* o_scale, int64_t m, int32_t* status, void* stream) {
+                                     const float* a_scale, const float* o_scale, int64_t m, int32_t variant, int32_t* status,
+                                     void* stream) {
     using namespace fused;
     if (!a_hi || !a_lo || !w_hi || !w_lo || !w_rows || !w_cols || !w_scale || !tiles || !y || m < 0) return FCB200_EINVAL;
     if (num_tiles <= 0 || num_tiles > kMaxTiles) return FCB200_ERANGE;
+    if (variant != 0 && variant != 1) return FCB200_EINVAL;
     if (lda % 8 || lda < a_cols || ldy % 4 || ldy < y_cols) return FCB200_EINVAL;
     if (!aligned16(a_hi) || !aligned16(a_lo) || !aligned16(y)) return FCB200_EALIGN;
     if (o_hi || o_lo) {
@@ -536,11 +776,29 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
     }
     prm.y = y, prm.ldy = ldy, prm.a_scale = a_scale, prm.o_scale = o_scale;
     prm.m_total = m, prm.status = status;
+    cudaStream_t st = static_cast<cudaStream_t>(stream);
+    if (variant == 1) {
+        CUtensorMap mwy[3];
+        for (int i = 0; i < 3; ++i) {
+            const int j = used[i] ? i : first;
+            rc = map_half(&mwy[i], w_hi[j], w_rows[j], w_cols[j], w_cols[j], BN / 2);
+            if (rc) return rc;
+        }
+        static bool attr_done[64] = {};
+        if (const int arc = ensure_dynamic_smem(so2_conv_pair_kernel, kPairSmemBytes, attr_done)) return arc;
+        const int64_t tiles_m = (m + 2 * BM - 1) / (2 * BM);
+        const int max_pairs = pair_capacity();
+        if (max_pairs <= 0) return FCB200_EINVAL;
+        const int pairs = (int)(tiles_m < max_pairs ? tiles_m : max_pairs);
+        so2_conv_pair_kernel<<<2 * pairs, kThreads, kPairSmemBytes, st>>>(mah, mal, mw[0], mw[1], mw[2], mw[3], mw[4], mw[5], mwy[0],
+                                                                         mwy[1], mwy[2], my, moh, mol, plan, prm, tiles_m);
+        return launch_status();
+    }
     static bool attr_done[64] = {};
     if (const int arc = ensure_dynamic_smem(so2_conv_fused_kernel, kSmemBytes, attr_done)) return arc;
     const int64_t tiles_m = (m + BM - 1) / BM;
     const int grid = (int)(tiles_m < sm_count() ? tiles_m : sm_count());
-    so2_conv_fused_kernel<<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(
-        mah, mal, mw[0], mw[1], mw[2], mw[3], mw[4], mw[5], my, moh, mol, plan, prm, tiles_m);
+    so2_conv_fused_kernel<<<grid, kThreads, kSmemBytes, st>>>(mah, mal, mw[0], mw[1], mw[2], mw[3], mw[4], mw[5], my, moh, mol, plan,
+                                                              prm, tiles_m);
     return launch_status();
 }

@@ -350,6 +350,20 @@ def radial_act_fwd_(pre: Tensor, table_src: Optional[Tensor], table_tgt: Optiona
              w, _stream()), nbytes=e * (8 * w + 16))
 
 
+@_op("radial_act_fwd_h", ("out_hi", "out_lo", "stats"))
+def radial_act_fwd_h_(pre: Tensor, table_src: Optional[Tensor], table_tgt: Optional[Tensor], z_src: Optional[Tensor],
+                      z_tgt: Optional[Tensor], ln_weight: Tensor, ln_bias: Tensor, eps: float, out_hi: Tensor, out_lo: Tensor,
+                      stats: Tensor) -> None:
+    """radial_act_fwd_ with the activation written as the half-precision (hi, lo) planes the next Linear reads."""
+    _chk(pre, table_src, table_tgt, z_src, z_tgt, ln_weight, ln_bias, out_hi, out_lo, stats)
+    _f32(pre, table_src, table_tgt, ln_weight, ln_bias, stats)
+    _h16(out_hi, out_lo)
+    e, w = pre.shape
+    _launch("radial_act_fwd", "fcb200_radial_act_fwd_h",
+            (_p(pre), _p(table_src), _p(table_tgt), _p(z_src), _p(z_tgt), _p(ln_weight), _p(ln_bias), eps, _p(out_hi), _p(out_lo),
+             _p(stats), e, w, _stream()), nbytes=e * (8 * w + 16))
+
+
 @_op("radial_act_bwd", ("grad_pre",))
 def radial_act_bwd_(grad_out: Tensor, pre: Tensor, table_src: Optional[Tensor], table_tgt: Optional[Tensor],
                     z_src: Optional[Tensor], z_tgt: Optional[Tensor], ln_weight: Tensor, ln_bias: Tensor, stats: Tensor,
@@ -538,18 +552,21 @@ def gemm_f16x2_presplit_(a_hi: Tensor, a_lo: Tensor, w_hi: Tensor, w_lo: Tensor,
 CONV_PLAIN, CONV_GATE_RAW, CONV_SILU, CONV_GATED, CONV_SILU_BWD, CONV_GATED_BWD = range(6)
 CONV_FIRST, CONV_LAST, CONV_KEEP, CONV_SYNC = 1, 2, 4, 8
 CONV_MAX_TILES = 40
+CONV_VARIANT = 1  # default launch form of so2_conv_fused_: CTA pairs
 
 
 @_op("so2_conv_fused", ("y", "o_hi", "o_lo", "status"))
 def so2_conv_fused_(a_hi: Tensor, a_lo: Tensor, w_hi: List[Tensor], w_lo: List[Tensor], w_scale: List[float],
                     bias0: Optional[Tensor], tiles: List[int], y: Tensor, o_hi: Optional[Tensor], o_lo: Optional[Tensor],
-                    a_scale: Optional[Tensor], o_scale: Optional[Tensor], status: Tensor, label: str = "") -> None:
+                    a_scale: Optional[Tensor], o_scale: Optional[Tensor], status: Tensor, label: str = "",
+                    variant: int = -1) -> None:
     """One launch for all m-blocks of an SO(2) convolution with the gate (or its derivative) in the epilogue.
 
     ``a_hi/a_lo`` [E, Ka] are the input planes, ``w_*`` the (up to three) half-split weight matrices, ``tiles`` a flat
     list of 9 integers per 128-column output tile (a_col, k, w, w_row, out_col, mode, y_col, gate_col, flags).  ``y``
     [E, >=gates] float32 receives the float32 modes and the raw gate scalars and is read by the gated modes; ``o_hi/o_lo``
-    receive the split modes."""
+    receive the split modes.  ``variant`` 0 runs one CTA per 128-edge tile, 1 CTA pairs on 256-edge tiles (default:
+    the module-level ``CONV_VARIANT``)."""
     for t in (a_hi, a_lo):
         if not t.is_cuda or t.dtype != torch.float16 or t.dim() != 2 or t.stride(1) != 1 or t.shape != a_hi.shape \
                 or t.stride(0) != a_hi.stride(0):
@@ -583,7 +600,8 @@ def so2_conv_fused_(a_hi: Tensor, a_lo: Tensor, w_hi: List[Tensor], w_lo: List[T
     _launch("so2_conv_fused" + label, "fcb200_so2_conv_fused",
             (_p(a_hi), _p(a_lo), a_hi.stride(0), a_hi.shape[1], whi, wlo, rows, cols, scales, biases, tl, nt,
              _p(y), y.stride(0), y.shape[1], _p(o_hi), _p(o_lo), 0 if o_hi is None else o_hi.stride(0),
-             0 if o_hi is None else o_hi.shape[1], _p(a_scale), _p(o_scale), m, _p(status), _stream()), nbytes=nbytes, flops=flops)
+             0 if o_hi is None else o_hi.shape[1], _p(a_scale), _p(o_scale), m, CONV_VARIANT if variant < 0 else variant,
+             _p(status), _stream()), nbytes=nbytes, flops=flops)
 
 
 def split_f16(w: Tensor):

@@ -157,6 +157,14 @@ int fcb200_so2_gate_bwd(const float* grad_out, const float* y, float* grad_y, in
 int fcb200_radial_act_fwd(const float* pre, const float* table_src, const float* table_tgt, const int32_t* z_src,
                           const int32_t* z_tgt, const float* ln_weight, const float* ln_bias, float eps, float* out,
                           float* stats, int64_t num_edges, int32_t width, void* stream);
+/*
+ * fcb200_radial_act_fwd with the activation written as the half-precision split (planes out_hi / out_lo of shape
+ * [E,128], scale 1) that the next Linear of the radial MLP reads with fcb200_gemm_f16x2_presplit /
+ * fcb200_so2_conv_fused: the hidden activations of RadialMLP (uma/nn/radial.py:61-86) only ever feed a contraction.
+ */
+int fcb200_radial_act_fwd_h(const float* pre, const float* table_src, const float* table_tgt, const int32_t* z_src,
+                            const int32_t* z_tgt, const float* ln_weight, const float* ln_bias, float eps, void* out_hi,
+                            void* out_lo, float* stats, int64_t num_edges, int32_t width, void* stream);
 /* Backward of fcb200_radial_act_fwd w.r.t. pre (the tables and LayerNorm parameters are frozen). */
 int fcb200_radial_act_bwd(const float* grad_out, const float* pre, const float* table_src, const float* table_tgt,
                           const int32_t* z_src, const int32_t* z_tgt, const float* ln_weight, const float* ln_bias,
@@ -350,13 +358,15 @@ int fcb200_gemm_f16x2_presplit(const void* a_hi, const void* a_lo, int64_t lda, 
  *   y            [M, y_cols] float32, row stride ldy; o_hi/o_lo [M, o_cols] half planes, row stride ldo, written
  *                times *o_scale (device pointers to powers of two, NULL = 1)
  *   status       as in fcb200_gemm_f16x2_presplit
+ *   variant      0: one CTA per 128-edge tile; 1: CTA pairs (tcgen05 cta_group::2) on 256-edge tiles, each CTA
+ *                streaming half of the weight operand (same results)
  * At most 40 tiles; every k a multiple of 32, w_row a multiple of 128.
  */
 int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t lda, int64_t a_cols, const void* const* w_hi,
                           const void* const* w_lo, const int64_t* w_rows, const int64_t* w_cols, const float* w_scale,
                           const float* const* bias, const int32_t* tiles, int32_t num_tiles, float* y, int64_t ldy,
                           int64_t y_cols, void* o_hi, void* o_lo, int64_t ldo, int64_t o_cols, const float* a_scale,
-                          const float* o_scale, int64_t m, int32_t* status, void* stream);
+                          const float* o_scale, int64_t m, int32_t variant, int32_t* status, void* stream);
 
 /*
  * The four kernels whose output is consumed only by an SO(2) contraction, writing that output as the

@@ -27,8 +27,17 @@ def _unplane(p, scale=1.0):
     return (p[0].float() + p[1].float() / 2048.0) / scale
 
 
-@pytest.mark.parametrize("lmax,e", [(2, 77), (2, 1000), (4, 300)])
-def test_fused_convolutions_match_the_separate_kernels(ops, lmax, e):
+@pytest.fixture(params=[0, 1], ids=["single_cta", "cta_pairs"])
+def variant(request, ops):
+    """Both launch forms of the fused kernel: one CTA per 128 edges, and CTA pairs (cta_group::2) per 256 edges."""
+    saved = ops.CONV_VARIANT
+    ops.CONV_VARIANT = request.param
+    yield request.param
+    ops.CONV_VARIANT = saved
+
+
+@pytest.mark.parametrize("lmax,e", [(2, 77), (2, 1000), (4, 300), (2, 40000)])
+def test_fused_convolutions_match_the_separate_kernels(ops, variant, lmax, e):
     from fairchem_b200 import backbone as B
 
     torch.manual_seed(lmax)
@@ -73,7 +82,7 @@ def test_fused_convolutions_match_the_separate_kernels(ops, lmax, e):
     torch.testing.assert_close(gm, gm_ref, rtol=1e-5, atol=1e-5 * float(gm_ref.abs().max()))
 
 
-def test_edge_block_is_the_same_with_and_without_the_fused_launches(ops):
+def test_edge_block_is_the_same_with_and_without_the_fused_launches(ops, variant):
     """Energy and forces of a small periodic system with the fused convolution launches on and off."""
     from fairchem_b200 import backbone as B
     from fairchem_b200 import synthetic, weights
