@@ -149,6 +149,8 @@ def run_b200(args):
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         dist.init_process_group("nccl", device_id=dev)
     B.set_gemm_precision(args.precision)
+    if args.conv_variant is not None:
+        ops.CONV_VARIANT = args.conv_variant
     if args.generic_kernels:
         from fairchem_b200 import ops as _ops
 
@@ -464,6 +466,8 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--generic-kernels", action="store_true",
                     help="route the lmax=2 model through the any-lmax edge-block kernels (A/B measurement)")
+    ap.add_argument("--conv-variant", type=int, default=None, choices=[0, 1],
+                    help="launch form of the fused convolution kernel: 0 one CTA per 128-edge tile, 1 CTA pairs (A/B measurement)")
     ap.add_argument("--profile-run", action="store_true",
                     help="for runs under a profiler: allows fewer than 3 warm-up steps; the printed number is not a bench value")
     args = ap.parse_args()

@@ -235,8 +235,13 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
                 float v[32];
                 {
                     uint32_t r[32], c[32];
-                    FCB_TMEM_LD32(r, acc_t + (uint32_t)col);
-                    FCB_TMEM_LD32(c, acc_t + (uint32_t)(BN + col));
+                    // single CTA: main sums in columns [0, 128), corrections in [128, 256).  Pair: 64-column blocks
+                    // hh(0:32, 64:96) | corr(0:64) | hh(32:64, 96:128) | corr(64:128)
+                    const int chunk = half * 2 + c2;
+                    const uint32_t main_col = PAIR ? (uint32_t)((chunk & 1) * 128 + (chunk >> 1) * 32) : (uint32_t)col;
+                    const uint32_t corr_col = PAIR ? (uint32_t)(64 + (chunk >> 1) * 128 + (chunk & 1) * 32) : (uint32_t)(BN + col);
+                    FCB_TMEM_LD32(r, acc_t + main_col);
+                    FCB_TMEM_LD32(c, acc_t + corr_col);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                     float poison = 0.f;  // becomes NaN if any value is inf or NaN (an overflowed half upstream)
 #pragma unroll
@@ -347,9 +352,14 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
             }
             if (!ok) break;
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            // 256 arrivals (per CTA) hand the accumulator back to the MMA thread
-            if (PAIR) mbar_arrive_cluster(tempty0 + 8u * buf);
-            else mbar_arrive(tempty0 + 8u * buf);
+            // hand the accumulator back to the MMA thread: every thread in the single-CTA kernel, one lane per warp in
+            // the pair kernel (there the barrier may sit in the other SM and an arrive is a round trip)
+            if (PAIR) {
+                __syncwarp();
+                if (lane == 0) mbar_arrive_cluster(tempty0 + 8u * buf);
+            } else {
+                mbar_arrive(tempty0 + 8u * buf);
+            }
         }
     }
     if (!(amax <= kHalfMax)) *range_flag = 1;  // also catches NaN
@@ -493,17 +503,22 @@ __global__ void __launch_bounds__(kThreads, 1)
 // ---------------------------------------------------------------------------------------------------------------
 // The same schedule on CTA pairs.  Two CTAs of a cluster own a 256-edge row tile (128 rows each); one thread of
 // the leader CTA issues tcgen05.mma.cta_group::2 (M = 256), which reads each CTA's A rows from that CTA's shared
-// memory and the B operand half from each: the 128-wide MMAs of a single CTA are bound by shared-memory bandwidth,
-// and the pair halves the B bytes each CTA streams per MMA.  Per stage a CTA holds
-//     A_hi | A_lo (its 128 rows) | X = W_hi[n0, n0+128) in the leader, W_lo[n0, n0+128) in the peer
-//                                | Y = W_hi[n0, n0+64) in the leader, W_hi[n0+64, n0+128) in the peer
-// so that  a_hi x [X_leader ; X_peer] = [a_hi w_hi | a_hi w_lo]  (one N = 256 MMA into main | correction) and
-//          a_lo x [Y_leader ; Y_peer] = a_lo w_hi                (one N = 128 MMA into the correction columns).
-// TMA loads carry no multicast: every CTA fetches what lands in its own shared memory; their completion is counted
-// on the leader's barrier.  tcgen05.commit with the pair mask frees a stage / publishes an accumulator in both CTAs.
+// memory and half of the B rows from each.  What bounds these contractions is the stream of operand bytes from L2
+// into shared memory (a 128 x 128 tile re-reads 32 KiB per 32-deep k-step); in a pair each CTA fetches only half of
+// the weight tile, 24 KiB per k-step, and the ring is one stage deeper.  Per stage a CTA holds
+//     A_hi | A_lo (its 128 rows) | X (128 weight rows, see below)
+//     X leader: W_hi[0:32) ; W_hi[64:96) ; W_lo[0:64)        X peer: W_hi[32:64) ; W_hi[96:128) ; W_lo[64:128)
+// (row ranges relative to the tile's first output column).  Then
+//     a_hi x [X_leader ; X_peer]                 (N = 256)  fills 64-column blocks  hh(0:32,64:96) | hl(0:64) | hh(32:64,96:128) | hl(64:128)
+//     a_lo x [X_leader[0:32)  ; X_peer[0:32)]    (N = 64)   adds  lh(0:64)   to the second block
+//     a_lo x [X_leader[32:64) ; X_peer[32:64)]   (N = 64)   adds  lh(64:128) to the fourth block
+// so every weight row is fetched once per pair and the main and correction sums of a 32-column chunk are still two
+// contiguous TMEM ranges.  TMA loads carry no multicast: every CTA fetches what lands in its own shared memory;
+// their completion is counted on the leader's barrier.  tcgen05.commit with the pair mask frees a stage / publishes
+// an accumulator in both CTAs.
 // ---------------------------------------------------------------------------------------------------------------
-constexpr int kPairStageBytes = 3 * kHalfTile + kHalfTile / 2;  // 28 KiB
-constexpr int kPairStages = 4;
+constexpr int kPairStageBytes = 3 * kHalfTile;  // 24 KiB
+constexpr int kPairStages = 5;
 constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kEpiWarps * kEpiWarpBytes + 1024 + 256;
 
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
@@ -511,8 +526,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                          const __grid_constant__ CUtensorMap map_whi0, const __grid_constant__ CUtensorMap map_wlo0,
                          const __grid_constant__ CUtensorMap map_whi1, const __grid_constant__ CUtensorMap map_wlo1,
                          const __grid_constant__ CUtensorMap map_whi2, const __grid_constant__ CUtensorMap map_wlo2,
-                         const __grid_constant__ CUtensorMap map_wy0, const __grid_constant__ CUtensorMap map_wy1,
-                         const __grid_constant__ CUtensorMap map_wy2, const __grid_constant__ CUtensorMap map_y,
+                         const __grid_constant__ CUtensorMap map_y,
                          const __grid_constant__ CUtensorMap map_ohi, const __grid_constant__ CUtensorMap map_olo,
                          const __grid_constant__ Plan plan, const __grid_constant__ Params prm, int64_t tiles_m) {
     constexpr int S = kPairStages;
@@ -530,7 +544,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_generic + 8 * (2 * S + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_generic + 8 * (2 * S + 4) + 4);
     volatile int* range_flag = reinterpret_cast<volatile int*>(bar_generic + 8 * (2 * S + 4) + 8);
-    // a stage: A_hi | A_lo | X | Y
+    // a stage: A_hi | A_lo | X   (the weight maps here have 32-row (W_hi) and 64-row (W_lo) boxes)
     auto part_addr = [&](int s, int which) { return base + s * kPairStageBytes + which * kHalfTile; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -541,12 +555,12 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S; ++s) {
-            mbar_init(full_bar(s), 2);   // one arrive.expect_tx from each CTA's producer
+            mbar_init(full_bar(s), 1);   // the leader's producer expects both CTAs' bytes; the peer only issues its loads
             mbar_init(empty_bar(s), 1);  // the leader's commit, delivered to both CTAs
         }
         for (int b = 0; b < 2; ++b) {
             mbar_init(tfull_bar(b), 1);
-            mbar_init(tempty_bar(b), 2 * 32 * kEpiWarps);  // both CTAs' epilogue threads
+            mbar_init(tempty_bar(b), 2 * kEpiWarps);  // one lane of every epilogue warp of both CTAs
         }
         for (int w = 0; w < kEpiWarps; ++w) mbar_init(ld_bar(w), 1);
         *abort_flag = 0;
@@ -574,9 +588,9 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                 const int row = (int)(mt * 2 * BM + rank * BM);
                 for (int ti = 0; ti < ntiles && ok; ++ti) {
                     const Tile& t = plan.t[ti];
-                    const CUtensorMap* wx = leader ? (t.w == 0 ? &map_whi0 : (t.w == 1 ? &map_whi1 : &map_whi2))
-                                                   : (t.w == 0 ? &map_wlo0 : (t.w == 1 ? &map_wlo1 : &map_wlo2));
-                    const CUtensorMap* wy = t.w == 0 ? &map_wy0 : (t.w == 1 ? &map_wy1 : &map_wy2);
+                    const CUtensorMap* whi = t.w == 0 ? &map_whi0 : (t.w == 1 ? &map_whi1 : &map_whi2);
+                    const CUtensorMap* wlo = t.w == 0 ? &map_wlo0 : (t.w == 1 ? &map_wlo1 : &map_wlo2);
+                    const int r_hi = t.w_row + (int)rank * 32, r_lo = t.w_row + (int)rank * 64;
                     const int num_kb = t.k / BK;
                     for (int kb = 0; kb < num_kb; ++kb, ++it) {
                         const int s = (int)(it % S);
@@ -584,11 +598,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag);
                         if (!ok) break;
                         const uint32_t lead_full = map_to_cta(full_bar(s), 0);
-                        mbar_expect_tx_cluster(lead_full, kPairStageBytes);
+                        // a remote arrive costs the issuing thread a round trip to the other SM: the leader alone announces
+                        // the bytes of both CTAs, the peer's loads just complete on the leader's barrier
+                        if (leader) mbar_expect_tx(full_bar(s), 2 * kPairStageBytes);
                         tma_load_2d_pair(part_addr(s, 0), &map_ahi, t.a_col + kb * BK, row, lead_full);
                         tma_load_2d_pair(part_addr(s, 1), &map_alo, t.a_col + kb * BK, row, lead_full);
-                        tma_load_2d_pair(part_addr(s, 2), wx, kb * BK, t.w_row, lead_full);
-                        tma_load_2d_pair(part_addr(s, 3), wy, kb * BK, t.w_row + (int)rank * (BN / 2), lead_full);
+                        tma_load_2d_pair(part_addr(s, 2), whi, kb * BK, r_hi, lead_full);
+                        tma_load_2d_pair(part_addr(s, 2) + 2048u, whi, kb * BK, r_hi + 64, lead_full);
+                        tma_load_2d_pair(part_addr(s, 2) + 4096u, wlo, kb * BK, r_lo, lead_full);
                     }
                 }
             }
@@ -613,13 +630,14 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                         if (!ok) break;
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         const uint64_t da_hi = smem_desc64(part_addr(s, 0)), da_lo = smem_desc64(part_addr(s, 1));
-                        const uint64_t dx = smem_desc64(part_addr(s, 2)), dy = smem_desc64(part_addr(s, 3));
+                        const uint64_t dx = smem_desc64(part_addr(s, 2)), dx32 = smem_desc64(part_addr(s, 2) + 2048u);
 #pragma unroll
                         for (int j = 0; j < BK / 16; ++j) {
                             const uint64_t adv = (uint64_t)(j * 2);
                             const uint32_t first = (kb > 0 || j > 0) ? 1u : 0u;
                             umma_f16_pair<2 * BN>(acc, da_hi + adv, dx + adv, first);
-                            umma_f16_pair<BN>(acc + BN, da_lo + adv, dy + adv, 1u);
+                            umma_f16_pair<BN / 2>(acc + 64, da_lo + adv, dx + adv, 1u);
+                            umma_f16_pair<BN / 2>(acc + 192, da_lo + adv, dx32 + adv, 1u);
                         }
                         umma_commit_pair(empty_bar(s));
                     }
@@ -705,6 +723,8 @@ static int pair_capacity() {
 
 using namespace fcb200;
 
+extern "C" int fcb200_conv_pair_capacity(void) { return fused::pair_capacity(); }
+
 extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t lda, int64_t a_cols, const void* const* w_hi,
                                      const void* const* w_lo, const int64_t* w_rows, const int64_t* w_cols,
                                      const float* w_scale, const float* const* bias, const int32_t* tiles, int32_t num_tiles,
@@ -713,6 +733,8 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
                                      void* stream) {
     using namespace fused;
     if (!a_hi || !a_lo || !w_hi || !w_lo || !w_rows || !w_cols || !w_scale || !tiles || !y || m < 0) return FCB200_EINVAL;
+    Plan plan{};
+    Params prm{};
     if (num_tiles <= 0 || num_tiles > kMaxTiles) return FCB200_ERANGE;
     if (variant != 0 && variant != 1) return FCB200_EINVAL;
     if (lda % 8 || lda < a_cols || ldy % 4 || ldy < y_cols) return FCB200_EINVAL;
@@ -721,8 +743,6 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
         if (!o_hi || !o_lo || ldo % 8 || ldo < o_cols) return FCB200_EINVAL;
         if (!aligned16(o_hi) || !aligned16(o_lo)) return FCB200_EALIGN;
     }
-    Plan plan{};
-    Params prm{};
     plan.ntiles = num_tiles;
     bool used[3] = {false, false, false};
     for (int i = 0; i < num_tiles; ++i) {
@@ -778,10 +798,11 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
     prm.m_total = m, prm.status = status;
     cudaStream_t st = static_cast<cudaStream_t>(stream);
     if (variant == 1) {
-        CUtensorMap mwy[3];
+        CUtensorMap mp[6];  // W_hi with 32-row boxes, W_lo with 64-row boxes
         for (int i = 0; i < 3; ++i) {
             const int j = used[i] ? i : first;
-            rc = map_half(&mwy[i], w_hi[j], w_rows[j], w_cols[j], w_cols[j], BN / 2);
+            rc = map_half(&mp[2 * i], w_hi[j], w_rows[j], w_cols[j], w_cols[j], 32);
+            if (!rc) rc = map_half(&mp[2 * i + 1], w_lo[j], w_rows[j], w_cols[j], w_cols[j], 64);
             if (rc) return rc;
         }
         static bool attr_done[64] = {};
@@ -790,8 +811,8 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
         const int max_pairs = pair_capacity();
         if (max_pairs <= 0) return FCB200_EINVAL;
         const int pairs = (int)(tiles_m < max_pairs ? tiles_m : max_pairs);
-        so2_conv_pair_kernel<<<2 * pairs, kThreads, kPairSmemBytes, st>>>(mah, mal, mw[0], mw[1], mw[2], mw[3], mw[4], mw[5], mwy[0],
-                                                                         mwy[1], mwy[2], my, moh, mol, plan, prm, tiles_m);
+        so2_conv_pair_kernel<<<2 * pairs, kThreads, kPairSmemBytes, st>>>(mah, mal, mp[0], mp[1], mp[2], mp[3], mp[4], mp[5], my, moh,
+                                                                         mol, plan, prm, tiles_m);
         return launch_status();
     }
     static bool attr_done[64] = {};

@@ -552,7 +552,7 @@ def gemm_f16x2_presplit_(a_hi: Tensor, a_lo: Tensor, w_hi: Tensor, w_lo: Tensor,
 CONV_PLAIN, CONV_GATE_RAW, CONV_SILU, CONV_GATED, CONV_SILU_BWD, CONV_GATED_BWD = range(6)
 CONV_FIRST, CONV_LAST, CONV_KEEP, CONV_SYNC = 1, 2, 4, 8
 CONV_MAX_TILES = 40
-CONV_VARIANT = 1  # default launch form of so2_conv_fused_: CTA pairs
+CONV_VARIANT = 0  # default launch form of so2_conv_fused_ (0: one CTA per 128-edge tile, 1: CTA pairs on 256-edge tiles)
 
 
 @_op("so2_conv_fused", ("y", "o_hi", "o_lo", "status"))

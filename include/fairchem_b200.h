@@ -362,6 +362,9 @@ int fcb200_gemm_f16x2_presplit(const void* a_hi, const void* a_lo, int64_t lda, 
  *                streaming half of the weight operand (same results)
  * At most 40 tiles; every k a multiple of 32, w_row a multiple of 128.
  */
+/* Number of CTA pairs variant 1 of fcb200_so2_conv_fused runs at once on the current device (0 if it cannot be told). */
+int fcb200_conv_pair_capacity(void);
+
 int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t lda, int64_t a_cols, const void* const* w_hi,
                           const void* const* w_lo, const int64_t* w_rows, const int64_t* w_cols, const float* w_scale,
                           const float* const* bias, const int32_t* tiles, int32_t num_tiles, float* y, int64_t ldy,
