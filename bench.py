@@ -221,7 +221,10 @@ def run_b200(args):
         torch.distributed.all_reduce(t)
         edges = int(t.item())
 
-    # end to end through the module interface with host buffers
+    # end to end through the public interface with host buffers
+    from fairchem_b200.predict import B200PredictUnit
+
+    unit = B200PredictUnit(bb, head, device=dev)
     pin_pos = data["pos"].detach().cpu().pin_memory()
     pin_f = torch.empty_like(pin_pos).pin_memory()
     pin_e = torch.empty(1, dtype=torch.float64).pin_memory()
@@ -234,8 +237,8 @@ def run_b200(args):
         data["pos"] = pin_pos.to(dev, non_blocking=True)
         if stepper is not None:
             energy, forces = stepper.step(data)
-        else:
-            out = head(data, bb(data))
+        else:  # the call a calculator makes: predict-unit surface over the backbone (graph rebuilt every step, skin 0)
+            out = unit.predict(data)
             energy, forces = out["energy"], out["forces"]
         pin_f.copy_(forces, non_blocking=True)
         pin_e.copy_(energy[:1], non_blocking=True)

@@ -1057,6 +1057,7 @@ class eSCNMDBackboneB200(nn.Module):
         self.norm = RMSNormSH(lmax, c)
         self.register_buffer("_wig_transpose", torch.tensor(_transpose_index()), persistent=False)
         self.last_graph = None
+        self.neighbor_list = None  # optional SkinNeighborList: reuse of the candidate list while atoms move less than skin / 2
 
     # -- reference-facing helpers ------------------------------------------------------------
     @property
@@ -1208,7 +1209,10 @@ class eSCNMDBackboneB200(nn.Module):
             with torch.no_grad():
                 from .graph import radius_graph_pbc_b200
 
-                edge_index, cell_offsets, neighbors = radius_graph_pbc_b200(data, self.cutoff, self.max_neighbors, False, pbc)
+                if self.neighbor_list is not None:  # candidate list kept between calls (fairchem_b200.graph.SkinNeighborList)
+                    edge_index, cell_offsets, neighbors = self.neighbor_list.update(data, pbc)
+                else:
+                    edge_index, cell_offsets, neighbors = radius_graph_pbc_b200(data, self.cutoff, self.max_neighbors, False, pbc)
         else:
             edge_index, cell_offsets = data["edge_index"], data["cell_offsets"]
             order = torch.sort(edge_index[1], stable=True).indices

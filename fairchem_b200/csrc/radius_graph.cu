@@ -231,6 +231,28 @@ __global__ void __launch_bounds__(256)
     }
 }
 
+// Distances of a kept candidate list at new positions: same arithmetic as the search (image position as the binning
+// computes it, unfused squared distance), +inf for a pair that is out of range now.  One warp per target.
+__global__ void __launch_bounds__(256)
+    rg_refresh_kernel(const float* __restrict__ pos, const int32_t* __restrict__ sys, int nsys, const int32_t* __restrict__ targets,
+                      int64_t num_targets, const int32_t* __restrict__ cand_ptr, const int32_t* __restrict__ cand_id,
+                      float radius_sq, float* __restrict__ cand_d2) {
+    const int lane = threadIdx.x & 31;
+    const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (t >= num_targets) return;
+    const int atom = targets ? targets[t] : (int)t;
+    const float tx = pos[(int64_t)atom * 3 + 0], ty = pos[(int64_t)atom * 3 + 1], tz = pos[(int64_t)atom * 3 + 2];
+    const int b = cand_ptr[t], e = cand_ptr[t + 1];
+    for (int i = b + lane; i < e; i += 32) {
+        Sys s;
+        float px, py, pz;
+        int cell;
+        source_of(sys, nsys, pos, cand_id[i], s, px, py, pz, cell);
+        const float d2 = dist_sq(tx, ty, tz, make_float4(px, py, pz, 0.f));
+        cand_d2[i] = (d2 <= radius_sq && d2 != 0.0f) ? d2 : __int_as_float(0x7f800000);
+    }
+}
+
 // one warp per target: max-neighbour threshold by bisection on the float bit patterns, then ordered compaction
 __global__ void __launch_bounds__(256)
     rg_select_kernel(const int32_t* __restrict__ sys, const int32_t* __restrict__ targets, const int32_t* __restrict__ target_sys,
@@ -242,9 +264,17 @@ __global__ void __launch_bounds__(256)
     const int64_t t = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (t >= num_targets) return;
     const int b = cand_ptr[t], m = cand_ptr[t + 1] - b;
-    float thr = __int_as_float(0x7f800000);  // +inf: keep everything
+    // entries marked +inf are candidates of a wider list that are out of range now (fcb200_rg_refresh): never kept
+    constexpr unsigned kInf = 0x7f800000u;
+    float thr = __uint_as_float(kInf - 1u);  // largest finite value: keep every live candidate
+    int live = m;
     if (max_neighbors > 0 && m > max_neighbors) {
-        unsigned lo = 0u, hi = 0x7f800000u;
+        int c = 0;
+        for (int i = lane; i < m; i += 32) c += (__float_as_uint(cand_d2[b + i]) < kInf) ? 1 : 0;
+        live = warp_sum_i(c);
+    }
+    if (max_neighbors > 0 && live > max_neighbors) {
+        unsigned lo = 0u, hi = kInf;
         while (lo < hi) {  // at most 31 rounds
             const unsigned mid = lo + ((hi - lo) >> 1);
             int c = 0;
@@ -252,7 +282,7 @@ __global__ void __launch_bounds__(256)
             c = warp_sum_i(c);
             if (c >= max_neighbors + 1) hi = mid; else lo = mid + 1;
         }
-        thr = __fadd_rn(__uint_as_float(lo), 0.01f);
+        thr = fminf(__fadd_rn(__uint_as_float(lo), 0.01f), __uint_as_float(kInf - 1u));
     }
     if (edge_ptr == nullptr) {
         int c = 0;
@@ -385,6 +415,15 @@ int fcb200_rg_select(const int32_t* sys, const int32_t* targets, const int32_t* 
     rg_select_kernel<<<(unsigned)((num_targets + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
         sys, targets, target_sys, num_targets, cand_ptr, cand_id, cand_d2, max_neighbors, keep_count, edge_ptr, edge_src, edge_tgt,
         edge_offsets);
+    return launch_status();
+}
+
+int fcb200_rg_refresh(const float* pos, const int32_t* sys, int32_t num_systems, const int32_t* targets, int64_t num_targets,
+                      const int32_t* cand_ptr, const int32_t* cand_id, float radius_sq, float* cand_d2, void* stream) {
+    if (!pos || !sys || !cand_ptr || !cand_id || !cand_d2 || num_systems <= 0 || num_targets < 0) return FCB200_EINVAL;
+    if (num_targets == 0) return FCB200_OK;
+    rg_refresh_kernel<<<(unsigned)((num_targets + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
+        pos, sys, num_systems, targets, num_targets, cand_ptr, cand_id, radius_sq, cand_d2);
     return launch_status();
 }
 

@@ -112,13 +112,16 @@ def build_system_table(pos: torch.Tensor, cell: torch.Tensor, pbc: torch.Tensor,
     return table, src_begin, grid_begin
 
 
-@torch.no_grad()
-def radius_graph_pbc_b200(data, radius, max_num_neighbors_threshold, enforce_max_neighbors_strictly: bool = False,
-                          pbc: torch.Tensor | None = None):
-    """(edge_index [2,E] int64 (source; target), cell_offsets [E,3], neighbors [B] int64)."""
-    if enforce_max_neighbors_strictly:
-        raise NotImplementedError("strict max-neighbour selection is not part of the eSCN-MD path "
-                                  "(escn_md.py:372 always passes False)")
+class _Candidates:
+    """Result of the cell-list search: per target the image-replicated sources within ``radius`` (ids and squared
+    distances in target order), plus what the selection step needs to turn them into edges."""
+
+    def __init__(self, **kw):
+        self.__dict__.update(kw)
+
+
+def _search(data, radius: float, pbc=None) -> _Candidates:
+    """Phases 1-3 of the radius graph: bin the image-replicated sources in a uniform grid, find every pair within ``radius``."""
     pos = data.pos
     if not pos.is_cuda:
         raise _lib.FairchemB200Error("radius_graph_pbc_b200 needs CUDA tensors (no CPU fallback)")
@@ -167,26 +170,93 @@ def radius_graph_pbc_b200(data, radius, max_num_neighbors_threshold, enforce_max
     cand_d2 = torch.empty(max(total_cand, 1), dtype=torch.float32, device=dev)
     _lib.call("fcb200_rg_search", _p(pos), _p(sys_t), _p(targets), _p(target_sys), num_targets, _p(cell_ptr),
               _p(bucket), r2, None, _p(cand_ptr), _p(cand_id), _p(cand_d2), st)
+    return _Candidates(sys_t=sys_t, nsys=nsys, targets=targets, target_sys=target_sys, num_targets=num_targets,
+                       cand_ptr=cand_ptr, cand_id=cand_id, cand_d2=cand_d2, device=dev, cell_dtype=data.cell.dtype)
 
-    # phase 4: max-neighbour rule and compaction
-    k = int(max_num_neighbors_threshold)
+
+def _select(c: _Candidates, max_neighbors: int):
+    """Phase 4: the max-neighbour rule (get_max_neighbors_mask, radius_graph_pbc.py:74-189, non-strict form) and the
+    compaction into (edge_index, cell_offsets, neighbors)."""
+    dev, st = c.device, _stream()
+    i32 = dict(dtype=torch.int32, device=dev)
+    num_targets, k = c.num_targets, int(max_neighbors)
     keep_count = torch.empty(max(num_targets, 1), **i32)
-    _lib.call("fcb200_rg_select", _p(sys_t), _p(targets), _p(target_sys), num_targets, _p(cand_ptr), _p(cand_id),
-              _p(cand_d2), k, _p(keep_count), None, None, None, None, st)
+    _lib.call("fcb200_rg_select", _p(c.sys_t), _p(c.targets), _p(c.target_sys), num_targets, _p(c.cand_ptr), _p(c.cand_id),
+              _p(c.cand_d2), k, _p(keep_count), None, None, None, None, st)
     edge_ptr = torch.empty(num_targets + 1, **i32)
     _lib.call("fcb200_exclusive_scan_i32", _p(keep_count), _p(edge_ptr), num_targets, st)
     num_edges = int(edge_ptr[-1].item())
     edge_index = torch.empty((2, max(num_edges, 1)), dtype=torch.int64, device=dev)
     offsets = torch.empty((max(num_edges, 1), 3), **i32)
-    _lib.call("fcb200_rg_select", _p(sys_t), _p(targets), _p(target_sys), num_targets, _p(cand_ptr), _p(cand_id),
-              _p(cand_d2), k, None, _p(edge_ptr), _p(edge_index[0]), _p(edge_index[1]), _p(offsets), st)
+    _lib.call("fcb200_rg_select", _p(c.sys_t), _p(c.targets), _p(c.target_sys), num_targets, _p(c.cand_ptr), _p(c.cand_id),
+              _p(c.cand_d2), k, None, _p(edge_ptr), _p(edge_index[0]), _p(edge_index[1]), _p(offsets), st)
     edge_index = edge_index[:, :num_edges]
     offsets = offsets[:num_edges]
-    if nsys == 1:
+    if c.nsys == 1:
         neighbors = torch.tensor([num_edges], dtype=torch.int64, device=dev)
     else:
-        neighbors = torch.bincount(target_sys.long(), weights=keep_count[:num_targets].double(), minlength=nsys).long()
-    return edge_index, offsets.to(data.cell.dtype), neighbors
+        neighbors = torch.bincount(c.target_sys.long(), weights=keep_count[:num_targets].double(), minlength=c.nsys).long()
+    return edge_index, offsets.to(c.cell_dtype), neighbors
+
+
+@torch.no_grad()
+def radius_graph_pbc_b200(data, radius, max_num_neighbors_threshold, enforce_max_neighbors_strictly: bool = False,
+                          pbc: torch.Tensor | None = None):
+    """(edge_index [2,E] int64 (source; target), cell_offsets [E,3], neighbors [B] int64)."""
+    if enforce_max_neighbors_strictly:
+        raise NotImplementedError("strict max-neighbour selection is not part of the eSCN-MD path "
+                                  "(escn_md.py:372 always passes False)")
+    return _select(_search(data, radius, pbc), max_num_neighbors_threshold)
+
+
+class SkinNeighborList:
+    """Radius graph of a system whose atoms move a little between calls (molecular dynamics, relaxations).
+
+    The cell-list search runs with radius ``cutoff + skin`` and its candidate list is kept; while no atom has moved by
+    more than ``skin / 2`` since then, and cell and composition are unchanged, a call only recomputes the candidates'
+    squared distances at the new positions (fcb200_rg_refresh) and repeats the max-neighbour selection, which yields
+    the edge set of a fresh search at the current positions.  An atom that the caller wrapped through a periodic
+    boundary shows up as a large displacement and simply triggers a new search.  (The reference rebuilds the whole
+    graph on every call, calculate/ase_calculator.py:237-240; this is the usual Verlet-list addition of MD codes.)"""
+
+    def __init__(self, cutoff: float, max_neighbors: int, skin: float = 0.5):
+        if skin < 0:
+            raise ValueError("skin must be non-negative")
+        self.cutoff, self.max_neighbors, self.skin = float(cutoff), int(max_neighbors), float(skin)
+        self._cand = self._pos0 = self._cell0 = None
+        self._key = None
+        self.searches = self.refreshes = 0
+
+    def _reusable(self, data) -> bool:
+        if self._cand is None or self.skin == 0.0:
+            return False
+        pos = data.pos
+        key = (int(pos.shape[0]), tuple(int(v) for v in data.natoms.shape), pos.device,
+               None if getattr(data, "node_partition", None) is None else int(data.node_partition.shape[0]))
+        if key != self._key or not torch.equal(data.cell.to(self._cell0.dtype), self._cell0):
+            return False
+        moved = (pos.detach().float() - self._pos0).square().sum(dim=1).max()
+        return float(moved) <= (0.5 * self.skin) ** 2
+
+    @torch.no_grad()
+    def update(self, data, pbc=None):
+        """(edge_index, cell_offsets, neighbors) at the current positions of ``data``."""
+        if not self._reusable(data):
+            self._cand = _search(data, self.cutoff + self.skin, pbc)
+            self._pos0 = data.pos.detach().float().clone()
+            self._cell0 = data.cell.detach().clone()
+            self._key = (int(data.pos.shape[0]), tuple(int(v) for v in data.natoms.shape), data.pos.device,
+                         None if getattr(data, "node_partition", None) is None else int(data.node_partition.shape[0]))
+            self.searches += 1
+            if self.skin == 0.0:
+                return _select(self._cand, self.max_neighbors)
+        else:
+            self.refreshes += 1
+        c = self._cand
+        pos = data.pos.detach().contiguous().float()
+        _lib.call("fcb200_rg_refresh", _p(pos), _p(c.sys_t), c.nsys, _p(c.targets), c.num_targets, _p(c.cand_ptr), _p(c.cand_id),
+                  float(np.float32(self.cutoff * self.cutoff)), _p(c.cand_d2), _stream())
+        return _select(c, self.max_neighbors)
 
 
 def get_pbc_shifts(cell: torch.Tensor, cell_offsets: torch.Tensor, edge_system: torch.Tensor | None) -> torch.Tensor:

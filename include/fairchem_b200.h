@@ -258,6 +258,18 @@ int fcb200_rg_select(const int32_t* sys, const int32_t* targets, const int32_t* 
                      int32_t* edge_offsets, void* stream);
 
 /*
+ * Skin-distance reuse of a candidate list (the Verlet-list practice of MD drivers; the reference rebuilds its graph
+ * on every call, src/fairchem/core/calculate/ase_calculator.py:237-240): a list searched once with radius
+ * cutoff + skin (fcb200_rg_search) stays a superset of every later neighbourhood while no atom has moved by more
+ * than skin / 2.  This entry recomputes the squared distances of the kept candidates at the current positions with
+ * the search's own arithmetic and marks pairs beyond radius_sq (or coincident) with +inf; fcb200_rg_select skips
+ * such entries, so the selected edge set equals that of a fresh search at the current positions.
+ *   cand_ptr [T+1], cand_id [cand_ptr[T]] as written by fcb200_rg_search; cand_d2 [cand_ptr[T]] out
+ */
+int fcb200_rg_refresh(const float* pos, const int32_t* sys, int32_t num_systems, const int32_t* targets, int64_t num_targets,
+                      const int32_t* cand_ptr, const int32_t* cand_id, float radius_sq, float* cand_d2, void* stream);
+
+/*
  * Allocation-free neighbour counting (no counterpart in the reference; added for embedders).
  *
  * Some hosts of this library cannot let it, or themselves, call cudaMalloc inside a time step: an MD

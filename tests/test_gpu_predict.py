@@ -1,0 +1,77 @@
+"""Predict-unit surface and the skin-distance neighbour list on the GPU."""
+
+import numpy as np
+import pytest
+import torch
+
+from fairchem_b200 import synthetic, weights
+
+pytestmark = pytest.mark.gpu
+
+
+def _sorted_edges(ei, co):
+    a = np.concatenate([ei.cpu().numpy().T, co.cpu().numpy().astype(np.int64)], axis=1)
+    return a[np.lexsort(a.T[::-1])]
+
+
+@pytest.mark.parametrize("make,reuses", [(lambda: synthetic.water_box(3000, seed=4), True),
+                                         # lattice sites on the cell faces: some atom is wrapped almost every step,
+                                         # which (correctly) forces a new search each time
+                                         (lambda: synthetic.fcc_cu((4, 4, 4), seed=1), False),
+                                         (lambda: synthetic.molecule_batch(6, seed=2), True)],
+                         ids=["water_3000", "fcc_cu_256", "molecules_6"])
+def test_skin_list_gives_the_edge_set_of_a_fresh_search_every_step(make, reuses):
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from fairchem_b200.graph import SkinNeighborList, radius_graph_pbc_b200
+
+    data = make().to("cuda")
+    nl = SkinNeighborList(6.0, 30, skin=0.6)
+    gen = torch.Generator(device="cuda").manual_seed(0)
+    box = torch.diagonal(data["cell"][0]) if bool(data["pbc"].all()) else None
+    for step in range(12):
+        ei, co, nb = nl.update(data)
+        ei_f, co_f, nb_f = radius_graph_pbc_b200(data, 6.0, 30, False, data["pbc"])
+        assert torch.equal(nb, nb_f)
+        assert np.array_equal(_sorted_edges(ei, co), _sorted_edges(ei_f, co_f)), f"step {step}"
+        assert bool((ei[1][1:] >= ei[1][:-1]).all())  # still grouped by target
+        # move every atom by up to 0.06 A per step; at step 8 a larger kick forces a new search
+        kick = 0.5 if step == 8 else 0.06
+        pos = data["pos"] + kick * (2 * torch.rand(data["pos"].shape, device="cuda", generator=gen) - 1) / 3 ** 0.5
+        if box is not None:  # the driver wraps atoms back into the cell: a wrapped atom must trigger a new search
+            pos = pos - torch.floor(pos / box) * box
+            pos = torch.where(pos >= box, torch.zeros_like(pos), pos)
+        data["pos"] = pos.contiguous()
+    assert nl.searches + nl.refreshes == 12 and nl.searches >= 2
+    if reuses:
+        assert nl.refreshes >= 6
+
+
+def test_predict_unit_matches_the_module_call():
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from fairchem_b200 import predict
+    from fairchem_b200.backbone import build_model, energy_forces
+
+    sd = weights.random_init_state_dict(weights.UMA_S, 0)
+    bb, head = build_model(weights.UMA_S, sd, edge_chunk_size=4096)
+    host = synthetic.water_box(600, seed=0)
+    ref = energy_forces(bb, head, host.to("cuda"))
+    table = torch.zeros(100, dtype=torch.float64)
+    table[1], table[8] = -0.5, -2.0
+    tasks = {"energy": predict.PredictTask("energy", "energy", ["omat", "omol"], normalizer=predict.Normalizer(0.25, 2.0),
+                                           element_references=predict.ElementReferences(table)),
+             "forces": predict.PredictTask("forces", "forces", ["omat", "omol"], level="atom", normalizer=predict.Normalizer(0.0, 2.0))}
+    unit = predict.B200PredictUnit(bb, head, tasks, skin=0.5)
+    pred = unit.predict(host)  # host tensors: moved to the device inside
+    z = host["atomic_numbers"]
+    e_want = ref["energy"] * 2.0 + 0.25 + float(table[z].sum())
+    assert abs(float(pred["energy"][0] - e_want[0])) < 1e-6 * abs(float(e_want[0]))
+    assert float((pred["forces"] - 2.0 * ref["forces"]).abs().max()) < 2e-6
+    raw = unit.predict(host, undo_element_references=False)
+    assert abs(float(raw["energy"][0] - (ref["energy"][0] * 2.0 + 0.25))) < 1e-6 * abs(float(ref["energy"][0]))
+    # device-resident input is used in place, and the neighbour list is reused on the second call
+    dev = host.to("cuda")
+    unit.predict(dev)
+    unit.predict(dev)
+    assert bb.neighbor_list.refreshes >= 1
