@@ -65,7 +65,7 @@ SIGNATURES = {
     "fcb200_exclusive_scan_i32": [P, P, I64, P],
     "fcb200_rg_fill_buckets": [P, P, I32, I64, P, P, P, P, I64, P],
     "fcb200_rg_search": [P, P, P, P, I64, P, P, F32, P, P, P, P, P],
-    "fcb200_rg_select": [P, P, P, I64, P, P, P, I32, P, P, P, P, P, P],
+    "fcb200_rg_select": [P, P, P, I64, P, P, P, I32, I32, P, P, P, P, P, P],
     "fcb200_rg_refresh": [P, P, I32, P, I64, P, P, F32, P, P],
     "fcb200_rg_neighbor_counts_static": [P, P, I32, I64, I64, P, P, I64, F32, P, P],
     "fcb200_gemm_tf32": [P, I64, P, P, I64, P, P, I64, I64, I32, I32, I32, P, P],

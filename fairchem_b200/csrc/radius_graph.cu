@@ -257,7 +257,7 @@ __global__ void __launch_bounds__(256)
 __global__ void __launch_bounds__(256)
     rg_select_kernel(const int32_t* __restrict__ sys, const int32_t* __restrict__ targets, const int32_t* __restrict__ target_sys,
                      int64_t num_targets, const int32_t* __restrict__ cand_ptr, const int32_t* __restrict__ cand_id,
-                     const float* __restrict__ cand_d2, int max_neighbors, int32_t* __restrict__ keep_count,
+                     const float* __restrict__ cand_d2, int max_neighbors, int strict, int32_t* __restrict__ keep_count,
                      const int32_t* __restrict__ edge_ptr, int64_t* __restrict__ edge_src, int64_t* __restrict__ edge_tgt,
                      int32_t* __restrict__ edge_offsets) {
     const int lane = threadIdx.x & 31;
@@ -280,23 +280,41 @@ __global__ void __launch_bounds__(256)
             int c = 0;
             for (int i = lane; i < m; i += 32) c += (__float_as_uint(cand_d2[b + i]) <= mid) ? 1 : 0;
             c = warp_sum_i(c);
-            if (c >= max_neighbors + 1) hi = mid; else lo = mid + 1;
+            if (c >= max_neighbors + (strict ? 0 : 1)) hi = mid; else lo = mid + 1;
         }
         thr = fminf(__fadd_rn(__uint_as_float(lo), 0.01f), __uint_as_float(kInf - 1u));
+        if (strict) thr = __uint_as_float(lo);  // exactly the k nearest: see below
+    }
+    // strict rule (enforce_max_neighbors_strictly, radius_graph_pbc.py:151-154): the k nearest and nothing else.  The
+    // bisection above found the k-th smallest value; everything below it is kept and the first of the candidates
+    // equal to it, in list order, fill what is left of the k places.
+    int quota = 0;
+    const bool strict_cut = strict && max_neighbors > 0 && live > max_neighbors;
+    if (strict_cut) {
+        int c = 0;
+        for (int i = lane; i < m; i += 32) c += (cand_d2[b + i] < thr) ? 1 : 0;
+        quota = max_neighbors - warp_sum_i(c);
     }
     if (edge_ptr == nullptr) {
         int c = 0;
-        for (int i = lane; i < m; i += 32) c += (cand_d2[b + i] <= thr) ? 1 : 0;
+        for (int i = lane; i < m; i += 32) c += (strict_cut ? cand_d2[b + i] < thr : cand_d2[b + i] <= thr) ? 1 : 0;
         c = warp_sum_i(c);
-        if (lane == 0) keep_count[t] = c;
+        if (lane == 0) keep_count[t] = c + (strict_cut ? quota : 0);
         return;
     }
     const Sys s = load_sys(sys, target_sys[t]);
     const int atom = targets ? targets[t] : (int)t;
     int w = edge_ptr[t];
+    int ties_taken = 0;
     for (int i0 = 0; i0 < m; i0 += 32) {
         const int i = i0 + lane;
-        const bool keep = i < m && cand_d2[b + i] <= thr;
+        const float d2 = i < m ? cand_d2[b + i] : __uint_as_float(kInf);
+        bool keep = i < m && (strict_cut ? d2 < thr : d2 <= thr);
+        if (strict_cut) {
+            const unsigned tied = __ballot_sync(kFull, i < m && d2 == thr);
+            keep = keep || (i < m && d2 == thr && ties_taken + __popc(tied & ((1u << lane) - 1u)) < quota);
+            ties_taken += __popc(tied);
+        }
         const unsigned mask = __ballot_sync(kFull, keep);
         if (keep) {
             const int64_t o = w + __popc(mask & ((1u << lane) - 1u));
@@ -406,15 +424,15 @@ int fcb200_rg_search(const float* pos, const int32_t* sys, const int32_t* target
 }
 
 int fcb200_rg_select(const int32_t* sys, const int32_t* targets, const int32_t* target_sys, int64_t num_targets,
-                     const int32_t* cand_ptr, const int32_t* cand_id, const float* cand_d2, int32_t max_neighbors,
+                     const int32_t* cand_ptr, const int32_t* cand_id, const float* cand_d2, int32_t max_neighbors, int32_t strict,
                      int32_t* keep_count, const int32_t* edge_ptr, int64_t* edge_src, int64_t* edge_tgt, int32_t* edge_offsets,
                      void* stream) {
     if (!sys || !target_sys || !cand_ptr || num_targets < 0) return FCB200_EINVAL;
     if (edge_ptr == nullptr ? !keep_count : (!edge_src || !edge_tgt || !edge_offsets)) return FCB200_EINVAL;
     if (num_targets == 0) return FCB200_OK;
     rg_select_kernel<<<(unsigned)((num_targets + 7) / 8), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        sys, targets, target_sys, num_targets, cand_ptr, cand_id, cand_d2, max_neighbors, keep_count, edge_ptr, edge_src, edge_tgt,
-        edge_offsets);
+        sys, targets, target_sys, num_targets, cand_ptr, cand_id, cand_d2, max_neighbors, strict != 0, keep_count, edge_ptr, edge_src,
+        edge_tgt, edge_offsets);
     return launch_status();
 }
 

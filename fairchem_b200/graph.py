@@ -174,7 +174,7 @@ def _search(data, radius: float, pbc=None) -> _Candidates:
                        cand_ptr=cand_ptr, cand_id=cand_id, cand_d2=cand_d2, device=dev, cell_dtype=data.cell.dtype)
 
 
-def _select(c: _Candidates, max_neighbors: int):
+def _select(c: _Candidates, max_neighbors: int, strict: bool = False):
     """Phase 4: the max-neighbour rule (get_max_neighbors_mask, radius_graph_pbc.py:74-189, non-strict form) and the
     compaction into (edge_index, cell_offsets, neighbors)."""
     dev, st = c.device, _stream()
@@ -182,14 +182,14 @@ def _select(c: _Candidates, max_neighbors: int):
     num_targets, k = c.num_targets, int(max_neighbors)
     keep_count = torch.empty(max(num_targets, 1), **i32)
     _lib.call("fcb200_rg_select", _p(c.sys_t), _p(c.targets), _p(c.target_sys), num_targets, _p(c.cand_ptr), _p(c.cand_id),
-              _p(c.cand_d2), k, _p(keep_count), None, None, None, None, st)
+              _p(c.cand_d2), k, int(strict), _p(keep_count), None, None, None, None, st)
     edge_ptr = torch.empty(num_targets + 1, **i32)
     _lib.call("fcb200_exclusive_scan_i32", _p(keep_count), _p(edge_ptr), num_targets, st)
     num_edges = int(edge_ptr[-1].item())
     edge_index = torch.empty((2, max(num_edges, 1)), dtype=torch.int64, device=dev)
     offsets = torch.empty((max(num_edges, 1), 3), **i32)
     _lib.call("fcb200_rg_select", _p(c.sys_t), _p(c.targets), _p(c.target_sys), num_targets, _p(c.cand_ptr), _p(c.cand_id),
-              _p(c.cand_d2), k, None, _p(edge_ptr), _p(edge_index[0]), _p(edge_index[1]), _p(offsets), st)
+              _p(c.cand_d2), k, int(strict), None, _p(edge_ptr), _p(edge_index[0]), _p(edge_index[1]), _p(offsets), st)
     edge_index = edge_index[:, :num_edges]
     offsets = offsets[:num_edges]
     if c.nsys == 1:
@@ -203,10 +203,7 @@ def _select(c: _Candidates, max_neighbors: int):
 def radius_graph_pbc_b200(data, radius, max_num_neighbors_threshold, enforce_max_neighbors_strictly: bool = False,
                           pbc: torch.Tensor | None = None):
     """(edge_index [2,E] int64 (source; target), cell_offsets [E,3], neighbors [B] int64)."""
-    if enforce_max_neighbors_strictly:
-        raise NotImplementedError("strict max-neighbour selection is not part of the eSCN-MD path "
-                                  "(escn_md.py:372 always passes False)")
-    return _select(_search(data, radius, pbc), max_num_neighbors_threshold)
+    return _select(_search(data, radius, pbc), max_num_neighbors_threshold, bool(enforce_max_neighbors_strictly))
 
 
 class SkinNeighborList:

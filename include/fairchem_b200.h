@@ -248,12 +248,14 @@ int fcb200_rg_search(const float* pos, const int32_t* sys, const int32_t* target
                      int64_t num_targets, const int32_t* cell_ptr, const float* bucket, float radius_sq,
                      int32_t* cand_count, const int32_t* cand_ptr, int32_t* cand_id, float* cand_d2, void* stream);
 /*
- * Phase 4: max-neighbour rule per target (non-strict: keep d2 <= d2_sorted[k] + 0.01f when a target
- * has more than k candidates).  Pass A: edge_ptr == NULL, writes keep_count[t].  Pass B: writes the
- * kept edges: src/tgt atom ids (int64, the reference's edge_index rows), cell offsets [E,3] int32.
+ * Phase 4: max-neighbour rule per target (get_max_neighbors_mask, graph/radius_graph_pbc.py:74-189).  strict == 0:
+ * keep d2 <= d2_sorted[k] + 0.01f when a target has more than k candidates; strict != 0: exactly the k nearest
+ * (candidates tied with the k-th keep their list order).  Candidates marked +inf (fcb200_rg_refresh) are skipped.
+ * Pass A: edge_ptr == NULL, writes keep_count[t].  Pass B: writes the kept edges: src/tgt atom ids (int64, the
+ * reference's edge_index rows), cell offsets [E,3] int32.
  */
 int fcb200_rg_select(const int32_t* sys, const int32_t* targets, const int32_t* target_sys, int64_t num_targets,
-                     const int32_t* cand_ptr, const int32_t* cand_id, const float* cand_d2, int32_t max_neighbors,
+                     const int32_t* cand_ptr, const int32_t* cand_id, const float* cand_d2, int32_t max_neighbors, int32_t strict,
                      int32_t* keep_count, const int32_t* edge_ptr, int64_t* edge_src, int64_t* edge_tgt,
                      int32_t* edge_offsets, void* stream);
 

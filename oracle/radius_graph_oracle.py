@@ -10,6 +10,7 @@ comparisons of squared distances, which this file reproduces operation by operat
   keep d2 <= float32(r*r) and d2 != 0                                (:753-759)
   per target with more than k candidates: sort d2, keep d2 <= d2_sorted[k] + float32(0.01)
   (k = max_neighbors used as a 0-based index, non-strict mode)       (:150-160)
+  strict mode (``strict=True``): the first k of the sorted list                 (:151-154)
 
 Candidates are found here with a k-d tree (any superset works) and then re-tested with the
 float32 rule above.  The result is the edge *set*, returned sorted by (target, source, offset)
@@ -49,7 +50,7 @@ def _offset_vectors(cell: np.ndarray, images: np.ndarray) -> np.ndarray:
     return ((t0 + t1).astype(F32) + t2).astype(F32)
 
 
-def radius_graph(pos, cell, pbc, natoms, radius: float, max_neighbors: int, node_partition=None):
+def radius_graph(pos, cell, pbc, natoms, radius: float, max_neighbors: int, node_partition=None, strict: bool = False):
     """Edge set of a batch.
 
     Returns ``edge_index [2,E] int64`` (row 0 source, row 1 target), ``cell_offsets [E,3] int64``
@@ -111,6 +112,9 @@ def radius_graph(pos, cell, pbc, natoms, radius: float, max_neighbors: int, node
             ptr = np.concatenate([[0], np.cumsum(counts)])
             for a in np.nonzero(counts > max_neighbors)[0]:
                 seg = e_d2[ptr[a]:ptr[a + 1]]
+                if strict:  # enforce_max_strictly (:151-154): the first k of the sorted list, ties in sorted order
+                    keep[ptr[a] + max_neighbors:ptr[a + 1]] = False
+                    continue
                 thr = F32(seg[max_neighbors] + F32(0.01))
                 keep[ptr[a]:ptr[a + 1]] = seg <= thr
         e_src, e_tgt, e_img, e_d2 = e_src[keep], e_tgt[keep], e_img[keep], e_d2[keep]

@@ -103,3 +103,26 @@ def test_full_size_properties_water_100k(rg):
     # idempotence: a second build gives the identical list, order included
     ei2, co2, _ = rg.radius_graph_pbc_b200(dd, 6.0, 30, False, dd.pbc)
     assert torch.equal(ei, ei2) and torch.equal(co, co2)
+
+
+@pytest.mark.parametrize("pbc,k,expect", [([True, False, False], 10, 4), ([True, False, False], 1, 1),
+                                           ([True, True, False], 20, 18), ([True, True, False], 2, 2),
+                                           ([True, True, True], 100, 78), ([True, True, True], 10, 10)])
+def test_known_neighbor_counts_strict(rg, pbc, k, expect):
+    # the enforce_max_neighbors_strictly=True answers of tests/core/graph/test_radius_graph.py:117-258 of the reference
+    dd = fcc_primitive(pbc).to("cuda")
+    ei, co, nb = rg.radius_graph_pbc_b200(dd, 6.0, k, True, dd.pbc)
+    assert int(nb[0]) == expect and ei.shape[1] == expect
+
+
+def test_strict_rule_keeps_exactly_the_k_nearest(rg):
+    """On a system without degenerate distances the strict edge set equals the oracle's; every target keeps min(k, m)."""
+    d = synthetic.water_box(900, seed=7)
+    dd = d.to("cuda")
+    k = 12
+    ei, co, nb = rg.radius_graph_pbc_b200(dd, 6.0, k, True, dd.pbc)
+    ei, co = ei.cpu().numpy(), co.cpu().numpy().astype(np.int64)
+    p = G.sort_edges(ei, co)
+    ei_o, co_o, _, nb_o = G.radius_graph(d.pos.numpy(), d.cell.numpy(), d.pbc.numpy(), d.natoms.numpy(), 6.0, k, strict=True)
+    assert np.array_equal(ei[:, p], ei_o) and np.array_equal(co[p], co_o) and int(nb[0]) == int(nb_o[0])
+    assert np.array_equal(np.bincount(ei[1], minlength=900), np.full(900, k))
