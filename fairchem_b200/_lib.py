@@ -45,7 +45,7 @@ SIGNATURES = {
     "fcb200_lx_so2_gate_fwd_h": [P, P, P, P, I64, I32, I32, P],
     "fcb200_lx_so2_gate_bwd_h": [P, P, P, P, P, I64, I32, I32, P],
     "fcb200_conv_pair_capacity": [],
-    "fcb200_so2_conv_fused": [P, P, I64, I64, P, P, P, P, P, P, P, I32, P, I64, I64, P, P, I64, I64, P, P, I64, I32, P, P],
+    "fcb200_so2_conv_fused": [P, P, I64, I64, P, P, P, P, P, P, P, I32, I32, P, I64, I64, P, P, I64, I64, P, P, I64, I32, P, P],
     "fcb200_split_f16": [P, I64, P, P, F32, I64, I64, P],
     "fcb200_lx_gather_rotate_fwd": [P, P, P, P, P, P, I64, I64, I32, I32, P],
     "fcb200_lx_gather_rotate_bwd": [P, P, P, P, P, P, P, P, P, P, I64, I64, I32, I32, P],

@@ -559,7 +559,7 @@ def _fused_linear(x, w: torch.Tensor, bias, out: torch.Tensor, label: str = "_li
     tiles = []
     for r0 in range(0, n, 128):
         tiles += [0, k, 0, r0, r0, ops.CONV_PLAIN, 0, 0, 0]
-    ops.so2_conv_fused_.raw(x[0], x[1], [hi], [lo], [sc], bias, tiles, out, None, None, None, None, _status(out.device), label)
+    ops.so2_conv_fused_.raw(x[0], x[1], [hi], [lo], [sc], bias, tiles, 0, out, None, None, None, None, _status(out.device), label)
     return out
 
 
@@ -697,9 +697,7 @@ class _FusedConvPlan:
                 flags = ops.CONV_KEEP if keep else 0
                 if r == 0:
                     return c - gates, ops.CONV_SILU, c, 0, flags
-                # the first gated tile waits for this warp's stores of the gate scalars before reading them back
-                sync = ops.CONV_SYNC if (r == 1 and j == 0) else 0
-                return c - gates, ops.CONV_GATED, c, (deg[r] - 1) * h + j, flags | sync
+                return c - gates, ops.CONV_GATED, c, (deg[r] - 1) * h + j, flags
             return _fused_tiles(s1, False, describe)
 
         rows_of = {l: [r for r, d in enumerate(deg) if d == l] for l in range(1, lmax + 1)}
@@ -753,14 +751,14 @@ def _fused_conv1_gate(ew, m, y_keep):
     ec, dev = m[0].shape[0], m[0].device
     y = y_keep if y_keep is not None else torch.empty(ec, p.gates, dtype=torch.float32, device=dev)
     a = _new_operand(ec, p.y_width - p.gates, dev)
-    ops.so2_conv_fused_.raw(m[0], m[1], list(p.w1[0]), list(p.w1[1]), list(p.w1[2]), p.bias1, p.fwd1[y_keep is not None], y,
+    ops.so2_conv_fused_.raw(m[0], m[1], list(p.w1[0]), list(p.w1[1]), list(p.w1[2]), p.bias1, p.fwd1[y_keep is not None], p.gates // 128, y,
                             a[0], a[1], None, None, _status(dev), "_conv1_gate")
     return a
 
 
 def _fused_conv2(ew, a, out):
     p = _fused_plan(ew)
-    ops.so2_conv_fused_.raw(a[0], a[1], list(p.w2[0]), list(p.w2[1]), list(p.w2[2]), p.bias2, p.fwd2, out, None, None,
+    ops.so2_conv_fused_.raw(a[0], a[1], list(p.w2[0]), list(p.w2[1]), list(p.w2[2]), p.bias2, p.fwd2, 0, out, None, None,
                             None, None, _status(out.device), "_conv2")
     return out
 
@@ -770,7 +768,7 @@ def _fused_conv2_gate_backward(ew, grad_msg, y, scale):
     p = _fused_plan(ew)
     ec, dev = y.shape[0], y.device
     gy = _new_operand(ec, p.y_width, dev)
-    ops.so2_conv_fused_.raw(grad_msg[0], grad_msg[1], list(p.w2t[0]), list(p.w2t[1]), list(p.w2t[2]), None, p.bwd2, y,
+    ops.so2_conv_fused_.raw(grad_msg[0], grad_msg[1], list(p.w2t[0]), list(p.w2t[1]), list(p.w2t[2]), None, p.bwd2, len(p.bwd2) // 9, y,
                             gy[0], gy[1], scale, scale, _status(dev), "_conv2_gate_bwd")
     return gy
 
@@ -779,7 +777,7 @@ def _fused_conv1_backward(ew, gy, scale):
     p = _fused_plan(ew)
     ec, dev = gy[0].shape[0], gy[0].device
     gm = torch.empty(ec, sum(w.shape[1] for w in p.w1[0]), dtype=torch.float32, device=dev)
-    ops.so2_conv_fused_.raw(gy[0], gy[1], list(p.w1t[0]), list(p.w1t[1]), list(p.w1t[2]), None, p.bwd1, gm, None, None,
+    ops.so2_conv_fused_.raw(gy[0], gy[1], list(p.w1t[0]), list(p.w1t[1]), list(p.w1t[2]), None, p.bwd1, 0, gm, None, None,
                             scale, None, _status(dev), "_conv1_bwd")
     return gm
 

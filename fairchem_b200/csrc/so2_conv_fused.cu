@@ -30,13 +30,13 @@ using namespace f16;
 
 enum Mode : int32_t {
     kPlain = 0,     // float32 tile -> y[:, out_col ...] through TMA
-    kGateRaw = 1,   // (unused: gate scalars are kPlain tiles; the first kGated tile after them carries kSync)
+    kGateRaw = 1,   // (unused: gate scalars are kPlain tiles listed before Plan::rot_begin)
     kSilu = 2,      // planes[:, out_col ...] = split(v * sigmoid(v));                       keep: y[:, y_col ...] = v
     kGated = 3,     // planes[:, out_col ...] = split(v * sigmoid(y[:, gate_col ...]));      keep: y[:, y_col ...] = v
     kSiluBwd = 4,   // planes[:, out_col ...] = split(v * d/dy silu(y[:, y_col ...]))
     kGatedBwd = 5,  // planes[:, out_col ...] = split(v * sigmoid(gate)); gate gradient summed over consecutive tiles
 };
-enum Flags : int32_t { kFirst = 1, kLast = 2, kKeep = 4, kSync = 8 };
+enum Flags : int32_t { kFirst = 1, kLast = 2, kKeep = 4 };
 
 struct Tile {
     int32_t a_col;     // first input column of this tile's K range
@@ -53,18 +53,31 @@ struct Tile {
 constexpr int kMaxTiles = 40;  // lmax 4: 19 rows x 2C = 38 column tiles in the conv-1 backward
 struct Plan {
     int32_t ntiles;
-    int32_t pad[3];
+    int32_t rot_begin;  // tiles [rot_begin, ntiles) may run in any order: every CTA starts at a different one of them
+    int32_t pad[2];
     Tile t[kMaxTiles];
 };
 
-constexpr int kStages = 4;
+// Loop position -> tile.  All CTAs walk the same weight tiles; started together they would ask L2 for the same lines
+// at the same moment, so each CTA (or pair) begins the freely ordered part of the list at its own offset.
+__device__ __forceinline__ int tile_at(const Plan& plan, int pos, int rot) {
+    const int free = plan.ntiles - plan.rot_begin;
+    return (pos < plan.rot_begin || free <= 1) ? pos : plan.rot_begin + (pos - plan.rot_begin + rot) % free;
+}
+
+// NBUF staging tiles per epilogue warp: 3 for plans with gated modes, 2 for plans of plain tiles only, which leaves
+// room for one more stage of the operand ring (the ring's depth is what covers the latency of the operand loads)
+template <int NBUF> struct Cfg {
+    static constexpr int kStages = NBUF == 3 ? 4 : 5;
+    static constexpr int kPairStages = NBUF == 3 ? 5 : 6;
+    static constexpr int kEpiWarpBytes = NBUF * 4096;
+};
 constexpr int kStageBytes = 4 * BM * BK * 2;           // A_hi | A_lo | W_hi | W_lo, 8 KiB each
 constexpr int kHalfTile = BM * BK * 2;
 constexpr int kEpiWarps = 8;
-constexpr int kEpiWarpBytes = 3 * 4096;                // three 32 x 32 float32 (or hi|lo half) tiles per epilogue warp
 constexpr int kThreads = 64 + 32 * kEpiWarps;          // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
 constexpr int kAccCols = 2 * BN, kTmemCols = 2 * kAccCols;
-constexpr int kSmemBytes = kStages * kStageBytes + kEpiWarps * kEpiWarpBytes + 1024 + 256;
+template <int NBUF> constexpr int smem_bytes() { return Cfg<NBUF>::kStages * kStageBytes + kEpiWarps * Cfg<NBUF>::kEpiWarpBytes + 1024 + 256; }
 
 struct Params {
     const float* bias[3];
@@ -175,7 +188,7 @@ __device__ __forceinline__ void ld_row8(uint32_t base, int lane, int u, float (&
 // PAIR: the CTA is one of a pair that shares 256-row tiles; `unit` is the tile stride owner (CTA or pair index),
 // `units` their number, `row_off` this CTA's first row inside a tile, and `tempty0` a shared::cluster address of the
 // leader's accumulator-free barriers.
-template <bool PAIR>
+template <bool PAIR, int NBUF>
 __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtensorMap& map_ohi, const CUtensorMap& map_olo,
                                          const Plan& plan, const Params& prm, int64_t tiles_m, uint32_t tmem_base,
                                          uint32_t epi_base, uint32_t tfull0, uint32_t tempty0, uint32_t ld_bar0,
@@ -186,7 +199,7 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
     const int q = warp & 3;
     const int ew = warp - 2;
     const int half = ew >> 2;
-    const uint32_t b0 = epi_base + (uint32_t)(ew * kEpiWarpBytes), b1 = b0 + 4096u, b2 = b0 + 8192u;
+    const uint32_t b0 = epi_base + (uint32_t)(ew * Cfg<NBUF>::kEpiWarpBytes), b1 = b0 + 4096u, b2 = b0 + 8192u;  // b2 only if NBUF == 3
     const uint32_t ld_bar = ld_bar0 + 8u * ew;
     uint32_t ld_phase = 0;
     int rot = 0;             // plain chunks staged so far (output buffer = rot % 3)
@@ -203,7 +216,7 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
         const int64_t row0 = mt * kTileRows + row_off + q * 32;
         const bool live = row0 < prm.m_total;  // else this warp's 32 rows lie entirely below the matrix
         for (int ti = 0; ti < ntiles; ++ti, ++tcount) {
-            const Tile& t = plan.t[ti];
+            const Tile& t = plan.t[tile_at(plan, ti, (int)(unit % 64))];
             const int buf = (int)(tcount & 1);
             const uint32_t use = (uint32_t)((tcount >> 1) & 1);
             ok = mbar_wait(tfull0 + 8u * buf, use, abort_flag);
@@ -225,7 +238,8 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
                 if (live && n_in > 0) {
                     if (lane == 0) {
                         if (last_kind == 0 || (n_in == 2 && b1_stored)) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                        if (t.flags & kSync) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // gate tiles stored by this thread have landed
+                        // first tile after the gate scalars: this thread's stores of them have landed before they are read back
+                        if (ti == plan.rot_begin && plan.rot_begin > 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");
                         mbar_expect_tx(ld_bar, (uint32_t)(n_in * 4096));
                         tma_load_2d(b0, &map_y, (mode == kSiluBwd ? t.y_col : t.gate_col) + col, (int)row0, ld_bar);
                         if (n_in == 2) tma_load_2d(b1, &map_y, t.y_col + col, (int)row0, ld_bar);
@@ -264,9 +278,10 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
                 if (mode == kPlain) {
                     if (lane == 0) {
                         if (last_kind != 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");
-                        else asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory");
+                        else if (NBUF == 3) asm volatile("cp.async.bulk.wait_group.read 2;" ::: "memory");
+                        else asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
                     }
-                    st_out = b0 + (uint32_t)((rot % 3) * 4096);
+                    st_out = b0 + (uint32_t)((rot % NBUF) * 4096);
                     ++rot;
                     last_kind = 0;
                 } else {
@@ -366,6 +381,7 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all stores of this warp have landed
 }
 
+template <int NBUF>
 __global__ void __launch_bounds__(kThreads, 1)
     so2_conv_fused_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
                           const __grid_constant__ CUtensorMap map_whi0, const __grid_constant__ CUtensorMap map_wlo0,
@@ -374,11 +390,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                           const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_ohi,
                           const __grid_constant__ CUtensorMap map_olo, const __grid_constant__ Plan plan,
                           const __grid_constant__ Params prm, int64_t tiles_m) {
-    constexpr int S = kStages;
+    constexpr int S = Cfg<NBUF>::kStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t epi_base = base + S * kStageBytes;
-    const uint32_t bar_base = epi_base + kEpiWarps * kEpiWarpBytes;
+    const uint32_t bar_base = epi_base + kEpiWarps * Cfg<NBUF>::kEpiWarpBytes;
     // barrier block: full[S] | empty[S] | tmem_full[2] | tmem_empty[2] | tmem slot, abort flag, range flag, pad | ld[8]
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
@@ -427,7 +443,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             bool ok = true;
             for (int64_t mt = blockIdx.x; mt < tiles_m && ok; mt += gridDim.x) {
                 for (int ti = 0; ti < ntiles && ok; ++ti) {
-                    const Tile& t = plan.t[ti];
+                    const Tile& t = plan.t[tile_at(plan, ti, (int)(blockIdx.x % 64))];
                     const CUtensorMap* whi = t.w == 0 ? &map_whi0 : (t.w == 1 ? &map_whi1 : &map_whi2);
                     const CUtensorMap* wlo = t.w == 0 ? &map_wlo0 : (t.w == 1 ? &map_wlo1 : &map_wlo2);
                     const int num_kb = t.k / BK;
@@ -451,7 +467,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             bool ok = true;
             for (int64_t mt = blockIdx.x; mt < tiles_m && ok; mt += gridDim.x) {
                 for (int ti = 0; ti < ntiles && ok; ++ti, ++tcount) {
-                    const int num_kb = plan.t[ti].k / BK;
+                    const int num_kb = plan.t[tile_at(plan, ti, (int)(blockIdx.x % 64))].k / BK;
                     const int buf = (int)(tcount & 1);
                     const uint32_t use = (uint32_t)((tcount >> 1) & 1);
                     ok = mbar_wait(tempty_bar(buf), use ^ 1u, abort_flag);  // epilogue has drained this accumulator
@@ -482,7 +498,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             }
         }
     } else {
-        epilogue<false>(map_y, map_ohi, map_olo, plan, prm, tiles_m, tmem_base, epi_base, tfull_bar(0), tempty_bar(0), ld_bar(0),
+        epilogue<false, NBUF>(map_y, map_ohi, map_olo, plan, prm, tiles_m, tmem_base, epi_base, tfull_bar(0), tempty_bar(0), ld_bar(0),
                         abort_flag, range_flag, blockIdx.x, gridDim.x, 0);
     }
 
@@ -518,9 +534,11 @@ __global__ void __launch_bounds__(kThreads, 1)
 // an accumulator in both CTAs.
 // ---------------------------------------------------------------------------------------------------------------
 constexpr int kPairStageBytes = 3 * kHalfTile;  // 24 KiB
-constexpr int kPairStages = 5;
-constexpr int kPairSmemBytes = kPairStages * kPairStageBytes + kEpiWarps * kEpiWarpBytes + 1024 + 256;
+template <int NBUF> constexpr int pair_smem_bytes() {
+    return Cfg<NBUF>::kPairStages * kPairStageBytes + kEpiWarps * Cfg<NBUF>::kEpiWarpBytes + 1024 + 256;
+}
 
+template <int NBUF>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
     so2_conv_pair_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
                          const __grid_constant__ CUtensorMap map_whi0, const __grid_constant__ CUtensorMap map_wlo0,
@@ -529,11 +547,11 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
                          const __grid_constant__ CUtensorMap map_y,
                          const __grid_constant__ CUtensorMap map_ohi, const __grid_constant__ CUtensorMap map_olo,
                          const __grid_constant__ Plan plan, const __grid_constant__ Params prm, int64_t tiles_m) {
-    constexpr int S = kPairStages;
+    constexpr int S = Cfg<NBUF>::kPairStages;
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const uint32_t epi_base = base + S * kPairStageBytes;
-    const uint32_t bar_base = epi_base + kEpiWarps * kEpiWarpBytes;
+    const uint32_t bar_base = epi_base + kEpiWarps * Cfg<NBUF>::kEpiWarpBytes;
     // barrier block as in the single-CTA kernel; full[] and tmem_empty[] are used in the leader only
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
     auto empty_bar = [&](int s) { return bar_base + 8u * (S + s); };
@@ -587,7 +605,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             for (int64_t mt = pair; mt < tiles_m && ok; mt += pairs) {
                 const int row = (int)(mt * 2 * BM + rank * BM);
                 for (int ti = 0; ti < ntiles && ok; ++ti) {
-                    const Tile& t = plan.t[ti];
+                    const Tile& t = plan.t[tile_at(plan, ti, (int)(pair % 64))];
                     const CUtensorMap* whi = t.w == 0 ? &map_whi0 : (t.w == 1 ? &map_whi1 : &map_whi2);
                     const CUtensorMap* wlo = t.w == 0 ? &map_wlo0 : (t.w == 1 ? &map_wlo1 : &map_wlo2);
                     const int r_hi = t.w_row + (int)rank * 32, r_lo = t.w_row + (int)rank * 64;
@@ -616,7 +634,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             bool ok = true;
             for (int64_t mt = pair; mt < tiles_m && ok; mt += pairs) {
                 for (int ti = 0; ti < ntiles && ok; ++ti, ++tcount) {
-                    const int num_kb = plan.t[ti].k / BK;
+                    const int num_kb = plan.t[tile_at(plan, ti, (int)(pair % 64))].k / BK;
                     const int buf = (int)(tcount & 1);
                     const uint32_t use = (uint32_t)((tcount >> 1) & 1);
                     ok = mbar_wait(tempty_bar(buf), use ^ 1u, abort_flag);  // both epilogues have drained this accumulator
@@ -646,7 +664,7 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
             }
         }
     } else {
-        epilogue<true>(map_y, map_ohi, map_olo, plan, prm, tiles_m, tmem_base, epi_base, tfull_bar(0), map_to_cta(tempty_bar(0), 0),
+        epilogue<true, NBUF>(map_y, map_ohi, map_olo, plan, prm, tiles_m, tmem_base, epi_base, tfull_bar(0), map_to_cta(tempty_bar(0), 0),
                        ld_bar(0), abort_flag, range_flag, pair, pairs, (int)rank * BM);
     }
 
@@ -701,7 +719,7 @@ static int pair_capacity() {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * 74, 1, 1);
     cfg.blockDim = dim3(kThreads, 1, 1);
-    cfg.dynamicSmemBytes = kPairSmemBytes;
+    cfg.dynamicSmemBytes = pair_smem_bytes<3>();
     cudaLaunchAttribute attr[1];
     attr[0].id = cudaLaunchAttributeClusterDimension;
     attr[0].val.clusterDim.x = 2;
@@ -710,7 +728,7 @@ static int pair_capacity() {
     cfg.attrs = attr;
     cfg.numAttrs = 1;
     int n = 0;
-    if (cudaOccupancyMaxActiveClusters(&n, so2_conv_pair_kernel, &cfg) != cudaSuccess || n <= 0) {
+    if (cudaOccupancyMaxActiveClusters(&n, so2_conv_pair_kernel<3>, &cfg) != cudaSuccess || n <= 0) {
         cudaGetLastError();
         n = sm_count() / 2;
     }
@@ -728,7 +746,7 @@ extern "C" int fcb200_conv_pair_capacity(void) { return fused::pair_capacity(); 
 extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t lda, int64_t a_cols, const void* const* w_hi,
                                      const void* const* w_lo, const int64_t* w_rows, const int64_t* w_cols,
                                      const float* w_scale, const float* const* bias, const int32_t* tiles, int32_t num_tiles,
-                                     float* y, int64_t ldy, int64_t y_cols, void* o_hi, void* o_lo, int64_t ldo, int64_t o_cols,
+                                     int32_t rot_begin, float* y, int64_t ldy, int64_t y_cols, void* o_hi, void* o_lo, int64_t ldo, int64_t o_cols,
                                      const float* a_scale, const float* o_scale, int64_t m, int32_t variant, int32_t* status,
                                      void* stream) {
     using namespace fused;
@@ -743,8 +761,11 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
         if (!o_hi || !o_lo || ldo % 8 || ldo < o_cols) return FCB200_EINVAL;
         if (!aligned16(o_hi) || !aligned16(o_lo)) return FCB200_EALIGN;
     }
+    if (rot_begin < 0 || rot_begin > num_tiles) return FCB200_EINVAL;
     plan.ntiles = num_tiles;
+    plan.rot_begin = rot_begin;
     bool used[3] = {false, false, false};
+    bool plain_only = true;
     for (int i = 0; i < num_tiles; ++i) {
         Tile& t = plan.t[i];
         const int32_t* d = tiles + 9 * i;
@@ -763,6 +784,7 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
         if (uses_y && (t.y_col < 0 || t.y_col % 4 || t.y_col + BN > y_cols)) return FCB200_EINVAL;
         if (t.mode == kGatedBwd && t.gate_col + BN > o_cols) return FCB200_EINVAL;
         used[t.w] = true;
+        plain_only = plain_only && t.mode == kPlain;
     }
     if (m == 0) return FCB200_OK;
     CUtensorMap mah, mal, mw[6], my, moh, mol;
@@ -805,21 +827,35 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
             if (!rc) rc = map_half(&mp[2 * i + 1], w_lo[j], w_rows[j], w_cols[j], w_cols[j], 64);
             if (rc) return rc;
         }
-        static bool attr_done[64] = {};
-        if (const int arc = ensure_dynamic_smem(so2_conv_pair_kernel, kPairSmemBytes, attr_done)) return arc;
         const int64_t tiles_m = (m + 2 * BM - 1) / (2 * BM);
         const int max_pairs = pair_capacity();
         if (max_pairs <= 0) return FCB200_EINVAL;
         const int pairs = (int)(tiles_m < max_pairs ? tiles_m : max_pairs);
-        so2_conv_pair_kernel<<<2 * pairs, kThreads, kPairSmemBytes, st>>>(mah, mal, mp[0], mp[1], mp[2], mp[3], mp[4], mp[5], my, moh,
-                                                                         mol, plan, prm, tiles_m);
+        if (plain_only) {
+            static bool attr_done[64] = {};
+            if (const int arc = ensure_dynamic_smem(so2_conv_pair_kernel<2>, pair_smem_bytes<2>(), attr_done)) return arc;
+            so2_conv_pair_kernel<2><<<2 * pairs, kThreads, pair_smem_bytes<2>(), st>>>(mah, mal, mp[0], mp[1], mp[2], mp[3], mp[4],
+                                                                                      mp[5], my, moh, mol, plan, prm, tiles_m);
+        } else {
+            static bool attr_done[64] = {};
+            if (const int arc = ensure_dynamic_smem(so2_conv_pair_kernel<3>, pair_smem_bytes<3>(), attr_done)) return arc;
+            so2_conv_pair_kernel<3><<<2 * pairs, kThreads, pair_smem_bytes<3>(), st>>>(mah, mal, mp[0], mp[1], mp[2], mp[3], mp[4],
+                                                                                      mp[5], my, moh, mol, plan, prm, tiles_m);
+        }
         return launch_status();
     }
-    static bool attr_done[64] = {};
-    if (const int arc = ensure_dynamic_smem(so2_conv_fused_kernel, kSmemBytes, attr_done)) return arc;
     const int64_t tiles_m = (m + BM - 1) / BM;
     const int grid = (int)(tiles_m < sm_count() ? tiles_m : sm_count());
-    so2_conv_fused_kernel<<<grid, kThreads, kSmemBytes, st>>>(mah, mal, mw[0], mw[1], mw[2], mw[3], mw[4], mw[5], my, moh, mol, plan,
-                                                              prm, tiles_m);
+    if (plain_only) {
+        static bool attr_done[64] = {};
+        if (const int arc = ensure_dynamic_smem(so2_conv_fused_kernel<2>, smem_bytes<2>(), attr_done)) return arc;
+        so2_conv_fused_kernel<2><<<grid, kThreads, smem_bytes<2>(), st>>>(mah, mal, mw[0], mw[1], mw[2], mw[3], mw[4], mw[5], my, moh,
+                                                                         mol, plan, prm, tiles_m);
+    } else {
+        static bool attr_done[64] = {};
+        if (const int arc = ensure_dynamic_smem(so2_conv_fused_kernel<3>, smem_bytes<3>(), attr_done)) return arc;
+        so2_conv_fused_kernel<3><<<grid, kThreads, smem_bytes<3>(), st>>>(mah, mal, mw[0], mw[1], mw[2], mw[3], mw[4], mw[5], my, moh,
+                                                                         mol, plan, prm, tiles_m);
+    }
     return launch_status();
 }

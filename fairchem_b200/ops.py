@@ -550,20 +550,21 @@ def gemm_f16x2_presplit_(a_hi: Tensor, a_lo: Tensor, w_hi: Tensor, w_lo: Tensor,
 
 # epilogue modes and flags of so2_conv_fused_ (csrc/so2_conv_fused.cu)
 CONV_PLAIN, CONV_GATE_RAW, CONV_SILU, CONV_GATED, CONV_SILU_BWD, CONV_GATED_BWD = range(6)
-CONV_FIRST, CONV_LAST, CONV_KEEP, CONV_SYNC = 1, 2, 4, 8
+CONV_FIRST, CONV_LAST, CONV_KEEP = 1, 2, 4
 CONV_MAX_TILES = 40
 CONV_VARIANT = 0  # default launch form of so2_conv_fused_ (0: one CTA per 128-edge tile, 1: CTA pairs on 256-edge tiles)
 
 
 @_op("so2_conv_fused", ("y", "o_hi", "o_lo", "status"))
 def so2_conv_fused_(a_hi: Tensor, a_lo: Tensor, w_hi: List[Tensor], w_lo: List[Tensor], w_scale: List[float],
-                    bias0: Optional[Tensor], tiles: List[int], y: Tensor, o_hi: Optional[Tensor], o_lo: Optional[Tensor],
+                    bias0: Optional[Tensor], tiles: List[int], rot_begin: int, y: Tensor, o_hi: Optional[Tensor], o_lo: Optional[Tensor],
                     a_scale: Optional[Tensor], o_scale: Optional[Tensor], status: Tensor, label: str = "",
                     variant: int = -1) -> None:
     """One launch for all m-blocks of an SO(2) convolution with the gate (or its derivative) in the epilogue.
 
     ``a_hi/a_lo`` [E, Ka] are the input planes, ``w_*`` the (up to three) half-split weight matrices, ``tiles`` a flat
-    list of 9 integers per 128-column output tile (a_col, k, w, w_row, out_col, mode, y_col, gate_col, flags).  ``y``
+    list of 9 integers per 128-column output tile (a_col, k, w, w_row, out_col, mode, y_col, gate_col, flags); tiles from
+    position ``rot_begin`` on may run in any order (every CTA starts at a different one).  ``y``
     [E, >=gates] float32 receives the float32 modes and the raw gate scalars and is read by the gated modes; ``o_hi/o_lo``
     receive the split modes.  ``variant`` 0 runs one CTA per 128-edge tile, 1 CTA pairs on 256-edge tiles (default:
     the module-level ``CONV_VARIANT``)."""
@@ -598,7 +599,7 @@ def so2_conv_fused_(a_hi: Tensor, a_lo: Tensor, w_hi: List[Tensor], w_lo: List[T
     flops = 2 * m * 128 * sum(tiles[9 * i + 1] for i in range(nt))
     nbytes = 4 * m * (a_hi.shape[1] + 128 * nt)
     _launch("so2_conv_fused" + label, "fcb200_so2_conv_fused",
-            (_p(a_hi), _p(a_lo), a_hi.stride(0), a_hi.shape[1], whi, wlo, rows, cols, scales, biases, tl, nt,
+            (_p(a_hi), _p(a_lo), a_hi.stride(0), a_hi.shape[1], whi, wlo, rows, cols, scales, biases, tl, nt, rot_begin,
              _p(y), y.stride(0), y.shape[1], _p(o_hi), _p(o_lo), 0 if o_hi is None else o_hi.stride(0),
              0 if o_hi is None else o_hi.shape[1], _p(a_scale), _p(o_scale), m, CONV_VARIANT if variant < 0 else variant,
              _p(status), _stream()), nbytes=nbytes, flops=flops)

@@ -368,7 +368,9 @@ int fcb200_gemm_f16x2_presplit(const void* a_hi, const void* a_lo, int64_t lda, 
  *                mode 5  planes[:, out_col..] = split(v * sigmoid(y[:, gate_col..])) and the gate gradient
  *                        sum_rows v * y[:, y_col..] summed over CONSECUTIVE tiles (flag 1: first row of the
  *                        degree, flag 2: last row -> planes[:, gate_col..] = split(sum * s * (1 - s)))
- *                flag 8 on the first mode-3 tile after the mode-0 tiles that wrote the gate scalars it reads
+ *   rot_begin    tiles [rot_begin, num_tiles) may run in any order (each CTA starts at a different one, so that the
+ *                CTAs do not all ask L2 for the same weight lines at once); mode-0 tiles that write gate scalars
+ *                read by mode-3 tiles come before rot_begin; num_tiles for a mode-5 plan (its order matters)
  *   y            [M, y_cols] float32, row stride ldy; o_hi/o_lo [M, o_cols] half planes, row stride ldo, written
  *                times *o_scale (device pointers to powers of two, NULL = 1)
  *   status       as in fcb200_gemm_f16x2_presplit
@@ -381,7 +383,8 @@ int fcb200_conv_pair_capacity(void);
 
 int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t lda, int64_t a_cols, const void* const* w_hi,
                           const void* const* w_lo, const int64_t* w_rows, const int64_t* w_cols, const float* w_scale,
-                          const float* const* bias, const int32_t* tiles, int32_t num_tiles, float* y, int64_t ldy,
+                          const float* const* bias, const int32_t* tiles, int32_t num_tiles, int32_t rot_begin, float* y,
+                          int64_t ldy,
                           int64_t y_cols, void* o_hi, void* o_lo, int64_t ldo, int64_t o_cols, const float* a_scale,
                           const float* o_scale, int64_t m, int32_t variant, int32_t* status, void* stream);
 
