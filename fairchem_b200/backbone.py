@@ -919,15 +919,21 @@ class _EdgeBlockFn(torch.autograd.Function):
                 gm = _conv_backward(ew.so2_conv_1, gy)
             del gy
             g_src = torch.empty(ec, nl, c, dtype=x.dtype, device=x.device)
-            g_tgt = torch.empty(ec, nl, c, dtype=x.dtype, device=x.device)
             grad_rad = torch.empty_like(rad_d)
-            ops.gather_rotate_bwd_.raw(gm, x, g.src[sl], g.tgt[sl], wig[sl], rad_d, g_src, g_tgt, gwig[sl], grad_rad)
+            if ew.lmax == 2 and c == 128 and not ops.generic_kernels():
+                # target rows of the chunk are contiguous: their gradient is summed per node inside the kernel
+                ops.gather_rotate_bwd_csr_.raw(gm, x, g.src[sl], g.tgt[sl], ch.row_ptr, ch.n0, wig[sl], rad_d, g_src,
+                                               gx[ch.n0:ch.n1], gwig[sl], grad_rad)
+            else:
+                g_tgt = torch.empty(ec, nl, c, dtype=x.dtype, device=x.device)
+                ops.gather_rotate_bwd_.raw(gm, x, g.src[sl], g.tgt[sl], wig[sl], rad_d, g_src, g_tgt, gwig[sl], grad_rad)
+                ops.segment_sum(g_tgt, ch.row_ptr, None, ch.n1 - ch.n0, out=gx[ch.n0:ch.n1], accumulate=True)
+                del g_tgt
             del gm
-            # node reductions: target rows of the chunk are contiguous; source rows are the chunk's distinct sources
-            ops.segment_sum(g_tgt, ch.row_ptr, None, ch.n1 - ch.n0, out=gx[ch.n0:ch.n1], accumulate=True)
+            # source rows are the chunk's distinct sources
             ops.segment_sum(g_src, ch.src_ptr, ch.src_perm, ch.src_nodes.shape[0], out=gx, out_index=ch.src_nodes,
                             accumulate=True)
-            del g_src, g_tgt
+            del g_src
             _radial_backward(rfn, tables, grad_rad, acts, ectx.z_src[sl], ectx.z_tgt[sl], nb, ggauss[sl])
             del rad_d, grad_rad, acts
         return gx, gwig, gwinv, ggauss, None, None, None, None, None

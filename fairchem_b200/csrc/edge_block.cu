@@ -133,7 +133,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
 // ---------------------------------------------------------------------------------------------
 // gather + rotate backward (per edge): g_src, g_tgt, grad_wig, grad_radial
 // ---------------------------------------------------------------------------------------------
-template <bool HAS_RAD>
+// HALVES = 2: source and target halves; HALVES = 1: the source half only (the target half is then done per target node
+// by gather_rotate_bwd_tgt_kernel, which adds its share to the grad_wig this kernel wrote)
+template <bool HAS_RAD, int HALVES = 2>
 __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
     gather_rotate_bwd_kernel(const float* __restrict__ grad_out, const float* __restrict__ x, const int32_t* __restrict__ src,
                              const int32_t* __restrict__ tgt, const float* __restrict__ wig, const float* __restrict__ radial,
@@ -151,7 +153,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
 #pragma unroll
         for (int i = 0; i < FCB200_WIG; ++i) dw[i] = 0.f;
 #pragma unroll
-        for (int half = 0; half < 2; ++half) {
+        for (int half = 0; half < HALVES; ++half) {
             const int64_t node = half == 0 ? src[e] : tgt[e];
             const float* x_base = x + node * node_stride;
             float* g_base = (half == 0 ? g_src : g_tgt) + e * node_stride;
@@ -202,6 +204,80 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
         warp_reduce_wig(dw, lane, mine, mine2);
         grad_wig[e * FCB200_WIG + lane] = mine;
         if (lane < FCB200_WIG - 32) grad_wig[e * FCB200_WIG + 32 + lane] = mine2;
+    }
+}
+
+// Target half of the gather+rotate backward, one warp per target node (128 channels: a lane owns one float4 of every
+// row).  The edges of a target are contiguous, so its node gradient is summed in registers over them and added to
+// the node row once -- the per-edge target gradients are never written and no separate segmented sum reads them
+// back.  Adds this half's Wigner gradient to the partial sums the source-half kernel left in grad_wig.
+template <bool HAS_RAD>
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
+    gather_rotate_bwd_tgt_kernel(const float* __restrict__ grad_out, const float* __restrict__ x, const int32_t* __restrict__ row_ptr,
+                                 int64_t tgt_base, const float* __restrict__ wig, const float* __restrict__ radial,
+                                 float* __restrict__ gx_tgt, float* __restrict__ grad_wig, float* __restrict__ grad_radial,
+                                 int64_t num_targets) {
+    constexpr int channels = 128;
+    const int lane = threadIdx.x & 31;
+    const int c0 = lane * 4;
+    const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
+    constexpr int order[9] = {0, 1, 2, 3, 5, 4, 6, 7, 8};
+    for (int64_t n = warp0; n < num_targets; n += nwarps) {
+        const int eb = row_ptr[n], ee = row_ptr[n + 1];
+        if (eb == ee) continue;
+        const float* x_base = x + (tgt_base + n) * 9LL * channels;
+        float4 xv[9], gt[9];
+#pragma unroll
+        for (int L = 0; L < 9; ++L) {
+            xv[L] = ld4(x_base + L * channels + c0);
+            gt[L] = f4zero();
+        }
+        for (int64_t e = eb; e < ee; ++e) {
+            float w[FCB200_WIG], dw[FCB200_WIG];
+            load_wig(wig, e, lane, w);
+#pragma unroll
+            for (int i = 0; i < FCB200_WIG; ++i) dw[i] = 0.f;
+            float4 pend = f4zero();
+#pragma unroll
+            for (int k = 0; k < 9; ++k) {
+                const int m = order[k];
+                const int L = m2l(m);
+                const int l = deg_of(L);
+                float4 go = ld4(edge_row(grad_out, e, m, 2 * channels) + channels + c0);
+                if (HAS_RAD) {
+                    float4 rot = f4zero();
+#pragma unroll
+                    for (int b = 0; b < 5; ++b)
+                        if (b < 2 * l + 1) rot = fma4(w[wix(L, l * l + b)], xv[l * l + b], rot);
+                    const int64_t roff = e * 12LL * channels + radslot(m) * 2 * channels + channels + c0;
+                    const float4 contrib = mul4(go, rot);
+                    if (m < 3) {
+                        st4(grad_radial + roff, contrib);
+                    } else if (m == 3 || m == 4 || m == 7) {
+                        pend = contrib;
+                    } else {
+                        st4(grad_radial + roff, add4(pend, contrib));
+                    }
+                    go = mul4(go, ld4(radial + roff));
+                }
+#pragma unroll
+                for (int b = 0; b < 5; ++b) {
+                    if (b < 2 * l + 1) {
+                        const int idx = wix(L, l * l + b);
+                        gt[l * l + b] = fma4(w[idx], go, gt[l * l + b]);
+                        dw[idx] += dot4(go, xv[l * l + b]);
+                    }
+                }
+            }
+            float mine, mine2;
+            warp_reduce_wig(dw, lane, mine, mine2);
+            grad_wig[e * FCB200_WIG + lane] += mine;
+            if (lane < FCB200_WIG - 32) grad_wig[e * FCB200_WIG + 32 + lane] += mine2;
+        }
+        float* g_base = gx_tgt + n * 9LL * channels;
+#pragma unroll
+        for (int L = 0; L < 9; ++L) st4(g_base + L * channels + c0, add4(ld4(g_base + L * channels + c0), gt[L]));
     }
 }
 
@@ -470,6 +546,35 @@ int fcb200_gather_rotate_bwd(const float* grad_out, const float* x, const int32_
     else
         gather_rotate_bwd_kernel<false><<<FCB_LAUNCH(num_edges)>>>(grad_out, x, src, tgt, wig, nullptr, g_src, g_tgt, grad_wig,
                                                                    nullptr, num_edges, channels);
+    return launch_status();
+}
+
+int fcb200_gather_rotate_bwd_csr(const float* grad_out, const float* x, const int32_t* src, const int32_t* tgt,
+                                 const int32_t* row_ptr, int64_t tgt_base, int64_t num_targets, const float* wig,
+                                 const float* radial, float* g_src, float* gx_tgt, float* grad_wig, float* grad_radial,
+                                 int64_t num_edges, int64_t num_nodes, int32_t channels, void* stream) {
+    int rc = check_common(grad_out, x, num_edges, channels);
+    if (rc) return rc;
+    if (channels != 128) return FCB200_EINVAL;
+    if (!src || !tgt || !row_ptr || !wig || !g_src || !gx_tgt || !grad_wig || num_nodes < 0 || num_targets < 0 || tgt_base < 0 ||
+        tgt_base + num_targets > num_nodes)
+        return FCB200_EINVAL;
+    if ((radial == nullptr) != (grad_radial == nullptr)) return FCB200_EINVAL;
+    if (!aligned16(g_src) || !aligned16(gx_tgt) || (radial && (!aligned16(radial) || !aligned16(grad_radial)))) return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    cudaStream_t st = FCB_STREAM;
+    const int tgrid = warp_grid(num_targets, kWarpsPerBlock);
+    if (radial) {
+        gather_rotate_bwd_kernel<true, 1><<<FCB_LAUNCH(num_edges)>>>(grad_out, x, src, tgt, wig, radial, g_src, nullptr, grad_wig,
+                                                                     grad_radial, num_edges, channels);
+        gather_rotate_bwd_tgt_kernel<true><<<tgrid, kWarpsPerBlock * kWarp, 0, st>>>(grad_out, x, row_ptr, tgt_base, wig, radial, gx_tgt,
+                                                                                    grad_wig, grad_radial, num_targets);
+    } else {
+        gather_rotate_bwd_kernel<false, 1><<<FCB_LAUNCH(num_edges)>>>(grad_out, x, src, tgt, wig, nullptr, g_src, nullptr, grad_wig,
+                                                                      nullptr, num_edges, channels);
+        gather_rotate_bwd_tgt_kernel<false><<<tgrid, kWarpsPerBlock * kWarp, 0, st>>>(grad_out, x, row_ptr, tgt_base, wig, nullptr, gx_tgt,
+                                                                                     grad_wig, nullptr, num_targets);
+    }
     return launch_status();
 }
 

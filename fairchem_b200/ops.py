@@ -67,6 +67,10 @@ def set_generic_kernels(flag: bool) -> None:
     _GENERIC = bool(flag)
 
 
+def generic_kernels() -> bool:
+    return _GENERIC
+
+
 def uses_transposed_inverse(lmax: int) -> bool:
     """Layout of the inverse rotation the rotate-back ops expect: the tuned lmax = 2 kernels take the
     compact entries of D^T (wig[:, transpose index] * envelope); the any-lmax kernels take wig * envelope."""
@@ -204,6 +208,24 @@ def gather_rotate_bwd_(grad_out: Tensor, x: Tensor, src: Tensor, tgt: Tensor, wi
                 flops=e * 6 * s.nw * 2 * c)
     else:
         _launch("gather_rotate_bwd", "fcb200_gather_rotate_bwd", args + (_stream(),), nbytes=nbytes, flops=e * 6 * s.nw * 2 * c)
+
+
+@_op("gather_rotate_bwd_csr", ("g_src", "gx_tgt", "grad_wig", "grad_radial"))
+def gather_rotate_bwd_csr_(grad_out: Tensor, x: Tensor, src: Tensor, tgt: Tensor, row_ptr: Tensor, tgt_base: int, wig: Tensor,
+                           radial: Optional[Tensor], g_src: Tensor, gx_tgt: Tensor, grad_wig: Tensor,
+                           grad_radial: Optional[Tensor]) -> None:
+    """gather_rotate_bwd_ for a target-sorted run of edges: the target half of the node gradient is summed per target
+    node inside the kernel and added to ``gx_tgt`` (the rows of the node-gradient array from node ``tgt_base`` on)."""
+    _chk(grad_out, x, src, tgt, row_ptr, wig, radial, g_src, gx_tgt, grad_wig, grad_radial)
+    _f32(grad_out, x, wig, radial, g_src, gx_tgt, grad_wig, grad_radial)
+    e, c, nt = src.shape[0], x.shape[2], row_ptr.shape[0] - 1
+    s = _shape(_BY_NL, x.shape[1], "rows per node")
+    if _lx(s) or c != 128 or gx_tgt.shape[0] != nt:
+        raise _lib.FairchemB200Error("gather_rotate_bwd_csr: lmax 2, 128 channels, one gx_tgt row block per target")
+    nbytes = e * (4 * (2 * s.nm * c + 2 * s.nl * c + 3 * s.nw + 4 * s.nrad * c) + 8) + nt * 4 * 3 * s.nl * c
+    _launch("gather_rotate_bwd", "fcb200_gather_rotate_bwd_csr",
+            (_p(grad_out), _p(x), _p(src), _p(tgt), _p(row_ptr), tgt_base, nt, _p(wig), _p(radial), _p(g_src), _p(gx_tgt),
+             _p(grad_wig), _p(grad_radial), e, x.shape[0], c, _stream()), nbytes=nbytes, flops=e * 6 * s.nw * 2 * c, launches=2)
 
 
 @_op("rotate_back_reduce_fwd", ("out",))

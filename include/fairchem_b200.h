@@ -103,6 +103,21 @@ int fcb200_gather_rotate_bwd(const float* grad_out, const float* x, const int32_
                              void* stream);
 
 /*
+ * fcb200_gather_rotate_bwd for a run of edges that is CSR-sorted by target (the chunks of the edge block are): the
+ * source half is done per edge as above, the target half by one warp per target node, which sums the node gradient
+ * over the target's edges in registers and ADDS it to the node's row once -- the reference scatters both halves with
+ * index_add_ atomics (src/fairchem/core/models/uma/triton/fused_wigner.py:228-236).  No per-edge target gradient is
+ * written and none has to be reduced afterwards.  lmax = 2, channels = 128.
+ *   row_ptr  [num_targets + 1] int32, relative to the first edge of the run; target t is node tgt_base + t
+ *   g_src    [E, 9, C]  out, to be summed by source node (fcb200_segment_sum)
+ *   gx_tgt   [num_targets, 9, C]  in/out: rows of the node-gradient array starting at node tgt_base
+ */
+int fcb200_gather_rotate_bwd_csr(const float* grad_out, const float* x, const int32_t* src, const int32_t* tgt,
+                                 const int32_t* row_ptr, int64_t tgt_base, int64_t num_targets, const float* wig,
+                                 const float* radial, float* g_src, float* gx_tgt, float* grad_wig, float* grad_radial,
+                                 int64_t num_edges, int64_t num_nodes, int32_t channels, void* stream);
+
+/*
  * Backward of fcb200_rotate_back_reduce_fwd: grad_msg = Winv^T grad_out[tgt] (M-major) and
  * grad_winv = sum_c grad_out[tgt] (x) msg on the block entries.  Replaces
  * permute_wigner_inv_edge_to_node_bwd_dx/_bwd_dw kernels (triton/kernels.py:1181, 1334) and

@@ -321,3 +321,43 @@ def test_rms_norm_sh_forward_backward(ops, with_extra):
     (ga,) = torch.autograd.grad(out, a, cot.cuda())
     (gb,) = torch.autograd.grad(ref, xd, cot.double())
     torch.testing.assert_close(ga.cpu(), gb.float(), rtol=1e-4, atol=1e-5 * max(1.0, gb.abs().max().item()))
+
+
+@pytest.mark.parametrize("with_radial", [True, False])
+def test_gather_rotate_backward_with_in_kernel_target_sum(ops, with_radial):
+    """fcb200_gather_rotate_bwd_csr against the per-edge kernel followed by the segmented sum over targets."""
+    g = torch.Generator().manual_seed(11)
+    n, c = 70, 128
+    deg = torch.randint(0, 9, (n,), generator=g)
+    deg[5] = 0
+    tgt = torch.repeat_interleave(torch.arange(n), deg)
+    e = int(tgt.shape[0])
+    src = torch.randint(0, n, (e,), generator=g)
+    row_ptr = torch.zeros(n + 1, dtype=torch.int32)
+    row_ptr[1:] = torch.cumsum(deg, 0)
+    x = torch.randn(n, 9, c, generator=g).cuda()
+    wig = torch.randn(e, 35, generator=g).cuda()
+    go = torch.randn(e, 9, 2 * c, generator=g).cuda()
+    rad = torch.randn(e, 6 * 2 * c, generator=g).cuda() if with_radial else None
+    src_c, tgt_c, rp = src.int().cuda(), tgt.int().cuda(), row_ptr.cuda()
+    f = lambda *s: torch.empty(*s, device="cuda")  # noqa: E731
+    g_src0, g_tgt0, gw0 = f(e, 9, c), f(e, 9, c), f(e, 35)
+    gr0 = torch.empty_like(rad) if with_radial else None
+    ops.gather_rotate_bwd_(go, x, src_c, tgt_c, wig, rad, g_src0, g_tgt0, gw0, gr0)
+    base = torch.randn(n, 9, c, generator=g).cuda()
+    want = base.clone()
+    ops.segment_sum(g_tgt0, rp, None, n, out=want, accumulate=True)
+    # a sub-range of targets, as the chunks of the edge block use it
+    n0, n1 = 10, 61
+    e0, e1 = int(row_ptr[n0]), int(row_ptr[n1])
+    g_src1, gw1 = f(e1 - e0, 9, c), f(e1 - e0, 35)
+    gr1 = torch.empty(e1 - e0, 6 * 2 * c, device="cuda") if with_radial else None
+    got = base.clone()
+    ops.gather_rotate_bwd_csr_(go[e0:e1], x, src_c[e0:e1], tgt_c[e0:e1], (rp[n0:n1 + 1] - e0).contiguous(), n0, wig[e0:e1],
+                               None if rad is None else rad[e0:e1], g_src1, got[n0:n1], gw1, gr1)
+    torch.testing.assert_close(got[n0:n1], want[n0:n1], rtol=1e-5, atol=1e-4)
+    assert torch.equal(got[:n0], base[:n0]) and torch.equal(got[n1:], base[n1:])
+    torch.testing.assert_close(g_src1, g_src0[e0:e1], rtol=0, atol=0)
+    torch.testing.assert_close(gw1, gw0[e0:e1], rtol=1e-5, atol=1e-4)
+    if with_radial:
+        torch.testing.assert_close(gr1, gr0[e0:e1], rtol=0, atol=0)
