@@ -44,3 +44,40 @@ def test_partitioned_run_matches_single_gpu(world, model, natoms):
     stats = got["stats"].numpy()
     assert stats[:, 0].sum() == natoms and stats[:, 0].max() - stats[:, 0].min() <= 1   # balanced ownership
     assert (stats[:, 1] > 0).all()                                                          # every rank has a halo
+
+
+def test_contraction_kernels_on_a_second_device_of_the_same_process():
+    """The kernels ask for more than 200 KB of dynamic shared memory, an attribute that is set per device: a process that
+    drives two GPUs must get it on both (run on device 1 after device 0)."""
+    if not torch.cuda.is_available() or torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 CUDA devices")
+    from fairchem_b200 import backbone as B
+    from fairchem_b200 import ops
+
+    g = torch.Generator().manual_seed(0)
+    a, w = torch.randn(300, 256, generator=g), torch.randn(128, 256, generator=g)
+    want = a.double() @ w.double().t()
+    for dev in ("cuda:0", "cuda:1"):
+        with torch.cuda.device(dev):
+            ad, wd = a.to(dev), w.to(dev)
+            y = torch.empty(300, 128, device=dev)
+            hi, lo, sc = ops.split_f16(wd)
+            status = torch.zeros(1, dtype=torch.int32, device=dev)
+            ops.gemm_f16x2_(ad, hi, lo, sc, None, None, y, status)                       # float32 A, split in the kernel
+            ah = ad.half()
+            planes = (ah, ((ad - ah.float()) * 2048.0).half())
+            y2 = torch.empty_like(y)
+            ops.gemm_f16x2_presplit_(planes[0], planes[1], hi, lo, sc, None, None, y2, status)
+            y3 = torch.empty_like(y)
+            tiles = [0, 256, 0, 0, 0, ops.CONV_PLAIN, 0, 0, 0]
+            for variant in (0, 1):                                                       # fused kernel, both launch forms
+                ops.so2_conv_fused_(planes[0], planes[1], [hi], [lo], [sc], None, tiles, 0, y3, None, None, None, None, status, "",
+                                    variant)
+                torch.testing.assert_close(y3.cpu().double(), want, rtol=1e-5, atol=1e-4)
+            hi3, lo3 = ops.split_tf32(wd)
+            y4 = torch.empty_like(y)
+            ops.gemm_tf32_(ad, hi3, lo3, None, y4, 3, status)
+            assert int(status.item()) == 0
+            for got in (y, y2, y4):
+                torch.testing.assert_close(got.cpu().double(), want, rtol=1e-5, atol=1e-4)
+    del B
