@@ -208,6 +208,7 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
     const float a_scale = prm.a_scale ? *prm.a_scale : 1.0f;
     const float o_scale = prm.o_scale ? *prm.o_scale : 1.0f;
     const int ntiles = plan.ntiles;
+    const uint64_t stream_out = l2_policy_evict_first();  // outputs are not read again by this kernel (the gate scalars are: default policy)
     float amax = 0.f;
     float acc[2][32];  // gate-gradient sums over the rows of a degree (kGatedBwd), per chunk
     int64_t tcount = 0;
@@ -351,14 +352,15 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
                 __syncwarp();
                 if (lane == 0) {
                     if (mode == kPlain) {
-                        tma_store_2d(&map_y, st_out, t.out_col + col, (int)row0);
+                        if (ti < plan.rot_begin) tma_store_2d(&map_y, st_out, t.out_col + col, (int)row0);  // gate scalars: read back
+                        else tma_store_2d_hint(&map_y, st_out, t.out_col + col, (int)row0, stream_out);
                     } else {
-                        if (keep) tma_store_2d(&map_y, b1, t.y_col + col, (int)row0);
-                        tma_store_2d(&map_ohi, st_out, t.out_col + col, (int)row0);
-                        tma_store_2d(&map_olo, st_out + 2048u, t.out_col + col, (int)row0);
+                        if (keep) tma_store_2d_hint(&map_y, b1, t.y_col + col, (int)row0, stream_out);
+                        tma_store_2d_hint(&map_ohi, st_out, t.out_col + col, (int)row0, stream_out);
+                        tma_store_2d_hint(&map_olo, st_out + 2048u, t.out_col + col, (int)row0, stream_out);
                         if (fin) {
-                            tma_store_2d(&map_ohi, b1, t.gate_col + col, (int)row0);
-                            tma_store_2d(&map_olo, b1 + 2048u, t.gate_col + col, (int)row0);
+                            tma_store_2d_hint(&map_ohi, b1, t.gate_col + col, (int)row0, stream_out);
+                            tma_store_2d_hint(&map_olo, b1 + 2048u, t.gate_col + col, (int)row0, stream_out);
                         }
                     }
                     asm volatile("cp.async.bulk.commit_group;" ::: "memory");
@@ -441,6 +443,9 @@ __global__ void __launch_bounds__(kThreads, 1)
         if (lane == 0) {
             int64_t it = 0;
             bool ok = true;
+            // an A tile is fetched again for each of the output tiles of its m-block, the weights by every CTA: keep
+            // both in L2 ahead of the streamed outputs
+            const uint64_t keep = l2_policy_evict_last();
             for (int64_t mt = blockIdx.x; mt < tiles_m && ok; mt += gridDim.x) {
                 for (int ti = 0; ti < ntiles && ok; ++ti) {
                     const Tile& t = plan.t[tile_at(plan, ti, (int)(blockIdx.x % 64))];
@@ -453,10 +458,10 @@ __global__ void __launch_bounds__(kThreads, 1)
                         ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag);
                         if (!ok) break;
                         mbar_expect_tx(full_bar(s), kStageBytes);
-                        tma_load_2d(half_addr(s, 0), &map_ahi, t.a_col + kb * BK, (int)(mt * BM), full_bar(s));
-                        tma_load_2d(half_addr(s, 1), &map_alo, t.a_col + kb * BK, (int)(mt * BM), full_bar(s));
-                        tma_load_2d(half_addr(s, 2), whi, kb * BK, t.w_row, full_bar(s));
-                        tma_load_2d(half_addr(s, 3), wlo, kb * BK, t.w_row, full_bar(s));
+                        tma_load_2d_hint(half_addr(s, 0), &map_ahi, t.a_col + kb * BK, (int)(mt * BM), full_bar(s), keep);
+                        tma_load_2d_hint(half_addr(s, 1), &map_alo, t.a_col + kb * BK, (int)(mt * BM), full_bar(s), keep);
+                        tma_load_2d_hint(half_addr(s, 2), whi, kb * BK, t.w_row, full_bar(s), keep);
+                        tma_load_2d_hint(half_addr(s, 3), wlo, kb * BK, t.w_row, full_bar(s), keep);
                     }
                 }
             }
