@@ -720,6 +720,11 @@ class _FusedConvPlan:
         self.bwd2 = [v for t in t2 for v in t]
         self.bwd1 = _fused_tiles(s1, True, plain)
         self.ok = max(len(t) // 9 for t in (self.fwd1[True], self.fwd2, self.bwd2, self.bwd1)) <= ops.CONV_MAX_TILES and h % 128 == 0
+        # the fused launch re-reads a 128-edge A tile once per output tile of its m-block and counts on L2 for it; with
+        # K beyond ~1024 (lmax 4: 1280 / 2048 / 1536) the tiles of all CTAs together no longer fit there and the separate
+        # GEMM launches (which share an A tile among the CTAs that run together) plus the gate kernel are faster
+        self.fuse_conv1_fwd = max(k for _, k in s1) <= 1024
+        self.fuse_conv1_bwd = max(n for n, _ in s1) <= 1024
         split = lambda ws: tuple(zip(*[_split16(w) for w in ws]))  # noqa: E731
         self.w1, self.w2 = split(w1), split(w2)
         self.w1t, self.w2t = split([_transposed(w) for w in w1]), split([_transposed(w) for w in w2])
@@ -839,7 +844,10 @@ class _EdgeBlockFn(torch.autograd.Function):
                 del rad
                 msg_out = torch.empty(ec, nm * c, dtype=x.dtype, device=x.device) if msg_all is None else msg_all[sl].view(ec, nm * c)
                 if fused:
-                    a = _fused_conv1_gate(ew, m, None if y_all is None else y_all[sl])
+                    if _fused_plan(ew).fuse_conv1_fwd:
+                        a = _fused_conv1_gate(ew, m, None if y_all is None else y_all[sl])
+                    else:
+                        a = _gate(_conv_forward(ew.so2_conv_1, m, out=None if y_all is None else y_all[sl]), h, nm)
                     del m
                     msg = _fused_conv2(ew, a, msg_out).view(ec, nm, c)
                     del a
@@ -884,6 +892,8 @@ class _EdgeBlockFn(torch.autograd.Function):
             msg = None if msg_all is None else msg_all[sl]
             if fused and (y is None or msg is None):
                 a = None
+                if y is None and not _fused_plan(ew).fuse_conv1_fwd:
+                    y = _conv_forward(ew.so2_conv_1, _gather_rotate(x, g, sl, wig, rad_d, nm))
                 if y is None:
                     y = torch.empty(ec, (ew.lmax + nm) * h, dtype=x.dtype, device=x.device)
                     a = _fused_conv1_gate(ew, _gather_rotate(x, g, sl, wig, rad_d, nm), y)
@@ -906,7 +916,7 @@ class _EdgeBlockFn(torch.autograd.Function):
             if fused:
                 gy = _fused_conv2_gate_backward(ew, grad_msg, y, scale)
                 del grad_msg, y
-                gm = _fused_conv1_backward(ew, gy, scale)
+                gm = _fused_conv1_backward(ew, gy, scale) if _fused_plan(ew).fuse_conv1_bwd else _conv_backward(ew.so2_conv_1, gy)
             else:
                 ga = _conv_backward(ew.so2_conv_2, grad_msg)
                 del grad_msg
