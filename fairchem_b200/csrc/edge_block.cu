@@ -23,7 +23,7 @@ __device__ __forceinline__ P* edge_row(P* buf, int64_t e, int m, int w) {
 // gather + rotate (+ radial scale) forward
 // ---------------------------------------------------------------------------------------------
 template <bool HAS_RAD, class Out>
-__global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp, 2)
     gather_rotate_fwd_kernel(const float* __restrict__ x, const int32_t* __restrict__ src, const int32_t* __restrict__ tgt,
                              const float* __restrict__ wig, const float* __restrict__ radial, Out out,
                              const float* __restrict__ scale_ptr, int64_t num_edges, int channels) {
@@ -35,37 +35,27 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
     for (int64_t e = warp0; e < num_edges; e += nwarps) {
         float w[FCB200_WIG];
         load_wig(wig, e, lane, w);
-        const float* xs_base = x + (int64_t)src[e] * node_stride;
-        const float* xt_base = x + (int64_t)tgt[e] * node_stride;
         const float* r_base = HAS_RAD ? radial + e * 12LL * channels : nullptr;
-        for (int c0 = lane * 4; c0 < channels; c0 += 128) {
-            float4 xs[9], xt[9];
+        // source half, then target half: nine node rows live at a time instead of eighteen, which lets two blocks share an
+        // SM and doubles the loads in flight
 #pragma unroll
-            for (int L = 0; L < 9; ++L) {
-                xs[L] = ld4(xs_base + L * channels + c0);
-                xt[L] = ld4(xt_base + L * channels + c0);
-            }
+        for (int half = 0; half < 2; ++half) {
+            const float* x_base = x + (int64_t)(half == 0 ? src[e] : tgt[e]) * node_stride;
+            for (int c0 = lane * 4; c0 < channels; c0 += 128) {
+                float4 xv[9];
 #pragma unroll
-            for (int m = 0; m < 9; ++m) {
-                const int L = m2l(m);
-                const int l = deg_of(L);
-                float4 as = f4zero(), at = f4zero();
+                for (int L = 0; L < 9; ++L) xv[L] = ld4(x_base + L * channels + c0);
 #pragma unroll
-                for (int b = 0; b < 5; ++b) {
-                    if (b < 2 * l + 1) {
-                        const float wv = w[wix(L, l * l + b)];
-                        as = fma4(wv, xs[l * l + b], as);
-                        at = fma4(wv, xt[l * l + b], at);
-                    }
+                for (int m = 0; m < 9; ++m) {
+                    const int L = m2l(m);
+                    const int l = deg_of(L);
+                    float4 a = f4zero();
+#pragma unroll
+                    for (int b = 0; b < 5; ++b)
+                        if (b < 2 * l + 1) a = fma4(w[wix(L, l * l + b)], xv[l * l + b], a);
+                    if (HAS_RAD) a = mul4(a, ld4(r_base + radslot(m) * 2 * channels + half * channels + c0));
+                    out.st((e * 9 + m) * 2LL * channels + half * channels + c0, a);
                 }
-                if (HAS_RAD) {
-                    const float* r = r_base + radslot(m) * 2 * channels + c0;
-                    as = mul4(as, ld4(r));
-                    at = mul4(at, ld4(r + channels));
-                }
-                const int64_t o = (e * 9 + m) * 2LL * channels + c0;
-                out.st(o, as);
-                out.st(o + channels, at);
             }
         }
     }
