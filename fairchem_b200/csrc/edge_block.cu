@@ -123,8 +123,6 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
 // ---------------------------------------------------------------------------------------------
 // gather + rotate backward (per edge): g_src, g_tgt, grad_wig, grad_radial
 // ---------------------------------------------------------------------------------------------
-// HALVES = 2: source and target halves; HALVES = 1: the source half only (the target half is then done per target node
-// by gather_rotate_bwd_tgt_kernel, which adds its share to the grad_wig this kernel wrote)
 template <bool HAS_RAD, int HALVES = 2>
 __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
     gather_rotate_bwd_kernel(const float* __restrict__ grad_out, const float* __restrict__ x, const int32_t* __restrict__ src,
@@ -197,77 +195,167 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
     }
 }
 
-// Target half of the gather+rotate backward, one warp per target node (128 channels: a lane owns one float4 of every
-// row).  The edges of a target are contiguous, so its node gradient is summed in registers over them and added to
-// the node row once -- the per-edge target gradients are never written and no separate segmented sum reads them
-// back.  Adds this half's Wigner gradient to the partial sums the source-half kernel left in grad_wig.
+// ---- gather + rotate backward, one degree at a time ------------------------------------------------------------
+// Working through the block-diagonal rotation degree by degree keeps at most the l = 2 block alive (25 Wigner entries,
+// 25 gradient sums, 5 node rows, 5 gradient rows: ~90 registers instead of ~180), so two blocks share an SM.
+template <int N, bool ACC>
+__device__ __forceinline__ void reduce_block(const float (&v)[N], int lane, float* __restrict__ out) {
+    if (N == 1) {
+        const float t = warp_sum(v[0]);
+        if (lane == 0) out[0] = ACC ? out[0] + t : t;
+        return;
+    }
+    float t[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) t[i] = i < N ? v[i] : 0.f;
+#pragma unroll
+    for (int h = 16; h >= 1; h >>= 1) {
+        const bool upper = (lane & h) != 0;
+#pragma unroll
+        for (int i = 0; i < h; ++i) {
+            const float a = t[i], b = t[i + h];
+            t[i] = (upper ? b : a) + __shfl_xor_sync(kFull, upper ? a : b, h);
+        }
+    }
+    if (lane < N) out[lane] = ACC ? out[lane] + t[0] : t[0];
+}
+
+// M-major rows of degree l in the order that finishes a shared radial slot right after its second row
+template <int l> struct DegRows;
+template <> struct DegRows<0> { static constexpr int n = 1; __device__ static constexpr int row(int i) { return 0; } };
+template <> struct DegRows<1> { static constexpr int n = 3; __device__ static constexpr int row(int i) { constexpr int t[3] = {1, 3, 5}; return t[i]; } };
+template <> struct DegRows<2> { static constexpr int n = 5; __device__ static constexpr int row(int i) { constexpr int t[5] = {2, 4, 6, 7, 8}; return t[i]; } };
+
+// One edge, one half (source or target columns), one degree: g[b] += W^T grad rows, dw += grad (x) x, radial gradient.
+template <int l, bool HAS_RAD>
+__device__ __forceinline__ void bwd_degree_rows(const float* __restrict__ grad_out, const float* __restrict__ radial,
+                                                float* __restrict__ grad_radial, int64_t e, int half, int channels, int c0,
+                                                const float (&w)[(2 * l + 1) * (2 * l + 1)], const float4 (&xv)[2 * l + 1],
+                                                float4 (&g)[2 * l + 1], float (&dw)[(2 * l + 1) * (2 * l + 1)]) {
+    constexpr int n = 2 * l + 1;
+    float4 pend = f4zero();
+#pragma unroll
+    for (int i = 0; i < DegRows<l>::n; ++i) {
+        const int m = DegRows<l>::row(i);
+        const int r = m2l(m) - l * l;  // row of the block
+        float4 go = ld4(edge_row(grad_out, e, m, 2 * channels) + half * channels + c0);
+        if (HAS_RAD) {
+            float4 rot = f4zero();
+#pragma unroll
+            for (int b = 0; b < n; ++b) rot = fma4(w[r * n + b], xv[b], rot);
+            const int64_t roff = e * 12LL * channels + radslot(m) * 2 * channels + half * channels + c0;
+            const float4 contrib = mul4(go, rot);
+            if (m < 3) {
+                st4(grad_radial + roff, contrib);
+            } else if (m == 3 || m == 4 || m == 7) {
+                pend = contrib;
+            } else {
+                st4(grad_radial + roff, add4(pend, contrib));
+            }
+            go = mul4(go, ld4(radial + roff));
+        }
+#pragma unroll
+        for (int b = 0; b < n; ++b) {
+            g[b] = fma4(w[r * n + b], go, g[b]);
+            dw[r * n + b] += dot4(go, xv[b]);
+        }
+    }
+}
+
+// source half, one warp per edge
+template <int l, bool HAS_RAD>
+__device__ __forceinline__ void bwd_src_degree(const float* __restrict__ grad_out, const float* __restrict__ x_base,
+                                               const float* __restrict__ wig_e, const float* __restrict__ radial,
+                                               float* __restrict__ g_base, float* __restrict__ grad_wig_e,
+                                               float* __restrict__ grad_radial, int64_t e, int lane, int channels) {
+    constexpr int n = 2 * l + 1, L0 = l * l;
+    float w[n * n], dw[n * n];
+#pragma unroll
+    for (int i = 0; i < n * n; ++i) {
+        w[i] = __ldg(wig_e + woff(l) + i);
+        dw[i] = 0.f;
+    }
+    for (int c0 = lane * 4; c0 < channels; c0 += 128) {
+        float4 xv[n], g[n];
+#pragma unroll
+        for (int b = 0; b < n; ++b) {
+            xv[b] = ld4(x_base + (L0 + b) * channels + c0);
+            g[b] = f4zero();
+        }
+        bwd_degree_rows<l, HAS_RAD>(grad_out, radial, grad_radial, e, 0, channels, c0, w, xv, g, dw);
+#pragma unroll
+        for (int b = 0; b < n; ++b) st4(g_base + (L0 + b) * channels + c0, g[b]);
+    }
+    reduce_block<n * n, false>(dw, lane, grad_wig_e + woff(l));
+}
+
 template <bool HAS_RAD>
-__global__ void __launch_bounds__(kWarpsPerBlock* kWarp)
-    gather_rotate_bwd_tgt_kernel(const float* __restrict__ grad_out, const float* __restrict__ x, const int32_t* __restrict__ row_ptr,
-                                 int64_t tgt_base, const float* __restrict__ wig, const float* __restrict__ radial,
-                                 float* __restrict__ gx_tgt, float* __restrict__ grad_wig, float* __restrict__ grad_radial,
-                                 int64_t num_targets) {
-    constexpr int channels = 128;
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp, 2)
+    gather_rotate_bwd_src_kernel(const float* __restrict__ grad_out, const float* __restrict__ x, const int32_t* __restrict__ src,
+                                 const float* __restrict__ wig, const float* __restrict__ radial, float* __restrict__ g_src,
+                                 float* __restrict__ grad_wig, float* __restrict__ grad_radial, int64_t num_edges, int channels) {
     const int lane = threadIdx.x & 31;
-    const int c0 = lane * 4;
     const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
-    constexpr int order[9] = {0, 1, 2, 3, 5, 4, 6, 7, 8};
+    const int64_t node_stride = 9LL * channels;
+    for (int64_t e = warp0; e < num_edges; e += nwarps) {
+        const float* x_base = x + (int64_t)src[e] * node_stride;
+        float* g_base = g_src + e * node_stride;
+        const float* wig_e = wig + e * FCB200_WIG;
+        float* gw = grad_wig + e * FCB200_WIG;
+        bwd_src_degree<0, HAS_RAD>(grad_out, x_base, wig_e, radial, g_base, gw, grad_radial, e, lane, channels);
+        bwd_src_degree<1, HAS_RAD>(grad_out, x_base, wig_e, radial, g_base, gw, grad_radial, e, lane, channels);
+        bwd_src_degree<2, HAS_RAD>(grad_out, x_base, wig_e, radial, g_base, gw, grad_radial, e, lane, channels);
+    }
+}
+
+// target half, one warp per target node and degree (128 channels): the node gradient of the degree's rows is summed
+// over the target's edges in registers and added to the node rows once; the Wigner gradient is added to what the
+// source kernel stored
+template <int l, bool HAS_RAD>
+__device__ __forceinline__ void bwd_tgt_degree(const float* __restrict__ grad_out, const float* __restrict__ x_base,
+                                               const float* __restrict__ wig, const float* __restrict__ radial,
+                                               float* __restrict__ g_base, float* __restrict__ grad_wig,
+                                               float* __restrict__ grad_radial, int eb, int ee, int lane) {
+    constexpr int n = 2 * l + 1, L0 = l * l, channels = 128;
+    const int c0 = lane * 4;
+    float4 xv[n], gt[n];
+#pragma unroll
+    for (int b = 0; b < n; ++b) {
+        xv[b] = ld4(x_base + (L0 + b) * channels + c0);
+        gt[b] = f4zero();
+    }
+    for (int64_t e = eb; e < ee; ++e) {
+        float w[n * n], dw[n * n];
+#pragma unroll
+        for (int i = 0; i < n * n; ++i) {
+            w[i] = __ldg(wig + e * FCB200_WIG + woff(l) + i);
+            dw[i] = 0.f;
+        }
+        bwd_degree_rows<l, HAS_RAD>(grad_out, radial, grad_radial, e, 1, channels, c0, w, xv, gt, dw);
+        reduce_block<n * n, true>(dw, lane, grad_wig + e * FCB200_WIG + woff(l));
+    }
+#pragma unroll
+    for (int b = 0; b < n; ++b) st4(g_base + (L0 + b) * channels + c0, add4(ld4(g_base + (L0 + b) * channels + c0), gt[b]));
+}
+
+template <bool HAS_RAD>
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp, 2)
+    gather_rotate_bwd_tgt_kernel(const float* __restrict__ grad_out, const float* __restrict__ x, const int32_t* __restrict__ row_ptr,
+                                  int64_t tgt_base, const float* __restrict__ wig, const float* __restrict__ radial,
+                                  float* __restrict__ gx_tgt, float* __restrict__ grad_wig, float* __restrict__ grad_radial,
+                                  int64_t num_targets) {
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
     for (int64_t n = warp0; n < num_targets; n += nwarps) {
         const int eb = row_ptr[n], ee = row_ptr[n + 1];
         if (eb == ee) continue;
-        const float* x_base = x + (tgt_base + n) * 9LL * channels;
-        float4 xv[9], gt[9];
-#pragma unroll
-        for (int L = 0; L < 9; ++L) {
-            xv[L] = ld4(x_base + L * channels + c0);
-            gt[L] = f4zero();
-        }
-        for (int64_t e = eb; e < ee; ++e) {
-            float w[FCB200_WIG], dw[FCB200_WIG];
-            load_wig(wig, e, lane, w);
-#pragma unroll
-            for (int i = 0; i < FCB200_WIG; ++i) dw[i] = 0.f;
-            float4 pend = f4zero();
-#pragma unroll
-            for (int k = 0; k < 9; ++k) {
-                const int m = order[k];
-                const int L = m2l(m);
-                const int l = deg_of(L);
-                float4 go = ld4(edge_row(grad_out, e, m, 2 * channels) + channels + c0);
-                if (HAS_RAD) {
-                    float4 rot = f4zero();
-#pragma unroll
-                    for (int b = 0; b < 5; ++b)
-                        if (b < 2 * l + 1) rot = fma4(w[wix(L, l * l + b)], xv[l * l + b], rot);
-                    const int64_t roff = e * 12LL * channels + radslot(m) * 2 * channels + channels + c0;
-                    const float4 contrib = mul4(go, rot);
-                    if (m < 3) {
-                        st4(grad_radial + roff, contrib);
-                    } else if (m == 3 || m == 4 || m == 7) {
-                        pend = contrib;
-                    } else {
-                        st4(grad_radial + roff, add4(pend, contrib));
-                    }
-                    go = mul4(go, ld4(radial + roff));
-                }
-#pragma unroll
-                for (int b = 0; b < 5; ++b) {
-                    if (b < 2 * l + 1) {
-                        const int idx = wix(L, l * l + b);
-                        gt[l * l + b] = fma4(w[idx], go, gt[l * l + b]);
-                        dw[idx] += dot4(go, xv[l * l + b]);
-                    }
-                }
-            }
-            float mine, mine2;
-            warp_reduce_wig(dw, lane, mine, mine2);
-            grad_wig[e * FCB200_WIG + lane] += mine;
-            if (lane < FCB200_WIG - 32) grad_wig[e * FCB200_WIG + 32 + lane] += mine2;
-        }
-        float* g_base = gx_tgt + n * 9LL * channels;
-#pragma unroll
-        for (int L = 0; L < 9; ++L) st4(g_base + L * channels + c0, add4(ld4(g_base + L * channels + c0), gt[L]));
+        const float* x_base = x + (tgt_base + n) * 9LL * 128;
+        float* g_base = gx_tgt + n * 9LL * 128;
+        bwd_tgt_degree<0, HAS_RAD>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, eb, ee, lane);
+        bwd_tgt_degree<1, HAS_RAD>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, eb, ee, lane);
+        bwd_tgt_degree<2, HAS_RAD>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, eb, ee, lane);
     }
 }
 
@@ -555,15 +643,15 @@ int fcb200_gather_rotate_bwd_csr(const float* grad_out, const float* x, const in
     cudaStream_t st = FCB_STREAM;
     const int tgrid = warp_grid(num_targets, kWarpsPerBlock);
     if (radial) {
-        gather_rotate_bwd_kernel<true, 1><<<FCB_LAUNCH(num_edges)>>>(grad_out, x, src, tgt, wig, radial, g_src, nullptr, grad_wig,
-                                                                     grad_radial, num_edges, channels);
+        gather_rotate_bwd_src_kernel<true><<<FCB_LAUNCH(num_edges)>>>(grad_out, x, src, wig, radial, g_src, grad_wig, grad_radial,
+                                                                      num_edges, channels);
         gather_rotate_bwd_tgt_kernel<true><<<tgrid, kWarpsPerBlock * kWarp, 0, st>>>(grad_out, x, row_ptr, tgt_base, wig, radial, gx_tgt,
-                                                                                    grad_wig, grad_radial, num_targets);
+                                                                                     grad_wig, grad_radial, num_targets);
     } else {
-        gather_rotate_bwd_kernel<false, 1><<<FCB_LAUNCH(num_edges)>>>(grad_out, x, src, tgt, wig, nullptr, g_src, nullptr, grad_wig,
-                                                                      nullptr, num_edges, channels);
+        gather_rotate_bwd_src_kernel<false><<<FCB_LAUNCH(num_edges)>>>(grad_out, x, src, wig, nullptr, g_src, grad_wig, nullptr,
+                                                                       num_edges, channels);
         gather_rotate_bwd_tgt_kernel<false><<<tgrid, kWarpsPerBlock * kWarp, 0, st>>>(grad_out, x, row_ptr, tgt_base, wig, nullptr, gx_tgt,
-                                                                                     grad_wig, nullptr, num_targets);
+                                                                                      grad_wig, nullptr, num_targets);
     }
     return launch_status();
 }
