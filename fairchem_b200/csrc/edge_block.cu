@@ -359,6 +359,60 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp, 2)
     }
 }
 
+// rotate-back backward with the Wigner gradient, one degree at a time (see the gather backward above): the l = 2 block
+// needs 25 + 25 entries, 5 gradient rows and 5 message rows, so two blocks share an SM
+template <int l, class Out>
+__device__ __forceinline__ void rotate_back_bwd_degree(const float* __restrict__ go_base, const float* __restrict__ msg_e,
+                                                       const float* __restrict__ winv_e, Out& grad_msg, int64_t out_base,
+                                                       float* __restrict__ grad_winv_e, int lane, int channels) {
+    constexpr int n = 2 * l + 1, L0 = l * l;
+    float w[n * n], dw[n * n];
+#pragma unroll
+    for (int i = 0; i < n * n; ++i) {
+        w[i] = __ldg(winv_e + woff(l) + i);
+        dw[i] = 0.f;
+    }
+    for (int c0 = lane * 4; c0 < channels; c0 += 128) {
+        float4 go[n];
+#pragma unroll
+        for (int a = 0; a < n; ++a) go[a] = ld4(go_base + (L0 + a) * channels + c0);
+#pragma unroll
+        for (int i = 0; i < DegRows<l>::n; ++i) {
+            const int m = DegRows<l>::row(i);
+            const int col = m2l(m) - L0;  // column of the block
+            const float4 y = ld4(msg_e + m * channels + c0);
+            float4 acc = f4zero();
+#pragma unroll
+            for (int a = 0; a < n; ++a) {
+                acc = fma4(w[a * n + col], go[a], acc);
+                dw[a * n + col] += dot4(go[a], y);
+            }
+            grad_msg.st(out_base + m * channels + c0, acc);
+        }
+    }
+    reduce_block<n * n, false>(dw, lane, grad_winv_e + woff(l));
+}
+
+template <class Out>
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp, 2)
+    rotate_back_bwd_deg_kernel(const float* __restrict__ grad_out, const float* __restrict__ msg, const float* __restrict__ winv,
+                               const int32_t* __restrict__ tgt, Out grad_msg, const float* __restrict__ scale_ptr,
+                               float* __restrict__ grad_winv, int64_t num_edges, int channels) {
+    grad_msg.load_scale(scale_ptr);
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
+    for (int64_t e = warp0; e < num_edges; e += nwarps) {
+        const float* go_base = grad_out + (int64_t)tgt[e] * 9LL * channels;
+        const float* msg_e = msg + e * 9LL * channels;
+        const float* winv_e = winv + e * FCB200_WIG;
+        float* gw = grad_winv + e * FCB200_WIG;
+        rotate_back_bwd_degree<0>(go_base, msg_e, winv_e, grad_msg, e * 9LL * channels, gw, lane, channels);
+        rotate_back_bwd_degree<1>(go_base, msg_e, winv_e, grad_msg, e * 9LL * channels, gw, lane, channels);
+        rotate_back_bwd_degree<2>(go_base, msg_e, winv_e, grad_msg, e * 9LL * channels, gw, lane, channels);
+    }
+}
+
 // ---------------------------------------------------------------------------------------------
 // rotate back backward (per edge): grad_msg (M-major) and grad_winv
 // ---------------------------------------------------------------------------------------------
@@ -665,7 +719,7 @@ int fcb200_rotate_back_bwd(const float* grad_out, const float* msg, const float*
     if (msg && !aligned16(msg)) return FCB200_EALIGN;
     if (num_edges == 0) return FCB200_OK;
     if (msg)
-        rotate_back_bwd_kernel<0, true, OutF32><<<FCB_LAUNCH(num_edges)>>>(grad_out, msg, winv, tgt, OutF32{grad_msg}, nullptr, grad_winv, 1.f, num_edges, channels);
+        rotate_back_bwd_deg_kernel<OutF32><<<FCB_LAUNCH(num_edges)>>>(grad_out, msg, winv, tgt, OutF32{grad_msg}, nullptr, grad_winv, num_edges, channels);
     else
         rotate_back_bwd_kernel<0, false, OutF32><<<FCB_LAUNCH(num_edges)>>>(grad_out, nullptr, winv, tgt, OutF32{grad_msg}, nullptr, nullptr, 1.f, num_edges,
                                                                     channels);
@@ -744,8 +798,7 @@ int fcb200_rotate_back_bwd_h(const float* grad_out, const float* msg, const floa
     if (num_edges == 0) return FCB200_OK;
     const OutSplit out{static_cast<__half*>(grad_msg_hi), static_cast<__half*>(grad_msg_lo), 1.0f};
     if (grad_winv)
-        rotate_back_bwd_kernel<0, true, OutSplit><<<FCB_LAUNCH(num_edges)>>>(grad_out, msg, winv, tgt, out, scale, grad_winv, 1.f,
-                                                                             num_edges, channels);
+        rotate_back_bwd_deg_kernel<OutSplit><<<FCB_LAUNCH(num_edges)>>>(grad_out, msg, winv, tgt, out, scale, grad_winv, num_edges, channels);
     else
         rotate_back_bwd_kernel<0, false, OutSplit><<<FCB_LAUNCH(num_edges)>>>(grad_out, nullptr, winv, tgt, out, scale, nullptr, 1.f,
                                                                               num_edges, channels);
