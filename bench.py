@@ -38,8 +38,10 @@ from fairchem_b200 import synthetic, weights  # noqa: E402
 ACC = 9.648533e-3  # (eV/A)/amu -> A/fs^2
 MASS = {1: 1.008, 6: 12.011, 7: 14.007, 8: 15.999, 24: 51.996, 25: 54.938, 26: 55.845, 27: 58.933, 28: 58.693, 29: 63.546}
 CPU_SAMPLE_ATOMS = 1500
-# DRAM bytes per edge per launch of so2_conv_fused_kernel from an ncu capture (None until one is taken)
-FUSED_TRAFFIC_PER_EDGE_LAUNCH = None
+# DRAM bytes (read + write) per edge of one launch of so2_conv_fused_kernel, mean over its four convolution plans, from the
+# ncu capture of 62 118-edge launches summarised in profiles/so2_conv_fused_kernel_bcc_alloy_2000.md:
+# (1520 + 597) + (348 + 244) + (875 + 317) + (460 + 526) MB over 4 launches; traffic grows in proportion to the edges
+FUSED_TRAFFIC_PER_EDGE_LAUNCH = (2117e6 + 592e6 + 1192e6 + 986e6) / 4 / 62118
 
 
 def load_peaks():
@@ -264,13 +266,14 @@ def run_b200(args):
     # the fused convolution kernel is one kernel launched with four tile plans: one roofline entry for it
     by_kernel = {}
     for k, v in summary.items():
-        key = "so2_conv_fused" if k.startswith("so2_conv_fused") else k
+        # (the radial MLP's output layer runs on the same kernel but is bound by storing its wide output: own entry)
+        key = "so2_conv_fused" if k.startswith("so2_conv_fused_conv") else k
         d = by_kernel.setdefault(key, {"ms": 0.0, "bytes": 0, "flops": 0, "launches": 0})
         for f in d:
             d[f] += v[f]
     top = max(by_kernel.items(), key=lambda kv: kv[1]["ms"]) if by_kernel else ("none", {"ms": 0.0, "bytes": 0, "flops": 0, "launches": 0})
     name, rec = top
-    if name in ("gemm_f16x2", "gemm_f16x2_presplit", "so2_conv_fused"):
+    if name in ("gemm_f16x2", "gemm_f16x2_presplit", "so2_conv_fused", "so2_conv_fused_radial_out"):
         peak = peaks["bf16_tflops"]
         ach = rec["flops"] / (rec["ms"] * 1e-3) / 1e12 if rec["ms"] else 0.0
         traffic = None
@@ -281,7 +284,8 @@ def run_b200(args):
             if n_chunks:
                 traffic = 203.6e6 * (edges / n_chunks) / 62119.0
         if name == "so2_conv_fused" and rec["launches"] and FUSED_TRAFFIC_PER_EDGE_LAUNCH:
-            traffic = FUSED_TRAFFIC_PER_EDGE_LAUNCH * edges / max(1, -(-edges // args.chunk)) if world == 1 else None
+            per_rank = edges / world  # every rank launches over its own targets' edges
+            traffic = FUSED_TRAFFIC_PER_EDGE_LAUNCH * per_rank / max(1, -(-int(per_rank) // args.chunk))
         roof = {"kernel": name + "_kernel", "bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s",
                 "frac": ach / peak, "traffic": traffic, "launches": rec["launches"], "issued": ach * 3, "frac_issued": ach * 3 / peak,
                 "peak_source": f"{peaks['source']} bf16 sustained (kind::f16 issues at the bf16 rate)",
