@@ -23,6 +23,7 @@ SIGNATURES = {
     "fcb200_edge_degree_fwd": [P, P, P, P, P, F32, I64, I64, I32, P],
     "fcb200_gather_rotate_bwd": [P, P, P, P, P, P, P, P, P, P, I64, I64, I32, P],
     "fcb200_gather_rotate_bwd_csr": [P, P, P, P, P, I64, I64, P, P, P, P, P, P, I64, I64, I32, P],
+    "fcb200_gather_rotate_bwd_csr_h": [P, P, P, P, P, I64, I64, P, P, P, P, P, P, P, P, I64, I64, I32, P],
     "fcb200_rotate_back_bwd": [P, P, P, P, P, P, I64, I64, I32, P],
     "fcb200_edge_degree_bwd": [P, P, P, P, P, P, F32, I64, I64, I32, P],
     "fcb200_segment_sum": [P, P, P, P, P, I32, F32, I64, I64, P],

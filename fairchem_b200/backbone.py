@@ -567,7 +567,11 @@ def _radial_backward(rad: RadialMLP, tables, grad_rad, acts, zs, zt, nb: int, ou
     """Gradient of the radial weights' loss with respect to the distance basis, into ``out`` [E, nb]."""
     w0, ln1, w1, ln2, w2 = rad.net[0], rad.net[1], rad.net[3], rad.net[4], rad.net[6]
     pre1, st1, pre2, st2 = acts
-    g = _dense(grad_rad, _transposed(w2.weight.detach()), None, grad=grad_rad)
+    if isinstance(grad_rad, tuple):  # half planes written with the block's gradient scale
+        g = torch.empty(grad_rad[0].shape[0], w2.weight.shape[1], dtype=torch.float32, device=grad_rad[0].device)
+        _contract(grad_rad, _transposed(w2.weight.detach()), None, g, _GemmState.a_scale)
+    else:
+        g = _dense(grad_rad, _transposed(w2.weight.detach()), None, grad=grad_rad)
     gp = torch.empty_like(g)
     ops.radial_act_bwd_.raw(g, pre2, None, None, None, None, ln2.weight.detach(), ln2.bias.detach(), st2, gp)
     _dense(gp, _transposed(w1.weight.detach()), None, out=g, grad=gp)
@@ -929,8 +933,13 @@ class _EdgeBlockFn(torch.autograd.Function):
                 gm = _conv_backward(ew.so2_conv_1, gy)
             del gy
             g_src = torch.empty(ec, nl, c, dtype=x.dtype, device=x.device)
-            grad_rad = torch.empty_like(rad_d)
-            if ew.lmax == 2 and c == 128 and not ops.generic_kernels():
+            csr = ew.lmax == 2 and c == 128 and not ops.generic_kernels()
+            # the radial gradient only feeds the radial MLP's backward contraction: half planes in the half-split mode
+            grad_rad = _new_operand(ec, rad_d.shape[1], x.device) if (csr and _presplit()) else torch.empty_like(rad_d)
+            if csr and isinstance(grad_rad, tuple):
+                ops.gather_rotate_bwd_csr_h_.raw(gm, x, g.src[sl], g.tgt[sl], ch.row_ptr, ch.n0, wig[sl], rad_d, g_src,
+                                                 gx[ch.n0:ch.n1], gwig[sl], grad_rad[0], grad_rad[1], scale)
+            elif csr:
                 # target rows of the chunk are contiguous: their gradient is summed per node inside the kernel
                 ops.gather_rotate_bwd_csr_.raw(gm, x, g.src[sl], g.tgt[sl], ch.row_ptr, ch.n0, wig[sl], rad_d, g_src,
                                                gx[ch.n0:ch.n1], gwig[sl], grad_rad)

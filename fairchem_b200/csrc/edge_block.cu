@@ -227,9 +227,10 @@ template <> struct DegRows<1> { static constexpr int n = 3; __device__ static co
 template <> struct DegRows<2> { static constexpr int n = 5; __device__ static constexpr int row(int i) { constexpr int t[5] = {2, 4, 6, 7, 8}; return t[i]; } };
 
 // One edge, one half (source or target columns), one degree: g[b] += W^T grad rows, dw += grad (x) x, radial gradient.
-template <int l, bool HAS_RAD>
+// RadOut: OutF32 or OutSplit for the radial gradient (it only feeds the radial MLP's backward contraction)
+template <int l, bool HAS_RAD, class RadOut>
 __device__ __forceinline__ void bwd_degree_rows(const float* __restrict__ grad_out, const float* __restrict__ radial,
-                                                float* __restrict__ grad_radial, int64_t e, int half, int channels, int c0,
+                                                const RadOut& grad_radial, int64_t e, int half, int channels, int c0,
                                                 const float (&w)[(2 * l + 1) * (2 * l + 1)], const float4 (&xv)[2 * l + 1],
                                                 float4 (&g)[2 * l + 1], float (&dw)[(2 * l + 1) * (2 * l + 1)]) {
     constexpr int n = 2 * l + 1;
@@ -246,11 +247,11 @@ __device__ __forceinline__ void bwd_degree_rows(const float* __restrict__ grad_o
             const int64_t roff = e * 12LL * channels + radslot(m) * 2 * channels + half * channels + c0;
             const float4 contrib = mul4(go, rot);
             if (m < 3) {
-                st4(grad_radial + roff, contrib);
+                grad_radial.st(roff, contrib);
             } else if (m == 3 || m == 4 || m == 7) {
                 pend = contrib;
             } else {
-                st4(grad_radial + roff, add4(pend, contrib));
+                grad_radial.st(roff, add4(pend, contrib));
             }
             go = mul4(go, ld4(radial + roff));
         }
@@ -263,11 +264,11 @@ __device__ __forceinline__ void bwd_degree_rows(const float* __restrict__ grad_o
 }
 
 // source half, one warp per edge
-template <int l, bool HAS_RAD>
+template <int l, bool HAS_RAD, class RadOut>
 __device__ __forceinline__ void bwd_src_degree(const float* __restrict__ grad_out, const float* __restrict__ x_base,
                                                const float* __restrict__ wig_e, const float* __restrict__ radial,
                                                float* __restrict__ g_base, float* __restrict__ grad_wig_e,
-                                               float* __restrict__ grad_radial, int64_t e, int lane, int channels) {
+                                               const RadOut& grad_radial, int64_t e, int lane, int channels) {
     constexpr int n = 2 * l + 1, L0 = l * l;
     float w[n * n], dw[n * n];
 #pragma unroll
@@ -282,18 +283,20 @@ __device__ __forceinline__ void bwd_src_degree(const float* __restrict__ grad_ou
             xv[b] = ld4(x_base + (L0 + b) * channels + c0);
             g[b] = f4zero();
         }
-        bwd_degree_rows<l, HAS_RAD>(grad_out, radial, grad_radial, e, 0, channels, c0, w, xv, g, dw);
+        bwd_degree_rows<l, HAS_RAD, RadOut>(grad_out, radial, grad_radial, e, 0, channels, c0, w, xv, g, dw);
 #pragma unroll
         for (int b = 0; b < n; ++b) st4(g_base + (L0 + b) * channels + c0, g[b]);
     }
     reduce_block<n * n, false>(dw, lane, grad_wig_e + woff(l));
 }
 
-template <bool HAS_RAD>
+template <bool HAS_RAD, class RadOut>
 __global__ void __launch_bounds__(kWarpsPerBlock* kWarp, 2)
     gather_rotate_bwd_src_kernel(const float* __restrict__ grad_out, const float* __restrict__ x, const int32_t* __restrict__ src,
                                  const float* __restrict__ wig, const float* __restrict__ radial, float* __restrict__ g_src,
-                                 float* __restrict__ grad_wig, float* __restrict__ grad_radial, int64_t num_edges, int channels) {
+                                 float* __restrict__ grad_wig, RadOut grad_radial, const float* __restrict__ scale_ptr,
+                                 int64_t num_edges, int channels) {
+    grad_radial.load_scale(scale_ptr);
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
@@ -303,20 +306,20 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp, 2)
         float* g_base = g_src + e * node_stride;
         const float* wig_e = wig + e * FCB200_WIG;
         float* gw = grad_wig + e * FCB200_WIG;
-        bwd_src_degree<0, HAS_RAD>(grad_out, x_base, wig_e, radial, g_base, gw, grad_radial, e, lane, channels);
-        bwd_src_degree<1, HAS_RAD>(grad_out, x_base, wig_e, radial, g_base, gw, grad_radial, e, lane, channels);
-        bwd_src_degree<2, HAS_RAD>(grad_out, x_base, wig_e, radial, g_base, gw, grad_radial, e, lane, channels);
+        bwd_src_degree<0, HAS_RAD, RadOut>(grad_out, x_base, wig_e, radial, g_base, gw, grad_radial, e, lane, channels);
+        bwd_src_degree<1, HAS_RAD, RadOut>(grad_out, x_base, wig_e, radial, g_base, gw, grad_radial, e, lane, channels);
+        bwd_src_degree<2, HAS_RAD, RadOut>(grad_out, x_base, wig_e, radial, g_base, gw, grad_radial, e, lane, channels);
     }
 }
 
 // target half, one warp per target node and degree (128 channels): the node gradient of the degree's rows is summed
 // over the target's edges in registers and added to the node rows once; the Wigner gradient is added to what the
 // source kernel stored
-template <int l, bool HAS_RAD>
+template <int l, bool HAS_RAD, class RadOut>
 __device__ __forceinline__ void bwd_tgt_degree(const float* __restrict__ grad_out, const float* __restrict__ x_base,
                                                const float* __restrict__ wig, const float* __restrict__ radial,
                                                float* __restrict__ g_base, float* __restrict__ grad_wig,
-                                               float* __restrict__ grad_radial, int eb, int ee, int lane) {
+                                               const RadOut& grad_radial, int eb, int ee, int lane) {
     constexpr int n = 2 * l + 1, L0 = l * l, channels = 128;
     const int c0 = lane * 4;
     float4 xv[n], gt[n];
@@ -332,19 +335,20 @@ __device__ __forceinline__ void bwd_tgt_degree(const float* __restrict__ grad_ou
             w[i] = __ldg(wig + e * FCB200_WIG + woff(l) + i);
             dw[i] = 0.f;
         }
-        bwd_degree_rows<l, HAS_RAD>(grad_out, radial, grad_radial, e, 1, channels, c0, w, xv, gt, dw);
+        bwd_degree_rows<l, HAS_RAD, RadOut>(grad_out, radial, grad_radial, e, 1, channels, c0, w, xv, gt, dw);
         reduce_block<n * n, true>(dw, lane, grad_wig + e * FCB200_WIG + woff(l));
     }
 #pragma unroll
     for (int b = 0; b < n; ++b) st4(g_base + (L0 + b) * channels + c0, add4(ld4(g_base + (L0 + b) * channels + c0), gt[b]));
 }
 
-template <bool HAS_RAD>
+template <bool HAS_RAD, class RadOut>
 __global__ void __launch_bounds__(kWarpsPerBlock* kWarp, 2)
     gather_rotate_bwd_tgt_kernel(const float* __restrict__ grad_out, const float* __restrict__ x, const int32_t* __restrict__ row_ptr,
                                   int64_t tgt_base, const float* __restrict__ wig, const float* __restrict__ radial,
-                                  float* __restrict__ gx_tgt, float* __restrict__ grad_wig, float* __restrict__ grad_radial,
-                                  int64_t num_targets) {
+                                  float* __restrict__ gx_tgt, float* __restrict__ grad_wig, RadOut grad_radial,
+                                  const float* __restrict__ scale_ptr, int64_t num_targets) {
+    grad_radial.load_scale(scale_ptr);
     const int lane = threadIdx.x & 31;
     const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
     const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
@@ -353,9 +357,9 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp, 2)
         if (eb == ee) continue;
         const float* x_base = x + (tgt_base + n) * 9LL * 128;
         float* g_base = gx_tgt + n * 9LL * 128;
-        bwd_tgt_degree<0, HAS_RAD>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, eb, ee, lane);
-        bwd_tgt_degree<1, HAS_RAD>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, eb, ee, lane);
-        bwd_tgt_degree<2, HAS_RAD>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, eb, ee, lane);
+        bwd_tgt_degree<0, HAS_RAD, RadOut>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, eb, ee, lane);
+        bwd_tgt_degree<1, HAS_RAD, RadOut>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, eb, ee, lane);
+        bwd_tgt_degree<2, HAS_RAD, RadOut>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, eb, ee, lane);
     }
 }
 
@@ -697,16 +701,40 @@ int fcb200_gather_rotate_bwd_csr(const float* grad_out, const float* x, const in
     cudaStream_t st = FCB_STREAM;
     const int tgrid = warp_grid(num_targets, kWarpsPerBlock);
     if (radial) {
-        gather_rotate_bwd_src_kernel<true><<<FCB_LAUNCH(num_edges)>>>(grad_out, x, src, wig, radial, g_src, grad_wig, grad_radial,
-                                                                      num_edges, channels);
-        gather_rotate_bwd_tgt_kernel<true><<<tgrid, kWarpsPerBlock * kWarp, 0, st>>>(grad_out, x, row_ptr, tgt_base, wig, radial, gx_tgt,
-                                                                                     grad_wig, grad_radial, num_targets);
+        gather_rotate_bwd_src_kernel<true, OutF32><<<FCB_LAUNCH(num_edges)>>>(grad_out, x, src, wig, radial, g_src, grad_wig,
+                                                                              OutF32{grad_radial}, nullptr, num_edges, channels);
+        gather_rotate_bwd_tgt_kernel<true, OutF32><<<tgrid, kWarpsPerBlock * kWarp, 0, st>>>(
+            grad_out, x, row_ptr, tgt_base, wig, radial, gx_tgt, grad_wig, OutF32{grad_radial}, nullptr, num_targets);
     } else {
-        gather_rotate_bwd_src_kernel<false><<<FCB_LAUNCH(num_edges)>>>(grad_out, x, src, wig, nullptr, g_src, grad_wig, nullptr,
-                                                                       num_edges, channels);
-        gather_rotate_bwd_tgt_kernel<false><<<tgrid, kWarpsPerBlock * kWarp, 0, st>>>(grad_out, x, row_ptr, tgt_base, wig, nullptr, gx_tgt,
-                                                                                      grad_wig, nullptr, num_targets);
+        gather_rotate_bwd_src_kernel<false, OutF32><<<FCB_LAUNCH(num_edges)>>>(grad_out, x, src, wig, nullptr, g_src, grad_wig,
+                                                                               OutF32{nullptr}, nullptr, num_edges, channels);
+        gather_rotate_bwd_tgt_kernel<false, OutF32><<<tgrid, kWarpsPerBlock * kWarp, 0, st>>>(
+            grad_out, x, row_ptr, tgt_base, wig, nullptr, gx_tgt, grad_wig, OutF32{nullptr}, nullptr, num_targets);
     }
+    return launch_status();
+}
+
+int fcb200_gather_rotate_bwd_csr_h(const float* grad_out, const float* x, const int32_t* src, const int32_t* tgt,
+                                   const int32_t* row_ptr, int64_t tgt_base, int64_t num_targets, const float* wig,
+                                   const float* radial, float* g_src, float* gx_tgt, float* grad_wig, void* grad_radial_hi,
+                                   void* grad_radial_lo, const float* scale, int64_t num_edges, int64_t num_nodes,
+                                   int32_t channels, void* stream) {
+    int rc = check_common(grad_out, x, num_edges, channels);
+    if (rc) return rc;
+    if (channels != 128) return FCB200_EINVAL;
+    if (!src || !tgt || !row_ptr || !wig || !radial || !g_src || !gx_tgt || !grad_wig || !grad_radial_hi || !grad_radial_lo ||
+        num_nodes < 0 || num_targets < 0 || tgt_base < 0 || tgt_base + num_targets > num_nodes)
+        return FCB200_EINVAL;
+    if (!aligned16(g_src) || !aligned16(gx_tgt) || !aligned16(radial) || !aligned8(grad_radial_hi) || !aligned8(grad_radial_lo))
+        return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    cudaStream_t st = FCB_STREAM;
+    const int tgrid = warp_grid(num_targets, kWarpsPerBlock);
+    const OutSplit out{static_cast<__half*>(grad_radial_hi), static_cast<__half*>(grad_radial_lo), 1.0f};
+    gather_rotate_bwd_src_kernel<true, OutSplit><<<FCB_LAUNCH(num_edges)>>>(grad_out, x, src, wig, radial, g_src, grad_wig, out, scale,
+                                                                            num_edges, channels);
+    gather_rotate_bwd_tgt_kernel<true, OutSplit><<<tgrid, kWarpsPerBlock * kWarp, 0, st>>>(grad_out, x, row_ptr, tgt_base, wig, radial,
+                                                                                         gx_tgt, grad_wig, out, scale, num_targets);
     return launch_status();
 }
 

@@ -228,6 +228,25 @@ def gather_rotate_bwd_csr_(grad_out: Tensor, x: Tensor, src: Tensor, tgt: Tensor
              _p(grad_wig), _p(grad_radial), e, x.shape[0], c, _stream()), nbytes=nbytes, flops=e * 6 * s.nw * 2 * c, launches=2)
 
 
+@_op("gather_rotate_bwd_csr_h", ("g_src", "gx_tgt", "grad_wig", "grad_radial_hi", "grad_radial_lo"))
+def gather_rotate_bwd_csr_h_(grad_out: Tensor, x: Tensor, src: Tensor, tgt: Tensor, row_ptr: Tensor, tgt_base: int, wig: Tensor,
+                             radial: Tensor, g_src: Tensor, gx_tgt: Tensor, grad_wig: Tensor, grad_radial_hi: Tensor,
+                             grad_radial_lo: Tensor, scale: Optional[Tensor]) -> None:
+    """gather_rotate_bwd_csr_ with the radial gradient written as the half-precision (hi, lo) planes of (value * scale)."""
+    _chk(grad_out, x, src, tgt, row_ptr, wig, radial, g_src, gx_tgt, grad_wig, grad_radial_hi, grad_radial_lo, scale)
+    _f32(grad_out, x, wig, radial, g_src, gx_tgt, grad_wig, scale)
+    _h16(grad_radial_hi, grad_radial_lo)
+    e, c, nt = src.shape[0], x.shape[2], row_ptr.shape[0] - 1
+    s = _shape(_BY_NL, x.shape[1], "rows per node")
+    if _lx(s) or c != 128 or gx_tgt.shape[0] != nt:
+        raise _lib.FairchemB200Error("gather_rotate_bwd_csr_h: lmax 2, 128 channels, one gx_tgt row block per target")
+    nbytes = e * (4 * (2 * s.nm * c + 2 * s.nl * c + 3 * s.nw + 4 * s.nrad * c) + 8) + nt * 4 * 3 * s.nl * c
+    _launch("gather_rotate_bwd", "fcb200_gather_rotate_bwd_csr_h",
+            (_p(grad_out), _p(x), _p(src), _p(tgt), _p(row_ptr), tgt_base, nt, _p(wig), _p(radial), _p(g_src), _p(gx_tgt),
+             _p(grad_wig), _p(grad_radial_hi), _p(grad_radial_lo), _p(scale), e, x.shape[0], c, _stream()), nbytes=nbytes,
+            flops=e * 6 * s.nw * 2 * c, launches=2)
+
+
 @_op("rotate_back_reduce_fwd", ("out",))
 def rotate_back_reduce_fwd_(msg: Tensor, winv: Tensor, row_ptr: Tensor, out: Tensor) -> None:
     _chk(msg, winv, row_ptr, out)

@@ -116,6 +116,13 @@ int fcb200_gather_rotate_bwd_csr(const float* grad_out, const float* x, const in
                                  const int32_t* row_ptr, int64_t tgt_base, int64_t num_targets, const float* wig,
                                  const float* radial, float* g_src, float* gx_tgt, float* grad_wig, float* grad_radial,
                                  int64_t num_edges, int64_t num_nodes, int32_t channels, void* stream);
+/* fcb200_gather_rotate_bwd_csr with the radial gradient written as half planes (values times *scale, a device pointer to
+ * a power of two or NULL): it only feeds the backward contraction of the radial MLP's output layer. */
+int fcb200_gather_rotate_bwd_csr_h(const float* grad_out, const float* x, const int32_t* src, const int32_t* tgt,
+                                   const int32_t* row_ptr, int64_t tgt_base, int64_t num_targets, const float* wig,
+                                   const float* radial, float* g_src, float* gx_tgt, float* grad_wig, void* grad_radial_hi,
+                                   void* grad_radial_lo, const float* scale, int64_t num_edges, int64_t num_nodes,
+                                   int32_t channels, void* stream);
 
 /*
  * Backward of fcb200_rotate_back_reduce_fwd: grad_msg = Winv^T grad_out[tgt] (M-major) and

@@ -361,3 +361,30 @@ def test_gather_rotate_backward_with_in_kernel_target_sum(ops, with_radial):
     torch.testing.assert_close(gw1, gw0[e0:e1], rtol=1e-5, atol=1e-4)
     if with_radial:
         torch.testing.assert_close(gr1, gr0[e0:e1], rtol=0, atol=0)
+
+
+def test_gather_rotate_backward_radial_gradient_as_half_planes(ops):
+    """fcb200_gather_rotate_bwd_csr_h: same results as the float32 form, the radial gradient as (hi, lo) planes times a scale."""
+    g = torch.Generator().manual_seed(12)
+    n, c = 40, 128
+    deg = torch.randint(1, 7, (n,), generator=g)
+    tgt = torch.repeat_interleave(torch.arange(n), deg)
+    e = int(tgt.shape[0])
+    src = torch.randint(0, n, (e,), generator=g).int().cuda()
+    row_ptr = torch.zeros(n + 1, dtype=torch.int32)
+    row_ptr[1:] = torch.cumsum(deg, 0)
+    x = torch.randn(n, 9, c, generator=g).cuda()
+    wig = torch.randn(e, 35, generator=g).cuda()
+    go = (torch.randn(e, 9, 2 * c, generator=g) * 1e-2).cuda()
+    rad = torch.randn(e, 6 * 2 * c, generator=g).cuda()
+    tgt_c, rp = tgt.int().cuda(), row_ptr.cuda()
+    f = lambda *s: torch.empty(*s, device="cuda")  # noqa: E731
+    gs0, gw0, gr0, gx0 = f(e, 9, c), f(e, 35), torch.empty_like(rad), torch.zeros(n, 9, c, device="cuda")
+    ops.gather_rotate_bwd_csr_(go, x, src, tgt_c, rp, 0, wig, rad, gs0, gx0, gw0, gr0)
+    gs1, gw1, gx1 = f(e, 9, c), f(e, 35), torch.zeros(n, 9, c, device="cuda")
+    hi, lo = torch.empty(e, 6 * 2 * c, dtype=torch.float16, device="cuda"), torch.empty(e, 6 * 2 * c, dtype=torch.float16, device="cuda")
+    scale = torch.tensor([256.0], device="cuda")
+    ops.gather_rotate_bwd_csr_h_(go, x, src, tgt_c, rp, 0, wig, rad, gs1, gx1, gw1, hi, lo, scale)
+    assert torch.equal(gs1, gs0) and torch.equal(gx1, gx0) and torch.equal(gw1, gw0)
+    got = (hi.float() + lo.float() / 2048.0) / 256.0
+    torch.testing.assert_close(got, gr0, rtol=1e-6, atol=1e-7 * float(gr0.abs().max()))
