@@ -84,14 +84,18 @@ __device__ __forceinline__ bool source_of(const int32_t* __restrict__ sys, int n
     return true;
 }
 
+// max_cells bounds the cell index against the caller's arrays: a system table that describes more cells than the
+// caller sized its counters for must not write past them (such sources are dropped like sources outside the grid)
 __global__ void rg_count_sources_kernel(const float* __restrict__ pos, const int32_t* __restrict__ sys, int nsys,
-                                        int64_t num_sources, int32_t* __restrict__ cell_count, int32_t* __restrict__ source_cell) {
+                                        int64_t num_sources, int32_t* __restrict__ cell_count, int32_t* __restrict__ source_cell,
+                                        int64_t max_cells) {
     const int64_t sid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (sid >= num_sources) return;
     Sys s;
     float px, py, pz;
     int cell;
-    if (source_of(sys, nsys, pos, sid, s, px, py, pz, cell)) atomicAdd(cell_count + cell, 1);
+    if (source_of(sys, nsys, pos, sid, s, px, py, pz, cell) && cell < max_cells) atomicAdd(cell_count + cell, 1);
+    else cell = -1;
     source_cell[sid] = cell;
 }
 
@@ -382,7 +386,7 @@ int fcb200_rg_count_sources(const float* pos, const int32_t* sys, int32_t num_sy
     if (num_sources >= (1LL << 31)) return FCB200_ERANGE;
     if (num_sources == 0) return FCB200_OK;
     rg_count_sources_kernel<<<(unsigned)((num_sources + 255) / 256), 256, 0, static_cast<cudaStream_t>(stream)>>>(
-        pos, sys, num_systems, num_sources, cell_count, source_cell);
+        pos, sys, num_systems, num_sources, cell_count, source_cell, (int64_t)1 << 40);  // the caller sized cell_count from the same table
     return launch_status();
 }
 
@@ -468,8 +472,9 @@ int fcb200_rg_neighbor_counts_static(const float* pos, const int32_t* sys, int32
     err = cudaMemsetAsync(cell_fill, 0, (size_t)(num_cells + 1) * 4, s);
     if (err != cudaSuccess) return static_cast<int>(err);
     if (num_sources > 0) {
+        // num_cells (checked against the fixed scratch above) bounds every cell index the kernels derive from the table
         rg_count_sources_kernel<<<(unsigned)((num_sources + 255) / 256), 256, 0, s>>>(pos, sys, num_systems, num_sources, cell_count,
-                                                                                    source_cell);
+                                                                                    source_cell, num_cells);
         rc = launch_status();
         if (rc) return rc;
     }

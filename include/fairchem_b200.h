@@ -307,6 +307,8 @@ int fcb200_rg_refresh(const float* pos, const int32_t* sys, int32_t num_systems,
  *   limits      num_sources <= FCB200_STATIC_MAX_SOURCES and num_cells <= FCB200_STATIC_MAX_CELLS
  *               (about 6 MiB of device memory per GPU that loads the library, held until exit);
  *               larger sizes return FCB200_ERANGE and launch nothing
+ *   sys         must describe exactly num_cells grid cells; a source whose cell index falls beyond num_cells is
+ *               dropped, never written
  *   first call  on each device looks up the array's device address (cudaGetSymbolAddress); make that
  *               call during set-up, before any stream capture
  *   sharing     all calls on a device use the same array, which keeps the previous call's contents

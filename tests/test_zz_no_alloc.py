@@ -67,6 +67,20 @@ def test_static_scratch_entry_matches_regular_entry_points_twice():
         assert int(want.sum()) > 0
 
 
+def test_static_scratch_entry_counts_match_the_cpu_oracle():
+    """Independent check (the regular entry points run the same kernels): candidates per target against the numpy
+    restatement of the reference's search with the max-neighbour rule switched off."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from oracle import radius_graph_oracle as G
+
+    data = synthetic.water_box(900, seed=6)
+    got, _, _, _ = _counts_both_ways(data, 6.0)
+    ei, _, _, _ = G.radius_graph(data.pos.numpy(), data.cell.numpy(), data.pbc.numpy(), data.natoms.numpy(), 6.0, 0)
+    want = np.bincount(ei[1], minlength=900)
+    assert np.array_equal(got.numpy(), want)
+
+
 def test_static_scratch_entry_rejects_oversized_problems():
     if not torch.cuda.is_available():
         pytest.skip("needs a CUDA device")
