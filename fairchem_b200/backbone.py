@@ -548,6 +548,67 @@ def _radial_forward(rad: RadialMLP, tables, gauss_c, zs, zt, nb: int, keep: Opti
     return _dense(h, w2.weight.detach(), w2.bias.detach(), out=out), (pre1, st1, pre2, st2)
 
 
+def _rows(x, sl):
+    return (x[0][sl], x[1][sl]) if isinstance(x, tuple) else x[sl]
+
+
+def _radial_hidden(rad: RadialMLP, tables, gauss, zs, zt, nb: int, keep: "_RadialKeep", from_kept: bool = False):
+    """The two hidden layers of the radial MLP for ALL edges of a layer in one go (their kernels are short: per chunk
+    they would be launch- and tail-bound): returns the second hidden activation (half planes in the half-split mode) with
+    pre-activations and LayerNorm statistics left in ``keep``.  ``from_kept``: the first layer's results are already in
+    ``keep``; only the last activation is recomputed from them."""
+    w0, ln1, w1, ln2 = rad.net[0], rad.net[1], rad.net[3], rad.net[4]
+    e, dev = gauss.shape[0], gauss.device
+    planes = _presplit() and _GemmState.fused_conv and keep.pre1.shape[1] == 128
+    h = _new_operand(e, keep.pre1.shape[1], dev) if planes else torch.empty(e, keep.pre1.shape[1], dtype=torch.float32, device=dev)
+
+    def act(pre, t0, t1, z0, z1, ln, st):
+        if planes:
+            ops.radial_act_fwd_h_.raw(pre, t0, t1, z0, z1, ln.weight.detach(), ln.bias.detach(), float(ln.eps), h[0], h[1], st)
+        else:
+            ops.radial_act_fwd_.raw(pre, t0, t1, z0, z1, ln.weight.detach(), ln.bias.detach(), float(ln.eps), h, st)
+
+    if not from_kept:
+        _dense(gauss, w0.weight.detach()[:, :nb], w0.bias.detach(), out=keep.pre1)
+        act(keep.pre1, tables[0], tables[1], zs, zt, ln1, keep.st1)
+        if planes:
+            _contract(h, w1.weight.detach(), w1.bias.detach(), keep.pre2, None)
+        else:
+            _dense(h, w1.weight.detach(), w1.bias.detach(), out=keep.pre2)
+    act(keep.pre2, None, None, None, None, ln2, keep.st2)
+    return h
+
+
+def _radial_out(rad: RadialMLP, h, out=None):
+    """Output layer of the radial MLP on a slice of the hidden activation."""
+    w2 = rad.net[6]
+    if isinstance(h, tuple):
+        if out is None:
+            out = torch.empty(h[0].shape[0], w2.weight.shape[0], dtype=torch.float32, device=h[0].device)
+        return _fused_linear(h, w2.weight.detach(), w2.bias.detach(), out, "_radial_out")
+    return _dense(h, w2.weight.detach(), w2.bias.detach(), out=out)
+
+
+def _radial_backward_hidden(rad: RadialMLP, tables, g, keep: "_RadialKeep", zs, zt, nb: int, out):
+    """From g = d loss / d (second hidden activation) for all edges of a layer to the gradient of the distance basis."""
+    w0, ln1, w1, ln2 = rad.net[0], rad.net[1], rad.net[3], rad.net[4]
+    gp = torch.empty_like(g)
+    ops.radial_act_bwd_.raw(g, keep.pre2, None, None, None, None, ln2.weight.detach(), ln2.bias.detach(), keep.st2, gp)
+    _dense(gp, _transposed(w1.weight.detach()), None, out=g, grad=gp)
+    ops.radial_act_bwd_.raw(g, keep.pre1, tables[0], tables[1], zs, zt, ln1.weight.detach(), ln1.bias.detach(), keep.st1, gp)
+    return _dense(gp, _transposed(w0.weight.detach()[:, :nb]), None, out=out, grad=gp)
+
+
+def _radial_out_backward(rad: RadialMLP, grad_rad, out):
+    """out = grad_rad @ W2 (gradient of the second hidden activation) for one chunk."""
+    w2 = rad.net[6]
+    if isinstance(grad_rad, tuple):  # half planes written with the block's gradient scale
+        _contract(grad_rad, _transposed(w2.weight.detach()), None, out, _GemmState.a_scale)
+    else:
+        _dense(grad_rad, _transposed(w2.weight.detach()), None, out=out, grad=grad_rad)
+    return out
+
+
 def _fused_linear(x, w: torch.Tensor, bias, out: torch.Tensor, label: str = "_linear"):
     """out = x @ w^T + bias for pre-split x [E, K] through the row-tile-major fused kernel (eight epilogue warps): the
     form for wide outputs over a short K, where storing the result is the bound.  N a multiple of 128, at most 40 tiles."""
@@ -835,15 +896,18 @@ class _EdgeBlockFn(torch.autograd.Function):
         y_all = torch.empty(rows, (ew.lmax + nm) * h, dtype=x.dtype, device=x.device)[: g.num_edges] if keep_level >= 1 else None
         msg_all = torch.empty(rows, nm, c, dtype=x.dtype, device=x.device)[: g.num_edges] if keep_level >= 2 else None
         rfn = ew.so2_conv_1.rad_func
-        rkeep = None
-        if keep_level >= 1:  # level 3 also keeps the radial weights
-            rkeep = _RadialKeep(g.num_edges, rfn.net[0].weight.shape[0], rfn.net[6].weight.shape[0], keep_level >= 3, x.device)
+        # pre-activations and statistics of the radial MLP's hidden layers (kept for the backward pass from level 1 on;
+        # level 3 also keeps the radial weights)
+        rkeep = _RadialKeep(g.num_edges, rfn.net[0].weight.shape[0], rfn.net[6].weight.shape[0], keep_level >= 3, x.device)
         fused = _use_fused(ew)
         with torch.no_grad():
+            h2 = _radial_hidden(rfn, tables, gauss, ectx.z_src, ectx.z_tgt, nb, rkeep) if g.num_edges else None
+            if keep_level < 1:
+                rkeep = None
             for ch in ectx.chunks:
                 sl = slice(ch.e0, ch.e1)
                 ec = ch.e1 - ch.e0
-                rad, _ = _radial_forward(rfn, tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb, rkeep, sl)
+                rad = _radial_out(rfn, _rows(h2, sl), None if rkeep is None or rkeep.out is None else rkeep.out[sl])
                 m = _gather_rotate(x, g, sl, wig, rad, nm)
                 del rad
                 msg_out = torch.empty(ec, nm * c, dtype=x.dtype, device=x.device) if msg_all is None else msg_all[sl].view(ec, nm * c)
@@ -860,6 +924,7 @@ class _EdgeBlockFn(torch.autograd.Function):
                     del m
                     msg = _conv_forward(ew.so2_conv_2, _gate(y, h, nm), out=msg_out).view(ec, nm, c)
                 ops.rotate_back_reduce_fwd_.raw(msg, winv[sl], ch.row_ptr, out[ch.n0:ch.n1])
+            del h2
         ctx.save_for_backward(x, wig, winv, gauss)
         ctx.ew, ctx.tables, ctx.ectx, ctx.nb, ctx.kept = ew, tables, ectx, nb, (y_all, msg_all, rkeep)
         return out
@@ -887,11 +952,17 @@ class _EdgeBlockFn(torch.autograd.Function):
         rfn = ew.so2_conv_1.rad_func
         scale = _GemmState.a_scale  # the power of two the gradient operands of this block are written with
         fused = _use_fused(ew)
+        have_hidden = rkeep is not None
+        if rkeep is None:
+            rkeep = _RadialKeep(g.num_edges, rfn.net[0].weight.shape[0], rfn.net[6].weight.shape[0], False, x.device)
+        h2 = None
+        if rkeep.out is None and g.num_edges:  # the radial weights are recomputed per chunk from the hidden activation
+            h2 = _radial_hidden(rfn, tables, gauss, ectx.z_src, ectx.z_tgt, nb, rkeep, from_kept=have_hidden)
+        g_hidden = torch.empty(g.num_edges, rfn.net[6].weight.shape[1], dtype=x.dtype, device=x.device)
         for ch in ectx.chunks:
             sl = slice(ch.e0, ch.e1)
             ec = ch.e1 - ch.e0
-            rad_d, acts = _radial_forward(rfn, tables, gauss[sl], ectx.z_src[sl], ectx.z_tgt[sl], nb, rkeep, sl,
-                                          from_kept=rkeep is not None)
+            rad_d = rkeep.out[sl] if rkeep.out is not None else _radial_out(rfn, _rows(h2, sl))
             y = None if y_all is None else y_all[sl]
             msg = None if msg_all is None else msg_all[sl]
             if fused and (y is None or msg is None):
@@ -953,8 +1024,11 @@ class _EdgeBlockFn(torch.autograd.Function):
             ops.segment_sum(g_src, ch.src_ptr, ch.src_perm, ch.src_nodes.shape[0], out=gx, out_index=ch.src_nodes,
                             accumulate=True)
             del g_src
-            _radial_backward(rfn, tables, grad_rad, acts, ectx.z_src[sl], ectx.z_tgt[sl], nb, ggauss[sl])
-            del rad_d, grad_rad, acts
+            _radial_out_backward(rfn, grad_rad, g_hidden[sl])
+            del rad_d, grad_rad
+        del h2
+        if g.num_edges:  # the hidden layers' backward over all edges of the layer at once
+            _radial_backward_hidden(rfn, tables, g_hidden, rkeep, ectx.z_src, ectx.z_tgt, nb, ggauss)
         return gx, gwig, gwinv, ggauss, None, None, None, None, None
 
 
