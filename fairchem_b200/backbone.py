@@ -742,48 +742,57 @@ def _fused_tiles(shapes, transposed: bool, describe) -> list:
     return tiles
 
 
+def fused_conv_tile_lists(lmax: int, h: int, s1, s2) -> dict:
+    """Tile lists of the four fused launches of one Edgewise module.  ``s1`` / ``s2`` = [(n_i, k_i)] of the m-blocks
+    of the first / second convolution; the first convolution's output is ``lmax*h`` gate columns followed by one
+    ``h``-wide block per M-major row.  Keys: "fwd1" / "fwd1_keep" (convolution 1 with the gate in the epilogue; the
+    keep form also stores the pre-activation), "fwd2", "bwd2" (transposed convolution 2 with the gate's backward in the
+    epilogue) and "bwd1".  Gate tiles of "fwd1" come first, so every gated tile finds its gate columns written."""
+    deg = _row_degrees(lmax)
+    gates = lmax * h
+
+    def fwd1(keep):
+        def describe(c):
+            if c < gates:
+                return c, ops.CONV_PLAIN, 0, 0, 0
+            r, j = divmod(c - gates, h)
+            flags = ops.CONV_KEEP if keep else 0
+            if r == 0:
+                return c - gates, ops.CONV_SILU, c, 0, flags
+            return c - gates, ops.CONV_GATED, c, (deg[r] - 1) * h + j, flags
+        return _fused_tiles(s1, False, describe)
+
+    rows_of = {l: [r for r, d in enumerate(deg) if d == l] for l in range(1, lmax + 1)}
+
+    def bwd2(c):
+        r, j = divmod(c, h)
+        if r == 0:
+            return gates + c, ops.CONV_SILU_BWD, gates + c, 0, 0
+        rows = rows_of[deg[r]]
+        flags = (ops.CONV_FIRST if r == rows[0] else 0) | (ops.CONV_LAST if r == rows[-1] else 0)
+        return gates + c, ops.CONV_GATED_BWD, gates + c, (deg[r] - 1) * h + j, flags
+
+    plain = lambda c: (c, ops.CONV_PLAIN, 0, 0, 0)  # noqa: E731
+    # the rows of one degree (and column tile) back to back: their gate-gradient sum stays in registers
+    t2 = _fused_tiles(s2, True, bwd2)
+    t2 = [t2[i:i + 9] for i in range(0, len(t2), 9)]
+    t2.sort(key=lambda t: (t[5] != ops.CONV_SILU_BWD, t[7], t[4]))
+    return {"fwd1": fwd1(False), "fwd1_keep": fwd1(True), "fwd2": _fused_tiles(s2, False, plain),
+            "bwd2": [v for t in t2 for v in t], "bwd1": _fused_tiles(s1, True, plain)}
+
+
 class _FusedConvPlan:
     """Tile lists and split weights of one Edgewise module's two convolutions for the fused launches."""
 
     def __init__(self, ew: "Edgewise"):
         h, lmax = ew.hidden, ew.lmax
-        deg = _row_degrees(lmax)
-        gates = lmax * h
         w1, w2 = _conv_weights(ew.so2_conv_1), _conv_weights(ew.so2_conv_2)
         s1, s2 = [tuple(w.shape) for w in w1], [tuple(w.shape) for w in w2]
-        self.gates, self.y_width = gates, gates + len(deg) * h
+        self.gates, self.y_width = lmax * h, lmax * h + len(_row_degrees(lmax)) * h
         self.versions = _conv_versions(ew)
-
-        def fwd1(keep):
-            def describe(c):
-                if c < gates:
-                    return c, ops.CONV_PLAIN, 0, 0, 0
-                r, j = divmod(c - gates, h)
-                flags = ops.CONV_KEEP if keep else 0
-                if r == 0:
-                    return c - gates, ops.CONV_SILU, c, 0, flags
-                return c - gates, ops.CONV_GATED, c, (deg[r] - 1) * h + j, flags
-            return _fused_tiles(s1, False, describe)
-
-        rows_of = {l: [r for r, d in enumerate(deg) if d == l] for l in range(1, lmax + 1)}
-
-        def bwd2(c):
-            r, j = divmod(c, h)
-            if r == 0:
-                return gates + c, ops.CONV_SILU_BWD, gates + c, 0, 0
-            rows = rows_of[deg[r]]
-            flags = (ops.CONV_FIRST if r == rows[0] else 0) | (ops.CONV_LAST if r == rows[-1] else 0)
-            return gates + c, ops.CONV_GATED_BWD, gates + c, (deg[r] - 1) * h + j, flags
-
-        plain = lambda c: (c, ops.CONV_PLAIN, 0, 0, 0)  # noqa: E731
-        self.fwd1 = {False: fwd1(False), True: fwd1(True)}
-        self.fwd2 = _fused_tiles(s2, False, plain)
-        # the rows of one degree (and column tile) back to back: their gate-gradient sum stays in registers
-        t2 = _fused_tiles(s2, True, bwd2)
-        t2 = [t2[i:i + 9] for i in range(0, len(t2), 9)]
-        t2.sort(key=lambda t: (t[5] != ops.CONV_SILU_BWD, t[7], t[4]))
-        self.bwd2 = [v for t in t2 for v in t]
-        self.bwd1 = _fused_tiles(s1, True, plain)
+        lists = fused_conv_tile_lists(lmax, h, s1, s2)
+        self.fwd1 = {False: lists["fwd1"], True: lists["fwd1_keep"]}
+        self.fwd2, self.bwd2, self.bwd1 = lists["fwd2"], lists["bwd2"], lists["bwd1"]
         self.ok = max(len(t) // 9 for t in (self.fwd1[True], self.fwd2, self.bwd2, self.bwd1)) <= ops.CONV_MAX_TILES and h % 128 == 0
         # the fused launch re-reads a 128-edge A tile once per output tile of its m-block and counts on L2 for it; with
         # K beyond ~1024 (lmax 4: 1280 / 2048 / 1536) the tiles of all CTAs together no longer fit there and the separate
