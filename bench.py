@@ -473,8 +473,9 @@ def main():
     ap.add_argument("--skip-cpu", action="store_true")
     ap.add_argument("--generic-kernels", action="store_true",
                     help="route the lmax=2 model through the any-lmax edge-block kernels (A/B measurement)")
-    ap.add_argument("--conv-variant", type=int, default=None, choices=[0, 1],
-                    help="launch form of the fused convolution kernel: 0 one CTA per 128-edge tile, 1 CTA pairs (A/B measurement)")
+    ap.add_argument("--conv-variant", type=int, default=None, choices=[-1, 0, 1, 2],
+                    help="launch form of the fused convolution kernel: 0 one CTA per 128-edge tile (32-deep stages), 1 CTA pairs, "
+                         "2 64-deep stages, -1 the default choice per launch (A/B measurement)")
     ap.add_argument("--profile-run", action="store_true",
                     help="for runs under a profiler: allows fewer than 3 warm-up steps; the printed number is not a bench value")
     args = ap.parse_args()

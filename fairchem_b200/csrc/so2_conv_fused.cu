@@ -77,7 +77,22 @@ constexpr int kHalfTile = BM * BK * 2;
 constexpr int kEpiWarps = 8;
 constexpr int kThreads = 64 + 32 * kEpiWarps;          // warp 0 TMA, warp 1 MMA, warps 2-9 epilogue
 constexpr int kAccCols = 2 * BN, kTmemCols = 2 * kAccCols;
-template <int NBUF> constexpr int smem_bytes() { return Cfg<NBUF>::kStages * kStageBytes + kEpiWarps * Cfg<NBUF>::kEpiWarpBytes + 1024 + 256; }
+// KB = k extent of one ring stage: 32 (64-byte rows, 64-byte swizzle) or 64 (128-byte rows, 128-byte swizzle, two
+// stages of 64 KiB)
+template <int NBUF, int KB> constexpr int ring_stages() { return KB == 64 ? 2 : Cfg<NBUF>::kStages; }
+template <int NBUF, int KB = BK> constexpr int smem_bytes() {
+    return ring_stages<NBUF, KB>() * 4 * BM * KB * 2 + kEpiWarps * Cfg<NBUF>::kEpiWarpBytes + 1024 + 256;
+}
+// K-major, 128-byte swizzle: rows at a 128 B pitch, 8-row groups 1024 B apart
+__device__ __forceinline__ uint64_t smem_desc128(uint32_t addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+    d |= (uint64_t)1 << 16;
+    d |= (uint64_t)(1024 >> 4) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;  // SWIZZLE_128B
+    return d;
+}
 
 struct Params {
     const float* bias[3];
@@ -383,7 +398,7 @@ __device__ __forceinline__ void epilogue(const CUtensorMap& map_y, const CUtenso
     if (lane == 0) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");  // all stores of this warp have landed
 }
 
-template <int NBUF>
+template <int NBUF, int KB = BK>
 __global__ void __launch_bounds__(kThreads, 1)
     so2_conv_fused_kernel(const __grid_constant__ CUtensorMap map_ahi, const __grid_constant__ CUtensorMap map_alo,
                           const __grid_constant__ CUtensorMap map_whi0, const __grid_constant__ CUtensorMap map_wlo0,
@@ -392,10 +407,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                           const __grid_constant__ CUtensorMap map_y, const __grid_constant__ CUtensorMap map_ohi,
                           const __grid_constant__ CUtensorMap map_olo, const __grid_constant__ Plan plan,
                           const __grid_constant__ Params prm, int64_t tiles_m) {
-    constexpr int S = Cfg<NBUF>::kStages;
+    constexpr int S = ring_stages<NBUF, KB>();
+    constexpr int kStage = 4 * BM * KB * 2, kPart = BM * KB * 2;  // A_hi | A_lo | W_hi | W_lo
     extern __shared__ uint8_t smem_raw[];
     const uint32_t base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const uint32_t epi_base = base + S * kStageBytes;
+    const uint32_t epi_base = base + S * kStage;
     const uint32_t bar_base = epi_base + kEpiWarps * Cfg<NBUF>::kEpiWarpBytes;
     // barrier block: full[S] | empty[S] | tmem_full[2] | tmem_empty[2] | tmem slot, abort flag, range flag, pad | ld[8]
     auto full_bar = [&](int s) { return bar_base + 8u * s; };
@@ -407,7 +423,7 @@ __global__ void __launch_bounds__(kThreads, 1)
     volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bar_generic + 8 * (2 * S + 4));
     volatile int* abort_flag = reinterpret_cast<volatile int*>(bar_generic + 8 * (2 * S + 4) + 4);
     volatile int* range_flag = reinterpret_cast<volatile int*>(bar_generic + 8 * (2 * S + 4) + 8);
-    auto half_addr = [&](int s, int which) { return base + s * kStageBytes + which * kHalfTile; };
+    auto half_addr = [&](int s, int which) { return base + s * kStage + which * kPart; };
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int ntiles = plan.ntiles;
@@ -451,17 +467,17 @@ __global__ void __launch_bounds__(kThreads, 1)
                     const Tile& t = plan.t[tile_at(plan, ti, (int)(blockIdx.x % 64))];
                     const CUtensorMap* whi = t.w == 0 ? &map_whi0 : (t.w == 1 ? &map_whi1 : &map_whi2);
                     const CUtensorMap* wlo = t.w == 0 ? &map_wlo0 : (t.w == 1 ? &map_wlo1 : &map_wlo2);
-                    const int num_kb = t.k / BK;
+                    const int num_kb = t.k / KB;
                     for (int kb = 0; kb < num_kb; ++kb, ++it) {
                         const int s = (int)(it % S);
                         const uint32_t ph = (uint32_t)((it / S) & 1);
                         ok = mbar_wait(empty_bar(s), ph ^ 1u, abort_flag);
                         if (!ok) break;
-                        mbar_expect_tx(full_bar(s), kStageBytes);
-                        tma_load_2d_hint(half_addr(s, 0), &map_ahi, t.a_col + kb * BK, (int)(mt * BM), full_bar(s), keep);
-                        tma_load_2d_hint(half_addr(s, 1), &map_alo, t.a_col + kb * BK, (int)(mt * BM), full_bar(s), keep);
-                        tma_load_2d_hint(half_addr(s, 2), whi, kb * BK, t.w_row, full_bar(s), keep);
-                        tma_load_2d_hint(half_addr(s, 3), wlo, kb * BK, t.w_row, full_bar(s), keep);
+                        mbar_expect_tx(full_bar(s), kStage);
+                        tma_load_2d_hint(half_addr(s, 0), &map_ahi, t.a_col + kb * KB, (int)(mt * BM), full_bar(s), keep);
+                        tma_load_2d_hint(half_addr(s, 1), &map_alo, t.a_col + kb * KB, (int)(mt * BM), full_bar(s), keep);
+                        tma_load_2d_hint(half_addr(s, 2), whi, kb * KB, t.w_row, full_bar(s), keep);
+                        tma_load_2d_hint(half_addr(s, 3), wlo, kb * KB, t.w_row, full_bar(s), keep);
                     }
                 }
             }
@@ -472,7 +488,7 @@ __global__ void __launch_bounds__(kThreads, 1)
             bool ok = true;
             for (int64_t mt = blockIdx.x; mt < tiles_m && ok; mt += gridDim.x) {
                 for (int ti = 0; ti < ntiles && ok; ++ti, ++tcount) {
-                    const int num_kb = plan.t[tile_at(plan, ti, (int)(blockIdx.x % 64))].k / BK;
+                    const int num_kb = plan.t[tile_at(plan, ti, (int)(blockIdx.x % 64))].k / KB;
                     const int buf = (int)(tcount & 1);
                     const uint32_t use = (uint32_t)((tcount >> 1) & 1);
                     ok = mbar_wait(tempty_bar(buf), use ^ 1u, abort_flag);  // epilogue has drained this accumulator
@@ -487,10 +503,11 @@ __global__ void __launch_bounds__(kThreads, 1)
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                         // W_hi | W_lo are adjacent: one 256-wide MMA on a_hi gives a_hi*w_hi (main accumulator) and
                         // a_hi*w_lo (correction accumulator); a 128-wide MMA adds a_lo*w_hi to the correction
-                        const uint64_t da_hi = smem_desc64(half_addr(s, 0)), da_lo = smem_desc64(half_addr(s, 1));
-                        const uint64_t dw = smem_desc64(half_addr(s, 2));
+                        auto desc = [](uint32_t addr) { return KB == 64 ? smem_desc128(addr) : smem_desc64(addr); };
+                        const uint64_t da_hi = desc(half_addr(s, 0)), da_lo = desc(half_addr(s, 1));
+                        const uint64_t dw = desc(half_addr(s, 2));
 #pragma unroll
-                        for (int j = 0; j < BK / 16; ++j) {
+                        for (int j = 0; j < KB / 16; ++j) {
                             const uint64_t adv = (uint64_t)(j * 2);
                             const uint32_t first = (kb > 0 || j > 0) ? 1u : 0u;
                             umma_f16<2 * BN>(acc, da_hi + adv, dw + adv, first);
@@ -687,15 +704,16 @@ __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
 }
 
 // 2-D row-major half matrix [rows, cols], row stride ld elements; box = 32 columns x box_rows rows, 64-byte swizzle
-static int map_half(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows) {
+static int map_half(CUtensorMap* map, const void* ptr, int64_t rows, int64_t cols, int64_t ld, int box_rows, int box_cols = 32) {
     EncodeTiledFn fn = encode_fn();
     if (!fn) return FCB200_EINVAL;
     cuuint64_t gdim[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
     cuuint64_t gstride[1] = {(cuuint64_t)ld * 2};
-    cuuint32_t box[2] = {32u, (cuuint32_t)box_rows};
+    cuuint32_t box[2] = {(cuuint32_t)box_cols, (cuuint32_t)box_rows};
     cuuint32_t estr[2] = {1, 1};
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(ptr), gdim, gstride, box, estr,
-                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, box_cols == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                    CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     return r == CUDA_SUCCESS ? FCB200_OK : FCB200_EINVAL;
 }
@@ -759,7 +777,11 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
     Plan plan{};
     Params prm{};
     if (num_tiles <= 0 || num_tiles > kMaxTiles) return FCB200_ERANGE;
-    if (variant != 0 && variant != 1) return FCB200_EINVAL;
+    if (variant < 0 || variant > 2) return FCB200_EINVAL;
+    if (variant == 2)  // 64-deep stages need every K extent to be a multiple of 64; otherwise the 32-deep form runs
+        for (int i = 0; i < num_tiles; ++i)
+            if (tiles[9 * i + 1] % 64) variant = 0;
+    const int kb_cols = variant == 2 ? 64 : 32;  // k extent of a ring stage
     if (lda % 8 || lda < a_cols || ldy % 4 || ldy < y_cols) return FCB200_EINVAL;
     if (!aligned16(a_hi) || !aligned16(a_lo) || !aligned16(y)) return FCB200_EALIGN;
     if (o_hi || o_lo) {
@@ -777,7 +799,7 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
         t.a_col = d[0], t.k = d[1], t.w = d[2], t.w_row = d[3], t.out_col = d[4], t.mode = d[5], t.y_col = d[6], t.gate_col = d[7];
         t.flags = d[8];
         if (t.w < 0 || t.w > 2 || !w_hi[t.w] || !w_lo[t.w]) return FCB200_EINVAL;
-        if (t.k <= 0 || t.k % BK || t.k > w_cols[t.w] || t.a_col < 0 || t.a_col % 8 || t.a_col + t.k > a_cols) return FCB200_EINVAL;
+        if (t.k <= 0 || t.k % kb_cols || t.k > w_cols[t.w] || t.a_col < 0 || t.a_col % 8 || t.a_col + t.k > a_cols) return FCB200_EINVAL;
         if (t.w_row < 0 || t.w_row % BN || t.w_row + BN > w_rows[t.w]) return FCB200_EINVAL;
         if (t.mode < kPlain || t.mode > kGatedBwd || t.mode == kGateRaw || t.out_col < 0 || t.out_col % 8) return FCB200_EINVAL;
         const bool split = t.mode >= kSilu;
@@ -793,15 +815,15 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
     }
     if (m == 0) return FCB200_OK;
     CUtensorMap mah, mal, mw[6], my, moh, mol;
-    int rc = map_half(&mah, a_hi, m, a_cols, lda, BM);
-    if (!rc) rc = map_half(&mal, a_lo, m, a_cols, lda, BM);
+    int rc = map_half(&mah, a_hi, m, a_cols, lda, BM, kb_cols);
+    if (!rc) rc = map_half(&mal, a_lo, m, a_cols, lda, BM, kb_cols);
     int first = -1;
     for (int i = 0; i < 3 && !rc; ++i) {
         if (!used[i]) continue;
         if (first < 0) first = i;
         if (w_cols[i] % 8 || !aligned16(w_hi[i]) || !aligned16(w_lo[i]) || !(w_scale[i] > 0.f)) return FCB200_EINVAL;
-        rc = map_half(&mw[2 * i], w_hi[i], w_rows[i], w_cols[i], w_cols[i], BN);
-        if (!rc) rc = map_half(&mw[2 * i + 1], w_lo[i], w_rows[i], w_cols[i], w_cols[i], BN);
+        rc = map_half(&mw[2 * i], w_hi[i], w_rows[i], w_cols[i], w_cols[i], BN, kb_cols);
+        if (!rc) rc = map_half(&mw[2 * i + 1], w_lo[i], w_rows[i], w_cols[i], w_cols[i], BN, kb_cols);
         prm.w_scale[i] = w_scale[i];
         prm.bias[i] = bias ? bias[i] : nullptr;
         if (prm.bias[i] && !aligned16(prm.bias[i])) return FCB200_EALIGN;
@@ -851,6 +873,20 @@ extern "C" int fcb200_so2_conv_fused(const void* a_hi, const void* a_lo, int64_t
     }
     const int64_t tiles_m = (m + BM - 1) / BM;
     const int grid = (int)(tiles_m < sm_count() ? tiles_m : sm_count());
+    if (variant == 2) {
+        if (plain_only) {
+            static bool attr_done[64] = {};
+            if (const int arc = ensure_dynamic_smem(so2_conv_fused_kernel<2, 64>, smem_bytes<2, 64>(), attr_done)) return arc;
+            so2_conv_fused_kernel<2, 64><<<grid, kThreads, smem_bytes<2, 64>(), st>>>(mah, mal, mw[0], mw[1], mw[2], mw[3], mw[4],
+                                                                                     mw[5], my, moh, mol, plan, prm, tiles_m);
+        } else {
+            static bool attr_done[64] = {};
+            if (const int arc = ensure_dynamic_smem(so2_conv_fused_kernel<3, 64>, smem_bytes<3, 64>(), attr_done)) return arc;
+            so2_conv_fused_kernel<3, 64><<<grid, kThreads, smem_bytes<3, 64>(), st>>>(mah, mal, mw[0], mw[1], mw[2], mw[3], mw[4],
+                                                                                     mw[5], my, moh, mol, plan, prm, tiles_m);
+        }
+        return launch_status();
+    }
     if (plain_only) {
         static bool attr_done[64] = {};
         if (const int arc = ensure_dynamic_smem(so2_conv_fused_kernel<2>, smem_bytes<2>(), attr_done)) return arc;

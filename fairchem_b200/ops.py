@@ -593,7 +593,12 @@ def gemm_f16x2_presplit_(a_hi: Tensor, a_lo: Tensor, w_hi: Tensor, w_lo: Tensor,
 CONV_PLAIN, CONV_GATE_RAW, CONV_SILU, CONV_GATED, CONV_SILU_BWD, CONV_GATED_BWD = range(6)
 CONV_FIRST, CONV_LAST, CONV_KEEP = 1, 2, 4
 CONV_MAX_TILES = 40
-CONV_VARIANT = 0  # default launch form of so2_conv_fused_ (0: one CTA per 128-edge tile, 1: CTA pairs on 256-edge tiles)
+# Launch form of so2_conv_fused_: 0 one CTA per 128-edge tile with 32-deep ring stages, 1 CTA pairs on 256-edge tiles,
+# 2 one CTA per tile with 64-deep stages (128-byte swizzle), -1 the measured choice per launch: 64-deep stages when no
+# tile's K exceeds CONV_K64_MAX (the second convolution, its backward and the radial output layer gain 1-10 %), else
+# 32-deep ones (the first convolution's wide plans lose 1-4 % with 64-deep stages)
+CONV_VARIANT = -1
+CONV_K64_MAX = 512
 
 
 @_op("so2_conv_fused", ("y", "o_hi", "o_lo", "status"))
@@ -607,8 +612,7 @@ def so2_conv_fused_(a_hi: Tensor, a_lo: Tensor, w_hi: List[Tensor], w_lo: List[T
     list of 9 integers per 128-column output tile (a_col, k, w, w_row, out_col, mode, y_col, gate_col, flags); tiles from
     position ``rot_begin`` on may run in any order (every CTA starts at a different one).  ``y``
     [E, >=gates] float32 receives the float32 modes and the raw gate scalars and is read by the gated modes; ``o_hi/o_lo``
-    receive the split modes.  ``variant`` 0 runs one CTA per 128-edge tile, 1 CTA pairs on 256-edge tiles (default:
-    the module-level ``CONV_VARIANT``)."""
+    receive the split modes.  ``variant`` selects the launch form (see ``CONV_VARIANT``, the default)."""
     for t in (a_hi, a_lo):
         if not t.is_cuda or t.dtype != torch.float16 or t.dim() != 2 or t.stride(1) != 1 or t.shape != a_hi.shape \
                 or t.stride(0) != a_hi.stride(0):
@@ -637,12 +641,17 @@ def so2_conv_fused_(a_hi: Tensor, a_lo: Tensor, w_hi: List[Tensor], w_lo: List[T
     scales = (c_float * 3)(*(list(w_scale) + [1.0] * (3 - nw)))
     biases = (c_void_p * 3)(None if bias0 is None else bias0.data_ptr(), None, None)
     tl = (c_int32 * len(tiles))(*tiles)
+    if variant < 0:
+        variant = CONV_VARIANT
+    if variant < 0:
+        ks = [tiles[9 * i + 1] for i in range(nt)]
+        variant = 2 if max(ks) <= CONV_K64_MAX and all(k % 64 == 0 for k in ks) else 0
     flops = 2 * m * 128 * sum(tiles[9 * i + 1] for i in range(nt))
     nbytes = 4 * m * (a_hi.shape[1] + 128 * nt)
     _launch("so2_conv_fused" + label, "fcb200_so2_conv_fused",
             (_p(a_hi), _p(a_lo), a_hi.stride(0), a_hi.shape[1], whi, wlo, rows, cols, scales, biases, tl, nt, rot_begin,
              _p(y), y.stride(0), y.shape[1], _p(o_hi), _p(o_lo), 0 if o_hi is None else o_hi.stride(0),
-             0 if o_hi is None else o_hi.shape[1], _p(a_scale), _p(o_scale), m, CONV_VARIANT if variant < 0 else variant,
+             0 if o_hi is None else o_hi.shape[1], _p(a_scale), _p(o_scale), m, variant,
              _p(status), _stream()), nbytes=nbytes, flops=flops)
 
 

@@ -398,8 +398,9 @@ int fcb200_gemm_f16x2_presplit(const void* a_hi, const void* a_lo, int64_t lda, 
  *   y            [M, y_cols] float32, row stride ldy; o_hi/o_lo [M, o_cols] half planes, row stride ldo, written
  *                times *o_scale (device pointers to powers of two, NULL = 1)
  *   status       as in fcb200_gemm_f16x2_presplit
- *   variant      0: one CTA per 128-edge tile; 1: CTA pairs (tcgen05 cta_group::2) on 256-edge tiles, each CTA
- *                streaming half of the weight operand (same results)
+ *   variant      0: one CTA per 128-edge tile, operand ring of 32-deep k stages; 1: CTA pairs (tcgen05
+ *                cta_group::2) on 256-edge tiles, each CTA streaming half of the weight operand; 2: as 0 with
+ *                64-deep k stages (128-byte swizzle; runs as 0 when some k is not a multiple of 64).  Same results.
  * At most 40 tiles; every k a multiple of 32, w_row a multiple of 128.
  */
 /* Number of CTA pairs variant 1 of fcb200_so2_conv_fused runs at once on the current device (0 if it cannot be told). */

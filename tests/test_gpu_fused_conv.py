@@ -27,9 +27,10 @@ def _unplane(p, scale=1.0):
     return (p[0].float() + p[1].float() / 2048.0) / scale
 
 
-@pytest.fixture(params=[0, 1], ids=["single_cta", "cta_pairs"])
+@pytest.fixture(params=[0, 1, 2, -1], ids=["single_cta", "cta_pairs", "single_cta_k64", "per_launch_choice"])
 def variant(request, ops):
-    """Both launch forms of the fused kernel: one CTA per 128 edges, and CTA pairs (cta_group::2) per 256 edges."""
+    """The launch forms of the fused kernel: one CTA per 128 edges with 32- or 64-deep ring stages, and CTA pairs
+    (cta_group::2) per 256 edges."""
     saved = ops.CONV_VARIANT
     ops.CONV_VARIANT = request.param
     yield request.param
