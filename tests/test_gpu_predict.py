@@ -75,3 +75,42 @@ def test_predict_unit_matches_the_module_call():
     unit.predict(dev)
     unit.predict(dev)
     assert bb.neighbor_list.refreshes >= 1
+
+
+def test_calculator_gives_the_module_results_for_unwrapped_atoms():
+    """B200Calculator (the reference's FAIRChemCalculator surface, ase_calculator.py:201-257) on atoms that have been
+    shifted by whole cell vectors: same energy, forces and Voigt stress as the direct call on the wrapped input."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import numpy as np
+
+    from fairchem_b200 import predict
+    from fairchem_b200.backbone import build_model, energy_forces
+    from fairchem_b200.calculator import B200Calculator, full_3x3_to_voigt_6
+
+    class Atoms:
+        def __init__(self, data, shift):
+            self.cell = data["cell"][0].double().numpy()
+            self.positions = data["pos"].double().numpy() + shift @ self.cell
+            self.numbers = data["atomic_numbers"].numpy()
+            self.pbc = data["pbc"][0].numpy()
+            self.info = {}
+
+        def __len__(self):
+            return len(self.numbers)
+
+    sd = weights.random_init_state_dict(weights.UMA_S, 0)
+    bb, head = build_model(weights.UMA_S, sd, edge_chunk_size=4096, regress_stress=True)
+    host = synthetic.fcc_cu((3, 3, 3), seed=2)
+    ref = energy_forces(bb, head, host.to("cuda"))
+    rng = np.random.default_rng(0)
+    shift = rng.integers(-2, 3, size=(host["pos"].shape[0], 3)).astype(np.float64)
+    calc = B200Calculator(predict.B200PredictUnit(bb, head), task_name="omat")
+    assert calc.implemented_properties == ["energy", "forces", "stress", "free_energy"]
+    atoms = Atoms(host, shift)
+    e = calc.get_potential_energy(atoms)
+    assert atoms.info == {"charge": 0, "spin": 0}
+    assert abs(e - float(ref["energy"][0])) < 2e-6 * abs(float(ref["energy"][0]))
+    assert float(np.abs(calc.results["forces"] - ref["forces"].cpu().numpy()).max()) < 5e-6
+    want = full_3x3_to_voigt_6(ref["stress"].cpu().numpy().reshape(3, 3))
+    np.testing.assert_allclose(calc.results["stress"], want, atol=5e-7 + 1e-4 * float(np.abs(want).max()))
