@@ -114,3 +114,39 @@ def test_calculator_gives_the_module_results_for_unwrapped_atoms():
     assert float(np.abs(calc.results["forces"] - ref["forces"].cpu().numpy()).max()) < 5e-6
     want = full_3x3_to_voigt_6(ref["stress"].cpu().numpy().reshape(3, 3))
     np.testing.assert_allclose(calc.results["stress"], want, atol=5e-7 + 1e-4 * float(np.abs(want).max()))
+
+
+def test_lammps_callback_fills_forces_energy_and_virial():
+    """The ``fix external`` callback (src/fairchem/lammps/lammps_fc.py:165-209) with the real predict unit behind a
+    stand-in for the ``lammps`` object: forces, energy and virial equal the direct evaluation."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    import types
+
+    import numpy as np
+
+    from fairchem_b200 import lammps_callback as L
+    from fairchem_b200 import predict
+    from fairchem_b200.backbone import build_model, energy_forces
+
+    sd = weights.random_init_state_dict(weights.UMA_S, 0)
+    bb, head = build_model(weights.UMA_S, sd, edge_chunk_size=4096, regress_stress=True)
+    host = synthetic.water_box(300, seed=3)
+    ref = energy_forces(bb, head, host.to("cuda"))
+    z = host["atomic_numbers"].numpy()
+    side = float(host["cell"][0, 0, 0])
+    got = {}
+    lmp = types.SimpleNamespace(
+        numpy=types.SimpleNamespace(extract_atom=lambda name: {"type": np.where(z == 8, 1, 2), "mass": np.array([0.0, 15.999, 1.008])}[name]),
+        extract_box=lambda: ([0.0] * 3, [side] * 3, 0.0, 0.0, 0.0, [1, 1, 1], 1),
+        fix_external_set_energy_global=lambda fid, e: got.__setitem__("energy", e),
+        fix_external_set_virial_global=lambda fid, v: got.__setitem__("virial", v),
+        _predictor=predict.B200PredictUnit(bb, head), _task_name="omat")
+    x = host["pos"].double().numpy() + side * np.array([1.0, -1.0, 2.0])  # outside the box: wrapped by the callback
+    f = np.zeros_like(x)
+    L.B200FixExternalCallback()(lmp, 0, len(z), None, x, f)
+    assert abs(got["energy"] - float(ref["energy"][0])) < 2e-6 * abs(float(ref["energy"][0]))
+    assert float(np.abs(f - ref["forces"].cpu().numpy()).max()) < 5e-6
+    s = ref["stress"].cpu().double().numpy().reshape(9) * side ** 3
+    want = -np.array([s[0], s[4], s[8], s[1], s[2], s[5]])
+    np.testing.assert_allclose(got["virial"], want, atol=1e-4 * float(np.abs(want).max()) + 1e-6)
