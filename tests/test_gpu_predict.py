@@ -150,3 +150,43 @@ def test_lammps_callback_fills_forces_energy_and_virial():
     s = ref["stress"].cpu().double().numpy().reshape(9) * side ** 3
     want = -np.array([s[0], s[4], s[8], s[1], s[2], s[5]])
     np.testing.assert_allclose(got["virial"], want, atol=1e-4 * float(np.abs(want).max()) + 1e-6)
+
+
+def test_torchsim_adapter_on_a_device_resident_two_system_state():
+    """B200TorchSimModel (the reference's FairChemModel.forward, torchsim_interface.py:276-316) on a batched state
+    that lives on the GPU and whose atoms sit outside their cells: energies, forces and stresses of the direct call."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from fairchem_b200 import predict
+    from fairchem_b200.backbone import build_model, energy_forces
+    from fairchem_b200.torchsim_model import B200TorchSimModel
+
+    sd = weights.random_init_state_dict(weights.UMA_S, 0)
+    bb, head = build_model(weights.UMA_S, sd, edge_chunk_size=4096, regress_stress=True)
+    host = synthetic.merge([synthetic.fcc_cu((3, 3, 3), seed=1), synthetic.bcc_alloy((4, 4, 4), seed=2)])
+    ref = energy_forces(bb, head, host.to("cuda"))
+
+    class State:
+        def __init__(self, d):
+            cells = d["cell"].cuda()
+            idx = d["batch"].cuda()
+            shift = torch.tensor([[1.0, 0.0, -2.0]], device="cuda").expand(len(idx), 3)
+            self.positions = d["pos"].cuda() + torch.einsum("ni,nij->nj", shift, cells[idx])
+            self.atomic_numbers, self.system_idx = d["atomic_numbers"].cuda().int(), idx
+            self.cell = cells.transpose(-2, -1).contiguous()
+            self.pbc = torch.tensor([True, True, True], device="cuda")
+            self.n_systems = len(d["natoms"])
+            self.row_vector_cell = cells
+            self.device = self.positions.device
+
+        def has_extras(self, name):
+            return False
+
+    model = B200TorchSimModel(predict.B200PredictUnit(bb, head), task_name="omat", compute_stress=True)
+    out = model(State(host))
+    assert out["energy"].is_cuda and out["forces"].is_cuda and out["stress"].shape == (2, 3, 3)
+    e = ref["energy"].float()
+    assert float((out["energy"] - e).abs().max()) <= 1e-5 * float(e.abs().max())
+    assert float((out["forces"] - ref["forces"]).abs().max()) < 5e-6
+    s = ref["stress"].float().view(2, 3, 3)
+    assert float((out["stress"] - s).abs().max()) <= 1e-4 * float(s.abs().max()) + 5e-7
