@@ -220,7 +220,7 @@ class SkinNeighborList:
         if skin < 0:
             raise ValueError("skin must be non-negative")
         self.cutoff, self.max_neighbors, self.skin = float(cutoff), int(max_neighbors), float(skin)
-        self._cand = self._pos0 = self._cell0 = None
+        self._cand = self._pos0 = self._cell0 = self._natoms0 = None
         self._key = None
         self.searches = self.refreshes = 0
 
@@ -232,6 +232,8 @@ class SkinNeighborList:
                None if getattr(data, "node_partition", None) is None else int(data.node_partition.shape[0]))
         if key != self._key or not torch.equal(data.cell.to(self._cell0.dtype), self._cell0):
             return False
+        if data.natoms.tolist() != self._natoms0:  # same totals, atoms split differently over the systems
+            return False
         moved = (pos.detach().float() - self._pos0).square().sum(dim=1).max()
         return float(moved) <= (0.5 * self.skin) ** 2
 
@@ -242,6 +244,7 @@ class SkinNeighborList:
             self._cand = _search(data, self.cutoff + self.skin, pbc)
             self._pos0 = data.pos.detach().float().clone()
             self._cell0 = data.cell.detach().clone()
+            self._natoms0 = data.natoms.tolist()
             self._key = (int(data.pos.shape[0]), tuple(int(v) for v in data.natoms.shape), data.pos.device,
                          None if getattr(data, "node_partition", None) is None else int(data.node_partition.shape[0]))
             self.searches += 1

@@ -190,3 +190,22 @@ def test_torchsim_adapter_on_a_device_resident_two_system_state():
     assert float((out["forces"] - ref["forces"]).abs().max()) < 5e-6
     s = ref["stress"].float().view(2, 3, 3)
     assert float((out["stress"] - s).abs().max()) <= 1e-4 * float(s.abs().max()) + 5e-7
+
+
+def test_skin_list_searches_again_when_the_systems_are_split_differently():
+    """Same atom count, same number of systems, same cells, but atoms assigned to the systems differently: the kept
+    candidate list belongs to the old split and must not be reused."""
+    if not torch.cuda.is_available():
+        pytest.skip("needs a CUDA device")
+    from fairchem_b200.graph import SkinNeighborList, radius_graph_pbc_b200
+
+    a = synthetic.merge([synthetic.molecule_batch(1, 30, 30, seed=1), synthetic.molecule_batch(1, 50, 50, seed=2)]).to("cuda")
+    b = a.clone()
+    b["natoms"] = torch.tensor([50, 30], device="cuda")
+    b["batch"] = torch.repeat_interleave(torch.arange(2, device="cuda"), b["natoms"])
+    nl = SkinNeighborList(6.0, 30, skin=1.0)
+    nl.update(a)
+    ei, _, nb = nl.update(b)
+    assert nl.searches == 2 and nl.refreshes == 0
+    ei_ref, _, nb_ref = radius_graph_pbc_b200(b, 6.0, 30)
+    assert torch.equal(nb, nb_ref) and ei.shape == ei_ref.shape
