@@ -220,11 +220,16 @@ class SkinNeighborList:
         if skin < 0:
             raise ValueError("skin must be non-negative")
         self.cutoff, self.max_neighbors, self.skin = float(cutoff), int(max_neighbors), float(skin)
-        self._cand = self._pos0 = self._cell0 = self._natoms0 = None
+        self._cand = self._pos0 = self._cell0 = self._natoms0 = self._pbc0 = None
         self._key = None
         self.searches = self.refreshes = 0
 
-    def _reusable(self, data) -> bool:
+    @staticmethod
+    def _pbc_of(data, pbc):
+        flags = data.pbc if pbc is None else pbc
+        return None if flags is None else torch.as_tensor(flags).reshape(-1).tolist()
+
+    def _reusable(self, data, pbc=None) -> bool:
         if self._cand is None or self.skin == 0.0:
             return False
         pos = data.pos
@@ -234,17 +239,20 @@ class SkinNeighborList:
             return False
         if data.natoms.tolist() != self._natoms0:  # same totals, atoms split differently over the systems
             return False
+        if self._pbc_of(data, pbc) != self._pbc0:
+            return False
         moved = (pos.detach().float() - self._pos0).square().sum(dim=1).max()
         return float(moved) <= (0.5 * self.skin) ** 2
 
     @torch.no_grad()
     def update(self, data, pbc=None):
         """(edge_index, cell_offsets, neighbors) at the current positions of ``data``."""
-        if not self._reusable(data):
+        if not self._reusable(data, pbc):
             self._cand = _search(data, self.cutoff + self.skin, pbc)
             self._pos0 = data.pos.detach().float().clone()
             self._cell0 = data.cell.detach().clone()
             self._natoms0 = data.natoms.tolist()
+            self._pbc0 = self._pbc_of(data, pbc)
             self._key = (int(data.pos.shape[0]), tuple(int(v) for v in data.natoms.shape), data.pos.device,
                          None if getattr(data, "node_partition", None) is None else int(data.node_partition.shape[0]))
             self.searches += 1
