@@ -153,6 +153,10 @@ def run_b200(args):
     B.set_gemm_precision(args.precision)
     if args.conv_variant is not None:
         ops.CONV_VARIANT = args.conv_variant
+    if args.edge_source_sums:
+        from fairchem_b200 import backbone as _bb
+
+        _bb._GemmState.node_sums = False
     if args.generic_kernels:
         from fairchem_b200 import ops as _ops
 
@@ -471,6 +475,8 @@ def main():
     ap.add_argument("--chunk", type=int, default=131072)
     ap.add_argument("--seed", type=int, default=0)
     ap.add_argument("--skip-cpu", action="store_true")
+    ap.add_argument("--edge-source-sums", action="store_true",
+                    help="gather backward with the source half per edge plus a segmented sum instead of per-node sums (A/B measurement)")
     ap.add_argument("--generic-kernels", action="store_true",
                     help="route the lmax=2 model through the any-lmax edge-block kernels (A/B measurement)")
     ap.add_argument("--conv-variant", type=int, default=None, choices=[-1, 0, 1, 2],

@@ -24,6 +24,8 @@ SIGNATURES = {
     "fcb200_gather_rotate_bwd": [P, P, P, P, P, P, P, P, P, P, I64, I64, I32, P],
     "fcb200_gather_rotate_bwd_csr": [P, P, P, P, P, I64, I64, P, P, P, P, P, P, I64, I64, I32, P],
     "fcb200_gather_rotate_bwd_csr_h": [P, P, P, P, P, I64, I64, P, P, P, P, P, P, P, P, I64, I64, I32, P],
+    "fcb200_gather_rotate_bwd_nodes": [P, P, P, P, P, I64, P, I64, I64, P, P, P, P, P, I64, I64, I32, P],
+    "fcb200_gather_rotate_bwd_nodes_h": [P, P, P, P, P, I64, P, I64, I64, P, P, P, P, P, P, P, I64, I64, I32, P],
     "fcb200_rotate_back_bwd": [P, P, P, P, P, P, I64, I64, I32, P],
     "fcb200_edge_degree_bwd": [P, P, P, P, P, P, F32, I64, I64, I32, P],
     "fcb200_segment_sum": [P, P, P, P, P, I32, F32, I64, I64, P],

@@ -338,6 +338,7 @@ class _GemmState:
     split16 = {}           # same key -> (weight ref, half high part, half low part, scale)
     a_scale = None         # precision 2: one-element device tensor, the power of two A operands are scaled by (None = 1)
     fused_conv = True      # precision 2: one launch per SO(2) convolution with the gate in the epilogue
+    node_sums = True       # gather backward: both halves summed per node in the kernels (else source half per edge + segmented sum)
 
 
 def set_gemm_precision(p: int) -> None:
@@ -1012,10 +1013,23 @@ class _EdgeBlockFn(torch.autograd.Function):
                 del ga, y
                 gm = _conv_backward(ew.so2_conv_1, gy)
             del gy
-            g_src = torch.empty(ec, nl, c, dtype=x.dtype, device=x.device)
             csr = ew.lmax == 2 and c == 128 and not ops.generic_kernels()
             # the radial gradient only feeds the radial MLP's backward contraction: half planes in the half-split mode
             grad_rad = _new_operand(ec, rad_d.shape[1], x.device) if (csr and _presplit()) else torch.empty_like(rad_d)
+            if csr and _GemmState.node_sums:
+                # both halves of the node gradient are summed per node inside the kernels (sources through the chunk's
+                # by-source tables): no per-edge node gradient is written
+                if isinstance(grad_rad, tuple):
+                    ops.gather_rotate_bwd_nodes_h_.raw(gm, x, ch.src_nodes, ch.src_ptr, ch.src_perm, ch.row_ptr, ch.n0, wig[sl],
+                                                       rad_d, gx, gwig[sl], grad_rad[0], grad_rad[1], scale)
+                else:
+                    ops.gather_rotate_bwd_nodes_.raw(gm, x, ch.src_nodes, ch.src_ptr, ch.src_perm, ch.row_ptr, ch.n0, wig[sl],
+                                                     rad_d, gx, gwig[sl], grad_rad)
+                del gm
+                _radial_out_backward(rfn, grad_rad, g_hidden[sl])
+                del rad_d, grad_rad
+                continue
+            g_src = torch.empty(ec, nl, c, dtype=x.dtype, device=x.device)
             if csr and isinstance(grad_rad, tuple):
                 ops.gather_rotate_bwd_csr_h_.raw(gm, x, g.src[sl], g.tgt[sl], ch.row_ptr, ch.n0, wig[sl], rad_d, g_src,
                                                  gx[ch.n0:ch.n1], gwig[sl], grad_rad[0], grad_rad[1], scale)

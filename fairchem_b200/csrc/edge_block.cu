@@ -312,14 +312,17 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp, 2)
     }
 }
 
-// target half, one warp per target node and degree (128 channels): the node gradient of the degree's rows is summed
-// over the target's edges in registers and added to the node rows once; the Wigner gradient is added to what the
-// source kernel stored
-template <int l, bool HAS_RAD, class RadOut>
-__device__ __forceinline__ void bwd_tgt_degree(const float* __restrict__ grad_out, const float* __restrict__ x_base,
-                                               const float* __restrict__ wig, const float* __restrict__ radial,
-                                               float* __restrict__ g_base, float* __restrict__ grad_wig,
-                                               const RadOut& grad_radial, int eb, int ee, int lane) {
+// One half (HALF 0 = source columns, 1 = target columns), one warp per node and degree (128 channels): the node
+// gradient of the degree's rows is summed over the node's edges in registers and added to the node rows once.  The
+// edges of a target are consecutive (PERM = false, edges [eb, ee)); the edges of a source come through the by-source
+// permutation of the chunk's edges (PERM = true, edges perm[eb .. ee)).  ACC_W: add the Wigner gradient to what the
+// other half stored, else store it.
+template <int l, bool HAS_RAD, class RadOut, int HALF, bool ACC_W, bool PERM>
+__device__ __forceinline__ void bwd_node_degree(const float* __restrict__ grad_out, const float* __restrict__ x_base,
+                                                const float* __restrict__ wig, const float* __restrict__ radial,
+                                                float* __restrict__ g_base, float* __restrict__ grad_wig,
+                                                const RadOut& grad_radial, const int32_t* __restrict__ perm, int eb, int ee,
+                                                int lane) {
     constexpr int n = 2 * l + 1, L0 = l * l, channels = 128;
     const int c0 = lane * 4;
     float4 xv[n], gt[n];
@@ -328,15 +331,16 @@ __device__ __forceinline__ void bwd_tgt_degree(const float* __restrict__ grad_ou
         xv[b] = ld4(x_base + (L0 + b) * channels + c0);
         gt[b] = f4zero();
     }
-    for (int64_t e = eb; e < ee; ++e) {
+    for (int k = eb; k < ee; ++k) {
+        const int64_t e = PERM ? (int64_t)__ldg(perm + k) : (int64_t)k;
         float w[n * n], dw[n * n];
 #pragma unroll
         for (int i = 0; i < n * n; ++i) {
             w[i] = __ldg(wig + e * FCB200_WIG + woff(l) + i);
             dw[i] = 0.f;
         }
-        bwd_degree_rows<l, HAS_RAD, RadOut>(grad_out, radial, grad_radial, e, 1, channels, c0, w, xv, gt, dw);
-        reduce_block<n * n, true>(dw, lane, grad_wig + e * FCB200_WIG + woff(l));
+        bwd_degree_rows<l, HAS_RAD, RadOut>(grad_out, radial, grad_radial, e, HALF, channels, c0, w, xv, gt, dw);
+        reduce_block<n * n, ACC_W>(dw, lane, grad_wig + e * FCB200_WIG + woff(l));
     }
 #pragma unroll
     for (int b = 0; b < n; ++b) st4(g_base + (L0 + b) * channels + c0, add4(ld4(g_base + (L0 + b) * channels + c0), gt[b]));
@@ -357,9 +361,35 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp, 2)
         if (eb == ee) continue;
         const float* x_base = x + (tgt_base + n) * 9LL * 128;
         float* g_base = gx_tgt + n * 9LL * 128;
-        bwd_tgt_degree<0, HAS_RAD, RadOut>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, eb, ee, lane);
-        bwd_tgt_degree<1, HAS_RAD, RadOut>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, eb, ee, lane);
-        bwd_tgt_degree<2, HAS_RAD, RadOut>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, eb, ee, lane);
+        bwd_node_degree<0, HAS_RAD, RadOut, 1, true, false>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, nullptr, eb, ee, lane);
+        bwd_node_degree<1, HAS_RAD, RadOut, 1, true, false>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, nullptr, eb, ee, lane);
+        bwd_node_degree<2, HAS_RAD, RadOut, 1, true, false>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, nullptr, eb, ee, lane);
+    }
+}
+
+// source half summed per source node: one warp per distinct source of the chunk, its edges through the by-source
+// permutation.  Stores the Wigner gradient (runs before the target kernel, which adds to it) and adds the node
+// gradient to gx[src_nodes[u]]; distinct sources are distinct rows, so no two warps touch the same row.
+template <bool HAS_RAD, class RadOut>
+__global__ void __launch_bounds__(kWarpsPerBlock* kWarp, 2)
+    gather_rotate_bwd_srcnode_kernel(const float* __restrict__ grad_out, const float* __restrict__ x,
+                                     const int32_t* __restrict__ src_nodes, const int32_t* __restrict__ src_ptr,
+                                     const int32_t* __restrict__ src_perm, const float* __restrict__ wig,
+                                     const float* __restrict__ radial, float* __restrict__ gx, float* __restrict__ grad_wig,
+                                     RadOut grad_radial, const float* __restrict__ scale_ptr, int64_t num_sources) {
+    grad_radial.load_scale(scale_ptr);
+    const int lane = threadIdx.x & 31;
+    const int64_t warp0 = (int64_t)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
+    const int64_t nwarps = (int64_t)gridDim.x * kWarpsPerBlock;
+    for (int64_t u = warp0; u < num_sources; u += nwarps) {
+        const int eb = src_ptr[u], ee = src_ptr[u + 1];
+        if (eb == ee) continue;
+        const int64_t node = src_nodes[u];
+        const float* x_base = x + node * 9LL * 128;
+        float* g_base = gx + node * 9LL * 128;
+        bwd_node_degree<0, HAS_RAD, RadOut, 0, false, true>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, src_perm, eb, ee, lane);
+        bwd_node_degree<1, HAS_RAD, RadOut, 0, false, true>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, src_perm, eb, ee, lane);
+        bwd_node_degree<2, HAS_RAD, RadOut, 0, false, true>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, src_perm, eb, ee, lane);
     }
 }
 
@@ -735,6 +765,59 @@ int fcb200_gather_rotate_bwd_csr_h(const float* grad_out, const float* x, const 
                                                                             num_edges, channels);
     gather_rotate_bwd_tgt_kernel<true, OutSplit><<<tgrid, kWarpsPerBlock * kWarp, 0, st>>>(grad_out, x, row_ptr, tgt_base, wig, radial,
                                                                                          gx_tgt, grad_wig, out, scale, num_targets);
+    return launch_status();
+}
+
+int fcb200_gather_rotate_bwd_nodes(const float* grad_out, const float* x, const int32_t* src_nodes, const int32_t* src_ptr,
+                                   const int32_t* src_perm, int64_t num_sources, const int32_t* row_ptr, int64_t tgt_base,
+                                   int64_t num_targets, const float* wig, const float* radial, float* gx, float* grad_wig,
+                                   float* grad_radial, int64_t num_edges, int64_t num_nodes, int32_t channels, void* stream) {
+    int rc = check_common(grad_out, x, num_edges, channels);
+    if (rc) return rc;
+    if (channels != 128) return FCB200_EINVAL;
+    if (!src_nodes || !src_ptr || !src_perm || !row_ptr || !wig || !gx || !grad_wig || num_nodes < 0 || num_targets < 0 ||
+        num_sources < 0 || tgt_base < 0 || tgt_base + num_targets > num_nodes)
+        return FCB200_EINVAL;
+    if ((radial == nullptr) != (grad_radial == nullptr)) return FCB200_EINVAL;
+    if (!aligned16(gx) || (radial && (!aligned16(radial) || !aligned16(grad_radial)))) return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    cudaStream_t st = FCB_STREAM;
+    const int sgrid = warp_grid(num_sources, kWarpsPerBlock), tgrid = warp_grid(num_targets, kWarpsPerBlock);
+    float* gx_tgt = gx + tgt_base * 9LL * 128;
+    if (radial) {
+        gather_rotate_bwd_srcnode_kernel<true, OutF32><<<sgrid, kWarpsPerBlock * kWarp, 0, st>>>(
+            grad_out, x, src_nodes, src_ptr, src_perm, wig, radial, gx, grad_wig, OutF32{grad_radial}, nullptr, num_sources);
+        gather_rotate_bwd_tgt_kernel<true, OutF32><<<tgrid, kWarpsPerBlock * kWarp, 0, st>>>(
+            grad_out, x, row_ptr, tgt_base, wig, radial, gx_tgt, grad_wig, OutF32{grad_radial}, nullptr, num_targets);
+    } else {
+        gather_rotate_bwd_srcnode_kernel<false, OutF32><<<sgrid, kWarpsPerBlock * kWarp, 0, st>>>(
+            grad_out, x, src_nodes, src_ptr, src_perm, wig, nullptr, gx, grad_wig, OutF32{nullptr}, nullptr, num_sources);
+        gather_rotate_bwd_tgt_kernel<false, OutF32><<<tgrid, kWarpsPerBlock * kWarp, 0, st>>>(
+            grad_out, x, row_ptr, tgt_base, wig, nullptr, gx_tgt, grad_wig, OutF32{nullptr}, nullptr, num_targets);
+    }
+    return launch_status();
+}
+
+int fcb200_gather_rotate_bwd_nodes_h(const float* grad_out, const float* x, const int32_t* src_nodes, const int32_t* src_ptr,
+                                     const int32_t* src_perm, int64_t num_sources, const int32_t* row_ptr, int64_t tgt_base,
+                                     int64_t num_targets, const float* wig, const float* radial, float* gx, float* grad_wig,
+                                     void* grad_radial_hi, void* grad_radial_lo, const float* scale, int64_t num_edges,
+                                     int64_t num_nodes, int32_t channels, void* stream) {
+    int rc = check_common(grad_out, x, num_edges, channels);
+    if (rc) return rc;
+    if (channels != 128) return FCB200_EINVAL;
+    if (!src_nodes || !src_ptr || !src_perm || !row_ptr || !wig || !radial || !gx || !grad_wig || !grad_radial_hi ||
+        !grad_radial_lo || num_nodes < 0 || num_targets < 0 || num_sources < 0 || tgt_base < 0 || tgt_base + num_targets > num_nodes)
+        return FCB200_EINVAL;
+    if (!aligned16(gx) || !aligned16(radial) || !aligned8(grad_radial_hi) || !aligned8(grad_radial_lo)) return FCB200_EALIGN;
+    if (num_edges == 0) return FCB200_OK;
+    cudaStream_t st = FCB_STREAM;
+    const int sgrid = warp_grid(num_sources, kWarpsPerBlock), tgrid = warp_grid(num_targets, kWarpsPerBlock);
+    const OutSplit out{static_cast<__half*>(grad_radial_hi), static_cast<__half*>(grad_radial_lo), 1.0f};
+    gather_rotate_bwd_srcnode_kernel<true, OutSplit><<<sgrid, kWarpsPerBlock * kWarp, 0, st>>>(
+        grad_out, x, src_nodes, src_ptr, src_perm, wig, radial, gx, grad_wig, out, scale, num_sources);
+    gather_rotate_bwd_tgt_kernel<true, OutSplit><<<tgrid, kWarpsPerBlock * kWarp, 0, st>>>(
+        grad_out, x, row_ptr, tgt_base, wig, radial, gx + tgt_base * 9LL * 128, grad_wig, out, scale, num_targets);
     return launch_status();
 }
 

@@ -247,6 +247,53 @@ def gather_rotate_bwd_csr_h_(grad_out: Tensor, x: Tensor, src: Tensor, tgt: Tens
             flops=e * 6 * s.nw * 2 * c, launches=2)
 
 
+def _nodes_bytes(s, e: int, c: int, nsrc: int, nt: int) -> int:
+    return e * (4 * (2 * s.nm * c + 3 * s.nw + 4 * s.nrad * c) + 4) + (nsrc + nt) * 4 * 3 * s.nl * c
+
+
+@_op("gather_rotate_bwd_nodes", ("gx", "grad_wig", "grad_radial"))
+def gather_rotate_bwd_nodes_(grad_out: Tensor, x: Tensor, src_nodes: Tensor, src_ptr: Tensor, src_perm: Tensor, row_ptr: Tensor,
+                             tgt_base: int, wig: Tensor, radial: Optional[Tensor], gx: Tensor, grad_wig: Tensor,
+                             grad_radial: Optional[Tensor]) -> None:
+    """gather_rotate_bwd_csr_ with the source half summed per node too: ``src_nodes`` are the run's distinct sources,
+    ``src_perm[src_ptr[u] : src_ptr[u + 1]]`` the (run-relative) edges of source u; both halves are added to ``gx``
+    [num_nodes, 9, C] and no per-edge node gradient is written."""
+    _chk(grad_out, x, src_nodes, src_ptr, src_perm, row_ptr, wig, radial, gx, grad_wig, grad_radial)
+    _f32(grad_out, x, wig, radial, gx, grad_wig, grad_radial)
+    e, c, nt, ns = src_perm.shape[0], x.shape[2], row_ptr.shape[0] - 1, src_nodes.shape[0]
+    s = _shape(_BY_NL, x.shape[1], "rows per node")
+    if _lx(s) or c != 128 or gx.shape != x.shape or src_ptr.shape[0] != ns + 1 or grad_out.shape[0] != e:
+        raise _lib.FairchemB200Error("gather_rotate_bwd_nodes: lmax 2, 128 channels, gx shaped like x, one src_ptr entry per source + 1")
+    for t in (src_nodes, src_ptr, src_perm, row_ptr):
+        if t.dtype != torch.int32:
+            raise _lib.FairchemB200Error("gather_rotate_bwd_nodes: int32 index arrays")
+    _launch("gather_rotate_bwd", "fcb200_gather_rotate_bwd_nodes",
+            (_p(grad_out), _p(x), _p(src_nodes), _p(src_ptr), _p(src_perm), ns, _p(row_ptr), tgt_base, nt, _p(wig), _p(radial),
+             _p(gx), _p(grad_wig), _p(grad_radial), e, x.shape[0], c, _stream()), nbytes=_nodes_bytes(s, e, c, ns, nt),
+            flops=e * 6 * s.nw * 2 * c, launches=2)
+
+
+@_op("gather_rotate_bwd_nodes_h", ("gx", "grad_wig", "grad_radial_hi", "grad_radial_lo"))
+def gather_rotate_bwd_nodes_h_(grad_out: Tensor, x: Tensor, src_nodes: Tensor, src_ptr: Tensor, src_perm: Tensor, row_ptr: Tensor,
+                               tgt_base: int, wig: Tensor, radial: Tensor, gx: Tensor, grad_wig: Tensor, grad_radial_hi: Tensor,
+                               grad_radial_lo: Tensor, scale: Optional[Tensor]) -> None:
+    """gather_rotate_bwd_nodes_ with the radial gradient written as the half-precision (hi, lo) planes of (value * scale)."""
+    _chk(grad_out, x, src_nodes, src_ptr, src_perm, row_ptr, wig, radial, gx, grad_wig, grad_radial_hi, grad_radial_lo, scale)
+    _f32(grad_out, x, wig, radial, gx, grad_wig, scale)
+    _h16(grad_radial_hi, grad_radial_lo)
+    e, c, nt, ns = src_perm.shape[0], x.shape[2], row_ptr.shape[0] - 1, src_nodes.shape[0]
+    s = _shape(_BY_NL, x.shape[1], "rows per node")
+    if _lx(s) or c != 128 or gx.shape != x.shape or src_ptr.shape[0] != ns + 1 or grad_out.shape[0] != e:
+        raise _lib.FairchemB200Error("gather_rotate_bwd_nodes_h: lmax 2, 128 channels, gx shaped like x, one src_ptr entry per source + 1")
+    for t in (src_nodes, src_ptr, src_perm, row_ptr):
+        if t.dtype != torch.int32:
+            raise _lib.FairchemB200Error("gather_rotate_bwd_nodes_h: int32 index arrays")
+    _launch("gather_rotate_bwd", "fcb200_gather_rotate_bwd_nodes_h",
+            (_p(grad_out), _p(x), _p(src_nodes), _p(src_ptr), _p(src_perm), ns, _p(row_ptr), tgt_base, nt, _p(wig), _p(radial),
+             _p(gx), _p(grad_wig), _p(grad_radial_hi), _p(grad_radial_lo), _p(scale), e, x.shape[0], c, _stream()),
+            nbytes=_nodes_bytes(s, e, c, ns, nt), flops=e * 6 * s.nw * 2 * c, launches=2)
+
+
 @_op("rotate_back_reduce_fwd", ("out",))
 def rotate_back_reduce_fwd_(msg: Tensor, winv: Tensor, row_ptr: Tensor, out: Tensor) -> None:
     _chk(msg, winv, row_ptr, out)

@@ -125,6 +125,27 @@ int fcb200_gather_rotate_bwd_csr_h(const float* grad_out, const float* x, const 
                                    int32_t channels, void* stream);
 
 /*
+ * fcb200_gather_rotate_bwd_csr with the source half summed per node as well: one warp per distinct source of the run
+ * walks that source's edges through a by-source permutation of the run's edges, sums the node gradient in registers and
+ * ADDS it to gx[src_nodes[u]] once, so no per-edge node gradient is written at all (the reference's two index_add_
+ * scatters, src/fairchem/core/models/uma/triton/fused_wigner.py:228-236).  lmax = 2, channels = 128.
+ *   src_nodes [num_sources] int32   distinct source nodes of the run
+ *   src_ptr   [num_sources + 1] int32, src_perm [E] int32: edges of source u are src_perm[src_ptr[u] .. src_ptr[u+1]),
+ *             relative to the first edge of the run; every edge of the run appears exactly once
+ *   gx        [num_nodes, 9, C]  in/out node-gradient array; targets are the rows from tgt_base on
+ */
+int fcb200_gather_rotate_bwd_nodes(const float* grad_out, const float* x, const int32_t* src_nodes, const int32_t* src_ptr,
+                                   const int32_t* src_perm, int64_t num_sources, const int32_t* row_ptr, int64_t tgt_base,
+                                   int64_t num_targets, const float* wig, const float* radial, float* gx, float* grad_wig,
+                                   float* grad_radial, int64_t num_edges, int64_t num_nodes, int32_t channels, void* stream);
+/* fcb200_gather_rotate_bwd_nodes with the radial gradient as half planes (see fcb200_gather_rotate_bwd_csr_h). */
+int fcb200_gather_rotate_bwd_nodes_h(const float* grad_out, const float* x, const int32_t* src_nodes, const int32_t* src_ptr,
+                                     const int32_t* src_perm, int64_t num_sources, const int32_t* row_ptr, int64_t tgt_base,
+                                     int64_t num_targets, const float* wig, const float* radial, float* gx, float* grad_wig,
+                                     void* grad_radial_hi, void* grad_radial_lo, const float* scale, int64_t num_edges,
+                                     int64_t num_nodes, int32_t channels, void* stream);
+
+/*
  * Backward of fcb200_rotate_back_reduce_fwd: grad_msg = Winv^T grad_out[tgt] (M-major) and
  * grad_winv = sum_c grad_out[tgt] (x) msg on the block entries.  Replaces
  * permute_wigner_inv_edge_to_node_bwd_dx/_bwd_dw kernels (triton/kernels.py:1181, 1334) and

@@ -388,3 +388,57 @@ def test_gather_rotate_backward_radial_gradient_as_half_planes(ops):
     assert torch.equal(gs1, gs0) and torch.equal(gx1, gx0) and torch.equal(gw1, gw0)
     got = (hi.float() + lo.float() / 2048.0) / 256.0
     torch.testing.assert_close(got, gr0, rtol=1e-6, atol=1e-7 * float(gr0.abs().max()))
+
+
+@pytest.mark.parametrize("with_radial", [True, False])
+def test_gather_rotate_backward_with_both_halves_summed_per_node(ops, with_radial):
+    """fcb200_gather_rotate_bwd_nodes(_h) against fcb200_gather_rotate_bwd_csr followed by the segmented sum by source:
+    a sub-range of targets whose sources are scattered over all nodes, some of them several times."""
+    g = torch.Generator().manual_seed(13)
+    n, c = 90, 128
+    deg = torch.randint(0, 9, (n,), generator=g)
+    deg[7] = 0
+    tgt = torch.repeat_interleave(torch.arange(n), deg)
+    e_all = int(tgt.shape[0])
+    src = torch.randint(0, n, (e_all,), generator=g)
+    row_ptr = torch.zeros(n + 1, dtype=torch.int32)
+    row_ptr[1:] = torch.cumsum(deg, 0)
+    n0, n1 = 12, 80
+    e0, e1 = int(row_ptr[n0]), int(row_ptr[n1])
+    e = e1 - e0
+    x = torch.randn(n, 9, c, generator=g).cuda()
+    wig = torch.randn(e, 35, generator=g).cuda()
+    go = (torch.randn(e, 9, 2 * c, generator=g) * 1e-2).cuda()
+    rad = torch.randn(e, 6 * 2 * c, generator=g).cuda() if with_radial else None
+    src_c, tgt_c = src[e0:e1].int().cuda(), tgt[e0:e1].int().cuda()
+    rp = (row_ptr[n0:n1 + 1] - e0).contiguous().cuda()
+    # by-source tables of the run, as the edge block's chunks hold them
+    order = torch.sort(src[e0:e1], stable=True).indices
+    uniq, counts = torch.unique_consecutive(src[e0:e1][order], return_counts=True)
+    sptr = torch.zeros(len(uniq) + 1, dtype=torch.int32)
+    sptr[1:] = torch.cumsum(counts, 0)
+    src_nodes, sptr, perm = uniq.int().cuda(), sptr.cuda(), order.int().cuda()
+    base = torch.randn(n, 9, c, generator=g).cuda()
+    f = lambda *s: torch.empty(*s, device="cuda")  # noqa: E731
+    want, g_src, gw0 = base.clone(), f(e, 9, c), f(e, 35)
+    gr0 = torch.empty_like(rad) if with_radial else None
+    ops.gather_rotate_bwd_csr_(go, x, src_c, tgt_c, rp, n0, wig, rad, g_src, want[n0:n1], gw0, gr0)
+    ops.segment_sum(g_src, sptr, perm, len(uniq), out=want, out_index=src_nodes, accumulate=True)
+    got, gw1 = base.clone(), f(e, 35)
+    gr1 = torch.empty_like(rad) if with_radial else None
+    ops.gather_rotate_bwd_nodes_(go, x, src_nodes, sptr, perm, rp, n0, wig, rad, got, gw1, gr1)
+    torch.testing.assert_close(got, want, rtol=1e-5, atol=1e-5)
+    untouched = torch.ones(n, dtype=torch.bool)
+    untouched[n0:n1] = False
+    untouched[uniq] = False
+    assert torch.equal(got[untouched.cuda()], base[untouched.cuda()])
+    torch.testing.assert_close(gw1, gw0, rtol=1e-5, atol=1e-5)
+    if with_radial:
+        assert torch.equal(gr1, gr0)
+        got_h, gw2 = base.clone(), f(e, 35)
+        hi, lo = (torch.empty(e, 6 * 2 * c, dtype=torch.float16, device="cuda") for _ in range(2))
+        scale = torch.tensor([256.0], device="cuda")
+        ops.gather_rotate_bwd_nodes_h_(go, x, src_nodes, sptr, perm, rp, n0, wig, rad, got_h, gw2, hi, lo, scale)
+        assert torch.equal(got_h, got) and torch.equal(gw2, gw1)
+        back = (hi.float() + lo.float() / 2048.0) / 256.0
+        torch.testing.assert_close(back, gr0, rtol=1e-6, atol=1e-7 * float(gr0.abs().max()))
