@@ -346,6 +346,45 @@ __device__ __forceinline__ void bwd_node_degree(const float* __restrict__ grad_o
     for (int b = 0; b < n; ++b) st4(g_base + (L0 + b) * channels + c0, add4(ld4(g_base + (L0 + b) * channels + c0), gt[b]));
 }
 
+// Degrees 0 and 1 of one node in a single pass over its edges: together they hold fewer registers than the l = 2 block
+// alone, and one pass with four rows in flight per edge hides the latency of the per-edge loads better than two passes
+// with one and three.
+template <bool HAS_RAD, class RadOut, int HALF, bool ACC_W, bool PERM>
+__device__ __forceinline__ void bwd_node_degrees01(const float* __restrict__ grad_out, const float* __restrict__ x_base,
+                                                   const float* __restrict__ wig, const float* __restrict__ radial,
+                                                   float* __restrict__ g_base, float* __restrict__ grad_wig,
+                                                   const RadOut& grad_radial, const int32_t* __restrict__ perm, int eb, int ee,
+                                                   int lane) {
+    constexpr int channels = 128;
+    const int c0 = lane * 4;
+    float4 xv0[1], gt0[1], xv1[3], gt1[3];
+    xv0[0] = ld4(x_base + c0);
+    gt0[0] = f4zero();
+#pragma unroll
+    for (int b = 0; b < 3; ++b) {
+        xv1[b] = ld4(x_base + (1 + b) * channels + c0);
+        gt1[b] = f4zero();
+    }
+    for (int k = eb; k < ee; ++k) {
+        const int64_t e = PERM ? (int64_t)__ldg(perm + k) : (int64_t)k;
+        float w0[1], dw0[1], w1[9], dw1[9];
+        w0[0] = __ldg(wig + e * FCB200_WIG + woff(0));
+        dw0[0] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 9; ++i) {
+            w1[i] = __ldg(wig + e * FCB200_WIG + woff(1) + i);
+            dw1[i] = 0.f;
+        }
+        bwd_degree_rows<0, HAS_RAD, RadOut>(grad_out, radial, grad_radial, e, HALF, channels, c0, w0, xv0, gt0, dw0);
+        bwd_degree_rows<1, HAS_RAD, RadOut>(grad_out, radial, grad_radial, e, HALF, channels, c0, w1, xv1, gt1, dw1);
+        reduce_block<1, ACC_W>(dw0, lane, grad_wig + e * FCB200_WIG + woff(0));
+        reduce_block<9, ACC_W>(dw1, lane, grad_wig + e * FCB200_WIG + woff(1));
+    }
+    st4(g_base + c0, add4(ld4(g_base + c0), gt0[0]));
+#pragma unroll
+    for (int b = 0; b < 3; ++b) st4(g_base + (1 + b) * channels + c0, add4(ld4(g_base + (1 + b) * channels + c0), gt1[b]));
+}
+
 template <bool HAS_RAD, class RadOut>
 __global__ void __launch_bounds__(kWarpsPerBlock* kWarp, 2)
     gather_rotate_bwd_tgt_kernel(const float* __restrict__ grad_out, const float* __restrict__ x, const int32_t* __restrict__ row_ptr,
@@ -361,8 +400,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp, 2)
         if (eb == ee) continue;
         const float* x_base = x + (tgt_base + n) * 9LL * 128;
         float* g_base = gx_tgt + n * 9LL * 128;
-        bwd_node_degree<0, HAS_RAD, RadOut, 1, true, false>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, nullptr, eb, ee, lane);
-        bwd_node_degree<1, HAS_RAD, RadOut, 1, true, false>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, nullptr, eb, ee, lane);
+        bwd_node_degrees01<HAS_RAD, RadOut, 1, true, false>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, nullptr, eb, ee, lane);
         bwd_node_degree<2, HAS_RAD, RadOut, 1, true, false>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, nullptr, eb, ee, lane);
     }
 }
@@ -387,8 +425,7 @@ __global__ void __launch_bounds__(kWarpsPerBlock* kWarp, 2)
         const int64_t node = src_nodes[u];
         const float* x_base = x + node * 9LL * 128;
         float* g_base = gx + node * 9LL * 128;
-        bwd_node_degree<0, HAS_RAD, RadOut, 0, false, true>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, src_perm, eb, ee, lane);
-        bwd_node_degree<1, HAS_RAD, RadOut, 0, false, true>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, src_perm, eb, ee, lane);
+        bwd_node_degrees01<HAS_RAD, RadOut, 0, false, true>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, src_perm, eb, ee, lane);
         bwd_node_degree<2, HAS_RAD, RadOut, 0, false, true>(grad_out, x_base, wig, radial, g_base, grad_wig, grad_radial, src_perm, eb, ee, lane);
     }
 }
