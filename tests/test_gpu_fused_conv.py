@@ -106,3 +106,26 @@ def test_edge_block_is_the_same_with_and_without_the_fused_launches(ops, variant
     for e1, f1 in results[1:]:
         assert abs(float(e1[0] - e0[0])) <= 2e-6 * abs(float(e0[0]))
         assert float((f1 - f0).abs().max()) <= 2e-6
+
+
+def test_edge_block_is_the_same_with_per_node_and_per_edge_source_gradients(ops):
+    """Forces with the source half of the gather backward summed per source node inside the kernel (default) and with
+    per-edge rows followed by the segmented sum (the form ``bench.py --edge-source-sums`` measures against)."""
+    from fairchem_b200 import backbone as B
+    from fairchem_b200 import synthetic, weights
+
+    data = synthetic.bcc_alloy((5, 5, 5), seed=3).to("cuda")
+    sd = weights.random_init_state_dict(weights.UMA_S, 0)
+    bb, head = B.build_model(weights.UMA_S, sd, device="cuda", edge_chunk_size=2048)  # several chunks per layer
+    results = []
+    for node_sums in (True, False):
+        B._GemmState.node_sums = node_sums
+        try:
+            d = data.clone()
+            out = head(d, bb(d))
+            results.append((out["energy"].clone(), out["forces"].clone()))
+        finally:
+            B._GemmState.node_sums = True
+    (e0, f0), (e1, f1) = results
+    assert abs(float(e1[0] - e0[0])) <= 1e-9 * abs(float(e0[0]))  # the forward pass is the same code
+    assert float((f1 - f0).abs().max()) <= 2e-6
